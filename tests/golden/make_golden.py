@@ -1,0 +1,248 @@
+"""Generate the golden fixtures in this directory by RUNNING THE REFERENCE.
+
+Usage (only where the reference tree is available):
+
+    PYTHONPATH=<reference root> python tests/golden/make_golden.py
+
+The reference (pure Python + PyTorch) is imported, its modules are built on CPU
+with a fixed seed, weights are rounded to bf16-representable values (so that a
+bf16 device path can start from identical bits; they are stored as raw bf16 bit
+patterns, uint16), the reference's own fp32 eval forward is run, and inputs,
+weights and outputs are written as ``.npz`` files.  Nothing here is imported by
+the package; the fixtures are read by ``tests/``.
+
+No dataset or public benchmark is involved: inputs are seeded synthetic tensors,
+as in the reference's own benchmarks.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def bf16_round_(t: torch.Tensor) -> torch.Tensor:
+    t.data.copy_(t.data.to(torch.bfloat16).to(t.dtype))
+    return t
+
+
+def to_bits(t: torch.Tensor) -> np.ndarray:
+    """fp32 tensor holding bf16-representable values -> uint16 bit patterns."""
+    b = t.detach().to(torch.bfloat16).contiguous().view(torch.int16).numpy().astype(np.uint16)
+    return b
+
+
+def f32(t: torch.Tensor) -> np.ndarray:
+    return t.detach().to(torch.float32).contiguous().numpy()
+
+
+def save(name: str, **arrs) -> None:
+    path = os.path.join(HERE, name)
+    np.savez_compressed(path, **arrs)
+    print(f"wrote {path}: {os.path.getsize(path) / 1e6:.2f} MB")
+
+
+# ----------------------------------------------------------------------------
+def gen_fused_ops() -> None:
+    from hydra.kernels import fused_ops as fo
+    from hydra.layers.common import AdaRMSNorm, RMSNorm
+
+    g = torch.Generator().manual_seed(2)
+    out = {}
+    # RoPE, head_dim 32 and 16, 4-D tables as the attention module passes them
+    for hd in (16, 32):
+        x = torch.randn(2, 3, 40, hd, generator=g)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2).float() / hd))
+        ang = torch.outer(torch.arange(64, dtype=torch.float32), inv)
+        cos, sin = ang.cos()[None, None], ang.sin()[None, None]
+        out[f"rope{hd}_x"] = f32(x)
+        out[f"rope{hd}_cos"] = f32(cos)
+        out[f"rope{hd}_sin"] = f32(sin)
+        out[f"rope{hd}_y"] = f32(fo._rope_pytorch(x, cos, sin))
+    q = torch.randn(2, 8, 24, 32, generator=g)
+    k = torch.randn(2, 2, 24, 32, generator=g)
+    qn, kn = fo._qk_norm_pytorch(q, k, 5.0, 1.7)
+    out.update(qkn_q=f32(q), qkn_k=f32(k), qkn_qo=f32(qn), qkn_ko=f32(kn))
+    gate = torch.randn(37, 264, generator=g) * 3
+    up = torch.randn(37, 264, generator=g)
+    out.update(swiglu_gate=f32(gate), swiglu_up=f32(up), swiglu_y=f32(fo._swiglu_pytorch(gate, up)))
+    x = torch.randn(19, 1024, generator=g)
+    w = 1.0 + 0.02 * torch.randn(1024, generator=g)
+    out.update(rms_x=f32(x), rms_w=f32(w), rms_y=f32(fo._rms_norm_pytorch(x, w, 1e-6)))
+    n1 = RMSNorm(1024)
+    n1.weight.data.copy_(w)
+    out["rms_module_y"] = f32(n1(x))
+    n2 = AdaRMSNorm(1024)
+    n2.weight.data.copy_(w)
+    out["ada_y"] = f32(n2(x))
+    save("fused_ops.npz", **out)
+
+
+# ----------------------------------------------------------------------------
+def gen_attention(name: str, dim: int, H: int, KV: int, B: int, S: int, seed: int,
+                  temperature: float | None = None) -> None:
+    from hydra.attention import build_hybrid_attention_module
+    import hydra.attention.backends.ccgqa.attention as attn_mod
+
+    torch.manual_seed(seed)
+    m = build_hybrid_attention_module("ccgqa", dim=dim, n_heads=H, n_kv_heads=KV, max_seq_len=S,
+                                      compression_factor=4, attention_kwargs={})
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() >= 2:
+                torch.nn.init.xavier_uniform_(p)
+        if temperature is not None:
+            m.key_temperature.fill_(temperature)
+        for p in m.parameters():
+            bf16_round_(p)
+    m.eval()
+    g = torch.Generator().manual_seed(seed + 100)
+    x = torch.randn(B, S, dim, generator=g).to(torch.bfloat16).to(torch.float32)
+
+    captured = {}
+    real_sdpa = F.scaled_dot_product_attention
+
+    def tap(q, k, v, *a, **kw):
+        captured["q"], captured["k"], captured["v"] = q.clone(), k.clone(), v.clone()
+        o = real_sdpa(q, k, v, *a, **kw)
+        captured["o"] = o.clone()
+        return o
+
+    attn_mod.F.scaled_dot_product_attention = tap
+    try:
+        with torch.no_grad():
+            y = m(x)
+            qkv = m.qkv_proj(x)
+    finally:
+        attn_mod.F.scaled_dot_product_attention = real_sdpa
+    G = H // KV
+    arrs = dict(
+        meta=np.array([dim, H, KV, B, S], dtype=np.int64),
+        x=to_bits(x), y=f32(y), qkv=f32(qkv),
+        q=f32(captured["q"]), k=f32(captured["k"][:, ::G]), v=f32(captured["v"][:, ::G]),
+        o=f32(captured["o"]),
+    )
+    for kname, t in m.state_dict().items():
+        arrs["w:" + kname] = to_bits(t) if t.dim() >= 2 else f32(t)
+    save(name, **arrs)
+
+
+# ----------------------------------------------------------------------------
+def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: int, mlp_ratio: float,
+              B: int, S: int, cap: float, seed: int) -> None:
+    from hydra.model.framework import HydraModel
+
+    torch.manual_seed(seed)
+    m = HydraModel(vocab_size=vocab, dim=dim, n_mor_blocks=NB, recursions_per_block=R, n_heads=H,
+                   n_kv_heads=KV, compression_factor=4, mlp_ratio=mlp_ratio, max_seq_len=S,
+                   mod_capacity=cap)
+    g = torch.Generator().manual_seed(seed + 1)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith("norm1.weight") or n.endswith("norm2.weight") or n.endswith("final_norm.weight") \
+                    or n == "norm.weight":
+                p.mul_(1.0 + 0.1 * torch.randn(p.shape, generator=g))
+            if "recursion_bias" in n:
+                p.copy_(0.05 * torch.randn(p.shape, generator=g))
+            if "router.weight" in n:
+                p.mul_(10.0)
+        for p in m.parameters():
+            bf16_round_(p)
+    m.eval()
+    m.set_global_step(10 ** 6)   # MoD hard routing is off in eval until the step passes its warm-up
+    ids = torch.randint(0, vocab, (B, S), generator=torch.Generator().manual_seed(seed + 2))
+    ids[0, 0] = vocab + 5        # out-of-range ids are clamped by the reference
+    ids[0, 1] = -3
+
+    mod_calls = []
+    hooks = []
+    for li, layer in enumerate(m.layers):
+        if layer.mod_mlp_wrapper is not None:
+            def hook(_mod, _inp, outp, li=li):
+                mod_calls.append((li, outp[1].clone(), outp[2].clone()))
+            hooks.append(layer.mod_mlp_wrapper.mod_router.register_forward_hook(hook))
+    block_out = []
+    for layer in m.layers:
+        hooks.append(layer.register_forward_hook(lambda _m, _i, o: block_out.append(o.clone())))
+    with torch.no_grad():
+        logits = m(ids)
+    depths = [layer._last_depths.clone() for layer in m.layers]
+    rlogits = [layer._last_router_logits.clone() for layer in m.layers]
+    for h in hooks:
+        h.remove()
+
+    arrs = dict(
+        meta=np.array([vocab, dim, NB, R, H, KV, B, S], dtype=np.int64),
+        cap=np.array([cap], dtype=np.float64),
+        ffn_hidden=np.array([m.layers[0].mlp.down.weight.shape[1]], dtype=np.int64),
+        ids=ids.numpy(), logits=f32(logits),
+    )
+    for i, d in enumerate(depths):
+        arrs[f"depths:{i}"] = d.numpy().astype(np.int32)
+        arrs[f"router_logits:{i}"] = f32(rlogits[i])
+        arrs[f"block_out:{i}"] = f32(block_out[i])
+    per_layer = {}
+    for li, idx, sc in mod_calls:
+        r = per_layer.get(li, 0)
+        per_layer[li] = r + 1
+        arrs[f"mod_idx:{li}:{r}"] = torch.sort(idx, dim=1)[0].numpy().astype(np.int32)
+        arrs[f"mod_scores:{li}:{r}"] = f32(sc)
+    for kname, t in m.state_dict().items():
+        if kname == "output.weight" or "_aux_loss" in kname or ".mod_mlp_wrapper.mlp." in kname:
+            continue   # tied / alias / bookkeeping tensors
+        arrs["w:" + kname] = to_bits(t) if t.dim() >= 2 and t.numel() > 4096 else f32(t)
+
+    # fixed-depth path (adaptive=False) and min_depth=1 on the same weights
+    for layer in m.layers:
+        layer.adaptive = False
+    with torch.no_grad():
+        arrs["logits_fixed"] = f32(m(ids))
+    for layer in m.layers:
+        layer.adaptive = True
+        object.__setattr__(layer.mor_router.config, "min_depth", 1)   # frozen dataclass
+    with torch.no_grad():
+        arrs["logits_min1"] = f32(m(ids))
+    for i, layer in enumerate(m.layers):
+        arrs[f"depths_min1:{i}"] = layer._last_depths.numpy().astype(np.int32)
+    # the reference's own bf16 path (whole module cast, as its bf16 benchmark does) on the same inputs
+    for layer in m.layers:
+        object.__setattr__(layer.mor_router.config, "min_depth", 0)
+    mb = m.to(torch.bfloat16)   # in place, after every fp32 run (its routers do not survive deepcopy)
+    mb.eval()
+    mb.set_global_step(10 ** 6)
+    with torch.no_grad():
+        lb = mb(ids).float()
+    err = (lb - logits)
+    arrs["ref_bf16_maxabs"] = np.array([float(err.abs().max())])
+    arrs["ref_bf16_rel_l2"] = np.array([float(err.norm() / logits.norm())])
+    agree = [float((mb.layers[i]._last_depths == depths[i]).float().mean()) for i in range(NB)]
+    arrs["ref_bf16_depth_agree"] = np.array(agree)
+
+    save(name, **arrs)
+
+
+if __name__ == "__main__":
+    try:
+        import hydra  # noqa: F401
+    except Exception as e:  # pragma: no cover
+        sys.exit(f"the reference package 'hydra' must be importable (set PYTHONPATH): {e}")
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    gen_fused_ops()
+    # config-2 shapes (dim 1024, 8q/2kv, hd 32) at a short sequence; temperature 1.0 as BASELINE config 2
+    gen_attention("ccgqa_hd32.npz", 1024, 8, 2, 1, 80, seed=1, temperature=1.0)
+    # config-1 shapes (dim 512, 8q/2kv, hd 16), default temperature sqrt(hd)
+    gen_attention("ccgqa_hd16.npz", 512, 8, 2, 2, 72, seed=3)
+    # odd KV count: the value-shift split falls inside a head (100M preset: 12q/3kv)
+    gen_attention("ccgqa_kv3.npz", 768, 12, 3, 1, 40, seed=4)
+    # n_groups == 1 branch of the QK-mean coupling (H == KV)
+    gen_attention("ccgqa_mha.npz", 256, 4, 4, 1, 33, seed=6)
+    # whole model, 4 blocks so that blocks 1 and 2 carry MoD
+    gen_model("model_hd16.npz", vocab=384, dim=256, NB=4, R=3, H=4, KV=2, mlp_ratio=1.0,
+              B=2, S=128, cap=0.75, seed=0)
+    gen_model("model_hd32.npz", vocab=384, dim=256, NB=3, R=4, H=2, KV=1, mlp_ratio=1.0,
+              B=2, S=96, cap=0.5, seed=5)

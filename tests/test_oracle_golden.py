@@ -1,0 +1,115 @@
+"""Pins the CPU oracle to the reference: every function of oracle/hydra_oracle.py is
+checked against outputs of the reference's own code (fixtures in tests/golden/, made by
+tests/golden/make_golden.py).  fp32, tolerance 2e-6 relative to the output scale; routing
+index lists and depths must be identical."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import hydra_oracle as O
+from tests import golden_io as G
+
+
+def close(a: torch.Tensor, b: np.ndarray, tol=2e-6):
+    b = torch.from_numpy(b)
+    scale = max(1.0, float(b.abs().max()))
+    err = float((a - b).abs().max())
+    assert err <= tol * scale, f"max abs err {err:.3e} (scale {scale:.3g})"
+
+
+def test_fused_op_semantics():
+    fx = G.load("fused_ops.npz")
+    t = lambda k: torch.from_numpy(fx[k])
+    for hd in (16, 32):
+        close(O.rope(t(f"rope{hd}_x"), t(f"rope{hd}_cos"), t(f"rope{hd}_sin")), fx[f"rope{hd}_y"])
+        c2, s2 = O.rope_tables(64, hd)
+        close(c2, fx[f"rope{hd}_cos"][0, 0], 1e-7)
+        close(s2, fx[f"rope{hd}_sin"][0, 0], 1e-7)
+    qo, ko = O.qk_norm(t("qkn_q"), t("qkn_k"), 5.0, 1.7)
+    close(qo, fx["qkn_qo"]); close(ko, fx["qkn_ko"])
+    q2, k2 = O.qk_norm_rsqrt(t("qkn_q"), t("qkn_k"), 5.0, 1.7)   # device formula differs only by its eps
+    close(q2, fx["qkn_qo"], 1e-5); close(k2, fx["qkn_ko"], 1e-5)
+    close(O.swiglu(t("swiglu_gate"), t("swiglu_up")), fx["swiglu_y"])
+    close(O.rms_norm(t("rms_x"), t("rms_w")), fx["rms_y"])
+    close(O.rms_norm(t("rms_x"), t("rms_w")), fx["rms_module_y"])
+    close(O.ada_rms_norm(t("rms_x"), t("rms_w")), fx["ada_y"])
+
+
+@pytest.mark.parametrize("name", ["ccgqa_hd32.npz", "ccgqa_hd16.npz", "ccgqa_kv3.npz", "ccgqa_mha.npz"])
+def test_ccgqa_attention(name):
+    fx, cfg, w = G.attention_fixture(name)
+    x = G.tensor(fx["x"])
+    B, S, _ = x.shape
+    qkv = x @ w["attn.qkv_proj.weight"].T
+    close(qkv, fx["qkv"])
+    cos, sin = O.rope_tables(S, cfg.head_dim)
+    q, k, v = O.ccgqa_pre_attention(torch.from_numpy(fx["qkv"]), w, "attn.", cfg, cos, sin)
+    close(q, fx["q"]); close(k, fx["k"]); close(v, fx["v"])
+    o = O.causal_gqa_attention(torch.from_numpy(fx["q"]), torch.from_numpy(fx["k"]), torch.from_numpy(fx["v"]))
+    close(o, fx["o"])
+    close(O.ccgqa_forward(x, w, "attn.", cfg), fx["y"])
+
+
+@pytest.mark.parametrize("name", ["model_hd16.npz", "model_hd32.npz"])
+def test_model_forward_and_routing(name):
+    fx, cfg, w = G.model_fixture(name)
+    ids = torch.from_numpy(fx["ids"])
+    taps = O.RoutingTaps()
+    logits = O.model_forward(ids, w, cfg, taps=taps)
+    close(logits, fx["logits"], 5e-6)
+    n_mod = 0
+    for i in range(cfg.n_mor_blocks):
+        assert np.array_equal(taps.depths[i].numpy().astype(np.int32), fx[f"depths:{i}"]), f"depths block {i}"
+        # the reference keeps the squashed logit 3*tanh(l/2) (mixture_of_recursions.py:268-269)
+        close(torch.tanh(taps.router_logits[i] / 2.0) * 3.0, fx[f"router_logits:{i}"], 5e-6)
+        close(taps.block_out[i], fx[f"block_out:{i}"], 5e-6)
+        for r in range(cfg.recursions_per_block):
+            key = f"mod_idx:{i}:{r}"
+            if cfg.block_has_mod(i):
+                assert np.array_equal(taps.mod_indices[(i, r)].numpy().astype(np.int32), fx[key]), key
+                close(taps.mod_scores[(i, r)], fx[f"mod_scores:{i}:{r}"], 5e-6)
+                n_mod += 1
+            else:
+                assert key not in fx
+    assert n_mod == (cfg.n_mor_blocks - 2) * cfg.recursions_per_block
+    # depth spread: the fixture exercises more than one exit depth
+    assert len(np.unique(np.concatenate([fx[f"depths:{i}"].ravel() for i in range(cfg.n_mor_blocks)]))) >= 2
+
+
+@pytest.mark.parametrize("name", ["model_hd16.npz", "model_hd32.npz"])
+def test_model_fixed_depth_and_min_depth(name):
+    fx, cfg, w = G.model_fixture(name)
+    ids = torch.from_numpy(fx["ids"])
+    cfg.adaptive = False
+    close(O.model_forward(ids, w, cfg), fx["logits_fixed"], 5e-6)
+    cfg.adaptive = True
+    cfg.mor_min_depth = 1
+    taps = O.RoutingTaps()
+    close(O.model_forward(ids, w, cfg, taps=taps), fx["logits_min1"], 5e-6)
+    for i in range(cfg.n_mor_blocks):
+        assert np.array_equal(taps.depths[i].numpy().astype(np.int32), fx[f"depths_min1:{i}"])
+
+
+def test_forced_routing_replay_is_identity():
+    """Replaying a run's own routing decisions reproduces it exactly."""
+    fx, cfg, w = G.model_fixture("model_hd16.npz")
+    ids = torch.from_numpy(fx["ids"])
+    taps = O.RoutingTaps()
+    a = O.model_forward(ids, w, cfg, taps=taps)
+    b = O.model_forward(ids, w, cfg, forced=taps)
+    assert torch.equal(a, b)
+
+
+def test_mod_k_and_select_edges():
+    assert O.mod_k(2048, 0.75) == 1536 and O.mod_k(512, 0.75) == 384
+    assert O.mod_k(3, 0.0) == 1 and O.mod_k(5, 2.0) == 5 and O.mod_k(1, 0.75) == 1
+    s = torch.tensor([[0.1, 0.9, -1.0, 0.5, 0.7]])
+    assert O.mod_select(s, 0.6).tolist() == [[1, 3, 4]]
+
+
+def test_mor_depths_rounding_half_even():
+    # sigmoid(0) * 3 = 1.5 -> 2 (half to even); probs*2 = 1.0 stays
+    d, p = O.mor_depths(torch.tensor([0.0, -50.0, 50.0]), 4)
+    assert d.tolist() == [2, 0, 3]
+    d1, _ = O.mor_depths(torch.tensor([-50.0, 50.0]), 4, min_depth=1)
+    assert d1.tolist() == [1, 3]
