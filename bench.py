@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""Headline benchmark: HYDRA-250M bf16 inference prefill throughput (tokens/s) on N B200s of one node.
+
+    python bench.py --gpus 1 --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the CPU arm: the oracle port of the reference's eager forward
+
+Workload (BASELINE.json configs[3]): dim 1024, 10 MoR blocks x 4 recursions, CCGQA 4x compression with 8 query /
+2 KV heads (head_dim 32), SwiGLU hidden 2816, MoD top-k at 75% capacity in the interior blocks, vocab 50257, tied
+output projection; batch 32 x 2048 synthetic token ids PER GPU (weak scaling: every rank is a full replica working
+on its own sequences; sequences never cross GPUs and there is no collective inside the timed region).  Weights are
+seeded random-init with the reference's distributions (no checkpoint or dataset is involved).
+
+One step = one full forward (embedding -> 10 blocks -> final norm -> all 65536 x 50257 logits).
+  value  tokens/s with the ids already resident in HBM (CUDA events, max over ranks)
+  e2e    the same through the public call HydraB200Model.prefill(): pinned host ids -> device, forward,
+         last-position logits -> host, copies inside the timed region
+  roofline  the dominant kernel (tcgen05 gate_up GEMM with the SwiGLU epilogue): FLOPs actually routed to it
+            divided by its summed launch time, both measured in the timed steps with CUDA events recorded by
+            the executor around every launch
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "hydra_250m_prefill_tokens_per_s"
+ARCH = dict(vocab_size=50257, dim=1024, n_mor_blocks=10, recursions_per_block=4, n_heads=8, n_kv_heads=2,
+            compression_factor=4, mlp_ratio=2.67, mod_capacity=0.75)
+SEQ = 2048
+SEED = 0
+
+
+def workload_config(batch_per_gpu: int, n_gpus: int) -> dict:
+    return {
+        "workload": "BASELINE configs[3]: HYDRA-250M prefill, dim 1024, 10 MoR blocks x 4 recursions, CCGQA 8q/2kv "
+                    "(head_dim 32), SwiGLU 2816, MoD top-k 0.75, vocab 50257, all logits computed",
+        "batch_per_gpu": batch_per_gpu, "global_batch": batch_per_gpu * n_gpus, "seq_len": SEQ,
+        "parallelism": f"replica-per-GPU x{n_gpus}, batch sharded by sequence, no data-path collective",
+        "weights": f"seeded random-init (seed {SEED}), reference init distributions",
+        "l2": "working set (weights 0.3 GB + activations > 1 GB + logits 6.6 GB) far exceeds the 126 MB L2; no flush needed",
+    }
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); smax.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_forward_tokens_per_s(n_seq: int, steps: int, warmup: int, state_dict=None) -> tuple[float, float, int]:
+    """The oracle port of the reference's eager fp32 forward, all host threads; returns (tok/s, s/step, threads)."""
+    from oracle import hydra_oracle as O
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(threads)
+    cfg = O.HydraConfig(vocab_size=ARCH["vocab_size"], dim=ARCH["dim"], n_mor_blocks=ARCH["n_mor_blocks"],
+                        recursions_per_block=ARCH["recursions_per_block"], n_heads=ARCH["n_heads"],
+                        n_kv_heads=ARCH["n_kv_heads"], max_seq_len=SEQ, mod_capacity=ARCH["mod_capacity"])
+    w = O.init_params(cfg, seed=SEED) if state_dict is None else {k: v.float().cpu() for k, v in state_dict.items()}
+    ids = torch.randint(0, ARCH["vocab_size"], (n_seq, SEQ), generator=torch.Generator().manual_seed(SEED))
+    with torch.no_grad():
+        for _ in range(warmup):
+            O.model_forward(ids, w, cfg)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            O.model_forward(ids, w, cfg)
+        dt = (time.perf_counter() - t0) / max(1, steps)
+    return n_seq * SEQ / dt, dt, threads
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_seq = 1
+    tps, dt, threads = cpu_forward_tokens_per_s(n_seq, args.steps, min(args.warmup, 1))
+    cfg = workload_config(args.batch, args.gpus)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
+                         "sample": f"{n_seq} sequence x {SEQ} tokens of the same workload per step "
+                                   "(CPU port of the reference's eager fp32 forward; the Python reference itself "
+                                   "cannot travel to the GPU box)"},
+        "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def routed_flops(records, mlp_rows, T: int) -> dict:
+    """FLOPs per kernel kind with the rows each launch really processed (device-counted launches use taps)."""
+    fl: dict = {}
+    for r in records:
+        kd = r["kind"]
+        if kd in ("gemm_gate_up", "gemm_down"):
+            m = int(mlp_rows[r["block"]][r["rec"]])
+        else:
+            m = r["m"]
+        if kd.startswith("gemm"):
+            f = 2.0 * m * r["n"] * r["k"]
+        elif kd == "attention":
+            f = 4.0 * T * r["n"] * (r["k"] + 1) / 2.0
+        else:
+            f = 0.0
+        fl[kd] = fl.get(kd, 0.0) + f
+    return fl
+
+
+def run_ours(args) -> None:
+    from hydra_b200.model import HydraB200Model, random_state_dict
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback "
+                         "(use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+
+    sd = random_state_dict(seed=SEED, device=dev, **ARCH)
+    model = HydraB200Model(sd, n_heads=ARCH["n_heads"], n_kv_heads=ARCH["n_kv_heads"], max_seq_len=SEQ,
+                           mod_capacity=ARCH["mod_capacity"], device=dev)
+    # every rank draws its own sequences (seed offset by rank): a sharded global batch of world*B sequences
+    ids_host = torch.randint(0, ARCH["vocab_size"], (B, SEQ),
+                             generator=torch.Generator().manual_seed(SEED + 1 + rank)).pin_memory()
+    ids = ids_host.to(dev)
+    T = B * SEQ
+    model.enable_profile(2048)
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    # routing statistics of this workload (deterministic): rows per (block, recursion)
+    model(ids, taps=True)
+    torch.cuda.synchronize(dev)
+    mlp_rows = model.last_taps.mlp_rows.cpu().tolist()
+    model.read_profile()
+    for _ in range(W):
+        model(ids)
+    sync_all()
+    model.read_profile()
+
+    # ---- timed region: K forwards, ids resident in HBM
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    per_step_records = []
+    ev0.record()
+    for _ in range(K):
+        model(ids)
+    ev1.record()
+    sync_all()
+    ms_total = ev0.elapsed_time(ev1)
+    records = model.read_profile()
+    launches_per_step = len(records) // max(1, K)
+    model.check_device_errors()
+
+    # ---- e2e: pinned host ids -> device, forward, last-position logits -> host, every step
+    out_host = torch.empty((B, ARCH["vocab_size"]), dtype=torch.bfloat16).pin_memory()
+    model.disable_profile()
+    for _ in range(2):
+        model.prefill(ids_host, out_host)
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        model.prefill(ids_host, out_host)
+    e1.record()
+    sync_all()
+    ms_e2e = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler is not None else None
+
+    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = float(t[0]), float(t[1])
+    tokens_all = world * T * K
+    value = tokens_all / (ms_total * 1e-3)
+    e2e = tokens_all / (ms_e2e * 1e-3)
+
+    # outside the timed region: gather the last-position logits of every rank (NCCL over NVLink)
+    if dist is not None:
+        last = model(ids)[:, -1, :].contiguous()
+        gathered = torch.empty((world * B, ARCH["vocab_size"]), dtype=last.dtype, device=dev)
+        dist.all_gather_into_tensor(gathered, last)
+        torch.cuda.synchronize(dev)
+        assert torch.isfinite(gathered.float()).all()
+
+    if rank == 0:
+        peaks, peak_src = measured_peaks()
+        by_kind: dict = {}
+        for r in records:
+            d = by_kind.setdefault(r["kind"], {"launches": 0, "ms": 0.0})
+            d["launches"] += 1
+            d["ms"] += r["ms"]
+        tot = sum(d["ms"] for d in by_kind.values()) or 1.0
+        fl = routed_flops(records, mlp_rows, T)
+        breakdown = {k: {"launches_per_step": d["launches"] // K, "ms_per_step": d["ms"] / K, "share": d["ms"] / tot,
+                         "tflops": (fl.get(k, 0.0) / (d["ms"] * 1e-3) / 1e12) if fl.get(k) else None}
+                     for k, d in sorted(by_kind.items(), key=lambda kv: -kv[1]["ms"])}
+        dom = "gemm_gate_up"
+        dom_ms = by_kind.get(dom, {"ms": 0.0})["ms"]
+        achieved = fl.get(dom, 0.0) / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else 0.0
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        all_gemm_fl = sum(v for k, v in fl.items())
+        routed_per_token = all_gemm_fl / (T * K)
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(B, world),
+            "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": world * B * SEQ * 8,
+                    "d2h_bytes_per_step": world * B * ARCH["vocab_size"] * 2, "ms_per_step": ms_e2e / K,
+                    "api": "HydraB200Model.prefill(pinned int64 ids [B,S]) -> last-position logits [B,V] bf16 on the host"},
+            "gpu_launches": launches_per_step * K,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<256> (gate_up + SwiGLU epilogue)",
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
+                         "peak_source": f"bf16_tflops_sustained, {peak_src}", "traffic": None,
+                         "launches_per_step": by_kind.get(dom, {"launches": 0})["launches"] // K},
+            "model_tflops": {"routed_flops_per_token": routed_per_token,
+                             "dense_flops_per_token": 823.4e6,
+                             "achieved_routed": routed_per_token * T * K / (ms_total * 1e-3) / 1e12 / 1.0,
+                             "frac_of_sustained_peak_routed": routed_per_token * T * K / (ms_total * 1e-3) / 1e12 / peak},
+            "breakdown": breakdown, "mlp_rows": mlp_rows, "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cpu_sd = {k: v.to(torch.bfloat16).float().cpu() for k, v in sd.items()}
+            tps, dt, threads = cpu_forward_tokens_per_s(1, 1, 0, cpu_sd)
+            line["cpu_baseline"] = {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
+                                    "sample": f"1 sequence x {SEQ} tokens of the same workload and weights, one timed "
+                                              f"forward ({dt:.1f} s), CPU port of the reference's eager fp32 forward"}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=32, help="sequences per GPU")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,17 @@
+"""hydra_b200 - B200 (sm_100a) implementation of HYDRA's inference forward hot path.
+
+Public surface (mirrors the reference's names for this path):
+
+* ``hydra_b200.kernels``   - ``fused_rope``, ``fused_qk_norm``, ``fused_swiglu``, ``fused_rms_norm`` and the
+  kernel-status helpers (reference: ``hydra.kernels``)
+* ``hydra_b200.attention`` - ``build_hybrid_attention_module``, registry helpers, ``CCGQAAttention``
+  (reference: ``hydra.attention``)
+* ``hydra_b200.model``     - ``HydraB200Model``: whole-model eval forward from a reference ``state_dict``
+* ``hydra_b200.install``   - ``install()`` rebinds the reference's module-level names to this package
+
+All compute runs in the CUDA extension ``libhydra_b200.so`` (C ABI in ``include/hydra_b200.h``); there is no
+CPU or PyTorch fallback.
+"""
+__version__ = "0.1.0"
+
+__all__ = ["kernels", "attention", "model", "install", "__version__"]

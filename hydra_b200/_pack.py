@@ -1,0 +1,134 @@
+"""Weight preparation shared by the attention module and the whole-model executor: reference ``state_dict``
+tensors -> the device layouts the kernels read (bf16 GEMM operands, repacked conv weights, interleaved
+gate_up rows, fp32 norm gains / router vectors / RoPE tables), plus the ctypes structs that point at them."""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from . import _lib
+
+Tensor = torch.Tensor
+
+
+def rope_tables(max_seq_len: int, head_dim: int, device, theta: float = 10000.0):
+    """fp32 cos/sin [max_seq_len, head_dim/2], computed exactly as the reference builds its cache
+    (hydra/attention/backends/ccgqa/attention.py:160-185): on the CPU in fp32, then moved."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2).float() / head_dim))
+    ang = torch.outer(torch.arange(max_seq_len, dtype=torch.float32), inv)
+    return ang.cos().to(device).contiguous(), ang.sin().to(device).contiguous()
+
+
+def _bf16(t: Tensor, device) -> Tensor:
+    return t.detach().to(device=device, dtype=torch.bfloat16).contiguous()
+
+
+def _f32(t: Tensor, device) -> Tensor:
+    return t.detach().to(device=device, dtype=torch.float32).contiguous()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def repack_conv(w: Tensor, device) -> Tensor:
+    """Conv1d weight [C_out, C_in/groups, 3] -> bf16 [C_out, 3*C_in/groups], (co, j*cin+ci) = w[co, ci, j]."""
+    src = _bf16(w, device)
+    co, ci, ks = src.shape
+    if ks != 3:
+        raise NotImplementedError(f"conv kernel size {ks}: the fused kernel is built for kernel size 3")
+    out = torch.empty((co, 3 * ci), dtype=torch.bfloat16, device=device)
+    _lib.check(_lib.lib().hb200_repack_conv_weight(src.data_ptr(), out.data_ptr(), co, ci, _stream(device)),
+               "repack_conv_weight")
+    return out
+
+
+def interleave_gate_up(w: Tensor, device) -> Tensor:
+    """gate_up.weight [2F, D] -> bf16 rows interleaved in groups of 8 (8 gate rows, 8 up rows, ...)."""
+    src = _bf16(w, device)
+    F2, K = src.shape
+    out = torch.empty_like(src)
+    _lib.check(_lib.lib().hb200_interleave_gate_up(src.data_ptr(), out.data_ptr(), F2 // 2, K, _stream(device)),
+               "interleave_gate_up")
+    return out
+
+
+class PackedBlock:
+    """Device tensors of one HydraMoRBlock (kept alive here) and the matching C struct."""
+
+    def __init__(self, sd: Dict[str, Tensor], pre: str, device, *, attention_only: bool = False):
+        a = pre if attention_only else pre + "attention."
+        t: Dict[str, Optional[Tensor]] = {}
+        t["w_qkv"] = _bf16(sd[a + "qkv_proj.weight"], device)
+        t["w_o"] = _bf16(sd[a + "o_proj.weight"], device)
+        t["w1_qk"] = torch.cat([repack_conv(sd[a + "q_conv.conv1.weight"], device),
+                                repack_conv(sd[a + "k_conv.conv1.weight"], device)], dim=0).contiguous()
+        t["w2_q"] = repack_conv(sd[a + "q_conv.conv2.weight"], device)
+        t["w2_k"] = repack_conv(sd[a + "k_conv.conv2.weight"], device)
+        t["key_temperature"] = _f32(sd[a + "key_temperature"], device).reshape(1)
+        for k in ("norm1_w", "norm2_w", "final_norm_w", "w_gate_up", "w_down", "mor_w", "mor_b", "rec",
+                  "mod_w", "mod_b"):
+            t[k] = None
+        if not attention_only:
+            t["norm1_w"] = _f32(sd[pre + "norm1.weight"], device)
+            t["norm2_w"] = _f32(sd[pre + "norm2.weight"], device)
+            t["final_norm_w"] = _f32(sd[pre + "final_norm.weight"], device)
+            t["w_gate_up"] = interleave_gate_up(sd[pre + "mlp.gate_up.weight"], device)
+            t["w_down"] = _bf16(sd[pre + "mlp.down.weight"], device)
+            t["mor_w"] = _f32(sd[pre + "mor_router.router.weight"], device).reshape(-1)
+            t["mor_b"] = _f32(sd[pre + "mor_router.router.bias"], device).reshape(1)
+            rb = sd[pre + "mor_executor.recursion_bias"]
+            re = sd[pre + "mor_executor.recursion_embed.weight"]
+            # the reference adds bias then embedding to the hidden state in its dtype; one fp32 vector here
+            t["rec"] = (_f32(rb, device).reshape(re.shape[0], -1) + _f32(re, device)).contiguous()
+            mk = pre + "mod_mlp_wrapper.mod_router.router."
+            if mk + "weight" in sd:
+                t["mod_w"] = _f32(sd[mk + "weight"], device).reshape(-1)
+                t["mod_b"] = _f32(sd[mk + "bias"], device).reshape(1)
+        self.tensors = t
+        self.struct = _lib.BlockWeights(**{k: (v.data_ptr() if v is not None else None) for k, v in t.items()})
+
+
+class PackedModel:
+    """hb200_model struct + everything it points to."""
+
+    def __init__(self, *, vocab: int, dim: int, n_rec: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 ffn_hidden: int, min_depth: int, adaptive: bool, max_seq_len: int, mod_capacity: float,
+                 norm_eps: float, residual_scale: float, output_scale: float, blocks: List[PackedBlock],
+                 tok_emb: Optional[Tensor], norm_w: Optional[Tensor], device, gemm_impl: int = 0):
+        self.blocks = blocks
+        self.block_array = (_lib.BlockWeights * len(blocks))(*[b.struct for b in blocks])
+        self.cos, self.sin = rope_tables(max_seq_len, head_dim, device)
+        self.tok_emb, self.norm_w = tok_emb, norm_w
+        self.struct = _lib.Model(
+            vocab=vocab, dim=dim, n_blocks=len(blocks), n_rec=n_rec, n_heads=n_heads, n_kv_heads=n_kv_heads,
+            head_dim=head_dim, ffn_hidden=ffn_hidden, min_depth=min_depth, adaptive=int(adaptive),
+            max_seq_len=max_seq_len, gemm_impl=gemm_impl, mod_capacity=mod_capacity, norm_eps=norm_eps,
+            residual_scale=residual_scale, output_scale=output_scale,
+            tok_emb=tok_emb.data_ptr() if tok_emb is not None else None,
+            norm_w=norm_w.data_ptr() if norm_w is not None else None,
+            rope_cos=self.cos.data_ptr(), rope_sin=self.sin.data_ptr(),
+            blocks=C.cast(self.block_array, C.POINTER(_lib.BlockWeights)))
+        self._ws: Dict[tuple, Tensor] = {}
+        self.device = device
+        self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def workspace(self, B: int, S: int) -> Tensor:
+        key = (B, S)
+        ws = self._ws.get(key)
+        if ws is None:
+            n = _lib.lib().hb200_model_workspace_bytes(C.byref(self.struct), B, S)
+            self._ws.clear()   # one live shape at a time keeps the footprint bounded
+            ws = torch.empty(n, dtype=torch.uint8, device=self.device)
+            self._ws[key] = ws
+        return ws
+
+    def check_device_errors(self) -> None:
+        """Synchronises and raises if a bounded in-kernel wait ran out during an earlier call."""
+        if int(self.err_flag.item()) != 0:
+            self.err_flag.zero_()
+            raise _lib.Hb200Error("a bounded wait inside a GEMM kernel ran out (status HB200_ERR_DEVICE_WAIT); "
+                                  "the results of that call are undefined")

@@ -1,0 +1,208 @@
+// Causal grouped-query attention in the CCGQA latent space (head_dim 16 / 32 / 64).
+//
+// One CTA = 64 query rows of one (batch, q-head): 4 warps x 16 rows.  K/V tiles of 64 keys are staged in
+// shared memory; S = QK^T and O += PV run on the tensor cores (mma.sync m16n8k16, bf16 in / fp32 acc),
+// with a base-2 online softmax in registers.  Heavy (late) query tiles are scheduled first so the causal
+// triangle balances across the SMs.  Output is token-major [B,S,H*hd], the A operand of the o_proj GEMM.
+#include "common.cuh"
+#include "mma.cuh"
+
+namespace hb200 {
+
+constexpr int ATT_BM = 64;   // query rows per CTA
+constexpr int ATT_BN = 64;   // keys per tile
+
+template <int HD>
+__global__ void __launch_bounds__(128) attention_causal_gqa_kernel(const __nv_bfloat16* __restrict__ q,
+                                                                   const __nv_bfloat16* __restrict__ k,
+                                                                   const __nv_bfloat16* __restrict__ v,
+                                                                   __nv_bfloat16* __restrict__ o, int S, int H,
+                                                                   int KV, float scale_log2) {
+  constexpr int LDS = HD + 8;                 // padded smem row (bf16 elements)
+  constexpr int KSTEPS = HD / 16;             // k-steps of QK^T
+  constexpr int NT_O = HD / 8;                // n-tiles of the output
+  __shared__ __align__(16) __nv_bfloat16 Ks[2][ATT_BN][LDS];
+  __shared__ __align__(16) __nv_bfloat16 Vs[2][ATT_BN][LDS];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int n_qt = (S + ATT_BM - 1) / ATT_BM;
+  const int qt = n_qt - 1 - (int)blockIdx.x;   // late tiles (most keys) first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (H / KV);
+  const int q0 = qt * ATT_BM;
+  const __nv_bfloat16* qp = q + ((size_t)b * H + h) * S * HD;
+  const __nv_bfloat16* kp = k + ((size_t)b * KV + kvh) * S * HD;
+  const __nv_bfloat16* vp = v + ((size_t)b * KV + kvh) * S * HD;
+
+  // Q fragments for this warp's 16 rows (rows beyond S read as zero)
+  const int r_lo = q0 + warp * 16 + g, r_hi = r_lo + 8;
+  uint32_t qa[KSTEPS][4];
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const int c = ks * 16 + 2 * t;
+    qa[ks][0] = r_lo < S ? *reinterpret_cast<const uint32_t*>(qp + (size_t)r_lo * HD + c) : 0u;
+    qa[ks][1] = r_hi < S ? *reinterpret_cast<const uint32_t*>(qp + (size_t)r_hi * HD + c) : 0u;
+    qa[ks][2] = r_lo < S ? *reinterpret_cast<const uint32_t*>(qp + (size_t)r_lo * HD + c + 8) : 0u;
+    qa[ks][3] = r_hi < S ? *reinterpret_cast<const uint32_t*>(qp + (size_t)r_hi * HD + c + 8) : 0u;
+  }
+
+  float oacc[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) oacc[i][c] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+  const int n_kt = qt + 1;   // causal: key tiles 0..qt (ATT_BM == ATT_BN)
+  auto load_tile = [&](int kt, int buf) {
+    const int k0 = kt * ATT_BN;
+    constexpr int PIECES = HD / 8;
+    for (int idx = tid; idx < ATT_BN * PIECES; idx += 128) {
+      const int r = idx / PIECES, pc = idx % PIECES;
+      const int key = k0 + r;
+      if (key < S) {
+        cp_async_16(&Ks[buf][r][pc * 8], kp + (size_t)key * HD + pc * 8);
+        cp_async_16(&Vs[buf][r][pc * 8], vp + (size_t)key * HD + pc * 8);
+      } else {
+        *reinterpret_cast<uint4*>(&Ks[buf][r][pc * 8]) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(&Vs[buf][r][pc * 8]) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    cp_async_commit();
+  };
+
+  load_tile(0, 0);
+  for (int kt = 0; kt < n_kt; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < n_kt) {
+      load_tile(kt + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    // S = Q K^T  (16 x 64 per warp)
+    float s[ATT_BN / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < ATT_BN / 8; ++nt) {
+      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const __nv_bfloat16* kr = &Ks[buf][nt * 8 + g][ks * 16 + 2 * t];
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + 8);
+        mma_bf16_16816(s[nt], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+      }
+    }
+    // scale to base-2 logits, causal mask on the diagonal tile
+    const int k0 = kt * ATT_BN;
+    const bool diag = (kt == qt);
+#pragma unroll
+    for (int nt = 0; nt < ATT_BN / 8; ++nt) {
+      const int c = k0 + nt * 8 + 2 * t;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = c + (e & 1);
+        const int row = (e < 2) ? r_lo : r_hi;
+        float val = s[nt][e] * scale_log2;
+        if (diag && key > row) val = -INFINITY;
+        s[nt][e] = val;
+      }
+    }
+    // online softmax (each row lives in the 4 lanes of a quad)
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < ATT_BN / 8; ++nt) {
+      mx_lo = fmaxf(mx_lo, fmaxf(s[nt][0], s[nt][1]));
+      mx_hi = fmaxf(mx_hi, fmaxf(s[nt][2], s[nt][3]));
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    // key 0 is visible to every row, so the running maximum is finite from the first tile on
+    const float a_lo = exp2f(m_lo - mn_lo), a_hi = exp2f(m_hi - mn_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    float rs_lo = 0.f, rs_hi = 0.f;
+    uint32_t pa[ATT_BN / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < ATT_BN / 8; ++nt) {
+      const float p0 = exp2f(s[nt][0] - mn_lo), p1 = exp2f(s[nt][1] - mn_lo);
+      const float p2 = exp2f(s[nt][2] - mn_hi), p3 = exp2f(s[nt][3] - mn_hi);
+      rs_lo += p0 + p1;
+      rs_hi += p2 + p3;
+      // C fragments of two adjacent n-tiles form the A fragment of one k16 step of P V
+      pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16x2(p0, p1);
+      pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+    }
+    l_lo = l_lo * a_lo + rs_lo;
+    l_hi = l_hi * a_hi + rs_hi;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) {
+      oacc[i][0] *= a_lo;
+      oacc[i][1] *= a_lo;
+      oacc[i][2] *= a_hi;
+      oacc[i][3] *= a_hi;
+    }
+    // O += P V  (k = key index inside the tile)
+#pragma unroll
+    for (int kk = 0; kk < ATT_BN / 16; ++kk) {
+#pragma unroll
+      for (int nt = 0; nt < NT_O; ++nt) {
+        uint32_t b0, b1;
+        ldmatrix_x2_trans(b0, b1, &Vs[buf][kk * 16 + (lane & 15)][nt * 8]);
+        mma_bf16_16816(oacc[nt], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
+      }
+    }
+    __syncthreads();
+  }
+
+  // finish: row sums across the quad, normalise, token-major bf16 store
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
+  const size_t ld_o = (size_t)H * HD;
+  __nv_bfloat16* ob = o + (size_t)b * S * ld_o + (size_t)h * HD;
+#pragma unroll
+  for (int nt = 0; nt < NT_O; ++nt) {
+    const int c = nt * 8 + 2 * t;
+    if (r_lo < S) *reinterpret_cast<uint32_t*>(ob + (size_t)r_lo * ld_o + c) = pack_bf16x2(oacc[nt][0] * i_lo, oacc[nt][1] * i_lo);
+    if (r_hi < S) *reinterpret_cast<uint32_t*>(ob + (size_t)r_hi * ld_o + c) = pack_bf16x2(oacc[nt][2] * i_hi, oacc[nt][3] * i_hi);
+  }
+}
+
+}  // namespace hb200
+
+using namespace hb200;
+
+extern "C" int hb200_attention_causal_gqa(const void* q, const void* k, const void* v, void* o, int B, int S, int H,
+                                          int KV, int hd, float scale, void* stream) {
+  HB_REQUIRE(q && k && v && o, HB200_ERR_INVALID, "attention: null pointer");
+  HB_REQUIRE(B >= 0 && S >= 0 && H >= 1 && KV >= 1 && H % KV == 0, HB200_ERR_INVALID, "attention: bad shape");
+  HB_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o), HB200_ERR_INVALID,
+             "attention: pointers must be 16-byte aligned");
+  HB_REQUIRE(B <= 65535 && H <= 65535, HB200_ERR_UNSUPPORTED, "attention: batch/head count beyond grid limits");
+  if ((int64_t)B * S == 0) return 0;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid((S + ATT_BM - 1) / ATT_BM, H, B);
+  cudaStream_t st = (cudaStream_t)stream;
+  const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k, *vp = (const __nv_bfloat16*)v;
+  if (hd == 16)
+    attention_causal_gqa_kernel<16><<<grid, 128, 0, st>>>(qp, kp, vp, (__nv_bfloat16*)o, S, H, KV, scale_log2);
+  else if (hd == 32)
+    attention_causal_gqa_kernel<32><<<grid, 128, 0, st>>>(qp, kp, vp, (__nv_bfloat16*)o, S, H, KV, scale_log2);
+  else if (hd == 64)
+    attention_causal_gqa_kernel<64><<<grid, 128, 0, st>>>(qp, kp, vp, (__nv_bfloat16*)o, S, H, KV, scale_log2);
+  else {
+    set_error("attention: head_dim %d not built (16, 32, 64)", hd);
+    return HB200_ERR_UNSUPPORTED;
+  }
+  HB_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,501 @@
+// Host-side executor of the HYDRA block / model forward (eval, dynamic MoR + hard MoD routing) and the small
+// row kernels that sit between the GEMMs.  Everything is enqueued on one stream; routing decisions stay on
+// the device (row lists + device-side counts feed the GEMMs), so a forward never synchronises with the host.
+//
+// Per block:
+//   a   = AdaRMSNorm(x)                                   rms_norm kernel
+//   qkv = a Wqkv^T                                        tcgen05 GEMM
+//   q,k,v = fused pre-attention(qkv)                      ccgqa_pre kernel
+//   o   = causal GQA attention                            attention kernel
+//   cur = x + 0.5*scale * o Wo^T                          tcgen05 GEMM, residual epilogue
+//   depth = MoR router(cur)                               mor_score kernel (recursion 0)
+//   for r < R:
+//     s    = MoD router(AdaRMSNorm(cur + rec_r))          mor_score kernel (all tokens, no activation written)
+//     rows = topk(s) AND depth >= r   (or depth >= r)     mod_select / compact_active kernel -> device row list
+//     ug   = AdaRMSNorm(cur[rows] + rec_r)                norm_gather kernel (compact)
+//     act  = silu(ug Wg^T) * (ug Wu^T)                    tcgen05 GEMM, SwiGLU epilogue, device row count
+//     cur[rows] += act Wd^T                               tcgen05 GEMM, scatter-add epilogue
+//   y = RMSNorm(cur)        (the executor's output accumulator equals the final `cur`: a token stops
+//                            changing after its exit recursion, and it exits exactly once)
+#include <cmath>
+#include <new>
+#include <utility>
+#include <vector>
+
+#include "gemm_epilogue.cuh"
+
+namespace hb200 {
+
+int launch_mod_select(const float* scores, int B, int L, int k, int32_t* idx_out, const int32_t* depth, int min_active,
+                      int32_t* rows_out, int32_t* count, const int32_t* forced_idx, cudaStream_t st);
+int launch_compact_active(const int32_t* depth, int64_t n, int min_active, int32_t* rows_out, int32_t* count,
+                          cudaStream_t st);
+
+// ---- per-launch event recorder ---------------------------------------------------------------------------
+struct Profile {
+  std::vector<cudaEvent_t> ev;          // 2 per launch
+  std::vector<hb200_launch_record> rec;
+  int count = 0;
+  int capacity = 0;
+};
+
+struct ProfScope {
+  Profile* p;
+  cudaStream_t st;
+  int slot;
+  ProfScope(void* prof, cudaStream_t s, int kind, int block, int rec, int m, int n, int k)
+      : p(static_cast<Profile*>(prof)), st(s), slot(-1) {
+    if (p != nullptr && p->count < p->capacity) {
+      slot = p->count++;
+      p->rec[slot] = hb200_launch_record{kind, block, rec, m, n, k};
+      cudaEventRecord(p->ev[2 * slot], st);
+    }
+  }
+  ~ProfScope() {
+    if (slot >= 0) cudaEventRecord(p->ev[2 * slot + 1], st);
+  }
+};
+
+constexpr int ROW_NCH = 8;   // row kernels keep up to 8 x 256 elements of a row in registers (dim <= 2048)
+
+// Loads row `src` (+ optional fp32 per-column offset), returns sum of squares; values stay in v.
+__device__ __forceinline__ float load_row_add(const __nv_bfloat16* __restrict__ src, const float* __restrict__ add,
+                                              int D, int lane, float (&v)[ROW_NCH][8]) {
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < ROW_NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) {
+      load_bf16x8(src + i, v[c]);
+      if (add != nullptr) {
+        const float4 a0 = *reinterpret_cast<const float4*>(add + i);
+        const float4 a1 = *reinterpret_cast<const float4*>(add + i + 4);
+        v[c][0] += a0.x; v[c][1] += a0.y; v[c][2] += a0.z; v[c][3] += a0.w;
+        v[c][4] += a1.x; v[c][5] += a1.y; v[c][6] += a1.z; v[c][7] += a1.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[c][j] * v[c][j];
+    }
+  }
+  return warp_sum(ss);
+}
+
+// v <- bf16-rounded (v * r * w)
+__device__ __forceinline__ void scale_row(const float* __restrict__ w, float r, int D, int lane,
+                                          float (&v)[ROW_NCH][8]) {
+#pragma unroll
+  for (int c = 0; c < ROW_NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) {
+      const float4 w0 = *reinterpret_cast<const float4*>(w + i);
+      const float4 w1 = *reinterpret_cast<const float4*>(w + i + 4);
+      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[c][j] = __bfloat162float(__float2bfloat16_rn(v[c][j] * r * ww[j]));
+    }
+  }
+}
+
+__device__ __forceinline__ float dot_row(const float* __restrict__ w, int D, int lane, const float (&v)[ROW_NCH][8]) {
+  float s = 0.f;
+#pragma unroll
+  for (int c = 0; c < ROW_NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) {
+      const float4 w0 = *reinterpret_cast<const float4*>(w + i);
+      const float4 w1 = *reinterpret_cast<const float4*>(w + i + 4);
+      s += v[c][0] * w0.x + v[c][1] * w0.y + v[c][2] * w0.z + v[c][3] * w0.w + v[c][4] * w1.x + v[c][5] * w1.y +
+           v[c][6] * w1.z + v[c][7] * w1.w;
+    }
+  }
+  return warp_sum(s);
+}
+
+// One warp per token.  Optionally: depth-router logit/depth from the raw row; MoD score from the normalised row.
+__global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __restrict__ cur,
+                                                        const float* __restrict__ rec, const float* __restrict__ w2,
+                                                        const float* __restrict__ mod_w, const float* __restrict__ mod_b,
+                                                        const float* __restrict__ mor_w, const float* __restrict__ mor_b,
+                                                        float* __restrict__ scores, float* __restrict__ logits,
+                                                        int32_t* __restrict__ depth, int64_t T, int D, float eps,
+                                                        int n_rec, int min_d) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= T) return;
+  float v[ROW_NCH][8];
+  if (mor_w != nullptr) {
+    load_row_add(cur + row * D, nullptr, D, lane, v);
+    const float l = dot_row(mor_w, D, lane, v) + mor_b[0];
+    if (lane == 0) {
+      if (logits != nullptr) logits[row] = l;
+      if (depth != nullptr) depth[row] = mor_depth_from_logit(l, n_rec, min_d);
+    }
+  }
+  if (mod_w != nullptr) {
+    const float ss = load_row_add(cur + row * D, rec, D, lane, v);
+    scale_row(w2, rsqrtf(ss / (float)D + eps), D, lane, v);
+    const float s = dot_row(mod_w, D, lane, v) + mod_b[0];
+    if (lane == 0) scores[row] = s;
+  }
+}
+
+// ug[j] = AdaRMSNorm(cur[rows[j]] + rec) for j < *count.  One warp per compact row.
+__global__ void __launch_bounds__(256) norm_gather_kernel(const __nv_bfloat16* __restrict__ cur,
+                                                          const float* __restrict__ rec, const float* __restrict__ w2,
+                                                          const int32_t* __restrict__ rows,
+                                                          const int32_t* __restrict__ count,
+                                                          __nv_bfloat16* __restrict__ ug, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t j = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (j >= *count) return;
+  const int64_t src = rows[j];
+  float v[ROW_NCH][8];
+  const float ss = load_row_add(cur + src * D, rec, D, lane, v);
+  scale_row(w2, rsqrtf(ss / (float)D + eps), D, lane, v);
+#pragma unroll
+  for (int c = 0; c < ROW_NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) store_bf16x8(ug + j * D + i, v[c]);
+  }
+}
+
+__global__ void fill_i32_kernel(int32_t* p, int64_t n, int32_t val) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = val;
+}
+
+// gate_up [2F,K] -> rows interleaved in groups of 8 (8 gate rows, 8 up rows, ...)
+__global__ void interleave_gate_up_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ o, int F,
+                                          int K) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one 16-byte piece
+  const int ppr = K / 8;
+  if (idx >= (int64_t)2 * F * ppr) return;
+  const int orow = (int)(idx / ppr), piece = (int)(idx % ppr);
+  const int grp = orow / 16, r = orow % 16;
+  const int srow = (r < 8) ? grp * 8 + r : F + grp * 8 + (r - 8);
+  *reinterpret_cast<uint4*>(o + (size_t)orow * K + piece * 8) =
+      *reinterpret_cast<const uint4*>(w + (size_t)srow * K + piece * 8);
+}
+
+// Conv1d weight [Cout, Cin, 3] -> [Cout, 3*Cin] with (co, j*Cin + ci) = w[co, ci, j]
+__global__ void repack_conv_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ o, int cout,
+                                   int cin) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)cout * cin * 3) return;
+  const int co = (int)(idx / (3 * cin)), rem = (int)(idx % (3 * cin));
+  const int j = rem / cin, ci = rem % cin;
+  o[idx] = w[((size_t)co * cin + ci) * 3 + j];
+}
+
+// ---- workspace ----------------------------------------------------------------------------------------------
+struct Workspace {
+  __nv_bfloat16 *x0, *x1, *a, *qkv, *q, *k, *v, *o, *cur, *ug, *act;
+  float *scores, *logits;
+  int32_t *depth, *rows, *sel_idx, *counts;
+  size_t bytes;
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static Workspace carve(const hb200_model* m, int B, int S, void* base) {
+  const size_t T = (size_t)B * S, D = m->dim, lat = (size_t)m->n_heads * m->head_dim,
+               kvd = (size_t)m->n_kv_heads * m->head_dim, F = m->ffn_hidden;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    void* p = base ? (void*)((char*)base + off) : nullptr;
+    off += align_up(bytes, 1024);
+    return p;
+  };
+  Workspace w{};
+  w.x0 = (__nv_bfloat16*)take(T * D * 2);
+  w.x1 = (__nv_bfloat16*)take(T * D * 2);
+  w.a = (__nv_bfloat16*)take(T * D * 2);
+  w.qkv = (__nv_bfloat16*)take(T * (lat + 2 * kvd) * 2);
+  w.q = (__nv_bfloat16*)take(T * lat * 2);
+  w.k = (__nv_bfloat16*)take(T * kvd * 2);
+  w.v = (__nv_bfloat16*)take(T * kvd * 2);
+  w.o = (__nv_bfloat16*)take(T * lat * 2);
+  w.cur = (__nv_bfloat16*)take(T * D * 2);
+  w.ug = (__nv_bfloat16*)take(T * D * 2);
+  w.act = (__nv_bfloat16*)take(T * F * 2);
+  w.scores = (float*)take(T * 4);
+  w.logits = (float*)take(T * 4);
+  w.depth = (int32_t*)take(T * 4);
+  w.rows = (int32_t*)take(T * 4);
+  w.sel_idx = (int32_t*)take(T * 4);
+  w.counts = (int32_t*)take((size_t)m->n_blocks * m->n_rec * 4);
+  w.bytes = off;
+  return w;
+}
+
+static int mod_k(int L, float cap) {
+  // k = max(1, min(L, int(L * clamp(cap, 1e-4, 1)))) evaluated in double like the reference's Python floats
+  double c = (double)cap;
+  c = c < 1e-4 ? 1e-4 : (c > 1.0 ? 1.0 : c);
+  int k = (int)((double)L * c);
+  return k < 1 ? 1 : (k > L ? L : k);
+}
+
+static int check_model(const hb200_model* m, int B, int S) {
+  HB_REQUIRE(m != nullptr && m->blocks != nullptr, HB200_ERR_INVALID, "model: null model or block table");
+  HB_REQUIRE(B >= 1 && S >= 1, HB200_ERR_INVALID, "model: batch and sequence length must be positive (B=%d S=%d)", B, S);
+  HB_REQUIRE(S <= m->max_seq_len, HB200_ERR_INVALID, "model: sequence length %d exceeds the RoPE table (%d)", S,
+             m->max_seq_len);
+  HB_REQUIRE(m->dim % 8 == 0 && m->dim <= 256 * ROW_NCH, HB200_ERR_UNSUPPORTED,
+             "model: dim %d must be a multiple of 8 and at most %d", m->dim, 256 * ROW_NCH);
+  HB_REQUIRE(m->ffn_hidden % 8 == 0, HB200_ERR_UNSUPPORTED, "model: ffn hidden %d must be a multiple of 8", m->ffn_hidden);
+  HB_REQUIRE(m->n_heads % m->n_kv_heads == 0, HB200_ERR_INVALID, "model: n_heads must be a multiple of n_kv_heads");
+  HB_REQUIRE(m->n_rec >= 1 && m->min_depth >= 0 && m->min_depth <= m->n_rec - 1, HB200_ERR_INVALID,
+             "model: bad recursion settings");
+  HB_REQUIRE((int64_t)B * S < (1ll << 31), HB200_ERR_UNSUPPORTED, "model: too many tokens");
+  return 0;
+}
+
+static int gemm(const hb200_model* m, int kind, int bi, int r, const void* A, const void* W, void* C, int M, int N,
+                int K, int64_t lda, int64_t ldw, int64_t ldc, int epi, const void* resid, float alpha,
+                const int32_t* rows, const int32_t* m_dev, int32_t* err, cudaStream_t st) {
+  ProfScope ps(m->profile, st, kind, bi, r, M, N, K);
+  return hb200_gemm_bf16(A, W, C, M, N, K, lda, ldw, ldc, epi, resid, alpha, rows, m_dev, m->gemm_impl, err, st);
+}
+
+// attention sub-block: y_out = epilogue(o Wo^T); resid == nullptr -> plain store scaled by alpha
+static int attention_part(const hb200_model* m, int bi, const hb200_block_weights& bw, const Workspace& w, const void* a_in,
+                          const void* resid, float alpha, void* out, int B, int S, int32_t* err, cudaStream_t st) {
+  const int T = B * S, D = m->dim, H = m->n_heads, KV = m->n_kv_heads, hd = m->head_dim;
+  const int lat = H * hd, kvd = KV * hd, nq = lat + 2 * kvd;
+  HB_PROPAGATE(gemm(m, HB200_K_GEMM_QKV, bi, 0, a_in, bw.w_qkv, w.qkv, T, nq, D, D, D, nq, EPI_STORE, nullptr, 1.0f,
+                    nullptr, nullptr, err, st));
+  {
+    ProfScope ps(m->profile, st, HB200_K_PRE_ATTENTION, bi, 0, T, nq, 0);
+    HB_PROPAGATE(hb200_ccgqa_pre_attention(w.qkv, bw.w1_qk, bw.w2_q, bw.w2_k, m->rope_cos, m->rope_sin,
+                                           bw.key_temperature, w.q, w.k, w.v, B, S, H, KV, hd, st));
+  }
+  {
+    ProfScope ps(m->profile, st, HB200_K_ATTENTION, bi, 0, T, lat, S);
+    HB_PROPAGATE(hb200_attention_causal_gqa(w.q, w.k, w.v, w.o, B, S, H, KV, hd, 1.0f / sqrtf((float)hd), st));
+  }
+  HB_PROPAGATE(gemm(m, HB200_K_GEMM_O, bi, 0, w.o, bw.w_o, out, T, D, lat, lat, lat, D, resid ? EPI_RESID : EPI_STORE, resid, alpha, nullptr,
+                    nullptr, err, st));
+  return 0;
+}
+
+static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, __nv_bfloat16* y, int B, int S,
+                         const Workspace& w, const hb200_taps* taps, int32_t* counts, int32_t* err, cudaStream_t st) {
+  const hb200_block_weights& bw = m->blocks[bi];
+  const int T = B * S, D = m->dim, F = m->ffn_hidden, R = m->n_rec;
+  const bool force = taps && taps->force_routing;
+  const bool has_mod = bw.mod_w != nullptr;
+  const int k = mod_k(S, m->mod_capacity);
+  const unsigned row_grid = (unsigned)ceil_div(T, 8);
+
+  // attention half
+  {
+    ProfScope ps(m->profile, st, HB200_K_RMS_NORM, bi, 0, T, D, 0);
+    HB_PROPAGATE(hb200_rms_norm(x, bw.norm1_w, w.a, T, D, m->norm_eps, HB200_BF16, HB200_F32, st));
+  }
+  HB_PROPAGATE(attention_part(m, bi, bw, w, w.a, x, m->residual_scale * m->output_scale, w.cur, B, S, err, st));
+
+  // routing buffers: the taps slots double as the working buffers when present
+  int32_t* depth = (taps && taps->depths) ? taps->depths + (size_t)bi * T : w.depth;
+  float* logits = (taps && taps->router_logits) ? taps->router_logits + (size_t)bi * T : w.logits;
+  if (force) HB_REQUIRE(taps->depths != nullptr, HB200_ERR_INVALID, "forced routing needs taps.depths");
+  if (force && has_mod) HB_REQUIRE(taps->mod_idx != nullptr, HB200_ERR_INVALID, "forced routing needs taps.mod_idx");
+  if (!m->adaptive && !force) {
+    ProfScope ps(m->profile, st, HB200_K_OTHER, bi, 0, T, 0, 0);
+    fill_i32_kernel<<<(unsigned)ceil_div(T, 256), 256, 0, st>>>(depth, T, R - 1);
+    HB_LAUNCH_CHECK();
+  }
+
+  for (int r = 0; r < R; ++r) {
+    const float* rec = bw.rec + (size_t)r * D;
+    const bool need_router = (r == 0) && m->adaptive;
+    float* scores = (taps && taps->mod_scores) ? taps->mod_scores + ((size_t)bi * R + r) * T : w.scores;
+    if (need_router || has_mod) {
+      ProfScope ps(m->profile, st, HB200_K_MOR_SCORE, bi, r, T, D, 0);
+      mor_score_kernel<<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, has_mod ? bw.mod_w : nullptr, bw.mod_b,
+                                                 need_router ? bw.mor_w : nullptr, bw.mor_b, scores, logits,
+                                                 force ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth);
+      HB_LAUNCH_CHECK();
+    }
+    int32_t* count = counts + (size_t)bi * R + r;
+    {
+    ProfScope ps(m->profile, st, HB200_K_SELECT, bi, r, T, 0, 0);
+    if (has_mod) {
+      int32_t* slot = (taps && taps->mod_idx) ? taps->mod_idx + ((size_t)bi * R + r) * B * k : w.sel_idx;
+      HB_PROPAGATE(launch_mod_select(scores, B, S, k, force ? nullptr : slot, depth, r, w.rows, count,
+                                     force ? slot : nullptr, st));
+    } else {
+      HB_PROPAGATE(launch_compact_active(depth, T, r, w.rows, count, st));
+    }
+    }
+    {
+      ProfScope ps(m->profile, st, HB200_K_NORM_GATHER, bi, r, T, D, 0);
+      norm_gather_kernel<<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, w.rows, count, w.ug, D, m->norm_eps);
+      HB_LAUNCH_CHECK();
+    }
+    HB_PROPAGATE(gemm(m, HB200_K_GEMM_GATE_UP, bi, r, w.ug, bw.w_gate_up, w.act, T, 2 * F, D, D, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count,
+                      err, st));
+    HB_PROPAGATE(gemm(m, HB200_K_GEMM_DOWN, bi, r, w.act, bw.w_down, w.cur, T, D, F, F, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count,
+                      err, st));
+  }
+  {
+    ProfScope ps(m->profile, st, HB200_K_RMS_NORM, bi, R, T, D, 0);
+    HB_PROPAGATE(hb200_rms_norm(w.cur, bw.final_norm_w, y, T, D, m->norm_eps, HB200_BF16, HB200_F32, st));
+  }
+  if (taps && taps->block_out)
+    HB_CUDA(cudaMemcpyAsync((__nv_bfloat16*)taps->block_out + (size_t)bi * T * D, y, (size_t)T * D * 2,
+                            cudaMemcpyDeviceToDevice, st));
+  return 0;
+}
+
+}  // namespace hb200
+
+using namespace hb200;
+
+extern "C" int hb200_gemm_bf16(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
+                               int64_t ldc, int epilogue, const void* resid, float alpha, const int32_t* rows,
+                               const int32_t* m_dev, int impl, int32_t* err_flag, void* stream) {
+  HB_REQUIRE(A && W && C, HB200_ERR_INVALID, "gemm: null pointer");
+  HB_REQUIRE(M >= 0 && N >= 1 && K >= 1, HB200_ERR_INVALID, "gemm: bad shape M=%d N=%d K=%d", M, N, K);
+  HB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ldc % 8 == 0 && lda >= K && ldw >= K, HB200_ERR_INVALID,
+             "gemm: K and leading dimensions must be multiples of 8 (K=%d lda=%lld ldw=%lld ldc=%lld)", K,
+             (long long)lda, (long long)ldw, (long long)ldc);
+  HB_REQUIRE(aligned16(A) && aligned16(W) && aligned16(C) && (resid == nullptr || aligned16(resid)), HB200_ERR_INVALID,
+             "gemm: pointers must be 16-byte aligned");
+  HB_REQUIRE(epilogue >= EPI_STORE && epilogue <= EPI_SCATTER_ADD, HB200_ERR_INVALID, "gemm: unknown epilogue %d", epilogue);
+  HB_REQUIRE(epilogue != EPI_RESID || resid != nullptr, HB200_ERR_INVALID, "gemm: residual epilogue needs resid");
+  HB_REQUIRE(epilogue != EPI_SCATTER_ADD || rows != nullptr, HB200_ERR_INVALID, "gemm: scatter-add epilogue needs rows");
+  HB_REQUIRE(epilogue != EPI_SWIGLU || N % 16 == 0, HB200_ERR_INVALID, "gemm: SwiGLU epilogue needs N %% 16 == 0");
+  HB_REQUIRE(epilogue == EPI_SWIGLU ? ldc >= N / 2 : ldc >= N, HB200_ERR_INVALID, "gemm: ldc too small");
+  HB_REQUIRE(impl == 0 || impl == 1, HB200_ERR_INVALID, "gemm: impl must be 0 (tcgen05) or 1 (mma.sync cross-check)");
+  if (M == 0) return 0;
+  GemmParams p{(const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, lda, ldw, ldc, epilogue,
+               (const __nv_bfloat16*)resid, epilogue == EPI_SCATTER_ADD ? 1.0f : alpha, rows, m_dev, err_flag};
+  return impl == 0 ? launch_gemm_tcgen05(p, (cudaStream_t)stream) : launch_gemm_mma(p, (cudaStream_t)stream);
+}
+
+extern "C" int hb200_interleave_gate_up(const void* w_gate_up, void* w_out, int F, int K, void* stream) {
+  HB_REQUIRE(w_gate_up && w_out && w_gate_up != w_out, HB200_ERR_INVALID, "interleave_gate_up: bad pointers");
+  HB_REQUIRE(F >= 8 && F % 8 == 0 && K % 8 == 0, HB200_ERR_INVALID, "interleave_gate_up: F and K must be multiples of 8");
+  const int64_t n = (int64_t)2 * F * (K / 8);
+  interleave_gate_up_kernel<<<(unsigned)ceil_div64(n, 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)w_gate_up, (__nv_bfloat16*)w_out, F, K);
+  HB_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int hb200_repack_conv_weight(const void* w, void* w_out, int c_out, int c_in, void* stream) {
+  HB_REQUIRE(w && w_out && w != w_out && c_out > 0 && c_in > 0, HB200_ERR_INVALID, "repack_conv_weight: bad arguments");
+  const int64_t n = (int64_t)c_out * c_in * 3;
+  repack_conv_kernel<<<(unsigned)ceil_div64(n, 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)w, (__nv_bfloat16*)w_out, c_out, c_in);
+  HB_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" size_t hb200_model_workspace_bytes(const hb200_model* m, int B, int S) {
+  if (m == nullptr || B < 1 || S < 1) return 0;
+  return carve(m, B, S, nullptr).bytes;
+}
+
+extern "C" int hb200_ccgqa_forward(const hb200_model* m, int block_index, const void* x, void* y, int B, int S,
+                                   void* workspace, size_t workspace_bytes, int32_t* err_flag, void* stream) {
+  HB_PROPAGATE(check_model(m, B, S));
+  HB_REQUIRE(x && y && workspace, HB200_ERR_INVALID, "ccgqa_forward: null pointer");
+  HB_REQUIRE(block_index >= 0 && block_index < m->n_blocks, HB200_ERR_INVALID, "ccgqa_forward: bad block index");
+  Workspace w = carve(m, B, S, workspace);
+  HB_REQUIRE(workspace_bytes >= w.bytes, HB200_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.bytes);
+  return attention_part(m, block_index, m->blocks[block_index], w, x, nullptr, m->output_scale, y, B, S, err_flag,
+                        (cudaStream_t)stream);
+}
+
+extern "C" int hb200_block_forward(const hb200_model* m, int block_index, const void* x, void* y, int B, int S,
+                                   void* workspace, size_t workspace_bytes, const hb200_taps* taps, int32_t* err_flag,
+                                   void* stream) {
+  HB_PROPAGATE(check_model(m, B, S));
+  HB_REQUIRE(x && y && workspace, HB200_ERR_INVALID, "block_forward: null pointer");
+  HB_REQUIRE(block_index >= 0 && block_index < m->n_blocks, HB200_ERR_INVALID, "block_forward: bad block index");
+  Workspace w = carve(m, B, S, workspace);
+  HB_REQUIRE(workspace_bytes >= w.bytes, HB200_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  int32_t* counts = (taps && taps->mlp_rows) ? taps->mlp_rows : w.counts;
+  HB_CUDA(cudaMemsetAsync(counts + (size_t)block_index * m->n_rec, 0, (size_t)m->n_rec * 4, st));
+  return block_forward(m, block_index, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, B, S, w, taps, counts, err_flag, st);
+}
+
+extern "C" int hb200_model_forward(const hb200_model* m, const int64_t* ids, int B, int S, void* workspace,
+                                   size_t workspace_bytes, void* logits, int64_t ld_logits, void* hidden_out,
+                                   const hb200_taps* taps, int32_t* err_flag, void* stream) {
+  HB_PROPAGATE(check_model(m, B, S));
+  HB_REQUIRE(ids && workspace, HB200_ERR_INVALID, "model_forward: null pointer");
+  HB_REQUIRE(logits == nullptr || (ld_logits >= m->vocab && ld_logits % 8 == 0), HB200_ERR_INVALID,
+             "model_forward: ld_logits must be >= vocab and a multiple of 8");
+  Workspace w = carve(m, B, S, workspace);
+  HB_REQUIRE(workspace_bytes >= w.bytes, HB200_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int T = B * S, D = m->dim;
+  int32_t* counts = (taps && taps->mlp_rows) ? taps->mlp_rows : w.counts;
+  HB_CUDA(cudaMemsetAsync(counts, 0, (size_t)m->n_blocks * m->n_rec * 4, st));
+  {
+    ProfScope ps(m->profile, st, HB200_K_EMBED, -1, 0, T, D, 0);
+    HB_PROPAGATE(hb200_embed(ids, m->tok_emb, w.x0, T, D, m->vocab, sqrtf((float)D), st));
+  }
+  __nv_bfloat16 *xin = w.x0, *xout = w.x1;
+  for (int bi = 0; bi < m->n_blocks; ++bi) {
+    HB_PROPAGATE(block_forward(m, bi, xin, xout, B, S, w, taps, counts, err_flag, st));
+    std::swap(xin, xout);
+  }
+  __nv_bfloat16* hid = hidden_out ? (__nv_bfloat16*)hidden_out : xout;
+  {
+    ProfScope ps(m->profile, st, HB200_K_RMS_NORM, m->n_blocks, 0, T, D, 0);
+    HB_PROPAGATE(hb200_rms_norm(xin, m->norm_w, hid, T, D, m->norm_eps, HB200_BF16, HB200_F32, st));
+  }
+  if (logits != nullptr)
+    HB_PROPAGATE(gemm(m, HB200_K_GEMM_LM_HEAD, m->n_blocks, 0, hid, m->tok_emb, logits, T, m->vocab, D, D, D, ld_logits, EPI_STORE, nullptr, 1.0f, nullptr,
+                      nullptr, err_flag, st));
+  return 0;
+}
+
+extern "C" void* hb200_profile_create(int capacity) {
+  if (capacity <= 0) return nullptr;
+  Profile* p = new (std::nothrow) Profile();
+  if (p == nullptr) return nullptr;
+  p->capacity = capacity;
+  p->rec.resize(capacity);
+  p->ev.resize(2 * (size_t)capacity, nullptr);
+  for (auto& e : p->ev) {
+    if (cudaEventCreate(&e) != cudaSuccess) {
+      for (auto& d : p->ev)
+        if (d) cudaEventDestroy(d);
+      delete p;
+      set_error("profile_create: cudaEventCreate failed");
+      return nullptr;
+    }
+  }
+  return p;
+}
+
+extern "C" void hb200_profile_destroy(void* profile) {
+  Profile* p = static_cast<Profile*>(profile);
+  if (p == nullptr) return;
+  for (auto& e : p->ev)
+    if (e) cudaEventDestroy(e);
+  delete p;
+}
+
+extern "C" int hb200_profile_reset(void* profile) {
+  HB_REQUIRE(profile != nullptr, HB200_ERR_INVALID, "profile_reset: null handle");
+  static_cast<Profile*>(profile)->count = 0;
+  return 0;
+}
+
+extern "C" int hb200_profile_read(void* profile, hb200_launch_record* records, float* ms, int max_records) {
+  HB_REQUIRE(profile != nullptr && records != nullptr && ms != nullptr, HB200_ERR_INVALID, "profile_read: null pointer");
+  Profile* p = static_cast<Profile*>(profile);
+  const int n = p->count < max_records ? p->count : max_records;
+  for (int i = 0; i < n; ++i) {
+    records[i] = p->rec[i];
+    HB_CUDA(cudaEventElapsedTime(&ms[i], p->ev[2 * i], p->ev[2 * i + 1]));
+  }
+  return p->count;
+}

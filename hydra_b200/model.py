@@ -1,0 +1,270 @@
+"""Whole-model executor: HydraModel.forward in eval (hydra/model/framework/model.py:408-506) as one call
+into the CUDA extension, fed from a reference ``state_dict`` (key layout: ``tok_emb.weight``,
+``layers.{i}.attention.*``, ``layers.{i}.{norm1,norm2,final_norm}.weight``, ``layers.{i}.mlp.*``,
+``layers.{i}.mor_router.router.*``, ``layers.{i}.mor_executor.*``,
+``layers.{i}.mod_mlp_wrapper.mod_router.router.*``, ``norm.weight``).
+
+Routing is the reference's eval behaviour with MoD enabled (hard top-k at ``mod_capacity`` in the interior
+blocks) and MoR dynamic depth routing; routing decisions stay on the device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from . import _lib, kernels
+from ._pack import PackedBlock, PackedModel, _bf16, _f32
+
+Tensor = torch.Tensor
+
+
+@dataclass
+class Taps:
+    """Routing decisions and per-block outputs of one forward (device tensors)."""
+
+    depths: Tensor            # int32 [NB, B*S]
+    mod_idx: Tensor           # int32 [NB, R, B, k]  ascending positions (valid for blocks that carry MoD)
+    mod_scores: Tensor        # fp32  [NB, R, B*S]
+    router_logits: Tensor     # fp32  [NB, B*S]
+    mlp_rows: Tensor          # int32 [NB, R] rows whose MLP result was used
+    block_out: Optional[Tensor] = None   # bf16 [NB, B*S, D]
+
+
+def mod_k(seq_len: int, capacity: float) -> int:
+    """k = max(1, min(L, int(L * clamp(cap, 1e-4, 1))))  (hydra/routing/mixture_of_depths.py:179-181)."""
+    cap = float(min(max(capacity, 1e-4), 1.0))
+    return max(1, min(seq_len, int(seq_len * cap)))
+
+
+def random_state_dict(*, vocab_size: int = 50257, dim: int, n_mor_blocks: int, recursions_per_block: int, n_heads: int,
+                      n_kv_heads: int, compression_factor: int = 4, mlp_ratio: float = 2.67,
+                      mod_capacity: float = 0.5, seed: int = 0, device="cuda") -> Dict[str, Tensor]:
+    """Seeded random-init weights of a HydraModel architecture, generated on `device`, with the reference's
+    key names and init distributions (hydra/model/framework/model.py:351-374: Linear / Embedding / Conv1d
+    N(0, 0.02), o_proj and down scaled by 1/sqrt(2*blocks*recursions), norm gains 1, recursion_bias 0,
+    recursion_embed N(0, 0.02), key_temperature sqrt(head_dim); depth-router bias
+    logit(0.2 + 0.3*i/(blocks-1)) and MoD-router bias logit(capacity), hydra/routing/base.py:16-19).
+    Synthetic stand-in for a checkpoint; the draw order is this function's own."""
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    lat = dim // compression_factor
+    hd = lat // n_heads
+    kvd = n_kv_heads * hd
+    F = ((int(dim * mlp_ratio) + 255) // 256) * 256
+    R, NB = recursions_per_block, n_mor_blocks
+    res = 1.0 / math.sqrt(2 * NB * R)
+
+    def nrm(*shape, std=0.02):
+        return torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * std
+
+    def logit(p):
+        p = min(max(p, 1e-4), 1 - 1e-4)
+        return math.log(p / (1 - p))
+
+    sd: Dict[str, Tensor] = {"tok_emb.weight": nrm(vocab_size, dim), "norm.weight": torch.ones(dim, device=dev)}
+    for i in range(NB):
+        pre = f"layers.{i}."
+        sd[pre + "attention.qkv_proj.weight"] = nrm(lat + 2 * kvd, dim)
+        sd[pre + "attention.o_proj.weight"] = nrm(dim, lat) * res
+        sd[pre + "attention.q_conv.conv1.weight"] = nrm(lat, hd, 3)
+        sd[pre + "attention.q_conv.conv2.weight"] = nrm(lat, lat, 3)
+        sd[pre + "attention.k_conv.conv1.weight"] = nrm(kvd, hd, 3)
+        sd[pre + "attention.k_conv.conv2.weight"] = nrm(kvd, kvd, 3)
+        sd[pre + "attention.key_temperature"] = torch.full((1,), float(hd ** 0.5), device=dev)
+        for n in ("norm1", "norm2", "final_norm"):
+            sd[pre + n + ".weight"] = torch.ones(dim, device=dev)
+        sd[pre + "mlp.gate_up.weight"] = nrm(2 * F, dim)
+        sd[pre + "mlp.down.weight"] = nrm(dim, F) * res
+        sd[pre + "mor_router.router.weight"] = nrm(1, dim)
+        sd[pre + "mor_router.router.bias"] = torch.tensor([logit(0.2 + 0.3 * i / max(1, NB - 1))], device=dev)
+        sd[pre + "mor_executor.recursion_bias"] = torch.zeros(R, 1, 1, dim, device=dev)
+        sd[pre + "mor_executor.recursion_embed.weight"] = nrm(R, dim)
+        if 0 < i < NB - 1 and mod_capacity and mod_capacity > 0:
+            sd[pre + "mod_mlp_wrapper.mod_router.router.weight"] = nrm(1, dim)
+            sd[pre + "mod_mlp_wrapper.mod_router.router.bias"] = torch.tensor([logit(mod_capacity)], device=dev)
+    return sd
+
+
+class HydraB200Model:
+    """Inference-only HYDRA model on one B200.
+
+    Args mirror ``HydraModel`` (model.py:180-215) where they affect the eval forward; shapes that the
+    ``state_dict`` determines (vocab, dim, blocks, recursions, MLP width) are read from it.
+    """
+
+    def __init__(self, state_dict: Dict[str, Tensor], *, n_heads: int, n_kv_heads: int, compression_factor: int = 4,
+                 max_seq_len: int = 2048, mod_capacity: float = 0.5, mor_min_depth: int = 0, adaptive: bool = True,
+                 device: str | torch.device = "cuda", norm_eps: float = 1e-6, gemm_impl: int = 0):
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise RuntimeError("HydraB200Model needs a CUDA device (there is no CPU fallback)")
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        sd = {(k[len("_orig_mod."):] if k.startswith("_orig_mod.") else k): v for k, v in state_dict.items()}
+        V, D = sd["tok_emb.weight"].shape
+        nb = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("layers."))
+        R = sd["layers.0.mor_executor.recursion_embed.weight"].shape[0]
+        F = sd["layers.0.mlp.down.weight"].shape[1]
+        lat = D // compression_factor
+        hd = lat // n_heads
+        self.vocab_size, self.dim, self.n_mor_blocks, self.recursions_per_block = V, D, nb, R
+        self.n_heads, self.n_kv_heads, self.head_dim, self.ffn_hidden = n_heads, n_kv_heads, hd, F
+        self.max_seq_len, self.mod_capacity, self.mor_min_depth, self.adaptive = max_seq_len, mod_capacity, mor_min_depth, adaptive
+        self.device = dev
+        with kernels._on(dev):
+            blocks = [PackedBlock(sd, f"layers.{i}.", dev) for i in range(nb)]
+            self.has_mod = [b.tensors["mod_w"] is not None for b in blocks]
+            self.packed = PackedModel(
+                vocab=V, dim=D, n_rec=R, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=hd, ffn_hidden=F,
+                min_depth=mor_min_depth, adaptive=adaptive, max_seq_len=max_seq_len, mod_capacity=mod_capacity,
+                norm_eps=norm_eps, residual_scale=0.5,
+                output_scale=float(os.environ.get("HYDRA_CCGQA_OUTPUT_SCALE", "1.0")), blocks=blocks,
+                tok_emb=_bf16(sd["tok_emb.weight"], dev), norm_w=_f32(sd["norm.weight"], dev), device=dev,
+                gemm_impl=gemm_impl)
+        self.ld_logits = (V + 7) // 8 * 8
+        self._logits: Optional[Tensor] = None
+        self.last_taps: Optional[Taps] = None
+
+    # -- reference-compatible conveniences ----------------------------------------------------------------------
+    def eval(self):
+        return self
+
+    def set_global_step(self, step: int) -> None:
+        """The reference enables MoD hard routing in eval only after its warm-up step
+        (hydra/model/framework/blocks.py:136-140); here it is always enabled, so this is a no-op."""
+
+    @classmethod
+    def from_reference(cls, model, **overrides) -> "HydraB200Model":
+        """Build from a reference ``HydraModel`` instance (reads its shape attributes and state_dict)."""
+        kw = dict(n_heads=model.n_heads, n_kv_heads=model.n_kv_heads, compression_factor=model.compression_factor,
+                  max_seq_len=model.max_seq_len, mod_capacity=model.mod_capacity,
+                  mor_min_depth=getattr(model, "mor_min_depth", 0), adaptive=model.adaptive)
+        kw.update(overrides)
+        return cls(model.state_dict(), **kw)
+
+    # -- forward ---------------------------------------------------------------------------------------------------
+    def _alloc_taps(self, B: int, S: int, block_out: bool) -> Taps:
+        NB, R, T = self.n_mor_blocks, self.recursions_per_block, B * S
+        k = mod_k(S, self.mod_capacity)
+        d = self.device
+        return Taps(depths=torch.zeros((NB, T), dtype=torch.int32, device=d),
+                    mod_idx=torch.zeros((NB, R, B, k), dtype=torch.int32, device=d),
+                    mod_scores=torch.zeros((NB, R, T), dtype=torch.float32, device=d),
+                    router_logits=torch.zeros((NB, T), dtype=torch.float32, device=d),
+                    mlp_rows=torch.zeros((NB, R), dtype=torch.int32, device=d),
+                    block_out=torch.zeros((NB, T, self.dim), dtype=torch.bfloat16, device=d) if block_out else None)
+
+    def forward(self, ids: Tensor, *, taps: bool = False, forced: Optional[Taps] = None, block_out: bool = False,
+                logits: bool = True, hidden: bool = False):
+        """ids int64 [B, S] on this model's device -> logits bf16 [B, S, vocab] (a view of a buffer whose rows are
+        padded to a multiple of 8 columns; the buffer is reused by the next call with the same shape).
+
+        taps=True records routing decisions in ``self.last_taps``; ``forced`` replays the decisions of an earlier
+        run (its ``depths`` and ``mod_idx``).  hidden=True returns the post-norm hidden state instead/as well.
+        """
+        if not ids.is_cuda or ids.device != self.device:
+            raise RuntimeError(f"ids must be on {self.device} (there is no CPU fallback)")
+        if ids.dim() != 2:
+            raise ValueError("ids must be [batch, seq_len]")
+        B, S = ids.shape
+        ids = ids.to(torch.int64).contiguous()
+        pm = self.packed
+        ws = pm.workspace(B, S)
+        T = B * S
+        out = None
+        if logits:
+            if self._logits is None or self._logits.shape[0] != T:
+                self._logits = None
+                self._logits = torch.empty((T, self.ld_logits), dtype=torch.bfloat16, device=self.device)
+            out = self._logits
+        hid = torch.empty((T, self.dim), dtype=torch.bfloat16, device=self.device) if hidden else None
+        tp = None
+        tstruct = None
+        if forced is not None:
+            tp = Taps(depths=forced.depths.contiguous(), mod_idx=forced.mod_idx.contiguous(),
+                      mod_scores=torch.zeros_like(forced.mod_scores), router_logits=torch.zeros_like(forced.router_logits),
+                      mlp_rows=torch.zeros_like(forced.mlp_rows),
+                      block_out=torch.zeros((self.n_mor_blocks, T, self.dim), dtype=torch.bfloat16, device=self.device)
+                      if block_out else None)
+        elif taps or block_out:
+            tp = self._alloc_taps(B, S, block_out)
+        if tp is not None:
+            tstruct = _lib.Taps(depths=tp.depths.data_ptr(), mod_idx=tp.mod_idx.data_ptr(),
+                                mod_scores=tp.mod_scores.data_ptr(), router_logits=tp.router_logits.data_ptr(),
+                                mlp_rows=tp.mlp_rows.data_ptr(),
+                                block_out=tp.block_out.data_ptr() if tp.block_out is not None else None,
+                                force_routing=1 if forced is not None else 0)
+        with kernels._on(self.device):
+            _lib.check(_lib.lib().hb200_model_forward(
+                C.byref(pm.struct), ids.data_ptr(), B, S, ws.data_ptr(), ws.numel(),
+                out.data_ptr() if out is not None else None, self.ld_logits,
+                hid.data_ptr() if hid is not None else None, C.byref(tstruct) if tstruct is not None else None,
+                pm.err_flag.data_ptr(), kernels._stream(self.device)), "model_forward")
+        self.last_taps = tp
+        lg = out[:, :self.vocab_size].view(B, S, self.vocab_size) if out is not None else None
+        if hidden and logits:
+            return lg, hid.view(B, S, self.dim)
+        if hidden:
+            return hid.view(B, S, self.dim)
+        return lg
+
+    __call__ = forward
+
+    def forward_hidden(self, ids: Tensor) -> Tensor:
+        """Post-norm hidden states [B, S, dim] (HydraModel.forward_hidden, model.py:508-520)."""
+        return self.forward(ids, logits=False, hidden=True)
+
+    def prefill(self, ids_host: Tensor, out_host: Optional[Tensor] = None) -> Tensor:
+        """End-to-end prefill from host memory: copies ids [B, S] (ideally pinned) to the device, runs the full
+        forward (all logits are computed and stay resident in HBM), and returns the last position's logits
+        [B, vocab] in host memory - what a decoder needs next."""
+        ids = ids_host.to(self.device, non_blocking=True)
+        lg = self.forward(ids)
+        last = lg[:, -1, :]
+        if out_host is None:
+            out_host = torch.empty(last.shape, dtype=last.dtype, pin_memory=True)
+        out_host.copy_(last, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return out_host
+
+    def check_device_errors(self) -> None:
+        self.packed.check_device_errors()
+
+    # -- per-launch timing (CUDA events recorded by the executor around every kernel it enqueues) ------------------
+    def enable_profile(self, capacity: int = 4096) -> None:
+        h = _lib.lib().hb200_profile_create(int(capacity))
+        if not h:
+            raise _lib.Hb200Error("could not create the launch recorder")
+        self._profile, self._profile_cap = h, int(capacity)
+        self.packed.struct.profile = h
+
+    def disable_profile(self) -> None:
+        if getattr(self, "_profile", None):
+            self.packed.struct.profile = None
+            _lib.lib().hb200_profile_destroy(self._profile)
+            self._profile = None
+
+    def read_profile(self, reset: bool = True) -> List[dict]:
+        """After a synchronise: one dict per recorded launch (kind, block, rec, m, n, k, ms)."""
+        cap = self._profile_cap
+        recs = (_lib.LaunchRecord * cap)()
+        ms = (C.c_float * cap)()
+        n = _lib.lib().hb200_profile_read(self._profile, recs, ms, cap)
+        if n < 0:
+            _lib.check(n, "profile_read")
+        out = [dict(kind=_lib.KERNEL_KINDS[recs[i].kind], block=recs[i].block, rec=recs[i].rec, m=recs[i].m,
+                    n=recs[i].n, k=recs[i].k, ms=float(ms[i])) for i in range(min(n, cap))]
+        if reset:
+            _lib.lib().hb200_profile_reset(self._profile)
+        return out
+
+    def get_routing_stats(self) -> dict:
+        """Rows whose MLP result was used per (block, recursion) in the last tapped forward."""
+        if self.last_taps is None:
+            return {}
+        return {"mlp_rows": self.last_taps.mlp_rows.cpu().tolist()}

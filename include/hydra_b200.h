@@ -1,0 +1,250 @@
+/*
+ * hydra_b200 — C ABI of the B200 (sm_100a) implementation of HYDRA's inference
+ * forward hot path.
+ *
+ * The reference (mcpirate17/HYDRA) is pure Python + Triton and has no FFI of its
+ * own: its replaceable boundary is a set of Python-level names.  Each entry point
+ * below names the reference interface it stands behind (file:line relative to
+ * the reference project root).  The Python package `hydra_b200` binds these
+ * symbols with ctypes and re-exposes them under the reference's own function
+ * signatures (`hydra.kernels.fused_*`, `hydra.attention.build_hybrid_attention_module`).
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative hb200_status;
+ *     hb200_last_error() returns a thread-local description of the last failure;
+ *   - all data pointers are DEVICE pointers, 16-byte aligned, owned by the caller;
+ *     no entry point allocates or frees device memory, synchronises the device,
+ *     or traps; work is enqueued on `stream` (a cudaStream_t passed as void*);
+ *   - tensors are row-major; "bf16" is the 16-bit brain float bit pattern;
+ *   - entry points are re-entrant per stream.
+ */
+#ifndef HYDRA_B200_H
+#define HYDRA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum hb200_status {
+  HB200_OK = 0,
+  HB200_ERR_INVALID = -1,      /* bad argument (null pointer, unsupported shape, misalignment) */
+  HB200_ERR_CUDA = -2,         /* a CUDA runtime / driver call failed */
+  HB200_ERR_WORKSPACE = -3,    /* workspace too small */
+  HB200_ERR_UNSUPPORTED = -4,  /* shape outside what the kernels are built for */
+  HB200_ERR_DEVICE_WAIT = -5   /* a bounded in-kernel wait ran out (see hb200_gemm_bf16) */
+} hb200_status;
+
+typedef enum hb200_dtype { HB200_F32 = 0, HB200_BF16 = 1, HB200_F16 = 2 } hb200_dtype;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int hb200_version(void);
+/* Thread-local text for the most recent non-zero status returned on this thread. */
+const char* hb200_last_error(void);
+
+/* ---------------------------------------------------------------------------
+ * Exported fused-op semantics  (hydra/kernels/__init__.py:13-38)
+ * ------------------------------------------------------------------------- */
+
+/* fused_rms_norm(x, weight, eps): y = x * rsqrt(mean(x^2) + eps) * w, row-wise.
+ * Replaces hydra/kernels/fused_ops.py:1114-1132 (and RMSNorm / AdaRMSNorm forward,
+ * hydra/layers/common.py:90-118,153-160).  x,y: [rows, dim] of `dtype`; w: [dim] of `w_dtype`. */
+int hb200_rms_norm(const void* x, const void* w, void* y, int64_t rows, int dim, float eps,
+                   int dtype, int w_dtype, void* stream);
+
+/* fused_rope(x, cos, sin): interleaved-pair rotary embedding.
+ * Replaces hydra/kernels/fused_ops.py:240-306.  x: [B,H,S,hd] with element strides
+ * (sb, sh, ss) and unit stride on hd (may be a transposed view); y: contiguous [B,H,S,hd];
+ * cos/sin: fp32 tables, row t at cos + t*table_ld, hd/2 entries per row. */
+int hb200_rope(const void* x, const float* cos_t, const float* sin_t, void* y,
+               int B, int H, int S, int hd, int64_t sb, int64_t sh, int64_t ss,
+               int table_ld, int dtype, void* stream);
+
+/* fused_qk_norm(q, k, scale, temperature): per-head-vector L2 normalisation.
+ * Replaces hydra/kernels/fused_ops.py:474-493.  mode 0: x / max(||x||, 1e-12) * s
+ * (the PyTorch path, fused_ops.py:587-596, also attention.py:260-262);
+ * mode 1: x * rsqrt(sum x^2 + 1e-8) * s (the reference's device kernel, fused_ops.py:350-369).
+ * q: [rows_q, hd], k: [rows_k, hd] contiguous; K is additionally multiplied by temperature. */
+int hb200_qk_norm(const void* q, const void* k, void* q_out, void* k_out, int64_t rows_q,
+                  int64_t rows_k, int hd, float scale, float temperature, int mode, int dtype,
+                  void* stream);
+
+/* fused_swiglu(gate, up) = silu(gate) * up.  Replaces hydra/kernels/fused_ops.py:808-883.
+ * gate/up: [rows, cols] with leading dimensions ld_gate / ld_up (chunk views of one
+ * [rows, 2*cols] buffer are the usual case); out contiguous [rows, cols]. */
+int hb200_swiglu(const void* gate, const void* up, void* out, int64_t rows, int cols,
+                 int64_t ld_gate, int64_t ld_up, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * CCGQA attention block pieces  (hydra/attention/backends/ccgqa/attention.py:201-331)
+ * ------------------------------------------------------------------------- */
+
+/* Dense contraction C = epilogue(A @ W^T) on the tcgen05 tensor cores; A [M,K], W [N,K] bf16.
+ * Stands for every nn.Linear on the path (attention.py:122-124,205,330;
+ * hydra/layers/common.py:221-230; hydra/model/framework/model.py:343,506).
+ *   epilogue 0  STORE        C[m,n]        = acc                       (C bf16 [M,N], ld ldc)
+ *   epilogue 1  RESID        C[m,n]        = resid[m,n] + alpha*acc    (resid bf16, ld ldc)
+ *   epilogue 2  SWIGLU       C[m,j]        = silu(g)*u, W rows interleaved in groups of 8:
+ *                            row 16*i+r is gate row 8*i+r (r<8) or up row 8*i+r-8 (r>=8);
+ *                            C is [M, N/2]
+ *   epilogue 3  SCATTER_ADD  C[rows[m], n] += acc  (rows int32 [M], each target row once)
+ * m_dev, when non-null, is a device int32 holding the live row count (<= M); rows beyond it
+ * are neither computed into C nor read from `rows`.
+ * impl 0 = tcgen05/TMEM/TMA kernel (product path); impl 1 = plain mma.sync kernel kept as an
+ * independent cross-check for tests.
+ * err_flag: optional device int32; set non-zero if a bounded in-kernel wait ran out (the kernel
+ * then returns without hanging; outputs are undefined). */
+int hb200_gemm_bf16(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda,
+                    int64_t ldw, int64_t ldc, int epilogue, const void* resid, float alpha,
+                    const int32_t* rows, const int32_t* m_dev, int impl, int32_t* err_flag,
+                    void* stream);
+
+/* Interleave a [2F, K] gate_up weight (gate rows then up rows, hydra/layers/common.py:225-226)
+ * into the row order epilogue 2 expects. */
+int hb200_interleave_gate_up(const void* w_gate_up, void* w_out, int F, int K, void* stream);
+
+/* Repack Conv1d weights [C, C/groups, 3] (kernels/fused_conv.py:22-37) to [C, 3*(C/groups)]
+ * with element (c_out, j*cin + c_in) = w[c_out, c_in, j], bf16 -> bf16. */
+int hb200_repack_conv_weight(const void* w, void* w_out, int c_out, int c_in, void* stream);
+
+/* Everything between qkv_proj and SDPA in one kernel (attention.py:208-266,
+ * kernels/fused_conv.py:39-62): value shift, grouped k=3 causal conv, dense k=3 causal conv,
+ * QK-mean coupling, L2 norm with key temperature, RoPE.
+ * qkv [B,S,lat+2*kvd] bf16 -> q [B,H,S,hd], k [B,KV,S,hd], v [B,KV,S,hd] bf16.
+ * w1_qk: repacked conv1 weights, q rows then k rows: [lat+kvd, 3*hd];
+ * w2_q [lat, 3*lat], w2_k [kvd, 3*kvd] repacked conv2 weights; cos/sin fp32 [>=S, hd/2];
+ * key_temperature: device fp32 scalar. */
+int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k,
+                              const float* cos_t, const float* sin_t, const float* key_temperature,
+                              void* q, void* k, void* v, int B, int S, int H, int KV, int hd,
+                              void* stream);
+
+/* Causal grouped-query attention in the latent space (attention.py:288-327):
+ * o[b,t,h,:] = softmax_causal(q[b,h] k[b,h/(H/KV)]^T * scale) v[b,h/(H/KV)].
+ * q [B,H,S,hd], k/v [B,KV,S,hd] bf16; o token-major [B,S,H*hd] bf16. */
+int hb200_attention_causal_gqa(const void* q, const void* k, const void* v, void* o, int B, int S,
+                               int H, int KV, int hd, float scale, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Routing  (hydra/routing/mixture_of_depths.py:159-216, mixture_of_recursions.py:251-291,
+ *           hydra/model/framework/blocks.py:243-269)
+ * ------------------------------------------------------------------------- */
+
+/* MoD selection: for each of B rows of fp32 scores [B,L], the ascending indices of the k
+ * largest (torch.topk + torch.sort, mixture_of_depths.py:187, blocks.py:261).  Among scores
+ * equal to the k-th largest the lowest indices are taken; NaN ranks above +inf.
+ * idx_out int32 [B,k].  If depth (int32 [B,L]) and rows_out are given, the flat token ids
+ * b*L+pos of the selected positions with depth >= min_active_depth are appended to rows_out
+ * and counted in *count (device int32, must be zero on entry). */
+int hb200_mod_topk_select(const float* scores, int B, int L, int k, int32_t* idx_out,
+                          const int32_t* depth, int min_active_depth, int32_t* rows_out,
+                          int32_t* count, void* stream);
+
+/* MoR depth assignment from raw router logits (mixture_of_recursions.py:268-289):
+ * depth = clamp(round_half_even(min_d + sigmoid(3*tanh(l/2))*(R-1-min_d)), min_d, R-1). */
+int hb200_mor_depths(const float* logits, int32_t* depth, int64_t n, int n_rec, int min_depth,
+                     void* stream);
+
+/* Token embedding (hydra/model/framework/model.py:51-73,427): ids clamped into [0,V),
+ * rows gathered and scaled.  ids int64 [T]; table bf16 [V,D]; out bf16 [T,D]. */
+int hb200_embed(const int64_t* ids, const void* table, void* out, int64_t T, int D, int V,
+                float scale, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Whole block / whole model  (hydra/model/framework/blocks.py:608-632,
+ *                             hydra/model/framework/model.py:408-506)
+ * ------------------------------------------------------------------------- */
+
+typedef struct hb200_block_weights {
+  const float* norm1_w;          /* [D] AdaRMSNorm gain before attention */
+  const float* norm2_w;          /* [D] AdaRMSNorm gain before the MLP   */
+  const float* final_norm_w;     /* [D] RMSNorm gain at block exit       */
+  const void* w_qkv;             /* bf16 [lat+2*kvd, D]                  */
+  const void* w_o;               /* bf16 [D, lat]                        */
+  const void* w1_qk;             /* bf16 repacked conv1 (q rows, k rows) */
+  const void* w2_q;              /* bf16 repacked conv2 for q            */
+  const void* w2_k;              /* bf16 repacked conv2 for k            */
+  const float* key_temperature;  /* device fp32 [1]                      */
+  const void* w_gate_up;         /* bf16 [2F, D], interleaved            */
+  const void* w_down;            /* bf16 [D, F]                          */
+  const float* mor_w;            /* fp32 [D] depth-router weight         */
+  const float* mor_b;            /* fp32 [1] depth-router bias           */
+  const float* rec;              /* fp32 [R, D] recursion_bias + recursion_embed */
+  const float* mod_w;            /* fp32 [D] MoD router weight, or NULL  */
+  const float* mod_b;            /* fp32 [1] MoD router bias, or NULL    */
+} hb200_block_weights;
+
+typedef struct hb200_model {
+  int32_t vocab, dim, n_blocks, n_rec, n_heads, n_kv_heads, head_dim, ffn_hidden;
+  int32_t min_depth, adaptive, max_seq_len, gemm_impl;
+  float mod_capacity, norm_eps, residual_scale, output_scale;
+  const void* tok_emb;            /* bf16 [V, D] (also the tied output projection) */
+  const float* norm_w;            /* fp32 [D] */
+  const float* rope_cos;          /* fp32 [max_seq_len, hd/2] */
+  const float* rope_sin;
+  const hb200_block_weights* blocks;   /* HOST array of n_blocks entries */
+  void* profile;                  /* optional hb200_profile handle (see below), or NULL */
+} hb200_model;
+
+/* Optional routing taps / forced routing for one forward (device pointers or NULL). */
+typedef struct hb200_taps {
+  int32_t* depths;        /* int32 [NB, B*S]: written; read instead if force_routing */
+  int32_t* mod_idx;       /* int32 [NB, R, B, k]: ascending MoD indices; read if force_routing */
+  float* mod_scores;      /* fp32 [NB, R, B*S] (written only) */
+  float* router_logits;   /* fp32 [NB, B*S] raw depth-router logits (written only) */
+  int32_t* mlp_rows;      /* int32 [NB, R]: rows whose MLP result was used (always written) */
+  void* block_out;        /* bf16 [NB, B*S, D] block outputs (written only) */
+  int32_t force_routing;  /* 1: take depths and mod_idx from the buffers above */
+} hb200_taps;
+
+/* Bytes of workspace hb200_model_forward needs for a [B,S] batch. */
+size_t hb200_model_workspace_bytes(const hb200_model* m, int B, int S);
+
+/* HydraModel.forward in eval (model.py:408-506): ids int64 [B,S] -> logits bf16 [B*S, ld_logits]
+ * (ld_logits >= vocab, multiple of 8).  `hidden_out` (bf16 [B*S, D], optional) receives the
+ * post-norm hidden state (forward_hidden).  If logits is NULL the output projection is skipped.
+ * err_flag: device int32, set non-zero if a bounded in-kernel wait ran out. */
+int hb200_model_forward(const hb200_model* m, const int64_t* ids, int B, int S, void* workspace,
+                        size_t workspace_bytes, void* logits, int64_t ld_logits, void* hidden_out,
+                        const hb200_taps* taps, int32_t* err_flag, void* stream);
+
+/* One HydraMoRBlock forward (blocks.py:608-632) on x bf16 [B*S, D] -> y bf16 [B*S, D];
+ * `block_index` selects the taps slot. Same workspace as the model. */
+int hb200_block_forward(const hb200_model* m, int block_index, const void* x, void* y, int B, int S,
+                        void* workspace, size_t workspace_bytes, const hb200_taps* taps,
+                        int32_t* err_flag, void* stream);
+
+/* CCGQAAttention.forward (attention.py:201-331) on x bf16 [B*S, D] -> y bf16 [B*S, D]
+ * (y = o_proj(attn) * output_scale; no residual). Uses blocks[block_index] weights. */
+int hb200_ccgqa_forward(const hb200_model* m, int block_index, const void* x, void* y, int B, int S,
+                        void* workspace, size_t workspace_bytes, int32_t* err_flag, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Measurement aid (no counterpart in the reference): per-launch CUDA-event timing of the kernels that
+ * hb200_model_forward / hb200_block_forward / hb200_ccgqa_forward enqueue.  When hb200_model.profile holds a
+ * handle, every kernel launch of the executor is bracketed by two events recorded on the launching stream.
+ * ------------------------------------------------------------------------- */
+typedef enum hb200_kernel_kind {
+  HB200_K_GEMM_QKV = 0, HB200_K_GEMM_O = 1, HB200_K_GEMM_GATE_UP = 2, HB200_K_GEMM_DOWN = 3,
+  HB200_K_GEMM_LM_HEAD = 4, HB200_K_RMS_NORM = 5, HB200_K_PRE_ATTENTION = 6, HB200_K_ATTENTION = 7,
+  HB200_K_MOR_SCORE = 8, HB200_K_SELECT = 9, HB200_K_NORM_GATHER = 10, HB200_K_EMBED = 11, HB200_K_OTHER = 12
+} hb200_kernel_kind;
+
+/* One record per launch: kind, block, recursion, M (upper bound for device-counted launches), N, K. */
+typedef struct hb200_launch_record { int32_t kind, block, rec, m, n, k; } hb200_launch_record;
+
+/* Create a recorder able to hold `capacity` launches (events are created here, once). NULL on failure. */
+void* hb200_profile_create(int capacity);
+void hb200_profile_destroy(void* profile);
+/* Forget the recorded launches (call between measured steps, after reading). */
+int hb200_profile_reset(void* profile);
+/* After the stream has been synchronised: copies up to `max_records` records and their durations in
+ * milliseconds; returns the number of launches recorded since the last reset (negative on error). */
+int hb200_profile_read(void* profile, hb200_launch_record* records, float* ms, int max_records);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HYDRA_B200_H */

@@ -1,0 +1,157 @@
+"""CPU-side checks of the drop-in boundary: the C-ABI library loads and exports every declared symbol, the
+registry / factory behave like the reference's (tests/test_attention_{registry,factory}.py semantics), the
+product path refuses CPU tensors instead of falling back, and install() rebinds the reference's names."""
+import ctypes
+import os
+import re
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from hydra_b200 import _lib, build
+    with open(os.path.join(ROOT, "include", "hydra_b200.h")) as f:
+        declared = sorted(set(re.findall(r"\b(hb200_[a-z0-9_]+)\s*\(", f.read())))
+    assert len(declared) >= 20
+    handle = _lib.lib()
+    for name in declared:
+        assert hasattr(handle, name), f"{name} declared in include/hydra_b200.h but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == set(declared)
+    assert handle.hb200_version() >= 100
+    assert os.path.dirname(build.LIB_PATH).endswith("hydra_b200"), "the extension must live in-tree"
+
+
+def test_struct_layouts_match_header_sizes():
+    from hydra_b200 import _lib
+    assert ctypes.sizeof(_lib.BlockWeights) == 16 * 8
+    assert ctypes.sizeof(_lib.Model) == 12 * 4 + 4 * 4 + 6 * 8
+    assert ctypes.sizeof(_lib.Taps) == 6 * 8 + 8
+    assert ctypes.sizeof(_lib.LaunchRecord) == 24
+
+
+def test_host_side_argument_validation_without_a_gpu():
+    """Argument checks run before any CUDA call, so they can be exercised on a CPU-only machine."""
+    from hydra_b200 import _lib
+    L = _lib.lib()
+    assert L.hb200_rms_norm(None, None, None, 4, 8, 1e-6, 1, 0, None) == -1
+    assert b"null" in L.hb200_last_error()
+    assert L.hb200_mod_topk_select(None, 1, 8, 4, None, None, 0, None, None, None) == -1
+    assert L.hb200_gemm_bf16(None, None, None, 1, 1, 1, 8, 8, 8, 0, None, 1.0, None, None, 0, None, None) == -1
+    assert L.hb200_model_workspace_bytes(None, 1, 1) == 0
+    assert L.hb200_profile_reset(None) == -1
+
+
+def test_registry_matches_reference_semantics():
+    from hydra_b200.attention import (HybridAttentionBackend, available_hybrid_attention_backends,
+                                      is_hybrid_attention_backend_available, resolve_hybrid_attention_backend)
+    assert available_hybrid_attention_backends() == ("ccqa",)
+    for name in ("ccqa", "CCGQA", "  ccgqa ", "CcQa"):
+        assert is_hybrid_attention_backend_available(name)
+        assert resolve_hybrid_attention_backend(name) == HybridAttentionBackend("ccqa")
+    assert resolve_hybrid_attention_backend(None).name == "ccqa"
+    assert not is_hybrid_attention_backend_available("lla3")
+    for bad in ("lla3", "flash", ""):
+        with pytest.raises(ValueError):
+            resolve_hybrid_attention_backend(bad)
+
+
+def test_factory_builds_module_with_reference_parameter_layout(monkeypatch):
+    from hydra_b200.attention import CCGQAAttention, build_hybrid_attention_module
+    m = build_hybrid_attention_module("ccgqa", dim=1024, n_heads=8, n_kv_heads=2, max_seq_len=128, compression_factor=4,
+                                      attention_kwargs={"mod_mlp_capacity": 0.5, "mor_warmup": 10, "use_fused_kernel": True})
+    assert isinstance(m, CCGQAAttention)
+    assert (m.latent_dim, m.head_dim, m.kv_dim, m.n_groups) == (256, 32, 64, 4)
+    shapes = {k: tuple(v.shape) for k, v in m.state_dict().items()}
+    assert shapes == {
+        "key_temperature": (1,), "qkv_proj.weight": (384, 1024), "o_proj.weight": (1024, 256),
+        "q_conv.conv1.weight": (256, 32, 3), "q_conv.conv2.weight": (256, 256, 3),
+        "k_conv.conv1.weight": (64, 32, 3), "k_conv.conv2.weight": (64, 64, 3)}
+    assert float(m.key_temperature) == pytest.approx(32 ** 0.5)
+    assert m.cos_cached.shape == (1, 1, 128, 16) and m.cos_cached.dtype == torch.float32
+    m._init_rope(256)
+    assert m.cos_cached.shape[2] == 256
+    with pytest.raises(ValueError):
+        build_hybrid_attention_module("lla3", dim=1024, n_heads=8, n_kv_heads=2, max_seq_len=128,
+                                      compression_factor=4, attention_kwargs={})
+    monkeypatch.setenv("HYDRA_CCQA_USE_FUSED_KERNEL", "0")
+    m2 = build_hybrid_attention_module("ccqa", dim=512, n_heads=8, n_kv_heads=2, max_seq_len=64, compression_factor=4,
+                                       attention_kwargs={})
+    assert m2.use_fused_kernel is False
+    with pytest.raises(NotImplementedError):
+        build_hybrid_attention_module("ccqa", dim=512, n_heads=8, n_kv_heads=2, max_seq_len=64, compression_factor=4,
+                                      attention_kwargs={"use_convs": False})
+
+
+def test_product_path_refuses_cpu_tensors():
+    import hydra_b200.kernels as K
+    from hydra_b200.attention import build_hybrid_attention_module
+    x = torch.randn(2, 8)
+    for call in (lambda: K.fused_rms_norm(x, torch.ones(8)), lambda: K.fused_swiglu(x, x),
+                 lambda: K.fused_qk_norm(x.view(1, 1, 2, 8), x.view(1, 1, 2, 8), 1.0),
+                 lambda: K.fused_rope(x.view(1, 1, 2, 8), torch.ones(2, 4), torch.zeros(2, 4))):
+        with pytest.raises(RuntimeError, match="CUDA"):
+            call()
+    m = build_hybrid_attention_module("ccqa", dim=512, n_heads=8, n_kv_heads=2, max_seq_len=64, compression_factor=4,
+                                      attention_kwargs={})
+    with pytest.raises(RuntimeError, match="CUDA"):
+        m(torch.randn(1, 4, 512))
+    from hydra_b200.model import HydraB200Model
+    with pytest.raises(RuntimeError, match="CUDA"):
+        HydraB200Model({}, n_heads=8, n_kv_heads=2, device="cpu")
+    st = K.get_kernel_status()
+    for key in ("triton_available", "use_triton_kernels", "fused_rope", "fused_qk_norm", "fused_swiglu",
+                "fused_rms_norm", "liger_ce_available", "use_liger_ce"):
+        assert key in st
+
+
+def test_nothing_in_the_package_imports_the_oracle():
+    pkg = os.path.join(ROOT, "hydra_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh")):
+                with open(os.path.join(dirpath, f)) as fh:
+                    text = fh.read()
+                assert "hydra_oracle" not in text and "import oracle" not in text and "from oracle" not in text, f
+
+
+class _FakeHydra:
+    """A stand-in for the reference package layout, enough for install() to patch."""
+
+
+def test_install_rebinds_reference_names_and_uninstall_restores(monkeypatch):
+    import types
+    mods = {}
+    def mk(name, **attrs):
+        m = types.ModuleType(name)
+        for k, v in attrs.items():
+            setattr(m, k, v)
+        mods[name] = m
+        monkeypatch.setitem(sys.modules, name, m)
+        return m
+    orig = lambda *a, **k: "reference"
+    mk("hydra")
+    mk("hydra.kernels", fused_rope=orig, fused_qk_norm=orig, fused_swiglu=orig, fused_rms_norm=orig)
+    mk("hydra.kernels.fused_ops", fused_rope=orig, fused_qk_norm=orig, fused_swiglu=orig, fused_rms_norm=orig)
+    mk("hydra.layers"); mk("hydra.layers.common", fused_swiglu=orig, fused_rms_norm=orig, FUSED_KERNELS_AVAILABLE=False)
+    mk("hydra.attention", build_hybrid_attention_module=orig, resolve_hybrid_attention_backend=orig,
+       available_hybrid_attention_backends=orig, is_hybrid_attention_backend_available=orig)
+    mk("hydra.attention.factory", build_hybrid_attention_module=orig)
+    mk("hydra.attention.backends"); mk("hydra.attention.backends.ccgqa")
+    mk("hydra.attention.backends.ccgqa.attention", fused_rope=orig, FUSED_KERNELS_AVAILABLE=False)
+    mk("hydra.model"); mk("hydra.model.framework"); mk("hydra.model.framework.blocks", build_hybrid_attention_module=orig)
+    from hydra_b200 import install as I, kernels as K, attention as A
+    done = I.install()
+    assert mods["hydra.layers.common"].fused_swiglu is K.fused_swiglu
+    assert mods["hydra.layers.common"].FUSED_KERNELS_AVAILABLE is True
+    assert mods["hydra.attention.backends.ccgqa.attention"].fused_rope is K.fused_rope
+    assert mods["hydra.model.framework.blocks"].build_hybrid_attention_module is A.build_hybrid_attention_module
+    assert "hydra.kernels" in done and "hydra.attention.factory" in done
+    I.uninstall()
+    assert mods["hydra.layers.common"].fused_swiglu is orig
+    assert mods["hydra.model.framework.blocks"].build_hybrid_attention_module is orig
+    assert mods["hydra.layers.common"].FUSED_KERNELS_AVAILABLE is False

@@ -1,0 +1,152 @@
+"""CCGQA attention block on the GPU against the oracle / reference fixtures: fused pre-attention kernel,
+attention core, whole module through the reference's factory entry point.  bf16 tolerances are stated per check."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import hydra_oracle as O
+from tests import golden_io as G
+from tests.gpu_util import assert_close_bf16, bf16_round, max_abs, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+FIXTURES = ["ccgqa_hd32.npz", "ccgqa_hd16.npz", "ccgqa_kv3.npz", "ccgqa_mha.npz"]
+
+
+@pytest.fixture(scope="module")
+def L():
+    from hydra_b200 import _lib
+    return _lib
+
+
+def pre_attention_gpu(L, qkv_bf16, w, cfg, S_tab=None):
+    from hydra_b200._pack import repack_conv, rope_tables
+    B, S, _ = qkv_bf16.shape
+    H, KV, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+    dev = torch.device("cuda", torch.cuda.current_device())
+    w1 = torch.cat([repack_conv(w["attn.q_conv.conv1.weight"], dev), repack_conv(w["attn.k_conv.conv1.weight"], dev)], 0).contiguous()
+    w2q = repack_conv(w["attn.q_conv.conv2.weight"], dev)
+    w2k = repack_conv(w["attn.k_conv.conv2.weight"], dev)
+    cos, sin = rope_tables(S_tab or S, hd, dev)
+    temp = w["attn.key_temperature"].float().cuda()
+    q = torch.full((B, H, S, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    k = torch.full((B, KV, S, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    v = torch.full((B, KV, S, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    L.check(L.lib().hb200_ccgqa_pre_attention(qkv_bf16.data_ptr(), w1.data_ptr(), w2q.data_ptr(), w2k.data_ptr(),
+                                              cos.data_ptr(), sin.data_ptr(), temp.data_ptr(), q.data_ptr(),
+                                              k.data_ptr(), v.data_ptr(), B, S, H, KV, hd,
+                                              torch.cuda.current_stream().cuda_stream), "pre_attention")
+    torch.cuda.synchronize()
+    return q, k, v
+
+
+@pytest.mark.parametrize("name", FIXTURES)
+def test_fused_pre_attention_kernel(L, name):
+    """Input: the reference's qkv rounded to bf16.  Oracle: fp32 on those same rounded values.  q and k are unit
+    vectors (k times the temperature), so the tolerance is absolute: 3 * 2^-8 of the vector norm, which covers the
+    bf16 rounding of the conv1 intermediate and of the output."""
+    fx, cfg, w = G.attention_fixture(name)
+    qkv = bf16_round(torch.from_numpy(fx["qkv"]))
+    B, S, _ = qkv.shape
+    cos, sin = O.rope_tables(S, cfg.head_dim)
+    rq, rk, rv = O.ccgqa_pre_attention(qkv, w, "attn.", cfg, cos, sin)
+    q, k, v = pre_attention_gpu(L, qkv.to(torch.bfloat16).cuda(), w, cfg)
+    assert torch.isfinite(q.float()).all() and torch.isfinite(k.float()).all() and torch.isfinite(v.float()).all()
+    temp = float(w["attn.key_temperature"])
+    assert max_abs(q, rq) <= 3 * 2 ** -8, f"q max abs {max_abs(q, rq):.4g}"
+    assert max_abs(k, rk) <= 3 * 2 ** -8 * temp, f"k max abs {max_abs(k, rk):.4g}"
+    assert torch.equal(v.float().cpu(), rv), "value shift is a pure copy and must be bit-exact"
+    assert rel_l2(q, rq) < 4e-3 and rel_l2(k, rk) < 4e-3
+
+
+def test_pre_attention_ragged_lengths_and_tile_boundaries(L):
+    """Sequence lengths around the 64-token tile (1, 2, 63, 64, 65, 129) and batch > 1: every sequence restarts its
+    causal padding; compare with the oracle run per sequence."""
+    fx, cfg, w = G.attention_fixture("ccgqa_hd16.npz")
+    g = torch.Generator().manual_seed(5)
+    for S in (1, 2, 63, 64, 65, 129):
+        qkv = bf16_round(torch.randn(3, S, cfg.latent_dim + 2 * cfg.kv_dim, generator=g))
+        cos, sin = O.rope_tables(S, cfg.head_dim)
+        rq, rk, rv = O.ccgqa_pre_attention(qkv, w, "attn.", cfg, cos, sin)
+        q, k, v = pre_attention_gpu(L, qkv.to(torch.bfloat16).cuda(), w, cfg)
+        temp = float(w["attn.key_temperature"])
+        assert max_abs(q, rq) <= 3 * 2 ** -8 and max_abs(k, rk) <= 3 * 2 ** -8 * temp, f"S={S}"
+        assert torch.equal(v.float().cpu(), rv), f"S={S}"
+
+
+@pytest.mark.parametrize("hd,H,KV,S", [(32, 8, 2, 300), (16, 8, 2, 257), (16, 12, 3, 64), (64, 2, 2, 130), (32, 2, 1, 1)])
+def test_attention_core(L, hd, H, KV, S):
+    """softmax is computed in fp32 from bf16 q,k,v; P is rounded to bf16 before PV: 2 bf16 ulps of the output scale."""
+    g = torch.Generator().manual_seed(7)
+    B = 2
+    q = torch.nn.functional.normalize(torch.randn(B, H, S, hd, generator=g), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(B, KV, S, hd, generator=g), dim=-1) * math.sqrt(hd)
+    v = torch.randn(B, KV, S, hd, generator=g)
+    q, k, v = bf16_round(q), bf16_round(k), bf16_round(v)
+    ref = O.causal_gqa_attention(q, k, v).transpose(1, 2).reshape(B, S, H * hd)
+    o = torch.full((B, S, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    qc, kc, vc = (t.to(torch.bfloat16).cuda().contiguous() for t in (q, k, v))
+    L.check(L.lib().hb200_attention_causal_gqa(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), B, S, H, KV,
+                                               hd, 1.0 / math.sqrt(hd), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.isfinite(o.float()).all()
+    assert_close_bf16(o, ref, ulps=2.0, what=f"attention hd={hd}")
+    assert rel_l2(o, ref) < 5e-3
+
+
+@pytest.mark.parametrize("name", FIXTURES)
+def test_module_through_factory_matches_reference_output(name):
+    """build_hybrid_attention_module -> load the reference state_dict -> forward, against the reference's own fp32
+    output.  Tolerance: rel-L2 1e-2 and max-abs 3% of the output range (bf16 storage between the four kernels)."""
+    from hydra_b200.attention import build_hybrid_attention_module
+    fx, cfg, w = G.attention_fixture(name)
+    m = build_hybrid_attention_module("ccgqa", dim=cfg.dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads,
+                                      max_seq_len=cfg.max_seq_len, compression_factor=4, attention_kwargs={})
+    missing, unexpected = m.load_state_dict({k[len("attn."):]: v for k, v in w.items()}, strict=True)
+    m = m.cuda()
+    x = G.tensor(fx["x"])
+    y = m(x.to(torch.bfloat16).cuda())
+    assert y.dtype == torch.bfloat16 and y.shape == x.shape
+    m._packed.check_device_errors()
+    ref = torch.from_numpy(fx["y"])
+    r, a = rel_l2(y, ref), max_abs(y, ref)
+    print(f"{name}: rel_l2 {r:.3e} max_abs {a:.3e} (ref range {float(ref.abs().max()):.3g})")
+    assert r < 1e-2 and a < 0.03 * float(ref.abs().max())
+    # fp32 input is accepted (computed in bf16) and returns fp32
+    y32 = m(x.cuda())
+    assert y32.dtype == torch.float32 and rel_l2(y32, ref) < 1e-2
+    # helper kept for API parity
+    q = torch.randn(1, cfg.n_heads, 8, cfg.head_dim, device="cuda")
+    c, s = O.rope_tables(8, cfg.head_dim)
+    assert max_abs(m._apply_rope(q, 8), O.rope(q.cpu(), c, s)) < 1e-5
+    with pytest.raises(NotImplementedError):
+        m(x.cuda(), mask=torch.ones(x.shape[:2], device="cuda"))
+
+
+def test_config2_block_batch_independence_and_determinism():
+    """BASELINE config 2 (B=8, S=2048, dim 1024, 8q/2kv, hd 32, temperature 1.0) is too large for the CPU oracle in
+    a unit test; check size-independent properties instead: running the batch equals running each sequence alone
+    (bit-exact: no kernel mixes sequences), a causal prefix is unchanged by what follows it, and two runs agree
+    bit for bit."""
+    from hydra_b200.attention import build_hybrid_attention_module
+    torch.manual_seed(1)
+    m = build_hybrid_attention_module("ccgqa", dim=1024, n_heads=8, n_kv_heads=2, max_seq_len=2048,
+                                      compression_factor=4, attention_kwargs={})
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() >= 2:
+                torch.nn.init.xavier_uniform_(p)
+        m.key_temperature.fill_(1.0)
+    m = m.cuda()
+    x = torch.randn(8, 2048, 1024, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    y = m(x)
+    y2 = m(x)
+    assert torch.equal(y, y2)
+    solo = m(x[3:4])
+    assert torch.equal(solo[0], y[3])
+    prefix = m(x[:, :1000])
+    assert torch.equal(prefix[5], y[5, :1000])
+    assert torch.isfinite(y.float()).all()
+    m._packed.check_device_errors()
