@@ -77,6 +77,8 @@ def _rms_norm_op(x: Tensor, weight: Tensor, eps: float) -> Tensor:
         w = w.float()
     y = torch.empty_like(xc)
     rows = xc.numel() // dim if dim else 0
+    if rows == 0:
+        return y
     with _on(dev):
         _lib.check(_lib.lib().hb200_rms_norm(xc.data_ptr(), w.data_ptr(), y.data_ptr(), rows, dim, float(eps),
                                              _dtype_code(xc), _dtype_code(w), _stream(dev)), "fused_rms_norm")
@@ -105,6 +107,8 @@ def _rope_op(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
     if x.stride(3) != 1 and x.numel() > 0:
         x = x.contiguous()
     y = torch.empty((B, H, S, hd), dtype=x.dtype, device=x.device)
+    if y.numel() == 0:
+        return y
     with _on(dev):
         _lib.check(_lib.lib().hb200_rope(x.data_ptr(), cos.data_ptr(), sin.data_ptr(), y.data_ptr(), B, H, S, hd,
                                          x.stride(0), x.stride(1), x.stride(2), cos.stride(0), _dtype_code(x),
@@ -125,9 +129,15 @@ def _qk_norm_op(q: Tensor, k: Tensor, scale: float, temperature: float, mode: in
     hd = q.shape[-1]
     qc, kc = q.contiguous(), k.contiguous()
     qo, ko = torch.empty_like(qc), torch.empty_like(kc)
+    if qc.numel() + kc.numel() == 0:
+        return qo, ko
+    if qc.numel() == 0 or kc.numel() == 0:   # an empty tensor has a null data pointer: give the kernel a valid one
+        dummy = torch.zeros(hd, dtype=q.dtype, device=q.device)
+        qc = qc if qc.numel() else dummy
+        kc = kc if kc.numel() else dummy
     with _on(dev):
         _lib.check(_lib.lib().hb200_qk_norm(qc.data_ptr(), kc.data_ptr(), qo.data_ptr(), ko.data_ptr(),
-                                            qc.numel() // hd, kc.numel() // hd, hd, float(scale), float(temperature),
+                                            qo.numel() // hd, ko.numel() // hd, hd, float(scale), float(temperature),
                                             int(mode), _dtype_code(qc), _stream(dev)), "fused_qk_norm")
     return qo, ko
 

@@ -17,12 +17,13 @@ def bf16_round(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.bfloat16).to(torch.float32)
 
 
-def assert_close_bf16(got: torch.Tensor, ref: torch.Tensor, *, ulps: float = 2.0, what: str = "") -> None:
-    """|got - ref| <= ulps * 2^-8 * max(|ref|, floor) elementwise, floor = 2^-8 * max|ref| (bf16 has an 8-bit
-    mantissa; the floor keeps near-zero outputs of a sum of O(max) terms from demanding absolute exactness)."""
+def assert_close_bf16(got: torch.Tensor, ref: torch.Tensor, *, ulps: float = 2.0, what: str = "",
+                      floor_frac: float = 2.0 ** -4) -> None:
+    """|got - ref| <= ulps * 2^-8 * max(|ref|, floor_frac * max|ref|) elementwise (bf16 has an 8-bit mantissa;
+    the floor keeps near-zero outputs of a sum of O(max) terms from demanding absolute exactness)."""
     got, ref = got.double().cpu(), ref.double().cpu()
     scale = ref.abs().max().clamp_min(1e-30)
-    tol = ulps * 2.0 ** -8 * torch.maximum(ref.abs(), scale * 2.0 ** -4)
+    tol = ulps * 2.0 ** -8 * torch.maximum(ref.abs(), scale * floor_frac)
     bad = (got - ref).abs() > tol
     if bad.any():
         i = int(((got - ref).abs() / tol).argmax())

@@ -78,7 +78,9 @@ def test_pre_attention_ragged_lengths_and_tile_boundaries(L):
 
 @pytest.mark.parametrize("hd,H,KV,S", [(32, 8, 2, 300), (16, 8, 2, 257), (16, 12, 3, 64), (64, 2, 2, 130), (32, 2, 1, 1)])
 def test_attention_core(L, hd, H, KV, S):
-    """softmax is computed in fp32 from bf16 q,k,v; P is rounded to bf16 before PV: 2 bf16 ulps of the output scale."""
+    """softmax is computed in fp32 from bf16 q,k,v; the probabilities are rounded to bf16 before PV, so every output
+    (a convex combination of values of the size of the output range) carries an ABSOLUTE error of about 2^-9 of
+    that range: tolerance 1 bf16 ulp of the output range elementwise, rel-L2 5e-3 overall."""
     g = torch.Generator().manual_seed(7)
     B = 2
     q = torch.nn.functional.normalize(torch.randn(B, H, S, hd, generator=g), dim=-1)
@@ -92,7 +94,7 @@ def test_attention_core(L, hd, H, KV, S):
                                                hd, 1.0 / math.sqrt(hd), torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     assert torch.isfinite(o.float()).all()
-    assert_close_bf16(o, ref, ulps=2.0, what=f"attention hd={hd}")
+    assert_close_bf16(o, ref, ulps=1.0, floor_frac=1.0, what=f"attention hd={hd}")
     assert rel_l2(o, ref) < 5e-3
 
 
