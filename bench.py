@@ -311,7 +311,24 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=32, help="sequences per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", default=None, help="run one single-kernel microbenchmark instead of the model "
+                    "(gemm, ccgqa_block, pre_attention, attention, rms_norm, rope, swiglu_ffn, swiglu_act)")
+    ap.add_argument("--m", type=int, default=16384)
+    ap.add_argument("--n", type=int, default=5632)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--epilogue", default="swiglu", choices=["store", "resid", "swiglu", "scatter"])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--gemm-impl", dest="impl_gemm", type=int, default=0)
     args = ap.parse_args()
+    if args.micro is not None:
+        from hydra_b200 import microbench
+        if args.micro != "gemm":
+            args.batch = 8 if args.batch == 32 else args.batch
+        args.impl = args.impl_gemm
+        names = list(microbench.CASES) if args.micro == "all" else [args.micro]
+        for nm in names:
+            print(json.dumps(microbench.run(nm, args, ROOT)), flush=True)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -70,7 +70,7 @@ class PackedBlock:
         t["w2_k"] = repack_conv(sd[a + "k_conv.conv2.weight"], device)
         t["key_temperature"] = _f32(sd[a + "key_temperature"], device).reshape(1)
         for k in ("norm1_w", "norm2_w", "final_norm_w", "w_gate_up", "w_down", "mor_w", "mor_b", "rec",
-                  "mod_w", "mod_b"):
+                  "mod_wn", "mod_b"):
             t[k] = None
         if not attention_only:
             t["norm1_w"] = _f32(sd[pre + "norm1.weight"], device)
@@ -86,7 +86,8 @@ class PackedBlock:
             t["rec"] = (_f32(rb, device).reshape(re.shape[0], -1) + _f32(re, device)).contiguous()
             mk = pre + "mod_mlp_wrapper.mod_router.router."
             if mk + "weight" in sd:
-                t["mod_w"] = _f32(sd[mk + "weight"], device).reshape(-1)
+                # Linear(norm(x)) = rsqrt(..) * sum x_d * (gain_d * w_d): fold the norm gain into the router weight
+                t["mod_wn"] = (_f32(sd[mk + "weight"], device).reshape(-1) * t["norm2_w"]).contiguous()
                 t["mod_b"] = _f32(sd[mk + "bias"], device).reshape(1)
         self.tensors = t
         self.struct = _lib.BlockWeights(**{k: (v.data_ptr() if v is not None else None) for k, v in t.items()})

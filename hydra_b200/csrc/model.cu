@@ -10,7 +10,8 @@
 //   cur = x + 0.5*scale * o Wo^T                          tcgen05 GEMM, residual epilogue
 //   depth = MoR router(cur)                               mor_score kernel (recursion 0)
 //   for r < R:
-//     s    = MoD router(AdaRMSNorm(cur + rec_r))          mor_score kernel (all tokens, no activation written)
+//     s    = MoD router(AdaRMSNorm(cur + rec_r))          mor_score kernel (all tokens, streaming, nothing written
+//                                                         but the scores)
 //     rows = topk(s) AND depth >= r   (or depth >= r)     mod_select / compact_active kernel -> device row list
 //     ug   = AdaRMSNorm(cur[rows] + rec_r)                norm_gather kernel (compact)
 //     act  = silu(ug Wg^T) * (ug Wu^T)                    tcgen05 GEMM, SwiGLU epilogue, device row count
@@ -111,31 +112,65 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ w, int D, int
   return warp_sum(s);
 }
 
-// One warp per token.  Optionally: depth-router logit/depth from the raw row; MoD score from the normalised row.
+// Router pass over ALL tokens, streaming (no activation is written): four rows per warp so that the per-column
+// vectors are fetched once per four rows.
+//   MoD score   s = rsqrt(mean((x+rec)^2) + eps) * sum_d (x_d + rec_d) * wn_d + b,  wn = norm2 gain * MoD weight
+//               (the fp32 value of Linear(AdaRMSNorm(x + rec)) without rounding the normalised row to bf16)
+//   MoR depth   from l = sum_d x_d * mor_w_d + b on the raw row (recursion 0 only)
+constexpr int SCORE_ROWS = 4;
 __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __restrict__ cur,
-                                                        const float* __restrict__ rec, const float* __restrict__ w2,
-                                                        const float* __restrict__ mod_w, const float* __restrict__ mod_b,
+                                                        const float* __restrict__ rec, const float* __restrict__ mod_wn,
+                                                        const float* __restrict__ mod_b,
                                                         const float* __restrict__ mor_w, const float* __restrict__ mor_b,
                                                         float* __restrict__ scores, float* __restrict__ logits,
                                                         int32_t* __restrict__ depth, int64_t T, int D, float eps,
                                                         int n_rec, int min_d) {
   const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= T) return;
-  float v[ROW_NCH][8];
-  if (mor_w != nullptr) {
-    load_row_add(cur + row * D, nullptr, D, lane, v);
-    const float l = dot_row(mor_w, D, lane, v) + mor_b[0];
-    if (lane == 0) {
-      if (logits != nullptr) logits[row] = l;
-      if (depth != nullptr) depth[row] = mor_depth_from_logit(l, n_rec, min_d);
+  const int64_t row0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * SCORE_ROWS;
+  if (row0 >= T) return;
+  float ss[SCORE_ROWS], dm[SCORE_ROWS], lm[SCORE_ROWS];
+#pragma unroll
+  for (int r = 0; r < SCORE_ROWS; ++r) ss[r] = dm[r] = lm[r] = 0.f;
+  for (int i = lane * 8; i < D; i += 256) {
+    float wn[8], rc[8], wr[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wn[j] = rc[j] = wr[j] = 0.f;
+    if (mod_wn != nullptr) {
+      const float4 a0 = *reinterpret_cast<const float4*>(mod_wn + i), a1 = *reinterpret_cast<const float4*>(mod_wn + i + 4);
+      const float4 b0 = *reinterpret_cast<const float4*>(rec + i), b1 = *reinterpret_cast<const float4*>(rec + i + 4);
+      wn[0] = a0.x; wn[1] = a0.y; wn[2] = a0.z; wn[3] = a0.w; wn[4] = a1.x; wn[5] = a1.y; wn[6] = a1.z; wn[7] = a1.w;
+      rc[0] = b0.x; rc[1] = b0.y; rc[2] = b0.z; rc[3] = b0.w; rc[4] = b1.x; rc[5] = b1.y; rc[6] = b1.z; rc[7] = b1.w;
+    }
+    if (mor_w != nullptr) {
+      const float4 a0 = *reinterpret_cast<const float4*>(mor_w + i), a1 = *reinterpret_cast<const float4*>(mor_w + i + 4);
+      wr[0] = a0.x; wr[1] = a0.y; wr[2] = a0.z; wr[3] = a0.w; wr[4] = a1.x; wr[5] = a1.y; wr[6] = a1.z; wr[7] = a1.w;
+    }
+#pragma unroll
+    for (int r = 0; r < SCORE_ROWS; ++r) {
+      if (row0 + r < T) {
+        float x[8];
+        load_bf16x8(cur + (row0 + r) * D + i, x);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xr = x[j] + rc[j];
+          ss[r] += xr * xr;
+          dm[r] += xr * wn[j];
+          lm[r] += x[j] * wr[j];
+        }
+      }
     }
   }
-  if (mod_w != nullptr) {
-    const float ss = load_row_add(cur + row * D, rec, D, lane, v);
-    scale_row(w2, rsqrtf(ss / (float)D + eps), D, lane, v);
-    const float s = dot_row(mod_w, D, lane, v) + mod_b[0];
-    if (lane == 0) scores[row] = s;
+#pragma unroll
+  for (int r = 0; r < SCORE_ROWS; ++r) {
+    const float s2 = warp_sum(ss[r]), d2 = warp_sum(dm[r]), l2 = warp_sum(lm[r]);
+    if (lane == 0 && row0 + r < T) {
+      if (mod_wn != nullptr) scores[row0 + r] = rsqrtf(s2 / (float)D + eps) * d2 + mod_b[0];
+      if (mor_w != nullptr) {
+        const float l = l2 + mor_b[0];
+        if (logits != nullptr) logits[row0 + r] = l;
+        if (depth != nullptr) depth[row0 + r] = mor_depth_from_logit(l, n_rec, min_d);
+      }
+    }
   }
 }
 
@@ -284,7 +319,7 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, _
   const hb200_block_weights& bw = m->blocks[bi];
   const int T = B * S, D = m->dim, F = m->ffn_hidden, R = m->n_rec;
   const bool force = taps && taps->force_routing;
-  const bool has_mod = bw.mod_w != nullptr;
+  const bool has_mod = bw.mod_wn != nullptr;
   const int k = mod_k(S, m->mod_capacity);
   const unsigned row_grid = (unsigned)ceil_div(T, 8);
 
@@ -312,7 +347,7 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, _
     float* scores = (taps && taps->mod_scores) ? taps->mod_scores + ((size_t)bi * R + r) * T : w.scores;
     if (need_router || has_mod) {
       ProfScope ps(m->profile, st, HB200_K_MOR_SCORE, bi, r, T, D, 0);
-      mor_score_kernel<<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, has_mod ? bw.mod_w : nullptr, bw.mod_b,
+      mor_score_kernel<<<(unsigned)ceil_div(T, 8 * SCORE_ROWS), 256, 0, st>>>(w.cur, rec, has_mod ? bw.mod_wn : nullptr, bw.mod_b,
                                                  need_router ? bw.mor_w : nullptr, bw.mor_b, scores, logits,
                                                  force ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth);
       HB_LAUNCH_CHECK();

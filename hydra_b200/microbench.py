@@ -1,0 +1,268 @@
+"""Single-kernel microbenchmarks on the BASELINE configs 2 and 3 shapes (CCGQA block; RMSNorm / RoPE / SwiGLU FFN)
+and on the GEMM shapes of the 250M model.  Run through ``python bench.py --micro NAME`` (one JSON line each) - also
+the small, self-terminating command lines used for ``ncu`` captures.
+
+Timing: CUDA events on the launching stream around ITERS launches after warm-up.  Bandwidth-bound kernels rotate
+through input/output buffer sets whose total size exceeds twice the 126 MB L2, so every launch reads from HBM;
+tensor-bound cases state their working set.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import math
+import os
+from typing import Callable, Dict
+
+import torch
+
+from . import _lib, kernels
+from ._pack import PackedBlock, PackedModel, interleave_gate_up, repack_conv, rope_tables
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _peaks(root: str) -> tuple[dict, str]:
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def _time(fn: Callable[[int], None], iters: int, warmup: int = 3) -> float:
+    """Average milliseconds per call of fn(i)."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def _sets(bytes_per_set: int) -> int:
+    return max(2, int(math.ceil(2.2 * L2_BYTES / max(1, bytes_per_set))))
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _rand_bf16(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------------------------------------
+def gemm(args) -> dict:
+    M, N, K = args.m, args.n, args.k
+    epi = {"store": 0, "resid": 1, "swiglu": 2, "scatter": 3}[args.epilogue]
+    n_out = N // 2 if epi == 2 else N
+    ldc = (n_out + 7) // 8 * 8
+    per_set = M * K * 2 + M * ldc * 2
+    ns = min(_sets(per_set), 4)
+    A = [_rand_bf16(M, K, seed=i) for i in range(ns)]
+    W = _rand_bf16(N, K, scale=0.03, seed=99)
+    Cs = [torch.zeros(M, ldc, dtype=torch.bfloat16, device="cuda") for _ in range(ns)]
+    X = _rand_bf16(M, ldc, seed=7) if epi == 1 else None
+    rows = torch.randperm(M, device="cuda").to(torch.int32) if epi == 3 else None
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib = _lib.lib()
+
+    def run(i):
+        j = i % ns
+        _lib.check(lib.hb200_gemm_bf16(A[j].data_ptr(), W.data_ptr(), Cs[j].data_ptr(), M, N, K, K, K, ldc, epi,
+                                       X.data_ptr() if X is not None else None, 0.5,
+                                       rows.data_ptr() if rows is not None else None, None, args.impl,
+                                       err.data_ptr(), _stream()))
+
+    ms = _time(run, args.iters)
+    assert int(err.item()) == 0
+    flops = 2.0 * M * N * K
+    return {"kernel": f"gemm_{'tcgen05' if args.impl == 0 else 'mma'} {args.epilogue}", "shape": [M, N, K], "ms": ms,
+            "bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "algorithmic_flops": flops, "working_set_mb": (per_set * ns + N * K * 2) / 1e6}
+
+
+def _attention_module(dim=1024, H=8, KV=2, S=2048, temperature=1.0):
+    from .attention import build_hybrid_attention_module
+    torch.manual_seed(1)
+    m = build_hybrid_attention_module("ccgqa", dim=dim, n_heads=H, n_kv_heads=KV, max_seq_len=S, compression_factor=4,
+                                      attention_kwargs={})
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() >= 2:
+                torch.nn.init.xavier_uniform_(p)
+        if temperature is not None:
+            m.key_temperature.fill_(temperature)
+    return m.cuda()
+
+
+def ccgqa_block(args) -> dict:
+    """BASELINE config 2: one CCGQA attention block, B=8 x S=2048 x dim 1024, 8q/2kv heads of 32, bf16, causal,
+    Xavier-uniform weights (seed 1), key temperature 1.0.  46.51 GFLOP and 68.9 MB of minimum traffic per call."""
+    B, S, D = args.batch, 2048, 1024
+    m = _attention_module()
+    ns = _sets(B * S * D * 2 * 2)
+    xs = [_rand_bf16(B, S, D, seed=i) for i in range(ns)]
+    m(xs[0])
+    pm = m._packed
+    prof = _lib.lib().hb200_profile_create(64)
+    pm.struct.profile = prof
+    ms = _time(lambda i: m(xs[i % ns]), args.iters)
+    _lib.lib().hb200_profile_reset(prof)
+    m(xs[0])
+    torch.cuda.synchronize()
+    recs = (_lib.LaunchRecord * 64)()
+    t = (C.c_float * 64)()
+    n = _lib.lib().hb200_profile_read(prof, recs, t, 64)
+    parts = {_lib.KERNEL_KINDS[recs[i].kind]: float(t[i]) for i in range(n)}
+    pm.struct.profile = None
+    _lib.lib().hb200_profile_destroy(prof)
+    pm.check_device_errors()
+    T, lat, kvd, hd = B * S, 256, 64, 32
+    flops = T * (2 * D * (lat + 2 * kvd) + 6 * (lat * hd + lat * lat + kvd * hd + kvd * kvd) + 4 * lat * (S + 1) / 2 + 2 * lat * D)
+    return {"kernel": "ccgqa_block (qkv GEMM + fused pre-attention + attention + o_proj GEMM)", "shape": [B, S, D],
+            "ms": ms, "bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "algorithmic_flops": flops, "parts_ms": parts}
+
+
+def pre_attention(args) -> dict:
+    """Fused pre-attention kernel at config-2 shapes: reads qkv once, writes q,k,v once: 1536 B/token + 0.47 MB."""
+    B, S, H, KV, hd = args.batch, 2048, 8, 2, 32
+    lat, kvd = H * hd, KV * hd
+    m = _attention_module()
+    sd = m.state_dict()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    w1 = torch.cat([repack_conv(sd["q_conv.conv1.weight"], dev), repack_conv(sd["k_conv.conv1.weight"], dev)], 0).contiguous()
+    w2q, w2k = repack_conv(sd["q_conv.conv2.weight"], dev), repack_conv(sd["k_conv.conv2.weight"], dev)
+    cos, sin = rope_tables(S, hd, dev)
+    temp = torch.ones(1, device="cuda")
+    per_set = B * S * (lat + 2 * kvd) * 2 * 2
+    ns = _sets(per_set)
+    qkv = [_rand_bf16(B, S, lat + 2 * kvd, seed=i) for i in range(ns)]
+    q = [torch.empty(B, H, S, hd, dtype=torch.bfloat16, device="cuda") for _ in range(ns)]
+    k = [torch.empty(B, KV, S, hd, dtype=torch.bfloat16, device="cuda") for _ in range(ns)]
+    v = [torch.empty(B, KV, S, hd, dtype=torch.bfloat16, device="cuda") for _ in range(ns)]
+    lib = _lib.lib()
+
+    def run(i):
+        j = i % ns
+        _lib.check(lib.hb200_ccgqa_pre_attention(qkv[j].data_ptr(), w1.data_ptr(), w2q.data_ptr(), w2k.data_ptr(),
+                                                 cos.data_ptr(), sin.data_ptr(), temp.data_ptr(), q[j].data_ptr(),
+                                                 k[j].data_ptr(), v[j].data_ptr(), B, S, H, KV, hd, _stream()))
+
+    ms = _time(run, args.iters)
+    T = B * S
+    nbytes = 4.0 * T * (lat + 2 * kvd) + 6.0 * (lat * hd + lat * lat + kvd * hd + kvd * kvd)
+    flops = 6.0 * T * (lat * hd + lat * lat + kvd * hd + kvd * kvd)
+    return {"kernel": "ccgqa_pre_kernel<32,8,4>", "shape": [B, S, lat + 2 * kvd], "ms": ms, "bound": "hbm",
+            "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "algorithmic_bytes": nbytes,
+            "conv_tflops": flops / (ms * 1e-3) / 1e12}
+
+
+def attention(args) -> dict:
+    B, S, H, KV, hd = args.batch, 2048, 8, 2, 32
+    q = _rand_bf16(B, H, S, hd)
+    q = torch.nn.functional.normalize(q.float(), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(_rand_bf16(B, KV, S, hd, seed=1).float(), dim=-1).to(torch.bfloat16)
+    v = _rand_bf16(B, KV, S, hd, seed=2)
+    o = torch.empty(B, S, H * hd, dtype=torch.bfloat16, device="cuda")
+    lib = _lib.lib()
+    ms = _time(lambda i: _lib.check(lib.hb200_attention_causal_gqa(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                                                    B, S, H, KV, hd, 1.0 / math.sqrt(hd), _stream())),
+               args.iters)
+    flops = 4.0 * B * S * H * hd * (S + 1) / 2
+    return {"kernel": "attention_causal_gqa_kernel<32>", "shape": [B, H, S, hd], "ms": ms, "bound": "tensor",
+            "achieved": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "algorithmic_flops": flops,
+            "note": "exp-throughput limited at head_dim 32: one ex2 per 128 MMA FLOPs"}
+
+
+def rms_norm(args) -> dict:
+    """Config 3: RMSNorm on 16384 x 1024 bf16, gain ~ N(1, 0.02): 4 B/element moved."""
+    T, D = 16384, 1024
+    ns = _sets(T * D * 4)
+    xs = [_rand_bf16(T, D, seed=i) for i in range(ns)]
+    w = (1 + 0.02 * torch.randn(D, device="cuda")).float()
+    ys = [torch.empty_like(x) for x in xs]
+    lib = _lib.lib()
+    ms = _time(lambda i: _lib.check(lib.hb200_rms_norm(xs[i % ns].data_ptr(), w.data_ptr(), ys[i % ns].data_ptr(), T, D,
+                                                       1e-6, 1, 0, _stream())), args.iters)
+    nbytes = 4.0 * T * D + 4 * D
+    return {"kernel": "rms_norm_vec_kernel<bf16,float,4>", "shape": [T, D], "ms": ms, "bound": "hbm",
+            "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "algorithmic_bytes": nbytes}
+
+
+def rope(args) -> dict:
+    """Config 3: RoPE theta 1e4, head_dim 32, positions 0..2047, q-shaped [8,8,2048,32] bf16: 4 B/element moved."""
+    B, H, S, hd = 8, 8, 2048, 32
+    n = B * H * S * hd
+    ns = _sets(n * 4)
+    xs = [_rand_bf16(B, H, S, hd, seed=i) for i in range(ns)]
+    ys = [torch.empty_like(x) for x in xs]
+    cos, sin = rope_tables(S, hd, torch.device("cuda"))
+    lib = _lib.lib()
+    ms = _time(lambda i: _lib.check(lib.hb200_rope(xs[i % ns].data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                                   ys[i % ns].data_ptr(), B, H, S, hd, H * S * hd, S * hd, hd, hd // 2, 1,
+                                                   _stream())), args.iters)
+    nbytes = 4.0 * n
+    return {"kernel": "rope_kernel<bf16,vec>", "shape": [B, H, S, hd], "ms": ms, "bound": "hbm",
+            "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "algorithmic_bytes": nbytes}
+
+
+def swiglu_ffn(args) -> dict:
+    """Config 3: SwiGLU FFN 1024 -> 2816 -> 1024 on 16384 tokens, weights N(0, 0.02): 283.5 GFLOP; the activation is
+    fused into the gate_up GEMM epilogue, so the [T, 2*2816] intermediate never reaches HBM."""
+    T, D, F = 16384, 1024, 2816
+    x = _rand_bf16(T, D)
+    wgu = interleave_gate_up(_rand_bf16(2 * F, D, scale=0.02, seed=1), torch.device("cuda", torch.cuda.current_device()))
+    wd = _rand_bf16(D, F, scale=0.02, seed=2)
+    act = torch.empty(T, F, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib = _lib.lib()
+
+    def run(i):
+        _lib.check(lib.hb200_gemm_bf16(x.data_ptr(), wgu.data_ptr(), act.data_ptr(), T, 2 * F, D, D, D, F, 2, None, 1.0,
+                                       None, None, 0, err.data_ptr(), _stream()))
+        _lib.check(lib.hb200_gemm_bf16(act.data_ptr(), wd.data_ptr(), y.data_ptr(), T, D, F, F, F, D, 0, None, 1.0,
+                                       None, None, 0, err.data_ptr(), _stream()))
+
+    ms = _time(run, args.iters)
+    assert int(err.item()) == 0
+    flops = 6.0 * T * D * F
+    return {"kernel": "swiglu_ffn (gate_up GEMM + SwiGLU epilogue, down GEMM)", "shape": [T, D, F], "ms": ms,
+            "bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "algorithmic_flops": flops}
+
+
+def swiglu_act(args) -> dict:
+    """The exported fused_swiglu op alone (6*F bytes per token when left unfused)."""
+    T, F = 16384, 2816
+    ns = _sets(T * F * 6)
+    gu = [_rand_bf16(T, 2 * F, seed=i) for i in range(ns)]
+    ms = _time(lambda i: kernels.fused_swiglu(*gu[i % ns].chunk(2, dim=-1)), args.iters)
+    nbytes = 6.0 * T * F
+    return {"kernel": "swiglu_kernel<bf16,vec>", "shape": [T, F], "ms": ms, "bound": "hbm",
+            "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "algorithmic_bytes": nbytes,
+            "note": "includes the torch custom-op dispatch and output allocation"}
+
+
+CASES: Dict[str, Callable] = {
+    "gemm": gemm, "ccgqa_block": ccgqa_block, "pre_attention": pre_attention, "attention": attention,
+    "rms_norm": rms_norm, "rope": rope, "swiglu_ffn": swiglu_ffn, "swiglu_act": swiglu_act,
+}
+
+
+def run(name: str, args, root: str) -> dict:
+    peaks, src = _peaks(root)
+    res = CASES[name](args)
+    if res["bound"] == "hbm":
+        peak = float(peaks["hbm_gbs"])
+    else:
+        peak = float(peaks["bf16_tflops"])   # burst figure: the kernel is timed alone
+    res.update({"micro": name, "peak": peak, "frac": res["achieved"] / peak, "peak_source": src, "iters": args.iters})
+    return res

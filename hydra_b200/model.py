@@ -118,7 +118,7 @@ class HydraB200Model:
         self.device = dev
         with kernels._on(dev):
             blocks = [PackedBlock(sd, f"layers.{i}.", dev) for i in range(nb)]
-            self.has_mod = [b.tensors["mod_w"] is not None for b in blocks]
+            self.has_mod = [b.tensors["mod_wn"] is not None for b in blocks]
             self.packed = PackedModel(
                 vocab=V, dim=D, n_rec=R, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=hd, ffn_hidden=F,
                 min_depth=mor_min_depth, adaptive=adaptive, max_seq_len=max_seq_len, mod_capacity=mod_capacity,

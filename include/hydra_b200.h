@@ -172,7 +172,7 @@ typedef struct hb200_block_weights {
   const float* mor_w;            /* fp32 [D] depth-router weight         */
   const float* mor_b;            /* fp32 [1] depth-router bias           */
   const float* rec;              /* fp32 [R, D] recursion_bias + recursion_embed */
-  const float* mod_w;            /* fp32 [D] MoD router weight, or NULL  */
+  const float* mod_wn;           /* fp32 [D] MoD router weight times the norm2 gain (elementwise), or NULL */
   const float* mod_b;            /* fp32 [1] MoD router bias, or NULL    */
 } hb200_block_weights;
 
