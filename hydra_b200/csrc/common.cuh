@@ -76,23 +76,29 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// 8 bf16 <-> 8 floats through one 16-byte access
-struct alignas(16) bf16x8 { __nv_bfloat162 h[4]; };
-
+// 8 bf16 <-> 8 floats through ONE 16-byte access (explicit uint4: a struct-of-bfloat162 copy is not guaranteed to
+// become a single vector instruction)
 __device__ __forceinline__ void load_bf16x8(const __nv_bfloat16* p, float (&f)[8]) {
-  bf16x8 v = *reinterpret_cast<const bf16x8*>(p);
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 t = __bfloat1622float2(v.h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
+    // bf16 -> fp32 is a 16-bit shift
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
   }
 }
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
 __device__ __forceinline__ void store_bf16x8(__nv_bfloat16* p, const float (&f)[8]) {
-  bf16x8 v;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) v.h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-  *reinterpret_cast<bf16x8*>(p) = v;
+  uint4 raw;
+  raw.x = pack_bf16x2_rn(f[0], f[1]);
+  raw.y = pack_bf16x2_rn(f[2], f[3]);
+  raw.z = pack_bf16x2_rn(f[4], f[5]);
+  raw.w = pack_bf16x2_rn(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = raw;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {

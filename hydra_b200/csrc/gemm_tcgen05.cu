@@ -4,8 +4,8 @@
 //               128B-swizzled shared-memory stages, completion on "full" mbarriers;
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16, kind::f16, fp32 accumulate in TMEM),
 //               tcgen05.commit releases smem stages ("empty") and publishes finished accumulators ("tmem_full");
-//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns per warp, fused epilogue (store / residual / SwiGLU /
-//               scatter-add), then "tmem_empty".
+//   warps 2-9   epilogue: two warps per TMEM lane quadrant, each owning half of the tile's columns; tcgen05.ld of
+//               32 lanes x 32 columns, fused epilogue (store / residual / SwiGLU / scatter-add), then "tmem_empty".
 //
 // TMEM holds two BN-column accumulators so the epilogue of tile i overlaps the mainloop of tile i+1.  The live
 // row count may come from device memory (MoD/MoR compaction), in which case the tile loop bounds are computed
@@ -26,6 +26,8 @@ constexpr int GBM = 128;            // tile rows  (UMMA M)
 constexpr int GBK = 64;             // K per stage = one 128-byte swizzle span of bf16
 constexpr int GROUP_M = 16;         // m-tiles per rasterisation group (keeps an A panel L2-resident)
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+constexpr int EPI_WARPS = 8;        // two per TMEM lane quadrant
+constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;
 
 template <int BN> struct GemmCfg {
   static constexpr int A_BYTES = GBM * GBK * 2;
@@ -163,7 +165,7 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 }
 
 template <int BN>
-__global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                               const __grid_constant__ CUtensorMap tma_b,
                                                               const GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -193,7 +195,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), EPI_WARPS);
     }
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -256,8 +258,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     }
     __syncwarp();
   } else {
-    // ------------------------------ epilogue warps (2..5) ------------------------------
+    // ------------------------------ epilogue warps (2..9) ------------------------------
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;          // which half of the tile's columns this warp drains
+    constexpr int CHUNKS = BN / 32 / (EPI_WARPS / 4);
     int as = 0;
     uint32_t aphase = 0;
     bool ok = true;
@@ -271,7 +275,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const int m = mt * GBM + quad * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(as * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * CHUNKS; c < (half + 1) * CHUNKS; ++c) {
         float v[32];
         tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);   // warp-collective
         const int col = nt * BN + c * 32;
@@ -352,7 +356,7 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
   }
   const int64_t tiles = (int64_t)ceil_div(p.M, GBM) * ceil_div(p.N, BN);
   const int grid = (int)std::min<int64_t>(tiles, sm_count());
-  kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
   HB_LAUNCH_CHECK();
   return 0;
 }
