@@ -69,6 +69,8 @@ SIGNATURES = {
     "hb200_block_forward": (c_i32, [C.POINTER(Model), c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_sz,
                                     C.POINTER(Taps), c_vp, c_vp]),
     "hb200_ccgqa_forward": (c_i32, [C.POINTER(Model), c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_sz, c_vp, c_vp]),
+    "hb200_ccgqa_forward_static_max_bytes": (c_sz, []),
+    "hb200_ccgqa_forward_static": (c_i32, [C.POINTER(Model), c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp]),
     "hb200_profile_create": (c_vp, [c_i32]),
     "hb200_profile_destroy": (None, [c_vp]),
     "hb200_profile_reset": (c_i32, [c_vp]),

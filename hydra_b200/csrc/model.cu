@@ -19,6 +19,7 @@
 //   y = RMSNorm(cur)        (the executor's output accumulator equals the final `cur`: a token stops
 //                            changing after its exit recursion, and it exits exactly once)
 #include <cmath>
+#include <mutex>
 #include <new>
 #include <utility>
 #include <vector>
@@ -440,6 +441,71 @@ extern "C" int hb200_ccgqa_forward(const hb200_model* m, int block_index, const 
   HB_REQUIRE(block_index >= 0 && block_index < m->n_blocks, HB200_ERR_INVALID, "ccgqa_forward: bad block index");
   Workspace w = carve(m, B, S, workspace);
   HB_REQUIRE(workspace_bytes >= w.bytes, HB200_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.bytes);
+  return attention_part(m, block_index, m->blocks[block_index], w, x, nullptr, m->output_scale, y, B, S, err_flag,
+                        (cudaStream_t)stream);
+}
+
+// ---- attention forward on library-owned scratch (no allocation anywhere on the call path) -------------------
+// The intermediates of the attention sub-block (qkv, q, k, v, o) live in this file-scope device array instead of a
+// caller-provided workspace.  Its name is only a host-side handle: the device address is obtained once per device
+// with cudaGetSymbolAddress (below) and that pointer is what the kernels receive.
+constexpr size_t STATIC_SCRATCH_BYTES = (size_t)8 << 20;   // 8 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned char g_attn_scratch[STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+static void* g_attn_scratch_ptr[MAX_DEVICES] = {};
+static std::mutex g_attn_scratch_mutex;
+
+static size_t attention_scratch_bytes(const hb200_model* m, int64_t T, Workspace* w, void* base) {
+  const size_t lat = (size_t)m->n_heads * m->head_dim, kvd = (size_t)m->n_kv_heads * m->head_dim;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    void* p = base ? (void*)((char*)base + off) : nullptr;
+    off += align_up(bytes, 256);
+    return p;
+  };
+  __nv_bfloat16* qkv = (__nv_bfloat16*)take((size_t)T * (lat + 2 * kvd) * 2);
+  __nv_bfloat16* q = (__nv_bfloat16*)take((size_t)T * lat * 2);
+  __nv_bfloat16* k = (__nv_bfloat16*)take((size_t)T * kvd * 2);
+  __nv_bfloat16* v = (__nv_bfloat16*)take((size_t)T * kvd * 2);
+  __nv_bfloat16* o = (__nv_bfloat16*)take((size_t)T * lat * 2);
+  if (w != nullptr) {
+    *w = Workspace{};
+    w->qkv = qkv; w->q = q; w->k = k; w->v = v; w->o = o;
+    w->bytes = off;
+  }
+  return off;
+}
+
+extern "C" size_t hb200_ccgqa_forward_static_max_bytes(void) { return STATIC_SCRATCH_BYTES; }
+
+extern "C" int hb200_ccgqa_forward_static(const hb200_model* m, int block_index, const void* x, void* y, int B, int S,
+                                          int32_t* err_flag, void* stream) {
+  HB_PROPAGATE(check_model(m, B, S));
+  HB_REQUIRE(x && y, HB200_ERR_INVALID, "ccgqa_forward_static: null pointer");
+  HB_REQUIRE(block_index >= 0 && block_index < m->n_blocks, HB200_ERR_INVALID, "ccgqa_forward_static: bad block index");
+  const size_t need = attention_scratch_bytes(m, (int64_t)B * S, nullptr, nullptr);
+  HB_REQUIRE(need <= STATIC_SCRATCH_BYTES, HB200_ERR_WORKSPACE,
+             "ccgqa_forward_static: %d x %d tokens need %zu bytes of scratch, the built-in array holds %zu; "
+             "use hb200_ccgqa_forward with a caller-provided workspace for larger batches",
+             B, S, need, STATIC_SCRATCH_BYTES);
+  int dev = -1;
+  HB_CUDA(cudaGetDevice(&dev));
+  HB_REQUIRE(dev >= 0 && dev < MAX_DEVICES, HB200_ERR_UNSUPPORTED, "ccgqa_forward_static: device index %d out of range", dev);
+  void* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_attn_scratch_mutex);
+    if (g_attn_scratch_ptr[dev] == nullptr) {
+      // once per device, with that device current: resolve the symbol to this device's copy of the array
+      void* ptr = nullptr;
+      HB_CUDA(cudaGetSymbolAddress(&ptr, g_attn_scratch));
+      HB_REQUIRE(ptr != nullptr, HB200_ERR_CUDA, "ccgqa_forward_static: cudaGetSymbolAddress returned a null address");
+      g_attn_scratch_ptr[dev] = ptr;
+    }
+    base = g_attn_scratch_ptr[dev];
+  }
+  Workspace w;
+  attention_scratch_bytes(m, (int64_t)B * S, &w, base);
   return attention_part(m, block_index, m->blocks[block_index], w, x, nullptr, m->output_scale, y, B, S, err_flag,
                         (cudaStream_t)stream);
 }

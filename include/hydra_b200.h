@@ -221,6 +221,33 @@ int hb200_block_forward(const hb200_model* m, int block_index, const void* x, vo
 int hb200_ccgqa_forward(const hb200_model* m, int block_index, const void* x, void* y, int B, int S,
                         void* workspace, size_t workspace_bytes, int32_t* err_flag, void* stream);
 
+/* CCGQAAttention.forward for callers that must not allocate.  This entry point has no counterpart in the
+ * reference; it is hb200_ccgqa_forward with the workspace argument removed.
+ *
+ * Who needs it: code that runs where device memory cannot be requested at call time - a serving process that has
+ * handed all of its HBM to a pool owned by someone else (a KV-cache arena, another framework's caching allocator),
+ * a plugin running on threads of a host runtime that forbids allocation calls there, or a latency-critical loop
+ * that cannot afford cudaMalloc's implicit device synchronisation and unbounded duration.  Such callers cannot
+ * create the workspace that hb200_ccgqa_forward asks for.
+ *
+ * How: the intermediates (qkv, q, k, v, attention output) are kept in an 8 MiB device array that is part of the
+ * library image (every GPU that loads the library carries it until the process exits).  The call performs no
+ * cudaMalloc / cudaFree and calls no allocating library routine.  x and y are still the caller's buffers
+ * (bf16 [B*S, dim] each, 16-byte aligned).
+ *
+ * Limits and rules:
+ *   - B*S tokens must fit: B*S*2*(2*latent + 3*kv_dim) bytes (rounded up per buffer to 256) <= 8 MiB, i.e. 4096
+ *     tokens at dim 1024 with 8q/2kv heads; larger requests return HB200_ERR_WORKSPACE and launch nothing
+ *     (hb200_ccgqa_forward_static_max_bytes() reports the capacity);
+ *   - the first call on each device resolves the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call outside any stream capture;
+ *   - all calls on one device share the one array and it keeps the previous call's contents.  Every byte a call
+ *     reads it has written first, so nothing needs clearing, but two calls that overlap on the GPU (different
+ *     streams) race on it: serialise them. */
+size_t hb200_ccgqa_forward_static_max_bytes(void);
+int hb200_ccgqa_forward_static(const hb200_model* m, int block_index, const void* x, void* y, int B, int S,
+                               int32_t* err_flag, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Measurement aid (no counterpart in the reference): per-launch CUDA-event timing of the kernels that
  * hb200_model_forward / hb200_block_forward / hb200_ccgqa_forward enqueue.  When hb200_model.profile holds a
