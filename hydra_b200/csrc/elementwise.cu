@@ -26,6 +26,21 @@ __device__ __forceinline__ void store_vec(T* p, const float* f) {
   *reinterpret_cast<uint4*>(p) = raw;
 }
 
+// V consecutive weights (fp32 or the activation dtype) through 16-byte loads
+template <typename WT, int V>
+__device__ __forceinline__ void load_weights(const WT* p, float* f) {
+  if constexpr (sizeof(WT) == 4) {
+#pragma unroll
+    for (int j = 0; j < V; j += 4) {
+      const float4 t = *reinterpret_cast<const float4*>(p + j);
+      f[j] = t.x; f[j + 1] = t.y; f[j + 2] = t.z; f[j + 3] = t.w;
+    }
+  } else {
+    static_assert(V == 8, "16-bit weights come with 16-bit activations");
+    load_vec<WT>(p, f);
+  }
+}
+
 // ---------------------------------------------------------------------------------
 // RMSNorm: one warp per row; the row stays in registers between the two passes when it fits.
 // ---------------------------------------------------------------------------------
@@ -55,9 +70,10 @@ __global__ void __launch_bounds__(256) rms_norm_vec_kernel(const T* __restrict__
   for (int c = 0; c < NCH; ++c) {
     const int i = (c * 32 + lane) * V;
     if (i < dim) {
-      float o[V];
+      float o[V], wv[V];
+      load_weights<WT, V>(w + i, wv);
 #pragma unroll
-      for (int j = 0; j < V; ++j) o[j] = v[c][j] * r * Cvt<WT>::to_f(w[i + j]);
+      for (int j = 0; j < V; ++j) o[j] = v[c][j] * r * wv[j];
       store_vec<T>(yr + i, o);
     }
   }
@@ -86,7 +102,7 @@ static int launch_rms_norm(const void* x, const void* w, void* y, int64_t rows, 
   constexpr int V = VecOf<T>::N;
   const int warps = 8;
   const unsigned grid = (unsigned)ceil_div64(rows, warps);
-  const bool vec_ok = (dim % V == 0) && aligned16(x) && aligned16(y);
+  const bool vec_ok = (dim % V == 0) && aligned16(x) && aligned16(y) && aligned16(w);
   if (vec_ok && dim <= 32 * V * 4) {
     rms_norm_vec_kernel<T, WT, 4><<<grid, warps * 32, 0, st>>>((const T*)x, (const WT*)w, (T*)y, rows, dim, eps);
   } else if (vec_ok && dim <= 32 * V * 8) {
@@ -127,9 +143,21 @@ __global__ void __launch_bounds__(256) rope_kernel(const T* __restrict__ x, cons
     f[0] = Cvt<T>::to_f(xp[0]);
     f[1] = Cvt<T>::to_f(xp[1]);
   }
+  float ct[V / 2], stt[V / 2];
+  if (VEC && (V / 2) % 4 == 0) {
+#pragma unroll
+    for (int p = 0; p < V / 2; p += 4) {
+      const float4 a = *reinterpret_cast<const float4*>(c + p), b = *reinterpret_cast<const float4*>(sp + p);
+      ct[p] = a.x; ct[p + 1] = a.y; ct[p + 2] = a.z; ct[p + 3] = a.w;
+      stt[p] = b.x; stt[p + 1] = b.y; stt[p + 2] = b.z; stt[p + 3] = b.w;
+    }
+  } else {
+#pragma unroll
+    for (int p = 0; p < V / 2; ++p) { ct[p] = c[p]; stt[p] = sp[p]; }
+  }
 #pragma unroll
   for (int p = 0; p < V / 2; ++p) {
-    const float cv = c[p], sv = sp[p];
+    const float cv = ct[p], sv = stt[p];
     o[2 * p] = f[2 * p] * cv - f[2 * p + 1] * sv;
     o[2 * p + 1] = f[2 * p] * sv + f[2 * p + 1] * cv;
   }
@@ -145,7 +173,8 @@ template <typename T>
 static int launch_rope(const void* x, const float* cs, const float* sn, void* y, int B, int H, int S, int hd,
                        int64_t sb, int64_t sh, int64_t ss, int table_ld, cudaStream_t st) {
   constexpr int V = VecOf<T>::N;
-  const bool vec = (hd % V == 0) && (sb % V == 0) && (sh % V == 0) && (ss % V == 0) && aligned16(x) && aligned16(y);
+  const bool vec = (hd % V == 0) && (sb % V == 0) && (sh % V == 0) && (ss % V == 0) && aligned16(x) && aligned16(y) &&
+                   (V != 8 || (aligned16(cs) && aligned16(sn) && table_ld % 4 == 0));
   const int64_t rows = (int64_t)B * H * S;
   if (vec) {
     const int64_t units = rows * (hd / V);

@@ -5,7 +5,10 @@
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16, kind::f16, fp32 accumulate in TMEM),
 //               tcgen05.commit releases smem stages ("empty") and publishes finished accumulators ("tmem_full");
 //   warps 2-9   epilogue: two warps per TMEM lane quadrant, each owning half of the tile's columns; tcgen05.ld of
-//               32 lanes x 32 columns, fused epilogue (store / residual / SwiGLU / scatter-add), then "tmem_empty".
+//               32 lanes x 32 columns, fused epilogue, then "tmem_empty".  Plain-store and SwiGLU results are staged
+//               per warp in 128B-swizzled shared memory and written with TMA bulk tensor stores (fully coalesced,
+//               asynchronous, clipped at the matrix edge by the tensor map); the residual and scatter-add epilogues
+//               read-modify-write their rows directly with 16-byte accesses.
 //
 // TMEM holds two BN-column accumulators so the epilogue of tile i overlaps the mainloop of tile i+1.  The live
 // row count may come from device memory (MoD/MoR compaction), in which case the tile loop bounds are computed
@@ -36,7 +39,9 @@ template <int BN> struct GemmCfg {
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + alignment slack
+  static constexpr int STORE_BOX_BYTES = 32 * 128;                 // one TMA store box: 32 rows x 64 bf16
+  static constexpr int STORE_BYTES = EPI_WARPS * STORE_BOX_BYTES;  // one staging box per epilogue warp
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + BAR_BYTES + 1024;   // + alignment slack
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------------------
@@ -92,6 +97,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
       : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int c0, int c1, uint32_t smem_src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(smem_src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -118,6 +133,10 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
@@ -167,18 +186,21 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                               const __grid_constant__ CUtensorMap tma_b,
+                                                              const __grid_constant__ CUtensorMap tma_c,
                                                               const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (s_addr(smem_dyn) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_dyn + (base - s_addr(smem_dyn));
-  const uint32_t bars = base + Cfg::STAGES * Cfg::STAGE_BYTES;
+  const uint32_t store_base = base + Cfg::STAGES * Cfg::STAGE_BYTES;   // 1024-byte aligned
+  const uint32_t bars = store_base + Cfg::STORE_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (Cfg::STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * Cfg::STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * Cfg::STAGES + 2 + a); };
   volatile uint32_t* tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + Cfg::STAGES * Cfg::STAGE_BYTES + 8 * (2 * Cfg::STAGES + 4));
+      reinterpret_cast<volatile uint32_t*>(base_ptr + Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::STORE_BYTES +
+                                           8 * (2 * Cfg::STAGES + 4));
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -262,6 +284,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;          // which half of the tile's columns this warp drains
     constexpr int CHUNKS = BN / 32 / (EPI_WARPS / 4);
+    const bool swiglu = (p.epilogue == EPI_SWIGLU);
+    const bool tma_store = (p.epilogue == EPI_STORE) || swiglu;
+    const int n_out = swiglu ? p.N / 2 : p.N;
+    const uint32_t my_box = store_base + (uint32_t)(warp - 2) * Cfg::STORE_BOX_BYTES;
     int as = 0;
     uint32_t aphase = 0;
     bool ok = true;
@@ -274,18 +300,69 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       tcgen05_fence_after();
       const int m = mt * GBM + quad * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(as * BN);
+      if (tma_store) {
+        // ---- staged path: 64 output columns per box, one box in flight per warp ----
+        constexpr int ACC_PER_BOX = 64;                       // accumulator columns feeding one box (plain store)
+        const int acc_per_box = swiglu ? 2 * ACC_PER_BOX : ACC_PER_BOX;
+        const int boxes = CHUNKS * 32 / acc_per_box;
+        for (int bx = 0; bx < boxes; ++bx) {
+          const int acc0 = half * CHUNKS * 32 + bx * acc_per_box;      // first accumulator column of the box
+          if (lane == 0) bulk_wait_read0();                            // previous box has left shared memory
+          __syncwarp();
+          const uint32_t row_smem = my_box + (uint32_t)lane * 128u;
+          for (int c = 0; c < acc_per_box / 32; ++c) {
+            float v[32];
+            tmem_ld_32x32(t_row + (uint32_t)(acc0 + c * 32), v);       // warp-collective
+            if (swiglu) {
+#pragma unroll
+              for (int h16 = 0; h16 < 2; ++h16) {
+                uint4 o;
+                o.x = pack_bf16x2_rn(silu_mul(v[h16 * 16 + 0], v[h16 * 16 + 8]), silu_mul(v[h16 * 16 + 1], v[h16 * 16 + 9]));
+                o.y = pack_bf16x2_rn(silu_mul(v[h16 * 16 + 2], v[h16 * 16 + 10]), silu_mul(v[h16 * 16 + 3], v[h16 * 16 + 11]));
+                o.z = pack_bf16x2_rn(silu_mul(v[h16 * 16 + 4], v[h16 * 16 + 12]), silu_mul(v[h16 * 16 + 5], v[h16 * 16 + 13]));
+                o.w = pack_bf16x2_rn(silu_mul(v[h16 * 16 + 6], v[h16 * 16 + 14]), silu_mul(v[h16 * 16 + 7], v[h16 * 16 + 15]));
+                const int piece = c * 2 + h16;                         // 16-byte piece inside the 128-byte row
+                st_shared_v4(row_smem + (uint32_t)((piece ^ (lane & 7)) << 4), o);
+              }
+            } else {
+#pragma unroll
+              for (int q8 = 0; q8 < 4; ++q8) {
+                uint4 o;
+                o.x = pack_bf16x2_rn(p.alpha * v[q8 * 8 + 0], p.alpha * v[q8 * 8 + 1]);
+                o.y = pack_bf16x2_rn(p.alpha * v[q8 * 8 + 2], p.alpha * v[q8 * 8 + 3]);
+                o.z = pack_bf16x2_rn(p.alpha * v[q8 * 8 + 4], p.alpha * v[q8 * 8 + 5]);
+                o.w = pack_bf16x2_rn(p.alpha * v[q8 * 8 + 6], p.alpha * v[q8 * 8 + 7]);
+                const int piece = c * 4 + q8;
+                st_shared_v4(row_smem + (uint32_t)((piece ^ (lane & 7)) << 4), o);
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int out_col = swiglu ? (nt * BN + acc0) / 2 : nt * BN + acc0;
+            if (out_col < n_out) {
+              tma_store_2d(&tma_c, out_col, mt * GBM + quad * 32, my_box);
+              bulk_commit();
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
-      for (int c = half * CHUNKS; c < (half + 1) * CHUNKS; ++c) {
-        float v[32];
-        tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);   // warp-collective
-        const int col = nt * BN + c * 32;
-        if (m < M && col < p.N) epilogue_row_chunk<32>(p, m, col, v);
+        for (int c = half * CHUNKS; c < (half + 1) * CHUNKS; ++c) {
+          float v[32];
+          tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);   // warp-collective
+          const int col = nt * BN + c * 32;
+          if (m < M && col < p.N) epilogue_row_chunk<32>(p, m, col, v);
+        }
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(as));
       if (++as == 2) { as = 0; aphase ^= 1u; }
     }
+    if (lane == 0) bulk_wait0();   // this thread's bulk stores have completed before the CTA may exit
+    __syncwarp();
   }
 
   // ------------------------------ teardown ------------------------------
@@ -317,7 +394,8 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
 }
 
 // 2-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld, box = [box_rows, 64 cols].
-static int make_tmap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+static int make_tmap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                     CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B) {
   auto fn = get_encode_fn();
   HB_REQUIRE(fn != nullptr, HB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t gdim[2] = {cols, rows};
@@ -325,7 +403,7 @@ static int make_tmap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t 
   cuuint32_t box[2] = {(cuuint32_t)GBK, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   HB_REQUIRE(r == CUDA_SUCCESS, HB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return 0;
@@ -345,9 +423,16 @@ static int sm_count() {
 template <int BN>
 static int launch_bn(const GemmParams& p, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tc;
   HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, GBM));
   HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, BN));
+  if (p.epilogue == EPI_STORE || p.epilogue == EPI_SWIGLU) {
+    // output map for the staged TMA-store epilogue: boxes of 32 rows x 64 columns, clipped at [M, n_out]
+    const uint64_t n_out = p.epilogue == EPI_SWIGLU ? (uint64_t)p.N / 2 : (uint64_t)p.N;
+    HB_PROPAGATE(make_tmap(&tc, p.C, (uint64_t)p.M, n_out, (uint64_t)p.ldc, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE));
+  } else {
+    tc = ta;   // unused by the direct epilogues
+  }
   auto kern = gemm_tcgen05_kernel<BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -356,14 +441,15 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
   }
   const int64_t tiles = (int64_t)ceil_div(p.M, GBM) * ceil_div(p.N, BN);
   const int grid = (int)std::min<int64_t>(tiles, sm_count());
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, tc, p);
   HB_LAUNCH_CHECK();
   return 0;
 }
 
 int launch_gemm_tcgen05(const GemmParams& p, cudaStream_t st) {
-  // wide tiles unless N is a small multiple of 128 (qkv projection: 384)
-  if (p.N % 256 != 0 && p.N % 128 == 0 && p.N <= 1024) return launch_bn<128>(p, st);
+  // wide tiles unless N is a small multiple of 128 (qkv projection: 384); the SwiGLU epilogue pairs columns inside
+  // 128-column halves of a 256-wide tile and always takes the wide kernel
+  if (p.epilogue != EPI_SWIGLU && p.N % 256 != 0 && p.N % 128 == 0 && p.N <= 1024) return launch_bn<128>(p, st);
   return launch_bn<256>(p, st);
 }
 

@@ -195,6 +195,73 @@ __global__ void __launch_bounds__(256) norm_gather_kernel(const __nv_bfloat16* _
   }
 }
 
+// y = RMSNorm(src; w1) rounded to bf16 (the block output), z = RMSNorm(y; w2) (the next block's pre-attention norm,
+// or the model's final norm): one read of src instead of three passes.  Either output may be omitted.
+__global__ void __launch_bounds__(256) dual_norm_kernel(const __nv_bfloat16* __restrict__ src,
+                                                        const float* __restrict__ w1, __nv_bfloat16* __restrict__ y,
+                                                        const float* __restrict__ w2, __nv_bfloat16* __restrict__ z,
+                                                        int64_t T, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= T) return;
+  float v[ROW_NCH][8];
+  const float ss = load_row_add(src + row * D, nullptr, D, lane, v);
+  scale_row(w1, rsqrtf(ss / (float)D + eps), D, lane, v);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int c = 0; c < ROW_NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) {
+      if (y != nullptr) store_bf16x8(y + row * D + i, v[c]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss2 += v[c][j] * v[c][j];
+    }
+  }
+  if (z == nullptr) return;
+  ss2 = warp_sum(ss2);
+  scale_row(w2, rsqrtf(ss2 / (float)D + eps), D, lane, v);
+#pragma unroll
+  for (int c = 0; c < ROW_NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) store_bf16x8(z + row * D + i, v[c]);
+  }
+}
+
+// x = bf16(table[clamp(id)] * scale), a = AdaRMSNorm(x; w): embedding and the first block's pre-attention norm.
+__global__ void __launch_bounds__(256) embed_norm_kernel(const int64_t* __restrict__ ids,
+                                                         const __nv_bfloat16* __restrict__ table,
+                                                         __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                         __nv_bfloat16* __restrict__ a, int64_t T, int D, int V,
+                                                         float scale, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= T) return;
+  int64_t id = ids[row];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  float v[ROW_NCH][8];
+  load_row_add(table + id * D, nullptr, D, lane, v);
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < ROW_NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[c][j] = __bfloat162float(__float2bfloat16_rn(v[c][j] * scale));
+        ss += v[c][j] * v[c][j];
+      }
+      store_bf16x8(x + row * D + i, v[c]);
+    }
+  }
+  ss = warp_sum(ss);
+  scale_row(w, rsqrtf(ss / (float)D + eps), D, lane, v);
+#pragma unroll
+  for (int c = 0; c < ROW_NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) store_bf16x8(a + row * D + i, v[c]);
+  }
+}
+
 __global__ void fill_i32_kernel(int32_t* p, int64_t n, int32_t val) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) p[i] = val;
@@ -315,7 +382,10 @@ static int attention_part(const hb200_model* m, int bi, const hb200_block_weight
   return 0;
 }
 
-static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, __nv_bfloat16* y, int B, int S,
+// x: block input; a_in: AdaRMSNorm(x; norm1) if the caller already has it (else computed here);
+// y: block output; next_w / a_next: optional gain and destination of the norm that consumes y next.
+static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, const __nv_bfloat16* a_in,
+                         __nv_bfloat16* y, const float* next_w, __nv_bfloat16* a_next, int B, int S,
                          const Workspace& w, const hb200_taps* taps, int32_t* counts, int32_t* err, cudaStream_t st) {
   const hb200_block_weights& bw = m->blocks[bi];
   const int T = B * S, D = m->dim, F = m->ffn_hidden, R = m->n_rec;
@@ -325,11 +395,12 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, _
   const unsigned row_grid = (unsigned)ceil_div(T, 8);
 
   // attention half
-  {
+  if (a_in == nullptr) {
     ProfScope ps(m->profile, st, HB200_K_RMS_NORM, bi, 0, T, D, 0);
     HB_PROPAGATE(hb200_rms_norm(x, bw.norm1_w, w.a, T, D, m->norm_eps, HB200_BF16, HB200_F32, st));
+    a_in = w.a;
   }
-  HB_PROPAGATE(attention_part(m, bi, bw, w, w.a, x, m->residual_scale * m->output_scale, w.cur, B, S, err, st));
+  HB_PROPAGATE(attention_part(m, bi, bw, w, a_in, x, m->residual_scale * m->output_scale, w.cur, B, S, err, st));
 
   // routing buffers: the taps slots double as the working buffers when present
   int32_t* depth = (taps && taps->depths) ? taps->depths + (size_t)bi * T : w.depth;
@@ -376,7 +447,9 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, _
   }
   {
     ProfScope ps(m->profile, st, HB200_K_RMS_NORM, bi, R, T, D, 0);
-    HB_PROPAGATE(hb200_rms_norm(w.cur, bw.final_norm_w, y, T, D, m->norm_eps, HB200_BF16, HB200_F32, st));
+    dual_norm_kernel<<<row_grid, 256, 0, st>>>(w.cur, bw.final_norm_w, y, next_w, next_w ? a_next : nullptr, T, D,
+                                               m->norm_eps);
+    HB_LAUNCH_CHECK();
   }
   if (taps && taps->block_out)
     HB_CUDA(cudaMemcpyAsync((__nv_bfloat16*)taps->block_out + (size_t)bi * T * D, y, (size_t)T * D * 2,
@@ -521,7 +594,8 @@ extern "C" int hb200_block_forward(const hb200_model* m, int block_index, const 
   cudaStream_t st = (cudaStream_t)stream;
   int32_t* counts = (taps && taps->mlp_rows) ? taps->mlp_rows : w.counts;
   HB_CUDA(cudaMemsetAsync(counts + (size_t)block_index * m->n_rec, 0, (size_t)m->n_rec * 4, st));
-  return block_forward(m, block_index, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, B, S, w, taps, counts, err_flag, st);
+  return block_forward(m, block_index, (const __nv_bfloat16*)x, nullptr, (__nv_bfloat16*)y, nullptr, nullptr, B, S, w,
+                       taps, counts, err_flag, st);
 }
 
 extern "C" int hb200_model_forward(const hb200_model* m, const int64_t* ids, int B, int S, void* workspace,
@@ -537,19 +611,25 @@ extern "C" int hb200_model_forward(const hb200_model* m, const int64_t* ids, int
   const int T = B * S, D = m->dim;
   int32_t* counts = (taps && taps->mlp_rows) ? taps->mlp_rows : w.counts;
   HB_CUDA(cudaMemsetAsync(counts, 0, (size_t)m->n_blocks * m->n_rec * 4, st));
+  HB_REQUIRE(aligned16(m->tok_emb) && m->norm_w != nullptr, HB200_ERR_INVALID, "model_forward: bad embedding / norm pointer");
   {
+    // embedding fused with the first block's pre-attention norm
     ProfScope ps(m->profile, st, HB200_K_EMBED, -1, 0, T, D, 0);
-    HB_PROPAGATE(hb200_embed(ids, m->tok_emb, w.x0, T, D, m->vocab, sqrtf((float)D), st));
+    embed_norm_kernel<<<(unsigned)ceil_div(T, 8), 256, 0, st>>>(ids, (const __nv_bfloat16*)m->tok_emb, w.x0,
+                                                                m->blocks[0].norm1_w, w.a, T, D, m->vocab,
+                                                                sqrtf((float)D), m->norm_eps);
+    HB_LAUNCH_CHECK();
   }
+  // each block's exit norm also produces the next consumer's input norm: the next block's norm1 into w.a, or the
+  // model's final norm into the hidden-state buffer after the last block
   __nv_bfloat16 *xin = w.x0, *xout = w.x1;
+  __nv_bfloat16* hid = hidden_out ? (__nv_bfloat16*)hidden_out : w.ug;   // ug is free once the last block is done
   for (int bi = 0; bi < m->n_blocks; ++bi) {
-    HB_PROPAGATE(block_forward(m, bi, xin, xout, B, S, w, taps, counts, err_flag, st));
+    const bool last = (bi == m->n_blocks - 1);
+    const float* next_w = last ? m->norm_w : m->blocks[bi + 1].norm1_w;
+    // w.a is read by this block's qkv GEMM long before its exit norm overwrites it with the next block's input
+    HB_PROPAGATE(block_forward(m, bi, xin, w.a, xout, next_w, last ? hid : w.a, B, S, w, taps, counts, err_flag, st));
     std::swap(xin, xout);
-  }
-  __nv_bfloat16* hid = hidden_out ? (__nv_bfloat16*)hidden_out : xout;
-  {
-    ProfScope ps(m->profile, st, HB200_K_RMS_NORM, m->n_blocks, 0, T, D, 0);
-    HB_PROPAGATE(hb200_rms_norm(xin, m->norm_w, hid, T, D, m->norm_eps, HB200_BF16, HB200_F32, st));
   }
   if (logits != nullptr)
     HB_PROPAGATE(gemm(m, HB200_K_GEMM_LM_HEAD, m->n_blocks, 0, hid, m->tok_emb, logits, T, m->vocab, D, D, D, ld_logits, EPI_STORE, nullptr, 1.0f, nullptr,

@@ -90,8 +90,9 @@ int hb200_swiglu(const void* gate, const void* up, void* out, int64_t rows, int 
  *                            row 16*i+r is gate row 8*i+r (r<8) or up row 8*i+r-8 (r>=8);
  *                            C is [M, N/2]
  *   epilogue 3  SCATTER_ADD  C[rows[m], n] += acc  (rows int32 [M], each target row once)
- * m_dev, when non-null, is a device int32 holding the live row count (<= M); rows beyond it
- * are neither computed into C nor read from `rows`.
+ * m_dev, when non-null, is a device int32 holding the live row count (<= M); tiles beyond it are
+ * skipped and `rows` is not read beyond it.  Epilogues 1 and 3 never touch rows of C beyond the live
+ * count; epilogues 0 and 2 write whole 32-row boxes, so rows [live, M) of C may be overwritten.
  * impl 0 = tcgen05/TMEM/TMA kernel (product path); impl 1 = plain mma.sync kernel kept as an
  * independent cross-check for tests.
  * err_flag: optional device int32; set non-zero if a bounded in-kernel wait ran out (the kernel
