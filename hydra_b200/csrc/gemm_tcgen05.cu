@@ -135,6 +135,8 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+__device__ __forceinline__ uint4 ld_global_v4(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -286,6 +288,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     constexpr int CHUNKS = BN / 32 / (EPI_WARPS / 4);
     const bool swiglu = (p.epilogue == EPI_SWIGLU);
     const bool tma_store = (p.epilogue == EPI_STORE) || swiglu;
+    const bool rmw = !tma_store && (p.N % 8 == 0);   // residual / scatter-add with whole 16-byte pieces
     const int n_out = swiglu ? p.N / 2 : p.N;
     const uint32_t my_box = store_base + (uint32_t)(warp - 2) * Cfg::STORE_BOX_BYTES;
     int as = 0;
@@ -294,11 +297,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       int mt, nt;
       tile_coords(tile, m_tiles, n_tiles, mt, nt);
+      const int m = mt * GBM + quad * 32 + lane;
+      // Read-modify-write epilogues: fetch this thread's residual / target row segment BEFORE waiting for the
+      // accumulator, so the global-load latency hides behind the mainloop of this tile.
+      uint4 pre[CHUNKS][4];
+      __nv_bfloat16* rmw_dst = nullptr;
+      if (rmw) {
+        const int col0 = nt * BN + half * CHUNKS * 32;
+        if (m < M) {
+          const size_t row = (p.epilogue == EPI_SCATTER_ADD) ? (size_t)p.rows[m] : (size_t)m;
+          rmw_dst = p.C + row * p.ldc + col0;
+          const __nv_bfloat16* src = (p.epilogue == EPI_RESID) ? p.resid + row * p.ldc + col0 : rmw_dst;
+#pragma unroll
+          for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8)
+              pre[c][q8] = (col0 + c * 32 + q8 * 8 + 8 <= p.N) ? ld_global_v4(src + c * 32 + q8 * 8)
+                                                               : make_uint4(0, 0, 0, 0);
+        }
+      }
       if (!mbar_wait(tfull_bar(as), aphase, abort_flag)) { ok = false; }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
-      const int m = mt * GBM + quad * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(as * BN);
       if (tma_store) {
         // ---- staged path: 64 output columns per box, one box in flight per warp ----
@@ -347,7 +368,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
             }
           }
         }
+      } else if (rmw) {
+        const int col0 = nt * BN + half * CHUNKS * 32;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          float v[32];
+          tmem_ld_32x32(t_row + (uint32_t)(half * CHUNKS * 32 + c * 32), v);   // warp-collective
+          if (rmw_dst != nullptr) {
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+              if (col0 + c * 32 + q8 * 8 + 8 <= p.N) {
+                const uint32_t w4[4] = {pre[c][q8].x, pre[c][q8].y, pre[c][q8].z, pre[c][q8].w};
+                uint4 o;
+                uint32_t* ow = &o.x;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float r0 = __uint_as_float(w4[j] << 16), r1 = __uint_as_float(w4[j] & 0xffff0000u);
+                  ow[j] = pack_bf16x2_rn(r0 + p.alpha * v[q8 * 8 + 2 * j], r1 + p.alpha * v[q8 * 8 + 2 * j + 1]);
+                }
+                *reinterpret_cast<uint4*>(rmw_dst + c * 32 + q8 * 8) = o;
+              }
+            }
+          }
+        }
       } else {
+        // generic fallback (column counts that are not a multiple of 8)
 #pragma unroll 1
         for (int c = half * CHUNKS; c < (half + 1) * CHUNKS; ++c) {
           float v[32];

@@ -60,15 +60,29 @@ struct ProfScope {
 
 constexpr int ROW_NCH = 8;   // row kernels keep up to 8 x 256 elements of a row in registers (dim <= 2048)
 
+// Launch a row kernel template with the smallest register-resident row that covers `dim`.
+#define HB_DISPATCH_NCH(dim, ...)                 \
+  do {                                            \
+    if ((dim) <= 256) { constexpr int NCH = 1; __VA_ARGS__; }        \
+    else if ((dim) <= 512) { constexpr int NCH = 2; __VA_ARGS__; }   \
+    else if ((dim) <= 1024) { constexpr int NCH = 4; __VA_ARGS__; }  \
+    else { constexpr int NCH = 8; __VA_ARGS__; }                     \
+  } while (0)
+
 // Loads row `src` (+ optional fp32 per-column offset), returns sum of squares; values stay in v.
+template <int NCH>
 __device__ __forceinline__ float load_row_add(const __nv_bfloat16* __restrict__ src, const float* __restrict__ add,
-                                              int D, int lane, float (&v)[ROW_NCH][8]) {
+                                              int D, int lane, float (&v)[NCH][8]) {
   float ss = 0.f;
 #pragma unroll
-  for (int c = 0; c < ROW_NCH; ++c) {
+  for (int c = 0; c < NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) load_bf16x8(src + i, v[c]);   // all loads of the row are issued before any is consumed
+  }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
     const int i = (c * 32 + lane) * 8;
     if (i < D) {
-      load_bf16x8(src + i, v[c]);
       if (add != nullptr) {
         const float4 a0 = *reinterpret_cast<const float4*>(add + i);
         const float4 a1 = *reinterpret_cast<const float4*>(add + i + 4);
@@ -83,10 +97,10 @@ __device__ __forceinline__ float load_row_add(const __nv_bfloat16* __restrict__ 
 }
 
 // v <- bf16-rounded (v * r * w)
-__device__ __forceinline__ void scale_row(const float* __restrict__ w, float r, int D, int lane,
-                                          float (&v)[ROW_NCH][8]) {
+template <int NCH>
+__device__ __forceinline__ void scale_row(const float* __restrict__ w, float r, int D, int lane, float (&v)[NCH][8]) {
 #pragma unroll
-  for (int c = 0; c < ROW_NCH; ++c) {
+  for (int c = 0; c < NCH; ++c) {
     const int i = (c * 32 + lane) * 8;
     if (i < D) {
       const float4 w0 = *reinterpret_cast<const float4*>(w + i);
@@ -98,27 +112,13 @@ __device__ __forceinline__ void scale_row(const float* __restrict__ w, float r, 
   }
 }
 
-__device__ __forceinline__ float dot_row(const float* __restrict__ w, int D, int lane, const float (&v)[ROW_NCH][8]) {
-  float s = 0.f;
-#pragma unroll
-  for (int c = 0; c < ROW_NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) {
-      const float4 w0 = *reinterpret_cast<const float4*>(w + i);
-      const float4 w1 = *reinterpret_cast<const float4*>(w + i + 4);
-      s += v[c][0] * w0.x + v[c][1] * w0.y + v[c][2] * w0.z + v[c][3] * w0.w + v[c][4] * w1.x + v[c][5] * w1.y +
-           v[c][6] * w1.z + v[c][7] * w1.w;
-    }
-  }
-  return warp_sum(s);
-}
-
 // Router pass over ALL tokens, streaming (no activation is written): four rows per warp so that the per-column
 // vectors are fetched once per four rows.
 //   MoD score   s = rsqrt(mean((x+rec)^2) + eps) * sum_d (x_d + rec_d) * wn_d + b,  wn = norm2 gain * MoD weight
 //               (the fp32 value of Linear(AdaRMSNorm(x + rec)) without rounding the normalised row to bf16)
 //   MoR depth   from l = sum_d x_d * mor_w_d + b on the raw row (recursion 0 only)
 constexpr int SCORE_ROWS = 4;
+template <int NCH>
 __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __restrict__ cur,
                                                         const float* __restrict__ rec, const float* __restrict__ mod_wn,
                                                         const float* __restrict__ mod_b,
@@ -129,35 +129,47 @@ __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __r
   const int lane = threadIdx.x & 31;
   const int64_t row0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * SCORE_ROWS;
   if (row0 >= T) return;
+  // issue every load of the four rows first (up to 16 x 16 bytes in flight per lane)
+  uint4 raw[SCORE_ROWS][NCH];
+#pragma unroll
+  for (int r = 0; r < SCORE_ROWS; ++r)
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int i = (c * 32 + lane) * 8;
+      raw[r][c] = (i < D && row0 + r < T) ? *reinterpret_cast<const uint4*>(cur + (row0 + r) * D + i)
+                                         : make_uint4(0, 0, 0, 0);
+    }
   float ss[SCORE_ROWS], dm[SCORE_ROWS], lm[SCORE_ROWS];
 #pragma unroll
   for (int r = 0; r < SCORE_ROWS; ++r) ss[r] = dm[r] = lm[r] = 0.f;
-  for (int i = lane * 8; i < D; i += 256) {
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
     float wn[8], rc[8], wr[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) wn[j] = rc[j] = wr[j] = 0.f;
-    if (mod_wn != nullptr) {
-      const float4 a0 = *reinterpret_cast<const float4*>(mod_wn + i), a1 = *reinterpret_cast<const float4*>(mod_wn + i + 4);
-      const float4 b0 = *reinterpret_cast<const float4*>(rec + i), b1 = *reinterpret_cast<const float4*>(rec + i + 4);
-      wn[0] = a0.x; wn[1] = a0.y; wn[2] = a0.z; wn[3] = a0.w; wn[4] = a1.x; wn[5] = a1.y; wn[6] = a1.z; wn[7] = a1.w;
-      rc[0] = b0.x; rc[1] = b0.y; rc[2] = b0.z; rc[3] = b0.w; rc[4] = b1.x; rc[5] = b1.y; rc[6] = b1.z; rc[7] = b1.w;
-    }
-    if (mor_w != nullptr) {
-      const float4 a0 = *reinterpret_cast<const float4*>(mor_w + i), a1 = *reinterpret_cast<const float4*>(mor_w + i + 4);
-      wr[0] = a0.x; wr[1] = a0.y; wr[2] = a0.z; wr[3] = a0.w; wr[4] = a1.x; wr[5] = a1.y; wr[6] = a1.z; wr[7] = a1.w;
+    if (i < D) {
+      if (mod_wn != nullptr) {
+        const float4 a0 = *reinterpret_cast<const float4*>(mod_wn + i), a1 = *reinterpret_cast<const float4*>(mod_wn + i + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(rec + i), b1 = *reinterpret_cast<const float4*>(rec + i + 4);
+        wn[0] = a0.x; wn[1] = a0.y; wn[2] = a0.z; wn[3] = a0.w; wn[4] = a1.x; wn[5] = a1.y; wn[6] = a1.z; wn[7] = a1.w;
+        rc[0] = b0.x; rc[1] = b0.y; rc[2] = b0.z; rc[3] = b0.w; rc[4] = b1.x; rc[5] = b1.y; rc[6] = b1.z; rc[7] = b1.w;
+      }
+      if (mor_w != nullptr) {
+        const float4 a0 = *reinterpret_cast<const float4*>(mor_w + i), a1 = *reinterpret_cast<const float4*>(mor_w + i + 4);
+        wr[0] = a0.x; wr[1] = a0.y; wr[2] = a0.z; wr[3] = a0.w; wr[4] = a1.x; wr[5] = a1.y; wr[6] = a1.z; wr[7] = a1.w;
+      }
     }
 #pragma unroll
     for (int r = 0; r < SCORE_ROWS; ++r) {
-      if (row0 + r < T) {
-        float x[8];
-        load_bf16x8(cur + (row0 + r) * D + i, x);
+      const uint32_t w4[4] = {raw[r][c].x, raw[r][c].y, raw[r][c].z, raw[r][c].w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float xr = x[j] + rc[j];
-          ss[r] += xr * xr;
-          dm[r] += xr * wn[j];
-          lm[r] += x[j] * wr[j];
-        }
+      for (int j = 0; j < 8; ++j) {
+        const float x = (j & 1) ? __uint_as_float(w4[j >> 1] & 0xffff0000u) : __uint_as_float(w4[j >> 1] << 16);
+        const float xr = x + rc[j];
+        ss[r] += xr * xr;
+        dm[r] += xr * wn[j];
+        lm[r] += x * wr[j];
       }
     }
   }
@@ -176,6 +188,7 @@ __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __r
 }
 
 // ug[j] = AdaRMSNorm(cur[rows[j]] + rec) for j < *count.  One warp per compact row.
+template <int NCH>
 __global__ void __launch_bounds__(256) norm_gather_kernel(const __nv_bfloat16* __restrict__ cur,
                                                           const float* __restrict__ rec, const float* __restrict__ w2,
                                                           const int32_t* __restrict__ rows,
@@ -185,11 +198,11 @@ __global__ void __launch_bounds__(256) norm_gather_kernel(const __nv_bfloat16* _
   const int64_t j = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (j >= *count) return;
   const int64_t src = rows[j];
-  float v[ROW_NCH][8];
-  const float ss = load_row_add(cur + src * D, rec, D, lane, v);
-  scale_row(w2, rsqrtf(ss / (float)D + eps), D, lane, v);
+  float v[NCH][8];
+  const float ss = load_row_add<NCH>(cur + src * D, rec, D, lane, v);
+  scale_row<NCH>(w2, rsqrtf(ss / (float)D + eps), D, lane, v);
 #pragma unroll
-  for (int c = 0; c < ROW_NCH; ++c) {
+  for (int c = 0; c < NCH; ++c) {
     const int i = (c * 32 + lane) * 8;
     if (i < D) store_bf16x8(ug + j * D + i, v[c]);
   }
@@ -197,6 +210,7 @@ __global__ void __launch_bounds__(256) norm_gather_kernel(const __nv_bfloat16* _
 
 // y = RMSNorm(src; w1) rounded to bf16 (the block output), z = RMSNorm(y; w2) (the next block's pre-attention norm,
 // or the model's final norm): one read of src instead of three passes.  Either output may be omitted.
+template <int NCH>
 __global__ void __launch_bounds__(256) dual_norm_kernel(const __nv_bfloat16* __restrict__ src,
                                                         const float* __restrict__ w1, __nv_bfloat16* __restrict__ y,
                                                         const float* __restrict__ w2, __nv_bfloat16* __restrict__ z,
@@ -204,12 +218,12 @@ __global__ void __launch_bounds__(256) dual_norm_kernel(const __nv_bfloat16* __r
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= T) return;
-  float v[ROW_NCH][8];
-  const float ss = load_row_add(src + row * D, nullptr, D, lane, v);
-  scale_row(w1, rsqrtf(ss / (float)D + eps), D, lane, v);
+  float v[NCH][8];
+  const float ss = load_row_add<NCH>(src + row * D, nullptr, D, lane, v);
+  scale_row<NCH>(w1, rsqrtf(ss / (float)D + eps), D, lane, v);
   float ss2 = 0.f;
 #pragma unroll
-  for (int c = 0; c < ROW_NCH; ++c) {
+  for (int c = 0; c < NCH; ++c) {
     const int i = (c * 32 + lane) * 8;
     if (i < D) {
       if (y != nullptr) store_bf16x8(y + row * D + i, v[c]);
@@ -219,15 +233,16 @@ __global__ void __launch_bounds__(256) dual_norm_kernel(const __nv_bfloat16* __r
   }
   if (z == nullptr) return;
   ss2 = warp_sum(ss2);
-  scale_row(w2, rsqrtf(ss2 / (float)D + eps), D, lane, v);
+  scale_row<NCH>(w2, rsqrtf(ss2 / (float)D + eps), D, lane, v);
 #pragma unroll
-  for (int c = 0; c < ROW_NCH; ++c) {
+  for (int c = 0; c < NCH; ++c) {
     const int i = (c * 32 + lane) * 8;
     if (i < D) store_bf16x8(z + row * D + i, v[c]);
   }
 }
 
 // x = bf16(table[clamp(id)] * scale), a = AdaRMSNorm(x; w): embedding and the first block's pre-attention norm.
+template <int NCH>
 __global__ void __launch_bounds__(256) embed_norm_kernel(const int64_t* __restrict__ ids,
                                                          const __nv_bfloat16* __restrict__ table,
                                                          __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
@@ -238,11 +253,11 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const int64_t* __restri
   if (row >= T) return;
   int64_t id = ids[row];
   id = id < 0 ? 0 : (id >= V ? V - 1 : id);
-  float v[ROW_NCH][8];
-  load_row_add(table + id * D, nullptr, D, lane, v);
+  float v[NCH][8];
+  load_row_add<NCH>(table + id * D, nullptr, D, lane, v);
   float ss = 0.f;
 #pragma unroll
-  for (int c = 0; c < ROW_NCH; ++c) {
+  for (int c = 0; c < NCH; ++c) {
     const int i = (c * 32 + lane) * 8;
     if (i < D) {
 #pragma unroll
@@ -254,9 +269,9 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const int64_t* __restri
     }
   }
   ss = warp_sum(ss);
-  scale_row(w, rsqrtf(ss / (float)D + eps), D, lane, v);
+  scale_row<NCH>(w, rsqrtf(ss / (float)D + eps), D, lane, v);
 #pragma unroll
-  for (int c = 0; c < ROW_NCH; ++c) {
+  for (int c = 0; c < NCH; ++c) {
     const int i = (c * 32 + lane) * 8;
     if (i < D) store_bf16x8(a + row * D + i, v[c]);
   }
@@ -419,9 +434,9 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
     float* scores = (taps && taps->mod_scores) ? taps->mod_scores + ((size_t)bi * R + r) * T : w.scores;
     if (need_router || has_mod) {
       ProfScope ps(m->profile, st, HB200_K_MOR_SCORE, bi, r, T, D, 0);
-      mor_score_kernel<<<(unsigned)ceil_div(T, 8 * SCORE_ROWS), 256, 0, st>>>(w.cur, rec, has_mod ? bw.mod_wn : nullptr, bw.mod_b,
-                                                 need_router ? bw.mor_w : nullptr, bw.mor_b, scores, logits,
-                                                 force ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth);
+      HB_DISPATCH_NCH(D, mor_score_kernel<NCH><<<(unsigned)ceil_div(T, 8 * SCORE_ROWS), 256, 0, st>>>(
+                             w.cur, rec, has_mod ? bw.mod_wn : nullptr, bw.mod_b, need_router ? bw.mor_w : nullptr,
+                             bw.mor_b, scores, logits, force ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth));
       HB_LAUNCH_CHECK();
     }
     int32_t* count = counts + (size_t)bi * R + r;
@@ -437,7 +452,8 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
     }
     {
       ProfScope ps(m->profile, st, HB200_K_NORM_GATHER, bi, r, T, D, 0);
-      norm_gather_kernel<<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, w.rows, count, w.ug, D, m->norm_eps);
+      HB_DISPATCH_NCH(D, norm_gather_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, w.rows, count, w.ug, D,
+                                                                           m->norm_eps));
       HB_LAUNCH_CHECK();
     }
     HB_PROPAGATE(gemm(m, HB200_K_GEMM_GATE_UP, bi, r, w.ug, bw.w_gate_up, w.act, T, 2 * F, D, D, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count,
@@ -447,8 +463,8 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
   }
   {
     ProfScope ps(m->profile, st, HB200_K_RMS_NORM, bi, R, T, D, 0);
-    dual_norm_kernel<<<row_grid, 256, 0, st>>>(w.cur, bw.final_norm_w, y, next_w, next_w ? a_next : nullptr, T, D,
-                                               m->norm_eps);
+    HB_DISPATCH_NCH(D, dual_norm_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, bw.final_norm_w, y, next_w,
+                                                                         next_w ? a_next : nullptr, T, D, m->norm_eps));
     HB_LAUNCH_CHECK();
   }
   if (taps && taps->block_out)
@@ -615,9 +631,9 @@ extern "C" int hb200_model_forward(const hb200_model* m, const int64_t* ids, int
   {
     // embedding fused with the first block's pre-attention norm
     ProfScope ps(m->profile, st, HB200_K_EMBED, -1, 0, T, D, 0);
-    embed_norm_kernel<<<(unsigned)ceil_div(T, 8), 256, 0, st>>>(ids, (const __nv_bfloat16*)m->tok_emb, w.x0,
-                                                                m->blocks[0].norm1_w, w.a, T, D, m->vocab,
-                                                                sqrtf((float)D), m->norm_eps);
+    HB_DISPATCH_NCH(D, embed_norm_kernel<NCH><<<(unsigned)ceil_div(T, 8), 256, 0, st>>>(
+                           ids, (const __nv_bfloat16*)m->tok_emb, w.x0, m->blocks[0].norm1_w, w.a, T, D, m->vocab,
+                           sqrtf((float)D), m->norm_eps));
     HB_LAUNCH_CHECK();
   }
   // each block's exit norm also produces the next consumer's input norm: the next block's norm1 into w.a, or the
