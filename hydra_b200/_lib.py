@@ -21,7 +21,7 @@ EPI_STORE, EPI_RESID, EPI_SWIGLU, EPI_SCATTER_ADD = 0, 1, 2, 3
 class BlockWeights(C.Structure):
     _fields_ = [(n, c_vp) for n in (
         "norm1_w", "norm2_w", "final_norm_w", "w_qkv", "w_o", "w1_qk", "w2_q", "w2_k", "key_temperature",
-        "w_gate_up", "w_down", "mor_w", "mor_b", "rec", "mod_wn", "mod_b")]
+        "w_gate_up", "w_down", "mor_w", "mor_b", "rec", "mod_wn", "mod_b")] + [("attn_logit_bound", c_f32)]
 
 
 class Model(C.Structure):
@@ -59,7 +59,8 @@ SIGNATURES = {
     "hb200_interleave_gate_up": (c_i32, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "hb200_repack_conv_weight": (c_i32, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "hb200_ccgqa_pre_attention": (c_i32, [c_vp] * 10 + [c_i32] * 5 + [c_vp]),
-    "hb200_attention_causal_gqa": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_f32, c_vp]),
+    "hb200_attention_causal_gqa": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_f32, c_f32,
+                                           c_vp, c_vp]),
     "hb200_mod_topk_select": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp]),
     "hb200_mor_depths": (c_i32, [c_vp, c_vp, c_i64, c_i32, c_i32, c_vp]),
     "hb200_embed": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_f32, c_vp]),

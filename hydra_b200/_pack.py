@@ -90,7 +90,13 @@ class PackedBlock:
                 t["mod_wn"] = (_f32(sd[mk + "weight"], device).reshape(-1) * t["norm2_w"]).contiguous()
                 t["mod_b"] = _f32(sd[mk + "bias"], device).reshape(1)
         self.tensors = t
-        self.struct = _lib.BlockWeights(**{k: (v.data_ptr() if v is not None else None) for k, v in t.items()})
+        # q is a unit vector and |k| = |key_temperature| after the fused pre-attention kernel (RoPE is a rotation), so
+        # |q.k| / sqrt(hd) <= |temperature| / sqrt(hd); 2% slack covers the bf16 rounding of q and k
+        hd = sd[a + "q_conv.conv1.weight"].shape[1]
+        temp = abs(float(sd[a + "key_temperature"].detach().float().reshape(-1)[0].item()))
+        self.attn_logit_bound = max(temp, 1e-3) / math.sqrt(hd) * 1.02
+        self.struct = _lib.BlockWeights(**{k: (v.data_ptr() if v is not None else None) for k, v in t.items()},
+                                        attn_logit_bound=self.attn_logit_bound)
 
 
 class PackedModel:

@@ -177,21 +177,28 @@ __global__ void __launch_bounds__(128) attention_causal_gqa_kernel(const __nv_bf
   }
 }
 
+int launch_attention_tcgen05(const void* q, const void* k, const void* v, void* o, int B, int S, int H, int KV, int hd,
+                             float scale, float logit_bound, int32_t* err_flag, cudaStream_t st);
+
 }  // namespace hb200
 
 using namespace hb200;
 
 extern "C" int hb200_attention_causal_gqa(const void* q, const void* k, const void* v, void* o, int B, int S, int H,
-                                          int KV, int hd, float scale, void* stream) {
+                                          int KV, int hd, float scale, float logit_bound, int32_t* err_flag,
+                                          void* stream) {
   HB_REQUIRE(q && k && v && o, HB200_ERR_INVALID, "attention: null pointer");
   HB_REQUIRE(B >= 0 && S >= 0 && H >= 1 && KV >= 1 && H % KV == 0, HB200_ERR_INVALID, "attention: bad shape");
   HB_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o), HB200_ERR_INVALID,
              "attention: pointers must be 16-byte aligned");
   HB_REQUIRE(B <= 65535 && H <= 65535, HB200_ERR_UNSUPPORTED, "attention: batch/head count beyond grid limits");
   if ((int64_t)B * S == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (logit_bound > 0.f && logit_bound <= 27.f && (hd == 16 || hd == 32 || hd == 64) &&
+      (int64_t)B * H * S < (1ll << 31))
+    return launch_attention_tcgen05(q, k, v, o, B, S, H, KV, hd, scale, logit_bound, err_flag, st);
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid((S + ATT_BM - 1) / ATT_BM, H, B);
-  cudaStream_t st = (cudaStream_t)stream;
   const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k, *vp = (const __nv_bfloat16*)v;
   if (hd == 16)
     attention_causal_gqa_kernel<16><<<grid, 128, 0, st>>>(qp, kp, vp, (__nv_bfloat16*)o, S, H, KV, scale_log2);

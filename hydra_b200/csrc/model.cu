@@ -390,7 +390,8 @@ static int attention_part(const hb200_model* m, int bi, const hb200_block_weight
   }
   {
     ProfScope ps(m->profile, st, HB200_K_ATTENTION, bi, 0, T, lat, S);
-    HB_PROPAGATE(hb200_attention_causal_gqa(w.q, w.k, w.v, w.o, B, S, H, KV, hd, 1.0f / sqrtf((float)hd), st));
+    HB_PROPAGATE(hb200_attention_causal_gqa(w.q, w.k, w.v, w.o, B, S, H, KV, hd, 1.0f / sqrtf((float)hd),
+                                            bw.attn_logit_bound, err, st));
   }
   HB_PROPAGATE(gemm(m, HB200_K_GEMM_O, bi, 0, w.o, bw.w_o, out, T, D, lat, lat, lat, D, resid ? EPI_RESID : EPI_STORE, resid, alpha, nullptr,
                     nullptr, err, st));

@@ -173,11 +173,16 @@ def attention(args) -> dict:
     v = _rand_bf16(B, KV, S, hd, seed=2)
     o = torch.empty(B, S, H * hd, dtype=torch.bfloat16, device="cuda")
     lib = _lib.lib()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bound = 0.0 if args.impl == 1 else 1.02 / math.sqrt(hd)     # q, k are unit vectors here
     ms = _time(lambda i: _lib.check(lib.hb200_attention_causal_gqa(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                                                                    B, S, H, KV, hd, 1.0 / math.sqrt(hd), _stream())),
+                                                                    B, S, H, KV, hd, 1.0 / math.sqrt(hd), bound,
+                                                                    err.data_ptr(), _stream())),
                args.iters)
+    assert int(err.item()) == 0
     flops = 4.0 * B * S * H * hd * (S + 1) / 2
-    return {"kernel": "attention_causal_gqa_kernel<32>", "shape": [B, H, S, hd], "ms": ms, "bound": "tensor",
+    return {"kernel": "attention_tcgen05_kernel<32>" if args.impl == 0 else "attention_causal_gqa_kernel<32> (mma.sync)",
+            "shape": [B, H, S, hd], "ms": ms, "bound": "tensor",
             "achieved": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "algorithmic_flops": flops,
             "note": "exp-throughput limited at head_dim 32: one ex2 per 128 MMA FLOPs"}
 

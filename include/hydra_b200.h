@@ -124,9 +124,15 @@ int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, const void* w2
 
 /* Causal grouped-query attention in the latent space (attention.py:288-327):
  * o[b,t,h,:] = softmax_causal(q[b,h] k[b,h/(H/KV)]^T * scale) v[b,h/(H/KV)].
- * q [B,H,S,hd], k/v [B,KV,S,hd] bf16; o token-major [B,S,H*hd] bf16. */
+ * q [B,H,S,hd], k/v [B,KV,S,hd] bf16; o token-major [B,S,H*hd] bf16.
+ * logit_bound > 0 is the caller's guarantee that |q.k| * scale <= logit_bound for every pair (CCGQA: q is a unit
+ * vector and |k| is the key temperature, so temperature * scale, plus rounding slack): the tcgen05/TMEM kernel then
+ * runs, which subtracts the bound instead of a running row maximum.  logit_bound <= 0 (unknown), or a bound above
+ * 27 (2^-80 would underflow the probabilities), selects the online-softmax mma.sync kernel.
+ * err_flag: optional device int32, set non-zero if a bounded in-kernel wait ran out. */
 int hb200_attention_causal_gqa(const void* q, const void* k, const void* v, void* o, int B, int S,
-                               int H, int KV, int hd, float scale, void* stream);
+                               int H, int KV, int hd, float scale, float logit_bound, int32_t* err_flag,
+                               void* stream);
 
 /* ---------------------------------------------------------------------------
  * Routing  (hydra/routing/mixture_of_depths.py:159-216, mixture_of_recursions.py:251-291,
@@ -175,6 +181,7 @@ typedef struct hb200_block_weights {
   const float* rec;              /* fp32 [R, D] recursion_bias + recursion_embed */
   const float* mod_wn;           /* fp32 [D] MoD router weight times the norm2 gain (elementwise), or NULL */
   const float* mod_b;            /* fp32 [1] MoD router bias, or NULL    */
+  float attn_logit_bound;        /* HOST value: |key_temperature| / sqrt(head_dim) * 1.02, or 0 if unknown */
 } hb200_block_weights;
 
 typedef struct hb200_model {
