@@ -312,13 +312,18 @@ static int launch_pre(const PreParams& p, cudaStream_t st) {
   return 0;
 }
 
+int launch_ccgqa_pre_tc(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k, const float* cos_t,
+                        const float* sin_t, const float* key_temperature, void* q, void* k, void* v, int B, int S, int H,
+                        int KV, int hd, int32_t* err_flag, cudaStream_t st);
+
 }  // namespace hb200
 
 using namespace hb200;
 
 extern "C" int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k,
                                          const float* cos_t, const float* sin_t, const float* key_temperature, void* q,
-                                         void* k, void* v, int B, int S, int H, int KV, int hd, void* stream) {
+                                         void* k, void* v, int B, int S, int H, int KV, int hd, int32_t* err_flag,
+                                         void* stream) {
   HB_REQUIRE(qkv && w1_qk && w2_q && w2_k && cos_t && sin_t && key_temperature && q && k && v, HB200_ERR_INVALID,
              "ccgqa_pre_attention: null pointer");
   HB_REQUIRE(B >= 0 && S >= 0 && H >= 1 && KV >= 1 && H % KV == 0, HB200_ERR_INVALID,
@@ -331,6 +336,12 @@ extern "C" int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, con
               (const __nv_bfloat16*)w2_k, cos_t, sin_t, key_temperature, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
               (__nv_bfloat16*)v, B, S, H, KV};
   cudaStream_t st = (cudaStream_t)stream;
+  {
+    // tcgen05 kernel for the 250M-class shapes; HB200_ERR_UNSUPPORTED means "not this shape", anything else is final
+    const int rc = launch_ccgqa_pre_tc(qkv, w1_qk, w2_q, w2_k, cos_t, sin_t, key_temperature, q, k, v, B, S, H, KV, hd,
+                                       err_flag, st);
+    if (rc != HB200_ERR_UNSUPPORTED) return rc;
+  }
 #define HB_PRE_CASE(HD_, NTQ_, NTK_) \
   if (hd == HD_ && lat == NTQ_ * 32 && kvd == NTK_ * 16) return launch_pre<HD_, NTQ_, NTK_>(p, st);
   HB_PRE_CASE(32, 8, 4)    // dim 1024: 8q/2kv heads of 32

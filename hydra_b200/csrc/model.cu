@@ -386,7 +386,7 @@ static int attention_part(const hb200_model* m, int bi, const hb200_block_weight
   {
     ProfScope ps(m->profile, st, HB200_K_PRE_ATTENTION, bi, 0, T, nq, 0);
     HB_PROPAGATE(hb200_ccgqa_pre_attention(w.qkv, bw.w1_qk, bw.w2_q, bw.w2_k, m->rope_cos, m->rope_sin,
-                                           bw.key_temperature, w.q, w.k, w.v, B, S, H, KV, hd, st));
+                                           bw.key_temperature, w.q, w.k, w.v, B, S, H, KV, hd, err, st));
   }
   {
     ProfScope ps(m->profile, st, HB200_K_ATTENTION, bi, 0, T, lat, S);

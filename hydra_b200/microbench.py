@@ -154,13 +154,16 @@ def pre_attention(args) -> dict:
         j = i % ns
         _lib.check(lib.hb200_ccgqa_pre_attention(qkv[j].data_ptr(), w1.data_ptr(), w2q.data_ptr(), w2k.data_ptr(),
                                                  cos.data_ptr(), sin.data_ptr(), temp.data_ptr(), q[j].data_ptr(),
-                                                 k[j].data_ptr(), v[j].data_ptr(), B, S, H, KV, hd, _stream()))
+                                                 k[j].data_ptr(), v[j].data_ptr(), B, S, H, KV, hd,
+                                                 err.data_ptr(), _stream()))
 
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
     ms = _time(run, args.iters)
+    assert int(err.item()) == 0
     T = B * S
     nbytes = 4.0 * T * (lat + 2 * kvd) + 6.0 * (lat * hd + lat * lat + kvd * hd + kvd * kvd)
     flops = 6.0 * T * (lat * hd + lat * lat + kvd * hd + kvd * kvd)
-    return {"kernel": "ccgqa_pre_kernel<32,8,4>", "shape": [B, S, lat + 2 * kvd], "ms": ms, "bound": "hbm",
+    return {"kernel": "ccgqa_pre_tc_kernel<32>", "shape": [B, S, lat + 2 * kvd], "ms": ms, "bound": "hbm",
             "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "algorithmic_bytes": nbytes,
             "conv_tflops": flops / (ms * 1e-3) / 1e12}
 

@@ -116,11 +116,14 @@ int hb200_repack_conv_weight(const void* w, void* w_out, int c_out, int c_in, vo
  * qkv [B,S,lat+2*kvd] bf16 -> q [B,H,S,hd], k [B,KV,S,hd], v [B,KV,S,hd] bf16.
  * w1_qk: repacked conv1 weights, q rows then k rows: [lat+kvd, 3*hd];
  * w2_q [lat, 3*lat], w2_k [kvd, 3*kvd] repacked conv2 weights; cos/sin fp32 [>=S, hd/2];
- * key_temperature: device fp32 scalar. */
+ * key_temperature: device fp32 scalar.
+ * For latent 256 / kv_dim 64 with head_dim 16 or 32 the dense conv runs on tcgen05 with TMEM accumulators and a
+ * TMA-fed weight ring; other shapes use the mma.sync kernel.  err_flag: optional device int32, set non-zero if a
+ * bounded in-kernel wait ran out. */
 int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k,
                               const float* cos_t, const float* sin_t, const float* key_temperature,
                               void* q, void* k, void* v, int B, int S, int H, int KV, int hd,
-                              void* stream);
+                              int32_t* err_flag, void* stream);
 
 /* Causal grouped-query attention in the latent space (attention.py:288-327):
  * o[b,t,h,:] = softmax_causal(q[b,h] k[b,h/(H/KV)]^T * scale) v[b,h/(H/KV)].

@@ -34,11 +34,13 @@ def pre_attention_gpu(L, qkv_bf16, w, cfg, S_tab=None):
     q = torch.full((B, H, S, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
     k = torch.full((B, KV, S, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
     v = torch.full((B, KV, S, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
     L.check(L.lib().hb200_ccgqa_pre_attention(qkv_bf16.data_ptr(), w1.data_ptr(), w2q.data_ptr(), w2k.data_ptr(),
                                               cos.data_ptr(), sin.data_ptr(), temp.data_ptr(), q.data_ptr(),
-                                              k.data_ptr(), v.data_ptr(), B, S, H, KV, hd,
+                                              k.data_ptr(), v.data_ptr(), B, S, H, KV, hd, err.data_ptr(),
                                               torch.cuda.current_stream().cuda_stream), "pre_attention")
     torch.cuda.synchronize()
+    assert int(err.item()) == 0, "a bounded wait inside the pre-attention kernel ran out"
     return q, k, v
 
 
@@ -61,12 +63,13 @@ def test_fused_pre_attention_kernel(L, name):
     assert rel_l2(q, rq) < 4e-3 and rel_l2(k, rk) < 4e-3
 
 
-def test_pre_attention_ragged_lengths_and_tile_boundaries(L):
-    """Sequence lengths around the 64-token tile (1, 2, 63, 64, 65, 129) and batch > 1: every sequence restarts its
-    causal padding; compare with the oracle run per sequence."""
-    fx, cfg, w = G.attention_fixture("ccgqa_hd16.npz")
+@pytest.mark.parametrize("name", ["ccgqa_hd16.npz", "ccgqa_hd32.npz"])
+def test_pre_attention_ragged_lengths_and_tile_boundaries(L, name):
+    """Sequence lengths around the token tiles (64 for the mma.sync kernel, 128 for the tcgen05 kernel) and batch > 1:
+    every sequence restarts its causal padding; compare with the oracle run per sequence."""
+    fx, cfg, w = G.attention_fixture(name)
     g = torch.Generator().manual_seed(5)
-    for S in (1, 2, 63, 64, 65, 129):
+    for S in (1, 2, 63, 64, 65, 127, 128, 129, 300):
         qkv = bf16_round(torch.randn(3, S, cfg.latent_dim + 2 * cfg.kv_dim, generator=g))
         cos, sin = O.rope_tables(S, cfg.head_dim)
         rq, rk, rv = O.ccgqa_pre_attention(qkv, w, "attn.", cfg, cos, sin)
@@ -74,6 +77,27 @@ def test_pre_attention_ragged_lengths_and_tile_boundaries(L):
         temp = float(w["attn.key_temperature"])
         assert max_abs(q, rq) <= 3 * 2 ** -8 and max_abs(k, rk) <= 3 * 2 ** -8 * temp, f"S={S}"
         assert torch.equal(v.float().cpu(), rv), f"S={S}"
+
+
+def test_pre_attention_16q_4kv_preset_shape(L):
+    """The reference's own 250M preset uses 16 query / 4 KV heads of 16 (latent 256, kv_dim 64): no fixture exists
+    for it, so the weights are seeded random (bf16-representable) and the fp32 oracle is the reference."""
+    g = torch.Generator().manual_seed(21)
+    cfg = O.HydraConfig(dim=1024, n_heads=16, n_kv_heads=4, max_seq_len=200)
+    lat, kvd, hd = 256, 64, 16
+    w = {"attn.q_conv.conv1.weight": bf16_round(torch.randn(lat, hd, 3, generator=g) * 0.15),
+         "attn.q_conv.conv2.weight": bf16_round(torch.randn(lat, lat, 3, generator=g) * 0.05),
+         "attn.k_conv.conv1.weight": bf16_round(torch.randn(kvd, hd, 3, generator=g) * 0.15),
+         "attn.k_conv.conv2.weight": bf16_round(torch.randn(kvd, kvd, 3, generator=g) * 0.1),
+         "attn.key_temperature": torch.tensor([2.5])}
+    B, S = 2, 200
+    qkv = bf16_round(torch.randn(B, S, lat + 2 * kvd, generator=g))
+    cos, sin = O.rope_tables(S, hd)
+    rq, rk, rv = O.ccgqa_pre_attention(qkv, w, "attn.", cfg, cos, sin)
+    q, k, v = pre_attention_gpu(L, qkv.to(torch.bfloat16).cuda(), w, cfg)
+    assert max_abs(q, rq) <= 3 * 2 ** -8 and max_abs(k, rk) <= 3 * 2 ** -8 * 2.5
+    assert torch.equal(v.float().cpu(), rv)
+    assert rel_l2(q, rq) < 4e-3 and rel_l2(k, rk) < 4e-3
 
 
 @pytest.mark.parametrize("bounded", [True, False], ids=["tcgen05-bounded", "mma-online"])
