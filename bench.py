@@ -322,10 +322,10 @@ def main() -> None:
     args = ap.parse_args()
     if args.micro is not None:
         from hydra_b200 import microbench
-        if args.micro != "gemm":
+        if args.micro not in ("gemm", "model_hidden"):
             args.batch = 8 if args.batch == 32 else args.batch
         args.impl = args.impl_gemm
-        names = list(microbench.CASES) if args.micro == "all" else [args.micro]
+        names = [n for n in microbench.CASES if n != "model_hidden"] if args.micro == "all" else [args.micro]
         for nm in names:
             print(json.dumps(microbench.run(nm, args, ROOT)), flush=True)
         return

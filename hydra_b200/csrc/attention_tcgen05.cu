@@ -9,8 +9,9 @@
 //              tcgen05.ld 32 columns of S at a time, p = 2^(s*scale*log2e - bound), causal mask on the diagonal tile,
 //              P as bf16 into a 128B-swizzled K-major A-operand tile in shared memory (double buffered).
 //   The softmax denominator is produced by the tensor core as well: a third, 16-column accumulator receives
-//   P x ones (the same bf16 P that multiplies V), so the softmax threads issue one FFMA and one ex2 per score and
-//   nothing else, and numerator and denominator see identical probabilities.
+//   P x ones (the same bf16 P that multiplies V), so the softmax threads issue one FFMA, one ex2 and half a
+//   byte-permute per score, and numerator and denominator see identical probabilities (which is also why P may
+//   be truncated to bf16 instead of rounded: the bias divides out).
 //
 // No running maximum and no rescaling of O: the caller supplies an upper bound of |q.k|*scale (in CCGQA q is a
 // unit vector and |k| is the key temperature, both after RoPE, so the bound is temperature/sqrt(hd)); softmax is
@@ -217,7 +218,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_tcgen05_kernel(const __
             if (key0 + i > qrow) p0 = 0.f;
             if (key0 + i + 1 > qrow) p1 = 0.f;
           }
-          packed[i >> 1] = pack_bf16x2_rn(p0, p1);
+          // bf16 by truncation: one byte-permute on the integer pipe instead of a conversion on the (saturated)
+          // special-function pipe.  The truncation bias cancels: the denominator is summed from the same bf16 values.
+          packed[i >> 1] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
         }
         // 32 keys = 64 bytes = four 16-byte pieces of this row inside half (c >> 1)
         const uint32_t half_base = prow + (uint32_t)(c >> 1) * (AQ * 128);

@@ -118,7 +118,7 @@ __device__ __forceinline__ void scale_row(const float* __restrict__ w, float r, 
 //               (the fp32 value of Linear(AdaRMSNorm(x + rec)) without rounding the normalised row to bf16)
 //   MoR depth   from l = sum_d x_d * mor_w_d + b on the raw row (recursion 0 only)
 constexpr int SCORE_ROWS = 4;
-template <int NCH>
+template <int NCH, bool HAS_MOD, bool HAS_ROUTER>
 __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __restrict__ cur,
                                                         const float* __restrict__ rec, const float* __restrict__ mod_wn,
                                                         const float* __restrict__ mod_b,
@@ -149,13 +149,13 @@ __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __r
 #pragma unroll
     for (int j = 0; j < 8; ++j) wn[j] = rc[j] = wr[j] = 0.f;
     if (i < D) {
-      if (mod_wn != nullptr) {
+      if (HAS_MOD) {
         const float4 a0 = *reinterpret_cast<const float4*>(mod_wn + i), a1 = *reinterpret_cast<const float4*>(mod_wn + i + 4);
         const float4 b0 = *reinterpret_cast<const float4*>(rec + i), b1 = *reinterpret_cast<const float4*>(rec + i + 4);
         wn[0] = a0.x; wn[1] = a0.y; wn[2] = a0.z; wn[3] = a0.w; wn[4] = a1.x; wn[5] = a1.y; wn[6] = a1.z; wn[7] = a1.w;
         rc[0] = b0.x; rc[1] = b0.y; rc[2] = b0.z; rc[3] = b0.w; rc[4] = b1.x; rc[5] = b1.y; rc[6] = b1.z; rc[7] = b1.w;
       }
-      if (mor_w != nullptr) {
+      if (HAS_ROUTER) {
         const float4 a0 = *reinterpret_cast<const float4*>(mor_w + i), a1 = *reinterpret_cast<const float4*>(mor_w + i + 4);
         wr[0] = a0.x; wr[1] = a0.y; wr[2] = a0.z; wr[3] = a0.w; wr[4] = a1.x; wr[5] = a1.y; wr[6] = a1.z; wr[7] = a1.w;
       }
@@ -166,19 +166,26 @@ __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __r
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float x = (j & 1) ? __uint_as_float(w4[j >> 1] & 0xffff0000u) : __uint_as_float(w4[j >> 1] << 16);
-        const float xr = x + rc[j];
-        ss[r] += xr * xr;
-        dm[r] += xr * wn[j];
-        lm[r] += x * wr[j];
+        if (HAS_MOD) {
+          const float xr = x + rc[j];
+          ss[r] += xr * xr;
+          dm[r] += xr * wn[j];
+        }
+        if (HAS_ROUTER) lm[r] += x * wr[j];
       }
     }
   }
 #pragma unroll
   for (int r = 0; r < SCORE_ROWS; ++r) {
-    const float s2 = warp_sum(ss[r]), d2 = warp_sum(dm[r]), l2 = warp_sum(lm[r]);
+    float s2 = 0.f, d2 = 0.f, l2 = 0.f;
+    if (HAS_MOD) {
+      s2 = warp_sum(ss[r]);
+      d2 = warp_sum(dm[r]);
+    }
+    if (HAS_ROUTER) l2 = warp_sum(lm[r]);
     if (lane == 0 && row0 + r < T) {
-      if (mod_wn != nullptr) scores[row0 + r] = rsqrtf(s2 / (float)D + eps) * d2 + mod_b[0];
-      if (mor_w != nullptr) {
+      if (HAS_MOD) scores[row0 + r] = rsqrtf(s2 / (float)D + eps) * d2 + mod_b[0];
+      if (HAS_ROUTER) {
         const float l = l2 + mor_b[0];
         if (logits != nullptr) logits[row0 + r] = l;
         if (depth != nullptr) depth[row0 + r] = mor_depth_from_logit(l, n_rec, min_d);
@@ -435,9 +442,14 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
     float* scores = (taps && taps->mod_scores) ? taps->mod_scores + ((size_t)bi * R + r) * T : w.scores;
     if (need_router || has_mod) {
       ProfScope ps(m->profile, st, HB200_K_MOR_SCORE, bi, r, T, D, 0);
-      HB_DISPATCH_NCH(D, mor_score_kernel<NCH><<<(unsigned)ceil_div(T, 8 * SCORE_ROWS), 256, 0, st>>>(
-                             w.cur, rec, has_mod ? bw.mod_wn : nullptr, bw.mod_b, need_router ? bw.mor_w : nullptr,
-                             bw.mor_b, scores, logits, force ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth));
+#define HB_SCORE(MOD_, ROUTER_)                                                                                   \
+  HB_DISPATCH_NCH(D, mor_score_kernel<NCH, MOD_, ROUTER_><<<(unsigned)ceil_div(T, 8 * SCORE_ROWS), 256, 0, st>>>( \
+                         w.cur, rec, bw.mod_wn, bw.mod_b, bw.mor_w, bw.mor_b, scores, logits,                     \
+                         force ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth))
+      if (has_mod && need_router) HB_SCORE(true, true);
+      else if (has_mod) HB_SCORE(true, false);
+      else HB_SCORE(false, true);
+#undef HB_SCORE
       HB_LAUNCH_CHECK();
     }
     int32_t* count = counts + (size_t)bi * R + r;

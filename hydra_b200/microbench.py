@@ -259,9 +259,26 @@ def swiglu_act(args) -> dict:
             "note": "includes the torch custom-op dispatch and output allocation"}
 
 
+def model_hidden(args) -> dict:
+    """The 250M model without the output projection (forward_hidden), batch x 2048: a few GB on the device, every
+    block kernel at its full-size shape - the command used to capture the row / routing kernels under ncu."""
+    from .model import HydraB200Model, random_state_dict
+    arch = dict(vocab_size=50257, dim=1024, n_mor_blocks=10, recursions_per_block=4, n_heads=8, n_kv_heads=2,
+                compression_factor=4, mlp_ratio=2.67, mod_capacity=0.75)
+    sd = random_state_dict(seed=0, device="cuda", **arch)
+    m = HydraB200Model(sd, n_heads=8, n_kv_heads=2, max_seq_len=2048, mod_capacity=0.75, device="cuda")
+    B = args.batch
+    ids = torch.randint(0, 50257, (B, 2048), generator=torch.Generator().manual_seed(1)).cuda()
+    ms = _time(lambda i: m.forward_hidden(ids), args.iters, warmup=1)
+    m.check_device_errors()
+    return {"kernel": "HydraB200Model.forward_hidden (10 blocks, no lm_head)", "shape": [B, 2048, 1024], "ms": ms,
+            "bound": "tensor", "achieved": B * 2048 / (ms * 1e-3) / 1e6, "unit": "Mtok/s"}
+
+
 CASES: Dict[str, Callable] = {
     "gemm": gemm, "ccgqa_block": ccgqa_block, "pre_attention": pre_attention, "attention": attention,
     "rms_norm": rms_norm, "rope": rope, "swiglu_ffn": swiglu_ffn, "swiglu_act": swiglu_act,
+    "model_hidden": model_hidden,
 }
 
 
