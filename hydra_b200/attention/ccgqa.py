@@ -101,6 +101,30 @@ class CCGQAAttention(nn.Module):
             self._packed_key = key
         return self._packed
 
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
+                              error_msgs):
+        """Accept the reference's older checkpoint layouts (attention.py:333-383): separate ``q_down`` / ``k_down`` /
+        ``v_down`` (/ ``v_shift_down``) projections are concatenated into ``qkv_proj``; flat ``q_conv1`` ...
+        ``k_conv2`` become ``q_conv.conv1`` ... ``k_conv.conv2``."""
+        for stem in ("q", "k"):
+            for n in ("1", "2"):
+                for suffix in ("weight", "bias"):
+                    old, new = f"{prefix}{stem}_conv{n}.{suffix}", f"{prefix}{stem}_conv.conv{n}.{suffix}"
+                    if old in state_dict:
+                        val = state_dict.pop(old)
+                        if suffix == "weight" and new not in state_dict:
+                            state_dict[new] = val
+        q_key, qkv_key = prefix + "q_down.weight", prefix + "qkv_proj.weight"
+        if q_key in state_dict and qkv_key not in state_dict:
+            parts = [state_dict.pop(q_key), state_dict.pop(prefix + "k_down.weight"),
+                     state_dict.pop(prefix + "v_down.weight")]
+            vs = prefix + "v_shift_down.weight"
+            if vs in state_dict:
+                parts.append(state_dict.pop(vs))
+            state_dict[qkv_key] = torch.cat(parts, dim=0)
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
+                                      error_msgs)
+
     def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         if mask is not None:
             raise NotImplementedError("hydra_b200 CCGQAAttention: the padding-mask path is not built (causal only)")

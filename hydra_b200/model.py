@@ -90,6 +90,55 @@ def random_state_dict(*, vocab_size: int = 50257, dim: int, n_mor_blocks: int, r
     return sd
 
 
+def normalize_state_dict(obj) -> Dict[str, Tensor]:
+    """Checkpoint payload -> flat state_dict with the current key names.
+
+    Accepts what the reference writes and what its evaluation helper reads
+    (diagnostics/eval_checkpoint.py:93-99, hydra/training/checkpointing.py:99-192): a bare state_dict or a dict
+    holding it under ``"model"`` / ``"model_state_dict"`` / ``"state_dict"``; ``_orig_mod.`` prefixes left by
+    torch.compile are stripped; the older attention layouts (attention.py:333-383: ``q_down``/``k_down``/``v_down``
+    (+``v_shift_down``) and flat ``q_conv1`` ... ``k_conv2``) are folded into ``qkv_proj`` / ``q_conv.conv1`` ...;
+    the tied ``output.weight`` and MoD bookkeeping buffers are dropped."""
+    sd = obj
+    if isinstance(obj, dict):
+        for key in ("model", "model_state_dict", "state_dict"):
+            if key in obj and isinstance(obj[key], dict):
+                sd = obj[key]
+                break
+    out: Dict[str, Tensor] = {}
+    for k, v in sd.items():
+        if not torch.is_tensor(v):
+            continue
+        while k.startswith("_orig_mod.") or k.startswith("module."):
+            k = k.split(".", 1)[1]
+        out[k] = v
+    prefixes = sorted({k[: -len("q_down.weight")] for k in out if k.endswith("attention.q_down.weight")})
+    for pre in prefixes:
+        if pre + "qkv_proj.weight" not in out:
+            parts = [out.pop(pre + "q_down.weight"), out.pop(pre + "k_down.weight"), out.pop(pre + "v_down.weight")]
+            if pre + "v_shift_down.weight" in out:
+                parts.append(out.pop(pre + "v_shift_down.weight"))
+            out[pre + "qkv_proj.weight"] = torch.cat(parts, dim=0)
+    for k in list(out):
+        for stem in ("q", "k"):
+            for n in ("1", "2"):
+                old = f"attention.{stem}_conv{n}.weight"
+                if k.endswith(old):
+                    out.setdefault(k[: -len(old)] + f"attention.{stem}_conv.conv{n}.weight", out.pop(k))
+    for k in list(out):
+        if k == "output.weight" or k.endswith("._aux_loss") or ".mod_mlp_wrapper.mlp." in k:
+            out.pop(k)
+    return out
+
+
+def load_checkpoint(path: str, **model_kwargs) -> "HydraB200Model":
+    """Build a HydraB200Model from a checkpoint file written by the reference's trainer (``torch.save`` payload with the
+    weights under ``"model"``).  Head counts and routing settings are not stored in the weights: pass ``n_heads``,
+    ``n_kv_heads`` and, unless the defaults apply, ``mod_capacity`` / ``mor_min_depth`` / ``max_seq_len``."""
+    payload = torch.load(path, map_location="cpu", weights_only=False)
+    return HydraB200Model(normalize_state_dict(payload), **model_kwargs)
+
+
 class HydraB200Model:
     """Inference-only HYDRA model on one B200.
 
@@ -105,7 +154,7 @@ class HydraB200Model:
             raise RuntimeError("HydraB200Model needs a CUDA device (there is no CPU fallback)")
         if dev.index is None:
             dev = torch.device("cuda", torch.cuda.current_device())
-        sd = {(k[len("_orig_mod."):] if k.startswith("_orig_mod.") else k): v for k, v in state_dict.items()}
+        sd = normalize_state_dict(state_dict)
         V, D = sd["tok_emb.weight"].shape
         nb = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("layers."))
         R = sd["layers.0.mor_executor.recursion_embed.weight"].shape[0]

@@ -87,6 +87,35 @@ def test_factory_builds_module_with_reference_parameter_layout(monkeypatch):
                                       attention_kwargs={"use_convs": False})
 
 
+def test_legacy_checkpoint_layouts_are_remapped():
+    """Older reference checkpoints (hydra/attention/backends/ccgqa/attention.py:333-383): separate down projections and
+    flat conv names load into the fused layout; compile / wrapper prefixes are stripped."""
+    from hydra_b200.attention import build_hybrid_attention_module
+    from hydra_b200.model import normalize_state_dict
+    m = build_hybrid_attention_module("ccqa", dim=512, n_heads=8, n_kv_heads=2, max_seq_len=32, compression_factor=4,
+                                      attention_kwargs={})
+    g = torch.Generator().manual_seed(0)
+    lat, kvd, hd = 128, 32, 16
+    legacy = {
+        "q_down.weight": torch.randn(lat, 512, generator=g), "k_down.weight": torch.randn(kvd, 512, generator=g),
+        "v_down.weight": torch.randn(kvd // 2, 512, generator=g), "v_shift_down.weight": torch.randn(kvd // 2, 512, generator=g),
+        "o_proj.weight": torch.randn(512, lat, generator=g), "key_temperature": torch.tensor([3.0]),
+        "q_conv1.weight": torch.randn(lat, hd, 3, generator=g), "q_conv2.weight": torch.randn(lat, lat, 3, generator=g),
+        "k_conv1.weight": torch.randn(kvd, hd, 3, generator=g), "k_conv2.weight": torch.randn(kvd, kvd, 3, generator=g),
+    }
+    m.load_state_dict(dict(legacy), strict=True)
+    want = torch.cat([legacy["q_down.weight"], legacy["k_down.weight"], legacy["v_down.weight"], legacy["v_shift_down.weight"]])
+    assert torch.equal(m.qkv_proj.weight, want)
+    assert torch.equal(m.q_conv.conv2.weight, legacy["q_conv2.weight"]) and torch.equal(m.k_conv.conv1.weight, legacy["k_conv1.weight"])
+    payload = {"model": {"_orig_mod.layers.0.attention." + k: v for k, v in legacy.items()}, "step": 7}
+    payload["model"]["_orig_mod.output.weight"] = torch.zeros(2, 2)
+    payload["model"]["_orig_mod.layers.0.mod_mlp_wrapper.mod_router._aux_loss"] = torch.zeros(())
+    sd = normalize_state_dict(payload)
+    assert "layers.0.attention.qkv_proj.weight" in sd and torch.equal(sd["layers.0.attention.qkv_proj.weight"], want)
+    assert "layers.0.attention.q_conv.conv1.weight" in sd and "output.weight" not in sd
+    assert not any("_aux_loss" in k or "q_down" in k or "_orig_mod" in k for k in sd)
+
+
 def test_product_path_refuses_cpu_tensors():
     import hydra_b200.kernels as K
     from hydra_b200.attention import build_hybrid_attention_module
