@@ -32,11 +32,14 @@ constexpr int GROUP_M = 16;         // m-tiles per rasterisation group (keeps an
 constexpr int EPI_WARPS = 8;        // two per TMEM lane quadrant
 constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;
 
-template <int BN> struct GemmCfg {
+// NSTAGES = 0 selects the default ring depth for the tile width; a shallow ring (2 stages, 128-wide tiles) leaves
+// room for two CTAs per SM, which is what the short-K, epilogue-bound contractions want (o_proj: K = 256).
+template <int BN, int NSTAGES = 0> struct GemmCfg {
   static constexpr int A_BYTES = GBM * GBK * 2;
   static constexpr int B_BYTES = BN * GBK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = NSTAGES > 0 ? NSTAGES : ((BN == 256) ? 4 : 6);
+  static constexpr int CTAS_PER_SM = (NSTAGES > 0 && NSTAGES <= 2 && BN == 128) ? 2 : 1;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int BAR_BYTES = 256;
   static constexpr int STORE_BOX_BYTES = 32 * 128;                 // one TMA store box: 32 rows x 64 bf16
@@ -55,12 +58,12 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   mt = first_m + in % gm;
 }
 
-template <int BN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
+template <int BN, int NSTAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_SM)) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                               const __grid_constant__ CUtensorMap tma_b,
                                                               const __grid_constant__ CUtensorMap tma_c,
                                                               const GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, NSTAGES>;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (s_addr(smem_dyn) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_dyn + (base - s_addr(smem_dyn));
@@ -335,9 +338,9 @@ static int sm_count() {
   return n;
 }
 
-template <int BN>
+template <int BN, int NSTAGES = 0>
 static int launch_bn(const GemmParams& p, cudaStream_t st) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, NSTAGES>;
   CUtensorMap ta, tb, tc;
   HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, GBM));
   HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, BN));
@@ -348,14 +351,14 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
   } else {
     tc = ta;   // unused by the direct epilogues
   }
-  auto kern = gemm_tcgen05_kernel<BN>;
+  auto kern = gemm_tcgen05_kernel<BN, NSTAGES>;
   static bool attr_set = false;
   if (!attr_set) {
     HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     attr_set = true;
   }
   const int64_t tiles = (int64_t)ceil_div(p.M, GBM) * ceil_div(p.N, BN);
-  const int grid = (int)std::min<int64_t>(tiles, sm_count());
+  const int grid = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * Cfg::CTAS_PER_SM);
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, tc, p);
   HB_LAUNCH_CHECK();
   return 0;
@@ -365,6 +368,10 @@ int launch_gemm_tcgen05(const GemmParams& p, cudaStream_t st) {
   // wide tiles unless N is a small multiple of 128 (qkv projection: 384); the SwiGLU epilogue pairs columns inside
   // 128-column halves of a 256-wide tile and always takes the wide kernel
   if (p.epilogue != EPI_SWIGLU && p.N % 256 != 0 && p.N % 128 == 0 && p.N <= 1024) return launch_bn<128>(p, st);
+  // short K with a read-modify-write epilogue (o_proj + residual): the epilogue dominates, so run two narrower CTAs
+  // per SM (2 x 256 TMEM columns, 2 x 97 KB of shared memory) and let their epilogues overlap
+  if ((p.epilogue == EPI_RESID || p.epilogue == EPI_SCATTER_ADD) && p.K <= 512 && p.N % 128 == 0)
+    return launch_bn<128, 2>(p, st);
   return launch_bn<256>(p, st);
 }
 
