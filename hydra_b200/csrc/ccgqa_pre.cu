@@ -18,11 +18,9 @@
 
 namespace hb200 {
 
-constexpr int TT = 64;          // tokens per tile
-constexpr int XR = TT + 18;     // x rows held (t0-18 .. t0+63)
-constexpr int YR = TT + 16;     // conv1 rows held (t0-16 .. t0+63), 5 m16 tiles
-constexpr int KC = 64;          // conv2 K chunk
-constexpr int WLD = KC + 8;     // padded row of a weight chunk (conflict-free fragment loads)
+// Tile geometry (template parameters of the kernel): TT tokens per tile, XR = TT + 18 input rows held
+// (t0-18 .. t0+TT-1), YR = TT + 16 conv1 rows held (t0-16 .. t0+TT-1), KC = conv2 K chunk, WLD = KC + 8 padded
+// weight-chunk row (conflict-free fragment loads).  64/64 is the default; latent 512 uses 32/32 to fit.
 
 struct PreParams {
   const __nv_bfloat16* qkv;
@@ -39,11 +37,12 @@ struct PreParams {
 };
 
 // out[m][n] (fp32 regs) = sum_{j<3} sum_{c<Cin} Y1[m + 14 + j][col_off + c] * W[n][j*Cin + c]
-template <int WM, int WN, int MT, int NT>
+template <int WM, int WN, int MT, int NT, int KC>
 __device__ __forceinline__ void conv2_tile(const __nv_bfloat16* __restrict__ Y1, int ldx, int col_off, int Cin,
                                            const __nv_bfloat16* __restrict__ Wg, __nv_bfloat16* wbuf,
                                            float (&acc)[MT][NT][4]) {
   static_assert(WM * WN == 8, "8 warps");
+  constexpr int WLD = KC + 8;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int warp_m = warp / WN, warp_n = warp % WN;
@@ -122,9 +121,11 @@ __device__ __forceinline__ void store_acc(float* out, int ldo, const float (&acc
     }
 }
 
-// HD: head dim; NTQ = lat/32; NTK = kvd/16
-template <int HD, int NTQ, int NTK>
+// HD: head dim; NTQ = lat/32; NTK = kvd/16; TT tokens per tile (64 or 32); KC conv2 K chunk
+template <int HD, int NTQ, int NTK, int TT, int KC>
 __global__ void __launch_bounds__(256, 1) ccgqa_pre_kernel(const PreParams p) {
+  constexpr int XR = TT + 18, YR = TT + 16, WLD = KC + 8;
+  constexpr int MTQ = TT / 32, MTK = TT / 64;   // m16 tiles per warp in the q (2 m-warps) and k (4 m-warps) conv2
   constexpr int LAT = NTQ * 32, KVD = NTK * 16, C = LAT + KVD;
   constexpr int LDX = C + 8;        // bf16 elements; 16-byte multiple, bank-staggered rows
   constexpr int LDQ = LAT + 4, LDK = KVD + 4;
@@ -198,14 +199,21 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_kernel(const PreParams p) {
 
   // ---- 3. conv2 (dense): K first (small), then Q ---------------------------------------------
   {
-    float acck[1][NTK][4];
-    conv2_tile<4, 2, 1, NTK>(Y1, LDX, LAT, KVD, p.w2k, Wb, acck);
-    store_acc<4, 2, 1, NTK>(OutK, LDK, acck);
+    if constexpr (MTK >= 1) {
+      float acck[MTK][NTK][4];
+      conv2_tile<4, 2, MTK, NTK, KC>(Y1, LDX, LAT, KVD, p.w2k, Wb, acck);
+      store_acc<4, 2, MTK, NTK>(OutK, LDK, acck);
+    } else {   // 32-token tile: two m-warps of 16 rows, four n-warps
+      static_assert(TT == 32 && NTK % 2 == 0, "32-token tiles need kv_dim divisible by 32");
+      float acck[1][NTK / 2][4];
+      conv2_tile<2, 4, 1, NTK / 2, KC>(Y1, LDX, LAT, KVD, p.w2k, Wb, acck);
+      store_acc<2, 4, 1, NTK / 2>(OutK, LDK, acck);
+    }
   }
   {
-    float accq[2][NTQ][4];
-    conv2_tile<2, 4, 2, NTQ>(Y1, LDX, 0, LAT, p.w2q, Wb, accq);   // ends with __syncthreads(): Y1/Wb are dead
-    store_acc<2, 4, 2, NTQ>(OutQ, LDQ, accq);
+    float accq[MTQ][NTQ][4];
+    conv2_tile<2, 4, MTQ, NTQ, KC>(Y1, LDX, 0, LAT, p.w2q, Wb, accq);   // ends with __syncthreads(): Y1/Wb are dead
+    store_acc<2, 4, MTQ, NTQ>(OutQ, LDQ, accq);
   }
   __syncthreads();
 
@@ -294,13 +302,14 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_kernel(const PreParams p) {
   }
 }
 
-template <int HD, int NTQ, int NTK>
+template <int HD, int NTQ, int NTK, int TT = 64, int KC = 64>
 static int launch_pre(const PreParams& p, cudaStream_t st) {
+  constexpr int XR = TT + 18, YR = TT + 16, WLD = KC + 8;
   constexpr int LAT = NTQ * 32, KVD = NTK * 16, C = LAT + KVD, LDX = C + 8;
   constexpr int WROWS = (LAT > KVD ? LAT : KVD);
   constexpr size_t smem = (size_t)(XR + YR) * LDX * 2 + (size_t)2 * WROWS * WLD * 2 + (size_t)TT * (KVD + 4) * 4;
   static_assert(smem <= 227 * 1024, "tile does not fit in shared memory");
-  auto kern = ccgqa_pre_kernel<HD, NTQ, NTK>;
+  auto kern = ccgqa_pre_kernel<HD, NTQ, NTK, TT, KC>;
   static bool attr_set = false;
   if (!attr_set) {
     HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -354,6 +363,8 @@ extern "C" int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, con
   HB_PRE_CASE(16, 2, 4)    // dim 256: 4q/4kv heads of 16 (H == KV)
   HB_PRE_CASE(64, 4, 8)    // dim 512: 2q/2kv heads of 64
 #undef HB_PRE_CASE
+  // latent 512 (dim 2048, 32q/4kv heads of 16: the 1.5B shape): 32-token tiles and 32-wide weight chunks to fit
+  if (hd == 16 && lat == 512 && kvd == 64) return launch_pre<16, 16, 4, 32, 32>(p, st);
   set_error("ccgqa_pre_attention: no kernel built for head_dim=%d latent=%d kv_dim=%d", hd, lat, kvd);
   return HB200_ERR_UNSUPPORTED;
 }

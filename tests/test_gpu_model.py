@@ -158,6 +158,37 @@ def test_config1_debug_variant_against_oracle(nb, label):
     compare_with_oracle(m, w, cfg, ids, None, None, label)
 
 
+def test_1p5b_shape_blocks_against_oracle():
+    """The 1.5B preset's block shape (dim 2048, 32 query / 4 KV heads of 16: latent 512, 8:1 GQA) at 3 blocks x 2
+    recursions with a small vocabulary, against the oracle."""
+    cfg = O.HydraConfig(vocab_size=512, dim=2048, n_mor_blocks=3, recursions_per_block=2, n_heads=32, n_kv_heads=4,
+                        max_seq_len=160, mod_capacity=0.75)
+    w = O.init_params(cfg, seed=3, perturb=True)
+    ids = torch.randint(0, 512, (2, 160), generator=torch.Generator().manual_seed(3))
+    compare_with_oracle(build(w, cfg), w, cfg, ids, None, None, "1.5B-shape")
+
+
+@pytest.mark.parametrize("B,S", [(1, 1), (1, 7), (3, 77), (2, 131), (1, 257)])
+def test_ragged_batch_and_sequence_sizes(B, S):
+    """Sizes that are not multiples of any tile (rows, keys, tokens per conv tile, TMA boxes), down to a single token."""
+    cfg = O.HydraConfig(vocab_size=1000, dim=512, n_mor_blocks=3, recursions_per_block=2, n_heads=8, n_kv_heads=2,
+                        max_seq_len=320, mod_capacity=0.75)
+    w = O.init_params(cfg, seed=7, perturb=True)
+    ids = torch.randint(0, 1000, (B, S), generator=torch.Generator().manual_seed(S))
+    m = build(w, cfg)
+    lg = m(ids.cuda(), taps=True).float().cpu()
+    m.check_device_errors()
+    rt = taps_to_oracle(m, m.last_taps, B, S)
+    ref = O.model_forward(ids, w, cfg, forced=rt)
+    assert lg.shape == (B, S, 1000) and torch.isfinite(lg).all()
+    assert rel_l2(lg, ref) <= 1e-2, f"B={B} S={S}: rel_l2 {rel_l2(lg, ref):.3e}"
+    free = O.RoutingTaps()
+    O.model_forward(ids, w, cfg, taps=free)
+    d = m.last_taps.depths.cpu().long().view(3, B, S)
+    agree = sum(int((d[i] == free.depths[i]).sum()) for i in range(3)) / (3 * B * S)
+    assert agree >= 0.97 or B * S < 40
+
+
 def test_batch_independence_determinism_and_sharding_250m():
     """BASELINE config 4 architecture (dim 1024, 10x4, 8q/2kv, F 2816, MoD 0.75, S 2048) at batch 4: properties that
     hold at any size - two runs agree bit for bit, a sequence run alone equals the same sequence inside the batch
