@@ -162,12 +162,29 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_const
   const uint32_t tmem_base = *tmem_slot;
 
   // ---------------- phase 1b: conv1 (grouped) on mma.sync: y1 row r <-> token t0-2+r ----------------
+  // Work units are (head, m16 tile), head-major; each warp takes a contiguous range, so it changes head at most
+  // twice and keeps the head's whole weight block (3*hd x hd) in registers as B fragments: the inner loop touches
+  // shared memory only (the 61 KB weight would not survive in the little L1 left beside 224 KB of shared memory).
   {
     constexpr int NT1 = HD / 8, KS1 = 3 * HD / 16, MT = YROWS / 16;
     const int units = MT * (H + KV);
-    for (int u = warp; u < units; u += 8) {
-      const int mt = u % MT, hg = u / MT;
+    const int u_begin = (units * warp) / 8, u_end = (units * (warp + 1)) / 8;
+    uint32_t bfrag[KS1][NT1][2];
+    int cur_head = -1;
+    for (int u = u_begin; u < u_end; ++u) {
+      const int hg = u / MT, mt = u % MT;
       const int cb = hg * HD;
+      if (hg != cur_head) {
+        cur_head = hg;
+#pragma unroll
+        for (int ks = 0; ks < KS1; ++ks)
+#pragma unroll
+          for (int nt = 0; nt < NT1; ++nt) {
+            const __nv_bfloat16* wr = p.w1 + (size_t)(cb + nt * 8 + g) * (3 * HD) + ks * 16 + 2 * t4;
+            bfrag[ks][nt][0] = __ldg(reinterpret_cast<const unsigned int*>(wr));
+            bfrag[ks][nt][1] = __ldg(reinterpret_cast<const unsigned int*>(wr + 8));
+          }
+      }
       float acc[NT1][4];
 #pragma unroll
       for (int i = 0; i < NT1; ++i)
@@ -184,12 +201,7 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_const
         const uint32_t a2 = *reinterpret_cast<const uint32_t*>(r0 + 8);
         const uint32_t a3 = *reinterpret_cast<const uint32_t*>(r1 + 8);
 #pragma unroll
-        for (int nt = 0; nt < NT1; ++nt) {
-          const __nv_bfloat16* wr = p.w1 + (size_t)(cb + nt * 8 + g) * (3 * HD) + kk0 + 2 * t4;
-          const uint32_t b0 = __ldg(reinterpret_cast<const unsigned int*>(wr));
-          const uint32_t b1 = __ldg(reinterpret_cast<const unsigned int*>(wr + 8));
-          mma_bf16_16816(acc[nt], a0, a1, a2, a3, b0, b1);
-        }
+        for (int nt = 0; nt < NT1; ++nt) mma_bf16_16816(acc[nt], a0, a1, a2, a3, bfrag[ks][nt][0], bfrag[ks][nt][1]);
       }
       // C fragment (row, cols 2t..2t+1 of n-tile nt) -> chunk (cb/8 + nt), row, element 2t
 #pragma unroll
