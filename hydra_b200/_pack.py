@@ -124,14 +124,19 @@ class PackedModel:
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)
 
     def workspace(self, B: int, S: int) -> Tensor:
-        key = (B, S)
-        ws = self._ws.get(key)
-        if ws is None:
-            n = _lib.lib().hb200_model_workspace_bytes(C.byref(self.struct), B, S)
-            self._ws.clear()   # one live shape at a time keeps the footprint bounded
+        """A workspace of at least hb200_model_workspace_bytes(B, S); one buffer is kept and grown on demand, so a
+        generation loop whose sequence grows by one token per step does not reallocate every step."""
+        n = _lib.lib().hb200_model_workspace_bytes(C.byref(self.struct), B, S)
+        ws = self._ws.get("buf")
+        if ws is None or ws.numel() < n:
+            self._ws.clear()
             ws = torch.empty(n, dtype=torch.uint8, device=self.device)
-            self._ws[key] = ws
+            self._ws["buf"] = ws
         return ws
+
+    def reserve(self, B: int, S: int) -> None:
+        """Allocate the workspace for the largest [B, S] that will be run."""
+        self.workspace(B, S)
 
     def check_device_errors(self) -> None:
         """Synchronises and raises if a bounded in-kernel wait ran out during an earlier call."""

@@ -299,9 +299,45 @@ __global__ void mor_depths_kernel(const float* __restrict__ logits, int32_t* __r
   if (i < n) depth[i] = mor_depth_from_logit(logits[i], n_rec, min_d);
 }
 
+// Greedy token choice: index of the largest value of each bf16 row (lowest index among equal maxima; NaN never wins).
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* __restrict__ x, int cols, int64_t ld,
+                                                          int64_t* __restrict__ out) {
+  __shared__ float s_val[8];
+  __shared__ int s_idx[8];
+  const __nv_bfloat16* row = x + (int64_t)blockIdx.x * ld;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    const float v = __bfloat162float(row[i]);
+    if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = best_i; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_i)) { best = s_val[w]; best_i = s_idx[w]; }
+    out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+  }
+}
+
 }  // namespace hb200
 
 using namespace hb200;
+
+extern "C" int hb200_argmax_rows(const void* x, int64_t rows, int cols, int64_t ld, int64_t* out, void* stream) {
+  HB_REQUIRE(x && out, HB200_ERR_INVALID, "argmax_rows: null pointer");
+  HB_REQUIRE(rows >= 0 && cols >= 1 && ld >= cols, HB200_ERR_INVALID, "argmax_rows: bad shape");
+  if (rows == 0) return 0;
+  argmax_rows_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, cols, ld, out);
+  HB_LAUNCH_CHECK();
+  return 0;
+}
 
 extern "C" int hb200_rms_norm(const void* x, const void* w, void* y, int64_t rows, int dim, float eps, int dtype,
                               int w_dtype, void* stream) {

@@ -281,6 +281,40 @@ class HydraB200Model:
         torch.cuda.current_stream(self.device).synchronize()
         return out_host
 
+    def generate(self, prompt_ids: Tensor, max_new_tokens: int) -> Tensor:
+        """Greedy generation in the reference's way: the whole sequence is run through the model again for every new
+        token (diagnostics/eval_checkpoint.py:127-160 re-forwards ``generated`` each step; the reference has no KV
+        cache).  Exact with respect to the eval forward, including MoD's top-k over the growing sequence, at O(S^2)
+        cost.  Only the last position is projected to the vocabulary.  Deterministic form of the reference's sampler
+        (temperature -> 0): next token = argmax of the last position's logits.
+        prompt_ids int64 [B, P] on this device -> int64 [B, P + max_new_tokens]."""
+        if not prompt_ids.is_cuda or prompt_ids.device != self.device:
+            raise RuntimeError(f"prompt_ids must be on {self.device} (there is no CPU fallback)")
+        B, P = prompt_ids.shape
+        total = P + int(max_new_tokens)
+        if total > self.max_seq_len:
+            raise ValueError(f"prompt + new tokens = {total} exceeds max_seq_len {self.max_seq_len}")
+        seq = torch.empty((B, total), dtype=torch.int64, device=self.device)
+        seq[:, :P] = prompt_ids
+        self.packed.reserve(B, total)
+        ld = self.ld_logits
+        last_logits = torch.empty((B, ld), dtype=torch.bfloat16, device=self.device)
+        nxt = torch.empty((B,), dtype=torch.int64, device=self.device)
+        lib = _lib.lib()
+        for cur in range(P, total):
+            hid = self.forward(seq[:, :cur], logits=False, hidden=True)            # [B, cur, D]
+            last = hid[:, -1, :].contiguous()
+            with kernels._on(self.device):
+                st = kernels._stream(self.device)
+                _lib.check(lib.hb200_gemm_bf16(last.data_ptr(), self.packed.tok_emb.data_ptr(), last_logits.data_ptr(),
+                                               B, self.vocab_size, self.dim, self.dim, self.dim, ld, _lib.EPI_STORE,
+                                               None, 1.0, None, None, self.packed.struct.gemm_impl,
+                                               self.packed.err_flag.data_ptr(), st), "lm_head (last position)")
+                _lib.check(lib.hb200_argmax_rows(last_logits.data_ptr(), B, self.vocab_size, ld, nxt.data_ptr(), st),
+                           "argmax_rows")
+            seq[:, cur] = nxt
+        return seq
+
     def check_device_errors(self) -> None:
         self.packed.check_device_errors()
 

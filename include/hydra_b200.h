@@ -162,6 +162,11 @@ int hb200_mor_depths(const float* logits, int32_t* depth, int64_t n, int n_rec, 
 int hb200_embed(const int64_t* ids, const void* table, void* out, int64_t T, int D, int V,
                 float scale, void* stream);
 
+/* Greedy next-token choice: out[r] = argmax over the first `cols` entries of bf16 row r (rows are `ld` elements
+ * apart; lowest index among equal maxima).  Stands for the sampling step of the reference's generation helper
+ * (diagnostics/eval_checkpoint.py:112-166) in its deterministic, temperature-free form. */
+int hb200_argmax_rows(const void* x, int64_t rows, int cols, int64_t ld, int64_t* out, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Whole block / whole model  (hydra/model/framework/blocks.py:608-632,
  *                             hydra/model/framework/model.py:408-506)

@@ -374,6 +374,24 @@ def model_forward(ids: Tensor, p: Dict[str, Tensor], cfg: HydraConfig,
     return h @ w_out.transpose(0, 1)
 
 
+def greedy_generate(prompt_ids: Tensor, p: Dict[str, Tensor], cfg: HydraConfig, max_new_tokens: int,
+                    return_margins: bool = False):
+    """Greedy form of the reference's generation loop (diagnostics/eval_checkpoint.py:127-160): the full forward is
+    re-run on the whole sequence for every new token (the reference has no KV cache); next token = argmax of the
+    last position's logits (its sampler with temperature -> 0, top-k/top-p off).  With ``return_margins`` also the
+    gap between the best and second-best logit at every step."""
+    seq = prompt_ids.clone()
+    margins = []
+    for _ in range(max_new_tokens):
+        logits = model_forward(seq, p, cfg)[:, -1, :]
+        top2 = logits.topk(2, dim=-1).values
+        margins.append(top2[:, 0] - top2[:, 1])
+        seq = torch.cat([seq, logits.argmax(dim=-1, keepdim=True)], dim=1)
+    if return_margins:
+        return seq, torch.stack(margins, dim=1)
+    return seq
+
+
 # ----------------------------------------------------------------------------
 # seeded random-init weights with the reference's distributions
 # ----------------------------------------------------------------------------
