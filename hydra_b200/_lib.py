@@ -46,6 +46,11 @@ class Taps(C.Structure):
                 ("mlp_rows", c_vp), ("block_out", c_vp), ("force_routing", C.c_int32)]
 
 
+class DecodeState(C.Structure):
+    _fields_ = [("batch", C.c_int32), ("capacity", C.c_int32), ("kcache", c_vp), ("vcache", c_vp), ("halo", c_vp),
+                ("vshift", c_vp), ("scores", c_vp), ("pos", c_vp), ("tokens", c_vp), ("history", c_vp)]
+
+
 # name -> (restype, argtypes); mirrors include/hydra_b200.h one to one
 SIGNATURES = {
     "hb200_version": (c_i32, []),
@@ -71,6 +76,10 @@ SIGNATURES = {
     "hb200_block_forward": (c_i32, [C.POINTER(Model), c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_sz,
                                     C.POINTER(Taps), c_vp, c_vp]),
     "hb200_ccgqa_forward": (c_i32, [C.POINTER(Model), c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_sz, c_vp, c_vp]),
+    "hb200_decode_workspace_bytes": (c_sz, [C.POINTER(Model), c_i32]),
+    "hb200_model_prefill_cached": (c_i32, [C.POINTER(Model), c_vp, c_i32, c_i32, c_vp, c_sz, C.POINTER(DecodeState),
+                                           c_vp, c_i64, c_vp, c_vp]),
+    "hb200_model_decode_step": (c_i32, [C.POINTER(Model), C.POINTER(DecodeState), c_vp, c_sz, c_vp, c_i64, c_vp, c_vp]),
     "hb200_ccgqa_forward_static_max_bytes": (c_sz, []),
     "hb200_ccgqa_forward_static": (c_i32, [C.POINTER(Model), c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp]),
     "hb200_profile_create": (c_vp, [c_i32]),

@@ -25,264 +25,9 @@
 #include <vector>
 
 #include "gemm_epilogue.cuh"
+#include "row_kernels.cuh"
 
 namespace hb200 {
-
-int launch_mod_select(const float* scores, int B, int L, int k, int32_t* idx_out, const int32_t* depth, int min_active,
-                      int32_t* rows_out, int32_t* count, const int32_t* forced_idx, cudaStream_t st);
-int launch_compact_active(const int32_t* depth, int64_t n, int min_active, int32_t* rows_out, int32_t* count,
-                          cudaStream_t st);
-
-// ---- per-launch event recorder ---------------------------------------------------------------------------
-struct Profile {
-  std::vector<cudaEvent_t> ev;          // 2 per launch
-  std::vector<hb200_launch_record> rec;
-  int count = 0;
-  int capacity = 0;
-};
-
-struct ProfScope {
-  Profile* p;
-  cudaStream_t st;
-  int slot;
-  ProfScope(void* prof, cudaStream_t s, int kind, int block, int rec, int m, int n, int k)
-      : p(static_cast<Profile*>(prof)), st(s), slot(-1) {
-    if (p != nullptr && p->count < p->capacity) {
-      slot = p->count++;
-      p->rec[slot] = hb200_launch_record{kind, block, rec, m, n, k};
-      cudaEventRecord(p->ev[2 * slot], st);
-    }
-  }
-  ~ProfScope() {
-    if (slot >= 0) cudaEventRecord(p->ev[2 * slot + 1], st);
-  }
-};
-
-constexpr int ROW_NCH = 8;   // row kernels keep up to 8 x 256 elements of a row in registers (dim <= 2048)
-
-// Launch a row kernel template with the smallest register-resident row that covers `dim`.
-#define HB_DISPATCH_NCH(dim, ...)                 \
-  do {                                            \
-    if ((dim) <= 256) { constexpr int NCH = 1; __VA_ARGS__; }        \
-    else if ((dim) <= 512) { constexpr int NCH = 2; __VA_ARGS__; }   \
-    else if ((dim) <= 1024) { constexpr int NCH = 4; __VA_ARGS__; }  \
-    else { constexpr int NCH = 8; __VA_ARGS__; }                     \
-  } while (0)
-
-// Loads row `src` (+ optional fp32 per-column offset), returns sum of squares; values stay in v.
-template <int NCH>
-__device__ __forceinline__ float load_row_add(const __nv_bfloat16* __restrict__ src, const float* __restrict__ add,
-                                              int D, int lane, float (&v)[NCH][8]) {
-  float ss = 0.f;
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) load_bf16x8(src + i, v[c]);   // all loads of the row are issued before any is consumed
-  }
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) {
-      if (add != nullptr) {
-        const float4 a0 = *reinterpret_cast<const float4*>(add + i);
-        const float4 a1 = *reinterpret_cast<const float4*>(add + i + 4);
-        v[c][0] += a0.x; v[c][1] += a0.y; v[c][2] += a0.z; v[c][3] += a0.w;
-        v[c][4] += a1.x; v[c][5] += a1.y; v[c][6] += a1.z; v[c][7] += a1.w;
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += v[c][j] * v[c][j];
-    }
-  }
-  return warp_sum(ss);
-}
-
-// v <- bf16-rounded (v * r * w)
-template <int NCH>
-__device__ __forceinline__ void scale_row(const float* __restrict__ w, float r, int D, int lane, float (&v)[NCH][8]) {
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) {
-      const float4 w0 = *reinterpret_cast<const float4*>(w + i);
-      const float4 w1 = *reinterpret_cast<const float4*>(w + i + 4);
-      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[c][j] = __bfloat162float(__float2bfloat16_rn(v[c][j] * r * ww[j]));
-    }
-  }
-}
-
-// Router pass over ALL tokens, streaming (no activation is written): four rows per warp so that the per-column
-// vectors are fetched once per four rows.
-//   MoD score   s = rsqrt(mean((x+rec)^2) + eps) * sum_d (x_d + rec_d) * wn_d + b,  wn = norm2 gain * MoD weight
-//               (the fp32 value of Linear(AdaRMSNorm(x + rec)) without rounding the normalised row to bf16)
-//   MoR depth   from l = sum_d x_d * mor_w_d + b on the raw row (recursion 0 only)
-constexpr int SCORE_ROWS = 4;
-template <int NCH, bool HAS_MOD, bool HAS_ROUTER>
-__global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __restrict__ cur,
-                                                        const float* __restrict__ rec, const float* __restrict__ mod_wn,
-                                                        const float* __restrict__ mod_b,
-                                                        const float* __restrict__ mor_w, const float* __restrict__ mor_b,
-                                                        float* __restrict__ scores, float* __restrict__ logits,
-                                                        int32_t* __restrict__ depth, int64_t T, int D, float eps,
-                                                        int n_rec, int min_d) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * SCORE_ROWS;
-  if (row0 >= T) return;
-  // issue every load of the four rows first (up to 16 x 16 bytes in flight per lane)
-  uint4 raw[SCORE_ROWS][NCH];
-#pragma unroll
-  for (int r = 0; r < SCORE_ROWS; ++r)
-#pragma unroll
-    for (int c = 0; c < NCH; ++c) {
-      const int i = (c * 32 + lane) * 8;
-      raw[r][c] = (i < D && row0 + r < T) ? *reinterpret_cast<const uint4*>(cur + (row0 + r) * D + i)
-                                         : make_uint4(0, 0, 0, 0);
-    }
-  float ss[SCORE_ROWS], dm[SCORE_ROWS], lm[SCORE_ROWS];
-#pragma unroll
-  for (int r = 0; r < SCORE_ROWS; ++r) ss[r] = dm[r] = lm[r] = 0.f;
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    float wn[8], rc[8], wr[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) wn[j] = rc[j] = wr[j] = 0.f;
-    if (i < D) {
-      if (HAS_MOD) {
-        const float4 a0 = *reinterpret_cast<const float4*>(mod_wn + i), a1 = *reinterpret_cast<const float4*>(mod_wn + i + 4);
-        const float4 b0 = *reinterpret_cast<const float4*>(rec + i), b1 = *reinterpret_cast<const float4*>(rec + i + 4);
-        wn[0] = a0.x; wn[1] = a0.y; wn[2] = a0.z; wn[3] = a0.w; wn[4] = a1.x; wn[5] = a1.y; wn[6] = a1.z; wn[7] = a1.w;
-        rc[0] = b0.x; rc[1] = b0.y; rc[2] = b0.z; rc[3] = b0.w; rc[4] = b1.x; rc[5] = b1.y; rc[6] = b1.z; rc[7] = b1.w;
-      }
-      if (HAS_ROUTER) {
-        const float4 a0 = *reinterpret_cast<const float4*>(mor_w + i), a1 = *reinterpret_cast<const float4*>(mor_w + i + 4);
-        wr[0] = a0.x; wr[1] = a0.y; wr[2] = a0.z; wr[3] = a0.w; wr[4] = a1.x; wr[5] = a1.y; wr[6] = a1.z; wr[7] = a1.w;
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < SCORE_ROWS; ++r) {
-      const uint32_t w4[4] = {raw[r][c].x, raw[r][c].y, raw[r][c].z, raw[r][c].w};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float x = (j & 1) ? __uint_as_float(w4[j >> 1] & 0xffff0000u) : __uint_as_float(w4[j >> 1] << 16);
-        if (HAS_MOD) {
-          const float xr = x + rc[j];
-          ss[r] += xr * xr;
-          dm[r] += xr * wn[j];
-        }
-        if (HAS_ROUTER) lm[r] += x * wr[j];
-      }
-    }
-  }
-#pragma unroll
-  for (int r = 0; r < SCORE_ROWS; ++r) {
-    float s2 = 0.f, d2 = 0.f, l2 = 0.f;
-    if (HAS_MOD) {
-      s2 = warp_sum(ss[r]);
-      d2 = warp_sum(dm[r]);
-    }
-    if (HAS_ROUTER) l2 = warp_sum(lm[r]);
-    if (lane == 0 && row0 + r < T) {
-      if (HAS_MOD) scores[row0 + r] = rsqrtf(s2 / (float)D + eps) * d2 + mod_b[0];
-      if (HAS_ROUTER) {
-        const float l = l2 + mor_b[0];
-        if (logits != nullptr) logits[row0 + r] = l;
-        if (depth != nullptr) depth[row0 + r] = mor_depth_from_logit(l, n_rec, min_d);
-      }
-    }
-  }
-}
-
-// ug[j] = AdaRMSNorm(cur[rows[j]] + rec) for j < *count.  One warp per compact row.
-template <int NCH>
-__global__ void __launch_bounds__(256) norm_gather_kernel(const __nv_bfloat16* __restrict__ cur,
-                                                          const float* __restrict__ rec, const float* __restrict__ w2,
-                                                          const int32_t* __restrict__ rows,
-                                                          const int32_t* __restrict__ count,
-                                                          __nv_bfloat16* __restrict__ ug, int D, float eps) {
-  const int lane = threadIdx.x & 31;
-  const int64_t j = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (j >= *count) return;
-  const int64_t src = rows[j];
-  float v[NCH][8];
-  const float ss = load_row_add<NCH>(cur + src * D, rec, D, lane, v);
-  scale_row<NCH>(w2, rsqrtf(ss / (float)D + eps), D, lane, v);
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) store_bf16x8(ug + j * D + i, v[c]);
-  }
-}
-
-// y = RMSNorm(src; w1) rounded to bf16 (the block output), z = RMSNorm(y; w2) (the next block's pre-attention norm,
-// or the model's final norm): one read of src instead of three passes.  Either output may be omitted.
-template <int NCH>
-__global__ void __launch_bounds__(256) dual_norm_kernel(const __nv_bfloat16* __restrict__ src,
-                                                        const float* __restrict__ w1, __nv_bfloat16* __restrict__ y,
-                                                        const float* __restrict__ w2, __nv_bfloat16* __restrict__ z,
-                                                        int64_t T, int D, float eps) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= T) return;
-  float v[NCH][8];
-  const float ss = load_row_add<NCH>(src + row * D, nullptr, D, lane, v);
-  scale_row<NCH>(w1, rsqrtf(ss / (float)D + eps), D, lane, v);
-  float ss2 = 0.f;
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) {
-      if (y != nullptr) store_bf16x8(y + row * D + i, v[c]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss2 += v[c][j] * v[c][j];
-    }
-  }
-  if (z == nullptr) return;
-  ss2 = warp_sum(ss2);
-  scale_row<NCH>(w2, rsqrtf(ss2 / (float)D + eps), D, lane, v);
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) store_bf16x8(z + row * D + i, v[c]);
-  }
-}
-
-// x = bf16(table[clamp(id)] * scale), a = AdaRMSNorm(x; w): embedding and the first block's pre-attention norm.
-template <int NCH>
-__global__ void __launch_bounds__(256) embed_norm_kernel(const int64_t* __restrict__ ids,
-                                                         const __nv_bfloat16* __restrict__ table,
-                                                         __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
-                                                         __nv_bfloat16* __restrict__ a, int64_t T, int D, int V,
-                                                         float scale, float eps) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= T) return;
-  int64_t id = ids[row];
-  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
-  float v[NCH][8];
-  load_row_add<NCH>(table + id * D, nullptr, D, lane, v);
-  float ss = 0.f;
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        v[c][j] = __bfloat162float(__float2bfloat16_rn(v[c][j] * scale));
-        ss += v[c][j] * v[c][j];
-      }
-      store_bf16x8(x + row * D + i, v[c]);
-    }
-  }
-  ss = warp_sum(ss);
-  scale_row<NCH>(w, rsqrtf(ss / (float)D + eps), D, lane, v);
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) store_bf16x8(a + row * D + i, v[c]);
-  }
-}
 
 __global__ void fill_i32_kernel(int32_t* p, int64_t n, int32_t val) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -405,11 +150,45 @@ static int attention_part(const hb200_model* m, int bi, const hb200_block_weight
   return 0;
 }
 
+// q|k rows of the last four positions and the last v_shift half of every sequence -> decode state
+__global__ void save_halo_kernel(const __nv_bfloat16* __restrict__ qkv, int S, int qkv_ld, int C, int kvd_half,
+                                 __nv_bfloat16* __restrict__ halo, __nv_bfloat16* __restrict__ vshift) {
+  const int b = blockIdx.x;
+  for (int i = threadIdx.x; i < 4 * C; i += blockDim.x) {
+    const int slot = i / C, c = i % C;
+    const int tok = S - 4 + slot;
+    halo[((size_t)b * 4 + slot) * C + c] = tok >= 0 ? qkv[((size_t)b * S + tok) * qkv_ld + c] : __float2bfloat16(0.f);
+  }
+  for (int c = threadIdx.x; c < kvd_half; c += blockDim.x)
+    vshift[(size_t)b * kvd_half + c] = qkv[((size_t)b * S + S - 1) * qkv_ld + C + kvd_half + c];
+}
+
+// After the attention half of block `bi` in a prefill: keys / values into the caches (row stride = capacity), conv
+// halo and v_shift from the qkv buffer.
+static int capture_attention_state(const hb200_model* m, int bi, const Workspace& w, int B, int S,
+                                   const hb200_decode_state* ds, cudaStream_t st) {
+  const int H = m->n_heads, KV = m->n_kv_heads, hd = m->head_dim;
+  const int lat = H * hd, kvd = KV * hd, C = lat + kvd;
+  const size_t cache_block = (size_t)B * KV * ds->capacity * hd;
+  __nv_bfloat16* kc = (__nv_bfloat16*)ds->kcache + (size_t)bi * cache_block;
+  __nv_bfloat16* vc = (__nv_bfloat16*)ds->vcache + (size_t)bi * cache_block;
+  HB_CUDA(cudaMemcpy2DAsync(kc, (size_t)ds->capacity * hd * 2, w.k, (size_t)S * hd * 2, (size_t)S * hd * 2,
+                            (size_t)B * KV, cudaMemcpyDeviceToDevice, st));
+  HB_CUDA(cudaMemcpy2DAsync(vc, (size_t)ds->capacity * hd * 2, w.v, (size_t)S * hd * 2, (size_t)S * hd * 2,
+                            (size_t)B * KV, cudaMemcpyDeviceToDevice, st));
+  save_halo_kernel<<<B, 256, 0, st>>>(w.qkv, S, lat + 2 * kvd, C, kvd / 2,
+                                      (__nv_bfloat16*)ds->halo + (size_t)bi * B * 4 * C,
+                                      (__nv_bfloat16*)ds->vshift + (size_t)bi * B * (kvd / 2));
+  HB_LAUNCH_CHECK();
+  return 0;
+}
+
 // x: block input; a_in: AdaRMSNorm(x; norm1) if the caller already has it (else computed here);
 // y: block output; next_w / a_next: optional gain and destination of the norm that consumes y next.
 static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, const __nv_bfloat16* a_in,
                          __nv_bfloat16* y, const float* next_w, __nv_bfloat16* a_next, int B, int S,
-                         const Workspace& w, const hb200_taps* taps, int32_t* counts, int32_t* err, cudaStream_t st) {
+                         const Workspace& w, const hb200_taps* taps, int32_t* counts, int32_t* err, cudaStream_t st,
+                         const hb200_decode_state* ds = nullptr) {
   const hb200_block_weights& bw = m->blocks[bi];
   const int T = B * S, D = m->dim, F = m->ffn_hidden, R = m->n_rec;
   const bool force = taps && taps->force_routing;
@@ -424,6 +203,8 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
     a_in = w.a;
   }
   HB_PROPAGATE(attention_part(m, bi, bw, w, a_in, x, m->residual_scale * m->output_scale, w.cur, B, S, err, st));
+
+  if (ds != nullptr) HB_PROPAGATE(capture_attention_state(m, bi, w, B, S, ds, st));
 
   // routing buffers: the taps slots double as the working buffers when present
   int32_t* depth = (taps && taps->depths) ? taps->depths + (size_t)bi * T : w.depth;
@@ -452,6 +233,9 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
 #undef HB_SCORE
       HB_LAUNCH_CHECK();
     }
+    if (ds != nullptr && has_mod)   // decode cache: the score of every prompt position, row stride = capacity
+      HB_CUDA(cudaMemcpy2DAsync(ds->scores + (((size_t)bi * R + r) * B) * ds->capacity, (size_t)ds->capacity * 4, scores,
+                                (size_t)S * 4, (size_t)S * 4, B, cudaMemcpyDeviceToDevice, st));
     int32_t* count = counts + (size_t)bi * R + r;
     {
     ProfScope ps(m->profile, st, HB200_K_SELECT, bi, r, T, 0, 0);
@@ -627,16 +411,9 @@ extern "C" int hb200_block_forward(const hb200_model* m, int block_index, const 
                        taps, counts, err_flag, st);
 }
 
-extern "C" int hb200_model_forward(const hb200_model* m, const int64_t* ids, int B, int S, void* workspace,
-                                   size_t workspace_bytes, void* logits, int64_t ld_logits, void* hidden_out,
-                                   const hb200_taps* taps, int32_t* err_flag, void* stream) {
-  HB_PROPAGATE(check_model(m, B, S));
-  HB_REQUIRE(ids && workspace, HB200_ERR_INVALID, "model_forward: null pointer");
-  HB_REQUIRE(logits == nullptr || (ld_logits >= m->vocab && ld_logits % 8 == 0), HB200_ERR_INVALID,
-             "model_forward: ld_logits must be >= vocab and a multiple of 8");
-  Workspace w = carve(m, B, S, workspace);
-  HB_REQUIRE(workspace_bytes >= w.bytes, HB200_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.bytes);
-  cudaStream_t st = (cudaStream_t)stream;
+static int run_model(const hb200_model* m, const int64_t* ids, int B, int S, const Workspace& w, void* logits,
+                     int64_t ld_logits, __nv_bfloat16* hid, const hb200_taps* taps, int32_t* err_flag, cudaStream_t st,
+                     const hb200_decode_state* ds) {
   const int T = B * S, D = m->dim;
   int32_t* counts = (taps && taps->mlp_rows) ? taps->mlp_rows : w.counts;
   HB_CUDA(cudaMemsetAsync(counts, 0, (size_t)m->n_blocks * m->n_rec * 4, st));
@@ -652,17 +429,80 @@ extern "C" int hb200_model_forward(const hb200_model* m, const int64_t* ids, int
   // each block's exit norm also produces the next consumer's input norm: the next block's norm1 into w.a, or the
   // model's final norm into the hidden-state buffer after the last block
   __nv_bfloat16 *xin = w.x0, *xout = w.x1;
-  __nv_bfloat16* hid = hidden_out ? (__nv_bfloat16*)hidden_out : w.ug;   // ug is free once the last block is done
   for (int bi = 0; bi < m->n_blocks; ++bi) {
     const bool last = (bi == m->n_blocks - 1);
     const float* next_w = last ? m->norm_w : m->blocks[bi + 1].norm1_w;
     // w.a is read by this block's qkv GEMM long before its exit norm overwrites it with the next block's input
-    HB_PROPAGATE(block_forward(m, bi, xin, w.a, xout, next_w, last ? hid : w.a, B, S, w, taps, counts, err_flag, st));
+    HB_PROPAGATE(block_forward(m, bi, xin, w.a, xout, next_w, last ? hid : w.a, B, S, w, taps, counts, err_flag, st, ds));
     std::swap(xin, xout);
   }
   if (logits != nullptr)
-    HB_PROPAGATE(gemm(m, HB200_K_GEMM_LM_HEAD, m->n_blocks, 0, hid, m->tok_emb, logits, T, m->vocab, D, D, D, ld_logits, EPI_STORE, nullptr, 1.0f, nullptr,
-                      nullptr, err_flag, st));
+    HB_PROPAGATE(gemm(m, HB200_K_GEMM_LM_HEAD, m->n_blocks, 0, hid, m->tok_emb, logits, T, m->vocab, D, D, D, ld_logits,
+                      EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err_flag, st));
+  return 0;
+}
+
+extern "C" int hb200_model_forward(const hb200_model* m, const int64_t* ids, int B, int S, void* workspace,
+                                   size_t workspace_bytes, void* logits, int64_t ld_logits, void* hidden_out,
+                                   const hb200_taps* taps, int32_t* err_flag, void* stream) {
+  HB_PROPAGATE(check_model(m, B, S));
+  HB_REQUIRE(ids && workspace, HB200_ERR_INVALID, "model_forward: null pointer");
+  HB_REQUIRE(logits == nullptr || (ld_logits >= m->vocab && ld_logits % 8 == 0), HB200_ERR_INVALID,
+             "model_forward: ld_logits must be >= vocab and a multiple of 8");
+  Workspace w = carve(m, B, S, workspace);
+  HB_REQUIRE(workspace_bytes >= w.bytes, HB200_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.bytes);
+  __nv_bfloat16* hid = hidden_out ? (__nv_bfloat16*)hidden_out : w.ug;   // ug is free once the last block is done
+  return run_model(m, ids, B, S, w, logits, ld_logits, hid, taps, err_flag, (cudaStream_t)stream, nullptr);
+}
+
+// last hidden row of every sequence -> compact [B, D]; prompt tokens -> history
+__global__ void prefill_tail_kernel(const __nv_bfloat16* __restrict__ hid, int S, int D, __nv_bfloat16* __restrict__ last,
+                                    const int64_t* __restrict__ ids, int64_t* __restrict__ history, int capacity) {
+  const int b = blockIdx.x;
+  for (int i = threadIdx.x * 8; i < D; i += blockDim.x * 8)
+    *reinterpret_cast<uint4*>(last + (size_t)b * D + i) =
+        *reinterpret_cast<const uint4*>(hid + ((size_t)b * S + S - 1) * D + i);
+  if (history != nullptr)
+    for (int t = threadIdx.x; t < S; t += blockDim.x) history[(size_t)b * capacity + t] = ids[(size_t)b * S + t];
+}
+
+__global__ void set_pos_kernel(int32_t* pos, int value, const int64_t* __restrict__ tokens, int64_t* __restrict__ history,
+                               int capacity, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B && history != nullptr && value < capacity) history[(size_t)b * capacity + value] = tokens[b];
+  if (b == 0) *pos = value;
+}
+
+extern "C" int hb200_model_prefill_cached(const hb200_model* m, const int64_t* ids, int B, int S, void* workspace,
+                                          size_t workspace_bytes, const hb200_decode_state* state, void* last_logits,
+                                          int64_t ld_logits, int32_t* err_flag, void* stream) {
+  HB_PROPAGATE(check_model(m, B, S));
+  HB_REQUIRE(ids && workspace && state, HB200_ERR_INVALID, "prefill_cached: null pointer");
+  HB_REQUIRE(state->kcache && state->vcache && state->halo && state->vshift && state->scores && state->pos &&
+                 state->tokens,
+             HB200_ERR_INVALID, "prefill_cached: incomplete decode state");
+  HB_REQUIRE(state->batch == B && state->capacity >= S && state->capacity <= m->max_seq_len, HB200_ERR_INVALID,
+             "prefill_cached: state is for batch %d / capacity %d (need batch %d, %d <= capacity <= %d)", state->batch,
+             state->capacity, B, S, m->max_seq_len);
+  HB_REQUIRE(ld_logits >= m->vocab && ld_logits % 8 == 0, HB200_ERR_INVALID, "prefill_cached: bad ld_logits");
+  HB_REQUIRE(m->dim % 8 == 0, HB200_ERR_UNSUPPORTED, "prefill_cached: dim must be a multiple of 8");
+  Workspace w = carve(m, B, S, workspace);
+  HB_REQUIRE(workspace_bytes >= w.bytes, HB200_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int D = m->dim;
+  HB_PROPAGATE(run_model(m, ids, B, S, w, nullptr, 0, w.ug, nullptr, err_flag, st, state));
+  // last position of every sequence -> logits -> greedy token; w.a / w.act are free now
+  __nv_bfloat16* last = w.a;
+  __nv_bfloat16* lg = last_logits ? (__nv_bfloat16*)last_logits : w.act;
+  HB_REQUIRE(last_logits != nullptr || (size_t)m->ffn_hidden * B * S >= (size_t)B * ld_logits, HB200_ERR_WORKSPACE,
+             "prefill_cached: pass last_logits (the workspace cannot hold them for this shape)");
+  prefill_tail_kernel<<<B, 128, 0, st>>>(w.ug, S, D, last, ids, state->history, state->capacity);
+  HB_LAUNCH_CHECK();
+  HB_PROPAGATE(gemm(m, HB200_K_GEMM_LM_HEAD, m->n_blocks, 0, last, m->tok_emb, lg, B, m->vocab, D, D, D, ld_logits,
+                    EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err_flag, st));
+  HB_PROPAGATE(hb200_argmax_rows(lg, B, m->vocab, ld_logits, state->tokens, st));
+  set_pos_kernel<<<ceil_div(B, 128), 128, 0, st>>>(state->pos, S, state->tokens, state->history, state->capacity, B);
+  HB_LAUNCH_CHECK();
   return 0;
 }
 

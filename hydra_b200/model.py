@@ -281,13 +281,20 @@ class HydraB200Model:
         torch.cuda.current_stream(self.device).synchronize()
         return out_host
 
-    def generate(self, prompt_ids: Tensor, max_new_tokens: int) -> Tensor:
-        """Greedy generation in the reference's way: the whole sequence is run through the model again for every new
+    def generate(self, prompt_ids: Tensor, max_new_tokens: int, mode: str = "reforward", use_graph: bool = True) -> Tensor:
+        """Greedy generation.  ``mode="reforward"`` (default) is the reference's way; ``mode="cached"`` runs
+        :meth:`generate_cached` (latent-space KV cache; an addition the reference does not have).
+
+        Re-forward: the whole sequence is run through the model again for every new
         token (diagnostics/eval_checkpoint.py:127-160 re-forwards ``generated`` each step; the reference has no KV
         cache).  Exact with respect to the eval forward, including MoD's top-k over the growing sequence, at O(S^2)
         cost.  Only the last position is projected to the vocabulary.  Deterministic form of the reference's sampler
         (temperature -> 0): next token = argmax of the last position's logits.
         prompt_ids int64 [B, P] on this device -> int64 [B, P + max_new_tokens]."""
+        if mode == "cached":
+            return self.generate_cached(prompt_ids, max_new_tokens, use_graph=use_graph)
+        if mode != "reforward":
+            raise ValueError(f"unknown generation mode {mode!r} (use 'reforward' or 'cached')")
         if not prompt_ids.is_cuda or prompt_ids.device != self.device:
             raise RuntimeError(f"prompt_ids must be on {self.device} (there is no CPU fallback)")
         B, P = prompt_ids.shape
@@ -313,6 +320,45 @@ class HydraB200Model:
                 _lib.check(lib.hb200_argmax_rows(last_logits.data_ptr(), B, self.vocab_size, ld, nxt.data_ptr(), st),
                            "argmax_rows")
             seq[:, cur] = nxt
+        return seq
+
+    # -- cached decode -----------------------------------------------------------------------------------------------
+    def new_decode_session(self, batch: int, capacity: int) -> "DecodeSession":
+        """Device state for ``batch`` sequences of up to ``capacity`` positions (prompt + generated)."""
+        return DecodeSession(self, batch, capacity)
+
+    def generate_cached(self, prompt_ids: Tensor, max_new_tokens: int, use_graph: bool = True,
+                        return_logits: bool = False):
+        """Greedy generation with the latent-space KV cache: one prefill of the prompt, then one decode step per new
+        token that touches only the newest position.  With ``mod_capacity == 1`` a step computes what the re-forward
+        computes for that position; with capacity < 1 a past token's MoD selection stays as decided when that token was
+        the newest (the re-forward re-decides it over the longer sequence), so the two modes may diverge.
+        With ``use_graph`` the launch sequence of one step is captured once into a CUDA graph and replayed.
+        prompt_ids int64 [B, P] on this device -> int64 [B, P + max_new_tokens] (and, if asked, the bf16 logits
+        [B, max_new_tokens, vocab] each choice was made from)."""
+        if not prompt_ids.is_cuda or prompt_ids.device != self.device:
+            raise RuntimeError(f"prompt_ids must be on {self.device} (there is no CPU fallback)")
+        B, P = prompt_ids.shape
+        n_new = int(max_new_tokens)
+        total = P + n_new
+        if total > self.max_seq_len:
+            raise ValueError(f"prompt + new tokens = {total} exceeds max_seq_len {self.max_seq_len}")
+        sess = self.new_decode_session(B, total)
+        keep = [] if return_logits else None
+        if n_new > 0:
+            sess.prefill(prompt_ids)
+            if keep is not None:
+                keep.append(sess.last_logits[:, :self.vocab_size].clone())
+            for _ in range(n_new - 1):
+                sess.step(use_graph=use_graph)
+                if keep is not None:
+                    keep.append(sess.last_logits[:, :self.vocab_size].clone())
+            seq = sess.history[:, :total].clone()
+        else:
+            seq = prompt_ids.clone()
+        self.check_device_errors()
+        if return_logits:
+            return seq, (torch.stack(keep, dim=1) if keep else None)
         return seq
 
     def check_device_errors(self) -> None:
@@ -351,3 +397,80 @@ class HydraB200Model:
         if self.last_taps is None:
             return {}
         return {"mlp_rows": self.last_taps.mlp_rows.cpu().tolist()}
+
+
+class DecodeSession:
+    """Caches and bookkeeping of a batch of sequences decoded in lockstep (``hb200_decode_state``).
+
+    ``prefill(prompt)`` runs the eval forward of the prompt and fills the caches; every ``step()`` then consumes the
+    token chosen by the previous call and chooses the next one greedily.  ``history`` [B, capacity] int64 holds the
+    token of every position; ``last_logits`` [B, ld] bf16 the logits of the latest choice."""
+
+    def __init__(self, model: HydraB200Model, batch: int, capacity: int):
+        if capacity > model.max_seq_len:
+            raise ValueError(f"capacity {capacity} exceeds max_seq_len {model.max_seq_len}")
+        self.model, self.batch, self.capacity = model, int(batch), int(capacity)
+        dev = model.device
+        nb, R, KV, hd = model.n_mor_blocks, model.recursions_per_block, model.n_kv_heads, model.head_dim
+        lat, kvd = model.n_heads * hd, KV * hd
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self.kcache = torch.zeros((nb, batch, KV, capacity, hd), **bf)
+        self.vcache = torch.zeros((nb, batch, KV, capacity, hd), **bf)
+        self.halo = torch.zeros((nb, batch, 4, lat + kvd), **bf)
+        self.vshift = torch.zeros((nb, batch, kvd // 2), **bf)
+        self.scores = torch.zeros((nb, R, batch, capacity), dtype=torch.float32, device=dev)
+        self.pos_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(batch, dtype=torch.int64, device=dev)
+        self.history = torch.zeros((batch, capacity), dtype=torch.int64, device=dev)
+        self.last_logits = torch.zeros((batch, model.ld_logits), **bf)
+        self.struct = _lib.DecodeState(
+            batch=batch, capacity=capacity, kcache=self.kcache.data_ptr(), vcache=self.vcache.data_ptr(),
+            halo=self.halo.data_ptr(), vshift=self.vshift.data_ptr(), scores=self.scores.data_ptr(),
+            pos=self.pos_dev.data_ptr(), tokens=self.tokens.data_ptr(), history=self.history.data_ptr())
+        n = _lib.lib().hb200_decode_workspace_bytes(C.byref(model.packed.struct), batch)
+        self.workspace = torch.empty(max(int(n), 1), dtype=torch.uint8, device=dev)
+        self.pos = 0            # host mirror of *pos
+        self._graph = None
+        self._eager_steps = 0
+
+    def prefill(self, prompt_ids: Tensor) -> None:
+        m = self.model
+        B, P = prompt_ids.shape
+        if B != self.batch or P < 1 or P >= self.capacity + 1:
+            raise ValueError(f"prompt shape {tuple(prompt_ids.shape)} does not fit batch {self.batch} / capacity {self.capacity}")
+        ids = prompt_ids.contiguous()
+        ws = m.packed.workspace(B, P)
+        with kernels._on(m.device):
+            _lib.check(_lib.lib().hb200_model_prefill_cached(
+                C.byref(m.packed.struct), ids.data_ptr(), B, P, ws.data_ptr(), ws.numel(), C.byref(self.struct),
+                self.last_logits.data_ptr(), m.ld_logits, m.packed.err_flag.data_ptr(), kernels._stream(m.device)),
+                "model_prefill_cached")
+        self.pos = P
+        self._graph = None
+
+    def _launch_step(self) -> None:
+        m = self.model
+        _lib.check(_lib.lib().hb200_model_decode_step(
+            C.byref(m.packed.struct), C.byref(self.struct), self.workspace.data_ptr(), self.workspace.numel(),
+            self.last_logits.data_ptr(), m.ld_logits, m.packed.err_flag.data_ptr(), kernels._stream(m.device)),
+            "model_decode_step")
+
+    def step(self, use_graph: bool = False) -> None:
+        """Process ``tokens`` at position ``pos`` and choose the next token.  The first step always launches
+        directly (one-time kernel attribute setup must not happen inside a capture); later steps replay a graph
+        of the identical launch sequence when ``use_graph`` is set."""
+        if self.pos >= self.capacity:
+            raise RuntimeError(f"decode cache is full ({self.capacity} positions)")
+        m = self.model
+        with kernels._on(m.device):
+            if not use_graph or self._eager_steps == 0:
+                self._launch_step()
+                self._eager_steps += 1
+            else:
+                if self._graph is None:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        self._launch_step()
+                    self._graph = g
+                self._graph.replay()
+        self.pos += 1

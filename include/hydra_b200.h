@@ -237,6 +237,44 @@ int hb200_block_forward(const hb200_model* m, int block_index, const void* x, vo
 int hb200_ccgqa_forward(const hb200_model* m, int block_index, const void* x, void* y, int B, int S,
                         void* workspace, size_t workspace_bytes, int32_t* err_flag, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Cached (incremental) decode.  The reference has no KV cache and no decode path: its generation helper
+ * re-runs the whole forward for every token (diagnostics/eval_checkpoint.py:127-160).  These entry points add the
+ * latent-space KV cache that BASELINE's decode configuration describes.  With MoD capacity 1.0 a cached step
+ * computes exactly what a re-forward computes for the newest position; with capacity < 1 a past token's MoD
+ * selection stays frozen at what it was when the token was newest (MoD's top-k over the sequence is not causal).
+ * ------------------------------------------------------------------------- */
+typedef struct hb200_decode_state {
+  int32_t batch, capacity;   /* B sequences advancing in lockstep; room for `capacity` positions            */
+  void* kcache;              /* bf16 [NB, B, KV, capacity, hd]  post-RoPE keys                               */
+  void* vcache;              /* bf16 [NB, B, KV, capacity, hd]  value-shifted values                         */
+  void* halo;                /* bf16 [NB, B, 4, lat+kvd]  pre-conv q|k rows of the last four positions       */
+  void* vshift;              /* bf16 [NB, B, kvd/2]  v_shift half of the last position                       */
+  float* scores;             /* fp32 [NB, R, B, capacity]  MoD router score of every cached position         */
+  int32_t* pos;              /* device int32: number of cached positions                                     */
+  int64_t* tokens;           /* device int64 [B]: token processed by the next step; each step overwrites it
+                                with its greedy choice                                                       */
+  int64_t* history;          /* device int64 [B, capacity] or NULL: token of every position (prompt + generated) */
+} hb200_decode_state;
+
+/* Bytes of workspace one decode step needs for B sequences. */
+size_t hb200_decode_workspace_bytes(const hb200_model* m, int B);
+
+/* Prefill with cache capture: the eval forward of ids [B,S] (workspace as hb200_model_forward) that also fills
+ * `state` (caches, halos, scores, pos = S) and leaves the greedy choice after the last prompt position in
+ * state->tokens (and history[:, S]).  last_logits: optional bf16 [B, ld_logits] output of the last position. */
+int hb200_model_prefill_cached(const hb200_model* m, const int64_t* ids, int B, int S, void* workspace,
+                               size_t workspace_bytes, const hb200_decode_state* state, void* last_logits,
+                               int64_t ld_logits, int32_t* err_flag, void* stream);
+
+/* One decode step: processes state->tokens at position *state->pos through every block against the caches,
+ * appends to the caches, writes the greedy next token back to state->tokens (and history), advances *pos.
+ * Everything position-dependent is read from device memory, so the identical launch sequence serves every step.
+ * last_logits: optional bf16 [B, ld_logits]. */
+int hb200_model_decode_step(const hb200_model* m, const hb200_decode_state* state, void* workspace,
+                            size_t workspace_bytes, void* last_logits, int64_t ld_logits, int32_t* err_flag,
+                            void* stream);
+
 /* CCGQAAttention.forward for callers that must not allocate.  This entry point has no counterpart in the
  * reference; it is hb200_ccgqa_forward with the workspace argument removed.
  *

@@ -1,0 +1,50 @@
+"""The cached-decode restatement of the oracle against the full re-forward (the reference's own generation semantics):
+with MoD capacity 1.0 they are the same computation and must agree to fp32 rounding; with capacity 0.75 cached decode
+is an approximation whose greedy tokens are compared step by step."""
+import torch
+
+from oracle import hydra_oracle as O
+from tests import golden_io as G
+
+
+def test_cached_decode_equals_reforward_at_full_capacity():
+    fx, cfg, w = G.model_fixture("model_hd16.npz")
+    cfg.mod_capacity = 1.0
+    prompt = torch.from_numpy(fx["ids"])[:, :9].clamp(0, cfg.vocab_size - 1)
+    n = 7
+    seq_c, logits_c = O.cached_generate(prompt, w, cfg, n, return_logits=True)
+    seq_r = prompt.clone()
+    for step in range(n):
+        full = O.model_forward(seq_r, w, cfg)[:, -1]
+        err = float((full - logits_c[:, step]).abs().max())
+        assert err < 2e-4, f"step {step}: cached vs re-forward logits differ by {err:.2e}"
+        seq_r = torch.cat([seq_r, full.argmax(-1, keepdim=True)], dim=1)
+    assert torch.equal(seq_c, seq_r)
+
+
+def test_cached_decode_short_prompt_and_fixed_depth():
+    """Prompt shorter than the conv halo (zero-filled history) and the fixed-depth (non-adaptive) path."""
+    fx, cfg, w = G.model_fixture("model_hd32.npz")
+    cfg.mod_capacity = 1.0
+    for adaptive in (True, False):
+        cfg.adaptive = adaptive
+        prompt = torch.from_numpy(fx["ids"])[:, 2:4].clamp(0, cfg.vocab_size - 1)     # 2 tokens
+        seq_c, logits_c = O.cached_generate(prompt, w, cfg, 5, return_logits=True)
+        seq_r = prompt.clone()
+        for step in range(5):
+            full = O.model_forward(seq_r, w, cfg)[:, -1]
+            assert float((full - logits_c[:, step]).abs().max()) < 2e-4
+            seq_r = torch.cat([seq_r, full.argmax(-1, keepdim=True)], dim=1)
+        assert torch.equal(seq_c, seq_r)
+
+
+def test_cached_decode_with_mod_is_a_close_approximation():
+    fx, cfg, w = G.model_fixture("model_hd16.npz")          # capacity 0.75
+    prompt = torch.from_numpy(fx["ids"])[:, :24].clamp(0, cfg.vocab_size - 1)
+    n = 8
+    seq_c, logits_c = O.cached_generate(prompt, w, cfg, n, return_logits=True)
+    ref = O.model_forward(prompt, w, cfg)[:, -1]
+    assert float((ref - logits_c[:, 0]).abs().max()) < 2e-4     # the prefill itself is exact
+    seq_r = O.greedy_generate(prompt, w, cfg, n)
+    agree = float((seq_c[:, 24:] == seq_r[:, 24:]).float().mean())
+    assert agree >= 0.5, f"greedy-token agreement {agree:.2f}"
