@@ -312,20 +312,25 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=32, help="sequences per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--micro", default=None, help="run one single-kernel microbenchmark instead of the model "
-                    "(gemm, ccgqa_block, pre_attention, attention, rms_norm, rope, swiglu_ffn, swiglu_act)")
+                    "(gemm, ccgqa_block, pre_attention, attention, rms_norm, rope, swiglu_ffn, swiglu_act, model_hidden, decode)")
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=5632)
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--epilogue", default="swiglu", choices=["store", "resid", "swiglu", "scatter"])
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--blocks", type=int, default=22, help="--micro decode: MoR blocks of the 1.5B shape")
+    ap.add_argument("--prompt", type=int, default=1024, help="--micro decode: prompt length")
+    ap.add_argument("--new-tokens", dest="new_tokens", type=int, default=256, help="--micro decode: tokens to generate")
     ap.add_argument("--gemm-impl", dest="impl_gemm", type=int, default=0)
     args = ap.parse_args()
     if args.micro is not None:
         from hydra_b200 import microbench
-        if args.micro not in ("gemm", "model_hidden"):
+        if args.micro == "decode":
+            args.batch = 64 if args.batch == 32 else args.batch
+        elif args.micro not in ("gemm", "model_hidden"):
             args.batch = 8 if args.batch == 32 else args.batch
         args.impl = args.impl_gemm
-        names = [n for n in microbench.CASES if n != "model_hidden"] if args.micro == "all" else [args.micro]
+        names = [n for n in microbench.CASES if n not in ("model_hidden", "decode")] if args.micro == "all" else [args.micro]
         for nm in names:
             print(json.dumps(microbench.run(nm, args, ROOT)), flush=True)
         return

@@ -61,6 +61,8 @@ SIGNATURES = {
     "hb200_swiglu": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i32, c_i64, c_i64, c_i32, c_vp]),
     "hb200_gemm_bf16": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i64, c_i64, c_i64, c_i32, c_vp, c_f32,
                                 c_vp, c_vp, c_i32, c_vp, c_vp]),
+    "hb200_gemm_skinny_bf16": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i64, c_i64, c_i64, c_i32, c_vp, c_f32,
+                                       c_vp, c_vp, c_vp, c_vp]),
     "hb200_interleave_gate_up": (c_i32, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "hb200_repack_conv_weight": (c_i32, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "hb200_ccgqa_pre_attention": (c_i32, [c_vp] * 10 + [c_i32] * 5 + [c_vp, c_vp]),

@@ -387,9 +387,16 @@ __global__ void decode_advance_kernel(int32_t* pos_ptr, const int64_t* __restric
   if (b == 0) *pos_ptr = pos + 1;
 }
 
-static int dgemm(const hb200_model* m, const void* A, const void* W, void* C, int M, int N, int K, int64_t ldc, int epi,
-                 const void* resid, float alpha, const int32_t* rows, const int32_t* m_dev, int32_t* err,
-                 cudaStream_t st) {
+// Contractions of a decode step: at most 128 rows -> the cluster split-K weight-streaming kernel (gemm_impl 0); larger
+// batches, or gemm_impl 1 (the mma.sync cross-check), take the general entry point.
+static int dgemm(const hb200_model* m, const DecodeWs& w, const void* A, const void* W, void* C, int M, int N, int K,
+                 int64_t ldc, int epi, const void* resid, float alpha, const int32_t* rows, const int32_t* m_dev,
+                 int32_t* err, cudaStream_t st) {
+  if (m->gemm_impl == 0 && M <= 128) {
+    GemmParams p{(const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, K, K, ldc, epi,
+                 (const __nv_bfloat16*)resid, epi == EPI_SCATTER_ADD ? 1.0f : alpha, rows, m_dev, err};
+    return launch_gemm_skinny(p, st);
+  }
   return hb200_gemm_bf16(A, W, C, M, N, K, K, K, ldc, epi, resid, alpha, rows, m_dev, m->gemm_impl, err, st);
 }
 
@@ -446,13 +453,13 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
     __nv_bfloat16* kc = (__nv_bfloat16*)ds->kcache + (size_t)bi * cache_block;
     __nv_bfloat16* vc = (__nv_bfloat16*)ds->vcache + (size_t)bi * cache_block;
     // ---- attention half ----
-    HB_PROPAGATE(dgemm(m, w.a, bw.w_qkv, w.qkv, B, nq, D, nq, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st));
+    HB_PROPAGATE(dgemm(m, w, w.a, bw.w_qkv, w.qkv, B, nq, D, nq, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st));
     decode_conv_prep_kernel<<<B, 256, (size_t)8 * C * sizeof(float), st>>>(
         w.qkv, (const __nv_bfloat16*)bw.w1_qk, (__nv_bfloat16*)ds->halo + (size_t)bi * B * 4 * C,
         (__nv_bfloat16*)ds->vshift + (size_t)bi * B * (kvd / 2), vc, w.aq, w.ak, w.qm, w.km, ds->pos, B, H, KV, hd, cap);
     HB_LAUNCH_CHECK();
-    HB_PROPAGATE(dgemm(m, w.aq, bw.w2_q, w.c2q, B, lat, 3 * lat, lat, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st));
-    HB_PROPAGATE(dgemm(m, w.ak, bw.w2_k, w.c2k, B, kvd, 3 * kvd, kvd, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st));
+    HB_PROPAGATE(dgemm(m, w, w.aq, bw.w2_q, w.c2q, B, lat, 3 * lat, lat, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st));
+    HB_PROPAGATE(dgemm(m, w, w.ak, bw.w2_k, w.c2k, B, kvd, 3 * kvd, kvd, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st));
     decode_qk_finish_kernel<<<B, 256, 0, st>>>(w.qkv, w.c2q, w.c2k, w.qm, w.km, m->rope_cos, m->rope_sin,
                                                bw.key_temperature, w.qnew, kc, ds->pos, H, KV, hd, cap);
     HB_LAUNCH_CHECK();
@@ -461,7 +468,7 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
       case 32: HB_PROPAGATE(launch_decode_attention<32>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st)); break;
       default: HB_PROPAGATE(launch_decode_attention<64>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st)); break;
     }
-    HB_PROPAGATE(dgemm(m, w.o, bw.w_o, w.cur, B, D, lat, D, EPI_RESID, xin, m->residual_scale * m->output_scale, nullptr,
+    HB_PROPAGATE(dgemm(m, w, w.o, bw.w_o, w.cur, B, D, lat, D, EPI_RESID, xin, m->residual_scale * m->output_scale, nullptr,
                        nullptr, err, st));
     // ---- MoR loop on the B new rows ----
     if (!m->adaptive) {
@@ -489,8 +496,8 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
       HB_DISPATCH_NCH(D, norm_gather_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, w.rows, count, w.ug, D,
                                                                            m->norm_eps));
       HB_LAUNCH_CHECK();
-      HB_PROPAGATE(dgemm(m, w.ug, bw.w_gate_up, w.act, B, 2 * F, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count, err, st));
-      HB_PROPAGATE(dgemm(m, w.act, bw.w_down, w.cur, B, D, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count, err, st));
+      HB_PROPAGATE(dgemm(m, w, w.ug, bw.w_gate_up, w.act, B, 2 * F, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count, err, st));
+      HB_PROPAGATE(dgemm(m, w, w.act, bw.w_down, w.cur, B, D, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count, err, st));
     }
     const float* next_w = last ? m->norm_w : m->blocks[bi + 1].norm1_w;
     HB_DISPATCH_NCH(D, dual_norm_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, bw.final_norm_w, xout, next_w,
@@ -499,7 +506,7 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
     std::swap(xin, xout);
   }
   __nv_bfloat16* lg = last_logits ? (__nv_bfloat16*)last_logits : w.logits;
-  HB_PROPAGATE(dgemm(m, w.hid, m->tok_emb, lg, B, m->vocab, D, (int64_t)ld, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err,
+  HB_PROPAGATE(dgemm(m, w, w.hid, m->tok_emb, lg, B, m->vocab, D, (int64_t)ld, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err,
                      st));
   HB_PROPAGATE(hb200_argmax_rows(lg, B, m->vocab, (int64_t)ld, ds->tokens, st));
   decode_advance_kernel<<<ceil_div(B, 1024), 1024, 0, st>>>(ds->pos, ds->tokens, ds->history, B, cap);

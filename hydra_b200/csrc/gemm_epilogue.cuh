@@ -69,5 +69,7 @@ __device__ __forceinline__ void epilogue_row_chunk(const GemmParams& p, int m, i
 
 int launch_gemm_tcgen05(const GemmParams& p, cudaStream_t st);
 int launch_gemm_mma(const GemmParams& p, cudaStream_t st);
+// M <= 128 rows: one CTA per (128 weight rows, K slice), split-K reduced across a thread-block cluster
+int launch_gemm_skinny(const GemmParams& p, cudaStream_t st);
 
 }  // namespace hb200

@@ -274,9 +274,8 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
 
 using namespace hb200;
 
-extern "C" int hb200_gemm_bf16(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
-                               int64_t ldc, int epilogue, const void* resid, float alpha, const int32_t* rows,
-                               const int32_t* m_dev, int impl, int32_t* err_flag, void* stream) {
+static int check_gemm_args(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
+                           int64_t ldc, int epilogue, const void* resid, const int32_t* rows) {
   HB_REQUIRE(A && W && C, HB200_ERR_INVALID, "gemm: null pointer");
   HB_REQUIRE(M >= 0 && N >= 1 && K >= 1, HB200_ERR_INVALID, "gemm: bad shape M=%d N=%d K=%d", M, N, K);
   HB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ldc % 8 == 0 && lda >= K && ldw >= K, HB200_ERR_INVALID,
@@ -289,11 +288,28 @@ extern "C" int hb200_gemm_bf16(const void* A, const void* W, void* C, int M, int
   HB_REQUIRE(epilogue != EPI_SCATTER_ADD || rows != nullptr, HB200_ERR_INVALID, "gemm: scatter-add epilogue needs rows");
   HB_REQUIRE(epilogue != EPI_SWIGLU || N % 16 == 0, HB200_ERR_INVALID, "gemm: SwiGLU epilogue needs N %% 16 == 0");
   HB_REQUIRE(epilogue == EPI_SWIGLU ? ldc >= N / 2 : ldc >= N, HB200_ERR_INVALID, "gemm: ldc too small");
+  return 0;
+}
+
+extern "C" int hb200_gemm_bf16(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
+                               int64_t ldc, int epilogue, const void* resid, float alpha, const int32_t* rows,
+                               const int32_t* m_dev, int impl, int32_t* err_flag, void* stream) {
+  HB_PROPAGATE(check_gemm_args(A, W, C, M, N, K, lda, ldw, ldc, epilogue, resid, rows));
   HB_REQUIRE(impl == 0 || impl == 1, HB200_ERR_INVALID, "gemm: impl must be 0 (tcgen05) or 1 (mma.sync cross-check)");
   if (M == 0) return 0;
   GemmParams p{(const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, lda, ldw, ldc, epilogue,
                (const __nv_bfloat16*)resid, epilogue == EPI_SCATTER_ADD ? 1.0f : alpha, rows, m_dev, err_flag};
   return impl == 0 ? launch_gemm_tcgen05(p, (cudaStream_t)stream) : launch_gemm_mma(p, (cudaStream_t)stream);
+}
+
+extern "C" int hb200_gemm_skinny_bf16(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
+                                      int64_t ldc, int epilogue, const void* resid, float alpha, const int32_t* rows,
+                                      const int32_t* m_dev, int32_t* err_flag, void* stream) {
+  HB_PROPAGATE(check_gemm_args(A, W, C, M, N, K, lda, ldw, ldc, epilogue, resid, rows));
+  if (M == 0) return 0;
+  GemmParams p{(const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, lda, ldw, ldc, epilogue,
+               (const __nv_bfloat16*)resid, epilogue == EPI_SCATTER_ADD ? 1.0f : alpha, rows, m_dev, err_flag};
+  return launch_gemm_skinny(p, (cudaStream_t)stream);
 }
 
 extern "C" int hb200_interleave_gate_up(const void* w_gate_up, void* w_out, int F, int K, void* stream) {

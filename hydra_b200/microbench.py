@@ -275,7 +275,53 @@ def model_hidden(args) -> dict:
             "bound": "tensor", "achieved": B * 2048 / (ms * 1e-3) / 1e6, "unit": "Mtok/s"}
 
 
+def decode(args) -> dict:
+    """Cached greedy decode at the 1.5B shape (dim 2048, 22 blocks x 4 recursions, 32 query / 4 KV heads of 16,
+    F 5632, MoD 0.75): `batch` sequences per GPU, prompt of 1024 uniform-random tokens, 256 new tokens.  Reports the
+    decode phase (steps replayed from one CUDA graph) against the weight-streaming bound: every step reads each
+    weight once (the activations of `batch` rows are negligible) plus the cached keys / values of every position."""
+    from .model import HydraB200Model, random_state_dict
+    arch = dict(vocab_size=50257, dim=2048, n_mor_blocks=args.blocks, recursions_per_block=4, n_heads=32, n_kv_heads=4,
+                compression_factor=4, mlp_ratio=2.67, mod_capacity=0.75)
+    sd = random_state_dict(seed=0, device="cuda", **arch)
+    P, n_new = args.prompt, args.new_tokens
+    m = HydraB200Model(sd, n_heads=32, n_kv_heads=4, max_seq_len=P + n_new, mod_capacity=0.75, device="cuda")
+    weight_bytes = 2.0 * sum(v.numel() for k, v in sd.items() if v.dim() >= 2 and "router" not in k and "recursion" not in k)
+    del sd
+    B = args.batch
+    prompt = torch.randint(0, 50257, (B, P), generator=torch.Generator().manual_seed(1)).cuda()
+    sess = m.new_decode_session(B, P + n_new)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    sess.prefill(prompt)                      # warm-up of the prefill kernels
+    torch.cuda.synchronize()
+    ev[0].record()
+    sess.prefill(prompt)
+    ev[1].record()
+    sess.step(use_graph=False)                # direct launch (one-time kernel setup), then the graph is captured
+    sess.step(use_graph=True)
+    torch.cuda.synchronize()
+    ev[2].record()
+    steps = n_new - 3
+    for _ in range(steps):
+        sess.step(use_graph=True)
+    ev[3].record()
+    torch.cuda.synchronize()
+    m.check_device_errors()
+    prefill_ms, decode_ms = ev[0].elapsed_time(ev[1]), ev[2].elapsed_time(ev[3])
+    # positions cached while the timed steps ran: P+2 .. P+2+steps-1, keys and values of 4 KV heads x 16
+    mean_pos = P + 2 + (steps - 1) / 2.0
+    kv_bytes = 2.0 * 2.0 * B * 4 * 16 * mean_pos * args.blocks
+    step_ms = decode_ms / steps
+    nbytes = weight_bytes + kv_bytes
+    return {"kernel": "hb200_model_decode_step (CUDA graph replay)", "shape": [B, P, n_new], "ms": step_ms,
+            "bound": "hbm", "achieved": nbytes / (step_ms * 1e-3) / 1e9, "unit": "GB/s", "algorithmic_bytes": nbytes,
+            "decode_tok_per_s": B / (step_ms * 1e-3), "timed_steps": steps,
+            "note": "prefill of the prompt measured separately: %.1f ms; weights %.2f GB + cache reads %.3f GB per step"
+                    % (prefill_ms, weight_bytes / 1e9, kv_bytes / 1e9)}
+
+
 CASES: Dict[str, Callable] = {
+    "decode": decode,
     "gemm": gemm, "ccgqa_block": ccgqa_block, "pre_attention": pre_attention, "attention": attention,
     "rms_norm": rms_norm, "rope": rope, "swiglu_ffn": swiglu_ffn, "swiglu_act": swiglu_act,
     "model_hidden": model_hidden,

@@ -135,3 +135,80 @@ def test_argument_errors_are_reported_not_faulted(L):
     assert f(A.data_ptr() + 2, W.data_ptr(), Cb.data_ptr(), 64, 64, 64, 64, 64, 64, 0, None, 1.0, None, None, 0, None, st) == -1
     assert f(A.data_ptr(), W.data_ptr(), Cb.data_ptr(), 64, 64, 64, 64, 64, 64, 3, None, 1.0, None, None, 0, None, st) == -1
     assert b"rows" in L.lib().hb200_last_error()
+
+
+# ---- skinny-M split-K kernel (decode) ---------------------------------------------------------------------------
+def skinny(L, A, W, *, epi=0, resid=None, alpha=1.0, rows=None, m_dev=None, C_out=None):
+    M, K = A.shape
+    N = W.shape[0]
+    n_out = N // 2 if epi == L.EPI_SWIGLU else N
+    ldc = (n_out + 7) // 8 * 8
+    if C_out is None:
+        C_out = torch.zeros((M, ldc), dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    L.check(L.lib().hb200_gemm_skinny_bf16(
+        A.data_ptr(), W.data_ptr(), C_out.data_ptr(), M, N, K, A.stride(0), W.stride(0), C_out.stride(0), epi,
+        resid.data_ptr() if resid is not None else None, alpha, rows.data_ptr() if rows is not None else None,
+        m_dev.data_ptr() if m_dev is not None else None, err.data_ptr(),
+        torch.cuda.current_stream().cuda_stream), "gemm_skinny")
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0, "a bounded wait inside the skinny GEMM ran out"
+    return C_out[:, :n_out]
+
+
+SKINNY_SHAPES = [(64, 2048, 5632), (64, 640, 2048), (8, 64, 192), (37, 512, 1536), (128, 2048, 512), (1, 256, 64),
+                 (77, 50257, 256), (64, 136, 72), (5, 11264, 2048), (100, 384, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", SKINNY_SHAPES)
+def test_skinny_store(L, M, N, K):
+    A, W = rnd(M, K, seed=21), rnd(N, K, seed=22, scale=0.05)
+    ref = A.float() @ W.float().T
+    out = skinny(L, A, W)
+    assert_close_bf16(out, ref, what=f"skinny store {M}x{N}x{K}")
+    assert torch.equal(out, skinny(L, A, W))          # fixed summation order: bit-reproducible
+
+
+def test_skinny_epilogues_and_device_row_count(L):
+    M, D, F = 64, 2048, 5632
+    # residual
+    A, W, X = rnd(M, 512, seed=23), rnd(D, 512, seed=24, scale=0.05), rnd(M, D, seed=25)
+    out = skinny(L, A, W, epi=L.EPI_RESID, resid=X, alpha=0.5)
+    assert_close_bf16(out, X.float() + 0.5 * (A.float() @ W.float().T), what="skinny resid")
+    # SwiGLU with the interleaved weight
+    A = rnd(M, D, seed=26)
+    Wgu = rnd(2 * F, D, seed=27, scale=0.02)
+    Wil = torch.empty_like(Wgu)
+    L.check(L.lib().hb200_interleave_gate_up(Wgu.data_ptr(), Wil.data_ptr(), F, D, torch.cuda.current_stream().cuda_stream))
+    gu = A.float() @ Wgu.float().T
+    out = skinny(L, A, Wil, epi=L.EPI_SWIGLU)
+    assert out.shape == (M, F)
+    assert_close_bf16(out, torch.nn.functional.silu(gu[:, :F]) * gu[:, F:], what="skinny swiglu")
+    # scatter-add of the first `live` compact rows into their target rows
+    live = 23
+    A, W = rnd(M, F, seed=28), rnd(D, F, seed=29, scale=0.02)
+    cur = rnd(M, D, seed=30)
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(31)).to(torch.int32).cuda()
+    m_dev = torch.tensor([live], dtype=torch.int32, device="cuda")
+    ref = cur.float().clone()
+    ref[rows[:live].long()] += (A.float() @ W.float().T)[:live]
+    out = skinny(L, A, W, epi=L.EPI_SCATTER_ADD, rows=rows, m_dev=m_dev, C_out=cur.clone())
+    assert_close_bf16(out, ref, what="skinny scatter_add")
+    untouched = torch.ones(M, dtype=torch.bool)
+    untouched[rows[:live].long().cpu()] = False
+    assert torch.equal(out[untouched.cuda()], cur[untouched.cuda()])
+    # zero live rows: nothing is written
+    m_dev.zero_()
+    out = skinny(L, A, W, epi=L.EPI_SCATTER_ADD, rows=rows, m_dev=m_dev, C_out=cur.clone())
+    assert torch.equal(out, cur)
+
+
+def test_skinny_agrees_with_the_large_kernel(L):
+    A, W = rnd(64, 2048, seed=33), rnd(640, 2048, seed=34, scale=0.05)
+    assert rel_l2(skinny(L, A, W).float(), gemm(L, A, W).float()) < 2e-3
+
+
+def test_skinny_argument_errors(L):
+    A, W = rnd(129, 64), rnd(128, 64)
+    with pytest.raises(L.Hb200Error):
+        skinny(L, A, W)                                # more than 128 rows
