@@ -51,6 +51,49 @@ void set_error(const char* fmt, ...);   // defined in api.cu (thread-local buffe
     if (_s != 0) return _s;     \
   } while (0)
 
+// ---- programmatic dependent launch ------------------------------------------------------------------------------
+// A chain of kernels in one stream in which each kernel lets its successor be scheduled early (chain_release, at the
+// top) and touches global memory only after its predecessor has completed and flushed (chain_wait).  The successor's
+// launch latency and prologue (barrier set-up, TMEM allocation) then overlap the predecessor's tail.  Both
+// instructions are no-ops in a kernel that was launched without the attribute.
+#ifdef __CUDACC__
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launch `kern` as a link of such a chain (chained = false: an ordinary launch).  cluster_x > 1 adds a cluster shape.
+template <typename... KArgs, typename... Args>
+inline int launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool chained,
+                          int cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (chained) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) {
+    set_error("kernel launch failed: %s", cudaGetErrorString(e));
+    return HB200_ERR_CUDA;
+  }
+  return 0;
+}
+#endif
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }

@@ -27,8 +27,10 @@
 
 namespace hb200 {
 
+int launch_argmax_rows(const void* x, int64_t rows, int cols, int64_t ld, int64_t* out, cudaStream_t st, bool chained);
+
 struct DecodeWs {
-  __nv_bfloat16 *x0, *x1, *a, *qkv, *aq, *ak, *c2q, *c2k, *qnew, *o, *cur, *ug, *act, *hid, *logits;
+  __nv_bfloat16 *x0, *x1, *a, *qkv, *aq, *ak, *c2q, *qnew, *o, *cur, *ug, *act, *hid, *logits;
   float *qm, *km, *score, *rlogit;
   int32_t *depth, *rows, *counts;
   size_t bytes;
@@ -53,7 +55,6 @@ static DecodeWs carve_decode(const hb200_model* m, int B, void* base) {
   w.aq = (__nv_bfloat16*)take(B * 3 * lat * 2);
   w.ak = (__nv_bfloat16*)take(B * 3 * kvd * 2);
   w.c2q = (__nv_bfloat16*)take(B * lat * 2);
-  w.c2k = (__nv_bfloat16*)take(B * kvd * 2);
   w.qnew = (__nv_bfloat16*)take(B * lat * 2);
   w.o = (__nv_bfloat16*)take(B * lat * 2);
   w.cur = (__nv_bfloat16*)take(B * D * 2);
@@ -77,13 +78,16 @@ static DecodeWs carve_decode(const hb200_model* m, int B, void* base) {
 __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
     const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ w1, __nv_bfloat16* __restrict__ halo,
     __nv_bfloat16* __restrict__ vshift, __nv_bfloat16* __restrict__ vcache, __nv_bfloat16* __restrict__ aq,
-    __nv_bfloat16* __restrict__ ak, float* __restrict__ qm, float* __restrict__ km, const int32_t* __restrict__ pos_ptr,
-    int B, int H, int KV, int hd, int capacity) {
+    __nv_bfloat16* __restrict__ ak, float* __restrict__ qm, float* __restrict__ km, int32_t* __restrict__ first_count,
+    const int32_t* __restrict__ pos_ptr, int B, int H, int KV, int hd, int capacity) {
   extern __shared__ float smem_f[];
+  chain_release();
+  chain_wait();
   const int lat = H * hd, kvd = KV * hd, C = lat + kvd, qkv_ld = lat + 2 * kvd, half = kvd / 2;
   float* win = smem_f;            // [5][C]: positions p-4 .. p
   float* y1 = smem_f + 5 * C;     // [3][C]: positions p-2 .. p
   const int b = blockIdx.x, tid = threadIdx.x;
+  if (b == 0 && tid == 0) *first_count = 0;   // row counter of this block's first recursion (see decode_route_kernel)
   const int pos = *pos_ptr;
   if (pos >= capacity) return;    // cache full: the step is a no-op (the host checks capacity before launching)
   __nv_bfloat16* hb = halo + (size_t)b * 4 * C;
@@ -91,15 +95,27 @@ __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
   for (int i = tid; i < 4 * C; i += 256) win[i] = __bfloat162float(hb[i]);
   for (int c = tid; c < C; c += 256) win[4 * C + c] = __bfloat162float(row[c]);
   __syncthreads();
-  // grouped conv1 (kernel 3, causal) on rows 2..4 of the window; rounded to bf16 like the prefill's y1 tile
-  for (int i = tid; i < 3 * C; i += 256) {
-    const int s = i / C, c = i % C;
-    const int hbse = (c / hd) * hd;
+  // grouped conv1 (kernel 3, causal) on rows 2..4 of the window; rounded to bf16 like the prefill's y1 tile.
+  // One thread per output channel: its weight row (3 taps x hd inputs, 16-byte loads) serves all three positions.
+  for (int c = tid; c < C; c += 256) {
+    const int hb0 = (c / hd) * hd;
     const __nv_bfloat16* wr = w1 + (size_t)c * 3 * hd;
-    float acc = 0.f;
-    for (int j = 0; j < 3; ++j)
-      for (int ci = 0; ci < hd; ++ci) acc += __bfloat162float(wr[j * hd + ci]) * win[(s + j) * C + hbse + ci];
-    y1[i] = __bfloat162float(__float2bfloat16_rn(acc));
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f;
+    for (int e = 0; e < 3 * hd; e += 8) {
+      float wv[8];
+      load_bf16x8(wr + e, wv);
+      const int j = e / hd, ci0 = e - j * hd;                 // hd % 8 == 0: the 8 weights share a tap
+      const float* x0 = win + j * C + hb0 + ci0;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        acc0 += wv[q] * x0[q];
+        acc1 += wv[q] * x0[C + q];
+        acc2 += wv[q] * x0[2 * C + q];
+      }
+    }
+    y1[c] = __bfloat162float(__float2bfloat16_rn(acc0));
+    y1[C + c] = __bfloat162float(__float2bfloat16_rn(acc1));
+    y1[2 * C + c] = __bfloat162float(__float2bfloat16_rn(acc2));
   }
   // QK-mean halves and the value row
   for (int d = tid; d < 2 * hd; d += 256) {
@@ -133,15 +149,36 @@ __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
 
 // ---- QK finish: one CTA per sequence, one warp per head ----------------------------------------------------------
 __global__ void __launch_bounds__(256) decode_qk_finish_kernel(
-    const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ c2q, const __nv_bfloat16* __restrict__ c2k,
-    const float* __restrict__ qm, const float* __restrict__ km, const float* __restrict__ cos_t,
+    const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ c2q, const __nv_bfloat16* __restrict__ ak,
+    const __nv_bfloat16* __restrict__ w2k, const float* __restrict__ qm, const float* __restrict__ km, const float* __restrict__ cos_t,
     const float* __restrict__ sin_t, const float* __restrict__ temp, __nv_bfloat16* __restrict__ qnew,
     __nv_bfloat16* __restrict__ kcache, const int32_t* __restrict__ pos_ptr, int H, int KV, int hd, int capacity) {
   const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  chain_release();
+  chain_wait();
   const int pos = *pos_ptr;
   if (pos >= capacity) return;
   const int lat = H * hd, kvd = KV * hd, qkv_ld = lat + 2 * kvd;
   const bool same_heads = (H == KV);
+  // the key side of the dense conv is small (kvd x 3 kvd): done here on the CUDA cores, one thread per output
+  // channel, im2col row in shared memory, result rounded to bf16 like a stored GEMM output
+  extern __shared__ float smem_f[];
+  float* a_row = smem_f;                 // [3 * kvd]
+  float* c2k = smem_f + 3 * kvd;         // [kvd]
+  for (int i = threadIdx.x; i < 3 * kvd; i += 256) a_row[i] = __bfloat162float(ak[(size_t)b * 3 * kvd + i]);
+  __syncthreads();
+  for (int n = threadIdx.x; n < kvd; n += 256) {
+    const __nv_bfloat16* wr = w2k + (size_t)n * 3 * kvd;
+    float acc = 0.f;
+    for (int e = 0; e < 3 * kvd; e += 8) {
+      float wv[8];
+      load_bf16x8(wr + e, wv);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc += wv[q] * a_row[e + q];
+    }
+    c2k[n] = __bfloat162float(__float2bfloat16_rn(acc));
+  }
+  __syncthreads();
   for (int hh = warp; hh < H + KV; hh += 8) {
     const bool is_k = hh >= H;
     const int h = is_k ? hh - H : hh;
@@ -149,7 +186,7 @@ __global__ void __launch_bounds__(256) decode_qk_finish_kernel(
     const int d0 = 2 * lane;
     float v0 = 0.f, v1 = 0.f;
     if (d0 < hd) {
-      const __nv_bfloat16* conv = is_k ? c2k + (size_t)b * kvd + h * hd : c2q + (size_t)b * lat + h * hd;
+      const __nv_bfloat16* conv = c2q + (size_t)b * lat + h * hd;
       float c0, c1;
       if (same_heads) {   // one query head per kv head: both sides couple with 0.5 * (q0 + k0) of that head
         const __nv_bfloat16* row = qkv + (size_t)b * qkv_ld;
@@ -160,8 +197,8 @@ __global__ void __launch_bounds__(256) decode_qk_finish_kernel(
         c0 = mean[d0];
         c1 = mean[d0 + 1];
       }
-      v0 = __bfloat162float(conv[d0]) + c0;
-      v1 = __bfloat162float(conv[d0 + 1]) + c1;
+      v0 = (is_k ? c2k[h * hd + d0] : __bfloat162float(conv[d0])) + c0;
+      v1 = (is_k ? c2k[h * hd + d0 + 1] : __bfloat162float(conv[d0 + 1])) + c1;
     }
     const float ss = warp_sum(v0 * v0 + v1 * v1);
     const float inv = (is_k ? *temp : 1.0f) / fmaxf(sqrtf(ss), 1e-12f);
@@ -193,6 +230,8 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
   constexpr int CH = HD / 8;                 // 16-byte chunks per row
   const int kvh = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = H / KV, lat = H * HD;
+  chain_release();
+  chain_wait();
   const int n_keys = min(*pos_ptr + 1, capacity);
   float* qs = smem_f;                          // [G][HD], pre-scaled by scale * log2(e)
   float* red = qs + DATT_GMAX * HD;            // [DATT_WARPS][DATT_GMAX]
@@ -315,63 +354,108 @@ static size_t decode_attention_smem(int hd, int G, int capacity) {
 template <int HD>
 static int launch_decode_attention(const __nv_bfloat16* qnew, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
                                    __nv_bfloat16* o, const int32_t* pos, int B, int H, int KV, int capacity, float scale,
-                                   cudaStream_t st) {
+                                   cudaStream_t st, bool chain) {
   const size_t smem = decode_attention_smem(HD, H / KV, capacity);
   static size_t attr_bytes = 0;
   if (smem > attr_bytes) {
     HB_CUDA(cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_bytes = smem;
   }
-  decode_attention_kernel<HD><<<dim3(KV, B), DATT_THREADS, smem, st>>>(qnew, kc, vc, o, pos, H, KV, capacity,
-                                                                       scale * 1.4426950408889634f);
-  HB_LAUNCH_CHECK();
-  return 0;
+  return launch_chained(decode_attention_kernel<HD>, dim3(KV, B), dim3(DATT_THREADS), smem, st, chain, 1, qnew, kc, vc, o,
+                        pos, H, KV, capacity, scale * 1.4426950408889634f);
 }
 
-// ---- MoD selection of the newest position + compaction over the batch: one CTA -----------------------------------
-// selected(b) iff fewer than k cached scores of sequence b are >= the new score, k = int((p+1) * capacity_ratio)
-// clamped to [1, p+1]; rows = ascending b with selected(b) and depth(b) >= r.  has_mod == 0: rows = {b: depth >= r}.
-__global__ void __launch_bounds__(1024) decode_select_kernel(float* __restrict__ score_cache,
-                                                             const float* __restrict__ new_score,
-                                                             const int32_t* __restrict__ depth, int min_active,
-                                                             int32_t* __restrict__ rows, int32_t* __restrict__ count,
-                                                             const int32_t* __restrict__ pos_ptr, int B, int capacity,
-                                                             float cap_ratio, int has_mod) {
-  __shared__ int flags[1024];
-  __shared__ int scan_buf[33];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+// ---- routing of the newest position + gather-norm: one warp per sequence ------------------------------------
+// Per recursion r of a block, for every sequence b:
+//   router (r == 0, adaptive): depth[b] from the raw row;
+//   MoD: score s_b of AdaRMSNorm(cur_b + rec) (same formula as the prefill's score pass); "selected" iff fewer than
+//        k cached scores of b are >= s_b, k = int((p+1) * capacity) clamped to [1, p+1] (the newest position loses
+//        ties); s_b is appended to the score cache;
+//   if selected(b) and depth[b] >= r: a compact slot j is taken from the counter, rows[j] = b and
+//   ug[j] = AdaRMSNorm(cur_b + rec) straight from the registers that hold the row.
+// Slots are handed out in arrival order: which slot a row gets does not change its result (rows of the two MLP
+// contractions are independent), only where it sits in the compact buffers.  *count must be zero on entry; the
+// kernel zeroes `next_count` (the counter of the following recursion) for its successor.
+template <int NCH, bool HAS_MOD, bool HAS_ROUTER>
+__global__ void __launch_bounds__(256) decode_route_kernel(
+    const __nv_bfloat16* __restrict__ cur, const float* __restrict__ rec, const float* __restrict__ norm2_w,
+    const float* __restrict__ mod_wn, const float* __restrict__ mod_b, const float* __restrict__ mor_w,
+    const float* __restrict__ mor_b, float* __restrict__ score_cache, int32_t* __restrict__ depth, int min_active,
+    int32_t* __restrict__ rows, int32_t* __restrict__ count, int32_t* __restrict__ next_count,
+    __nv_bfloat16* __restrict__ ug, const int32_t* __restrict__ pos_ptr, int B, int D, int capacity, float cap_ratio,
+    float eps, int n_rec, int min_d) {
+  const int lane = threadIdx.x & 31;
+  const int b = blockIdx.x * 8 + (threadIdx.x >> 5);
+  chain_release();
+  chain_wait();
+  if (next_count != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *next_count = 0;
+  if (b >= B) return;
   const int pos = *pos_ptr;
-  if (tid < 1024) flags[tid] = 0;
-  __syncthreads();
-  if (pos < capacity) {
+  const bool room = pos < capacity;
+  float v[NCH][8];
+  const float ss = load_row_add<NCH>(cur + (size_t)b * D, rec, D, lane, v);   // sum (x + rec)^2
+  const float ri = rsqrtf(ss / (float)D + eps);
+  float dm = 0.f, lm = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) {
+      if (HAS_MOD) {
+        const float4 a0 = *reinterpret_cast<const float4*>(mod_wn + i), a1 = *reinterpret_cast<const float4*>(mod_wn + i + 4);
+        dm += v[c][0] * a0.x + v[c][1] * a0.y + v[c][2] * a0.z + v[c][3] * a0.w + v[c][4] * a1.x + v[c][5] * a1.y +
+              v[c][6] * a1.z + v[c][7] * a1.w;
+      }
+      if (HAS_ROUTER) {   // the depth router sees the raw row (no recursion offset)
+        const float4 a0 = *reinterpret_cast<const float4*>(mor_w + i), a1 = *reinterpret_cast<const float4*>(mor_w + i + 4);
+        float raw[8];
+        load_bf16x8(cur + (size_t)b * D + i, raw);
+        lm += raw[0] * a0.x + raw[1] * a0.y + raw[2] * a0.z + raw[3] * a0.w + raw[4] * a1.x + raw[5] * a1.y +
+              raw[6] * a1.z + raw[7] * a1.w;
+      }
+    }
+  }
+  int dep;
+  if (HAS_ROUTER) {
+    lm = warp_sum(lm);
+    dep = mor_depth_from_logit(lm + mor_b[0], n_rec, min_d);
+    if (lane == 0) depth[b] = dep;
+  } else {
+    dep = depth[b];
+  }
+  bool sel = true;
+  if (HAS_MOD) {
     double c = (double)cap_ratio;
     c = c < 1e-4 ? 1e-4 : (c > 1.0 ? 1.0 : c);
     int k = (int)((double)(pos + 1) * c);
     k = k < 1 ? 1 : (k > pos + 1 ? pos + 1 : k);
-    for (int b = warp; b < B; b += 32) {
-      bool sel = true;
-      if (has_mod) {
-        const float s = new_score[b];
-        const float* sc = score_cache + (size_t)b * capacity;
-        int cnt = 0;
-        for (int i = lane; i < pos; i += 32) cnt += (sc[i] >= s) ? 1 : 0;
+    dm = warp_sum(dm);
+    const float s = ri * dm + mod_b[0];
+    float* sc = score_cache + (size_t)b * capacity;
+    int cnt = 0;
+    for (int i = lane; i < pos && i < capacity; i += 32) cnt += (sc[i] >= s) ? 1 : 0;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
-        sel = cnt < k;
-        if (lane == 0) score_cache[(size_t)b * capacity + pos] = s;
-      }
-      if (lane == 0) flags[b] = (sel && depth[b] >= min_active) ? 1 : 0;
-    }
+    for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
+    sel = cnt < k;
+    if (lane == 0 && room) sc[pos] = s;
   }
-  __syncthreads();
-  const int f = (tid < B) ? flags[tid] : 0;
-  int total;
-  const int off = block_exclusive_scan(f, scan_buf, total);
-  if (f) rows[off] = tid;
-  if (tid == 0) *count = total;
+  if (!(room && sel && dep >= min_active)) return;      // warp-uniform
+  int j = 0;
+  if (lane == 0) {
+    j = atomicAdd(count, 1);
+    rows[j] = b;
+  }
+  j = __shfl_sync(0xffffffffu, j, 0);
+  scale_row<NCH>(norm2_w, ri, D, lane, v);
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    if (i < D) store_bf16x8(ug + (size_t)j * D + i, v[c]);
+  }
 }
 
 __global__ void decode_fill_kernel(int32_t* p, int n, int32_t val) {
+  chain_release();
+  chain_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) p[i] = val;
 }
@@ -379,6 +463,8 @@ __global__ void decode_fill_kernel(int32_t* p, int n, int32_t val) {
 // greedy token bookkeeping at the end of a step
 __global__ void decode_advance_kernel(int32_t* pos_ptr, const int64_t* __restrict__ tokens, int64_t* __restrict__ history,
                                       int B, int capacity) {
+  chain_release();
+  chain_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   const int pos = *pos_ptr;
   if (pos >= capacity) return;
@@ -391,11 +477,11 @@ __global__ void decode_advance_kernel(int32_t* pos_ptr, const int64_t* __restric
 // batches, or gemm_impl 1 (the mma.sync cross-check), take the general entry point.
 static int dgemm(const hb200_model* m, const DecodeWs& w, const void* A, const void* W, void* C, int M, int N, int K,
                  int64_t ldc, int epi, const void* resid, float alpha, const int32_t* rows, const int32_t* m_dev,
-                 int32_t* err, cudaStream_t st) {
+                 int32_t* err, cudaStream_t st, bool chain) {
   if (m->gemm_impl == 0 && M <= 128) {
     GemmParams p{(const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, K, K, ldc, epi,
                  (const __nv_bfloat16*)resid, epi == EPI_SCATTER_ADD ? 1.0f : alpha, rows, m_dev, err};
-    return launch_gemm_skinny(p, st);
+    return launch_gemm_skinny(p, st, chain);
   }
   return hb200_gemm_bf16(A, W, C, M, N, K, K, K, ldc, epi, resid, alpha, rows, m_dev, m->gemm_impl, err, st);
 }
@@ -440,11 +526,16 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
   const size_t cache_block = (size_t)B * KV * cap * hd;
   const float scale = 1.0f / sqrtf((float)hd);
 
-  HB_CUDA(cudaMemsetAsync(w.counts, 0, (size_t)m->n_blocks * R * 4, st));
-  HB_DISPATCH_NCH(D, embed_norm_kernel<NCH><<<row_grid, 256, 0, st>>>(ds->tokens, (const __nv_bfloat16*)m->tok_emb, w.x0,
-                                                                       m->blocks[0].norm1_w, w.a, B, D, m->vocab,
-                                                                       sqrtf((float)D), m->norm_eps));
-  HB_LAUNCH_CHECK();
+  // Every launch of the step is a link of one programmatic-dependent-launch chain: a kernel's scheduling and
+  // prologue overlap its predecessor's tail, and each kernel reads global memory only after chain_wait().
+  static const bool chain = [] {
+    const char* e = getenv("HB200_DECODE_CHAIN");
+    return e == nullptr || e[0] != '0';
+  }();
+#define HB_ROW_LAUNCH(KERNEL, GRID, ...) \
+  HB_DISPATCH_NCH(D, HB_PROPAGATE(launch_chained(KERNEL<NCH>, dim3(GRID), dim3(256), 0, st, chain, 1, __VA_ARGS__)))
+  HB_ROW_LAUNCH(embed_norm_kernel, row_grid, (const int64_t*)ds->tokens, (const __nv_bfloat16*)m->tok_emb, w.x0,
+                m->blocks[0].norm1_w, w.a, (int64_t)B, D, m->vocab, sqrtf((float)D), m->norm_eps);
   __nv_bfloat16 *xin = w.x0, *xout = w.x1;
   for (int bi = 0; bi < m->n_blocks; ++bi) {
     const hb200_block_weights& bw = m->blocks[bi];
@@ -453,63 +544,59 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
     __nv_bfloat16* kc = (__nv_bfloat16*)ds->kcache + (size_t)bi * cache_block;
     __nv_bfloat16* vc = (__nv_bfloat16*)ds->vcache + (size_t)bi * cache_block;
     // ---- attention half ----
-    HB_PROPAGATE(dgemm(m, w, w.a, bw.w_qkv, w.qkv, B, nq, D, nq, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st));
-    decode_conv_prep_kernel<<<B, 256, (size_t)8 * C * sizeof(float), st>>>(
-        w.qkv, (const __nv_bfloat16*)bw.w1_qk, (__nv_bfloat16*)ds->halo + (size_t)bi * B * 4 * C,
-        (__nv_bfloat16*)ds->vshift + (size_t)bi * B * (kvd / 2), vc, w.aq, w.ak, w.qm, w.km, ds->pos, B, H, KV, hd, cap);
-    HB_LAUNCH_CHECK();
-    HB_PROPAGATE(dgemm(m, w, w.aq, bw.w2_q, w.c2q, B, lat, 3 * lat, lat, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st));
-    HB_PROPAGATE(dgemm(m, w, w.ak, bw.w2_k, w.c2k, B, kvd, 3 * kvd, kvd, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st));
-    decode_qk_finish_kernel<<<B, 256, 0, st>>>(w.qkv, w.c2q, w.c2k, w.qm, w.km, m->rope_cos, m->rope_sin,
-                                               bw.key_temperature, w.qnew, kc, ds->pos, H, KV, hd, cap);
-    HB_LAUNCH_CHECK();
+    HB_PROPAGATE(dgemm(m, w, w.a, bw.w_qkv, w.qkv, B, nq, D, nq, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st, chain));
+    HB_PROPAGATE(launch_chained(decode_conv_prep_kernel, dim3(B), dim3(256), (size_t)8 * C * sizeof(float), st, chain, 1,
+                                w.qkv, (const __nv_bfloat16*)bw.w1_qk, (__nv_bfloat16*)ds->halo + (size_t)bi * B * 4 * C,
+                                (__nv_bfloat16*)ds->vshift + (size_t)bi * B * (kvd / 2), vc, w.aq, w.ak, w.qm, w.km,
+                                w.counts + (size_t)bi * R, (const int32_t*)ds->pos, B, H, KV, hd, cap));
+    HB_PROPAGATE(dgemm(m, w, w.aq, bw.w2_q, w.c2q, B, lat, 3 * lat, lat, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st,
+                       chain));
+    HB_PROPAGATE(launch_chained(decode_qk_finish_kernel, dim3(B), dim3(256), (size_t)4 * kvd * sizeof(float), st, chain, 1,
+                                w.qkv, w.c2q, w.ak, (const __nv_bfloat16*)bw.w2_k, w.qm, w.km, m->rope_cos, m->rope_sin,
+                                bw.key_temperature, w.qnew, kc, (const int32_t*)ds->pos, H, KV, hd, cap));
     switch (hd) {
-      case 16: HB_PROPAGATE(launch_decode_attention<16>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st)); break;
-      case 32: HB_PROPAGATE(launch_decode_attention<32>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st)); break;
-      default: HB_PROPAGATE(launch_decode_attention<64>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st)); break;
+      case 16: HB_PROPAGATE(launch_decode_attention<16>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st, chain)); break;
+      case 32: HB_PROPAGATE(launch_decode_attention<32>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st, chain)); break;
+      default: HB_PROPAGATE(launch_decode_attention<64>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st, chain)); break;
     }
     HB_PROPAGATE(dgemm(m, w, w.o, bw.w_o, w.cur, B, D, lat, D, EPI_RESID, xin, m->residual_scale * m->output_scale, nullptr,
-                       nullptr, err, st));
+                       nullptr, err, st, chain));
     // ---- MoR loop on the B new rows ----
-    if (!m->adaptive) {
-      decode_fill_kernel<<<ceil_div(B, 256), 256, 0, st>>>(w.depth, B, R - 1);
-      HB_LAUNCH_CHECK();
-    }
+    if (!m->adaptive)
+      HB_PROPAGATE(launch_chained(decode_fill_kernel, dim3(ceil_div(B, 256)), dim3(256), 0, st, chain, 1, w.depth, B, R - 1));
     for (int r = 0; r < R; ++r) {
       const float* rec = bw.rec + (size_t)r * D;
       const bool need_router = (r == 0) && m->adaptive;
-      if (need_router || has_mod) {
-#define HB_DSCORE(MOD_, ROUTER_)                                                                                  \
-  HB_DISPATCH_NCH(D, mor_score_kernel<NCH, MOD_, ROUTER_><<<(unsigned)ceil_div(B, 8 * SCORE_ROWS), 256, 0, st>>>( \
-                         w.cur, rec, bw.mod_wn, bw.mod_b, bw.mor_w, bw.mor_b, w.score, w.rlogit, w.depth, B, D,   \
-                         m->norm_eps, R, m->min_depth))
-        if (has_mod && need_router) HB_DSCORE(true, true);
-        else if (has_mod) HB_DSCORE(true, false);
-        else HB_DSCORE(false, true);
-#undef HB_DSCORE
-        HB_LAUNCH_CHECK();
-      }
       int32_t* count = w.counts + (size_t)bi * R + r;
-      decode_select_kernel<<<1, 1024, 0, st>>>(has_mod ? ds->scores + (((size_t)bi * R + r) * B) * cap : nullptr, w.score,
-                                               w.depth, r, w.rows, count, ds->pos, B, cap, m->mod_capacity, has_mod ? 1 : 0);
-      HB_LAUNCH_CHECK();
-      HB_DISPATCH_NCH(D, norm_gather_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, w.rows, count, w.ug, D,
-                                                                           m->norm_eps));
-      HB_LAUNCH_CHECK();
-      HB_PROPAGATE(dgemm(m, w, w.ug, bw.w_gate_up, w.act, B, 2 * F, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count, err, st));
-      HB_PROPAGATE(dgemm(m, w, w.act, bw.w_down, w.cur, B, D, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count, err, st));
+      float* cache = has_mod ? ds->scores + (((size_t)bi * R + r) * B) * cap : nullptr;
+#define HB_DROUTE(MOD_, ROUTER_)                                                                                       \
+  HB_DISPATCH_NCH(D, HB_PROPAGATE(launch_chained(decode_route_kernel<NCH, MOD_, ROUTER_>, dim3(row_grid), dim3(256), 0,   \
+                                                 st, chain, 1, (const __nv_bfloat16*)w.cur, rec, bw.norm2_w, bw.mod_wn,  \
+                                                 bw.mod_b, bw.mor_w, bw.mor_b, cache, w.depth, r, w.rows, count,         \
+                                                 (r + 1 < R) ? count + 1 : (int32_t*)nullptr, w.ug,                      \
+                                                 (const int32_t*)ds->pos, B, D, cap, m->mod_capacity, m->norm_eps, R,    \
+                                                 m->min_depth)))
+      if (has_mod && need_router) HB_DROUTE(true, true);
+      else if (has_mod) HB_DROUTE(true, false);
+      else if (need_router) HB_DROUTE(false, true);
+      else HB_DROUTE(false, false);
+#undef HB_DROUTE
+      HB_PROPAGATE(dgemm(m, w, w.ug, bw.w_gate_up, w.act, B, 2 * F, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count, err, st,
+                         chain));
+      HB_PROPAGATE(dgemm(m, w, w.act, bw.w_down, w.cur, B, D, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count, err, st,
+                         chain));
     }
     const float* next_w = last ? m->norm_w : m->blocks[bi + 1].norm1_w;
-    HB_DISPATCH_NCH(D, dual_norm_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, bw.final_norm_w, xout, next_w,
-                                                                       last ? w.hid : w.a, B, D, m->norm_eps));
-    HB_LAUNCH_CHECK();
+    HB_ROW_LAUNCH(dual_norm_kernel, row_grid, (const __nv_bfloat16*)w.cur, bw.final_norm_w, xout, next_w,
+                  last ? w.hid : w.a, (int64_t)B, D, m->norm_eps);
     std::swap(xin, xout);
   }
+#undef HB_ROW_LAUNCH
   __nv_bfloat16* lg = last_logits ? (__nv_bfloat16*)last_logits : w.logits;
   HB_PROPAGATE(dgemm(m, w, w.hid, m->tok_emb, lg, B, m->vocab, D, (int64_t)ld, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err,
-                     st));
-  HB_PROPAGATE(hb200_argmax_rows(lg, B, m->vocab, (int64_t)ld, ds->tokens, st));
-  decode_advance_kernel<<<ceil_div(B, 1024), 1024, 0, st>>>(ds->pos, ds->tokens, ds->history, B, cap);
-  HB_LAUNCH_CHECK();
+                     st, chain));
+  HB_PROPAGATE(launch_argmax_rows(lg, B, m->vocab, (int64_t)ld, ds->tokens, st, chain));
+  HB_PROPAGATE(launch_chained(decode_advance_kernel, dim3(ceil_div(B, 1024)), dim3(1024), 0, st, chain, 1, ds->pos,
+                              (const int64_t*)ds->tokens, ds->history, B, cap));
   return 0;
 }

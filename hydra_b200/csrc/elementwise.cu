@@ -304,13 +304,42 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* _
                                                           int64_t* __restrict__ out) {
   __shared__ float s_val[8];
   __shared__ int s_idx[8];
+  chain_release();
+  chain_wait();
   const __nv_bfloat16* row = x + (int64_t)blockIdx.x * ld;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-    const float v = __bfloat162float(row[i]);
+  auto take = [&](float v, int i) {
     if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+  };
+  int done = 0;
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // 16-byte pieces, four in flight per thread
+    const int vec = cols / 8;
+    constexpr int UN = 4;
+    for (int v0 = threadIdx.x; v0 < vec; v0 += blockDim.x * UN) {
+      uint4 raw[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const int vi = v0 + u * blockDim.x;
+        raw[u] = vi < vec ? *reinterpret_cast<const uint4*>(row + (size_t)vi * 8) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const int vi = v0 + u * blockDim.x;
+        if (vi < vec) {
+          const uint32_t w4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            take(__uint_as_float(w4[j] << 16), vi * 8 + 2 * j);
+            take(__uint_as_float(w4[j] & 0xffff0000u), vi * 8 + 2 * j + 1);
+          }
+        }
+      }
+    }
+    done = vec * 8;
   }
+  for (int i = done + threadIdx.x; i < cols; i += blockDim.x) take(__bfloat162float(row[i]), i);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -326,6 +355,13 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* _
   }
 }
 
+}  // namespace hb200
+
+namespace hb200 {
+int launch_argmax_rows(const void* x, int64_t rows, int cols, int64_t ld, int64_t* out, cudaStream_t st, bool chained) {
+  return launch_chained(argmax_rows_kernel, dim3((unsigned)rows), dim3(256), 0, st, chained, 1,
+                        (const __nv_bfloat16*)x, cols, ld, out);
+}
 }  // namespace hb200
 
 using namespace hb200;

@@ -70,6 +70,7 @@ __device__ __forceinline__ void epilogue_row_chunk(const GemmParams& p, int m, i
 int launch_gemm_tcgen05(const GemmParams& p, cudaStream_t st);
 int launch_gemm_mma(const GemmParams& p, cudaStream_t st);
 // M <= 128 rows: one CTA per (128 weight rows, K slice), split-K reduced across a thread-block cluster
-int launch_gemm_skinny(const GemmParams& p, cudaStream_t st);
+// chained: launched as a link of a programmatic-dependent-launch chain (see common.cuh)
+int launch_gemm_skinny(const GemmParams& p, cudaStream_t st, bool chained = false);
 
 }  // namespace hb200

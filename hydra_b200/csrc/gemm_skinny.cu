@@ -26,22 +26,33 @@ constexpr int SK_STAGES = 6;
 constexpr int SK_A_BYTES = SK_BM * SK_BK * 2, SK_B_BYTES = SK_BN * SK_BK * 2, SK_STAGE_BYTES = SK_A_BYTES + SK_B_BYTES;
 constexpr int SK_THREADS = 6 * 32;          // producer, MMA issuer, 4 epilogue warps
 constexpr int SK_SMEM_BYTES = SK_STAGES * SK_STAGE_BYTES + 256 + 1024;
-constexpr int SK_MAX_SPLIT = 8;             // portable cluster size
 constexpr int SK_MIN_KB_PER_SPLIT = 2;
 static_assert(SK_BM * SK_BN * 4 <= SK_STAGES * SK_STAGE_BYTES, "the fp32 partial reuses the operand ring");
 
 struct SkinnyPlan {
-  int n_tiles, k_blocks, ksplit, kb_per;
+  int bn, n_tiles, k_blocks, ksplit, kb_per;
 };
 
+// Tile width (64 / 96 / 128 weight rows) and K split (1 / 2 / 4 / 8 slices = cluster size) that put the most CTAs on
+// the SMs without exceeding one wave; every slice keeps at least two K blocks and every cluster member a column share
+// that is a multiple of 16 (the SwiGLU epilogue pairs columns in groups of 16).
 static SkinnyPlan skinny_plan(int N, int K) {
+  static const int cand[9][2] = {{128, 1}, {128, 2}, {128, 4}, {128, 8}, {96, 1}, {96, 2}, {64, 1}, {64, 2}, {64, 4}};
+  const int k_blocks = ceil_div(K, SK_BK), sms = sm_count();
+  int best = 0, best_ctas = -1;
+  for (int i = 0; i < 9; ++i) {
+    const int bn = cand[i][0], ks = cand[i][1];
+    if (ks > 1 && k_blocks / ks < SK_MIN_KB_PER_SPLIT) continue;
+    const int ctas = ceil_div(N, bn) * ks;
+    if (ctas > sms) continue;
+    if (ctas > best_ctas) { best = i; best_ctas = ctas; }   // earlier candidates (wider tile, fewer slices) win ties
+  }
   SkinnyPlan s;
-  s.n_tiles = ceil_div(N, SK_BN);
-  s.k_blocks = ceil_div(K, SK_BK);
-  const int want = std::min(sm_count() / s.n_tiles, s.k_blocks / SK_MIN_KB_PER_SPLIT);
-  s.ksplit = 1;
-  while (s.ksplit * 2 <= std::min(want, SK_MAX_SPLIT)) s.ksplit *= 2;   // power of two: column shares of 128 / ksplit
-  s.kb_per = ceil_div(s.k_blocks, s.ksplit);
+  s.bn = best_ctas < 0 ? 128 : cand[best][0];
+  s.ksplit = best_ctas < 0 ? 1 : cand[best][1];
+  s.n_tiles = ceil_div(N, s.bn);
+  s.k_blocks = k_blocks;
+  s.kb_per = ceil_div(k_blocks, s.ksplit);
   return s;
 }
 
@@ -60,9 +71,37 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
   return v;
 }
 
+// Row m of this CTA's column share [c_first, c_first + cw) of the tile: sum the KS partials (all loads of a 16-column
+// group in flight at once, then added in slice order) and apply the epilogue.
+template <int KS>
+__device__ __forceinline__ void reduce_share(const GemmParams& p, uint32_t part_addr, int m, int tile_col0, int c_first,
+                                             int cw) {
+  uint32_t peer[KS];
+#pragma unroll
+  for (int s = 0; s < KS; ++s) peer[s] = map_to_cta(part_addr + (uint32_t)((c_first * SK_BM + m) * 4), (uint32_t)s);
+#pragma unroll 1
+  for (int g = 0; g < cw / 16; ++g) {
+    const int col = tile_col0 + c_first + g * 16;
+    if (col >= p.N) break;
+    float t[KS][16];
+#pragma unroll
+    for (int s = 0; s < KS; ++s)
+#pragma unroll
+      for (int j = 0; j < 16; ++j) t[s][j] = ld_dsmem_f32(peer[s] + (uint32_t)((g * 16 + j) * SK_BM * 4));
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      v[j] = t[0][j];
+#pragma unroll
+      for (int s = 1; s < KS; ++s) v[j] += t[s][j];
+    }
+    epilogue_row_chunk<16>(p, m, col, v);
+  }
+}
+
 __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                                     const __grid_constant__ CUtensorMap tma_b,
-                                                                    const GemmParams p, int ksplit, int kb_per,
+                                                                    const GemmParams p, int bn, int ksplit, int kb_per,
                                                                     int k_blocks) {
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (s_addr(smem_dyn) + 1023u) & ~1023u;
@@ -74,13 +113,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
   volatile uint32_t* tmem_slot =
       reinterpret_cast<volatile uint32_t*>(base_ptr + SK_STAGES * SK_STAGE_BYTES + 8 * (2 * SK_STAGES + 2));
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  float* part = reinterpret_cast<float*>(base_ptr);       // [SK_BN columns][SK_BM rows] fp32, over the operand ring
+  float* part = reinterpret_cast<float*>(base_ptr);       // [bn columns][SK_BM rows] fp32, over the operand ring
+  const uint32_t stage_tx = (uint32_t)(SK_A_BYTES + bn * SK_BK * 2);   // bytes one stage receives
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int M = p.m_dev ? min(*p.m_dev, p.M) : p.M;
-  const int nt = blockIdx.x / ksplit, ks = blockIdx.x - nt * ksplit;   // ks == rank in the cluster
-  const int kb0 = ks * kb_per, kb1 = (M > 0) ? min(k_blocks, kb0 + kb_per) : kb0;
-  const bool has_work = kb1 > kb0;                                      // a trailing slice may be empty
+  chain_release();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < SK_STAGES; ++s) {
@@ -97,6 +134,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // everything above is independent of earlier kernels; from here on their results are read
+  chain_wait();
+  const int M = p.m_dev ? min(*p.m_dev, p.M) : p.M;
+  const int nt = blockIdx.x / ksplit, ks = blockIdx.x - nt * ksplit;   // ks == rank in the cluster
+  const int kb0 = ks * kb_per, kb1 = (M > 0) ? min(k_blocks, kb0 + kb_per) : kb0;
+  const bool has_work = kb1 > kb0;                                      // a trailing slice may be empty
+
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
@@ -105,9 +149,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
         const uint32_t sa = base + stage * SK_STAGE_BYTES;
-        mbar_arrive_expect_tx(full_bar(stage), SK_STAGE_BYTES);
+        mbar_arrive_expect_tx(full_bar(stage), stage_tx);
         tma_load_2d(sa, &tma_a, kb * SK_BK, 0, full_bar(stage));
-        tma_load_2d(sa + SK_A_BYTES, &tma_b, kb * SK_BK, nt * SK_BN, full_bar(stage));
+        tma_load_2d(sa + SK_A_BYTES, &tma_b, kb * SK_BK, nt * bn, full_bar(stage));
         if (++stage == SK_STAGES) { stage = 0; phase ^= 1u; }
       }
     }
@@ -115,7 +159,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0 && has_work) {
-      constexpr uint32_t idesc = make_idesc(SK_BM, SK_BN);
+      const uint32_t idesc = make_idesc(SK_BM, bn);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -148,16 +192,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
       if (ksplit == 1) {
         if (has_work) {
 #pragma unroll 1
-          for (int c = 0; c < SK_BN / 32; ++c) {
+          for (int c = 0; c < bn / 32; ++c) {
             float v[32];
             tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
-            const int col = nt * SK_BN + c * 32;
+            const int col = nt * bn + c * 32;
             if (m < M && col < p.N) epilogue_row_chunk<32>(p, m, col, v);
           }
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < SK_BN / 32; ++c) {
+        for (int c = 0; c < bn / 32; ++c) {
           float v[32];
           if (has_work) {
             tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
@@ -178,27 +222,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
     cluster_sync_all();                                            // all partials are in place
     if (warp >= 2 && *abort_flag == 0u) {
       const int m = (warp & 3) * 32 + lane;
-      const int cw = SK_BN / ksplit;                               // this CTA's share of the tile's columns (>= 16)
       if (m < M) {
-        const uint32_t part_addr = s_addr(part);
-#pragma unroll 1
-        for (int g = 0; g < cw / 16; ++g) {
-          const int c0 = ks * cw + g * 16;                         // column inside the tile
-          const int col = nt * SK_BN + c0;
-          if (col >= p.N) break;
-          float v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          for (int s = 0; s < ksplit; ++s) {                       // fixed order: deterministic sum
-            const uint32_t peer = map_to_cta(part_addr + (uint32_t)((c0 * SK_BM + m) * 4), (uint32_t)s);
-            float t[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) t[j] = ld_dsmem_f32(peer + (uint32_t)(j * SK_BM * 4));
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] += t[j];
-          }
-          epilogue_row_chunk<16>(p, m, col, v);
-        }
+        const int cw = bn / ksplit;                                // this CTA's share of the tile's columns
+        if (ksplit == 2) reduce_share<2>(p, s_addr(part), m, nt * bn, ks * cw, cw);
+        else if (ksplit == 4) reduce_share<4>(p, s_addr(part), m, nt * bn, ks * cw, cw);
+        else reduce_share<8>(p, s_addr(part), m, nt * bn, ks * cw, cw);
       }
     }
     cluster_sync_all();                                            // nobody leaves while a peer may still read it
@@ -217,32 +245,19 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
   if (warp == 1) tmem_dealloc(tmem_base, SK_BN);
 }
 
-int launch_gemm_skinny(const GemmParams& p, cudaStream_t st) {
+int launch_gemm_skinny(const GemmParams& p, cudaStream_t st, bool chained) {
   HB_REQUIRE(p.M >= 1 && p.M <= SK_BM, HB200_ERR_UNSUPPORTED, "skinny gemm: M = %d (1..%d rows)", p.M, SK_BM);
   const SkinnyPlan s = skinny_plan(p.N, p.K);
   CUtensorMap ta, tb;
   HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, SK_BM));
-  HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, SK_BN));
+  HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, (uint32_t)s.bn));
   static bool attr_set = false;
   if (!attr_set) {
     HB_CUDA(cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_BYTES));
     attr_set = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(s.n_tiles * s.ksplit), 1, 1);
-  cfg.blockDim = dim3(SK_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = SK_SMEM_BYTES;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)s.ksplit;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  HB_CUDA(cudaLaunchKernelEx(&cfg, gemm_skinny_kernel, ta, tb, p, s.ksplit, s.kb_per, s.k_blocks));
-  HB_LAUNCH_CHECK();
-  return 0;
+  return launch_chained(gemm_skinny_kernel, dim3((unsigned)(s.n_tiles * s.ksplit)), dim3(SK_THREADS), SK_SMEM_BYTES, st,
+                        chained, s.ksplit, ta, tb, p, s.bn, s.ksplit, s.kb_per, s.k_blocks);
 }
 
 }  // namespace hb200

@@ -201,6 +201,8 @@ __global__ void __launch_bounds__(256) dual_norm_kernel(const __nv_bfloat16* __r
                                                         const float* __restrict__ w1, __nv_bfloat16* __restrict__ y,
                                                         const float* __restrict__ w2, __nv_bfloat16* __restrict__ z,
                                                         int64_t T, int D, float eps) {
+  chain_release();
+  chain_wait();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= T) return;
@@ -234,6 +236,8 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const int64_t* __restri
                                                          __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                                                          __nv_bfloat16* __restrict__ a, int64_t T, int D, int V,
                                                          float scale, float eps) {
+  chain_release();
+  chain_wait();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= T) return;
