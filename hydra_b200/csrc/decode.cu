@@ -246,6 +246,7 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
   float mx[DATT_GMAX];
 #pragma unroll
   for (int g = 0; g < DATT_GMAX; ++g) mx[g] = -INFINITY;
+#pragma unroll 2
   for (int key = tid; key < n_keys; key += DATT_THREADS) {
     float kf[HD];
 #pragma unroll
@@ -312,6 +313,7 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
   for (int g = 0; g < DATT_GMAX; ++g)
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
+#pragma unroll 4
   for (int key = slice; key < n_keys; key += NSLICE) {
     float vf[8];
     load_bf16x8(vb + (size_t)key * HD + chunk * 8, vf);
@@ -392,14 +394,33 @@ __global__ void __launch_bounds__(256) decode_route_kernel(
   if (b >= B) return;
   const int pos = *pos_ptr;
   const bool room = pos < capacity;
+  // one pass over the row: every load (row pieces, then the per-column vectors) is issued before it is needed
+  uint4 raw[NCH];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int i = (c * 32 + lane) * 8;
+    raw[c] = (i < D) ? *reinterpret_cast<const uint4*>(cur + (size_t)b * D + i) : make_uint4(0, 0, 0, 0);
+  }
   float v[NCH][8];
-  const float ss = load_row_add<NCH>(cur + (size_t)b * D, rec, D, lane, v);   // sum (x + rec)^2
-  const float ri = rsqrtf(ss / (float)D + eps);
-  float dm = 0.f, lm = 0.f;
+  float ss = 0.f, dm = 0.f, lm = 0.f;
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int i = (c * 32 + lane) * 8;
     if (i < D) {
+      const float4 r0 = *reinterpret_cast<const float4*>(rec + i), r1 = *reinterpret_cast<const float4*>(rec + i + 4);
+      const float rc[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+      const uint32_t w4[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+      float x[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        x[2 * j] = __uint_as_float(w4[j] << 16);
+        x[2 * j + 1] = __uint_as_float(w4[j] & 0xffff0000u);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[c][j] = x[j] + rc[j];
+        ss += v[c][j] * v[c][j];
+      }
       if (HAS_MOD) {
         const float4 a0 = *reinterpret_cast<const float4*>(mod_wn + i), a1 = *reinterpret_cast<const float4*>(mod_wn + i + 4);
         dm += v[c][0] * a0.x + v[c][1] * a0.y + v[c][2] * a0.z + v[c][3] * a0.w + v[c][4] * a1.x + v[c][5] * a1.y +
@@ -407,13 +428,12 @@ __global__ void __launch_bounds__(256) decode_route_kernel(
       }
       if (HAS_ROUTER) {   // the depth router sees the raw row (no recursion offset)
         const float4 a0 = *reinterpret_cast<const float4*>(mor_w + i), a1 = *reinterpret_cast<const float4*>(mor_w + i + 4);
-        float raw[8];
-        load_bf16x8(cur + (size_t)b * D + i, raw);
-        lm += raw[0] * a0.x + raw[1] * a0.y + raw[2] * a0.z + raw[3] * a0.w + raw[4] * a1.x + raw[5] * a1.y +
-              raw[6] * a1.z + raw[7] * a1.w;
+        lm += x[0] * a0.x + x[1] * a0.y + x[2] * a0.z + x[3] * a0.w + x[4] * a1.x + x[5] * a1.y + x[6] * a1.z + x[7] * a1.w;
       }
     }
   }
+  ss = warp_sum(ss);
+  const float ri = rsqrtf(ss / (float)D + eps);
   int dep;
   if (HAS_ROUTER) {
     lm = warp_sum(lm);
@@ -432,7 +452,24 @@ __global__ void __launch_bounds__(256) decode_route_kernel(
     const float s = ri * dm + mod_b[0];
     float* sc = score_cache + (size_t)b * capacity;
     int cnt = 0;
-    for (int i = lane; i < pos && i < capacity; i += 32) cnt += (sc[i] >= s) ? 1 : 0;
+    const int n = min(pos, capacity);
+    if ((capacity & 3) == 0) {
+      // 16-byte pieces of the cached scores, several in flight per lane; entries at or beyond n do not count
+      const float4* sc4 = reinterpret_cast<const float4*>(sc);
+      const int n4 = (n + 3) >> 2;
+#pragma unroll 4
+      for (int i = lane; i < n4; i += 32) {
+        const float4 q = sc4[i];
+        const int i0 = i * 4;
+        cnt += (q.x >= s) ? 1 : 0;
+        cnt += (i0 + 1 < n && q.y >= s) ? 1 : 0;
+        cnt += (i0 + 2 < n && q.z >= s) ? 1 : 0;
+        cnt += (i0 + 3 < n && q.w >= s) ? 1 : 0;
+      }
+    } else {
+#pragma unroll 4
+      for (int i = lane; i < n; i += 32) cnt += (sc[i] >= s) ? 1 : 0;
+    }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
     sel = cnt < k;

@@ -3,9 +3,11 @@
 // With a handful of rows the contraction is bound by streaming W from HBM once, so the work is cut for bandwidth,
 // not for tensor throughput: one CTA per (128 weight rows, one slice of K), so even a 2048 x 5632 weight (16 row
 // tiles) keeps 128 SMs streaming.  Inside a CTA the pipeline is the one of the large GEMM: warp 0 issues TMA loads of
-// the A slice [128 x 64] (rows beyond M are zero-filled by the tensor map and cost no traffic) and the W tile
-// [128 x 64] into a 6-deep 128B-swizzled ring, warp 1 issues tcgen05.mma (M=128, N=128, K=16) into a TMEM
-// accumulator, warps 2-5 (one per TMEM lane quadrant) drain it.
+// the A slice (a 64-row box when M <= 64, else 128 rows; rows beyond M are zero-filled by the tensor map and cost no
+// traffic) and the W tile [64|96|128 x 64] into a 128B-swizzled ring of up to 12 stages, warp 1 issues tcgen05.mma
+// (M=128, N = tile width, K=16) into a TMEM accumulator, warps 2-5 (one per TMEM lane quadrant) drain it.  With the
+// 64-row box the MMA's rows 64..127 read the bytes that follow in the stage (the W tile): finite garbage that lands
+// in accumulator rows nobody reads.
 //
 // Split-K reduction through distributed shared memory: the CTAs that share a row tile form one thread-block cluster
 // (2, 4 or 8 CTAs, cluster rank = K slice).  Each parks its fp32 partial in its own shared memory; after a cluster
@@ -22,12 +24,13 @@
 namespace hb200 {
 
 constexpr int SK_BM = 128, SK_BN = 128, SK_BK = 64;
-constexpr int SK_STAGES = 6;
-constexpr int SK_A_BYTES = SK_BM * SK_BK * 2, SK_B_BYTES = SK_BN * SK_BK * 2, SK_STAGE_BYTES = SK_A_BYTES + SK_B_BYTES;
+constexpr int SK_RING_BYTES = 192 * 1024;   // operand ring: as many stages of (A rows + tile width) x 64 as fit, at most 12
+constexpr int SK_MAX_STAGES = 12;
 constexpr int SK_THREADS = 6 * 32;          // producer, MMA issuer, 4 epilogue warps
-constexpr int SK_SMEM_BYTES = SK_STAGES * SK_STAGE_BYTES + 256 + 1024;
+constexpr int SK_SMEM_BYTES = SK_RING_BYTES + 512 + 1024;
 constexpr int SK_MIN_KB_PER_SPLIT = 2;
-static_assert(SK_BM * SK_BN * 4 <= SK_STAGES * SK_STAGE_BYTES, "the fp32 partial reuses the operand ring");
+static_assert(SK_BM * SK_BN * 4 <= SK_RING_BYTES, "the fp32 partial reuses the operand ring");
+static_assert(8 * (2 * SK_MAX_STAGES + 1) + 16 <= 512, "barrier block");
 
 struct SkinnyPlan {
   int bn, n_tiles, k_blocks, ksplit, kb_per;
@@ -101,26 +104,28 @@ __device__ __forceinline__ void reduce_share(const GemmParams& p, uint32_t part_
 
 __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                                     const __grid_constant__ CUtensorMap tma_b,
-                                                                    const GemmParams p, int bn, int ksplit, int kb_per,
-                                                                    int k_blocks) {
+                                                                    const GemmParams p, int bn, int a_rows, int ksplit,
+                                                                    int kb_per, int k_blocks) {
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (s_addr(smem_dyn) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_dyn + (base - s_addr(smem_dyn));
-  const uint32_t bars = base + SK_STAGES * SK_STAGE_BYTES;
+  const uint32_t a_bytes = (uint32_t)a_rows * SK_BK * 2, stage_bytes = a_bytes + (uint32_t)bn * SK_BK * 2;
+  const int n_stages = min(SK_MAX_STAGES, SK_RING_BYTES / (int)stage_bytes);
+  const uint32_t bars = base + SK_RING_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (SK_STAGES + s); };
-  const uint32_t tfull_bar = bars + 8u * (2 * SK_STAGES);
+  auto empty_bar = [&](int s) { return bars + 8u * (SK_MAX_STAGES + s); };
+  const uint32_t tfull_bar = bars + 8u * (2 * SK_MAX_STAGES);
   volatile uint32_t* tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + SK_STAGES * SK_STAGE_BYTES + 8 * (2 * SK_STAGES + 2));
+      reinterpret_cast<volatile uint32_t*>(base_ptr + SK_RING_BYTES + 8 * (2 * SK_MAX_STAGES + 1));
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* part = reinterpret_cast<float*>(base_ptr);       // [bn columns][SK_BM rows] fp32, over the operand ring
-  const uint32_t stage_tx = (uint32_t)(SK_A_BYTES + bn * SK_BK * 2);   // bytes one stage receives
+  const uint32_t stage_tx = stage_bytes;                  // bytes one stage receives (out-of-range rows count too)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   chain_release();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < SK_STAGES; ++s) {
+    for (int s = 0; s < n_stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -148,11 +153,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
       uint32_t phase = 0;
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
-        const uint32_t sa = base + stage * SK_STAGE_BYTES;
+        const uint32_t sa = base + stage * stage_bytes;
         mbar_arrive_expect_tx(full_bar(stage), stage_tx);
         tma_load_2d(sa, &tma_a, kb * SK_BK, 0, full_bar(stage));
-        tma_load_2d(sa + SK_A_BYTES, &tma_b, kb * SK_BK, nt * bn, full_bar(stage));
-        if (++stage == SK_STAGES) { stage = 0; phase ^= 1u; }
+        tma_load_2d(sa + a_bytes, &tma_b, kb * SK_BK, nt * bn, full_bar(stage));
+        if (++stage == n_stages) { stage = 0; phase ^= 1u; }
       }
     }
     __syncwarp();
@@ -166,13 +171,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
-        const uint32_t sa = base + stage * SK_STAGE_BYTES;
+        const uint32_t sa = base + stage * stage_bytes;
         const uint64_t da = make_smem_desc(sa);
-        const uint64_t db = make_smem_desc(sa + SK_A_BYTES);
+        const uint64_t db = make_smem_desc(sa + a_bytes);
 #pragma unroll
         for (int k = 0; k < SK_BK / 16; ++k) umma_bf16(tmem_base, da + 2u * k, db + 2u * k, idesc, (kb > kb0 || k) ? 1u : 0u);
         umma_commit(empty_bar(stage));
-        if (++stage == SK_STAGES) { stage = 0; phase ^= 1u; }
+        if (++stage == n_stages) { stage = 0; phase ^= 1u; }
       }
       if (ok) umma_commit(tfull_bar);
     }
@@ -249,7 +254,8 @@ int launch_gemm_skinny(const GemmParams& p, cudaStream_t st, bool chained) {
   HB_REQUIRE(p.M >= 1 && p.M <= SK_BM, HB200_ERR_UNSUPPORTED, "skinny gemm: M = %d (1..%d rows)", p.M, SK_BM);
   const SkinnyPlan s = skinny_plan(p.N, p.K);
   CUtensorMap ta, tb;
-  HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, SK_BM));
+  const int a_rows = p.M <= 64 ? 64 : SK_BM;
+  HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, (uint32_t)a_rows));
   HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, (uint32_t)s.bn));
   static bool attr_set = false;
   if (!attr_set) {
@@ -257,7 +263,7 @@ int launch_gemm_skinny(const GemmParams& p, cudaStream_t st, bool chained) {
     attr_set = true;
   }
   return launch_chained(gemm_skinny_kernel, dim3((unsigned)(s.n_tiles * s.ksplit)), dim3(SK_THREADS), SK_SMEM_BYTES, st,
-                        chained, s.ksplit, ta, tb, p, s.bn, s.ksplit, s.kb_per, s.k_blocks);
+                        chained, s.ksplit, ta, tb, p, s.bn, a_rows, s.ksplit, s.kb_per, s.k_blocks);
 }
 
 }  // namespace hb200
