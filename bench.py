@@ -327,10 +327,10 @@ def main() -> None:
         from hydra_b200 import microbench
         if args.micro == "decode":
             args.batch = 64 if args.batch == 32 else args.batch
-        elif args.micro not in ("gemm", "model_hidden"):
+        elif args.micro not in ("gemm", "gemm_skinny", "model_hidden"):
             args.batch = 8 if args.batch == 32 else args.batch
         args.impl = args.impl_gemm
-        names = [n for n in microbench.CASES if n not in ("model_hidden", "decode")] if args.micro == "all" else [args.micro]
+        names = [n for n in microbench.CASES if n not in ("model_hidden", "decode", "gemm_skinny")] if args.micro == "all" else [args.micro]
         for nm in names:
             print(json.dumps(microbench.run(nm, args, ROOT)), flush=True)
         return

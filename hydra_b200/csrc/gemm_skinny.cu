@@ -139,25 +139,48 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // everything above is independent of earlier kernels; from here on their results are read
+  // Everything so far is independent of earlier kernels, and so are the weights: the producer starts streaming the
+  // W tiles of the first ring-full of K blocks before it waits for the predecessor (expect_tx without an arrival
+  // keeps each stage's barrier open until the matching A load has been issued).  W must not be written by the
+  // preceding kernels of the chain.
+  const int nt = blockIdx.x / ksplit, ks = blockIdx.x - nt * ksplit;   // ks == rank in the cluster
+  const int kb0 = ks * kb_per, kb1_full = min(k_blocks, kb0 + kb_per);
+  const int pre = max(0, min(n_stages, kb1_full - kb0));
+  const uint32_t b_bytes = stage_bytes - a_bytes;
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(full_bar(i), b_bytes);
+      tma_load_2d(base + i * stage_bytes + a_bytes, &tma_b, (kb0 + i) * SK_BK, nt * bn, full_bar(i));
+    }
+  }
   chain_wait();
   const int M = p.m_dev ? min(*p.m_dev, p.M) : p.M;
-  const int nt = blockIdx.x / ksplit, ks = blockIdx.x - nt * ksplit;   // ks == rank in the cluster
-  const int kb0 = ks * kb_per, kb1 = (M > 0) ? min(k_blocks, kb0 + kb_per) : kb0;
+  const int kb1 = (M > 0) ? kb1_full : kb0;
   const bool has_work = kb1 > kb0;                                      // a trailing slice may be empty
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
-        const uint32_t sa = base + stage * stage_bytes;
-        mbar_arrive_expect_tx(full_bar(stage), stage_tx);
-        tma_load_2d(sa, &tma_a, kb * SK_BK, 0, full_bar(stage));
-        tma_load_2d(sa + a_bytes, &tma_b, kb * SK_BK, nt * bn, full_bar(stage));
-        if (++stage == n_stages) { stage = 0; phase ^= 1u; }
+      if (!has_work) {
+        // no live rows: let the prefetched W tiles land (their barriers need the arrival), then leave
+        for (int i = 0; i < pre; ++i) mbar_arrive(full_bar(i));
+        for (int i = 0; i < pre; ++i)
+          if (!mbar_wait(full_bar(i), 0u, abort_flag)) break;
+      } else {
+        for (int i = 0; i < pre; ++i) {
+          mbar_arrive_expect_tx(full_bar(i), a_bytes);
+          tma_load_2d(base + i * stage_bytes, &tma_a, (kb0 + i) * SK_BK, 0, full_bar(i));
+        }
+        int stage = pre % n_stages;
+        uint32_t phase = (pre == n_stages) ? 1u : 0u;
+        for (int kb = kb0 + pre; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
+          const uint32_t sa = base + stage * stage_bytes;
+          mbar_arrive_expect_tx(full_bar(stage), stage_tx);
+          tma_load_2d(sa, &tma_a, kb * SK_BK, 0, full_bar(stage));
+          tma_load_2d(sa + a_bytes, &tma_b, kb * SK_BK, nt * bn, full_bar(stage));
+          if (++stage == n_stages) { stage = 0; phase ^= 1u; }
+        }
       }
     }
     __syncwarp();

@@ -88,6 +88,36 @@ def gemm(args) -> dict:
             "algorithmic_flops": flops, "working_set_mb": (per_set * ns + N * K * 2) / 1e6}
 
 
+def gemm_skinny(args) -> dict:
+    """The decode contraction (M <= 128 rows) with weight sets rotated so that every call streams W from HBM:
+    achieved = bytes of W (+ A and C) per call / time, against the HBM peak."""
+    M, N, K = min(args.m, 128), args.n, args.k
+    epi = {"store": 0, "resid": 1, "swiglu": 2, "scatter": 3}[args.epilogue]
+    n_out = N // 2 if epi == 2 else N
+    ldc = (n_out + 7) // 8 * 8
+    ns = _sets(N * K * 2)
+    W = [_rand_bf16(N, K, scale=0.03, seed=90 + i) for i in range(ns)]
+    A = _rand_bf16(M, K, seed=1)
+    Cm = torch.zeros(M, ldc, dtype=torch.bfloat16, device="cuda")
+    X = _rand_bf16(M, ldc, seed=7) if epi == 1 else None
+    rows = torch.randperm(M, device="cuda").to(torch.int32) if epi == 3 else None
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib = _lib.lib()
+
+    def run(i):
+        _lib.check(lib.hb200_gemm_skinny_bf16(A.data_ptr(), W[i % ns].data_ptr(), Cm.data_ptr(), M, N, K, K, K, ldc, epi,
+                                              X.data_ptr() if X is not None else None, 0.5,
+                                              rows.data_ptr() if rows is not None else None, None, err.data_ptr(),
+                                              _stream()))
+
+    ms = _time(run, args.iters)
+    assert int(err.item()) == 0
+    nbytes = 2.0 * (N * K + M * K + M * n_out * (2 if epi in (1, 3) else 1))
+    return {"kernel": f"gemm_skinny {args.epilogue}", "shape": [M, N, K], "ms": ms, "bound": "hbm",
+            "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "algorithmic_bytes": nbytes,
+            "working_set_mb": ns * N * K * 2 / 1e6}
+
+
 def _attention_module(dim=1024, H=8, KV=2, S=2048, temperature=1.0):
     from .attention import build_hybrid_attention_module
     torch.manual_seed(1)
@@ -297,13 +327,14 @@ def decode(args) -> dict:
     ev[0].record()
     sess.prefill(prompt)
     ev[1].record()
+    graph = os.environ.get("HB200_DECODE_GRAPH", "1") != "0"
     sess.step(use_graph=False)                # direct launch (one-time kernel setup), then the graph is captured
-    sess.step(use_graph=True)
+    sess.step(use_graph=graph)
     torch.cuda.synchronize()
     ev[2].record()
     steps = n_new - 3
     for _ in range(steps):
-        sess.step(use_graph=True)
+        sess.step(use_graph=graph)
     ev[3].record()
     torch.cuda.synchronize()
     m.check_device_errors()
@@ -313,7 +344,7 @@ def decode(args) -> dict:
     kv_bytes = 2.0 * 2.0 * B * 4 * 16 * mean_pos * args.blocks
     step_ms = decode_ms / steps
     nbytes = weight_bytes + kv_bytes
-    return {"kernel": "hb200_model_decode_step (CUDA graph replay)", "shape": [B, P, n_new], "ms": step_ms,
+    return {"kernel": "hb200_model_decode_step (%s)" % ("CUDA graph replay" if graph else "direct launches"), "shape": [B, P, n_new], "ms": step_ms,
             "bound": "hbm", "achieved": nbytes / (step_ms * 1e-3) / 1e9, "unit": "GB/s", "algorithmic_bytes": nbytes,
             "decode_tok_per_s": B / (step_ms * 1e-3), "timed_steps": steps,
             "note": "prefill of the prompt measured separately: %.1f ms; weights %.2f GB + cache reads %.3f GB per step"
@@ -321,7 +352,7 @@ def decode(args) -> dict:
 
 
 CASES: Dict[str, Callable] = {
-    "decode": decode,
+    "decode": decode, "gemm_skinny": gemm_skinny,
     "gemm": gemm, "ccgqa_block": ccgqa_block, "pre_attention": pre_attention, "attention": attention,
     "rms_norm": rms_norm, "rope": rope, "swiglu_ffn": swiglu_ffn, "swiglu_act": swiglu_act,
     "model_hidden": model_hidden,
