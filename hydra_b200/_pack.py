@@ -59,7 +59,9 @@ def interleave_gate_up(w: Tensor, device) -> Tensor:
 class PackedBlock:
     """Device tensors of one HydraMoRBlock (kept alive here) and the matching C struct."""
 
-    def __init__(self, sd: Dict[str, Tensor], pre: str, device, *, attention_only: bool = False):
+    def __init__(self, sd: Dict[str, Tensor], pre: str, device, *, attention_only: bool = False, plain: bool = False):
+        """plain: a HydraBlock (blocks.py:33-70) - attention and one MLP pass, no routers, no recursion offsets, no exit
+        norm; expressed as a one-recursion block with a zero offset."""
         a = pre if attention_only else pre + "attention."
         t: Dict[str, Optional[Tensor]] = {}
         t["w_qkv"] = _bf16(sd[a + "qkv_proj.weight"], device)
@@ -75,9 +77,12 @@ class PackedBlock:
         if not attention_only:
             t["norm1_w"] = _f32(sd[pre + "norm1.weight"], device)
             t["norm2_w"] = _f32(sd[pre + "norm2.weight"], device)
-            t["final_norm_w"] = _f32(sd[pre + "final_norm.weight"], device)
             t["w_gate_up"] = interleave_gate_up(sd[pre + "mlp.gate_up.weight"], device)
             t["w_down"] = _bf16(sd[pre + "mlp.down.weight"], device)
+        if plain:
+            t["rec"] = torch.zeros((1, t["norm1_w"].numel()), dtype=torch.float32, device=device)
+        elif not attention_only:
+            t["final_norm_w"] = _f32(sd[pre + "final_norm.weight"], device)
             t["mor_w"] = _f32(sd[pre + "mor_router.router.weight"], device).reshape(-1)
             t["mor_b"] = _f32(sd[pre + "mor_router.router.bias"], device).reshape(1)
             rb = sd[pre + "mor_executor.recursion_bias"]

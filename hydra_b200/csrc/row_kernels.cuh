@@ -195,7 +195,8 @@ __global__ void __launch_bounds__(256) norm_gather_kernel(const __nv_bfloat16* _
 }
 
 // y = RMSNorm(src; w1) rounded to bf16 (the block output), z = RMSNorm(y; w2) (the next block's pre-attention norm,
-// or the model's final norm): one read of src instead of three passes.  Either output may be omitted.
+// or the model's final norm): one read of src instead of three passes.  Either output may be omitted.  w1 == nullptr
+// (a block without an exit norm): y = src.
 template <int NCH>
 __global__ void __launch_bounds__(256) dual_norm_kernel(const __nv_bfloat16* __restrict__ src,
                                                         const float* __restrict__ w1, __nv_bfloat16* __restrict__ y,
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(256) dual_norm_kernel(const __nv_bfloat16* __r
   if (row >= T) return;
   float v[NCH][8];
   const float ss = load_row_add<NCH>(src + row * D, nullptr, D, lane, v);
-  scale_row<NCH>(w1, rsqrtf(ss / (float)D + eps), D, lane, v);
+  if (w1 != nullptr) scale_row<NCH>(w1, rsqrtf(ss / (float)D + eps), D, lane, v);
   float ss2 = 0.f;
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {

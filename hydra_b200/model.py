@@ -399,6 +399,58 @@ class HydraB200Model:
         return {"mlp_rows": self.last_taps.mlp_rows.cpu().tolist()}
 
 
+class HydraB200BaseModel(HydraB200Model):
+    """``HydraBaseModel`` (hydra/model/framework/model.py:82-160): the routing-free baseline - ``n_layers`` plain
+    pre-norm blocks (``HydraBlock``, blocks.py:33-70: ``h = x + attn(norm1 x)``, ``h + mlp(norm2 h)``), final RMSNorm,
+    tied output projection.  Runs on the same executor as the routed model: every block is a one-recursion block with
+    a zero recursion offset, full residual scale, no routers and no exit norm.  ``state_dict`` keys:
+    ``tok_emb.weight``, ``layers.{i}.attention.*``, ``layers.{i}.{norm1,norm2}.weight``, ``layers.{i}.mlp.*``,
+    ``norm.weight`` (``output.weight`` must be the tied embedding if present)."""
+
+    def __init__(self, state_dict: Dict[str, Tensor], *, n_heads: int, n_kv_heads: int, compression_factor: int = 4,
+                 max_seq_len: int = 2048, device: str | torch.device = "cuda", norm_eps: float = 1e-6,
+                 gemm_impl: int = 0):
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise RuntimeError("HydraB200BaseModel needs a CUDA device (there is no CPU fallback)")
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        sd = normalize_state_dict(state_dict)
+        if "output.weight" in sd and not torch.equal(sd["output.weight"].cpu(), sd["tok_emb.weight"].cpu()):
+            raise NotImplementedError("HydraB200BaseModel: an untied output projection is not built")
+        V, D = sd["tok_emb.weight"].shape
+        nb = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("layers."))
+        F = sd["layers.0.mlp.down.weight"].shape[1]
+        lat = D // compression_factor
+        hd = lat // n_heads
+        self.vocab_size, self.dim, self.n_mor_blocks, self.recursions_per_block = V, D, nb, 1
+        self.n_layers = nb
+        self.n_heads, self.n_kv_heads, self.head_dim, self.ffn_hidden = n_heads, n_kv_heads, hd, F
+        self.max_seq_len, self.mod_capacity, self.mor_min_depth, self.adaptive = max_seq_len, 1.0, 0, False
+        self.device = dev
+        with kernels._on(dev):
+            blocks = [PackedBlock(sd, f"layers.{i}.", dev, plain=True) for i in range(nb)]
+            self.has_mod = [False] * nb
+            self.packed = PackedModel(
+                vocab=V, dim=D, n_rec=1, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=hd, ffn_hidden=F,
+                min_depth=0, adaptive=False, max_seq_len=max_seq_len, mod_capacity=1.0, norm_eps=norm_eps,
+                residual_scale=1.0, output_scale=float(os.environ.get("HYDRA_CCGQA_OUTPUT_SCALE", "1.0")),
+                blocks=blocks, tok_emb=_bf16(sd["tok_emb.weight"], dev), norm_w=_f32(sd["norm.weight"], dev),
+                device=dev, gemm_impl=gemm_impl)
+        self.ld_logits = (V + 7) // 8 * 8
+        self._logits = None
+        self.last_taps = None
+
+    @classmethod
+    def from_reference(cls, model, **overrides) -> "HydraB200BaseModel":
+        """Build from a reference ``HydraBaseModel`` instance."""
+        attn = model.layers[0].attention
+        kw = dict(n_heads=attn.n_heads, n_kv_heads=attn.n_kv_heads, compression_factor=attn.compression_factor,
+                  max_seq_len=attn.cos_cached.shape[0])
+        kw.update(overrides)
+        return cls(model.state_dict(), **kw)
+
+
 class DecodeSession:
     """Caches and bookkeeping of a batch of sequences decoded in lockstep (``hb200_decode_state``).
 

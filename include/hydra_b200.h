@@ -183,7 +183,7 @@ int hb200_argmax_rows(const void* x, int64_t rows, int cols, int64_t ld, int64_t
 typedef struct hb200_block_weights {
   const float* norm1_w;          /* [D] AdaRMSNorm gain before attention */
   const float* norm2_w;          /* [D] AdaRMSNorm gain before the MLP   */
-  const float* final_norm_w;     /* [D] RMSNorm gain at block exit       */
+  const float* final_norm_w;     /* [D] RMSNorm gain at block exit, or NULL: no exit norm (HydraBlock, blocks.py:33-70) */
   const void* w_qkv;             /* bf16 [lat+2*kvd, D]                  */
   const void* w_o;               /* bf16 [D, lat]                        */
   const void* w1_qk;             /* bf16 repacked conv1 (q rows, k rows) */

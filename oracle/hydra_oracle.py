@@ -374,6 +374,28 @@ def model_forward(ids: Tensor, p: Dict[str, Tensor], cfg: HydraConfig,
     return h @ w_out.transpose(0, 1)
 
 
+def base_block_forward(x: Tensor, p: Dict[str, Tensor], i: int, cfg: HydraConfig) -> Tensor:
+    """HydraBlock.forward (blocks.py:68-70): h = x + attn(norm1 x); h + mlp(norm2 h).  No routing, no residual
+    scale, no exit norm."""
+    pre = f"layers.{i}."
+    h = x + ccgqa_forward(rms_norm(x, p[pre + "norm1.weight"], cfg.norm_eps), p, pre + "attention.", cfg)
+    return h + swiglu_mlp(rms_norm(h, p[pre + "norm2.weight"], cfg.norm_eps), p[pre + "mlp.gate_up.weight"],
+                          p[pre + "mlp.down.weight"])
+
+
+def base_model_forward(ids: Tensor, p: Dict[str, Tensor], cfg: HydraConfig, taps: Optional[list] = None) -> Tensor:
+    """HydraBaseModel.forward (model.py:140-159): the routing-free baseline; cfg.n_mor_blocks is its n_layers.
+    `taps`, if given, receives every block's output."""
+    h = embed(ids, p, cfg)
+    for i in range(cfg.n_mor_blocks):
+        h = base_block_forward(h, p, i, cfg)
+        if taps is not None:
+            taps.append(h)
+    h = rms_norm(h, p["norm.weight"], cfg.norm_eps)
+    w_out = p["output.weight"] if "output.weight" in p else p["tok_emb.weight"]
+    return h @ w_out.transpose(0, 1)
+
+
 def greedy_generate(prompt_ids: Tensor, p: Dict[str, Tensor], cfg: HydraConfig, max_new_tokens: int,
                     return_margins: bool = False):
     """Greedy form of the reference's generation loop (diagnostics/eval_checkpoint.py:127-160): the full forward is

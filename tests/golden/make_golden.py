@@ -2,7 +2,8 @@
 
 Usage (only where the reference tree is available):
 
-    PYTHONPATH=<reference root> python tests/golden/make_golden.py
+    PYTHONPATH=<reference root> python tests/golden/make_golden.py          # every fixture
+    PYTHONPATH=<reference root> python tests/golden/make_golden.py base     # only base_model_hd16.npz
 
 The reference (pure Python + PyTorch) is imported, its modules are built on CPU
 with a fixed seed, weights are rounded to bf16-representable values (so that a
@@ -226,12 +227,60 @@ def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: i
     save(name, **arrs)
 
 
+def gen_base_model(name: str, *, vocab: int, dim: int, n_layers: int, H: int, KV: int, mlp_ratio: float, B: int, S: int,
+                   seed: int) -> None:
+    """HydraBaseModel (no routing): logits, every block's output and the reference's own bf16 error."""
+    from hydra.model.framework import HydraBaseModel
+
+    torch.manual_seed(seed)
+    m = HydraBaseModel(vocab_size=vocab, dim=dim, n_layers=n_layers, n_heads=H, n_kv_heads=KV, compression_factor=4,
+                       mlp_ratio=mlp_ratio, max_seq_len=S)
+    g = torch.Generator().manual_seed(seed + 1)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith("norm1.weight") or n.endswith("norm2.weight") or n == "norm.weight":
+                p.mul_(1.0 + 0.1 * torch.randn(p.shape, generator=g))
+        for p in m.parameters():
+            bf16_round_(p)
+    m.eval()
+    ids = torch.randint(0, vocab, (B, S), generator=torch.Generator().manual_seed(seed + 2))
+    ids[0, 0] = vocab + 5
+    ids[0, 1] = -3
+    block_out = []
+    hooks = [layer.register_forward_hook(lambda _m, _i, o: block_out.append(o.clone())) for layer in m.layers]
+    with torch.no_grad():
+        logits = m(ids)
+    for h in hooks:
+        h.remove()
+    arrs = dict(meta=np.array([vocab, dim, n_layers, 1, H, KV, B, S], dtype=np.int64),
+                cap=np.array([1.0], dtype=np.float64),
+                ffn_hidden=np.array([m.layers[0].mlp.down.weight.shape[1]], dtype=np.int64),
+                ids=ids.numpy(), logits=f32(logits))
+    for i, bo in enumerate(block_out):
+        arrs[f"block_out:{i}"] = f32(bo)
+    for kname, t in m.state_dict().items():
+        if kname == "output.weight":
+            continue   # tied to tok_emb.weight
+        arrs["w:" + kname] = to_bits(t) if t.dim() >= 2 and t.numel() > 4096 else f32(t)
+    mb = m.to(torch.bfloat16)
+    mb.eval()
+    with torch.no_grad():
+        lb = mb(ids).float()
+    err = lb - logits
+    arrs["ref_bf16_maxabs"] = np.array([float(err.abs().max())])
+    arrs["ref_bf16_rel_l2"] = np.array([float(err.norm() / logits.norm())])
+    save(name, **arrs)
+
+
 if __name__ == "__main__":
     try:
         import hydra  # noqa: F401
     except Exception as e:  # pragma: no cover
         sys.exit(f"the reference package 'hydra' must be importable (set PYTHONPATH): {e}")
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+    if len(sys.argv) > 1 and sys.argv[1] == "base":     # only the routing-free baseline model
+        gen_base_model("base_model_hd16.npz", vocab=384, dim=256, n_layers=3, H=4, KV=2, mlp_ratio=1.0, B=2, S=112, seed=8)
+        sys.exit(0)
     gen_fused_ops()
     # config-2 shapes (dim 1024, 8q/2kv, hd 32) at a short sequence; temperature 1.0 as BASELINE config 2
     gen_attention("ccgqa_hd32.npz", 1024, 8, 2, 1, 80, seed=1, temperature=1.0)
@@ -246,3 +295,4 @@ if __name__ == "__main__":
               B=2, S=128, cap=0.75, seed=0)
     gen_model("model_hd32.npz", vocab=384, dim=256, NB=3, R=4, H=2, KV=1, mlp_ratio=1.0,
               B=2, S=96, cap=0.5, seed=5)
+    gen_base_model("base_model_hd16.npz", vocab=384, dim=256, n_layers=3, H=4, KV=2, mlp_ratio=1.0, B=2, S=112, seed=8)

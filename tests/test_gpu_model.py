@@ -271,3 +271,33 @@ def test_errors():
     from hydra_b200._lib import Hb200Error
     with pytest.raises(Hb200Error):
         m(torch.zeros(1, cfg.max_seq_len + 1, dtype=torch.int64).cuda())   # beyond the RoPE table
+
+
+def test_base_model_without_routing():
+    """HydraBaseModel on the same executor (one-recursion blocks, zero offset, no exit norm): against the golden logits
+    of the reference (tolerance: twice the reference's own bf16 error), against the oracle block by block, and
+    generation in both modes (no MoD, so cached decode and re-forward compute the same thing)."""
+    from hydra_b200.model import HydraB200BaseModel
+    fx, cfg, w = G.model_fixture("base_model_hd16.npz")
+    ids = torch.from_numpy(fx["ids"])
+    m = HydraB200BaseModel(w, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, max_seq_len=cfg.max_seq_len)
+    lg = m(ids.cuda(), block_out=True).float().cpu()
+    m.check_device_errors()
+    ref = torch.from_numpy(fx["logits"])
+    err = rel_l2(lg, ref)
+    print(f"base model vs reference fp32 logits: rel_l2 {err:.3e}; reference's own bf16 path: {float(fx['ref_bf16_rel_l2'][0]):.3e}")
+    assert err <= 2.0 * float(fx["ref_bf16_rel_l2"][0]) + 1e-3
+    bo = m.last_taps.block_out.float().cpu().view(cfg.n_mor_blocks, *ids.shape, -1)
+    for i in range(cfg.n_mor_blocks):
+        assert rel_l2(bo[i], torch.from_numpy(fx[f"block_out:{i}"])) <= 1e-2, f"block {i}"
+    taps = []
+    assert max_abs(O.base_model_forward(ids, w, cfg, taps=taps), ref) < 5e-5
+    prompt = ids[:, :30].clamp(0, cfg.vocab_size - 1).cuda()
+    a = m.generate(prompt, 6)
+    b, lgc = m.generate_cached(prompt, 6, return_logits=True)
+    full = m(b[:, :-1]).float()                    # re-forward of the cached sequence: logits of every chosen token
+    assert rel_l2(lgc.float().cpu(), full[:, 29:].cpu()) < 1e-2
+    margin = full[:, 29:].topk(2, dim=-1).values
+    clear = ((margin[..., 0] - margin[..., 1]) > 0.06).cpu()
+    assert torch.equal(b[:, 30:].cpu()[clear], full[:, 29:].argmax(-1).cpu()[clear])
+    assert a.shape == b.shape

@@ -113,3 +113,16 @@ def test_mor_depths_rounding_half_even():
     assert d.tolist() == [2, 0, 3]
     d1, _ = O.mor_depths(torch.tensor([-50.0, 50.0]), 4, min_depth=1)
     assert d1.tolist() == [1, 3]
+
+
+def test_base_model_without_routing_matches_reference():
+    """HydraBaseModel (HydraBlock layers, no routers, no exit norms): logits and every block output."""
+    fx, cfg, w = G.model_fixture("base_model_hd16.npz")
+    ids = torch.from_numpy(fx["ids"])
+    taps = []
+    lg = O.base_model_forward(ids, w, cfg, taps=taps)
+    ref = torch.from_numpy(fx["logits"])
+    assert float((lg - ref).abs().max()) <= 5e-6 * max(1.0, float(ref.abs().max()))
+    for i, bo in enumerate(taps):
+        r = torch.from_numpy(fx[f"block_out:{i}"])
+        assert float((bo - r).abs().max()) <= 5e-6 * max(1.0, float(r.abs().max())), f"block {i}"
