@@ -271,6 +271,14 @@ def run_ours(args) -> None:
         dom_ms = by_kind.get(dom, {"ms": 0.0})["ms"]
         achieved = fl.get(dom, 0.0) / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else 0.0
         peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        # DRAM traffic of one gate_up launch, scaled from the ncu capture of the same kernel at M = 8192 rows
+        # (N = 5632, K = 1024: 28.40 MB read of which 11.53 MB is the weight, 5.02 MB written before the launch ended):
+        # the weight is read once per launch whatever M is, everything else grows with the rows of the launch.
+        cap_rows, cap_read, cap_write, cap_weight = 8192.0, 28.40e6, 5.02e6, 2.0 * 5632 * 1024
+        n_dom = max(1, by_kind.get(dom, {"launches": 0})["launches"])
+        dom_nk = next((r["n"] * r["k"] for r in records if r["kind"] == dom), 0)
+        avg_rows = fl.get(dom, 0.0) / (2.0 * dom_nk) / n_dom if dom_nk else 0.0
+        traffic = cap_weight + (cap_read - cap_weight + cap_write) / cap_rows * avg_rows
         all_gemm_fl = sum(v for k, v in fl.items())
         routed_per_token = all_gemm_fl / (T * K)
         line = {
@@ -283,7 +291,9 @@ def run_ours(args) -> None:
             "gpu_launches": launches_per_step * K,
             "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<256> (gate_up + SwiGLU epilogue)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
-                         "peak_source": f"bf16_tflops_sustained, {peak_src}", "traffic": None,
+                         "peak_source": f"bf16_tflops_sustained, {peak_src}", "traffic": traffic,
+                         "traffic_unit": "B/launch (DRAM read + write, scaled by rows from the ncu capture at M=8192)",
+                         "avg_rows_per_launch": avg_rows,
                          "launches_per_step": by_kind.get(dom, {"launches": 0})["launches"] // K},
             "model_tflops": {"routed_flops_per_token": routed_per_token,
                              "dense_flops_per_token": 823.4e6,
