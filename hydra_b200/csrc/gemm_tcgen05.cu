@@ -172,23 +172,30 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
       int mt, nt;
       tile_coords(tile, m_tiles, n_tiles, mt, nt);
       const int m = mt * GBM + quad * 32 + lane;
-      // Read-modify-write epilogues: fetch this thread's residual / target row segment BEFORE waiting for the
-      // accumulator, so the global-load latency hides behind the mainloop of this tile.
-      uint4 pre[CHUNKS][4];
-      __nv_bfloat16* rmw_dst = nullptr;
-      if (rmw) {
-        const int col0 = nt * BN + half * CHUNKS * 32;
-        if (m < M) {
-          const size_t row = (p.epilogue == EPI_SCATTER_ADD) ? (size_t)p.rows[m] : (size_t)m;
-          rmw_dst = p.C + row * p.ldc + col0;
-          const __nv_bfloat16* src = (p.epilogue == EPI_RESID) ? p.resid + row * p.ldc + col0 : rmw_dst;
+      // Read-modify-write epilogues (residual, scatter-add).  The accumulator comes out of TMEM with thread = row, but
+      // rows are 2 KB or more apart in memory, so row-per-thread 16-byte accesses would touch 32 partial sectors per
+      // request.  Instead the warp's staging box (32 rows x 64 columns, 128B-swizzled) is the meeting point: the old
+      // values are fetched with eight lanes per row (whole 128-byte lines, cp.async, issued BEFORE the accumulator
+      // wait so the latency hides behind the mainloop), each thread then updates its own row inside the box, and the
+      // box leaves again with eight lanes per row.
+      constexpr int RMW_BOXES = CHUNKS * 32 / 64;
+      const int rmw_col0 = nt * BN + half * CHUNKS * 32;
+      long long grow = -1;                       // global row this lane's tile row reads / writes, -1 = none
+      const __nv_bfloat16* rmw_src = (p.epilogue == EPI_RESID) ? p.resid : p.C;
+      auto rmw_fetch = [&](int bx) {
 #pragma unroll
-          for (int c = 0; c < CHUNKS; ++c)
-#pragma unroll
-            for (int q8 = 0; q8 < 4; ++q8)
-              pre[c][q8] = (col0 + c * 32 + q8 * 8 + 8 <= p.N) ? ld_global_v4(src + c * 32 + q8 * 8)
-                                                               : make_uint4(0, 0, 0, 0);
+        for (int it = 0; it < 8; ++it) {
+          const int rr = it * 4 + (lane >> 3), piece = lane & 7;
+          const long long gr = __shfl_sync(0xffffffffu, grow, rr);
+          const int col = rmw_col0 + bx * 64 + piece * 8;
+          if (gr >= 0 && col < p.N)
+            cp_async16(my_box + (uint32_t)(rr * 128 + ((piece ^ (rr & 7)) << 4)), rmw_src + (size_t)gr * p.ldc + col);
         }
+        cp_async16_commit();
+      };
+      if (rmw) {
+        if (m < M) grow = (p.epilogue == EPI_SCATTER_ADD) ? (long long)p.rows[m] : (long long)m;
+        rmw_fetch(0);
       }
       if (!mbar_wait(tfull_bar(as), aphase, abort_flag)) { ok = false; }
       ok = __all_sync(0xffffffffu, ok);
@@ -243,27 +250,46 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
           }
         }
       } else if (rmw) {
-        const int col0 = nt * BN + half * CHUNKS * 32;
+#pragma unroll 1
+        for (int bx = 0; bx < RMW_BOXES; ++bx) {
+          cp_async16_wait_all();
+          __syncwarp();                                            // every lane's pieces of the box have landed
 #pragma unroll
-        for (int c = 0; c < CHUNKS; ++c) {
-          float v[32];
-          tmem_ld_32x32(t_row + (uint32_t)(half * CHUNKS * 32 + c * 32), v);   // warp-collective
-          if (rmw_dst != nullptr) {
+          for (int c2 = 0; c2 < 2; ++c2) {
+            float v[32];
+            tmem_ld_32x32(t_row + (uint32_t)(half * CHUNKS * 32 + bx * 64 + c2 * 32), v);   // warp-collective
+            if (grow >= 0) {
 #pragma unroll
-            for (int q8 = 0; q8 < 4; ++q8) {
-              if (col0 + c * 32 + q8 * 8 + 8 <= p.N) {
-                const uint32_t w4[4] = {pre[c][q8].x, pre[c][q8].y, pre[c][q8].z, pre[c][q8].w};
-                uint4 o;
-                uint32_t* ow = &o.x;
+              for (int q8 = 0; q8 < 4; ++q8) {
+                const int piece = c2 * 4 + q8;
+                if (rmw_col0 + bx * 64 + piece * 8 < p.N) {
+                  const uint32_t addr = my_box + (uint32_t)(lane * 128 + ((piece ^ (lane & 7)) << 4));
+                  const uint4 old4 = ld_shared_v4(addr);
+                  const uint32_t w4[4] = {old4.x, old4.y, old4.z, old4.w};
+                  uint4 o;
+                  uint32_t* ow = &o.x;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float r0 = __uint_as_float(w4[j] << 16), r1 = __uint_as_float(w4[j] & 0xffff0000u);
-                  ow[j] = pack_bf16x2_rn(r0 + p.alpha * v[q8 * 8 + 2 * j], r1 + p.alpha * v[q8 * 8 + 2 * j + 1]);
+                  for (int j = 0; j < 4; ++j) {
+                    const float r0 = __uint_as_float(w4[j] << 16), r1 = __uint_as_float(w4[j] & 0xffff0000u);
+                    ow[j] = pack_bf16x2_rn(r0 + p.alpha * v[q8 * 8 + 2 * j], r1 + p.alpha * v[q8 * 8 + 2 * j + 1]);
+                  }
+                  st_shared_v4(addr, o);
                 }
-                *reinterpret_cast<uint4*>(rmw_dst + c * 32 + q8 * 8) = o;
               }
             }
           }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3), piece = lane & 7;
+            const long long gr = __shfl_sync(0xffffffffu, grow, rr);
+            const int col = rmw_col0 + bx * 64 + piece * 8;
+            if (gr >= 0 && col < p.N)
+              *reinterpret_cast<uint4*>(p.C + (size_t)gr * p.ldc + col) =
+                  ld_shared_v4(my_box + (uint32_t)(rr * 128 + ((piece ^ (rr & 7)) << 4)));
+          }
+          __syncwarp();                                            // the box is free again
+          if (bx + 1 < RMW_BOXES) rmw_fetch(bx + 1);
         }
       } else {
         // generic fallback (column counts that are not a multiple of 8)
