@@ -6,7 +6,7 @@
         bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference ...      # the CPU arm: the oracle port of the reference's eager forward
 
-Workload (BASELINE.json configs[3]): dim 1024, 10 MoR blocks x 4 recursions, CCGQA 4x compression with 8 query /
+Workload (the HYDRA-250M prefill benchmark configuration): dim 1024, 10 MoR blocks x 4 recursions, CCGQA 4x compression with 8 query /
 2 KV heads (head_dim 32), SwiGLU hidden 2816, MoD top-k at 75% capacity in the interior blocks, vocab 50257, tied
 output projection; batch 32 x 2048 synthetic token ids PER GPU (weak scaling: every rank is a full replica working
 on its own sequences; sequences never cross GPUs and there is no collective inside the timed region).  Weights are

@@ -1,6 +1,6 @@
 // Cached decode: one new token per sequence through every block against the latent-space KV cache.
 //
-// The reference has no decode path; this executor adds the cache that BASELINE's decode configuration asks for.
+// The reference has no decode path; this executor adds a latent-space KV cache for autoregressive decode.
 // Per block and step (B sequences in lockstep, position p = *state.pos read from device memory by every kernel, so
 // the same launch sequence - and a CUDA graph of it - serves every step):
 //

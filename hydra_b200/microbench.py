@@ -1,4 +1,4 @@
-"""Single-kernel microbenchmarks on the BASELINE configs 2 and 3 shapes (CCGQA block; RMSNorm / RoPE / SwiGLU FFN)
+"""Single-kernel microbenchmarks on the shapes of the two microbenchmark configurations (CCGQA block; RMSNorm / RoPE / SwiGLU FFN)
 and on the GEMM shapes of the 250M model.  Run through ``python bench.py --micro NAME`` (one JSON line each) - also
 the small, self-terminating command lines used for ``ncu`` captures.
 
@@ -133,7 +133,7 @@ def _attention_module(dim=1024, H=8, KV=2, S=2048, temperature=1.0):
 
 
 def ccgqa_block(args) -> dict:
-    """BASELINE config 2: one CCGQA attention block, B=8 x S=2048 x dim 1024, 8q/2kv heads of 32, bf16, causal,
+    """One CCGQA attention block, B=8 x S=2048 x dim 1024, 8q/2kv heads of 32, bf16, causal,
     Xavier-uniform weights (seed 1), key temperature 1.0.  46.51 GFLOP and 68.9 MB of minimum traffic per call."""
     B, S, D = args.batch, 2048, 1024
     m = _attention_module()

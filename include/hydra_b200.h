@@ -247,8 +247,8 @@ int hb200_ccgqa_forward(const hb200_model* m, int block_index, const void* x, vo
 
 /* ---------------------------------------------------------------------------
  * Cached (incremental) decode.  The reference has no KV cache and no decode path: its generation helper
- * re-runs the whole forward for every token (diagnostics/eval_checkpoint.py:127-160).  These entry points add the
- * latent-space KV cache that BASELINE's decode configuration describes.  With MoD capacity 1.0 a cached step
+ * re-runs the whole forward for every token (diagnostics/eval_checkpoint.py:127-160).  These entry points add a
+ * latent-space KV cache for autoregressive decode.  With MoD capacity 1.0 a cached step
  * computes exactly what a re-forward computes for the newest position; with capacity < 1 a past token's MoD
  * selection stays frozen at what it was when the token was newest (MoD's top-k over the sequence is not causal).
  * ------------------------------------------------------------------------- */

@@ -282,7 +282,7 @@ if __name__ == "__main__":
         gen_base_model("base_model_hd16.npz", vocab=384, dim=256, n_layers=3, H=4, KV=2, mlp_ratio=1.0, B=2, S=112, seed=8)
         sys.exit(0)
     gen_fused_ops()
-    # config-2 shapes (dim 1024, 8q/2kv, hd 32) at a short sequence; temperature 1.0 as BASELINE config 2
+    # config-2 shapes (dim 1024, 8q/2kv, hd 32) at a short sequence; temperature 1.0 as in the CCGQA block microbenchmark
     gen_attention("ccgqa_hd32.npz", 1024, 8, 2, 1, 80, seed=1, temperature=1.0)
     # config-1 shapes (dim 512, 8q/2kv, hd 16), default temperature sqrt(hd)
     gen_attention("ccgqa_hd16.npz", 512, 8, 2, 2, 72, seed=3)

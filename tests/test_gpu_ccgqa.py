@@ -159,7 +159,7 @@ def test_module_through_factory_matches_reference_output(name):
 
 
 def test_config2_block_batch_independence_and_determinism():
-    """BASELINE config 2 (B=8, S=2048, dim 1024, 8q/2kv, hd 32, temperature 1.0) is too large for the CPU oracle in
+    """The CCGQA block microbenchmark shape (B=8, S=2048, dim 1024, 8q/2kv, hd 32, temperature 1.0) is too large for the CPU oracle in
     a unit test; check size-independent properties instead: running the batch equals running each sequence alone
     (bit-exact: no kernel mixes sequences), a causal prefix is unchanged by what follows it, and two runs agree
     bit for bit."""

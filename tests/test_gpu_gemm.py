@@ -111,7 +111,7 @@ def test_tcgen05_agrees_with_mma_sync_kernel(L):
 
 
 def test_full_size_linearity_property(L):
-    """BASELINE config-4 sized MLP contraction (65536 x 5632 x 1024 is too slow for a CPU oracle): check the
+    """The 250M prefill's MLP contraction (65536 x 5632 x 1024 is too slow for a CPU oracle): check the
     size-independent property (A1 + A2) W^T == A1 W^T + A2 W^T on rows sampled across all tiles, and that
     duplicated rows give identical outputs wherever they sit in the M dimension."""
     M, N, K = 65536, 5632, 1024

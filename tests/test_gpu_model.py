@@ -148,7 +148,7 @@ def test_gemm_implementations_agree_on_the_model():
 
 @pytest.mark.parametrize("nb,label", [(2, "config1 (2 blocks, no MoD)"), (4, "config1b (4 blocks, MoD in 1-2)")])
 def test_config1_debug_variant_against_oracle(nb, label):
-    """BASELINE config 1: dim 512, 2x2 (and the 4-block variant that carries MoD), vocab 50257, 8q/2kv, hd 16,
+    """The debug-variant configuration: dim 512, 2x2 (and the 4-block variant that carries MoD), vocab 50257, 8q/2kv, hd 16,
     F 1536, batch 4 x 512, seed 0, seeded random-init weights with the reference's distributions."""
     cfg = O.HydraConfig(vocab_size=50257, dim=512, n_mor_blocks=nb, recursions_per_block=2, n_heads=8, n_kv_heads=2,
                         max_seq_len=512, mod_capacity=0.75)
@@ -190,7 +190,7 @@ def test_ragged_batch_and_sequence_sizes(B, S):
 
 
 def test_batch_independence_determinism_and_sharding_250m():
-    """BASELINE config 4 architecture (dim 1024, 10x4, 8q/2kv, F 2816, MoD 0.75, S 2048) at batch 4: properties that
+    """The 250M prefill architecture (dim 1024, 10x4, 8q/2kv, F 2816, MoD 0.75, S 2048) at batch 4: properties that
     hold at any size - two runs agree bit for bit, a sequence run alone equals the same sequence inside the batch
     (this is what makes batch sharding across GPUs exact), MoD counts are consistent."""
     cfg = O.HydraConfig(vocab_size=50257, dim=1024, n_mor_blocks=10, recursions_per_block=4, n_heads=8, n_kv_heads=2,
