@@ -379,7 +379,9 @@ class HydraB200Model:
             self._profile = None
 
     def read_profile(self, reset: bool = True) -> List[dict]:
-        """After a synchronise: one dict per recorded launch (kind, block, rec, m, n, k, ms)."""
+        """One dict per recorded launch (kind, block, rec, m, n, k, ms); waits for the device first (the events of the
+        last launches must have completed before their times can be read)."""
+        torch.cuda.synchronize(self.device)
         cap = self._profile_cap
         recs = (_lib.LaunchRecord * cap)()
         ms = (C.c_float * cap)()
