@@ -29,7 +29,7 @@ namespace hb200 {
 
 constexpr int GBM = 128;            // tile rows  (UMMA M)
 constexpr int GBK = 64;             // K per stage = one 128-byte swizzle span of bf16
-constexpr int GROUP_M = 16;         // m-tiles per rasterisation group (keeps an A panel L2-resident)
+constexpr int GROUP_M_DEFAULT = 16; // m-tiles per rasterisation group (keeps an A panel L2-resident)
 constexpr int EPI_WARPS = 8;        // two per TMEM lane quadrant
 constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;
 
@@ -48,12 +48,12 @@ template <int BN, int NSTAGES = 0> struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + BAR_BYTES + 1024;   // + alignment slack
 };
 
-// tile index -> (m_tile, n_tile): groups of GROUP_M m-tiles, n outer / m inner inside a group
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
-  const int per_group = GROUP_M * n_tiles;
+// tile index -> (m_tile, n_tile): groups of group_m m-tiles, n outer / m inner inside a group
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int& mt, int& nt) {
+  const int per_group = group_m * n_tiles;
   const int grp = tile / per_group;
-  const int first_m = grp * GROUP_M;
-  const int gm = min(GROUP_M, m_tiles - first_m);
+  const int first_m = grp * group_m;
+  const int gm = min(group_m, m_tiles - first_m);
   const int in = tile - grp * per_group;
   nt = in / gm;
   mt = first_m + in % gm;
@@ -63,7 +63,7 @@ template <int BN, int NSTAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_SM)) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                               const __grid_constant__ CUtensorMap tma_b,
                                                               const __grid_constant__ CUtensorMap tma_c,
-                                                              const GemmParams p) {
+                                                              const GemmParams p, const int group_m) {
   using Cfg = GemmCfg<BN, NSTAGES>;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (s_addr(smem_dyn) + 1023u) & ~1023u;
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         int mt, nt;
-        tile_coords(tile, m_tiles, n_tiles, mt, nt);
+        tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       int mt, nt;
-      tile_coords(tile, m_tiles, n_tiles, mt, nt);
+      tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
       const int m = mt * GBM + quad * 32 + lane;
       // Read-modify-write epilogues (residual, scatter-add).  The accumulator comes out of TMEM with thread = row, but
       // rows are 2 KB or more apart in memory, so row-per-thread 16-byte accesses would touch 32 partial sectors per
@@ -346,7 +346,12 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
   }
   const int64_t tiles = (int64_t)ceil_div(p.M, GBM) * ceil_div(p.N, BN);
   const int grid = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * Cfg::CTAS_PER_SM);
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, tc, p);
+  // Rasterisation group: the weight matrix is re-streamed once per group of m-tiles, so when it is too large to
+  // stay in L2 next to the output stream (the vocabulary projection: 103 MB) a taller group cuts its HBM re-reads;
+  // the group's A panel (group_m x 128 rows x K) must itself stay L2-resident (<= 16 MB).
+  int group_m = GROUP_M_DEFAULT;
+  if ((size_t)p.N * p.K * 2 > (size_t)48 << 20) group_m = (int)std::max<size_t>(16, std::min<size_t>(64, ((size_t)16 << 20) / ((size_t)GBM * p.K * 2)));
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, tc, p, group_m);
   HB_LAUNCH_CHECK();
   return 0;
 }
