@@ -325,11 +325,7 @@ static int launch_att(const void* q, const void* k, const void* v, const AttPara
   HB_PROPAGATE(make_rows_map(&tk, k, (uint64_t)B * p.KV * p.S, HD));
   HB_PROPAGATE(make_rows_map(&tv, v, (uint64_t)B * p.KV * p.S, HD));
   auto kern = attention_tcgen05_kernel<HD>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-    attr_set = true;
-  }
+  HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(Cfg::SMEM_BYTES)));
   dim3 grid((p.S + AQ - 1) / AQ, p.H, B);
   kern<<<grid, ATT_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
   HB_LAUNCH_CHECK();

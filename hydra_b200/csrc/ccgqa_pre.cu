@@ -310,11 +310,7 @@ static int launch_pre(const PreParams& p, cudaStream_t st) {
   constexpr size_t smem = (size_t)(XR + YR) * LDX * 2 + (size_t)2 * WROWS * WLD * 2 + (size_t)TT * (KVD + 4) * 4;
   static_assert(smem <= 227 * 1024, "tile does not fit in shared memory");
   auto kern = ccgqa_pre_kernel<HD, NTQ, NTK, TT, KC>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_set = true;
-  }
+  HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)((int)smem)));
   const int tiles = p.B * ((p.S + TT - 1) / TT);
   kern<<<tiles, 256, smem, st>>>(p);
   HB_LAUNCH_CHECK();

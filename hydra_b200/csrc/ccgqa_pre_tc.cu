@@ -433,19 +433,11 @@ int launch_ccgqa_pre_tc(const void* qkv, const void* w1_qk, const void* w2_q, co
   const int tiles = B * ((S + TT - 1) / TT);
   if (hd == 32) {
     auto kern = ccgqa_pre_tc_kernel<32>;
-    static bool attr_set = false;
-    if (!attr_set) {
-      HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_set = true;
-    }
+    HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(SMEM_BYTES)));
     kern<<<tiles, 256, SMEM_BYTES, st>>>(tq, tk, p);
   } else {
     auto kern = ccgqa_pre_tc_kernel<16>;
-    static bool attr_set = false;
-    if (!attr_set) {
-      HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_set = true;
-    }
+    HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(SMEM_BYTES)));
     kern<<<tiles, 256, SMEM_BYTES, st>>>(tq, tk, p);
   }
   HB_LAUNCH_CHECK();

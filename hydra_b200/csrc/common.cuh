@@ -94,6 +94,10 @@ inline int launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
 }
 #endif
 
+// Raises a kernel's dynamic shared memory limit to at least `bytes` on the current device (the attribute is a
+// per-device property of the kernel; the sizes already set are remembered per (kernel, device)).  Defined in api.cu.
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }

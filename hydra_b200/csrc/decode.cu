@@ -358,11 +358,7 @@ static int launch_decode_attention(const __nv_bfloat16* qnew, const __nv_bfloat1
                                    __nv_bfloat16* o, const int32_t* pos, int B, int H, int KV, int capacity, float scale,
                                    cudaStream_t st, bool chain) {
   const size_t smem = decode_attention_smem(HD, H / KV, capacity);
-  static size_t attr_bytes = 0;
-  if (smem > attr_bytes) {
-    HB_CUDA(cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_bytes = smem;
-  }
+  HB_PROPAGATE(ensure_dynamic_smem((const void*)decode_attention_kernel<HD>, smem));
   return launch_chained(decode_attention_kernel<HD>, dim3(KV, B), dim3(DATT_THREADS), smem, st, chain, 1, qnew, kc, vc, o,
                         pos, H, KV, capacity, scale * 1.4426950408889634f);
 }

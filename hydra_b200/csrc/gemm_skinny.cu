@@ -280,11 +280,7 @@ int launch_gemm_skinny(const GemmParams& p, cudaStream_t st, bool chained) {
   const int a_rows = p.M <= 64 ? 64 : SK_BM;
   HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, (uint32_t)a_rows));
   HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, (uint32_t)s.bn));
-  static bool attr_set = false;
-  if (!attr_set) {
-    HB_CUDA(cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_BYTES));
-    attr_set = true;
-  }
+  HB_PROPAGATE(ensure_dynamic_smem((const void*)gemm_skinny_kernel, (size_t)(SK_SMEM_BYTES)));
   return launch_chained(gemm_skinny_kernel, dim3((unsigned)(s.n_tiles * s.ksplit)), dim3(SK_THREADS), SK_SMEM_BYTES, st,
                         chained, s.ksplit, ta, tb, p, s.bn, a_rows, s.ksplit, s.kb_per, s.k_blocks);
 }

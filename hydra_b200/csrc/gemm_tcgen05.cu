@@ -339,11 +339,7 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
     tc = ta;   // unused by the direct epilogues
   }
   auto kern = gemm_tcgen05_kernel<BN, NSTAGES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    HB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-    attr_set = true;
-  }
+  HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(Cfg::SMEM_BYTES)));
   const int64_t tiles = (int64_t)ceil_div(p.M, GBM) * ceil_div(p.N, BN);
   const int grid = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * Cfg::CTAS_PER_SM);
   // Rasterisation group: the weight matrix is re-streamed once per group of m-tiles, so when it is too large to

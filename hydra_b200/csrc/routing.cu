@@ -173,11 +173,7 @@ int launch_mod_select(const float* scores, int B, int L, int k, int32_t* idx_out
   const size_t smem = (size_t)L * sizeof(uint32_t);
   HB_REQUIRE(smem <= 200 * 1024, HB200_ERR_UNSUPPORTED, "mod_topk_select: sequence length %d too long (max 51200)", L);
   if (smem > 48 * 1024) {
-    static bool attr_set = false;   // benign race: the attribute is idempotent
-    if (!attr_set) {
-      HB_CUDA(cudaFuncSetAttribute(mod_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      attr_set = true;
-    }
+    HB_PROPAGATE(ensure_dynamic_smem((const void*)mod_select_kernel, (size_t)(200 * 1024)));
   }
   mod_select_kernel<<<B, 1024, smem, st>>>(scores, L, k, idx_out, depth, min_active, rows_out, count, forced_idx);
   HB_LAUNCH_CHECK();
