@@ -129,6 +129,35 @@ def test_attention_core(L, hd, H, KV, S, bounded):
     assert rel_l2(o, ref) < 5e-3
 
 
+def test_attention_core_long_sequence_two_kernels_agree(L):
+    """S = 8192 (the reference's default max_seq_len; 64 key tiles per query tile) is beyond what the CPU oracle finishes
+    in seconds: the tcgen05 kernel (bounded softmax) and the independent mma.sync kernel (online softmax) must agree, the
+    first rows must match the oracle computed on a prefix (causality), and the first row must equal the first value."""
+    hd, H, KV, S, B = 32, 8, 2, 8192, 1
+    g = torch.Generator().manual_seed(11)
+    q = bf16_round(torch.nn.functional.normalize(torch.randn(B, H, S, hd, generator=g), dim=-1))
+    k = bf16_round(torch.nn.functional.normalize(torch.randn(B, KV, S, hd, generator=g), dim=-1) * math.sqrt(hd))
+    v = bf16_round(torch.randn(B, KV, S, hd, generator=g))
+    qc, kc, vc = (t.to(torch.bfloat16).cuda().contiguous() for t in (q, k, v))
+    outs = []
+    for bound in (1.02, 0.0):
+        o = torch.full((B, S, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        L.check(L.lib().hb200_attention_causal_gqa(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), B, S, H, KV,
+                                                   hd, 1.0 / math.sqrt(hd), bound, err.data_ptr(),
+                                                   torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0 and torch.isfinite(o.float()).all()
+        outs.append(o.float().cpu())
+    assert rel_l2(outs[0], outs[1]) < 5e-3
+    P = 384                                                  # causal: the first P rows only see the first P keys
+    ref = O.causal_gqa_attention(q[:, :, :P], k[:, :, :P], v[:, :, :P]).transpose(1, 2).reshape(B, P, H * hd)
+    for o in outs:
+        assert_close_bf16(o[:, :P], ref, ulps=1.5, floor_frac=1.0, what="attention S=8192 prefix")
+        first = v[:, :, 0].repeat_interleave(H // KV, dim=1).reshape(B, H * hd)
+        assert torch.equal(o[:, 0], first)                   # one key: the output is that key's value
+
+
 @pytest.mark.parametrize("name", FIXTURES)
 def test_module_through_factory_matches_reference_output(name):
     """build_hybrid_attention_module -> load the reference state_dict -> forward, against the reference's own fp32

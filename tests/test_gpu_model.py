@@ -189,6 +189,24 @@ def test_ragged_batch_and_sequence_sizes(B, S):
     assert agree >= 0.97 or B * S < 40
 
 
+def test_long_sequence_beyond_one_select_pass():
+    """S = 4100: 33 attention tiles, MoD top-k over 4100 scores (k = 3075), conv tiles with a ragged tail."""
+    cfg = O.HydraConfig(vocab_size=1000, dim=256, n_mor_blocks=3, recursions_per_block=2, n_heads=4, n_kv_heads=2,
+                        max_seq_len=4224, mod_capacity=0.75)
+    w = O.init_params(cfg, seed=9, perturb=True)
+    ids = torch.randint(0, 1000, (1, 4100), generator=torch.Generator().manual_seed(4))
+    m = build(w, cfg)
+    lg = m(ids.cuda(), taps=True).float().cpu()
+    m.check_device_errors()
+    rt = taps_to_oracle(m, m.last_taps, 1, 4100)
+    ref = O.model_forward(ids, w, cfg, forced=rt)
+    assert torch.isfinite(lg).all() and rel_l2(lg, ref) <= 1e-2
+    idx = m.last_taps.mod_idx.cpu().long()[1, 0]
+    assert idx.shape == (1, O.mod_k(4100, 0.75))
+    sc = m.last_taps.mod_scores.cpu().view(3, 2, 1, 4100)
+    assert torch.equal(idx, O.mod_select(sc[1, 0], 0.75))
+
+
 def test_batch_independence_determinism_and_sharding_250m():
     """The 250M prefill architecture (dim 1024, 10x4, 8q/2kv, F 2816, MoD 0.75, S 2048) at batch 4: properties that
     hold at any size - two runs agree bit for bit, a sequence run alone equals the same sequence inside the batch
