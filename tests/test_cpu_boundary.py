@@ -32,6 +32,9 @@ def test_struct_layouts_match_header_sizes():
     assert ctypes.sizeof(_lib.Model) == 12 * 4 + 4 * 4 + 6 * 8
     assert ctypes.sizeof(_lib.Taps) == 6 * 8 + 8
     assert ctypes.sizeof(_lib.LaunchRecord) == 24
+    assert ctypes.sizeof(_lib.DecodeState) == 2 * 4 + 8 * 8    # batch, capacity, eight device pointers
+    assert [f[0] for f in _lib.DecodeState._fields_] == ["batch", "capacity", "kcache", "vcache", "halo", "vshift",
+                                                         "scores", "pos", "tokens", "history"]
 
 
 def test_host_side_argument_validation_without_a_gpu():
