@@ -39,9 +39,13 @@ template <int BN, int NSTAGES = 0> struct GemmCfg {
   static constexpr int A_BYTES = GBM * GBK * 2;
   static constexpr int B_BYTES = BN * GBK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = NSTAGES > 0 ? NSTAGES : ((BN == 256) ? 4 : 6);
+  static constexpr int STAGES = NSTAGES > 0 ? NSTAGES : ((BN == 384) ? 3 : ((BN == 256) ? 4 : 6));
   static constexpr int CTAS_PER_SM = (NSTAGES > 0 && NSTAGES <= 2 && BN == 128) ? 2 : 1;
-  static constexpr int TMEM_COLS = 2 * BN;
+  // 384-wide tiles (a whole qkv projection row block: A is fetched once instead of three times) fill most of TMEM,
+  // so they run with a single accumulator; narrower tiles double-buffer it
+  static constexpr int ACCS = (BN == 384) ? 1 : 2;
+  static constexpr int TMEM_COLS = (BN == 384) ? 512 : 2 * BN;
+  static constexpr int B_BOX_ROWS = (BN > 256) ? 128 : BN;             // a TMA box holds at most 256 rows
   static constexpr int BAR_BYTES = 256;
   static constexpr int STORE_BOX_BYTES = 32 * 128;                 // one TMA store box: 32 rows x 64 bf16
   static constexpr int STORE_BYTES = EPI_WARPS * STORE_BOX_BYTES;  // one staging box per epilogue warp
@@ -91,7 +95,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < Cfg::ACCS; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), EPI_WARPS);
     }
@@ -118,7 +122,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
           const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
           mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
           tma_load_2d(sa, &tma_a, kb * GBK, mt * GBM, full_bar(stage));
-          tma_load_2d(sa + Cfg::A_BYTES, &tma_b, kb * GBK, nt * BN, full_bar(stage));
+#pragma unroll
+          for (int bb = 0; bb < BN / Cfg::B_BOX_ROWS; ++bb)
+            tma_load_2d(sa + Cfg::A_BYTES + bb * Cfg::B_BOX_ROWS * GBK * 2, &tma_b, kb * GBK,
+                        nt * BN + bb * Cfg::B_BOX_ROWS, full_bar(stage));
           if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -127,7 +134,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(GBM, BN);
+      constexpr uint32_t idesc = make_idesc(GBM, BN > 256 ? 256 : BN);
+      constexpr uint32_t idesc_tail = make_idesc(GBM, BN > 256 ? BN - 256 : 16);   // columns beyond one MMA's 256
       int stage = 0, as = 0;
       uint32_t phase = 0, aphase = 0;
       bool ok = true;
@@ -145,13 +153,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
           for (int k = 0; k < GBK / 16; ++k) {
             // advance 16 elements (32 bytes) along K inside the swizzle span: +2 in 16-byte units
             umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) ? 1u : 0u);
+            if constexpr (BN > 256) {
+              // B rows 256.. start 256 rows x 128 bytes further on; their accumulator columns follow the first 256
+              const uint64_t db_tail = make_smem_desc(sa + Cfg::A_BYTES + 256 * GBK * 2);
+              umma_bf16(d_tmem + 256u, da + 2u * k, db_tail + 2u * k, idesc_tail, (kb | k) ? 1u : 0u);
+            }
           }
           umma_commit(empty_bar(stage));   // stage reusable once these MMAs have read it
           if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         umma_commit(tfull_bar(as));        // accumulator complete
-        if (++as == 2) { as = 0; aphase ^= 1u; }
+        if (++as == Cfg::ACCS) { as = 0; aphase ^= 1u; }
       }
     }
     __syncwarp();
@@ -304,7 +317,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(as));
-      if (++as == 2) { as = 0; aphase ^= 1u; }
+      if (++as == Cfg::ACCS) { as = 0; aphase ^= 1u; }
     }
     if (lane == 0) bulk_wait0();   // this thread's bulk stores have completed before the CTA may exit
     __syncwarp();
@@ -330,7 +343,7 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
   using Cfg = GemmCfg<BN, NSTAGES>;
   CUtensorMap ta, tb, tc;
   HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, GBM));
-  HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, BN));
+  HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, Cfg::B_BOX_ROWS));
   if (p.epilogue == EPI_STORE || p.epilogue == EPI_SWIGLU) {
     // output map for the staged TMA-store epilogue: boxes of 32 rows x 64 columns, clipped at [M, n_out]
     const uint64_t n_out = p.epilogue == EPI_SWIGLU ? (uint64_t)p.N / 2 : (uint64_t)p.N;
@@ -355,6 +368,9 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
 int launch_gemm_tcgen05(const GemmParams& p, cudaStream_t st) {
   // wide tiles unless N is a small multiple of 128 (qkv projection: 384); the SwiGLU epilogue pairs columns inside
   // 128-column halves of a 256-wide tile and always takes the wide kernel
+  // a 384-column projection (qkv of the 8q/2kv and 16q/4kv shapes at latent 256) as one tile per row block: the A
+  // panel is fetched once instead of once per 128-column tile
+  if (p.epilogue == EPI_STORE && p.N == 384) return launch_bn<384>(p, st);
   if (p.epilogue != EPI_SWIGLU && p.N % 256 != 0 && p.N % 128 == 0 && p.N <= 1024) return launch_bn<128>(p, st);
   // short K with a read-modify-write epilogue (o_proj + residual): the epilogue dominates, so run two narrower CTAs
   // per SM (2 x 256 TMEM columns, 2 x 97 KB of shared memory) and let their epilogues overlap
