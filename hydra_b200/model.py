@@ -490,7 +490,7 @@ class DecodeSession:
     def prefill(self, prompt_ids: Tensor) -> None:
         m = self.model
         B, P = prompt_ids.shape
-        if B != self.batch or P < 1 or P >= self.capacity + 1:
+        if B != self.batch or P < 1 or P > self.capacity:
             raise ValueError(f"prompt shape {tuple(prompt_ids.shape)} does not fit batch {self.batch} / capacity {self.capacity}")
         ids = prompt_ids.contiguous()
         ws = m.packed.workspace(B, P)
