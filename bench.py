@@ -135,7 +135,8 @@ def run_reference(args) -> None:
     cfg = workload_config(args.batch, args.gpus)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": getattr(args, "scaling_mode", "weak"),
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
         "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
                          "sample": f"{n_seq} sequence x {SEQ} tokens of the same workload per step "
@@ -283,7 +284,8 @@ def run_ours(args) -> None:
         routed_per_token = all_gemm_fl / (T * K)
         line = {
             "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": getattr(args, "scaling_mode", "weak"),
+            "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(B, world),
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": world * B * SEQ * 8,
                     "d2h_bytes_per_step": world * B * ARCH["vocab_size"] * 2, "ms_per_step": ms_e2e / K,
@@ -320,6 +322,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=32, help="sequences per GPU")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                    help="weak (default): --batch sequences on every GPU; strong: --batch sequences in total, split over the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--micro", default=None, help="run one single-kernel microbenchmark instead of the model "
                     "(gemm, ccgqa_block, pre_attention, attention, rms_norm, rope, swiglu_ffn, swiglu_act, model_hidden, decode)")
@@ -344,6 +348,12 @@ def main() -> None:
         for nm in names:
             print(json.dumps(microbench.run(nm, args, ROOT)), flush=True)
         return
+    args.scaling_mode = args.scaling
+    if args.scaling == "strong":
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if args.batch % world != 0:
+            sys.exit(f"--scaling strong needs --batch ({args.batch}) divisible by the number of ranks ({world})")
+        args.batch //= world
     if args.impl == "reference":
         run_reference(args)
     else:
