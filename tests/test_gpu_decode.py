@@ -134,6 +134,15 @@ def test_equal_head_counts_and_batch_beyond_one_row_tile():
     check_against_oracle(build(w, cfg), w, cfg, prompt, 5, "MHA, B=37")
 
 
+def test_odd_kv_head_count_value_shift_split_inside_a_head():
+    """12 query / 3 KV heads of 16: the value-shift boundary (kv_dim / 2 = 24 channels) falls inside the second KV head."""
+    cfg = O.HydraConfig(vocab_size=500, dim=768, n_mor_blocks=3, recursions_per_block=2, n_heads=12, n_kv_heads=3,
+                        max_seq_len=96, mod_capacity=0.75)
+    w = O.init_params(cfg, seed=13, perturb=True)
+    prompt = torch.randint(0, 500, (2, 41), generator=torch.Generator().manual_seed(6))
+    check_against_oracle(build(w, cfg), w, cfg, prompt, 6, "12q/3kv")
+
+
 def test_session_errors():
     fx, cfg, w = G.model_fixture("model_hd16.npz")
     m = build(w, cfg)
