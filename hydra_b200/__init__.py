@@ -6,7 +6,9 @@ Public surface (mirrors the reference's names for this path):
   kernel-status helpers (reference: ``hydra.kernels``)
 * ``hydra_b200.attention`` - ``build_hybrid_attention_module``, registry helpers, ``CCGQAAttention``
   (reference: ``hydra.attention``)
-* ``hydra_b200.model``     - ``HydraB200Model``: whole-model eval forward from a reference ``state_dict``
+* ``hydra_b200.model``     - ``HydraB200Model`` (whole-model eval forward from a reference ``state_dict``, greedy
+  generation by re-forward or with a latent-space KV cache), ``HydraB200BaseModel`` (the routing-free baseline),
+  ``load_checkpoint``
 * ``hydra_b200.install``   - ``install()`` rebinds the reference's module-level names to this package
 
 All compute runs in the CUDA extension ``libhydra_b200.so`` (C ABI in ``include/hydra_b200.h``); there is no
