@@ -126,6 +126,30 @@ def cpu_forward_tokens_per_s(n_seq: int, steps: int, warmup: int, state_dict=Non
     return n_seq * SEQ / dt, dt, threads
 
 
+def cpu_generation_baseline(blocks: int, prompt: int) -> dict:
+    """What the reference does to generate one token (its helper re-runs the whole forward on the sequence so far,
+    diagnostics/eval_checkpoint.py:127-160), timed with the oracle port on the host cores at the 1.5B shape:
+    one eval forward of one sequence of `prompt` tokens, and one cached step of the oracle's own decode for comparison."""
+    from oracle import hydra_oracle as O
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(threads)
+    cfg = O.HydraConfig(vocab_size=50257, dim=2048, n_mor_blocks=blocks, recursions_per_block=4, n_heads=32, n_kv_heads=4,
+                        max_seq_len=prompt + 8, mod_capacity=0.75)
+    w = O.init_params(cfg, seed=SEED)
+    ids = torch.randint(0, 50257, (1, prompt), generator=torch.Generator().manual_seed(SEED))
+    with torch.no_grad():
+        t0 = time.perf_counter()
+        logits, cache = O.cached_prefill(ids, w, cfg)
+        t_forward = time.perf_counter() - t0
+        nxt = logits[:, -1].argmax(-1)
+        t0 = time.perf_counter()
+        O.cached_decode_step(nxt, w, cfg, cache)
+        t_step = time.perf_counter() - t0
+    return {"value": 1.0 / t_forward, "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"1 sequence, {blocks} blocks: one eval forward of {prompt} tokens = the reference's cost of one generated "
+                      f"token ({t_forward:.2f} s); one cached step of the CPU port: {t_step * 1e3:.0f} ms"}
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -346,7 +370,10 @@ def main() -> None:
         args.impl = args.impl_gemm
         names = [n for n in microbench.CASES if n not in ("model_hidden", "decode", "gemm_skinny")] if args.micro == "all" else [args.micro]
         for nm in names:
-            print(json.dumps(microbench.run(nm, args, ROOT)), flush=True)
+            res = microbench.run(nm, args, ROOT)
+            if nm == "decode" and not args.no_cpu_baseline:
+                res["cpu_baseline"] = cpu_generation_baseline(args.blocks, args.prompt)
+            print(json.dumps(res), flush=True)
         return
     args.scaling_mode = args.scaling
     if args.scaling == "strong":
