@@ -135,6 +135,22 @@ __device__ __forceinline__ void load_bf16x8(const __nv_bfloat16* p, float (&f)[8
     f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
   }
 }
+// Loads that bypass L1 (ld.global.cg).  Kernels of a programmatic-dependent-launch chain start before their
+// predecessor has finished, so the L1 invalidation of a kernel boundary no longer separates a predecessor's reads of a
+// buffer from a later kernel's reads of the same buffer after another SM rewrote it: everything such kernels read
+// that other kernels of the chain write goes through L2.
+__device__ __forceinline__ void load_bf16x8_cg(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ float ldcg_bf16(const __nv_bfloat16* p) {
+  return __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(p)) << 16);
+}
 __device__ __forceinline__ uint32_t pack_bf16x2_rn(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);

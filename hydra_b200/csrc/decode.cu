@@ -88,12 +88,13 @@ __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
   float* y1 = smem_f + 5 * C;     // [3][C]: positions p-2 .. p
   const int b = blockIdx.x, tid = threadIdx.x;
   if (b == 0 && tid == 0) *first_count = 0;   // row counter of this block's first recursion (see decode_route_kernel)
-  const int pos = *pos_ptr;
+  const int pos = __ldcg(pos_ptr);
   if (pos >= capacity) return;    // cache full: the step is a no-op (the host checks capacity before launching)
   __nv_bfloat16* hb = halo + (size_t)b * 4 * C;
   const __nv_bfloat16* row = qkv + (size_t)b * qkv_ld;
-  for (int i = tid; i < 4 * C; i += 256) win[i] = __bfloat162float(hb[i]);
-  for (int c = tid; c < C; c += 256) win[4 * C + c] = __bfloat162float(row[c]);
+  // (everything other kernels of the chain write is read through L2, see load_bf16x8_cg)
+  for (int i = tid; i < 4 * C; i += 256) win[i] = ldcg_bf16(hb + i);
+  for (int c = tid; c < C; c += 256) win[4 * C + c] = ldcg_bf16(row + c);
   __syncthreads();
   // grouped conv1 (kernel 3, causal) on rows 2..4 of the window; rounded to bf16 like the prefill's y1 tile.
   // One thread per output channel: its weight row (3 taps x hd inputs, 16-byte loads) serves all three positions.
@@ -131,7 +132,8 @@ __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
     }
   }
   for (int c = tid; c < kvd; c += 256) {
-    const __nv_bfloat16 val = (c < half) ? row[C + c] : vshift[(size_t)b * half + (c - half)];
+    const __nv_bfloat16 val =
+        __float2bfloat16_rn((c < half) ? ldcg_bf16(row + C + c) : ldcg_bf16(vshift + (size_t)b * half + (c - half)));
     vcache[(((size_t)b * KV + c / hd) * capacity + pos) * hd + (c % hd)] = val;
   }
   __syncthreads();
@@ -144,7 +146,7 @@ __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
   }
   // advance the halo (drop the oldest row) and the v_shift half
   for (int i = tid; i < 4 * C; i += 256) hb[i] = __float2bfloat16_rn(win[C + i]);
-  for (int c = tid; c < half; c += 256) vshift[(size_t)b * half + c] = row[C + half + c];
+  for (int c = tid; c < half; c += 256) vshift[(size_t)b * half + c] = __float2bfloat16_rn(ldcg_bf16(row + C + half + c));
 }
 
 // ---- QK finish: one CTA per sequence, one warp per head ----------------------------------------------------------
@@ -156,7 +158,7 @@ __global__ void __launch_bounds__(256) decode_qk_finish_kernel(
   const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   chain_release();
   chain_wait();
-  const int pos = *pos_ptr;
+  const int pos = __ldcg(pos_ptr);
   if (pos >= capacity) return;
   const int lat = H * hd, kvd = KV * hd, qkv_ld = lat + 2 * kvd;
   const bool same_heads = (H == KV);
@@ -165,7 +167,7 @@ __global__ void __launch_bounds__(256) decode_qk_finish_kernel(
   extern __shared__ float smem_f[];
   float* a_row = smem_f;                 // [3 * kvd]
   float* c2k = smem_f + 3 * kvd;         // [kvd]
-  for (int i = threadIdx.x; i < 3 * kvd; i += 256) a_row[i] = __bfloat162float(ak[(size_t)b * 3 * kvd + i]);
+  for (int i = threadIdx.x; i < 3 * kvd; i += 256) a_row[i] = ldcg_bf16(ak + (size_t)b * 3 * kvd + i);
   __syncthreads();
   for (int n = threadIdx.x; n < kvd; n += 256) {
     const __nv_bfloat16* wr = w2k + (size_t)n * 3 * kvd;
@@ -190,15 +192,15 @@ __global__ void __launch_bounds__(256) decode_qk_finish_kernel(
       float c0, c1;
       if (same_heads) {   // one query head per kv head: both sides couple with 0.5 * (q0 + k0) of that head
         const __nv_bfloat16* row = qkv + (size_t)b * qkv_ld;
-        c0 = 0.5f * (__bfloat162float(row[h * hd + d0]) + __bfloat162float(row[lat + h * hd + d0]));
-        c1 = 0.5f * (__bfloat162float(row[h * hd + d0 + 1]) + __bfloat162float(row[lat + h * hd + d0 + 1]));
+        c0 = 0.5f * (ldcg_bf16(row + h * hd + d0) + ldcg_bf16(row + lat + h * hd + d0));
+        c1 = 0.5f * (ldcg_bf16(row + h * hd + d0 + 1) + ldcg_bf16(row + lat + h * hd + d0 + 1));
       } else {            // otherwise with half the head-mean of the other side
         const float* mean = (is_k ? qm : km) + (size_t)b * hd;
-        c0 = mean[d0];
-        c1 = mean[d0 + 1];
+        c0 = __ldcg(mean + d0);
+        c1 = __ldcg(mean + d0 + 1);
       }
-      v0 = (is_k ? c2k[h * hd + d0] : __bfloat162float(conv[d0])) + c0;
-      v1 = (is_k ? c2k[h * hd + d0 + 1] : __bfloat162float(conv[d0 + 1])) + c1;
+      v0 = (is_k ? c2k[h * hd + d0] : ldcg_bf16(conv + d0)) + c0;
+      v1 = (is_k ? c2k[h * hd + d0 + 1] : ldcg_bf16(conv + d0 + 1)) + c1;
     }
     const float ss = warp_sum(v0 * v0 + v1 * v1);
     const float inv = (is_k ? *temp : 1.0f) / fmaxf(sqrtf(ss), 1e-12f);
@@ -232,13 +234,13 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
   const int G = H / KV, lat = H * HD;
   chain_release();
   chain_wait();
-  const int n_keys = min(*pos_ptr + 1, capacity);
+  const int n_keys = min(__ldcg(pos_ptr) + 1, capacity);
   float* qs = smem_f;                          // [G][HD], pre-scaled by scale * log2(e)
   float* red = qs + DATT_GMAX * HD;            // [DATT_WARPS][DATT_GMAX]
   float* part = red + DATT_WARPS * DATT_GMAX;  // [DATT_WARPS][DATT_GMAX][HD]
   float* sc = part + DATT_WARPS * DATT_GMAX * HD;   // [G][capacity]
   for (int i = tid; i < G * HD; i += DATT_THREADS)
-    qs[i] = __bfloat162float(qnew[(size_t)b * lat + (size_t)(kvh * G) * HD + i]) * scale_log2;
+    qs[i] = ldcg_bf16(qnew + (size_t)b * lat + (size_t)(kvh * G) * HD + i) * scale_log2;
   __syncthreads();
   const __nv_bfloat16* kb = kcache + ((size_t)b * KV + kvh) * capacity * HD;
   const __nv_bfloat16* vb = vcache + ((size_t)b * KV + kvh) * capacity * HD;
@@ -250,7 +252,7 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
   for (int key = tid; key < n_keys; key += DATT_THREADS) {
     float kf[HD];
 #pragma unroll
-    for (int c = 0; c < CH; ++c) load_bf16x8(kb + (size_t)key * HD + c * 8, *reinterpret_cast<float(*)[8]>(&kf[c * 8]));
+    for (int c = 0; c < CH; ++c) load_bf16x8_cg(kb + (size_t)key * HD + c * 8, *reinterpret_cast<float(*)[8]>(&kf[c * 8]));
 #pragma unroll
     for (int g = 0; g < DATT_GMAX; ++g) {
       if (g < G) {
@@ -316,7 +318,7 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
 #pragma unroll 4
   for (int key = slice; key < n_keys; key += NSLICE) {
     float vf[8];
-    load_bf16x8(vb + (size_t)key * HD + chunk * 8, vf);
+    load_bf16x8_cg(vb + (size_t)key * HD + chunk * 8, vf);
 #pragma unroll
     for (int g = 0; g < DATT_GMAX; ++g) {
       if (g < G) {
@@ -363,7 +365,7 @@ static int launch_decode_attention(const __nv_bfloat16* qnew, const __nv_bfloat1
                         pos, H, KV, capacity, scale * 1.4426950408889634f);
 }
 
-// ---- routing of the newest position + gather-norm: one warp per sequence ------------------------------------
+// ---- routing of the newest position + gather-norm: one CTA per sequence -------------------------------------
 // Per recursion r of a block, for every sequence b:
 //   router (r == 0, adaptive): depth[b] from the raw row;
 //   MoD: score s_b of AdaRMSNorm(cur_b + rec) (same formula as the prefill's score pass); "selected" iff fewer than
@@ -374,116 +376,195 @@ static int launch_decode_attention(const __nv_bfloat16* qnew, const __nv_bfloat1
 // Slots are handed out in arrival order: which slot a row gets does not change its result (rows of the two MLP
 // contractions are independent), only where it sits in the compact buffers.  *count must be zero on entry; the
 // kernel zeroes `next_count` (the counter of the following recursion) for its successor.
-template <int NCH, bool HAS_MOD, bool HAS_ROUTER>
-__global__ void __launch_bounds__(256) decode_route_kernel(
+//
+// The kernel is a latency chain, not a bandwidth problem (one 4 KB row per CTA), so it is laid out to need two
+// memory round trips: every thread owns 8 columns; the per-column vectors (static weights) are requested before
+// the wait on the predecessor, and the row piece, the position, the depth and this thread's slice of the score cache
+// (read up to the cache capacity, masked by the position afterwards) are all requested together right after it.
+constexpr int ROUTE_THREADS = 256;
+constexpr int ROUTE_CACHE_PER_THREAD = 16;     // score-cache entries per thread kept in registers: capacity <= 4096
+template <bool HAS_MOD, bool HAS_ROUTER>
+__global__ void __launch_bounds__(ROUTE_THREADS) decode_route_kernel(
     const __nv_bfloat16* __restrict__ cur, const float* __restrict__ rec, const float* __restrict__ norm2_w,
     const float* __restrict__ mod_wn, const float* __restrict__ mod_b, const float* __restrict__ mor_w,
     const float* __restrict__ mor_b, float* __restrict__ score_cache, int32_t* __restrict__ depth, int min_active,
     int32_t* __restrict__ rows, int32_t* __restrict__ count, int32_t* __restrict__ next_count,
     __nv_bfloat16* __restrict__ ug, const int32_t* __restrict__ pos_ptr, int B, int D, int capacity, float cap_ratio,
     float eps, int n_rec, int min_d) {
-  const int lane = threadIdx.x & 31;
-  const int b = blockIdx.x * 8 + (threadIdx.x >> 5);
+  __shared__ float red[ROUTE_THREADS / 32][4];
+  __shared__ int bcast[2];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = blockIdx.x;
+  const int i = tid * 8;
+  const bool have = i < D;
   chain_release();
-  chain_wait();
-  if (next_count != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *next_count = 0;
-  if (b >= B) return;
-  const int pos = *pos_ptr;
-  const bool room = pos < capacity;
-  // one pass over the row: every load (row pieces, then the per-column vectors) is issued before it is needed
-  uint4 raw[NCH];
+  // ---- static per-column vectors: independent of the predecessor
+  float rc[8], g2[8], wn[8], wr[8];
 #pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    raw[c] = (i < D) ? *reinterpret_cast<const uint4*>(cur + (size_t)b * D + i) : make_uint4(0, 0, 0, 0);
-  }
-  float v[NCH][8];
-  float ss = 0.f, dm = 0.f, lm = 0.f;
-#pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) {
-      const float4 r0 = *reinterpret_cast<const float4*>(rec + i), r1 = *reinterpret_cast<const float4*>(rec + i + 4);
-      const float rc[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-      const uint32_t w4[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
-      float x[8];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        x[2 * j] = __uint_as_float(w4[j] << 16);
-        x[2 * j + 1] = __uint_as_float(w4[j] & 0xffff0000u);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        v[c][j] = x[j] + rc[j];
-        ss += v[c][j] * v[c][j];
-      }
-      if (HAS_MOD) {
-        const float4 a0 = *reinterpret_cast<const float4*>(mod_wn + i), a1 = *reinterpret_cast<const float4*>(mod_wn + i + 4);
-        dm += v[c][0] * a0.x + v[c][1] * a0.y + v[c][2] * a0.z + v[c][3] * a0.w + v[c][4] * a1.x + v[c][5] * a1.y +
-              v[c][6] * a1.z + v[c][7] * a1.w;
-      }
-      if (HAS_ROUTER) {   // the depth router sees the raw row (no recursion offset)
-        const float4 a0 = *reinterpret_cast<const float4*>(mor_w + i), a1 = *reinterpret_cast<const float4*>(mor_w + i + 4);
-        lm += x[0] * a0.x + x[1] * a0.y + x[2] * a0.z + x[3] * a0.w + x[4] * a1.x + x[5] * a1.y + x[6] * a1.z + x[7] * a1.w;
-      }
+  for (int j = 0; j < 8; ++j) rc[j] = g2[j] = wn[j] = wr[j] = 0.f;
+  float bias_mod = 0.f, bias_mor = 0.f;
+  if (have) {
+    const float4 a0 = *reinterpret_cast<const float4*>(rec + i), a1 = *reinterpret_cast<const float4*>(rec + i + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(norm2_w + i), b1 = *reinterpret_cast<const float4*>(norm2_w + i + 4);
+    rc[0] = a0.x; rc[1] = a0.y; rc[2] = a0.z; rc[3] = a0.w; rc[4] = a1.x; rc[5] = a1.y; rc[6] = a1.z; rc[7] = a1.w;
+    g2[0] = b0.x; g2[1] = b0.y; g2[2] = b0.z; g2[3] = b0.w; g2[4] = b1.x; g2[5] = b1.y; g2[6] = b1.z; g2[7] = b1.w;
+    if (HAS_MOD) {
+      const float4 c0 = *reinterpret_cast<const float4*>(mod_wn + i), c1 = *reinterpret_cast<const float4*>(mod_wn + i + 4);
+      wn[0] = c0.x; wn[1] = c0.y; wn[2] = c0.z; wn[3] = c0.w; wn[4] = c1.x; wn[5] = c1.y; wn[6] = c1.z; wn[7] = c1.w;
+    }
+    if (HAS_ROUTER) {
+      const float4 d0 = *reinterpret_cast<const float4*>(mor_w + i), d1 = *reinterpret_cast<const float4*>(mor_w + i + 4);
+      wr[0] = d0.x; wr[1] = d0.y; wr[2] = d0.z; wr[3] = d0.w; wr[4] = d1.x; wr[5] = d1.y; wr[6] = d1.z; wr[7] = d1.w;
     }
   }
-  ss = warp_sum(ss);
-  const float ri = rsqrtf(ss / (float)D + eps);
-  int dep;
-  if (HAS_ROUTER) {
-    lm = warp_sum(lm);
-    dep = mor_depth_from_logit(lm + mor_b[0], n_rec, min_d);
-    if (lane == 0) depth[b] = dep;
-  } else {
-    dep = depth[b];
+  if (HAS_MOD) bias_mod = mod_b[0];
+  if (HAS_ROUTER) bias_mor = mor_b[0];
+  chain_wait();
+  // ---- everything that depends on earlier kernels, requested in one go
+  if (next_count != nullptr && b == 0 && tid == 0) *next_count = 0;
+  const int pos = __ldcg(pos_ptr);
+  const uint4 raw = have ? __ldcg(reinterpret_cast<const uint4*>(cur + (size_t)b * D + i)) : make_uint4(0, 0, 0, 0);
+  int dep = HAS_ROUTER ? 0 : __ldcg(depth + b);
+  float cached[ROUTE_CACHE_PER_THREAD];
+  float* sc = score_cache + (size_t)b * capacity;
+  if (HAS_MOD) {
+#pragma unroll
+    for (int q = 0; q < ROUTE_CACHE_PER_THREAD; ++q) {
+      const int idx = q * ROUTE_THREADS + tid;
+      cached[q] = (idx < capacity) ? __ldcg(sc + idx) : 0.f;   // entries at or beyond the position are masked below
+    }
   }
+  // ---- row statistics
+  float v[8], x[8];
+  {
+    const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      x[2 * j] = __uint_as_float(w4[j] << 16);
+      x[2 * j + 1] = __uint_as_float(w4[j] & 0xffff0000u);
+    }
+  }
+  float ss = 0.f, dm = 0.f, lm = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    v[j] = have ? x[j] + rc[j] : 0.f;
+    ss += v[j] * v[j];
+    if (HAS_MOD) dm += v[j] * wn[j];
+    if (HAS_ROUTER) lm += x[j] * wr[j];
+  }
+  ss = warp_sum(ss);
+  if (HAS_MOD) dm = warp_sum(dm);
+  if (HAS_ROUTER) lm = warp_sum(lm);
+  if (lane == 0) { red[warp][0] = ss; red[warp][1] = dm; red[warp][2] = lm; }
+  __syncthreads();
+  ss = dm = lm = 0.f;
+#pragma unroll
+  for (int w8 = 0; w8 < ROUTE_THREADS / 32; ++w8) { ss += red[w8][0]; dm += red[w8][1]; lm += red[w8][2]; }
+  const float ri = rsqrtf(ss / (float)D + eps);
+  if (HAS_ROUTER) dep = mor_depth_from_logit(lm + bias_mor, n_rec, min_d);
+  const bool room = pos < capacity;
   bool sel = true;
+  float s = 0.f;
   if (HAS_MOD) {
     double c = (double)cap_ratio;
     c = c < 1e-4 ? 1e-4 : (c > 1.0 ? 1.0 : c);
     int k = (int)((double)(pos + 1) * c);
     k = k < 1 ? 1 : (k > pos + 1 ? pos + 1 : k);
-    dm = warp_sum(dm);
-    const float s = ri * dm + mod_b[0];
-    float* sc = score_cache + (size_t)b * capacity;
-    int cnt = 0;
+    s = ri * dm + bias_mod;
     const int n = min(pos, capacity);
-    if ((capacity & 3) == 0) {
-      // 16-byte pieces of the cached scores, several in flight per lane; entries at or beyond n do not count
-      const float4* sc4 = reinterpret_cast<const float4*>(sc);
-      const int n4 = (n + 3) >> 2;
-#pragma unroll 4
-      for (int i = lane; i < n4; i += 32) {
-        const float4 q = sc4[i];
-        const int i0 = i * 4;
-        cnt += (q.x >= s) ? 1 : 0;
-        cnt += (i0 + 1 < n && q.y >= s) ? 1 : 0;
-        cnt += (i0 + 2 < n && q.z >= s) ? 1 : 0;
-        cnt += (i0 + 3 < n && q.w >= s) ? 1 : 0;
-      }
-    } else {
-#pragma unroll 4
-      for (int i = lane; i < n; i += 32) cnt += (sc[i] >= s) ? 1 : 0;
+    int cnt = 0;
+#pragma unroll
+    for (int q = 0; q < ROUTE_CACHE_PER_THREAD; ++q) {
+      const int idx = q * ROUTE_THREADS + tid;
+      cnt += (idx < n && cached[q] >= s) ? 1 : 0;
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
-    sel = cnt < k;
-    if (lane == 0 && room) sc[pos] = s;
-  }
-  if (!(room && sel && dep >= min_active)) return;      // warp-uniform
-  int j = 0;
-  if (lane == 0) {
-    j = atomicAdd(count, 1);
-    rows[j] = b;
-  }
-  j = __shfl_sync(0xffffffffu, j, 0);
-  scale_row<NCH>(norm2_w, ri, D, lane, v);
+    if (lane == 0) red[warp][3] = __int_as_float(cnt);
+    __syncthreads();
+    int total = 0;
 #pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int i = (c * 32 + lane) * 8;
-    if (i < D) store_bf16x8(ug + (size_t)j * D + i, v[c]);
+    for (int w8 = 0; w8 < ROUTE_THREADS / 32; ++w8) total += __float_as_int(red[w8][3]);
+    sel = total < k;
   }
+  const bool take = room && sel && dep >= min_active;
+  if (tid == 0) {
+    if (HAS_ROUTER) depth[b] = dep;
+    if (HAS_MOD && room) sc[pos] = s;
+    int j = -1;
+    if (take) {
+      j = atomicAdd(count, 1);
+      rows[j] = b;
+    }
+    bcast[0] = j;
+  }
+  __syncthreads();
+  const int j = bcast[0];
+  if (j < 0 || !have) return;
+  float o[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) o[q] = v[q] * ri * g2[q];
+  store_bf16x8(ug + (size_t)j * D + i, o);
+}
+
+// ---- block exit for one row per CTA: y = RMSNorm(src; w1) (or src if w1 == nullptr), z = RMSNorm(y; w2) --------
+// Same arithmetic as dual_norm_kernel (row kernels of the prefill), laid out for latency: every thread owns 8 columns,
+// both gain vectors are requested before the wait on the predecessor, the row piece right after it.
+__global__ void __launch_bounds__(256) decode_dual_norm_kernel(const __nv_bfloat16* __restrict__ src,
+                                                               const float* __restrict__ w1, __nv_bfloat16* __restrict__ y,
+                                                               const float* __restrict__ w2, __nv_bfloat16* __restrict__ z,
+                                                               int D, float eps) {
+  __shared__ float red[2][8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int i = tid * 8;
+  const bool have = i < D;
+  const size_t row = blockIdx.x;
+  chain_release();
+  float g1[8], g2[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) g1[j] = g2[j] = 1.f;
+  if (have) {
+    if (w1 != nullptr) {
+      const float4 a0 = *reinterpret_cast<const float4*>(w1 + i), a1 = *reinterpret_cast<const float4*>(w1 + i + 4);
+      g1[0] = a0.x; g1[1] = a0.y; g1[2] = a0.z; g1[3] = a0.w; g1[4] = a1.x; g1[5] = a1.y; g1[6] = a1.z; g1[7] = a1.w;
+    }
+    const float4 b0 = *reinterpret_cast<const float4*>(w2 + i), b1 = *reinterpret_cast<const float4*>(w2 + i + 4);
+    g2[0] = b0.x; g2[1] = b0.y; g2[2] = b0.z; g2[3] = b0.w; g2[4] = b1.x; g2[5] = b1.y; g2[6] = b1.z; g2[7] = b1.w;
+  }
+  chain_wait();
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  if (have) load_bf16x8_cg(src + row * D + i, v);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+  ss = warp_sum(ss);
+  if (lane == 0) red[0][warp] = ss;
+  __syncthreads();
+  ss = 0.f;
+#pragma unroll
+  for (int w8 = 0; w8 < 8; ++w8) ss += red[0][w8];
+  if (w1 != nullptr) {
+    const float r1 = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j] * r1 * g1[j]));
+  }
+  if (have) store_bf16x8(y + row * D + i, v);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss2 += v[j] * v[j];
+  ss2 = warp_sum(ss2);
+  if (lane == 0) red[1][warp] = ss2;
+  __syncthreads();
+  ss2 = 0.f;
+#pragma unroll
+  for (int w8 = 0; w8 < 8; ++w8) ss2 += red[1][w8];
+  const float r2 = rsqrtf(ss2 / (float)D + eps);
+  float o[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = v[j] * r2 * g2[j];
+  if (have) store_bf16x8(z + row * D + i, o);
 }
 
 __global__ void decode_fill_kernel(int32_t* p, int n, int32_t val) {
@@ -499,9 +580,9 @@ __global__ void decode_advance_kernel(int32_t* pos_ptr, const int64_t* __restric
   chain_release();
   chain_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
-  const int pos = *pos_ptr;
+  const int pos = __ldcg(pos_ptr);
   if (pos >= capacity) return;
-  if (b < B && history != nullptr && pos + 1 < capacity) history[(size_t)b * capacity + pos + 1] = tokens[b];
+  if (b < B && history != nullptr && pos + 1 < capacity) history[(size_t)b * capacity + pos + 1] = __ldcg(tokens + b);
   __syncthreads();
   if (b == 0) *pos_ptr = pos + 1;
 }
@@ -546,6 +627,9 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
              HB200_ERR_UNSUPPORTED, "decode_step: at most %d query heads per kv head", DATT_GMAX);
   HB_REQUIRE((size_t)8 * (m->n_heads + m->n_kv_heads) * m->head_dim * sizeof(float) <= 48 * 1024, HB200_ERR_UNSUPPORTED,
              "decode_step: latent + kv width too large for the conv window in shared memory");
+  HB_REQUIRE(ds->capacity <= ROUTE_THREADS * ROUTE_CACHE_PER_THREAD, HB200_ERR_UNSUPPORTED,
+             "decode_step: capacity %d beyond the routing kernel's %d cached scores", ds->capacity,
+             ROUTE_THREADS * ROUTE_CACHE_PER_THREAD);
   HB_REQUIRE(decode_attention_smem(m->head_dim, m->n_heads / m->n_kv_heads, ds->capacity) <= 200 * 1024,
              HB200_ERR_UNSUPPORTED, "decode_step: capacity %d needs more shared memory than one CTA has", ds->capacity);
   const size_t ld = ((size_t)m->vocab + 7) / 8 * 8;
@@ -565,10 +649,16 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
     const char* e = getenv("HB200_DECODE_CHAIN");
     return e == nullptr || e[0] != '0';
   }();
+  // per-launch event recorder (only when the model carries a profile handle; the events serialise the chain)
+#define PS(KIND, REC, N_, K_) ProfScope ps_(m->profile, st, KIND, bi_prof, REC, B, N_, K_)
+  int bi_prof = 0;
 #define HB_ROW_LAUNCH(KERNEL, GRID, ...) \
   HB_DISPATCH_NCH(D, HB_PROPAGATE(launch_chained(KERNEL<NCH>, dim3(GRID), dim3(256), 0, st, chain, 1, __VA_ARGS__)))
+  {
+  PS(HB200_K_EMBED, 0, D, 0);
   HB_ROW_LAUNCH(embed_norm_kernel, row_grid, (const int64_t*)ds->tokens, (const __nv_bfloat16*)m->tok_emb, w.x0,
                 m->blocks[0].norm1_w, w.a, (int64_t)B, D, m->vocab, sqrtf((float)D), m->norm_eps);
+  }
   __nv_bfloat16 *xin = w.x0, *xout = w.x1;
   for (int bi = 0; bi < m->n_blocks; ++bi) {
     const hb200_block_weights& bw = m->blocks[bi];
@@ -577,23 +667,30 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
     __nv_bfloat16* kc = (__nv_bfloat16*)ds->kcache + (size_t)bi * cache_block;
     __nv_bfloat16* vc = (__nv_bfloat16*)ds->vcache + (size_t)bi * cache_block;
     // ---- attention half ----
-    HB_PROPAGATE(dgemm(m, w, w.a, bw.w_qkv, w.qkv, B, nq, D, nq, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st, chain));
+    bi_prof = bi;
+    { PS(HB200_K_GEMM_QKV, 0, nq, D);
+    HB_PROPAGATE(dgemm(m, w, w.a, bw.w_qkv, w.qkv, B, nq, D, nq, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st, chain)); }
+    { PS(HB200_K_PRE_ATTENTION, 0, C, 0);
     HB_PROPAGATE(launch_chained(decode_conv_prep_kernel, dim3(B), dim3(256), (size_t)8 * C * sizeof(float), st, chain, 1,
                                 w.qkv, (const __nv_bfloat16*)bw.w1_qk, (__nv_bfloat16*)ds->halo + (size_t)bi * B * 4 * C,
                                 (__nv_bfloat16*)ds->vshift + (size_t)bi * B * (kvd / 2), vc, w.aq, w.ak, w.qm, w.km,
-                                w.counts + (size_t)bi * R, (const int32_t*)ds->pos, B, H, KV, hd, cap));
+                                w.counts + (size_t)bi * R, (const int32_t*)ds->pos, B, H, KV, hd, cap)); }
+    { PS(HB200_K_OTHER, 0, lat, 3 * lat);
     HB_PROPAGATE(dgemm(m, w, w.aq, bw.w2_q, w.c2q, B, lat, 3 * lat, lat, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st,
-                       chain));
+                       chain)); }
+    { PS(HB200_K_PRE_ATTENTION, 1, lat, 0);
     HB_PROPAGATE(launch_chained(decode_qk_finish_kernel, dim3(B), dim3(256), (size_t)4 * kvd * sizeof(float), st, chain, 1,
                                 w.qkv, w.c2q, w.ak, (const __nv_bfloat16*)bw.w2_k, w.qm, w.km, m->rope_cos, m->rope_sin,
-                                bw.key_temperature, w.qnew, kc, (const int32_t*)ds->pos, H, KV, hd, cap));
+                                bw.key_temperature, w.qnew, kc, (const int32_t*)ds->pos, H, KV, hd, cap)); }
+    { PS(HB200_K_ATTENTION, 0, lat, cap);
     switch (hd) {
       case 16: HB_PROPAGATE(launch_decode_attention<16>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st, chain)); break;
       case 32: HB_PROPAGATE(launch_decode_attention<32>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st, chain)); break;
       default: HB_PROPAGATE(launch_decode_attention<64>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st, chain)); break;
-    }
+    } }
+    { PS(HB200_K_GEMM_O, 0, D, lat);
     HB_PROPAGATE(dgemm(m, w, w.o, bw.w_o, w.cur, B, D, lat, D, EPI_RESID, xin, m->residual_scale * m->output_scale, nullptr,
-                       nullptr, err, st, chain));
+                       nullptr, err, st, chain)); }
     // ---- MoR loop on the B new rows ----
     if (!m->adaptive)
       HB_PROPAGATE(launch_chained(decode_fill_kernel, dim3(ceil_div(B, 256)), dim3(256), 0, st, chain, 1, w.depth, B, R - 1));
@@ -602,34 +699,40 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
       const bool need_router = (r == 0) && m->adaptive;
       int32_t* count = w.counts + (size_t)bi * R + r;
       float* cache = has_mod ? ds->scores + (((size_t)bi * R + r) * B) * cap : nullptr;
-#define HB_DROUTE(MOD_, ROUTER_)                                                                                       \
-  HB_DISPATCH_NCH(D, HB_PROPAGATE(launch_chained(decode_route_kernel<NCH, MOD_, ROUTER_>, dim3(row_grid), dim3(256), 0,   \
-                                                 st, chain, 1, (const __nv_bfloat16*)w.cur, rec, bw.norm2_w, bw.mod_wn,  \
-                                                 bw.mod_b, bw.mor_w, bw.mor_b, cache, w.depth, r, w.rows, count,         \
-                                                 (r + 1 < R) ? count + 1 : (int32_t*)nullptr, w.ug,                      \
-                                                 (const int32_t*)ds->pos, B, D, cap, m->mod_capacity, m->norm_eps, R,    \
-                                                 m->min_depth)))
+#define HB_DROUTE(MOD_, ROUTER_)                                                                                     \
+  HB_PROPAGATE(launch_chained(decode_route_kernel<MOD_, ROUTER_>, dim3(B), dim3(ROUTE_THREADS), 0, st, chain, 1,         \
+                              (const __nv_bfloat16*)w.cur, rec, bw.norm2_w, bw.mod_wn, bw.mod_b, bw.mor_w, bw.mor_b,     \
+                              cache, w.depth, r, w.rows, count, (r + 1 < R) ? count + 1 : (int32_t*)nullptr, w.ug,       \
+                              (const int32_t*)ds->pos, B, D, cap, m->mod_capacity, m->norm_eps, R, m->min_depth))
+      { PS(HB200_K_SELECT, r, D, 0);
       if (has_mod && need_router) HB_DROUTE(true, true);
       else if (has_mod) HB_DROUTE(true, false);
       else if (need_router) HB_DROUTE(false, true);
-      else HB_DROUTE(false, false);
+      else HB_DROUTE(false, false); }
 #undef HB_DROUTE
+      { PS(HB200_K_GEMM_GATE_UP, r, 2 * F, D);
       HB_PROPAGATE(dgemm(m, w, w.ug, bw.w_gate_up, w.act, B, 2 * F, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count, err, st,
-                         chain));
+                         chain)); }
+      { PS(HB200_K_GEMM_DOWN, r, D, F);
       HB_PROPAGATE(dgemm(m, w, w.act, bw.w_down, w.cur, B, D, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count, err, st,
-                         chain));
+                         chain)); }
     }
     const float* next_w = last ? m->norm_w : m->blocks[bi + 1].norm1_w;
-    HB_ROW_LAUNCH(dual_norm_kernel, row_grid, (const __nv_bfloat16*)w.cur, bw.final_norm_w, xout, next_w,
-                  last ? w.hid : w.a, (int64_t)B, D, m->norm_eps);
+    { PS(HB200_K_RMS_NORM, R, D, 0);
+    HB_PROPAGATE(launch_chained(decode_dual_norm_kernel, dim3(B), dim3(256), 0, st, chain, 1, (const __nv_bfloat16*)w.cur,
+                                bw.final_norm_w, xout, next_w, last ? w.hid : w.a, D, m->norm_eps)); }
     std::swap(xin, xout);
   }
 #undef HB_ROW_LAUNCH
   __nv_bfloat16* lg = last_logits ? (__nv_bfloat16*)last_logits : w.logits;
+  bi_prof = m->n_blocks;
+  { PS(HB200_K_GEMM_LM_HEAD, 0, m->vocab, D);
   HB_PROPAGATE(dgemm(m, w, w.hid, m->tok_emb, lg, B, m->vocab, D, (int64_t)ld, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err,
-                     st, chain));
-  HB_PROPAGATE(launch_argmax_rows(lg, B, m->vocab, (int64_t)ld, ds->tokens, st, chain));
+                     st, chain)); }
+  { PS(HB200_K_OTHER, 1, m->vocab, 0);
+  HB_PROPAGATE(launch_argmax_rows(lg, B, m->vocab, (int64_t)ld, ds->tokens, st, chain)); }
   HB_PROPAGATE(launch_chained(decode_advance_kernel, dim3(ceil_div(B, 1024)), dim3(1024), 0, st, chain, 1, ds->pos,
                               (const int64_t*)ds->tokens, ds->history, B, cap));
+#undef PS
   return 0;
 }

@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* _
 #pragma unroll
       for (int u = 0; u < UN; ++u) {
         const int vi = v0 + u * blockDim.x;
-        raw[u] = vi < vec ? *reinterpret_cast<const uint4*>(row + (size_t)vi * 8) : make_uint4(0, 0, 0, 0);
+        raw[u] = vi < vec ? __ldcg(reinterpret_cast<const uint4*>(row + (size_t)vi * 8)) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int u = 0; u < UN; ++u) {
@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* _
     }
     done = vec * 8;
   }
-  for (int i = done + threadIdx.x; i < cols; i += blockDim.x) take(__bfloat162float(row[i]), i);
+  for (int i = done + threadIdx.x; i < cols; i += blockDim.x) take(ldcg_bf16(row + i), i);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);

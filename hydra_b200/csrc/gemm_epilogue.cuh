@@ -38,7 +38,7 @@ __device__ __forceinline__ void epilogue_row_chunk(const GemmParams& p, int m, i
     }
     return;
   }
-  const size_t row = (p.epilogue == EPI_SCATTER_ADD) ? (size_t)p.rows[m] : (size_t)m;
+  const size_t row = (p.epilogue == EPI_SCATTER_ADD) ? (size_t)__ldcg(p.rows + m) : (size_t)m;
   __nv_bfloat16* dst = p.C + row * p.ldc + col;
   const __nv_bfloat16* src = (p.epilogue == EPI_RESID) ? p.resid + row * p.ldc + col
                                                        : (p.epilogue == EPI_SCATTER_ADD ? dst : nullptr);
@@ -49,7 +49,7 @@ __device__ __forceinline__ void epilogue_row_chunk(const GemmParams& p, int m, i
       float o[8];
       if (src != nullptr) {
         float r[8];
-        load_bf16x8(src + v8 * 8, r);
+        load_bf16x8_cg(src + v8 * 8, r);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = r[j] + p.alpha * acc[v8 * 8 + j];
       } else {
@@ -60,7 +60,7 @@ __device__ __forceinline__ void epilogue_row_chunk(const GemmParams& p, int m, i
     } else {
       for (int j = 0; j < 8 && c + j < p.N; ++j) {
         float val = p.alpha * acc[v8 * 8 + j];
-        if (src != nullptr) val += __bfloat162float(src[v8 * 8 + j]);
+        if (src != nullptr) val += ldcg_bf16(src + v8 * 8 + j);
         dst[v8 * 8 + j] = __float2bfloat16_rn(val);
       }
     }

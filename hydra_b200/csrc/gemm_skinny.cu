@@ -76,14 +76,18 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
 
 // Row m of this CTA's column share [c_first, c_first + cw) of the tile: sum the KS partials (all loads of a 16-column
 // group in flight at once, then added in slice order) and apply the epilogue.
+// For the read-modify-write epilogues the old values of the row segment were requested before the mainloop finished
+// (`old`, `grow` = global row); groups that were not prefetched (column tail) take the generic epilogue.
+constexpr int SK_MAX_GROUPS = 4;    // column share of a cluster member: at most 64 columns = 4 groups of 16
 template <int KS>
 __device__ __forceinline__ void reduce_share(const GemmParams& p, uint32_t part_addr, int m, int tile_col0, int c_first,
-                                             int cw) {
+                                             int cw, long long grow, const uint4 (&old)[SK_MAX_GROUPS][2]) {
   uint32_t peer[KS];
 #pragma unroll
   for (int s = 0; s < KS; ++s) peer[s] = map_to_cta(part_addr + (uint32_t)((c_first * SK_BM + m) * 4), (uint32_t)s);
-#pragma unroll 1
-  for (int g = 0; g < cw / 16; ++g) {
+#pragma unroll
+  for (int g = 0; g < SK_MAX_GROUPS; ++g) {
+    if (g >= cw / 16) break;
     const int col = tile_col0 + c_first + g * 16;
     if (col >= p.N) break;
     float t[KS][16];
@@ -98,7 +102,23 @@ __device__ __forceinline__ void reduce_share(const GemmParams& p, uint32_t part_
 #pragma unroll
       for (int s = 1; s < KS; ++s) v[j] += t[s][j];
     }
-    epilogue_row_chunk<16>(p, m, col, v);
+    if (grow >= 0 && col + 16 <= p.N) {
+      __nv_bfloat16* dst = p.C + (size_t)grow * p.ldc + col;
+#pragma unroll
+      for (int h8 = 0; h8 < 2; ++h8) {
+        const uint32_t w4[4] = {old[g][h8].x, old[g][h8].y, old[g][h8].z, old[g][h8].w};
+        uint4 o;
+        uint32_t* ow = &o.x;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float r0 = __uint_as_float(w4[j] << 16), r1 = __uint_as_float(w4[j] & 0xffff0000u);
+          ow[j] = pack_bf16x2_rn(r0 + p.alpha * v[h8 * 8 + 2 * j], r1 + p.alpha * v[h8 * 8 + 2 * j + 1]);
+        }
+        *reinterpret_cast<uint4*>(dst + h8 * 8) = o;
+      }
+    } else {
+      epilogue_row_chunk<16>(p, m, col, v);
+    }
   }
 }
 
@@ -154,23 +174,28 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
     }
   }
   chain_wait();
-  const int M = p.m_dev ? min(*p.m_dev, p.M) : p.M;
+  // the A slices of the prefetched stages go out before the live row count is even read: if it turns out to be zero
+  // the tiles are simply not consumed
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < pre; ++i) {
+      mbar_arrive_expect_tx(full_bar(i), a_bytes);
+      tma_load_2d(base + i * stage_bytes, &tma_a, (kb0 + i) * SK_BK, 0, full_bar(i));
+    }
+  }
+  const int M = p.m_dev ? min(__ldcg(p.m_dev), p.M) : p.M;
   const int kb1 = (M > 0) ? kb1_full : kb0;
   const bool has_work = kb1 > kb0;                                      // a trailing slice may be empty
 
+  long long rmw_row = -1;                       // epilogue warps only (see below)
+  uint4 rmw_old[SK_MAX_GROUPS][2];
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       if (!has_work) {
-        // no live rows: let the prefetched W tiles land (their barriers need the arrival), then leave
-        for (int i = 0; i < pre; ++i) mbar_arrive(full_bar(i));
+        // no live rows: let the requested tiles land, then leave
         for (int i = 0; i < pre; ++i)
           if (!mbar_wait(full_bar(i), 0u, abort_flag)) break;
       } else {
-        for (int i = 0; i < pre; ++i) {
-          mbar_arrive_expect_tx(full_bar(i), a_bytes);
-          tma_load_2d(base + i * stage_bytes, &tma_a, (kb0 + i) * SK_BK, 0, full_bar(i));
-        }
         int stage = pre % n_stages;
         uint32_t phase = (pre == n_stages) ? 1u : 0u;
         for (int kb = kb0 + pre; kb < kb1; ++kb) {
@@ -210,6 +235,21 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
     const int quad = warp & 3;
     const int m = quad * 32 + lane;
     bool ok = true;
+    // read-modify-write epilogues of split tiles: this thread's row index and the old values of its column share are
+    // requested now, so both round trips hide behind the mainloop
+    if (ksplit > 1 && (p.epilogue == EPI_RESID || p.epilogue == EPI_SCATTER_ADD) && (p.N % 8 == 0) && m < M) {
+      rmw_row = (p.epilogue == EPI_SCATTER_ADD) ? (long long)__ldcg(p.rows + m) : (long long)m;
+      const __nv_bfloat16* src = (p.epilogue == EPI_RESID) ? p.resid : p.C;
+      const int cw = bn / ksplit;
+#pragma unroll
+      for (int g = 0; g < SK_MAX_GROUPS; ++g) {
+        const int col = nt * bn + ks * cw + g * 16;
+        if (g < cw / 16 && col + 16 <= p.N) {
+          rmw_old[g][0] = __ldcg(reinterpret_cast<const uint4*>(src + (size_t)rmw_row * p.ldc + col));
+          rmw_old[g][1] = __ldcg(reinterpret_cast<const uint4*>(src + (size_t)rmw_row * p.ldc + col + 8));
+        }
+      }
+    }
     if (has_work) {
       if (!mbar_wait(tfull_bar, 0u, abort_flag)) ok = false;      // all MMAs done: the ring is free, TMEM is final
       ok = __all_sync(0xffffffffu, ok);
@@ -252,9 +292,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid
       const int m = (warp & 3) * 32 + lane;
       if (m < M) {
         const int cw = bn / ksplit;                                // this CTA's share of the tile's columns
-        if (ksplit == 2) reduce_share<2>(p, s_addr(part), m, nt * bn, ks * cw, cw);
-        else if (ksplit == 4) reduce_share<4>(p, s_addr(part), m, nt * bn, ks * cw, cw);
-        else reduce_share<8>(p, s_addr(part), m, nt * bn, ks * cw, cw);
+        if (ksplit == 2) reduce_share<2>(p, s_addr(part), m, nt * bn, ks * cw, cw, rmw_row, rmw_old);
+        else if (ksplit == 4) reduce_share<4>(p, s_addr(part), m, nt * bn, ks * cw, cw, rmw_row, rmw_old);
+        else reduce_share<8>(p, s_addr(part), m, nt * bn, ks * cw, cw, rmw_row, rmw_old);
       }
     }
     cluster_sync_all();                                            // nobody leaves while a peer may still read it

@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const int64_t* __restri
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= T) return;
-  int64_t id = ids[row];
+  int64_t id = __ldcg(ids + row);   // written by the previous decode step's argmax (see load_bf16x8_cg)
   id = id < 0 ? 0 : (id >= V ? V - 1 : id);
   float v[NCH][8];
   load_row_add<NCH>(table + id * D, nullptr, D, lane, v);
