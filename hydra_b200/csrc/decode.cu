@@ -24,6 +24,7 @@
 
 #include "gemm_epilogue.cuh"
 #include "row_kernels.cuh"
+#include "tcgen05.cuh"
 
 namespace hb200 {
 
@@ -74,38 +75,71 @@ static DecodeWs carve_decode(const hb200_model* m, int B, void* base) {
 }
 
 // ---- conv prep: one CTA per sequence ---------------------------------------------------------------------------
-// dynamic smem: win[5][C] + y1[3][C] floats
+// dynamic smem: win[5][C] + y1[3][C] floats.  Laid out for latency: the conv1 weight rows of this thread's (up to
+// three) output channels are static and are requested before the wait on the predecessor (head_dim <= 32: they fit in
+// registers); the position, the halo, the new q|k row and the value pieces are requested together right after it.
+constexpr int CONV_CPT = 3;       // output channels per thread held in registers: latent + kv width <= 768
+template <int HD>
 __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
     const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ w1, __nv_bfloat16* __restrict__ halo,
     __nv_bfloat16* __restrict__ vshift, __nv_bfloat16* __restrict__ vcache, __nv_bfloat16* __restrict__ aq,
     __nv_bfloat16* __restrict__ ak, float* __restrict__ qm, float* __restrict__ km, int32_t* __restrict__ first_count,
-    const int32_t* __restrict__ pos_ptr, int B, int H, int KV, int hd, int capacity) {
+    const int32_t* __restrict__ pos_ptr, int B, int H, int KV, int capacity) {
   extern __shared__ float smem_f[];
-  chain_release();
-  chain_wait();
+  constexpr int hd = HD;
+  constexpr int WV = 3 * HD / 8;                  // 16-byte pieces of one weight row
+  constexpr bool PRE = HD <= 32;
   const int lat = H * hd, kvd = KV * hd, C = lat + kvd, qkv_ld = lat + 2 * kvd, half = kvd / 2;
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const bool in_regs = PRE && C <= CONV_CPT * 256;
+  chain_release();
+  uint4 wreg[PRE ? CONV_CPT : 1][PRE ? WV : 1];
+  if (in_regs) {
+#pragma unroll
+    for (int k = 0; k < CONV_CPT; ++k) {
+      const int c = tid + k * 256;
+      if (c < C) {
+#pragma unroll
+        for (int e = 0; e < WV; ++e) wreg[k][e] = *reinterpret_cast<const uint4*>(w1 + (size_t)c * 3 * hd + e * 8);
+      }
+    }
+  }
+  chain_wait();
   float* win = smem_f;            // [5][C]: positions p-4 .. p
   float* y1 = smem_f + 5 * C;     // [3][C]: positions p-2 .. p
-  const int b = blockIdx.x, tid = threadIdx.x;
   if (b == 0 && tid == 0) *first_count = 0;   // row counter of this block's first recursion (see decode_route_kernel)
   const int pos = __ldcg(pos_ptr);
-  if (pos >= capacity) return;    // cache full: the step is a no-op (the host checks capacity before launching)
   __nv_bfloat16* hb = halo + (size_t)b * 4 * C;
   const __nv_bfloat16* row = qkv + (size_t)b * qkv_ld;
   // (everything other kernels of the chain write is read through L2, see load_bf16x8_cg)
-  for (int i = tid; i < 4 * C; i += 256) win[i] = ldcg_bf16(hb + i);
-  for (int c = tid; c < C; c += 256) win[4 * C + c] = ldcg_bf16(row + c);
+  for (int i = tid * 8; i < 5 * C; i += 256 * 8) {        // C % 8 == 0: a piece never straddles halo and new row
+    float f[8];
+    load_bf16x8_cg(i < 4 * C ? hb + i : row + (i - 4 * C), f);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) win[i + q] = f[q];
+  }
+  // this thread's value channel: current half from the new row, shifted half from the previous position
+  float vval = 0.f, vnext = 0.f;
+  if (tid < kvd) vval = (tid < half) ? ldcg_bf16(row + C + tid) : ldcg_bf16(vshift + (size_t)b * half + (tid - half));
+  if (tid < half) vnext = ldcg_bf16(row + C + half + tid);
+  if (pos >= capacity) return;    // cache full: the step is a no-op (the host checks capacity before launching)
   __syncthreads();
   // grouped conv1 (kernel 3, causal) on rows 2..4 of the window; rounded to bf16 like the prefill's y1 tile.
-  // One thread per output channel: its weight row (3 taps x hd inputs, 16-byte loads) serves all three positions.
-  for (int c = tid; c < C; c += 256) {
+  // One thread per output channel: its weight row (3 taps x hd inputs) serves all three positions.
+  auto conv_channel = [&](int c, auto&& weight_piece) {
     const int hb0 = (c / hd) * hd;
-    const __nv_bfloat16* wr = w1 + (size_t)c * 3 * hd;
     float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f;
-    for (int e = 0; e < 3 * hd; e += 8) {
+#pragma unroll
+    for (int e = 0; e < WV; ++e) {
+      const uint4 raw = weight_piece(e);
+      const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
       float wv[8];
-      load_bf16x8(wr + e, wv);
-      const int j = e / hd, ci0 = e - j * hd;                 // hd % 8 == 0: the 8 weights share a tap
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        wv[2 * q] = __uint_as_float(w4[q] << 16);
+        wv[2 * q + 1] = __uint_as_float(w4[q] & 0xffff0000u);
+      }
+      const int j = (e * 8) / hd, ci0 = e * 8 - j * hd;        // hd % 8 == 0: the 8 weights share a tap
       const float* x0 = win + j * C + hb0 + ci0;
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
@@ -117,6 +151,18 @@ __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
     y1[c] = __bfloat162float(__float2bfloat16_rn(acc0));
     y1[C + c] = __bfloat162float(__float2bfloat16_rn(acc1));
     y1[2 * C + c] = __bfloat162float(__float2bfloat16_rn(acc2));
+  };
+  if (in_regs) {
+#pragma unroll
+    for (int k = 0; k < CONV_CPT; ++k) {
+      const int c = tid + k * 256;
+      if (c < C) conv_channel(c, [&](int e) { return wreg[k][e]; });
+    }
+  } else {
+    for (int c = tid; c < C; c += 256) {
+      const __nv_bfloat16* wr = w1 + (size_t)c * 3 * hd;
+      conv_channel(c, [&](int e) { return *reinterpret_cast<const uint4*>(wr + e * 8); });
+    }
   }
   // QK-mean halves and the value row
   for (int d = tid; d < 2 * hd; d += 256) {
@@ -131,11 +177,7 @@ __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
       km[(size_t)b * hd + dd] = sacc * (0.5f / (float)KV);
     }
   }
-  for (int c = tid; c < kvd; c += 256) {
-    const __nv_bfloat16 val =
-        __float2bfloat16_rn((c < half) ? ldcg_bf16(row + C + c) : ldcg_bf16(vshift + (size_t)b * half + (c - half)));
-    vcache[(((size_t)b * KV + c / hd) * capacity + pos) * hd + (c % hd)] = val;
-  }
+  if (tid < kvd) vcache[(((size_t)b * KV + tid / hd) * capacity + pos) * hd + (tid % hd)] = __float2bfloat16_rn(vval);
   __syncthreads();
   // im2col rows of the dense conv: [tap 0 | tap 1 | tap 2], each tap = y1 of one position
   for (int i = tid; i < 3 * C; i += 256) {
@@ -146,7 +188,7 @@ __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
   }
   // advance the halo (drop the oldest row) and the v_shift half
   for (int i = tid; i < 4 * C; i += 256) hb[i] = __float2bfloat16_rn(win[C + i]);
-  for (int c = tid; c < half; c += 256) vshift[(size_t)b * half + c] = __float2bfloat16_rn(ldcg_bf16(row + C + half + c));
+  if (tid < half) vshift[(size_t)b * half + tid] = __float2bfloat16_rn(vnext);
 }
 
 // ---- QK finish: one CTA per sequence, one warp per head ----------------------------------------------------------
@@ -220,10 +262,13 @@ __global__ void __launch_bounds__(256) decode_qk_finish_kernel(
 // Pass 1: one thread per cached key, logits of the G query heads of this kv head into shared memory, row maxima.
 // Pass 2: exponentials and row sums.  Pass 3: P V with 16-byte loads of V (lane = 8-dim chunk, key slices across
 // the rest of the CTA), reduced by shuffles and a small shared-memory table.  Exact softmax for any temperature.
+// STAGED: the cached K and V rows of this (sequence, kv head) are first copied into shared memory with cp.async (one
+// round trip with every 16-byte piece in flight at once, L1 bypassed) and both passes read them from there; used
+// whenever 2 x capacity x head_dim x 2 bytes fit next to the score table.
 constexpr int DATT_THREADS = 256;
 constexpr int DATT_WARPS = DATT_THREADS / 32;
 constexpr int DATT_GMAX = 8;      // query heads per kv head
-template <int HD>
+template <int HD, bool STAGED>
 __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
     const __nv_bfloat16* __restrict__ qnew, const __nv_bfloat16* __restrict__ kcache,
     const __nv_bfloat16* __restrict__ vcache, __nv_bfloat16* __restrict__ o, const int32_t* __restrict__ pos_ptr, int H,
@@ -239,11 +284,36 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
   float* red = qs + DATT_GMAX * HD;            // [DATT_WARPS][DATT_GMAX]
   float* part = red + DATT_WARPS * DATT_GMAX;  // [DATT_WARPS][DATT_GMAX][HD]
   float* sc = part + DATT_WARPS * DATT_GMAX * HD;   // [G][capacity]
-  for (int i = tid; i < G * HD; i += DATT_THREADS)
-    qs[i] = ldcg_bf16(qnew + (size_t)b * lat + (size_t)(kvh * G) * HD + i) * scale_log2;
-  __syncthreads();
   const __nv_bfloat16* kb = kcache + ((size_t)b * KV + kvh) * capacity * HD;
   const __nv_bfloat16* vb = vcache + ((size_t)b * KV + kvh) * capacity * HD;
+  // staged copies of the cached rows (16-byte aligned: the tables before them are multiples of 4 floats)
+  const uint32_t stage_k = s_addr(sc + (size_t)((G * capacity + 3) & ~3));
+  const uint32_t stage_v = stage_k + (uint32_t)capacity * HD * 2;
+  if (STAGED) {
+    const int pieces = n_keys * CH;
+    for (int i = tid; i < pieces; i += DATT_THREADS) {
+      cp_async16(stage_k + (uint32_t)i * 16u, kb + (size_t)i * 8);
+      cp_async16(stage_v + (uint32_t)i * 16u, vb + (size_t)i * 8);
+    }
+    cp_async16_commit();
+  }
+  for (int i = tid; i < G * HD; i += DATT_THREADS)
+    qs[i] = ldcg_bf16(qnew + (size_t)b * lat + (size_t)(kvh * G) * HD + i) * scale_log2;
+  if (STAGED) cp_async16_wait_all();
+  __syncthreads();
+  auto row8 = [&](uint32_t stage, const __nv_bfloat16* gptr, int key, int c, float (&f)[8]) {
+    if (STAGED) {
+      const uint4 raw = ld_shared_v4(stage + (uint32_t)(key * HD + c * 8) * 2u);
+      const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        f[2 * q] = __uint_as_float(w4[q] << 16);
+        f[2 * q + 1] = __uint_as_float(w4[q] & 0xffff0000u);
+      }
+    } else {
+      load_bf16x8_cg(gptr + (size_t)key * HD + c * 8, f);
+    }
+  };
   // pass 1
   float mx[DATT_GMAX];
 #pragma unroll
@@ -252,7 +322,7 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
   for (int key = tid; key < n_keys; key += DATT_THREADS) {
     float kf[HD];
 #pragma unroll
-    for (int c = 0; c < CH; ++c) load_bf16x8_cg(kb + (size_t)key * HD + c * 8, *reinterpret_cast<float(*)[8]>(&kf[c * 8]));
+    for (int c = 0; c < CH; ++c) row8(stage_k, kb, key, c, *reinterpret_cast<float(*)[8]>(&kf[c * 8]));
 #pragma unroll
     for (int g = 0; g < DATT_GMAX; ++g) {
       if (g < G) {
@@ -318,7 +388,7 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
 #pragma unroll 4
   for (int key = slice; key < n_keys; key += NSLICE) {
     float vf[8];
-    load_bf16x8_cg(vb + (size_t)key * HD + chunk * 8, vf);
+    row8(stage_v, vb, key, chunk, vf);
 #pragma unroll
     for (int g = 0; g < DATT_GMAX; ++g) {
       if (g < G) {
@@ -359,10 +429,16 @@ template <int HD>
 static int launch_decode_attention(const __nv_bfloat16* qnew, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
                                    __nv_bfloat16* o, const int32_t* pos, int B, int H, int KV, int capacity, float scale,
                                    cudaStream_t st, bool chain) {
-  const size_t smem = decode_attention_smem(HD, H / KV, capacity);
-  HB_PROPAGATE(ensure_dynamic_smem((const void*)decode_attention_kernel<HD>, smem));
-  return launch_chained(decode_attention_kernel<HD>, dim3(KV, B), dim3(DATT_THREADS), smem, st, chain, 1, qnew, kc, vc, o,
-                        pos, H, KV, capacity, scale * 1.4426950408889634f);
+  const size_t base = decode_attention_smem(HD, H / KV, capacity) + 16;
+  const size_t staged = base + (size_t)2 * capacity * HD * 2;
+  if (staged <= 200 * 1024) {
+    HB_PROPAGATE(ensure_dynamic_smem((const void*)decode_attention_kernel<HD, true>, staged));
+    return launch_chained(decode_attention_kernel<HD, true>, dim3(KV, B), dim3(DATT_THREADS), staged, st, chain, 1, qnew, kc,
+                          vc, o, pos, H, KV, capacity, scale * 1.4426950408889634f);
+  }
+  HB_PROPAGATE(ensure_dynamic_smem((const void*)decode_attention_kernel<HD, false>, base));
+  return launch_chained(decode_attention_kernel<HD, false>, dim3(KV, B), dim3(DATT_THREADS), base, st, chain, 1, qnew, kc, vc,
+                        o, pos, H, KV, capacity, scale * 1.4426950408889634f);
 }
 
 // ---- routing of the newest position + gather-norm: one CTA per sequence -------------------------------------
@@ -627,6 +703,8 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
              HB200_ERR_UNSUPPORTED, "decode_step: at most %d query heads per kv head", DATT_GMAX);
   HB_REQUIRE((size_t)8 * (m->n_heads + m->n_kv_heads) * m->head_dim * sizeof(float) <= 48 * 1024, HB200_ERR_UNSUPPORTED,
              "decode_step: latent + kv width too large for the conv window in shared memory");
+  HB_REQUIRE(m->n_kv_heads * m->head_dim <= 256, HB200_ERR_UNSUPPORTED, "decode_step: kv width %d beyond 256",
+             m->n_kv_heads * m->head_dim);
   HB_REQUIRE(ds->capacity <= ROUTE_THREADS * ROUTE_CACHE_PER_THREAD, HB200_ERR_UNSUPPORTED,
              "decode_step: capacity %d beyond the routing kernel's %d cached scores", ds->capacity,
              ROUTE_THREADS * ROUTE_CACHE_PER_THREAD);
@@ -671,10 +749,17 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
     { PS(HB200_K_GEMM_QKV, 0, nq, D);
     HB_PROPAGATE(dgemm(m, w, w.a, bw.w_qkv, w.qkv, B, nq, D, nq, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st, chain)); }
     { PS(HB200_K_PRE_ATTENTION, 0, C, 0);
-    HB_PROPAGATE(launch_chained(decode_conv_prep_kernel, dim3(B), dim3(256), (size_t)8 * C * sizeof(float), st, chain, 1,
-                                w.qkv, (const __nv_bfloat16*)bw.w1_qk, (__nv_bfloat16*)ds->halo + (size_t)bi * B * 4 * C,
-                                (__nv_bfloat16*)ds->vshift + (size_t)bi * B * (kvd / 2), vc, w.aq, w.ak, w.qm, w.km,
-                                w.counts + (size_t)bi * R, (const int32_t*)ds->pos, B, H, KV, hd, cap)); }
+#define HB_CONV_PREP(HD_)                                                                                               \
+  HB_PROPAGATE(launch_chained(decode_conv_prep_kernel<HD_>, dim3(B), dim3(256), (size_t)8 * C * sizeof(float), st, chain, 1,  \
+                              (const __nv_bfloat16*)w.qkv, (const __nv_bfloat16*)bw.w1_qk,                                     \
+                              (__nv_bfloat16*)ds->halo + (size_t)bi * B * 4 * C,                                               \
+                              (__nv_bfloat16*)ds->vshift + (size_t)bi * B * (kvd / 2), vc, w.aq, w.ak, w.qm, w.km,             \
+                              w.counts + (size_t)bi * R, (const int32_t*)ds->pos, B, H, KV, cap))
+    if (hd == 16) HB_CONV_PREP(16);
+    else if (hd == 32) HB_CONV_PREP(32);
+    else HB_CONV_PREP(64);
+#undef HB_CONV_PREP
+    }
     { PS(HB200_K_OTHER, 0, lat, 3 * lat);
     HB_PROPAGATE(dgemm(m, w, w.aq, bw.w2_q, w.c2q, B, lat, 3 * lat, lat, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err, st,
                        chain)); }
