@@ -25,6 +25,7 @@
 #include "gemm_epilogue.cuh"
 #include "row_kernels.cuh"
 #include "tcgen05.cuh"
+#include "tma_host.cuh"
 
 namespace hb200 {
 
@@ -192,45 +193,84 @@ __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
 }
 
 // ---- QK finish: one CTA per sequence, one warp per head ----------------------------------------------------------
+// Latency layout: the temperature and (when they fit in registers) this thread's share of the key conv weights are
+// static and requested before the wait; the q / k finishing runs lph = hd/2 lanes per head (one RoPE pair per lane),
+// i.e. up to four heads per warp side by side, so all heads of a sequence are done in one or two passes.
+constexpr int QKF_WPT = 8;        // 16-byte weight pieces per thread held in registers
 __global__ void __launch_bounds__(256) decode_qk_finish_kernel(
     const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ c2q, const __nv_bfloat16* __restrict__ ak,
     const __nv_bfloat16* __restrict__ w2k, const float* __restrict__ qm, const float* __restrict__ km, const float* __restrict__ cos_t,
     const float* __restrict__ sin_t, const float* __restrict__ temp, __nv_bfloat16* __restrict__ qnew,
     __nv_bfloat16* __restrict__ kcache, const int32_t* __restrict__ pos_ptr, int H, int KV, int hd, int capacity) {
-  const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  chain_release();
-  chain_wait();
-  const int pos = __ldcg(pos_ptr);
-  if (pos >= capacity) return;
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int lat = H * hd, kvd = KV * hd, qkv_ld = lat + 2 * kvd;
   const bool same_heads = (H == KV);
-  // the key side of the dense conv is small (kvd x 3 kvd): done here on the CUDA cores, one thread per output
-  // channel, im2col row in shared memory, result rounded to bf16 like a stored GEMM output
   extern __shared__ float smem_f[];
   float* a_row = smem_f;                 // [3 * kvd]
   float* c2k = smem_f + 3 * kvd;         // [kvd]
-  for (int i = threadIdx.x; i < 3 * kvd; i += 256) a_row[i] = ldcg_bf16(ak + (size_t)b * 3 * kvd + i);
-  __syncthreads();
-  for (int n = threadIdx.x; n < kvd; n += 256) {
-    const __nv_bfloat16* wr = w2k + (size_t)n * 3 * kvd;
-    float acc = 0.f;
-    for (int e = 0; e < 3 * kvd; e += 8) {
-      float wv[8];
-      load_bf16x8(wr + e, wv);
+  // key conv: tpc threads per output channel, each a contiguous run of `per` 16-byte pieces of the channel's weight row
+  const int pieces = 3 * kvd / 8;
+  const int tpc = 256 / kvd;             // > 0: kvd <= 256
+  const bool pow2 = tpc > 0 && (tpc & (tpc - 1)) == 0 && tpc <= 32;
+  const int per = pow2 ? (pieces + tpc - 1) / tpc : 0;
+  const bool in_regs = pow2 && per <= QKF_WPT;
+  const int n_ch = in_regs ? tid / tpc : 0, part = in_regs ? tid % tpc : 0;
+  chain_release();
+  uint4 wreg[QKF_WPT];
+  if (in_regs) {
 #pragma unroll
-      for (int q = 0; q < 8; ++q) acc += wv[q] * a_row[e + q];
+    for (int q = 0; q < QKF_WPT; ++q) {
+      const int e = part * per + q;
+      if (q < per && e < pieces) wreg[q] = *reinterpret_cast<const uint4*>(w2k + (size_t)n_ch * 3 * kvd + e * 8);
     }
-    c2k[n] = __bfloat162float(__float2bfloat16_rn(acc));
+  }
+  const float temperature = *temp;
+  chain_wait();
+  const int pos = __ldcg(pos_ptr);
+  for (int i = tid; i < 3 * kvd; i += 256) a_row[i] = ldcg_bf16(ak + (size_t)b * 3 * kvd + i);
+  if (pos >= capacity) return;
+  __syncthreads();
+  // the key side of the dense conv is small (kvd x 3 kvd): done here on the CUDA cores, result rounded to bf16 like a
+  // stored GEMM output
+  if (in_regs) {
+    float acc = 0.f;
+#pragma unroll
+    for (int q = 0; q < QKF_WPT; ++q) {
+      const int e = part * per + q;
+      if (q < per && e < pieces) {
+        const uint32_t w4[4] = {wreg[q].x, wreg[q].y, wreg[q].z, wreg[q].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc += __uint_as_float(w4[j] << 16) * a_row[e * 8 + 2 * j] + __uint_as_float(w4[j] & 0xffff0000u) * a_row[e * 8 + 2 * j + 1];
+      }
+    }
+    for (int off = tpc >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (part == 0 && n_ch < kvd) c2k[n_ch] = __bfloat162float(__float2bfloat16_rn(acc));
+  } else {
+    for (int n = tid; n < kvd; n += 256) {
+      const __nv_bfloat16* wr = w2k + (size_t)n * 3 * kvd;
+      float acc = 0.f;
+      for (int e = 0; e < 3 * kvd; e += 8) {
+        float wv[8];
+        load_bf16x8(wr + e, wv);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc += wv[q] * a_row[e + q];
+      }
+      c2k[n] = __bfloat162float(__float2bfloat16_rn(acc));
+    }
   }
   __syncthreads();
-  for (int hh = warp; hh < H + KV; hh += 8) {
+  // lph lanes per head, hpw heads per warp
+  const int lph = hd / 2, hpw = 32 / lph, sub = lane / lph, l = lane % lph;
+  const int d0 = 2 * l;
+  const float cs = cos_t[(size_t)pos * lph + l], sn = sin_t[(size_t)pos * lph + l];
+  for (int base_h = warp * hpw; base_h < H + KV; base_h += 8 * hpw) {     // warp-uniform trip count
+    const int hh = base_h + sub;
+    const bool valid = hh < H + KV;
     const bool is_k = hh >= H;
     const int h = is_k ? hh - H : hh;
-    // hd <= 64: each lane owns elements 2*lane and 2*lane+1 (one RoPE pair)
-    const int d0 = 2 * lane;
     float v0 = 0.f, v1 = 0.f;
-    if (d0 < hd) {
-      const __nv_bfloat16* conv = c2q + (size_t)b * lat + h * hd;
+    if (valid) {
       float c0, c1;
       if (same_heads) {   // one query head per kv head: both sides couple with 0.5 * (q0 + k0) of that head
         const __nv_bfloat16* row = qkv + (size_t)b * qkv_ld;
@@ -241,15 +281,16 @@ __global__ void __launch_bounds__(256) decode_qk_finish_kernel(
         c0 = __ldcg(mean + d0);
         c1 = __ldcg(mean + d0 + 1);
       }
+      const __nv_bfloat16* conv = c2q + (size_t)b * lat + h * hd;
       v0 = (is_k ? c2k[h * hd + d0] : ldcg_bf16(conv + d0)) + c0;
       v1 = (is_k ? c2k[h * hd + d0 + 1] : ldcg_bf16(conv + d0 + 1)) + c1;
     }
-    const float ss = warp_sum(v0 * v0 + v1 * v1);
-    const float inv = (is_k ? *temp : 1.0f) / fmaxf(sqrtf(ss), 1e-12f);
-    if (d0 < hd) {
+    float ss = v0 * v0 + v1 * v1;
+    for (int off = lph >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if (valid) {
+      const float inv = (is_k ? temperature : 1.0f) / fmaxf(sqrtf(ss), 1e-12f);
       v0 *= inv;
       v1 *= inv;
-      const float cs = cos_t[(size_t)pos * (hd / 2) + lane], sn = sin_t[(size_t)pos * (hd / 2) + lane];
       const __nv_bfloat162 out = __floats2bfloat162_rn(v0 * cs - v1 * sn, v0 * sn + v1 * cs);
       __nv_bfloat16* dst = is_k ? kcache + (((size_t)b * KV + h) * capacity + pos) * hd + d0
                                 : qnew + (size_t)b * lat + h * hd + d0;
@@ -431,7 +472,9 @@ static int launch_decode_attention(const __nv_bfloat16* qnew, const __nv_bfloat1
                                    cudaStream_t st, bool chain) {
   const size_t base = decode_attention_smem(HD, H / KV, capacity) + 16;
   const size_t staged = base + (size_t)2 * capacity * HD * 2;
-  if (staged <= 200 * 1024) {
+  // staging costs one CTA per SM: worth it while the grid still fits in one wave (small batches, where the kernel is a
+  // latency chain); larger grids keep four CTAs per SM and stream from L2
+  if (staged <= 200 * 1024 && (long long)KV * B <= sm_count()) {
     HB_PROPAGATE(ensure_dynamic_smem((const void*)decode_attention_kernel<HD, true>, staged));
     return launch_chained(decode_attention_kernel<HD, true>, dim3(KV, B), dim3(DATT_THREADS), staged, st, chain, 1, qnew, kc,
                           vc, o, pos, H, KV, capacity, scale * 1.4426950408889634f);
