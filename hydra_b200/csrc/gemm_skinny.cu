@@ -1,10 +1,11 @@
 // Skinny-M bf16 GEMM for decode (M <= 128 rows):  C = epilogue(A W^T),  A [M,K], W [N,K], both K-major.
 //
 // With a handful of rows the contraction is bound by streaming W from HBM once, so the work is cut for bandwidth,
-// not for tensor throughput: one CTA per (128 weight rows, one slice of K), so even a 2048 x 5632 weight (16 row
-// tiles) keeps 128 SMs streaming.  Inside a CTA the pipeline is the one of the large GEMM: warp 0 issues TMA loads of
+// not for tensor throughput: one CTA per (64..128 weight rows, one slice of K), two CTAs per SM, so even a 2048 x 5632
+// weight (16 row tiles) keeps 128 CTAs streaming and the CTAs of the next contraction of a chain can move in (and start
+// their weight stream) while the current one drains.  Inside a CTA the pipeline is the one of the large GEMM: warp 0 issues TMA loads of
 // the A slice (a 64-row box when M <= 64, else 128 rows; rows beyond M are zero-filled by the tensor map and cost no
-// traffic) and the W tile [64|96|128 x 64] into a 128B-swizzled ring of up to 12 stages, warp 1 issues tcgen05.mma
+// traffic) and the W tile [64|96|128 x 64] into a 128B-swizzled 96 KB ring (4-6 stages), warp 1 issues tcgen05.mma
 // (M=128, N = tile width, K=16) into a TMEM accumulator, warps 2-5 (one per TMEM lane quadrant) drain it.  With the
 // 64-row box the MMA's rows 64..127 read the bytes that follow in the stage (the W tile): finite garbage that lands
 // in accumulator rows nobody reads.
@@ -24,8 +25,10 @@
 namespace hb200 {
 
 constexpr int SK_BM = 128, SK_BN = 128, SK_BK = 64;
-constexpr int SK_RING_BYTES = 192 * 1024;   // operand ring: as many stages of (A rows + tile width) x 64 as fit, at most 12
+constexpr int SK_RING_BYTES = 96 * 1024;   // operand ring: as many stages of (A rows + tile width) x 64 as fit, at most 12
 constexpr int SK_MAX_STAGES = 12;
+constexpr int SK_CTAS_PER_SM = 2;          // two CTAs share an SM, so the weight prefetch of the next contraction of a chain
+                                            // overlaps the tail of the current one
 constexpr int SK_THREADS = 6 * 32;          // producer, MMA issuer, 4 epilogue warps
 constexpr int SK_SMEM_BYTES = SK_RING_BYTES + 512 + 1024;
 constexpr int SK_MIN_KB_PER_SPLIT = 2;
@@ -47,7 +50,7 @@ static SkinnyPlan skinny_plan(int N, int K) {
     const int bn = cand[i][0], ks = cand[i][1];
     if (ks > 1 && k_blocks / ks < SK_MIN_KB_PER_SPLIT) continue;
     const int ctas = ceil_div(N, bn) * ks;
-    if (ctas > sms) continue;
+    if (ctas > SK_CTAS_PER_SM * sms) continue;
     if (ctas > best_ctas) { best = i; best_ctas = ctas; }   // earlier candidates (wider tile, fewer slices) win ties
   }
   SkinnyPlan s;
@@ -122,7 +125,7 @@ __device__ __forceinline__ void reduce_share(const GemmParams& p, uint32_t part_
   }
 }
 
-__global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_a,
+__global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                                     const __grid_constant__ CUtensorMap tma_b,
                                                                     const GemmParams p, int bn, int a_rows, int ksplit,
                                                                     int kb_per, int k_blocks) {
