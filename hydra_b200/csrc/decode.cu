@@ -303,9 +303,9 @@ __global__ void __launch_bounds__(256) decode_qk_finish_kernel(
 // Pass 1: one thread per cached key, logits of the G query heads of this kv head into shared memory, row maxima.
 // Pass 2: exponentials and row sums.  Pass 3: P V with 16-byte loads of V (lane = 8-dim chunk, key slices across
 // the rest of the CTA), reduced by shuffles and a small shared-memory table.  Exact softmax for any temperature.
-// STAGED: the cached K and V rows of this (sequence, kv head) are first copied into shared memory with cp.async (one
-// round trip with every 16-byte piece in flight at once, L1 bypassed) and both passes read them from there; used
-// whenever 2 x capacity x head_dim x 2 bytes fit next to the score table.
+// STAGED: the cached K rows of this (sequence, kv head) are first copied into shared memory with cp.async (one round
+// trip with every 16-byte piece in flight at once, L1 bypassed); once the logits exist the same buffer receives the V
+// rows while the exponentials are computed.  Used while all CTAs of the grid are resident at once.
 constexpr int DATT_THREADS = 256;
 constexpr int DATT_WARPS = DATT_THREADS / 32;
 constexpr int DATT_GMAX = 8;      // query heads per kv head
@@ -329,13 +329,10 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
   const __nv_bfloat16* vb = vcache + ((size_t)b * KV + kvh) * capacity * HD;
   // staged copies of the cached rows (16-byte aligned: the tables before them are multiples of 4 floats)
   const uint32_t stage_k = s_addr(sc + (size_t)((G * capacity + 3) & ~3));
-  const uint32_t stage_v = stage_k + (uint32_t)capacity * HD * 2;
+  const uint32_t stage_v = stage_k;              // V follows K in the same buffer (after pass 1)
+  const int pieces = n_keys * CH;
   if (STAGED) {
-    const int pieces = n_keys * CH;
-    for (int i = tid; i < pieces; i += DATT_THREADS) {
-      cp_async16(stage_k + (uint32_t)i * 16u, kb + (size_t)i * 8);
-      cp_async16(stage_v + (uint32_t)i * 16u, vb + (size_t)i * 8);
-    }
+    for (int i = tid; i < pieces; i += DATT_THREADS) cp_async16(stage_k + (uint32_t)i * 16u, kb + (size_t)i * 8);
     cp_async16_commit();
   }
   for (int i = tid; i < G * HD; i += DATT_THREADS)
@@ -391,6 +388,10 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
     mx[g] = v;
   }
   __syncthreads();
+  if (STAGED) {   // every thread is past pass 1: the K rows are dead, V takes their place while pass 2 runs
+    for (int i = tid; i < pieces; i += DATT_THREADS) cp_async16(stage_v + (uint32_t)i * 16u, vb + (size_t)i * 8);
+    cp_async16_commit();
+  }
   // pass 2 (each thread revisits the logits it wrote)
   float sum[DATT_GMAX];
 #pragma unroll
@@ -410,6 +411,7 @@ __global__ void __launch_bounds__(DATT_THREADS) decode_attention_kernel(
     const float v = warp_sum(sum[g]);
     if (lane == 0) red[warp * DATT_GMAX + g] = v;
   }
+  if (STAGED) cp_async16_wait_all();
   __syncthreads();
 #pragma unroll
   for (int g = 0; g < DATT_GMAX; ++g) {
@@ -471,10 +473,11 @@ static int launch_decode_attention(const __nv_bfloat16* qnew, const __nv_bfloat1
                                    __nv_bfloat16* o, const int32_t* pos, int B, int H, int KV, int capacity, float scale,
                                    cudaStream_t st, bool chain) {
   const size_t base = decode_attention_smem(HD, H / KV, capacity) + 16;
-  const size_t staged = base + (size_t)2 * capacity * HD * 2;
-  // staging costs one CTA per SM: worth it while the grid still fits in one wave (small batches, where the kernel is a
-  // latency chain); larger grids keep four CTAs per SM and stream from L2
-  if (staged <= 200 * 1024 && (long long)KV * B <= sm_count()) {
+  const size_t staged = base + (size_t)capacity * HD * 2;
+  // staging is worth it while every CTA of the grid is resident at once (the kernel is then a latency chain); larger
+  // grids keep the small footprint and stream from L2
+  const long long resident = staged <= 200 * 1024 ? (long long)sm_count() * ((226 * 1024) / (staged + 1024)) : 0;
+  if ((long long)KV * B <= resident) {
     HB_PROPAGATE(ensure_dynamic_smem((const void*)decode_attention_kernel<HD, true>, staged));
     return launch_chained(decode_attention_kernel<HD, true>, dim3(KV, B), dim3(DATT_THREADS), staged, st, chain, 1, qnew, kc,
                           vc, o, pos, H, KV, capacity, scale * 1.4426950408889634f);
