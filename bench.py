@@ -369,11 +369,32 @@ def main() -> None:
             args.batch = 8 if args.batch == 32 else args.batch
         args.impl = args.impl_gemm
         names = [n for n in microbench.CASES if n not in ("model_hidden", "decode", "gemm_skinny")] if args.micro == "all" else [args.micro]
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        rank = int(os.environ.get("RANK", "0"))
+        dist = None
+        if world > 1:
+            # replicas: every rank runs the same microbenchmark on its own GPU (sequences are sharded by rank, nothing
+            # is exchanged); the slowest rank's time is reported, tokens/s summed over the ranks
+            import torch.distributed as dist
+            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+            dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
         for nm in names:
             res = microbench.run(nm, args, ROOT)
-            if nm == "decode" and not args.no_cpu_baseline:
+            if dist is not None:
+                t = torch.tensor([res["ms"]], dtype=torch.float64, device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                res["ms"] = float(t.item())
+                res["n_gpus"] = world
+                if "decode_tok_per_s" in res:
+                    res["decode_tok_per_s"] = world * args.batch / (res["ms"] * 1e-3)
+                    res["scaling"] = "weak"
+            if nm == "decode" and not args.no_cpu_baseline and rank == 0:
                 res["cpu_baseline"] = cpu_generation_baseline(args.blocks, args.prompt)
-            print(json.dumps(res), flush=True)
+            if rank == 0:
+                print(json.dumps(res), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
         return
     args.scaling_mode = args.scaling
     if args.scaling == "strong":
