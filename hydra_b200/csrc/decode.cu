@@ -4,21 +4,28 @@
 // Per block and step (B sequences in lockstep, position p = *state.pos read from device memory by every kernel, so
 // the same launch sequence - and a CUDA graph of it - serves every step):
 //
-//   a    = AdaRMSNorm(x)                                       (dual_norm of the previous block / embed_norm)
-//   qkv  = a Wqkv^T                                            tcgen05 GEMM, M = B
+//   a    = AdaRMSNorm(x)                                       (exit norm of the previous block / embed_norm)
+//   qkv  = a Wqkv^T                                            skinny tcgen05 GEMM (gemm_skinny.cu), M = B
 //   conv prep: window of q|k rows p-4..p (halo + new row), grouped conv1 on its last three rows, written as the
 //              im2col rows [y1(p-2) | y1(p-1) | y1(p)] of the dense conv; value row [v_curr(p) | v_shift(p-1)] appended
 //              to the value cache; halo and v_shift advanced                         decode_conv_prep_kernel
-//   c2q  = im2col_q W2q^T,  c2k = im2col_k W2k^T               tcgen05 GEMMs (the repacked conv2 weights ARE the
+//   c2q  = im2col_q W2q^T                                      skinny GEMM (the repacked conv2 weights ARE the
 //                                                              [C_out, 3*C_in] matrices these products need)
-//   QK-mean, L2 norm, temperature, RoPE(p); key appended to the key cache            decode_qk_finish_kernel
+//   c2k  = im2col_k W2k^T (small: on the CUDA cores), QK-mean, L2 norm, temperature, RoPE(p); key appended to the
+//          key cache                                                                 decode_qk_finish_kernel
 //   o    = softmax(q K^T / sqrt(hd)) V over the p+1 cached positions                 decode_attention_kernel
-//   cur  = x + 0.5 * o Wo^T                                    tcgen05 GEMM, residual epilogue
-//   MoR depth, then per recursion: MoD score; "selected" iff fewer than k cached scores are >= the new score
-//   (k = int((p+1) * capacity), the newest position loses ties); norm-gather of the selected & active rows;
-//   gate_up / down GEMMs with the device-side row count                              row kernels shared with prefill
-//   x'   = RMSNorm(cur) (+ next block's input norm)
+//   cur  = x + 0.5 * o Wo^T                                    skinny GEMM, residual epilogue
+//   per recursion: MoR depth (first recursion), MoD score; "selected" iff fewer than k cached scores are >= the new
+//   score (k = int((p+1) * capacity), the newest position loses ties); gather-norm of the selected & active rows
+//                                                                                    decode_route_kernel
+//   gate_up / down skinny GEMMs with the device-side row count
+//   x'   = RMSNorm(cur) (+ next block's input norm)                                  decode_dual_norm_kernel
 // then the final norm, the output projection for the B rows, the greedy choice, and p += 1.
+//
+// The step is a chain of ~19 small launches per block, each a programmatic-dependent-launch link.  What bounds it is
+// the number of dependent memory round trips per kernel, not bytes or launches, so every kernel here requests its
+// static weights before the wait on its predecessor and everything else in one batch right after it; and because a
+// chained kernel starts before its predecessor ends, everything the chain writes is read through L2 only.
 #include <cmath>
 #include <utility>
 
@@ -192,7 +199,7 @@ __global__ void __launch_bounds__(256) decode_conv_prep_kernel(
   if (tid < half) vshift[(size_t)b * half + tid] = __float2bfloat16_rn(vnext);
 }
 
-// ---- QK finish: one CTA per sequence, one warp per head ----------------------------------------------------------
+// ---- QK finish: one CTA per sequence, hd/2 lanes per head ---------------------------------------------------------
 // Latency layout: the temperature and (when they fit in registers) this thread's share of the key conv weights are
 // static and requested before the wait; the q / k finishing runs lph = hd/2 lanes per head (one RoPE pair per lane),
 // i.e. up to four heads per warp side by side, so all heads of a sequence are done in one or two passes.
