@@ -110,11 +110,13 @@ class PackedModel:
     def __init__(self, *, vocab: int, dim: int, n_rec: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  ffn_hidden: int, min_depth: int, adaptive: bool, max_seq_len: int, mod_capacity: float,
                  norm_eps: float, residual_scale: float, output_scale: float, blocks: List[PackedBlock],
-                 tok_emb: Optional[Tensor], norm_w: Optional[Tensor], device, gemm_impl: int = 0):
+                 tok_emb: Optional[Tensor], norm_w: Optional[Tensor], device, gemm_impl: int = 0,
+                 lm_head: Optional[Tensor] = None):
         self.blocks = blocks
         self.block_array = (_lib.BlockWeights * len(blocks))(*[b.struct for b in blocks])
         self.cos, self.sin = rope_tables(max_seq_len, head_dim, device)
-        self.tok_emb, self.norm_w = tok_emb, norm_w
+        self.tok_emb, self.norm_w, self.lm_head = tok_emb, norm_w, lm_head
+        self.out_proj = lm_head if lm_head is not None else tok_emb      # weight of the output projection
         self.struct = _lib.Model(
             vocab=vocab, dim=dim, n_blocks=len(blocks), n_rec=n_rec, n_heads=n_heads, n_kv_heads=n_kv_heads,
             head_dim=head_dim, ffn_hidden=ffn_hidden, min_depth=min_depth, adaptive=int(adaptive),
@@ -123,7 +125,8 @@ class PackedModel:
             tok_emb=tok_emb.data_ptr() if tok_emb is not None else None,
             norm_w=norm_w.data_ptr() if norm_w is not None else None,
             rope_cos=self.cos.data_ptr(), rope_sin=self.sin.data_ptr(),
-            blocks=C.cast(self.block_array, C.POINTER(_lib.BlockWeights)))
+            blocks=C.cast(self.block_array, C.POINTER(_lib.BlockWeights)),
+            lm_head=lm_head.data_ptr() if lm_head is not None else None)
         self._ws: Dict[tuple, Tensor] = {}
         self.device = device
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)

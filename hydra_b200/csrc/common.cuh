@@ -14,6 +14,9 @@
 
 namespace hb200 {
 
+// Weight of the output projection: the untied matrix when the model carries one, else the embedding table.
+inline const void* output_weight(const hb200_model* m) { return m->lm_head ? m->lm_head : m->tok_emb; }
+
 // ---- host-side status plumbing ------------------------------------------------
 void set_error(const char* fmt, ...);   // defined in api.cu (thread-local buffer)
 

@@ -865,7 +865,7 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
   __nv_bfloat16* lg = last_logits ? (__nv_bfloat16*)last_logits : w.logits;
   bi_prof = m->n_blocks;
   { PS(HB200_K_GEMM_LM_HEAD, 0, m->vocab, D);
-  HB_PROPAGATE(dgemm(m, w, w.hid, m->tok_emb, lg, B, m->vocab, D, (int64_t)ld, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err,
+  HB_PROPAGATE(dgemm(m, w, w.hid, output_weight(m), lg, B, m->vocab, D, (int64_t)ld, EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err,
                      st, chain)); }
   { PS(HB200_K_OTHER, 1, m->vocab, 0);
   HB_PROPAGATE(launch_argmax_rows(lg, B, m->vocab, (int64_t)ld, ds->tokens, st, chain)); }

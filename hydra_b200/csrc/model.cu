@@ -433,7 +433,8 @@ static int run_model(const hb200_model* m, const int64_t* ids, int B, int S, con
   const int T = B * S, D = m->dim;
   int32_t* counts = (taps && taps->mlp_rows) ? taps->mlp_rows : w.counts;
   HB_CUDA(cudaMemsetAsync(counts, 0, (size_t)m->n_blocks * m->n_rec * 4, st));
-  HB_REQUIRE(aligned16(m->tok_emb) && m->norm_w != nullptr, HB200_ERR_INVALID, "model_forward: bad embedding / norm pointer");
+  HB_REQUIRE(aligned16(m->tok_emb) && aligned16(m->lm_head) && m->norm_w != nullptr, HB200_ERR_INVALID,
+             "model_forward: bad embedding / output projection / norm pointer");
   {
     // embedding fused with the first block's pre-attention norm
     ProfScope ps(m->profile, st, HB200_K_EMBED, -1, 0, T, D, 0);
@@ -453,7 +454,7 @@ static int run_model(const hb200_model* m, const int64_t* ids, int B, int S, con
     std::swap(xin, xout);
   }
   if (logits != nullptr)
-    HB_PROPAGATE(gemm(m, HB200_K_GEMM_LM_HEAD, m->n_blocks, 0, hid, m->tok_emb, logits, T, m->vocab, D, D, D, ld_logits,
+    HB_PROPAGATE(gemm(m, HB200_K_GEMM_LM_HEAD, m->n_blocks, 0, hid, output_weight(m), logits, T, m->vocab, D, D, D, ld_logits,
                       EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err_flag, st));
   return 0;
 }
@@ -514,7 +515,7 @@ extern "C" int hb200_model_prefill_cached(const hb200_model* m, const int64_t* i
              "prefill_cached: pass last_logits (the workspace cannot hold them for this shape)");
   prefill_tail_kernel<<<B, 128, 0, st>>>(w.ug, S, D, last, ids, state->history, state->capacity);
   HB_LAUNCH_CHECK();
-  HB_PROPAGATE(gemm(m, HB200_K_GEMM_LM_HEAD, m->n_blocks, 0, last, m->tok_emb, lg, B, m->vocab, D, D, D, ld_logits,
+  HB_PROPAGATE(gemm(m, HB200_K_GEMM_LM_HEAD, m->n_blocks, 0, last, output_weight(m), lg, B, m->vocab, D, D, D, ld_logits,
                     EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err_flag, st));
   HB_PROPAGATE(hb200_argmax_rows(lg, B, m->vocab, ld_logits, state->tokens, st));
   set_pos_kernel<<<ceil_div(B, 128), 128, 0, st>>>(state->pos, S, state->tokens, state->history, state->capacity, B);

@@ -98,7 +98,8 @@ def normalize_state_dict(obj) -> Dict[str, Tensor]:
     holding it under ``"model"`` / ``"model_state_dict"`` / ``"state_dict"``; ``_orig_mod.`` prefixes left by
     torch.compile are stripped; the older attention layouts (attention.py:333-383: ``q_down``/``k_down``/``v_down``
     (+``v_shift_down``) and flat ``q_conv1`` ... ``k_conv2``) are folded into ``qkv_proj`` / ``q_conv.conv1`` ...;
-    the tied ``output.weight`` and MoD bookkeeping buffers are dropped."""
+    MoD bookkeeping buffers are dropped, and so is ``output.weight`` when it is the tied embedding (same storage or
+    equal values); an untied projection (``tie_weights=False``, model.py:343-349) is kept."""
     sd = obj
     if isinstance(obj, dict):
         for key in ("model", "model_state_dict", "state_dict"):
@@ -126,9 +127,23 @@ def normalize_state_dict(obj) -> Dict[str, Tensor]:
                 if k.endswith(old):
                     out.setdefault(k[: -len(old)] + f"attention.{stem}_conv.conv{n}.weight", out.pop(k))
     for k in list(out):
-        if k == "output.weight" or k.endswith("._aux_loss") or ".mod_mlp_wrapper.mlp." in k:
+        if k.endswith("._aux_loss") or ".mod_mlp_wrapper.mlp." in k:
             out.pop(k)
+    if "output.weight" in out and "tok_emb.weight" in out:
+        o, e = out["output.weight"], out["tok_emb.weight"]
+        if o.data_ptr() == e.data_ptr() or (o.shape == e.shape and o.device == e.device and torch.equal(o, e)):
+            out.pop("output.weight")
     return out
+
+
+def _untied_output(sd: Dict[str, Tensor], dev) -> Optional[Tensor]:
+    """bf16 copy of an untied output projection left in a normalised state_dict, or None when the projection is tied."""
+    o = sd.get("output.weight")
+    if o is None:
+        return None
+    if tuple(o.shape) != tuple(sd["tok_emb.weight"].shape):
+        raise ValueError(f"output.weight {tuple(o.shape)} does not match tok_emb.weight {tuple(sd['tok_emb.weight'].shape)}")
+    return _bf16(o, dev)
 
 
 def load_checkpoint(path: str, **model_kwargs) -> "HydraB200Model":
@@ -174,7 +189,7 @@ class HydraB200Model:
                 norm_eps=norm_eps, residual_scale=0.5,
                 output_scale=float(os.environ.get("HYDRA_CCGQA_OUTPUT_SCALE", "1.0")), blocks=blocks,
                 tok_emb=_bf16(sd["tok_emb.weight"], dev), norm_w=_f32(sd["norm.weight"], dev), device=dev,
-                gemm_impl=gemm_impl)
+                gemm_impl=gemm_impl, lm_head=_untied_output(sd, dev))
         self.ld_logits = (V + 7) // 8 * 8
         self._logits: Optional[Tensor] = None
         self.last_taps: Optional[Taps] = None
@@ -313,7 +328,7 @@ class HydraB200Model:
             last = hid[:, -1, :].contiguous()
             with kernels._on(self.device):
                 st = kernels._stream(self.device)
-                _lib.check(lib.hb200_gemm_bf16(last.data_ptr(), self.packed.tok_emb.data_ptr(), last_logits.data_ptr(),
+                _lib.check(lib.hb200_gemm_bf16(last.data_ptr(), self.packed.out_proj.data_ptr(), last_logits.data_ptr(),
                                                B, self.vocab_size, self.dim, self.dim, self.dim, ld, _lib.EPI_STORE,
                                                None, 1.0, None, None, self.packed.struct.gemm_impl,
                                                self.packed.err_flag.data_ptr(), st), "lm_head (last position)")
@@ -407,7 +422,7 @@ class HydraB200BaseModel(HydraB200Model):
     tied output projection.  Runs on the same executor as the routed model: every block is a one-recursion block with
     a zero recursion offset, full residual scale, no routers and no exit norm.  ``state_dict`` keys:
     ``tok_emb.weight``, ``layers.{i}.attention.*``, ``layers.{i}.{norm1,norm2}.weight``, ``layers.{i}.mlp.*``,
-    ``norm.weight`` (``output.weight`` must be the tied embedding if present)."""
+    ``norm.weight``, and ``output.weight`` when the projection is untied."""
 
     def __init__(self, state_dict: Dict[str, Tensor], *, n_heads: int, n_kv_heads: int, compression_factor: int = 4,
                  max_seq_len: int = 2048, device: str | torch.device = "cuda", norm_eps: float = 1e-6,
@@ -418,8 +433,6 @@ class HydraB200BaseModel(HydraB200Model):
         if dev.index is None:
             dev = torch.device("cuda", torch.cuda.current_device())
         sd = normalize_state_dict(state_dict)
-        if "output.weight" in sd and not torch.equal(sd["output.weight"].cpu(), sd["tok_emb.weight"].cpu()):
-            raise NotImplementedError("HydraB200BaseModel: an untied output projection is not built")
         V, D = sd["tok_emb.weight"].shape
         nb = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("layers."))
         F = sd["layers.0.mlp.down.weight"].shape[1]
@@ -438,7 +451,7 @@ class HydraB200BaseModel(HydraB200Model):
                 min_depth=0, adaptive=False, max_seq_len=max_seq_len, mod_capacity=1.0, norm_eps=norm_eps,
                 residual_scale=1.0, output_scale=float(os.environ.get("HYDRA_CCGQA_OUTPUT_SCALE", "1.0")),
                 blocks=blocks, tok_emb=_bf16(sd["tok_emb.weight"], dev), norm_w=_f32(sd["norm.weight"], dev),
-                device=dev, gemm_impl=gemm_impl)
+                device=dev, gemm_impl=gemm_impl, lm_head=_untied_output(sd, dev))
         self.ld_logits = (V + 7) // 8 * 8
         self._logits = None
         self.last_taps = None

@@ -204,12 +204,14 @@ typedef struct hb200_model {
   int32_t vocab, dim, n_blocks, n_rec, n_heads, n_kv_heads, head_dim, ffn_hidden;
   int32_t min_depth, adaptive, max_seq_len, gemm_impl;
   float mod_capacity, norm_eps, residual_scale, output_scale;
-  const void* tok_emb;            /* bf16 [V, D] (also the tied output projection) */
+  const void* tok_emb;            /* bf16 [V, D] (also the output projection when lm_head is NULL) */
   const float* norm_w;            /* fp32 [D] */
   const float* rope_cos;          /* fp32 [max_seq_len, hd/2] */
   const float* rope_sin;
   const hb200_block_weights* blocks;   /* HOST array of n_blocks entries */
   void* profile;                  /* optional hb200_profile handle (see below), or NULL */
+  const void* lm_head;            /* bf16 [V, D] untied output projection (tie_weights=False, model.py:343-349),
+                                     or NULL: the output projection is tok_emb */
 } hb200_model;
 
 /* Optional routing taps / forced routing for one forward (device pointers or NULL). */

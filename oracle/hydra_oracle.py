@@ -495,7 +495,7 @@ def cached_prefill(ids: Tensor, p: Dict[str, Tensor], cfg: HydraConfig) -> Tuple
         cache.scores[key] = sc.clone()
     cache.pos = S
     hN = rms_norm(h, p["norm.weight"], cfg.norm_eps)
-    return hN @ p["tok_emb.weight"].transpose(0, 1), cache
+    return hN @ p.get("output.weight", p["tok_emb.weight"]).transpose(0, 1), cache
 
 
 def cached_decode_step(tokens: Tensor, p: Dict[str, Tensor], cfg: HydraConfig, cache: DecodeCache) -> Tensor:
@@ -555,7 +555,7 @@ def cached_decode_step(tokens: Tensor, p: Dict[str, Tensor], cfg: HydraConfig, c
         x = rms_norm(cur, p[pre + "final_norm.weight"], cfg.norm_eps)
     cache.pos = t + 1
     hN = rms_norm(x, p["norm.weight"], cfg.norm_eps)
-    return hN @ p["tok_emb.weight"].transpose(0, 1)
+    return hN @ p.get("output.weight", p["tok_emb.weight"]).transpose(0, 1)
 
 
 def cached_generate(prompt_ids: Tensor, p: Dict[str, Tensor], cfg: HydraConfig, max_new_tokens: int,

@@ -135,13 +135,13 @@ def gen_attention(name: str, dim: int, H: int, KV: int, B: int, S: int, seed: in
 
 # ----------------------------------------------------------------------------
 def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: int, mlp_ratio: float,
-              B: int, S: int, cap: float, seed: int) -> None:
+              B: int, S: int, cap: float, seed: int, tie: bool = True) -> None:
     from hydra.model.framework import HydraModel
 
     torch.manual_seed(seed)
     m = HydraModel(vocab_size=vocab, dim=dim, n_mor_blocks=NB, recursions_per_block=R, n_heads=H,
                    n_kv_heads=KV, compression_factor=4, mlp_ratio=mlp_ratio, max_seq_len=S,
-                   mod_capacity=cap)
+                   mod_capacity=cap, tie_weights=tie)
     g = torch.Generator().manual_seed(seed + 1)
     with torch.no_grad():
         for n, p in m.named_parameters():
@@ -194,7 +194,7 @@ def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: i
         arrs[f"mod_idx:{li}:{r}"] = torch.sort(idx, dim=1)[0].numpy().astype(np.int32)
         arrs[f"mod_scores:{li}:{r}"] = f32(sc)
     for kname, t in m.state_dict().items():
-        if kname == "output.weight" or "_aux_loss" in kname or ".mod_mlp_wrapper.mlp." in kname:
+        if (kname == "output.weight" and tie) or "_aux_loss" in kname or ".mod_mlp_wrapper.mlp." in kname:
             continue   # tied / alias / bookkeeping tensors
         arrs["w:" + kname] = to_bits(t) if t.dim() >= 2 and t.numel() > 4096 else f32(t)
 
@@ -281,6 +281,10 @@ if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "base":     # only the routing-free baseline model
         gen_base_model("base_model_hd16.npz", vocab=384, dim=256, n_layers=3, H=4, KV=2, mlp_ratio=1.0, B=2, S=112, seed=8)
         sys.exit(0)
+    if len(sys.argv) > 1 and sys.argv[1] == "untied":   # only the model with its own output projection
+        gen_model("model_untied.npz", vocab=200, dim=256, NB=3, R=2, H=4, KV=2, mlp_ratio=1.0,
+                  B=2, S=64, cap=0.75, seed=21, tie=False)
+        sys.exit(0)
     gen_fused_ops()
     # config-2 shapes (dim 1024, 8q/2kv, hd 32) at a short sequence; temperature 1.0 as in the CCGQA block microbenchmark
     gen_attention("ccgqa_hd32.npz", 1024, 8, 2, 1, 80, seed=1, temperature=1.0)
@@ -296,3 +300,6 @@ if __name__ == "__main__":
     gen_model("model_hd32.npz", vocab=384, dim=256, NB=3, R=4, H=2, KV=1, mlp_ratio=1.0,
               B=2, S=96, cap=0.5, seed=5)
     gen_base_model("base_model_hd16.npz", vocab=384, dim=256, n_layers=3, H=4, KV=2, mlp_ratio=1.0, B=2, S=112, seed=8)
+    # tie_weights=False: the output projection is a matrix of its own
+    gen_model("model_untied.npz", vocab=200, dim=256, NB=3, R=2, H=4, KV=2, mlp_ratio=1.0,
+              B=2, S=64, cap=0.75, seed=21, tie=False)

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layouts_match_header_sizes():
     from hydra_b200 import _lib
     assert ctypes.sizeof(_lib.BlockWeights) == 16 * 8 + 8      # 16 pointers + one float, padded
-    assert ctypes.sizeof(_lib.Model) == 12 * 4 + 4 * 4 + 6 * 8
+    assert ctypes.sizeof(_lib.Model) == 12 * 4 + 4 * 4 + 7 * 8
     assert ctypes.sizeof(_lib.Taps) == 6 * 8 + 8
     assert ctypes.sizeof(_lib.LaunchRecord) == 24
     assert ctypes.sizeof(_lib.DecodeState) == 2 * 4 + 8 * 8    # batch, capacity, eight device pointers
@@ -111,12 +111,16 @@ def test_legacy_checkpoint_layouts_are_remapped():
     assert torch.equal(m.qkv_proj.weight, want)
     assert torch.equal(m.q_conv.conv2.weight, legacy["q_conv2.weight"]) and torch.equal(m.k_conv.conv1.weight, legacy["k_conv1.weight"])
     payload = {"model": {"_orig_mod.layers.0.attention." + k: v for k, v in legacy.items()}, "step": 7}
-    payload["model"]["_orig_mod.output.weight"] = torch.zeros(2, 2)
+    emb = torch.randn(6, 4, generator=g)
+    payload["model"]["_orig_mod.tok_emb.weight"] = emb
+    payload["model"]["_orig_mod.output.weight"] = emb.clone()            # a tied projection saved twice
     payload["model"]["_orig_mod.layers.0.mod_mlp_wrapper.mod_router._aux_loss"] = torch.zeros(())
     sd = normalize_state_dict(payload)
     assert "layers.0.attention.qkv_proj.weight" in sd and torch.equal(sd["layers.0.attention.qkv_proj.weight"], want)
     assert "layers.0.attention.q_conv.conv1.weight" in sd and "output.weight" not in sd
     assert not any("_aux_loss" in k or "q_down" in k or "_orig_mod" in k for k in sd)
+    payload["model"]["_orig_mod.output.weight"] = emb + 1.0              # tie_weights=False: kept
+    assert torch.equal(normalize_state_dict(payload)["output.weight"], emb + 1.0)
 
 
 def test_product_path_refuses_cpu_tensors():

@@ -319,3 +319,34 @@ def test_base_model_without_routing():
     clear = ((margin[..., 0] - margin[..., 1]) > 0.06).cpu()
     assert torch.equal(b[:, 30:].cpu()[clear], full[:, 29:].argmax(-1).cpu()[clear])
     assert a.shape == b.shape
+
+
+def test_untied_output_projection():
+    """tie_weights=False (model.py:343-349): logits come from output.weight, not the embedding table - prefill against
+    the reference's golden logits, the last-position projections of both generation modes, and the state_dict rule
+    (an output.weight equal to the embedding is dropped as tied, a different one is kept)."""
+    from hydra_b200.model import normalize_state_dict
+    fx, cfg, w = G.model_fixture("model_untied.npz")
+    assert "output.weight" in normalize_state_dict(w)
+    tied = dict(w)
+    tied["output.weight"] = w["tok_emb.weight"].clone()
+    assert "output.weight" not in normalize_state_dict(tied)
+    ids = torch.from_numpy(fx["ids"])
+    m = build(w, cfg)
+    assert m.packed.lm_head is not None and m.packed.out_proj is m.packed.lm_head
+    ref_err = (float(fx["ref_bf16_maxabs"][0]), float(fx["ref_bf16_rel_l2"][0]))
+    lg, _ = compare_with_oracle(m, w, cfg, ids, torch.from_numpy(fx["logits"]), ref_err, "untied")
+    h = m.forward_hidden(ids.cuda()).float().cpu()
+    assert rel_l2(h @ w["output.weight"].T, lg) < 5e-3
+    assert rel_l2(h @ w["tok_emb.weight"].T, lg) > 0.5          # the embedding table would give other logits
+    # generation: re-forward mode picks the argmax of the untied projection; cached mode against the oracle
+    prompt = ids[:, 2:22].clamp(0, cfg.vocab_size - 1)
+    seq = m.generate(prompt.cuda(), 3).cpu()
+    ref_seq, margins = O.greedy_generate(prompt, w, cfg, 3, return_margins=True)
+    for b in range(prompt.shape[0]):
+        for i in range(3):
+            if int(seq[b, 20 + i]) != int(ref_seq[b, 20 + i]):
+                assert float(margins[b, i]) < 0.06, f"row {b} step {i}: token differs with a clear margin"
+                break    # diverged: later steps see different inputs
+    from tests.test_gpu_decode import check_against_oracle
+    check_against_oracle(m, w, cfg, prompt, 5, "untied cached decode")

@@ -48,3 +48,17 @@ def test_cached_decode_with_mod_is_a_close_approximation():
     seq_r = O.greedy_generate(prompt, w, cfg, n)
     agree = float((seq_c[:, 24:] == seq_r[:, 24:]).float().mean())
     assert agree >= 0.5, f"greedy-token agreement {agree:.2f}"
+
+
+def test_cached_decode_with_an_untied_output_projection():
+    """tie_weights=False: the cached path projects with output.weight, as the forward does."""
+    fx, cfg, w = G.model_fixture("model_untied.npz")
+    cfg.mod_capacity = 1.0
+    prompt = torch.from_numpy(fx["ids"])[:, :11].clamp(0, cfg.vocab_size - 1)
+    seq_c, logits_c = O.cached_generate(prompt, w, cfg, 4, return_logits=True)
+    seq_r = prompt.clone()
+    for step in range(4):
+        full = O.model_forward(seq_r, w, cfg)[:, -1]
+        assert float((full - logits_c[:, step]).abs().max()) < 2e-4
+        seq_r = torch.cat([seq_r, full.argmax(-1, keepdim=True)], dim=1)
+    assert torch.equal(seq_c, seq_r)

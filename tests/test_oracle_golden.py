@@ -50,9 +50,13 @@ def test_ccgqa_attention(name):
     close(O.ccgqa_forward(x, w, "attn.", cfg), fx["y"])
 
 
-@pytest.mark.parametrize("name", ["model_hd16.npz", "model_hd32.npz"])
+@pytest.mark.parametrize("name", ["model_hd16.npz", "model_hd32.npz", "model_untied.npz"])
 def test_model_forward_and_routing(name):
     fx, cfg, w = G.model_fixture(name)
+    # model_untied.npz was made with tie_weights=False: the output projection is a matrix of its own
+    assert ("output.weight" in w) == (name == "model_untied.npz")
+    if "output.weight" in w:
+        assert not torch.equal(w["output.weight"], w["tok_emb.weight"])
     ids = torch.from_numpy(fx["ids"])
     taps = O.RoutingTaps()
     logits = O.model_forward(ids, w, cfg, taps=taps)
@@ -76,7 +80,7 @@ def test_model_forward_and_routing(name):
     assert len(np.unique(np.concatenate([fx[f"depths:{i}"].ravel() for i in range(cfg.n_mor_blocks)]))) >= 2
 
 
-@pytest.mark.parametrize("name", ["model_hd16.npz", "model_hd32.npz"])
+@pytest.mark.parametrize("name", ["model_hd16.npz", "model_hd32.npz", "model_untied.npz"])
 def test_model_fixed_depth_and_min_depth(name):
     fx, cfg, w = G.model_fixture(name)
     ids = torch.from_numpy(fx["ids"])
