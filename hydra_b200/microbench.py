@@ -351,8 +351,32 @@ def decode(args) -> dict:
                     % (prefill_ms, weight_bytes / 1e9, kv_bytes / 1e9)}
 
 
+def sample_rows(args) -> dict:
+    """Next-token sampling (temperature 0.8, top-k 50, top-p 0.9: the reference sampler's defaults) and the greedy
+    argmax on --batch logit rows of 50257 bf16 columns: one read of the rows is the algorithmic traffic."""
+    from .sampling import sample_rows as sample
+    B, V, ld = int(args.batch), 50257, 50264
+    ns = _sets(B * ld * 2)
+    xs = [_rand_bf16(B, ld, scale=2.5, seed=i) for i in range(ns)]
+    u = torch.rand(B, device="cuda")
+    out = torch.empty(B, dtype=torch.int64, device="cuda")
+    lib = _lib.lib()
+    sample(xs[0], 0.8, 50, 0.9, uniforms=u, vocab=V, out=out)           # the public wrapper once; timed below without it
+
+    def call(i, t, k, p):
+        _lib.check(lib.hb200_sample_rows(xs[i % ns].data_ptr(), B, V, ld, t, k, p, u.data_ptr(), out.data_ptr(), _stream()))
+    ms = _time(lambda i: call(i, 0.8, 50, 0.9), args.iters)
+    ms_nuc = _time(lambda i: call(i, 1.0, 0, 0.9), args.iters)
+    ms_arg = _time(lambda i: _lib.check(lib.hb200_argmax_rows(xs[i % ns].data_ptr(), B, V, ld, out.data_ptr(), _stream())),
+                   args.iters)
+    nbytes = 2.0 * B * V
+    return {"kernel": "sample_rows_kernel", "shape": [B, V], "ms": ms, "bound": "hbm",
+            "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "algorithmic_bytes": nbytes,
+            "ms_nucleus_only": ms_nuc, "ms_argmax_rows": ms_arg}
+
+
 CASES: Dict[str, Callable] = {
-    "decode": decode, "gemm_skinny": gemm_skinny,
+    "decode": decode, "gemm_skinny": gemm_skinny, "sample_rows": sample_rows,
     "gemm": gemm, "ccgqa_block": ccgqa_block, "pre_attention": pre_attention, "attention": attention,
     "rms_norm": rms_norm, "rope": rope, "swiglu_ffn": swiglu_ffn, "swiglu_act": swiglu_act,
     "model_hidden": model_hidden,

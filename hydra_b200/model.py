@@ -19,6 +19,7 @@ import torch
 
 from . import _lib, kernels
 from ._pack import PackedBlock, PackedModel, _bf16, _f32
+from .sampling import sample_rows
 
 Tensor = torch.Tensor
 
@@ -296,9 +297,14 @@ class HydraB200Model:
         torch.cuda.current_stream(self.device).synchronize()
         return out_host
 
-    def generate(self, prompt_ids: Tensor, max_new_tokens: int, mode: str = "reforward", use_graph: bool = True) -> Tensor:
-        """Greedy generation.  ``mode="reforward"`` (default) is the reference's way; ``mode="cached"`` runs
+    def generate(self, prompt_ids: Tensor, max_new_tokens: int, mode: str = "reforward", use_graph: bool = True,
+                 temperature: Optional[float] = None, top_k: int = 50, top_p: float = 0.9,
+                 generator: Optional[torch.Generator] = None) -> Tensor:
+        """Generation.  ``mode="reforward"`` (default) is the reference's way; ``mode="cached"`` runs
         :meth:`generate_cached` (latent-space KV cache; an addition the reference does not have).
+        ``temperature=None`` (default) chooses greedily; a number turns on the reference's sampler
+        (diagnostics/eval_checkpoint.py:133-155: temperature, ``top_k``, ``top_p``; its defaults are 0.8 / 50 / 0.9)
+        with uniform numbers drawn from ``generator`` (:func:`hydra_b200.sampling.sample_rows`).
 
         Re-forward: the whole sequence is run through the model again for every new
         token (diagnostics/eval_checkpoint.py:127-160 re-forwards ``generated`` each step; the reference has no KV
@@ -307,7 +313,8 @@ class HydraB200Model:
         (temperature -> 0): next token = argmax of the last position's logits.
         prompt_ids int64 [B, P] on this device -> int64 [B, P + max_new_tokens]."""
         if mode == "cached":
-            return self.generate_cached(prompt_ids, max_new_tokens, use_graph=use_graph)
+            return self.generate_cached(prompt_ids, max_new_tokens, use_graph=use_graph, temperature=temperature,
+                                        top_k=top_k, top_p=top_p, generator=generator)
         if mode != "reforward":
             raise ValueError(f"unknown generation mode {mode!r} (use 'reforward' or 'cached')")
         if not prompt_ids.is_cuda or prompt_ids.device != self.device:
@@ -332,8 +339,12 @@ class HydraB200Model:
                                                B, self.vocab_size, self.dim, self.dim, self.dim, ld, _lib.EPI_STORE,
                                                None, 1.0, None, None, self.packed.struct.gemm_impl,
                                                self.packed.err_flag.data_ptr(), st), "lm_head (last position)")
-                _lib.check(lib.hb200_argmax_rows(last_logits.data_ptr(), B, self.vocab_size, ld, nxt.data_ptr(), st),
-                           "argmax_rows")
+                if temperature is None:
+                    _lib.check(lib.hb200_argmax_rows(last_logits.data_ptr(), B, self.vocab_size, ld, nxt.data_ptr(), st),
+                               "argmax_rows")
+                else:
+                    sample_rows(last_logits, temperature, top_k, top_p, generator=generator, vocab=self.vocab_size,
+                                out=nxt)
             seq[:, cur] = nxt
         return seq
 
@@ -343,8 +354,9 @@ class HydraB200Model:
         return DecodeSession(self, batch, capacity)
 
     def generate_cached(self, prompt_ids: Tensor, max_new_tokens: int, use_graph: bool = True,
-                        return_logits: bool = False):
-        """Greedy generation with the latent-space KV cache: one prefill of the prompt, then one decode step per new
+                        return_logits: bool = False, temperature: Optional[float] = None, top_k: int = 50,
+                        top_p: float = 0.9, generator: Optional[torch.Generator] = None):
+        """Generation (greedy, or sampled when ``temperature`` is a number) with the latent-space KV cache: one prefill of the prompt, then one decode step per new
         token that touches only the newest position.  With ``mod_capacity == 1`` a step computes what the re-forward
         computes for that position; with capacity < 1 a past token's MoD selection stays as decided when that token was
         the newest (the re-forward re-decides it over the longer sequence), so the two modes may diverge.
@@ -362,10 +374,14 @@ class HydraB200Model:
         keep = [] if return_logits else None
         if n_new > 0:
             sess.prefill(prompt_ids)
+            if temperature is not None:
+                sess.resample(temperature, top_k, top_p, generator=generator)
             if keep is not None:
                 keep.append(sess.last_logits[:, :self.vocab_size].clone())
             for _ in range(n_new - 1):
                 sess.step(use_graph=use_graph)
+                if temperature is not None:
+                    sess.resample(temperature, top_k, top_p, generator=generator)
                 if keep is not None:
                     keep.append(sess.last_logits[:, :self.vocab_size].clone())
             seq = sess.history[:, :total].clone()
@@ -514,6 +530,18 @@ class DecodeSession:
                 "model_prefill_cached")
         self.pos = P
         self._graph = None
+
+    def resample(self, temperature: float = 0.8, top_k: int = 50, top_p: float = 0.9,
+                 uniforms: Optional[Tensor] = None, generator: Optional[torch.Generator] = None) -> Tensor:
+        """Replace the greedy choice made by the latest ``prefill`` / ``step`` with a draw from ``last_logits``
+        (the reference's sampler, :func:`hydra_b200.sampling.sample_rows`): the next ``step`` processes the drawn
+        tokens, and ``history`` records them.  Returns the tokens (the session's own buffer)."""
+        if self.pos < 1 or self.pos >= self.capacity:
+            raise RuntimeError("resample() needs a prefill first and room for the chosen token in the history")
+        sample_rows(self.last_logits, temperature, top_k, top_p, uniforms=uniforms, generator=generator,
+                    vocab=self.model.vocab_size, out=self.tokens)
+        self.history[:, self.pos] = self.tokens
+        return self.tokens
 
     def _launch_step(self) -> None:
         m = self.model

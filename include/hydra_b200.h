@@ -175,6 +175,17 @@ int hb200_embed(const int64_t* ids, const void* table, void* out, int64_t T, int
  * (diagnostics/eval_checkpoint.py:112-166) in its deterministic, temperature-free form. */
 int hb200_argmax_rows(const void* x, int64_t rows, int cols, int64_t ld, int64_t* out, void* stream);
 
+/* The sampling step of the reference's generation helper (diagnostics/eval_checkpoint.py:133-155) for bf16 rows:
+ * logits / temperature; top_k > 0: values below the k-th largest are removed (ties with it stay); top_p < 1: in
+ * descending order a token is removed iff the probability mass before it exceeds top_p (the first always stays),
+ * probabilities being the softmax of what top-k left; then one draw from the renormalised rest.  The reference draws
+ * with torch.multinomial; here out[r] is the inverse CDF, in descending-logit order with equal logits by ascending
+ * index, at uniforms[r] in [0,1) (device fp32 [rows]) - a function of (row, uniform), reproducible on any stream.
+ * temperature <= 0 or top_k == 1 gives the argmax (uniforms may then be NULL).  cols <= 65535.  Arithmetic: fp32
+ * exponentials of the bf16 logits, masses accumulated exactly in 64-bit fixed point. */
+int hb200_sample_rows(const void* logits, int64_t rows, int cols, int64_t ld, float temperature, int top_k,
+                      float top_p, const float* uniforms, int64_t* out, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Whole block / whole model  (hydra/model/framework/blocks.py:608-632,
  *                             hydra/model/framework/model.py:408-506)

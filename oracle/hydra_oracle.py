@@ -414,6 +414,44 @@ def greedy_generate(prompt_ids: Tensor, p: Dict[str, Tensor], cfg: HydraConfig, 
     return seq
 
 
+def sample_filter(logits: Tensor, temperature: float, top_k: int, top_p: float) -> Tensor:
+    """The filtering of the reference's sampler (diagnostics/eval_checkpoint.py:133-151) on [B, V] logits: divide by
+    the temperature, remove what lies below the k-th largest value (``top_k > 0``; ties with it stay), then in
+    descending order remove a token iff the probability mass up to and including its predecessor exceeds ``top_p``
+    (the first always stays).  Removed entries are -inf.  Equal logits are ordered by ascending token id."""
+    x = logits.to(torch.float32) / temperature
+    if top_k > 0:
+        kth = torch.topk(x, min(int(top_k), x.shape[-1]))[0][..., -1, None]
+        x = x.masked_fill(x < kth, float("-inf"))
+    if top_p < 1.0:
+        sorted_logits, sorted_idx = torch.sort(x, descending=True, stable=True)
+        cum = torch.cumsum(torch.softmax(sorted_logits, dim=-1), dim=-1)
+        rem = cum > top_p
+        rem[..., 1:] = rem[..., :-1].clone()
+        rem[..., 0] = False
+        x = x.masked_fill(rem.scatter(1, sorted_idx, rem), float("-inf"))
+    return x
+
+
+def sample_next_token(logits: Tensor, temperature: float, top_k: int, top_p: float, uniforms: Tensor) -> Tensor:
+    """One draw per row from softmax(sample_filter(...)) (eval_checkpoint.py:153-155).  The reference draws with
+    torch.multinomial; this draw is the inverse CDF in descending-logit order (equal logits by ascending id) at
+    ``uniforms`` [B] in [0, 1): the first token whose cumulative probability exceeds the uniform number.
+    ``temperature <= 0`` or ``top_k == 1``: the argmax (lowest id among equal maxima)."""
+    if not temperature > 0.0 or top_k == 1:
+        m = logits.max(dim=-1, keepdim=True).values
+        return (logits == m).to(torch.int64).argmax(dim=-1)
+    x = sample_filter(logits, temperature, top_k, top_p)
+    sx, si = torch.sort(x, descending=True, stable=True)
+    cdf = torch.cumsum(torch.softmax(sx.to(torch.float64), dim=-1), dim=-1)
+    kept = torch.isfinite(sx).sum(dim=-1)
+    j = (cdf > uniforms.to(torch.float64)[:, None]).to(torch.int64).argmax(dim=-1)
+    j = torch.minimum(j, kept - 1)
+    miss = ~(cdf > uniforms.to(torch.float64)[:, None]).any(dim=-1)      # rounding left the last cdf entry below u
+    j = torch.where(miss, kept - 1, j)
+    return si.gather(1, j[:, None])[:, 0]
+
+
 # ----------------------------------------------------------------------------
 # cached (incremental) decode - NOT in the reference
 # ----------------------------------------------------------------------------

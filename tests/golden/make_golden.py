@@ -272,6 +272,58 @@ def gen_base_model(name: str, *, vocab: int, dim: int, n_layers: int, H: int, KV
     save(name, **arrs)
 
 
+def gen_sampler(name: str = "sampler.npz") -> None:
+    """The filtered next-token distribution of the reference's generation helper (diagnostics/eval_checkpoint.py:
+    111-166).  generate_text is run with a stand-in model that returns prepared logits and a stand-in tokenizer, and
+    torch.multinomial is replaced for the call by a recorder that keeps the probabilities it is handed (and returns the
+    most probable token), so what is stored is exactly what the reference would draw from."""
+    import diagnostics.eval_checkpoint as E
+
+    V = 1024
+    g = torch.Generator().manual_seed(31)
+    settings = [(0.8, 50, 0.9), (1.0, 0, 0.9), (0.7, 20, 1.0), (1.3, 0, 1.0), (0.5, 5, 0.5), (1.0, 200, 0.95),
+                (2.0, 1000, 0.99), (0.25, 3, 0.1)]
+    rows_per = 3
+    logits, probs, used = [], [], []
+    for (temp, k, p) in settings:
+        rows = bf16_round_(torch.randn(rows_per, V, generator=g) * 3.0)
+        rows[1, :40] = rows[1, 40]                       # a block of equal logits (ties at the thresholds)
+        rec = []
+
+        class Model(torch.nn.Module):
+            calls = 0
+
+            def forward(self, ids):
+                r = rows[Model.calls]
+                Model.calls += 1
+                return r.view(1, 1, V).expand(1, ids.shape[1], V).clone()
+
+        class Tok:
+            eos_token_id = -1
+
+            def encode(self, prompt, return_tensors="pt"):
+                return torch.zeros(1, 1, dtype=torch.int64)
+
+            def decode(self, ids, skip_special_tokens=True):
+                return ""
+
+        def recorder(pr, num_samples=1):
+            rec.append(pr.clone())
+            return pr.argmax(dim=-1, keepdim=True)
+
+        keep = torch.multinomial
+        torch.multinomial = recorder
+        try:
+            E.generate_text(Model(), Tok(), "x", max_new_tokens=rows_per, temperature=temp, top_k=k, top_p=p, device="cpu")
+        finally:
+            torch.multinomial = keep
+        assert len(rec) == rows_per
+        logits.append(rows)
+        probs.append(torch.cat(rec, dim=0))
+        used.extend([(temp, k, p)] * rows_per)
+    save(name, logits=f32(torch.cat(logits)), probs=f32(torch.cat(probs)), settings=np.array(used, dtype=np.float64))
+
+
 if __name__ == "__main__":
     try:
         import hydra  # noqa: F401
@@ -280,6 +332,9 @@ if __name__ == "__main__":
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     if len(sys.argv) > 1 and sys.argv[1] == "base":     # only the routing-free baseline model
         gen_base_model("base_model_hd16.npz", vocab=384, dim=256, n_layers=3, H=4, KV=2, mlp_ratio=1.0, B=2, S=112, seed=8)
+        sys.exit(0)
+    if len(sys.argv) > 1 and sys.argv[1] == "sampler":  # only the sampler's filtered distributions
+        gen_sampler()
         sys.exit(0)
     if len(sys.argv) > 1 and sys.argv[1] == "untied":   # only the model with its own output projection
         gen_model("model_untied.npz", vocab=200, dim=256, NB=3, R=2, H=4, KV=2, mlp_ratio=1.0,
@@ -303,3 +358,4 @@ if __name__ == "__main__":
     # tie_weights=False: the output projection is a matrix of its own
     gen_model("model_untied.npz", vocab=200, dim=256, NB=3, R=2, H=4, KV=2, mlp_ratio=1.0,
               B=2, S=64, cap=0.75, seed=21, tie=False)
+    gen_sampler()

@@ -130,3 +130,45 @@ def test_base_model_without_routing_matches_reference():
     for i, bo in enumerate(taps):
         r = torch.from_numpy(fx[f"block_out:{i}"])
         assert float((bo - r).abs().max()) <= 5e-6 * max(1.0, float(r.abs().max())), f"block {i}"
+
+
+def test_sampler_filter_matches_the_reference_distributions():
+    """tests/golden/sampler.npz holds the probabilities the reference's generate_text handed to torch.multinomial
+    (diagnostics/eval_checkpoint.py:133-153) for prepared logits.  The oracle's filter must keep the same number of
+    tokens with the same probabilities; which of several equal logits straddling the nucleus edge stays is the one
+    thing the reference leaves to its sort, so membership may differ there and only there."""
+    fx = G.load("sampler.npz")
+    lg, pr, st = torch.from_numpy(fx["logits"]), torch.from_numpy(fx["probs"]), fx["settings"]
+    differing = 0
+    for r in range(lg.shape[0]):
+        t, k, p = float(st[r, 0]), int(st[r, 1]), float(st[r, 2])
+        q = torch.softmax(O.sample_filter(lg[r:r + 1], t, k, p), dim=-1)[0]
+        assert int((q > 0).sum()) == int((pr[r] > 0).sum()), f"row {r}: kept-token count"
+        close(q.sort().values, pr[r].sort().values.numpy(), 1e-6)
+        diff = (q > 0) != (pr[r] > 0)
+        if diff.any():
+            differing += 1
+            assert len(set(lg[r][diff].tolist())) == 1, f"row {r}: membership differs beyond one tied logit value"
+        else:
+            close(q, pr[r].numpy(), 1e-6)
+    assert differing < lg.shape[0] // 2
+
+
+def test_sampler_draw_is_the_inverse_cdf():
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(3, 50, generator=g)
+    # u -> 0 picks the most probable token, u -> 1 the least probable kept one
+    lo = O.sample_next_token(x, 1.0, 10, 1.0, torch.zeros(3))
+    assert torch.equal(lo, x.argmax(-1))
+    hi = O.sample_next_token(x, 1.0, 10, 1.0, torch.full((3,), 0.9999999))
+    assert torch.equal(hi, x.topk(10).indices[:, -1])
+    # greedy limits
+    assert torch.equal(O.sample_next_token(x, 0.0, 0, 1.0, torch.rand(3)), x.argmax(-1))
+    assert torch.equal(O.sample_next_token(x, 0.8, 1, 0.9, torch.rand(3)), x.argmax(-1))
+    # frequencies over many uniforms follow softmax(filtered)
+    row = torch.randn(1, 30, generator=g)
+    n = 20000
+    draws = O.sample_next_token(row.expand(n, -1), 0.8, 8, 0.9, torch.rand(n, generator=g))
+    probs = torch.softmax(O.sample_filter(row, 0.8, 8, 0.9), -1)[0]
+    freq = torch.bincount(draws, minlength=30).double() / n
+    assert float(freq[probs == 0].sum()) == 0.0 and float((freq - probs).abs().max()) < 0.02
