@@ -185,6 +185,48 @@ static int capture_attention_state(const hb200_model* m, int bi, const Workspace
 
 // x: block input; a_in: AdaRMSNorm(x; norm1) if the caller already has it (else computed here);
 // y: block output; next_w / a_next: optional gain and destination of the norm that consumes y next.
+// Static routing (dense compute, soft weights), one thread per 8 columns of a row:
+//   cur += q * mlp + (1 - q) * u   with q = sigmoid(clamp(score, -10, 10)) in a MoD block (blocks.py:190-241), else q = 1;
+//   out (+)= w_r * cur             with the soft depth weight w_r = exp(-(d - r)^2) / (sum_j exp(-(d - j)^2) + 1e-8),
+//                                  d = sigmoid(3 tanh(l / 2)) * (R - 1)  (mixture_of_recursions.py:482-558).
+template <bool HAS_MOD, bool HAS_OUT>
+__global__ void __launch_bounds__(256) static_update_kernel(__nv_bfloat16* __restrict__ cur,
+                                                            const __nv_bfloat16* __restrict__ mlp,
+                                                            const __nv_bfloat16* __restrict__ u,
+                                                            const float* __restrict__ scores,
+                                                            const float* __restrict__ logits,
+                                                            __nv_bfloat16* __restrict__ out, int64_t T, int D, int r, int R) {
+  const int per_row = D / 8;
+  const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= T * per_row) return;
+  const int64_t t = idx / per_row;
+  const int64_t at = t * D + (idx - t * per_row) * 8;
+  float q = 1.f, wr = 0.f;
+  if (HAS_MOD) q = 1.f / (1.f + expf(-fminf(fmaxf(scores[t], -10.f), 10.f)));
+  if (HAS_OUT) {
+    const float d = (float)(R - 1) / (1.f + expf(-3.f * tanhf(0.5f * logits[t])));
+    float sum = 0.f;
+    for (int j = 0; j < R; ++j) {
+      const float e = expf(-(d - (float)j) * (d - (float)j));
+      sum += e;
+      if (j == r) wr = e;
+    }
+    wr /= sum + 1e-8f;
+  }
+  float c[8], m[8], un[8], o[8];
+  load_bf16x8(cur + at, c);
+  load_bf16x8(mlp + at, m);
+  if (HAS_MOD) load_bf16x8(u + at, un);
+  if (HAS_OUT && r > 0) load_bf16x8(out + at, o);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    c[j] += HAS_MOD ? q * m[j] + (1.f - q) * un[j] : m[j];
+    if (HAS_OUT) o[j] = (r > 0 ? o[j] : 0.f) + wr * c[j];
+  }
+  store_bf16x8(cur + at, c);
+  if (HAS_OUT) store_bf16x8(out + at, o);
+}
+
 static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, const __nv_bfloat16* a_in,
                          __nv_bfloat16* y, const float* next_w, __nv_bfloat16* a_next, int B, int S,
                          const Workspace& w, const hb200_taps* taps, int32_t* counts, int32_t* err, cudaStream_t st,
@@ -211,7 +253,12 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
   float* logits = (taps && taps->router_logits) ? taps->router_logits + (size_t)bi * T : w.logits;
   if (force) HB_REQUIRE(taps->depths != nullptr, HB200_ERR_INVALID, "forced routing needs taps.depths");
   if (force && has_mod) HB_REQUIRE(taps->mod_idx != nullptr, HB200_ERR_INVALID, "forced routing needs taps.mod_idx");
-  if (!m->adaptive && !force) {
+  const bool stat = m->static_routing != 0;
+  if (stat) {
+    HB_REQUIRE(!force, HB200_ERR_INVALID, "static routing makes no routing decisions to replay");
+    HB_REQUIRE(ds == nullptr, HB200_ERR_UNSUPPORTED, "static routing: cached decode is not built (use the re-forward mode)");
+  }
+  if ((!m->adaptive || stat) && !force) {                  // static routing: every token runs every recursion
     ProfScope ps(m->profile, st, HB200_K_OTHER, bi, 0, T, 0, 0);
     fill_i32_kernel<<<(unsigned)ceil_div(T, 256), 256, 0, st>>>(depth, T, R - 1);
     HB_LAUNCH_CHECK();
@@ -226,7 +273,7 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
 #define HB_SCORE(MOD_, ROUTER_)                                                                                   \
   HB_DISPATCH_NCH(D, mor_score_kernel<NCH, MOD_, ROUTER_><<<(unsigned)ceil_div(T, 8 * SCORE_ROWS), 256, 0, st>>>( \
                          w.cur, rec, bw.mod_wn, bw.mod_b, bw.mor_w, bw.mor_b, scores, logits,                     \
-                         force ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth))
+                         (force || stat) ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth))
       if (has_mod && need_router) HB_SCORE(true, true);
       else if (has_mod) HB_SCORE(true, false);
       else HB_SCORE(false, true);
@@ -239,7 +286,7 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
     int32_t* count = counts + (size_t)bi * R + r;
     {
     ProfScope ps(m->profile, st, HB200_K_SELECT, bi, r, T, 0, 0);
-    if (has_mod) {
+    if (has_mod && !stat) {
       int32_t* slot = (taps && taps->mod_idx) ? taps->mod_idx + ((size_t)bi * R + r) * B * k : w.sel_idx;
       HB_PROPAGATE(launch_mod_select(scores, B, S, k, force ? nullptr : slot, depth, r, w.rows, count,
                                      force ? slot : nullptr, st));
@@ -255,12 +302,32 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
     }
     HB_PROPAGATE(gemm(m, HB200_K_GEMM_GATE_UP, bi, r, w.ug, bw.w_gate_up, w.act, T, 2 * F, D, D, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count,
                       err, st));
-    HB_PROPAGATE(gemm(m, HB200_K_GEMM_DOWN, bi, r, w.act, bw.w_down, w.cur, T, D, F, F, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count,
+    if (!stat) {
+      HB_PROPAGATE(gemm(m, HB200_K_GEMM_DOWN, bi, r, w.act, bw.w_down, w.cur, T, D, F, F, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count,
+                        err, st));
+      continue;
+    }
+    // static routing: the MLP result of every row goes to w.a (free between the attention half and the exit norm),
+    // then one pass mixes it into cur and, with the depth router, accumulates the weighted state in y
+    HB_PROPAGATE(gemm(m, HB200_K_GEMM_DOWN, bi, r, w.act, bw.w_down, w.a, T, D, F, F, F, D, EPI_STORE, nullptr, 1.0f, nullptr, nullptr,
                       err, st));
+    {
+      ProfScope ps(m->profile, st, HB200_K_OTHER, bi, r, T, D, 0);
+      const unsigned grid = (unsigned)ceil_div64((int64_t)T * (D / 8), 256);
+#define HB_STATIC(MOD_, OUT_)                                                                                         \
+  static_update_kernel<MOD_, OUT_><<<grid, 256, 0, st>>>(w.cur, w.a, w.ug, scores, logits, y, (int64_t)T, D, r, R)
+      if (has_mod && m->adaptive) HB_STATIC(true, true);
+      else if (has_mod) HB_STATIC(true, false);
+      else if (m->adaptive) HB_STATIC(false, true);
+      else HB_STATIC(false, false);
+#undef HB_STATIC
+      HB_LAUNCH_CHECK();
+    }
   }
   {
     ProfScope ps(m->profile, st, HB200_K_RMS_NORM, bi, R, T, D, 0);
-    HB_DISPATCH_NCH(D, dual_norm_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, bw.final_norm_w, y, next_w,
+    const __nv_bfloat16* exit_src = (stat && m->adaptive) ? y : w.cur;      // static + depth router: the weighted sum
+    HB_DISPATCH_NCH(D, dual_norm_kernel<NCH><<<row_grid, 256, 0, st>>>(exit_src, bw.final_norm_w, y, next_w,
                                                                          next_w ? a_next : nullptr, T, D, m->norm_eps));
     HB_LAUNCH_CHECK();
   }

@@ -196,10 +196,11 @@ __global__ void __launch_bounds__(256) norm_gather_kernel(const __nv_bfloat16* _
 
 // y = RMSNorm(src; w1) rounded to bf16 (the block output), z = RMSNorm(y; w2) (the next block's pre-attention norm,
 // or the model's final norm): one read of src instead of three passes.  Either output may be omitted.  w1 == nullptr
-// (a block without an exit norm): y = src.
+// (a block without an exit norm): y = src.  y may be src itself (a row is read completely before any of it is
+// written), which is why neither pointer is declared restrict.
 template <int NCH>
-__global__ void __launch_bounds__(256) dual_norm_kernel(const __nv_bfloat16* __restrict__ src,
-                                                        const float* __restrict__ w1, __nv_bfloat16* __restrict__ y,
+__global__ void __launch_bounds__(256) dual_norm_kernel(const __nv_bfloat16* src,
+                                                        const float* __restrict__ w1, __nv_bfloat16* y,
                                                         const float* __restrict__ w2, __nv_bfloat16* __restrict__ z,
                                                         int64_t T, int D, float eps) {
   chain_release();

@@ -223,6 +223,10 @@ typedef struct hb200_model {
   void* profile;                  /* optional hb200_profile handle (see below), or NULL */
   const void* lm_head;            /* bf16 [V, D] untied output projection (tie_weights=False, model.py:343-349),
                                      or NULL: the output projection is tok_emb */
+  int32_t static_routing;         /* 1: the model was built with static_routing_mode (model.py:202, honoured in eval
+                                     too): every token runs every recursion; MoD mixes mlp(u) with u by the router
+                                     probability (blocks.py:190-241), MoR weights each recursion's state by soft depth
+                                     weights (mixture_of_recursions.py:482-558).  Prefill / forward only. */
 } hb200_model;
 
 /* Optional routing taps / forced routing for one forward (device pointers or NULL). */

@@ -56,6 +56,7 @@ class HydraConfig:
     norm_eps: float = 1e-6
     rope_theta: float = 10000.0
     hidden_dim: Optional[int] = None  # override of the MLP width (op-level tests)
+    static_routing: bool = False     # static_routing_mode (model.py:202): dense compute with soft routing weights
 
     @property
     def latent_dim(self) -> int:
@@ -288,6 +289,54 @@ class RoutingTaps:
     mlp_rows: Dict[Tuple[int, int], int] = field(default_factory=dict) # (block, rec) -> rows whose MLP result is used
 
 
+def static_block_forward(x: Tensor, p: Dict[str, Tensor], i: int, cfg: HydraConfig,
+                         taps: Optional[RoutingTaps] = None) -> Tensor:
+    """HydraMoRBlock with ``static_routing_mode`` (the model flag is honoured in eval as well): every token runs every
+    recursion and the routers only weight the results.
+    MoD wrapper (blocks.py:190-241): ``mlp(u) * q + u * (1 - q)``, q = sigmoid(clamp(score(u), -10, 10)), u the
+    normalised MLP input.  MoR executor (mixture_of_recursions.py:482-558): ``cur += delta`` for all tokens each
+    recursion; output = sum_r w_r * cur_r with w_r = exp(-(d - r)^2) / (sum_j exp(-(d - j)^2) + 1e-8),
+    d = sigmoid(3 tanh(l / 2)) * (R - 1) (min_depth plays no part).  Fixed-depth blocks (blocks.py:593-606) only get
+    the MoD mixing."""
+    pre = f"layers.{i}."
+    R = cfg.recursions_per_block
+    B, L, D = x.shape
+    a = ada_rms_norm(x, p[pre + "norm1.weight"], cfg.norm_eps)
+    h = x + cfg.residual_scale * ccgqa_forward(a, p, pre + "attention.", cfg)
+    if cfg.adaptive:
+        logits = h @ p[pre + "mor_router.router.weight"].reshape(-1) + p[pre + "mor_router.router.bias"]
+        d = torch.sigmoid(torch.tanh(logits / 2.0) * 3.0) * (R - 1)
+        wts = torch.exp(-((d.unsqueeze(0) - torch.arange(R, dtype=h.dtype).view(-1, 1, 1)) ** 2))
+        wts = wts / (wts.sum(dim=0, keepdim=True) + 1e-8)
+    else:
+        logits = h.new_zeros(B, L)
+    if taps is not None:
+        taps.router_logits.append(logits.clone())
+    rec_bias = p[pre + "mor_executor.recursion_bias"].reshape(R, D)
+    rec_embed = p[pre + "mor_executor.recursion_embed.weight"]
+    cur = h
+    out = torch.zeros_like(h)
+    for r in range(R):
+        u = ada_rms_norm(cur + rec_bias[r] + rec_embed[r], p[pre + "norm2.weight"], cfg.norm_eps)
+        delta = swiglu_mlp(u, p[pre + "mlp.gate_up.weight"], p[pre + "mlp.down.weight"])
+        if cfg.block_has_mod(i):
+            mp = pre + "mod_mlp_wrapper.mod_router.router."
+            scores = u @ p[mp + "weight"].reshape(-1) + p[mp + "bias"]
+            q = torch.sigmoid(scores.clamp(-10.0, 10.0)).unsqueeze(-1)
+            delta = delta * q + u * (1 - q)
+            if taps is not None:
+                taps.mod_scores[(i, r)] = scores.clone()
+        if taps is not None:
+            taps.mlp_rows[(i, r)] = B * L
+        cur = cur + delta
+        if cfg.adaptive:
+            out = out + wts[r].unsqueeze(-1) * cur
+    y = rms_norm(out if cfg.adaptive else cur, p[pre + "final_norm.weight"], cfg.norm_eps)
+    if taps is not None:
+        taps.block_out.append(y.clone())
+    return y
+
+
 def mor_block_forward(x: Tensor, p: Dict[str, Tensor], i: int, cfg: HydraConfig,
                       taps: Optional[RoutingTaps] = None,
                       forced: Optional[RoutingTaps] = None) -> Tensor:
@@ -297,6 +346,10 @@ def mor_block_forward(x: Tensor, p: Dict[str, Tensor], i: int, cfg: HydraConfig,
     ``forced`` replays another run's depths / MoD index lists instead of computing
     them, so numerical error can be separated from routing flips.
     """
+    if cfg.static_routing:
+        if forced is not None:
+            raise ValueError("static routing makes no routing decisions to replay")
+        return static_block_forward(x, p, i, cfg, taps)
     pre = f"layers.{i}."
     R = cfg.recursions_per_block
     B, L, D = x.shape

@@ -135,13 +135,13 @@ def gen_attention(name: str, dim: int, H: int, KV: int, B: int, S: int, seed: in
 
 # ----------------------------------------------------------------------------
 def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: int, mlp_ratio: float,
-              B: int, S: int, cap: float, seed: int, tie: bool = True) -> None:
+              B: int, S: int, cap: float, seed: int, tie: bool = True, static: bool = False) -> None:
     from hydra.model.framework import HydraModel
 
     torch.manual_seed(seed)
     m = HydraModel(vocab_size=vocab, dim=dim, n_mor_blocks=NB, recursions_per_block=R, n_heads=H,
                    n_kv_heads=KV, compression_factor=4, mlp_ratio=mlp_ratio, max_seq_len=S,
-                   mod_capacity=cap, tie_weights=tie)
+                   mod_capacity=cap, tie_weights=tie, static_routing_mode=static)
     g = torch.Generator().manual_seed(seed + 1)
     with torch.no_grad():
         for n, p in m.named_parameters():
@@ -181,7 +181,7 @@ def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: i
         meta=np.array([vocab, dim, NB, R, H, KV, B, S], dtype=np.int64),
         cap=np.array([cap], dtype=np.float64),
         ffn_hidden=np.array([m.layers[0].mlp.down.weight.shape[1]], dtype=np.int64),
-        ids=ids.numpy(), logits=f32(logits),
+        ids=ids.numpy(), logits=f32(logits), static=np.array([int(static)], dtype=np.int64),
     )
     for i, d in enumerate(depths):
         arrs[f"depths:{i}"] = d.numpy().astype(np.int32)
@@ -336,6 +336,10 @@ if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "sampler":  # only the sampler's filtered distributions
         gen_sampler()
         sys.exit(0)
+    if len(sys.argv) > 1 and sys.argv[1] == "static":   # only the static-routing model
+        gen_model("model_static.npz", vocab=200, dim=256, NB=3, R=3, H=4, KV=2, mlp_ratio=1.0,
+                  B=2, S=64, cap=0.75, seed=23, static=True)
+        sys.exit(0)
     if len(sys.argv) > 1 and sys.argv[1] == "untied":   # only the model with its own output projection
         gen_model("model_untied.npz", vocab=200, dim=256, NB=3, R=2, H=4, KV=2, mlp_ratio=1.0,
                   B=2, S=64, cap=0.75, seed=21, tie=False)
@@ -359,3 +363,6 @@ if __name__ == "__main__":
     gen_model("model_untied.npz", vocab=200, dim=256, NB=3, R=2, H=4, KV=2, mlp_ratio=1.0,
               B=2, S=64, cap=0.75, seed=21, tie=False)
     gen_sampler()
+    # static_routing_mode=True: dense compute, soft routing weights (also honoured in eval)
+    gen_model("model_static.npz", vocab=200, dim=256, NB=3, R=3, H=4, KV=2, mlp_ratio=1.0,
+              B=2, S=64, cap=0.75, seed=23, static=True)

@@ -350,3 +350,58 @@ def test_untied_output_projection():
                 break    # diverged: later steps see different inputs
     from tests.test_gpu_decode import check_against_oracle
     check_against_oracle(m, w, cfg, prompt, 5, "untied cached decode")
+
+
+def test_static_routing_mode():
+    """static_routing_mode (dense compute, soft routing weights; the reference honours the flag in eval): logits against
+    the reference's own run (tolerance: twice its own bf16 error), every block's output and MoD score against the
+    oracle, the fixed-depth variant, generation by re-forward; no routing decision exists to replay and the cached
+    decode is not built for this mode."""
+    fx, cfg, w = G.model_fixture("model_static.npz")
+    assert cfg.static_routing
+    ids = torch.from_numpy(fx["ids"])
+    B, S = ids.shape
+    m = build(w, cfg, static_routing_mode=True)
+    lg = m(ids.cuda(), taps=True, block_out=True).float().cpu()
+    m.check_device_errors()
+    ref = torch.from_numpy(fx["logits"])
+    err, own = rel_l2(lg, ref), float(fx["ref_bf16_rel_l2"][0])
+    print(f"static routing vs reference fp32 logits: rel_l2 {err:.3e}; reference's own bf16 path: {own:.3e}")
+    assert err <= 2.0 * own + 1e-3
+    ot = O.RoutingTaps()
+    assert max_abs(O.model_forward(ids, w, cfg, taps=ot), ref) < 5e-5
+    tp = m.last_taps
+    bo = tp.block_out.float().cpu().view(cfg.n_mor_blocks, B, S, -1)
+    sc = tp.mod_scores.cpu().view(cfg.n_mor_blocks, cfg.recursions_per_block, B, S)
+    rl = tp.router_logits.cpu().view(cfg.n_mor_blocks, B, S)
+    for i in range(cfg.n_mor_blocks):
+        assert rel_l2(bo[i], ot.block_out[i]) <= 1e-2, f"block {i}"
+        assert rel_l2(rl[i], ot.router_logits[i]) <= 2e-2
+        for r in range(cfg.recursions_per_block):
+            if cfg.block_has_mod(i):
+                assert rel_l2(sc[i, r], ot.mod_scores[(i, r)]) <= 2e-2
+    assert (tp.mlp_rows.cpu() == B * S).all()                  # every token, every recursion
+    # the flag changes the result: hard routing on the same weights
+    hard = build(w, cfg)(ids.cuda()).float().cpu()
+    assert rel_l2(hard, lg) > 1.5e-2
+    # fixed-depth blocks: only the MoD mixing remains
+    cfg.adaptive = False
+    mf = build(w, cfg, static_routing_mode=True)
+    lf = mf(ids.cuda()).float().cpu()
+    assert rel_l2(lf, O.model_forward(ids, w, cfg)) <= 1e-2
+    assert rel_l2(lf, torch.from_numpy(fx["logits_fixed"])) <= 2.0 * own + 2e-3
+    cfg.adaptive = True
+    # generation: the re-forward mode runs, cached decode and forced replay are refused
+    prompt = ids[:, 2:20].clamp(0, cfg.vocab_size - 1)
+    seq = m.generate(prompt.cuda(), 3).cpu()
+    ref_seq, margins = O.greedy_generate(prompt, w, cfg, 3, return_margins=True)
+    for b in range(B):
+        for i in range(3):
+            if int(seq[b, 18 + i]) != int(ref_seq[b, 18 + i]):
+                assert float(margins[b, i]) < 0.06
+                break
+    with pytest.raises(NotImplementedError):
+        m.generate(prompt.cuda(), 3, mode="cached")
+    from hydra_b200._lib import Hb200Error
+    with pytest.raises(Hb200Error):
+        m(ids.cuda(), forced=tp)

@@ -172,3 +172,24 @@ def test_sampler_draw_is_the_inverse_cdf():
     probs = torch.softmax(O.sample_filter(row, 0.8, 8, 0.9), -1)[0]
     freq = torch.bincount(draws, minlength=30).double() / n
     assert float(freq[probs == 0].sum()) == 0.0 and float((freq - probs).abs().max()) < 0.02
+
+
+def test_static_routing_mode_matches_reference():
+    """HydraModel(static_routing_mode=True) in eval: dense compute, MoD mixes mlp(u) with u by the router probability,
+    MoR weights every recursion's state by soft depth weights.  Logits, block outputs, router logits, and the
+    fixed-depth variant (adaptive=False: MoD mixing only) against the reference's run."""
+    fx, cfg, w = G.model_fixture("model_static.npz")
+    assert cfg.static_routing
+    ids = torch.from_numpy(fx["ids"])
+    taps = O.RoutingTaps()
+    close(O.model_forward(ids, w, cfg, taps=taps), fx["logits"], 5e-6)
+    for i in range(cfg.n_mor_blocks):
+        close(taps.block_out[i], fx[f"block_out:{i}"], 5e-6)
+        close(torch.tanh(taps.router_logits[i] / 2.0) * 3.0, fx[f"router_logits:{i}"], 5e-6)
+    assert all(v == ids.numel() for v in taps.mlp_rows.values())
+    assert not any(k.startswith("mod_idx") for k in fx)          # nothing is selected in this mode
+    cfg.adaptive = False
+    close(O.model_forward(ids, w, cfg), fx["logits_fixed"], 5e-6)
+    # the mode matters: hard routing on the same weights gives other logits
+    cfg.adaptive, cfg.static_routing = True, False
+    assert float((O.model_forward(ids, w, cfg) - torch.from_numpy(fx["logits"])).abs().max()) > 1e-2
