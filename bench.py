@@ -47,7 +47,7 @@ SEED = 0
 
 def workload_config(batch_per_gpu: int, n_gpus: int) -> dict:
     return {
-        "workload": "BASELINE configs[3]: HYDRA-250M prefill, dim 1024, 10 MoR blocks x 4 recursions, CCGQA 8q/2kv "
+        "workload": "configs[3]: HYDRA-250M prefill, dim 1024, 10 MoR blocks x 4 recursions, CCGQA 8q/2kv "
                     "(head_dim 32), SwiGLU 2816, MoD top-k 0.75, vocab 50257, all logits computed",
         "batch_per_gpu": batch_per_gpu, "global_batch": batch_per_gpu * n_gpus, "seq_len": SEQ,
         "parallelism": f"replica-per-GPU x{n_gpus}, batch sharded by sequence, no data-path collective",
