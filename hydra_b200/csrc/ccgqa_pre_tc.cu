@@ -135,26 +135,20 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_const
   if (warp == 1) tmem_alloc(s_addr(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
 
   // ---------------- phase 1a: q|k columns of the tile -> shared memory ----------------
+  // every 16-byte piece is its own asynchronous copy (23 per thread, all in flight at once: one memory latency for the
+  // whole tile instead of one per batch of register-staged loads); rows outside the sequence are zero
   {
     constexpr int PIECES = XROWS * (C / 8);
-    constexpr int BATCH = 8;   // loads in flight per thread
-    for (int i0 = tid; i0 < PIECES; i0 += 256 * BATCH) {
-      uint4 val[BATCH];
-#pragma unroll
-      for (int u = 0; u < BATCH; ++u) {
-        const int idx = i0 + u * 256;
-        const int r = idx / (C / 8), piece = idx % (C / 8);
-        const int tok = t0 - 4 + r;
-        val[u] = make_uint4(0, 0, 0, 0);
-        if (idx < PIECES && tok >= 0 && tok < S)
-          val[u] = *reinterpret_cast<const uint4*>(qkv_b + (size_t)tok * QKV_LD + piece * 8);
-      }
-#pragma unroll
-      for (int u = 0; u < BATCH; ++u) {
-        const int idx = i0 + u * 256;
-        if (idx < PIECES) *reinterpret_cast<uint4*>(X + (idx / (C / 8)) * LDX + (idx % (C / 8)) * 8) = val[u];
-      }
+    const uint32_t x_s = s_addr(X);
+    for (int idx = tid; idx < PIECES; idx += 256) {
+      const int r = idx / (C / 8), piece = idx % (C / 8);
+      const int tok = t0 - 4 + r;
+      const uint32_t dst = x_s + (uint32_t)(r * LDX + piece * 8) * 2u;
+      if (tok >= 0 && tok < S) cp_async16(dst, qkv_b + (size_t)tok * QKV_LD + piece * 8);
+      else st_shared_v4(dst, make_uint4(0u, 0u, 0u, 0u));
     }
+    cp_async16_commit();
+    cp_async16_wait_all();
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -217,6 +211,13 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_const
   __syncthreads();
 
   // ---------------- phase 2: warp-specialised ----------------
+  // epilogue geometry: thread = token r of the tile, for warp w and warp w + 4 alike (TMEM lane quarter w % 4)
+  const int quad = warp & 3;
+  const int r = quad * 32 + lane;
+  const int tok = t0 + r;
+  const bool valid = tok < S;
+  const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+  float qm[HD], km[HD], cs[HD / 2], sn[HD / 2];
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0;
@@ -293,14 +294,8 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_const
       }
     }
   } else {
-    // ---- epilogue warps 4..7: thread = token ----
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;
-    const int tok = t0 + r;
-    const bool valid = tok < S;
-    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    // ---- warps 4..7 prepare the per-token vectors of the epilogue while the contraction runs ----
     // QK-mean vectors of this token (0.5 * mean over heads), straight from its qkv row
-    float qm[HD], km[HD];
 #pragma unroll
     for (int d = 0; d < HD; ++d) qm[d] = km[d] = 0.f;
     if (valid) {
@@ -341,37 +336,58 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_const
     const float sq = 0.5f / (float)H, sk = 0.5f / (float)KV;
 #pragma unroll
     for (int d = 0; d < HD; ++d) { qm[d] *= sq; km[d] *= sk; }
-    float cs[HD / 2], sn[HD / 2];
 #pragma unroll
     for (int i = 0; i < HD / 2; ++i) {
       cs[i] = valid ? p.cos_t[(size_t)tok * (HD / 2) + i] : 1.f;
       sn[i] = valid ? p.sin_t[(size_t)tok * (HD / 2) + i] : 0.f;
     }
+  }
+
+  // ---------------- epilogue: all 8 warps, thread = token, the ten 32-column chunks split 5 + 5 ----------------
+  // Warps 0-3 are done with their roles by now (the producer long before).  Warps 4-7 hand their token's vectors to
+  // warps 0-3 through the weight ring, which is idle once the accumulators are complete.
+  {
     const float temp = *p.temp;
     bool ok = mbar_wait(acc_full, 0u, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
+    tcgen05_fence_after();
+    float* hand = reinterpret_cast<float*>(base_ptr);        // [2*HD + HD][128] floats: field-major, token-minor
+    if (warp >= 4) {
+#pragma unroll
+      for (int d = 0; d < HD; ++d) { hand[d * TT + r] = qm[d]; hand[(HD + d) * TT + r] = km[d]; }
+#pragma unroll
+      for (int i = 0; i < HD / 2; ++i) { hand[(2 * HD + i) * TT + r] = cs[i]; hand[(2 * HD + HD / 2 + i) * TT + r] = sn[i]; }
+    }
+    __syncthreads();
+    if (warp < 4) {
+#pragma unroll
+      for (int d = 0; d < HD; ++d) { qm[d] = hand[d * TT + r]; km[d] = hand[(HD + d) * TT + r]; }
+#pragma unroll
+      for (int i = 0; i < HD / 2; ++i) { cs[i] = hand[(2 * HD + i) * TT + r]; sn[i] = hand[(2 * HD + HD / 2 + i) * TT + r]; }
+    }
     if (ok) {
-      tcgen05_fence_after();
-      // queries: LAT accumulator columns = H heads of HD
+      constexpr int QCH = LAT / 32, KCH = KVD / 32, HALF = (QCH + KCH) / 2;
+      const int c_begin = warp >= 4 ? 0 : HALF, c_end = warp >= 4 ? HALF : QCH + KCH;
 #pragma unroll 1
-      for (int c = 0; c < LAT / 32; ++c) {
+      for (int c = c_begin; c < c_end; ++c) {
         float v[32];
-        tmem_ld_32x32(tmem_base + lane_off + (uint32_t)(c * 32), v);   // warp-collective
+        if (c < QCH) {
+          // queries: LAT accumulator columns = H heads of HD
+          tmem_ld_32x32(tmem_base + lane_off + (uint32_t)(c * 32), v);   // warp-collective
 #pragma unroll
-        for (int hh = 0; hh < 32 / HD; ++hh) {
-          const int h = c * (32 / HD) + hh;
-          finish_head<HD>(v + hh * HD, km, 1.0f, cs, sn, p.q + (((size_t)b * H + h) * S + tok) * HD, valid);
-        }
-      }
-      // keys: KVD columns at 256..
-#pragma unroll 1
-      for (int c = 0; c < KVD / 32; ++c) {
-        float v[32];
-        tmem_ld_32x32(tmem_base + lane_off + (uint32_t)(256 + c * 32), v);
+          for (int hh = 0; hh < 32 / HD; ++hh) {
+            const int h = c * (32 / HD) + hh;
+            finish_head<HD>(v + hh * HD, km, 1.0f, cs, sn, p.q + (((size_t)b * H + h) * S + tok) * HD, valid);
+          }
+        } else {
+          // keys: KVD columns at 256..
+          const int ck = c - QCH;
+          tmem_ld_32x32(tmem_base + lane_off + (uint32_t)(256 + ck * 32), v);
 #pragma unroll
-        for (int hh = 0; hh < 32 / HD; ++hh) {
-          const int h = c * (32 / HD) + hh;
-          finish_head<HD>(v + hh * HD, qm, temp, cs, sn, p.k + (((size_t)b * KV + h) * S + tok) * HD, valid);
+          for (int hh = 0; hh < 32 / HD; ++hh) {
+            const int h = ck * (32 / HD) + hh;
+            finish_head<HD>(v + hh * HD, qm, temp, cs, sn, p.k + (((size_t)b * KV + h) * S + tok) * HD, valid);
+          }
         }
       }
     }
