@@ -131,6 +131,10 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_const
     mbar_init(acc_full, 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // the first weight block starts its trip now: ring slot i lives in physical stage (i + 3) % 4, and the last
+    // physical stage is the one the input tile does not occupy during phase 1
+    mbar_arrive_expect_tx(full_bar(0), LAT * 64 * 2);
+    tma_load_2d(base + (STAGES - 1) * STAGE_BYTES, &tma_w2q, 0, 0, full_bar(0));
   }
   if (warp == 1) tmem_alloc(s_addr(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
 
@@ -220,11 +224,11 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_const
   float qm[HD], km[HD], cs[HD / 2], sn[HD / 2];
   if (warp == 0) {
     if (lane == 0) {
-      int stage = 0;
+      int stage = 1;                                   // block 0 was issued at kernel start
       uint32_t phase = 0;
-      for (int kb = 0; kb < QBLOCKS + KBLOCKS; ++kb) {
+      for (int kb = 1; kb < QBLOCKS + KBLOCKS; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
-        const uint32_t dst = base + stage * STAGE_BYTES;
+        const uint32_t dst = base + ((stage + STAGES - 1) % STAGES) * STAGE_BYTES;
         if (kb < QBLOCKS) {
           mbar_arrive_expect_tx(full_bar(stage), LAT * 64 * 2);
           tma_load_2d(dst, &tma_w2q, kb * 64, 0, full_bar(stage));
@@ -251,7 +255,7 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_const
         const int cin = is_q ? LAT : KVD;
         const int j = (kq * 64) / cin;                         // conv tap of this K block
         const int ch0 = (kq * 64) % cin + (is_q ? 0 : LAT);    // first y1 channel of this K block
-        const uint32_t sb = base + stage * STAGE_BYTES;
+        const uint32_t sb = base + ((stage + STAGES - 1) % STAGES) * STAGE_BYTES;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           // A: y1 rows j..j+127, 16 channels = two 16-byte chunks CHUNK_BYTES apart; 8-row groups are 128 B apart
