@@ -317,6 +317,141 @@ static int launch_pre(const PreParams& p, cudaStream_t st) {
   return 0;
 }
 
+// ---- any other shape: CUDA-core kernel ---------------------------------------------------------------------------
+// Head counts the tiled kernels above are not instantiated for (H and KV are run-time values here; head_dim 16, 32 or
+// 64).  Same arithmetic: the grouped conv's result is rounded to bf16 before the dense conv (as the tensor-core
+// kernels round their operand), everything after it stays in fp32 until the final store.  One CTA = TT tokens of one
+// sequence; thread = output channel in both convs (its weight row is read once and used for all TT tokens, the
+// activations come from shared memory as broadcasts).  Built for coverage, not speed.
+template <int HD, int TT>
+__global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams p) {
+  extern __shared__ __align__(16) float gsm[];
+  const int H = p.H, KV = p.KV, S = p.S;
+  const int LAT = H * HD, KVD = KV * HD, C = LAT + KVD, QKV_LD = LAT + 2 * KVD;
+  float* xs = gsm;                        // [TT + 4][C]  q|k columns of tokens t0-4 .. t0+TT-1 (0 before the sequence)
+  float* y1 = xs + (TT + 4) * C;          // [TT + 2][C]  grouped-conv output of tokens t0-2 .. (0 before the sequence)
+  float* y2 = y1 + (TT + 2) * C;          // [TT][C]      dense-conv output of tokens t0 ..
+  float* mean = y2 + TT * C;              // [TT][2][HD]  0.5 * mean over heads of q0 / of k0 (H != KV only)
+  const int tid = threadIdx.x;
+  const int tiles_per_seq = (S + TT - 1) / TT;
+  const int b = blockIdx.x / tiles_per_seq;
+  const int t0 = (blockIdx.x % tiles_per_seq) * TT;
+  const __nv_bfloat16* qkv_b = p.qkv + (size_t)b * S * QKV_LD;
+
+  for (int idx = tid; idx < (TT + 4) * C; idx += 256) {
+    const int r = idx / C, c = idx - r * C, tok = t0 - 4 + r;
+    xs[idx] = (tok >= 0 && tok < S) ? __bfloat162float(qkv_b[(size_t)tok * QKV_LD + c]) : 0.f;
+  }
+  __syncthreads();
+
+  // grouped conv: y1[t][c] = sum_j sum_i w1[c][j*HD + i] * x[t-2+j][head(c)*HD + i]
+  for (int c = tid; c < C; c += 256) {
+    float acc[TT + 2];
+#pragma unroll
+    for (int r = 0; r < TT + 2; ++r) acc[r] = 0.f;
+    const __nv_bfloat16* w = p.w1 + (size_t)c * 3 * HD;
+    const int c0 = (c / HD) * HD;
+    for (int j = 0; j < 3; ++j)
+      for (int i = 0; i < HD; ++i) {
+        const float wv = __bfloat162float(w[j * HD + i]);
+#pragma unroll
+        for (int r = 0; r < TT + 2; ++r) acc[r] += wv * xs[(r + j) * C + c0 + i];
+      }
+#pragma unroll
+    for (int r = 0; r < TT + 2; ++r)
+      y1[r * C + c] = (t0 - 2 + r >= 0) ? __bfloat162float(__float2bfloat16(acc[r])) : 0.f;   // conv2 pads with zeros
+  }
+  __syncthreads();
+
+  // dense conv: y2[t][c] = sum_j sum_ci w2[c][j*Cin + ci] * y1[t-2+j][off + ci]
+  for (int c = tid; c < C; c += 256) {
+    float acc[TT];
+#pragma unroll
+    for (int r = 0; r < TT; ++r) acc[r] = 0.f;
+    const bool is_q = c < LAT;
+    const int cin = is_q ? LAT : KVD, off = is_q ? 0 : LAT;
+    const __nv_bfloat16* w = is_q ? p.w2q + (size_t)c * 3 * LAT : p.w2k + (size_t)(c - LAT) * 3 * KVD;
+    for (int j = 0; j < 3; ++j)
+      for (int ci = 0; ci < cin; ++ci) {
+        const float wv = __bfloat162float(w[j * cin + ci]);
+#pragma unroll
+        for (int r = 0; r < TT; ++r) acc[r] += wv * y1[(r + j) * C + off + ci];
+      }
+#pragma unroll
+    for (int r = 0; r < TT; ++r) y2[r * C + c] = acc[r];
+  }
+  // QK-mean vectors from the un-convolved q0 / k0 of each token
+  if (H != KV) {
+    for (int idx = tid; idx < TT * 2 * HD; idx += 256) {
+      const int r = idx / (2 * HD), which = (idx / HD) & 1, d = idx % HD;
+      const float* row = xs + (r + 4) * C;
+      float sum = 0.f;
+      if (which == 0) { for (int h = 0; h < H; ++h) sum += row[h * HD + d]; sum *= 0.5f / (float)H; }
+      else            { for (int h = 0; h < KV; ++h) sum += row[LAT + h * HD + d]; sum *= 0.5f / (float)KV; }
+      mean[idx] = sum;
+    }
+  }
+  __syncthreads();
+
+  // finish: coupling, L2 norm, temperature, RoPE; one thread per (token, head)
+  const float temp = *p.temp;
+  for (int idx = tid; idx < TT * (H + KV); idx += 256) {
+    const int r = idx / (H + KV), hh = idx - r * (H + KV), tok = t0 + r;
+    if (tok >= S) continue;
+    const bool is_q = hh < H;
+    const int h = is_q ? hh : hh - H;
+    const int c0 = is_q ? h * HD : LAT + h * HD;
+    const float* x0 = xs + (r + 4) * C;
+    float v[HD];
+    float ss = 0.f;
+#pragma unroll
+    for (int d = 0; d < HD; ++d) {
+      float couple;
+      if (H == KV) couple = 0.5f * (x0[h * HD + d] + x0[LAT + h * HD + d]);   // m = 0.5 (q0 + k0), channel by channel
+      else couple = is_q ? mean[(r * 2 + 1) * HD + d] : mean[(r * 2 + 0) * HD + d];
+      v[d] = y2[r * C + c0 + d] + couple;
+      ss += v[d] * v[d];
+    }
+    const float inv = (is_q ? 1.0f : temp) / fmaxf(sqrtf(ss), 1e-12f);
+    __nv_bfloat16* dst = is_q ? p.q + (((size_t)b * H + h) * S + tok) * HD : p.k + (((size_t)b * KV + h) * S + tok) * HD;
+    const float* cs = p.cos_t + (size_t)tok * (HD / 2);
+    const float* sn = p.sin_t + (size_t)tok * (HD / 2);
+#pragma unroll
+    for (int i = 0; i < HD / 2; ++i) {
+      const float a0 = v[2 * i] * inv, a1 = v[2 * i + 1] * inv;
+      dst[2 * i] = __float2bfloat16(a0 * cs[i] - a1 * sn[i]);
+      dst[2 * i + 1] = __float2bfloat16(a0 * sn[i] + a1 * cs[i]);
+    }
+  }
+  // value shift: first half of the channels from this token, second half from the previous one
+  for (int idx = tid; idx < TT * KVD; idx += 256) {
+    const int r = idx / KVD, c = idx - r * KVD, tok = t0 + r;
+    if (tok >= S) continue;
+    const int src = (c < KVD / 2) ? tok : tok - 1;
+    p.v[(((size_t)b * KV + c / HD) * S + tok) * HD + (c % HD)] =
+        src >= 0 ? qkv_b[(size_t)src * QKV_LD + LAT + KVD + c] : __float2bfloat16(0.f);
+  }
+}
+
+template <int HD>
+static int launch_pre_generic(const PreParams& p, cudaStream_t st) {
+  const size_t C = (size_t)(p.H + p.KV) * HD;
+  auto bytes = [&](int tt) { return ((size_t)(3 * tt + 6) * C + (size_t)tt * 2 * HD) * sizeof(float); };
+  if (bytes(16) <= 200 * 1024) {
+    auto kern = ccgqa_pre_generic_kernel<HD, 16>;
+    HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, bytes(16)));
+    kern<<<p.B * ((p.S + 15) / 16), 256, bytes(16), st>>>(p);
+  } else {
+    HB_REQUIRE(bytes(4) <= 227 * 1024, HB200_ERR_UNSUPPORTED,
+               "ccgqa_pre_attention: latent + kv width %d does not fit the generic kernel", (int)C);
+    auto kern = ccgqa_pre_generic_kernel<HD, 4>;
+    HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, bytes(4)));
+    kern<<<p.B * ((p.S + 3) / 4), 256, bytes(4), st>>>(p);
+  }
+  HB_LAUNCH_CHECK();
+  return 0;
+}
+
 int launch_ccgqa_pre_tc(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k, const float* cos_t,
                         const float* sin_t, const float* key_temperature, void* q, void* k, void* v, int B, int S, int H,
                         int KV, int hd, int32_t* err_flag, cudaStream_t st);
@@ -358,9 +493,20 @@ extern "C" int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, con
   HB_PRE_CASE(32, 2, 2)    // dim 256: 2q/1kv heads of 32
   HB_PRE_CASE(16, 2, 4)    // dim 256: 4q/4kv heads of 16 (H == KV)
   HB_PRE_CASE(64, 4, 8)    // dim 512: 2q/2kv heads of 64
+  HB_PRE_CASE(16, 3, 2)    // dim 384: 6q/2kv heads of 16
+  HB_PRE_CASE(16, 9, 3)    // dim 1152: 18q/3kv heads of 16 (the reference's 300M preset)
 #undef HB_PRE_CASE
   // latent 512 (dim 2048, 32q/4kv heads of 16: the 1.5B shape): 32-token tiles and 32-wide weight chunks to fit
   if (hd == 16 && lat == 512 && kvd == 64) return launch_pre<16, 16, 4, 32, 32>(p, st);
-  set_error("ccgqa_pre_attention: no kernel built for head_dim=%d latent=%d kv_dim=%d", hd, lat, kvd);
+  // the reference's other presets, same tile shape: dim 1792 (28q/4kv: 500M, 1B), dim 1536 (24q/4kv: 750M) and the
+  // trainer's default dim 1280 (20q/5kv)
+  if (hd == 16 && lat == 448 && kvd == 64) return launch_pre<16, 14, 4, 32, 32>(p, st);
+  if (hd == 16 && lat == 384 && kvd == 64) return launch_pre<16, 12, 4, 32, 32>(p, st);
+  if (hd == 16 && lat == 320 && kvd == 80) return launch_pre<16, 10, 5, 64, 32>(p, st);
+  // everything else with a head_dim the attention kernels are built for
+  if (hd == 16) return launch_pre_generic<16>(p, st);
+  if (hd == 32) return launch_pre_generic<32>(p, st);
+  if (hd == 64) return launch_pre_generic<64>(p, st);
+  set_error("ccgqa_pre_attention: head_dim %d not built (16, 32, 64)", hd);
   return HB200_ERR_UNSUPPORTED;
 }

@@ -405,3 +405,31 @@ def test_static_routing_mode():
     from hydra_b200._lib import Hb200Error
     with pytest.raises(Hb200Error):
         m(ids.cuda(), forced=tp)
+
+
+@pytest.mark.parametrize("dim,H,KV,note", [
+    (384, 6, 2, "6q/2kv x16 (tiled kernel)"), (1152, 18, 3, "300M preset, group of 6"),
+    (1792, 28, 4, "500M / 1B presets, group of 7"), (1536, 24, 4, "750M preset, group of 6"),
+    (1280, 20, 5, "trainer default, 5 KV heads"), (1344, 21, 3, "base-model default: latent 336, CUDA-core kernel"),
+    (768, 6, 3, "heads of 32, 3 KV heads: CUDA-core kernel"), (512, 2, 1, "heads of 64, one KV head: CUDA-core kernel"),
+    (192, 3, 3, "H == KV with three heads: CUDA-core kernel")])
+def test_head_shapes_of_the_reference_presets(dim, H, KV, note):
+    """Every (dim, heads, kv heads) of the reference's size presets (hydra/training/config.py:460-580) and a few shapes
+    no tiled pre-attention kernel is instantiated for (they take the CUDA-core kernel): prefill against the oracle with
+    the GPU's routing replayed, then cached decode against the oracle's cached decode."""
+    from tests.test_gpu_decode import teacher_forced_oracle
+    cfg = O.HydraConfig(vocab_size=160, dim=dim, n_mor_blocks=3, recursions_per_block=2, n_heads=H, n_kv_heads=KV,
+                        max_seq_len=80, mod_capacity=0.75, hidden_dim=256)
+    w = O.init_params(cfg, seed=dim + H, perturb=True)
+    ids = torch.randint(0, 160, (2, 70), generator=torch.Generator().manual_seed(dim))
+    m = build(w, cfg)
+    lg = m(ids.cuda(), taps=True).float().cpu()
+    m.check_device_errors()
+    ref = O.model_forward(ids, w, cfg, forced=taps_to_oracle(m, m.last_taps, *ids.shape))
+    e = rel_l2(lg, ref)
+    prompt = ids[:, :66]
+    seq, dl = m.generate_cached(prompt.cuda(), 4, return_logits=True)
+    m.check_device_errors()
+    e2 = rel_l2(dl.float().cpu(), teacher_forced_oracle(prompt, seq.cpu()[:, 66:], w, cfg))
+    print(f"{note}: prefill rel_l2 {e:.2e}, cached decode rel_l2 {e2:.2e}")
+    assert e <= 1e-2 and e2 <= 1.5e-2
