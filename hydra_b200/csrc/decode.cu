@@ -511,7 +511,7 @@ static int launch_decode_attention(const __nv_bfloat16* qnew, const __nv_bfloat1
 // the wait on the predecessor, and the row piece, the position, the depth and this thread's slice of the score cache
 // (read up to the cache capacity, masked by the position afterwards) are all requested together right after it.
 constexpr int ROUTE_THREADS = 256;
-constexpr int ROUTE_CACHE_PER_THREAD = 16;     // score-cache entries per thread kept in registers: capacity <= 4096
+constexpr int ROUTE_CACHE_PER_THREAD = 16;     // score-cache entries per thread requested up front (the first 4096)
 template <bool HAS_MOD, bool HAS_ROUTER>
 __global__ void __launch_bounds__(ROUTE_THREADS) decode_route_kernel(
     const __nv_bfloat16* __restrict__ cur, const float* __restrict__ rec, const float* __restrict__ norm2_w,
@@ -607,6 +607,9 @@ __global__ void __launch_bounds__(ROUTE_THREADS) decode_route_kernel(
       const int idx = q * ROUTE_THREADS + tid;
       cnt += (idx < n && cached[q] >= s) ? 1 : 0;
     }
+    // positions beyond the register-resident slice (a cache longer than 4096 entries): read on demand
+    for (int idx = ROUTE_CACHE_PER_THREAD * ROUTE_THREADS + tid; idx < n; idx += ROUTE_THREADS)
+      cnt += (__ldcg(sc + idx) >= s) ? 1 : 0;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
     if (lane == 0) red[warp][3] = __int_as_float(cnt);
@@ -758,9 +761,6 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
              "decode_step: latent + kv width too large for the conv window in shared memory");
   HB_REQUIRE(m->n_kv_heads * m->head_dim <= 256, HB200_ERR_UNSUPPORTED, "decode_step: kv width %d beyond 256",
              m->n_kv_heads * m->head_dim);
-  HB_REQUIRE(ds->capacity <= ROUTE_THREADS * ROUTE_CACHE_PER_THREAD, HB200_ERR_UNSUPPORTED,
-             "decode_step: capacity %d beyond the routing kernel's %d cached scores", ds->capacity,
-             ROUTE_THREADS * ROUTE_CACHE_PER_THREAD);
   HB_REQUIRE(decode_attention_smem(m->head_dim, m->n_heads / m->n_kv_heads, ds->capacity) <= 200 * 1024,
              HB200_ERR_UNSUPPORTED, "decode_step: capacity %d needs more shared memory than one CTA has", ds->capacity);
   const size_t ld = ((size_t)m->vocab + 7) / 8 * 8;

@@ -167,3 +167,13 @@ def test_session_errors():
         m.generate(prompt, 2, mode="nope")
     with pytest.raises(RuntimeError):
         m.generate_cached(prompt.cpu(), 2)
+
+
+def test_cache_longer_than_the_routing_kernels_register_slice():
+    """4100 cached positions: the MoD rank of the newest token counts the first 4096 cached scores from registers and the
+    rest on demand."""
+    cfg = O.HydraConfig(vocab_size=300, dim=256, n_mor_blocks=3, recursions_per_block=2, n_heads=4, n_kv_heads=2,
+                        max_seq_len=4120, mod_capacity=0.75, hidden_dim=256)
+    w = O.init_params(cfg, seed=19, perturb=True)
+    prompt = torch.randint(0, 300, (2, 4100), generator=torch.Generator().manual_seed(9))
+    check_against_oracle(build(w, cfg), w, cfg, prompt, 4, "P=4100")
