@@ -71,6 +71,7 @@ SIGNATURES = {
     "hb200_mod_topk_select": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp]),
     "hb200_mor_depths": (c_i32, [c_vp, c_vp, c_i64, c_i32, c_i32, c_vp]),
     "hb200_argmax_rows": (c_i32, [c_vp, c_i64, c_i32, c_i64, c_vp, c_vp]),
+    "hb200_cross_entropy_rows": (c_i32, [c_vp, c_vp, c_i64, c_i32, c_i64, c_i64, c_vp, c_vp]),
     "hb200_sample_rows": (c_i32, [c_vp, c_i64, c_i32, c_i64, c_f32, c_i32, c_f32, c_vp, c_vp, c_vp]),
     "hb200_embed": (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_f32, c_vp]),
     "hb200_model_workspace_bytes": (c_sz, [C.POINTER(Model), c_i32, c_i32]),

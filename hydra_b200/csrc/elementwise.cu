@@ -355,6 +355,71 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* _
   }
 }
 
+// Per-row negative log-likelihood of bf16 logits: nll[r] = logsumexp(row r) - row[target[r]] in fp32 (0 where the
+// target is `ignore_index`).  One pass: each thread keeps a running maximum and a sum of exponentials relative to it.
+__global__ void __launch_bounds__(256) cross_entropy_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                 const int64_t* __restrict__ targets, int cols, int64_t ld,
+                                                                 int64_t ignore_index, float* __restrict__ nll) {
+  __shared__ float s_max[8], s_sum[8];
+  const int64_t tgt = targets[blockIdx.x];
+  if (tgt == ignore_index) {
+    if (threadIdx.x == 0) nll[blockIdx.x] = 0.f;
+    return;
+  }
+  const __nv_bfloat16* row = x + (int64_t)blockIdx.x * ld;
+  float mx = -INFINITY, sum = 0.f;
+  auto take = [&](float v) {
+    if (v > mx) { sum = sum * __expf(mx - v) + 1.f; mx = v; }      // exp(-inf) = 0 covers the first element
+    else if (v > -INFINITY) sum += __expf(v - mx);                  // -inf adds nothing (and -inf - -inf is NaN)
+  };
+  int done = 0;
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const int vec = cols / 8;
+    constexpr int UN = 4;
+    for (int v0 = threadIdx.x; v0 < vec; v0 += blockDim.x * UN) {
+      uint4 raw[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const int vi = v0 + u * blockDim.x;
+        raw[u] = vi < vec ? __ldcg(reinterpret_cast<const uint4*>(row + (size_t)vi * 8)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        if (v0 + u * (int)blockDim.x < vec) {
+          const uint32_t w4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            take(__uint_as_float(w4[j] << 16));
+            take(__uint_as_float(w4[j] & 0xffff0000u));
+          }
+        }
+      }
+    }
+    done = vec * 8;
+  }
+  for (int i = done + threadIdx.x; i < cols; i += blockDim.x) take(ldcg_bf16(row + i));
+  // merge (max, sum) pairs: lanes, then warps
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, mx, o), os = __shfl_xor_sync(0xffffffffu, sum, o);
+    const float nm = fmaxf(mx, om);
+    sum = (mx == -INFINITY ? 0.f : sum * __expf(mx - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+    mx = nm;
+  }
+  if ((threadIdx.x & 31) == 0) { s_max[threadIdx.x >> 5] = mx; s_sum[threadIdx.x >> 5] = sum; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = s_max[0], t = s_sum[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+      const float nm = fmaxf(m, s_max[w]);
+      t = (m == -INFINITY ? 0.f : t * __expf(m - nm)) + (s_max[w] == -INFINITY ? 0.f : s_sum[w] * __expf(s_max[w] - nm));
+      m = nm;
+    }
+    const int64_t ti = tgt < 0 ? 0 : (tgt >= cols ? cols - 1 : tgt);       // the host has checked the range
+    nll[blockIdx.x] = m + logf(t) - ldcg_bf16(row + ti);
+  }
+}
+
 }  // namespace hb200
 
 namespace hb200 {
@@ -371,6 +436,17 @@ extern "C" int hb200_argmax_rows(const void* x, int64_t rows, int cols, int64_t 
   HB_REQUIRE(rows >= 0 && cols >= 1 && ld >= cols, HB200_ERR_INVALID, "argmax_rows: bad shape");
   if (rows == 0) return 0;
   argmax_rows_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, cols, ld, out);
+  HB_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int hb200_cross_entropy_rows(const void* logits, const int64_t* targets, int64_t rows, int cols, int64_t ld,
+                                        int64_t ignore_index, float* nll, void* stream) {
+  HB_REQUIRE(logits && targets && nll, HB200_ERR_INVALID, "cross_entropy_rows: null pointer");
+  HB_REQUIRE(rows >= 0 && cols >= 1 && ld >= cols, HB200_ERR_INVALID, "cross_entropy_rows: bad shape");
+  if (rows == 0) return 0;
+  cross_entropy_rows_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, targets, cols,
+                                                                             ld, ignore_index, nll);
   HB_LAUNCH_CHECK();
   return 0;
 }

@@ -19,7 +19,7 @@ import torch
 
 from . import _lib, kernels
 from ._pack import PackedBlock, PackedModel, _bf16, _f32
-from .sampling import sample_rows
+from .sampling import cross_entropy_rows, sample_rows
 
 Tensor = torch.Tensor
 
@@ -283,6 +283,31 @@ class HydraB200Model:
         return lg
 
     __call__ = forward
+
+    def eval_loss(self, ids: Tensor, targets: Optional[Tensor] = None, reduction: str = "mean",
+                  ignore_index: int = -100):
+        """Next-token cross-entropy as the reference's evaluation helper computes it (diagnostics/eval_checkpoint.py:
+        168-193): with ``targets=None`` the model runs on ``ids[:, :-1]`` and is scored against ``ids[:, 1:]``;
+        otherwise ``targets`` [B, S] pairs with ``ids`` [B, S] (``ignore_index`` entries do not count).
+        ``reduction``: "mean" (over counted tokens), "sum", or "none" (fp32 [B, S] per-token losses)."""
+        if reduction not in ("mean", "sum", "none"):
+            raise ValueError(f"unknown reduction {reduction!r}")
+        if targets is None:
+            if ids.shape[1] < 2:
+                raise ValueError("eval_loss needs at least two tokens per sequence")
+            ids, targets = ids[:, :-1], ids[:, 1:]
+        if tuple(targets.shape) != tuple(ids.shape):
+            raise ValueError("targets must have the shape of ids")
+        B, S = ids.shape
+        self.forward(ids)
+        nll = cross_entropy_rows(self._logits, targets.to(self.device).reshape(-1), vocab=self.vocab_size,
+                                 ignore_index=ignore_index)
+        if reduction == "none":
+            return nll.view(B, S)
+        total = nll.sum()
+        if reduction == "sum":
+            return total
+        return total / (targets != ignore_index).sum().clamp(min=1).to(total.dtype)
 
     def forward_hidden(self, ids: Tensor) -> Tensor:
         """Post-norm hidden states [B, S, dim] (HydraModel.forward_hidden, model.py:508-520)."""

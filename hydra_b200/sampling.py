@@ -12,6 +12,31 @@ from torch import Tensor
 from . import _lib, kernels
 
 
+def cross_entropy_rows(logits: Tensor, targets: Tensor, vocab: Optional[int] = None, ignore_index: int = -100) -> Tensor:
+    """Per-row negative log-likelihood (``hb200_cross_entropy_rows``): logits bf16 [N, ld] on a CUDA device (row
+    stride ``logits.stride(0)``, the first ``vocab`` columns count), targets int64 [N] -> fp32 [N], 0 where the target
+    is ``ignore_index``.  Summed or averaged it is ``F.cross_entropy`` of the reference's evaluation helper
+    (diagnostics/eval_checkpoint.py:168-193), computed in fp32 from the bf16 logits."""
+    if not logits.is_cuda or targets.device != logits.device:
+        raise RuntimeError("cross_entropy_rows needs CUDA tensors on one device (there is no CPU fallback)")
+    if logits.dtype != torch.bfloat16 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("cross_entropy_rows: logits must be bf16 [N, V] with unit column stride")
+    N = logits.shape[0]
+    V = int(vocab) if vocab is not None else logits.shape[1]
+    targets = targets.to(torch.int64).contiguous().view(-1)
+    if targets.numel() != N or not 1 <= V <= logits.shape[1]:
+        raise ValueError("cross_entropy_rows: one target per row, vocab within the row length")
+    bad = (targets != ignore_index) & ((targets < 0) | (targets >= V))
+    if bool(bad.any()):
+        raise ValueError("cross_entropy_rows: a target lies outside [0, vocab)")
+    out = torch.empty(N, dtype=torch.float32, device=logits.device)
+    with kernels._on(logits.device):
+        _lib.check(_lib.lib().hb200_cross_entropy_rows(
+            logits.data_ptr(), targets.data_ptr(), N, V, logits.stride(0) if N > 1 else max(logits.stride(0), V),
+            int(ignore_index), out.data_ptr(), kernels._stream(logits.device)), "cross_entropy_rows")
+    return out
+
+
 def sample_rows(logits: Tensor, temperature: float = 0.8, top_k: int = 50, top_p: float = 0.9,
                 uniforms: Optional[Tensor] = None, generator: Optional[torch.Generator] = None,
                 vocab: Optional[int] = None, out: Optional[Tensor] = None) -> Tensor:

@@ -175,6 +175,13 @@ int hb200_embed(const int64_t* ids, const void* table, void* out, int64_t T, int
  * (diagnostics/eval_checkpoint.py:112-166) in its deterministic, temperature-free form. */
 int hb200_argmax_rows(const void* x, int64_t rows, int cols, int64_t ld, int64_t* out, void* stream);
 
+/* Token-level cross-entropy of bf16 logit rows, the loss of the reference's evaluation helper
+ * (diagnostics/eval_checkpoint.py:168-193: F.cross_entropy of the logits against the next tokens):
+ * nll[r] = logsumexp(row r over the first `cols` entries) - row[targets[r]], fp32; 0 where targets[r] == ignore_index
+ * (F.cross_entropy's default -100).  Other targets must lie in [0, cols).  The caller reduces (sum / mean). */
+int hb200_cross_entropy_rows(const void* logits, const int64_t* targets, int64_t rows, int cols, int64_t ld,
+                             int64_t ignore_index, float* nll, void* stream);
+
 /* The sampling step of the reference's generation helper (diagnostics/eval_checkpoint.py:133-155) for bf16 rows:
  * logits / temperature; top_k > 0: values below the k-th largest are removed (ties with it stay); top_p < 1: in
  * descending order a token is removed iff the probability mass before it exceeds top_p (the first always stays),

@@ -745,3 +745,15 @@ def config_from_state_dict(sd: Dict[str, Tensor], *, n_heads: int, n_kv_heads: i
                        n_kv_heads=n_kv_heads, compression_factor=compression_factor,
                        max_seq_len=max_seq_len, mod_capacity=mod_capacity, mor_min_depth=mor_min_depth,
                        hidden_dim=F_)
+
+
+def eval_loss(ids: Tensor, p: Dict[str, Tensor], cfg: HydraConfig, reduction: str = "mean") -> Tensor:
+    """The loss of the reference's evaluation helper (diagnostics/eval_checkpoint.py:168-193): the model on
+    ``ids[:, :-1]``, F.cross_entropy against ``ids[:, 1:]`` (sum over tokens there; "mean" divides by their number,
+    which is what the helper returns at the end)."""
+    logits = model_forward(ids[:, :-1], p, cfg)
+    tgt = ids[:, 1:].clamp(0, cfg.vocab_size - 1)
+    nll = torch.nn.functional.cross_entropy(logits.reshape(-1, logits.shape[-1]), tgt.reshape(-1), reduction="none")
+    if reduction == "none":
+        return nll.view(tgt.shape)
+    return nll.sum() if reduction == "sum" else nll.mean()

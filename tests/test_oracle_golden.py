@@ -193,3 +193,15 @@ def test_static_routing_mode_matches_reference():
     # the mode matters: hard routing on the same weights gives other logits
     cfg.adaptive, cfg.static_routing = True, False
     assert float((O.model_forward(ids, w, cfg) - torch.from_numpy(fx["logits"])).abs().max()) > 1e-2
+
+
+def test_eval_loss_is_cross_entropy_of_the_forward():
+    """eval_checkpoint.py:168-193: F.cross_entropy(model(tokens[:, :-1]), tokens[:, 1:]), summed, divided by the count."""
+    fx, cfg, w = G.model_fixture("model_hd32.npz")
+    ids = torch.from_numpy(fx["ids"]).clamp(0, cfg.vocab_size - 1)[:, :40]
+    logits = O.model_forward(ids[:, :-1], w, cfg)
+    want = torch.nn.functional.cross_entropy(logits.reshape(-1, cfg.vocab_size), ids[:, 1:].reshape(-1), reduction="sum")
+    assert float(O.eval_loss(ids, w, cfg, reduction="sum")) == pytest.approx(float(want), rel=1e-6)
+    assert float(O.eval_loss(ids, w, cfg)) == pytest.approx(float(want) / ids[:, 1:].numel(), rel=1e-6)
+    # an untrained model scores near the uniform loss
+    assert abs(float(O.eval_loss(ids, w, cfg)) - float(torch.log(torch.tensor(float(cfg.vocab_size))))) < 1.5
