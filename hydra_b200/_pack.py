@@ -131,6 +131,15 @@ class PackedModel:
         self.device = device
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)
 
+    def resize_rope(self, max_seq_len: int) -> None:
+        """Grow the RoPE tables (never shrinks them); the old tables stay alive until the stream has drained."""
+        if max_seq_len <= self.struct.max_seq_len:
+            return
+        torch.cuda.current_stream(self.device).synchronize()
+        self.cos, self.sin = rope_tables(max_seq_len, self.struct.head_dim, self.device)
+        self.struct.rope_cos, self.struct.rope_sin = self.cos.data_ptr(), self.sin.data_ptr()
+        self.struct.max_seq_len = max_seq_len
+
     def workspace(self, B: int, S: int) -> Tensor:
         """A workspace of at least hb200_model_workspace_bytes(B, S); one buffer is kept and grown on demand, so a
         generation loop whose sequence grows by one token per step does not reallocate every step."""

@@ -309,6 +309,14 @@ class HydraB200Model:
             return total
         return total / (targets != ignore_index).sum().clamp(min=1).to(total.dtype)
 
+    def resize_rope_cache(self, new_max_seq_len: int) -> None:
+        """HydraModel.resize_rope_cache (model.py:376-392): longer sequences than the model was built for.  The tables
+        only ever grow; ``max_seq_len`` takes the new value, as in the reference."""
+        new_max_seq_len = int(new_max_seq_len)
+        with kernels._on(self.device):
+            self.packed.resize_rope(new_max_seq_len)
+        self.max_seq_len = new_max_seq_len
+
     def forward_hidden(self, ids: Tensor) -> Tensor:
         """Post-norm hidden states [B, S, dim] (HydraModel.forward_hidden, model.py:508-520)."""
         return self.forward(ids, logits=False, hidden=True)

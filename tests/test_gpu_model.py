@@ -433,3 +433,21 @@ def test_head_shapes_of_the_reference_presets(dim, H, KV, note):
     e2 = rel_l2(dl.float().cpu(), teacher_forced_oracle(prompt, seq.cpu()[:, 66:], w, cfg))
     print(f"{note}: prefill rel_l2 {e:.2e}, cached decode rel_l2 {e2:.2e}")
     assert e <= 1e-2 and e2 <= 1.5e-2
+
+
+def test_resize_rope_cache():
+    """HydraModel.resize_rope_cache (model.py:376-392): a model built for 64 positions, grown to 200, gives the logits of
+    a model built for 200 bit for bit; before the resize the longer input is refused."""
+    from hydra_b200._lib import Hb200Error
+    fx, cfg, w = G.model_fixture("model_hd16.npz")
+    ids = torch.from_numpy(fx["ids"]).clamp(0, cfg.vocab_size - 1)
+    long_ids = torch.cat([ids, ids[:, :40]], dim=1).cuda()             # 168 positions
+    small = build(w, cfg, max_seq_len=64)
+    with pytest.raises(Hb200Error):
+        small(long_ids)
+    small.resize_rope_cache(200)
+    assert small.max_seq_len == 200
+    big = build(w, cfg, max_seq_len=200)
+    assert torch.equal(small(long_ids), big(long_ids))
+    small.resize_rope_cache(100)                                       # never shrinks the tables
+    assert torch.equal(small(long_ids), big(long_ids))
