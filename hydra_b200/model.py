@@ -228,10 +228,13 @@ class HydraB200Model:
                     mlp_rows=torch.zeros((NB, R), dtype=torch.int32, device=d),
                     block_out=torch.zeros((NB, T, self.dim), dtype=torch.bfloat16, device=d) if block_out else None)
 
-    def forward(self, ids: Tensor, *, taps: bool = False, forced: Optional[Taps] = None, block_out: bool = False,
-                logits: bool = True, hidden: bool = False):
+    def forward(self, ids: Tensor, mask: Optional[Tensor] = None, *, taps: bool = False, forced: Optional[Taps] = None,
+                block_out: bool = False, logits: bool = True, hidden: bool = False):
         """ids int64 [B, S] on this model's device -> logits bf16 [B, S, vocab] (a view of a buffer whose rows are
         padded to a multiple of 8 columns; the buffer is reused by the next call with the same shape).
+
+        ``mask`` is accepted and ignored, exactly as the reference does: ``HydraModel.forward(x, mask)`` hands it to
+        its blocks, and both block types drop it before the attention call (blocks.py:645-657, model.py:143-159).
 
         taps=True records routing decisions in ``self.last_taps``; ``forced`` replays the decisions of an earlier
         run (its ``depths`` and ``mod_idx``).  hidden=True returns the post-norm hidden state instead/as well.

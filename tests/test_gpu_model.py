@@ -451,3 +451,13 @@ def test_resize_rope_cache():
     assert torch.equal(small(long_ids), big(long_ids))
     small.resize_rope_cache(100)                                       # never shrinks the tables
     assert torch.equal(small(long_ids), big(long_ids))
+
+
+def test_model_level_mask_is_ignored_as_in_the_reference():
+    """HydraModel.forward(x, mask) hands the mask to blocks that drop it (blocks.py:645-657): the logits do not depend on it."""
+    fx, cfg, w = G.model_fixture("model_hd32.npz")
+    ids = torch.from_numpy(fx["ids"]).clamp(0, cfg.vocab_size - 1).cuda()
+    m = build(w, cfg)
+    mask = torch.ones_like(ids)
+    mask[:, -7:] = 0
+    assert torch.equal(m(ids, mask).clone(), m(ids))
