@@ -719,12 +719,12 @@ __global__ void decode_advance_kernel(int32_t* pos_ptr, const int64_t* __restric
   if (b == 0) *pos_ptr = pos + 1;
 }
 
-// Contractions of a decode step: at most 128 rows -> the cluster split-K weight-streaming kernel (gemm_impl 0); larger
-// batches, or gemm_impl 1 (the mma.sync cross-check), take the general entry point.
+// Contractions of a decode step: up to 512 rows (four 128-row tiles) -> the cluster split-K weight-streaming kernel
+// (gemm_impl 0); larger batches, or gemm_impl 1 (the mma.sync cross-check), take the general entry point.
 static int dgemm(const hb200_model* m, const DecodeWs& w, const void* A, const void* W, void* C, int M, int N, int K,
                  int64_t ldc, int epi, const void* resid, float alpha, const int32_t* rows, const int32_t* m_dev,
                  int32_t* err, cudaStream_t st, bool chain) {
-  if (m->gemm_impl == 0 && M <= 128) {
+  if (m->gemm_impl == 0 && M <= 512) {
     GemmParams p{(const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, K, K, ldc, epi,
                  (const __nv_bfloat16*)resid, epi == EPI_SCATTER_ADD ? 1.0f : alpha, rows, m_dev, err};
     return launch_gemm_skinny(p, st, chain);

@@ -1,4 +1,5 @@
-// Skinny-M bf16 GEMM for decode (M <= 128 rows):  C = epilogue(A W^T),  A [M,K], W [N,K], both K-major.
+// Skinny-M bf16 GEMM for decode (M <= 512 rows, one 128-row tile per grid.y):  C = epilogue(A W^T),  A [M,K], W [N,K],
+// both K-major.
 //
 // With a handful of rows the contraction is bound by streaming W from HBM once, so the work is cut for bandwidth,
 // not for tensor throughput: one CTA per (64..128 weight rows, one slice of K), two CTAs per SM, so even a 2048 x 5632
@@ -25,6 +26,7 @@
 namespace hb200 {
 
 constexpr int SK_BM = 128, SK_BN = 128, SK_BK = 64;
+constexpr int SK_MAX_M = 512;              // up to four 128-row tiles (grid.y); beyond that the general kernel is the better fit
 constexpr int SK_RING_BYTES = 96 * 1024;   // operand ring: as many stages of (A rows + tile width) x 64 as fit, at most 12
 constexpr int SK_MAX_STAGES = 12;
 constexpr int SK_CTAS_PER_SM = 2;          // two CTAs share an SM, so the weight prefetch of the next contraction of a chain
@@ -83,8 +85,9 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
 // (`old`, `grow` = global row); groups that were not prefetched (column tail) take the generic epilogue.
 constexpr int SK_MAX_GROUPS = 4;    // column share of a cluster member: at most 64 columns = 4 groups of 16
 template <int KS>
-__device__ __forceinline__ void reduce_share(const GemmParams& p, uint32_t part_addr, int m, int tile_col0, int c_first,
-                                             int cw, long long grow, const uint4 (&old)[SK_MAX_GROUPS][2]) {
+__device__ __forceinline__ void reduce_share(const GemmParams& p, uint32_t part_addr, int m, int m_glob, int tile_col0,
+                                             int c_first, int cw, long long grow,
+                                             const uint4 (&old)[SK_MAX_GROUPS][2]) {
   uint32_t peer[KS];
 #pragma unroll
   for (int s = 0; s < KS; ++s) peer[s] = map_to_cta(part_addr + (uint32_t)((c_first * SK_BM + m) * 4), (uint32_t)s);
@@ -120,7 +123,7 @@ __device__ __forceinline__ void reduce_share(const GemmParams& p, uint32_t part_
         *reinterpret_cast<uint4*>(dst + h8 * 8) = o;
       }
     } else {
-      epilogue_row_chunk<16>(p, m, col, v);
+      epilogue_row_chunk<16>(p, m_glob, col, v);
     }
   }
 }
@@ -167,6 +170,7 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) gemm_skinny_kernel
   // keeps each stage's barrier open until the matching A load has been issued).  W must not be written by the
   // preceding kernels of the chain.
   const int nt = blockIdx.x / ksplit, ks = blockIdx.x - nt * ksplit;   // ks == rank in the cluster
+  const int m_base = (int)blockIdx.y * SK_BM;                          // 128-row tile of A / C (batches beyond 128 rows)
   const int kb0 = ks * kb_per, kb1_full = min(k_blocks, kb0 + kb_per);
   const int pre = max(0, min(n_stages, kb1_full - kb0));
   const uint32_t b_bytes = stage_bytes - a_bytes;
@@ -182,10 +186,11 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) gemm_skinny_kernel
   if (warp == 0 && lane == 0) {
     for (int i = 0; i < pre; ++i) {
       mbar_arrive_expect_tx(full_bar(i), a_bytes);
-      tma_load_2d(base + i * stage_bytes, &tma_a, (kb0 + i) * SK_BK, 0, full_bar(i));
+      tma_load_2d(base + i * stage_bytes, &tma_a, (kb0 + i) * SK_BK, m_base, full_bar(i));
     }
   }
-  const int M = p.m_dev ? min(__ldcg(p.m_dev), p.M) : p.M;
+  const int M_all = p.m_dev ? min(__ldcg(p.m_dev), p.M) : p.M;
+  const int M = min(max(M_all - m_base, 0), SK_BM);                     // live rows of this tile
   const int kb1 = (M > 0) ? kb1_full : kb0;
   const bool has_work = kb1 > kb0;                                      // a trailing slice may be empty
 
@@ -205,7 +210,7 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) gemm_skinny_kernel
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
           const uint32_t sa = base + stage * stage_bytes;
           mbar_arrive_expect_tx(full_bar(stage), stage_tx);
-          tma_load_2d(sa, &tma_a, kb * SK_BK, 0, full_bar(stage));
+          tma_load_2d(sa, &tma_a, kb * SK_BK, m_base, full_bar(stage));
           tma_load_2d(sa + a_bytes, &tma_b, kb * SK_BK, nt * bn, full_bar(stage));
           if (++stage == n_stages) { stage = 0; phase ^= 1u; }
         }
@@ -241,7 +246,7 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) gemm_skinny_kernel
     // read-modify-write epilogues of split tiles: this thread's row index and the old values of its column share are
     // requested now, so both round trips hide behind the mainloop
     if (ksplit > 1 && (p.epilogue == EPI_RESID || p.epilogue == EPI_SCATTER_ADD) && (p.N % 8 == 0) && m < M) {
-      rmw_row = (p.epilogue == EPI_SCATTER_ADD) ? (long long)__ldcg(p.rows + m) : (long long)m;
+      rmw_row = (p.epilogue == EPI_SCATTER_ADD) ? (long long)__ldcg(p.rows + m_base + m) : (long long)(m_base + m);
       const __nv_bfloat16* src = (p.epilogue == EPI_RESID) ? p.resid : p.C;
       const int cw = bn / ksplit;
 #pragma unroll
@@ -267,7 +272,7 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) gemm_skinny_kernel
             float v[32];
             tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
             const int col = nt * bn + c * 32;
-            if (m < M && col < p.N) epilogue_row_chunk<32>(p, m, col, v);
+            if (m < M && col < p.N) epilogue_row_chunk<32>(p, m_base + m, col, v);
           }
         }
       } else {
@@ -295,9 +300,9 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) gemm_skinny_kernel
       const int m = (warp & 3) * 32 + lane;
       if (m < M) {
         const int cw = bn / ksplit;                                // this CTA's share of the tile's columns
-        if (ksplit == 2) reduce_share<2>(p, s_addr(part), m, nt * bn, ks * cw, cw, rmw_row, rmw_old);
-        else if (ksplit == 4) reduce_share<4>(p, s_addr(part), m, nt * bn, ks * cw, cw, rmw_row, rmw_old);
-        else reduce_share<8>(p, s_addr(part), m, nt * bn, ks * cw, cw, rmw_row, rmw_old);
+        if (ksplit == 2) reduce_share<2>(p, s_addr(part), m, m_base + m, nt * bn, ks * cw, cw, rmw_row, rmw_old);
+        else if (ksplit == 4) reduce_share<4>(p, s_addr(part), m, m_base + m, nt * bn, ks * cw, cw, rmw_row, rmw_old);
+        else reduce_share<8>(p, s_addr(part), m, m_base + m, nt * bn, ks * cw, cw, rmw_row, rmw_old);
       }
     }
     cluster_sync_all();                                            // nobody leaves while a peer may still read it
@@ -317,14 +322,15 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) gemm_skinny_kernel
 }
 
 int launch_gemm_skinny(const GemmParams& p, cudaStream_t st, bool chained) {
-  HB_REQUIRE(p.M >= 1 && p.M <= SK_BM, HB200_ERR_UNSUPPORTED, "skinny gemm: M = %d (1..%d rows)", p.M, SK_BM);
+  HB_REQUIRE(p.M >= 1 && p.M <= SK_MAX_M, HB200_ERR_UNSUPPORTED, "skinny gemm: M = %d (1..%d rows)", p.M, SK_MAX_M);
   const SkinnyPlan s = skinny_plan(p.N, p.K);
   CUtensorMap ta, tb;
   const int a_rows = p.M <= 64 ? 64 : SK_BM;
   HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, (uint32_t)a_rows));
   HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, (uint32_t)s.bn));
   HB_PROPAGATE(ensure_dynamic_smem((const void*)gemm_skinny_kernel, (size_t)(SK_SMEM_BYTES)));
-  return launch_chained(gemm_skinny_kernel, dim3((unsigned)(s.n_tiles * s.ksplit)), dim3(SK_THREADS), SK_SMEM_BYTES, st,
+  const unsigned m_tiles = (unsigned)((p.M + SK_BM - 1) / SK_BM);     // each streams W again: from L2 after the first
+  return launch_chained(gemm_skinny_kernel, dim3((unsigned)(s.n_tiles * s.ksplit), m_tiles), dim3(SK_THREADS), SK_SMEM_BYTES, st,
                         chained, s.ksplit, ta, tb, p, s.bn, a_rows, s.ksplit, s.kb_per, s.k_blocks);
 }
 

@@ -102,8 +102,8 @@ int hb200_gemm_bf16(const void* A, const void* W, void* C, int M, int N, int K, 
                     const int32_t* rows, const int32_t* m_dev, int impl, int32_t* err_flag,
                     void* stream);
 
-/* The same contraction for M <= 128 rows (decode), where streaming W from HBM once is the bound: one CTA per
- * (128 weight rows, slice of K) so that all SMs stream, tcgen05/TMEM/TMA inside a CTA, and the K slices of a row tile
+/* The same contraction for M <= 512 rows (decode; one 128-row tile per grid.y), where streaming W from HBM once is the
+ * bound: one CTA per (128 weight rows, slice of K) so that all SMs stream, tcgen05/TMEM/TMA inside a CTA, and the K slices of a row tile
  * reduced in fixed order through the distributed shared memory of a thread-block cluster (deterministic; no global
  * scratch, no atomics).  No counterpart in the reference (which has no decode path); arguments as hb200_gemm_bf16. */
 int hb200_gemm_skinny_bf16(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda,

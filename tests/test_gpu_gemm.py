@@ -157,7 +157,8 @@ def skinny(L, A, W, *, epi=0, resid=None, alpha=1.0, rows=None, m_dev=None, C_ou
 
 
 SKINNY_SHAPES = [(64, 2048, 5632), (64, 640, 2048), (8, 64, 192), (37, 512, 1536), (128, 2048, 512), (1, 256, 64),
-                 (77, 50257, 256), (64, 136, 72), (5, 11264, 2048), (100, 384, 1024)]
+                 (77, 50257, 256), (64, 136, 72), (5, 11264, 2048), (100, 384, 1024),
+                 (129, 512, 256), (256, 2048, 5632), (300, 640, 2048), (512, 1000, 192)]      # several 128-row tiles
 
 
 @pytest.mark.parametrize("M,N,K", SKINNY_SHAPES)
@@ -203,12 +204,33 @@ def test_skinny_epilogues_and_device_row_count(L):
     assert torch.equal(out, cur)
 
 
+def test_skinny_row_tiles_with_read_modify_write_epilogues(L):
+    """200 rows = two 128-row tiles: residual, and scatter-add with a device-side row count that ends inside the
+    second tile, inside the first one (the second tile's CTAs find no live rows), and at zero."""
+    M, D, F = 200, 1024, 1408
+    A, W, X = rnd(M, 512, seed=41), rnd(D, 512, seed=42, scale=0.05), rnd(M, D, seed=43)
+    out = skinny(L, A, W, epi=L.EPI_RESID, resid=X, alpha=0.5)
+    assert_close_bf16(out, X.float() + 0.5 * (A.float() @ W.float().T), what="skinny resid, 2 tiles")
+    A, W = rnd(M, F, seed=44), rnd(D, F, seed=45, scale=0.02)
+    cur = rnd(M, D, seed=46)
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(47)).to(torch.int32).cuda()
+    for live in (171, 60, 128, 0):
+        m_dev = torch.tensor([live], dtype=torch.int32, device="cuda")
+        ref = cur.float().clone()
+        ref[rows[:live].long()] += (A.float() @ W.float().T)[:live]
+        out = skinny(L, A, W, epi=L.EPI_SCATTER_ADD, rows=rows, m_dev=m_dev, C_out=cur.clone())
+        assert_close_bf16(out, ref, what=f"skinny scatter_add, {live} live rows")
+        untouched = torch.ones(M, dtype=torch.bool)
+        untouched[rows[:live].long().cpu()] = False
+        assert torch.equal(out[untouched.cuda()], cur[untouched.cuda()])
+
+
 def test_skinny_agrees_with_the_large_kernel(L):
     A, W = rnd(64, 2048, seed=33), rnd(640, 2048, seed=34, scale=0.05)
     assert rel_l2(skinny(L, A, W).float(), gemm(L, A, W).float()) < 2e-3
 
 
 def test_skinny_argument_errors(L):
-    A, W = rnd(129, 64), rnd(128, 64)
+    A, W = rnd(513, 64), rnd(128, 64)
     with pytest.raises(L.Hb200Error):
-        skinny(L, A, W)                                # more than 128 rows
+        skinny(L, A, W)                                # more than four 128-row tiles
