@@ -143,13 +143,15 @@ def test_odd_kv_head_count_value_shift_split_inside_a_head():
     check_against_oracle(build(w, cfg), w, cfg, prompt, 6, "12q/3kv")
 
 
-def test_batch_beyond_the_skinny_gemm_limit():
-    """130 sequences: the contractions of the step fall back from the 128-row decode kernel to the general one."""
+@pytest.mark.parametrize("B", [130, 520])
+def test_batches_beyond_one_row_tile(B):
+    """130 sequences: the decode contractions run as two 128-row tiles of the weight-streaming kernel; 520: beyond its
+    four tiles, they fall back to the general GEMM kernel."""
     cfg = O.HydraConfig(vocab_size=320, dim=256, n_mor_blocks=3, recursions_per_block=2, n_heads=4, n_kv_heads=2,
                         max_seq_len=48, mod_capacity=0.75)
     w = O.init_params(cfg, seed=17, perturb=True)
-    prompt = torch.randint(0, 320, (130, 9), generator=torch.Generator().manual_seed(8))
-    check_against_oracle(build(w, cfg), w, cfg, prompt, 4, "B=130")
+    prompt = torch.randint(0, 320, (B, 9), generator=torch.Generator().manual_seed(8))
+    check_against_oracle(build(w, cfg), w, cfg, prompt, 4, f"B={B}")
 
 
 def test_session_errors():
