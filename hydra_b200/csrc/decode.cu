@@ -41,7 +41,7 @@ int launch_argmax_rows(const void* x, int64_t rows, int cols, int64_t ld, int64_
 struct DecodeWs {
   __nv_bfloat16 *x0, *x1, *a, *qkv, *aq, *ak, *c2q, *qnew, *o, *cur, *ug, *act, *hid, *logits;
   float *qm, *km, *score, *rlogit;
-  int32_t *depth, *rows, *counts;
+  int32_t *depth, *rows, *counts, *hints;
   size_t bytes;
 };
 
@@ -78,6 +78,7 @@ static DecodeWs carve_decode(const hb200_model* m, int B, void* base) {
   w.depth = (int32_t*)take(B * 4);
   w.rows = (int32_t*)take(B * 4);
   w.counts = (int32_t*)take((size_t)m->n_blocks * m->n_rec * 4);
+  w.hints = (int32_t*)take((size_t)m->n_blocks * m->n_rec * 2 * 4);   // row counts of the previous step, per GEMM site
   w.bytes = off;
   return w;
 }
@@ -723,10 +724,10 @@ __global__ void decode_advance_kernel(int32_t* pos_ptr, const int64_t* __restric
 // (gemm_impl 0); larger batches, or gemm_impl 1 (the mma.sync cross-check), take the general entry point.
 static int dgemm(const hb200_model* m, const DecodeWs& w, const void* A, const void* W, void* C, int M, int N, int K,
                  int64_t ldc, int epi, const void* resid, float alpha, const int32_t* rows, const int32_t* m_dev,
-                 int32_t* err, cudaStream_t st, bool chain) {
+                 int32_t* err, cudaStream_t st, bool chain, int32_t* m_hint = nullptr) {
   if (m->gemm_impl == 0 && M <= 512) {
     GemmParams p{(const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, K, K, ldc, epi,
-                 (const __nv_bfloat16*)resid, epi == EPI_SCATTER_ADD ? 1.0f : alpha, rows, m_dev, err};
+                 (const __nv_bfloat16*)resid, epi == EPI_SCATTER_ADD ? 1.0f : alpha, rows, m_dev, err, m_hint};
     return launch_gemm_skinny(p, st, chain);
   }
   return hb200_gemm_bf16(A, W, C, M, N, K, K, K, ldc, epi, resid, alpha, rows, m_dev, m->gemm_impl, err, st);
@@ -849,11 +850,12 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
       else HB_DROUTE(false, false); }
 #undef HB_DROUTE
       { PS(HB200_K_GEMM_GATE_UP, r, 2 * F, D);
+      int32_t* hint = (r > 0) ? w.hints + ((size_t)bi * R + r) * 2 : nullptr;   // recursion 0 always has rows
       HB_PROPAGATE(dgemm(m, w, w.ug, bw.w_gate_up, w.act, B, 2 * F, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count, err, st,
-                         chain)); }
+                         chain, hint)); }
       { PS(HB200_K_GEMM_DOWN, r, D, F);
       HB_PROPAGATE(dgemm(m, w, w.act, bw.w_down, w.cur, B, D, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count, err, st,
-                         chain)); }
+                         chain, (r > 0) ? w.hints + ((size_t)bi * R + r) * 2 + 1 : nullptr)); }
     }
     const float* next_w = last ? m->norm_w : m->blocks[bi + 1].norm1_w;
     { PS(HB200_K_RMS_NORM, R, D, 0);

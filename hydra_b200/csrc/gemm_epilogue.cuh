@@ -18,6 +18,8 @@ struct GemmParams {
   const int32_t* rows;    // SCATTER_ADD target rows
   const int32_t* m_dev;   // optional live row count on the device
   int32_t* err_flag;
+  int32_t* m_hint = nullptr;   // skinny kernel only: the live row count this launch site saw the last time (written by
+                               // the kernel, read before the wait on the predecessor): 0 -> no speculative weight prefetch
 };
 
 // Consume `n` consecutive fp32 accumulator columns [col, col+n) of logical output row `m`

@@ -172,7 +172,10 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) gemm_skinny_kernel
   const int nt = blockIdx.x / ksplit, ks = blockIdx.x - nt * ksplit;   // ks == rank in the cluster
   const int m_base = (int)blockIdx.y * SK_BM;                          // 128-row tile of A / C (batches beyond 128 rows)
   const int kb0 = ks * kb_per, kb1_full = min(k_blocks, kb0 + kb_per);
-  const int pre = max(0, min(n_stages, kb1_full - kb0));
+  // a launch site whose rows ran out the last time (a late MoR recursion) most likely has none now either: do not
+  // stream weights for it ahead of the wait.  A wrong guess costs the prefetch, nothing else.
+  const bool expect_rows = (p.m_hint == nullptr) || (__ldcg(p.m_hint) > (int)blockIdx.y * SK_BM);
+  const int pre = expect_rows ? max(0, min(n_stages, kb1_full - kb0)) : 0;
   const uint32_t b_bytes = stage_bytes - a_bytes;
   if (warp == 0 && lane == 0) {
     for (int i = 0; i < pre; ++i) {
@@ -191,6 +194,7 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM) gemm_skinny_kernel
   }
   const int M_all = p.m_dev ? min(__ldcg(p.m_dev), p.M) : p.M;
   const int M = min(max(M_all - m_base, 0), SK_BM);                     // live rows of this tile
+  if (p.m_hint != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *p.m_hint = M_all;
   const int kb1 = (M > 0) ? kb1_full : kb0;
   const bool has_work = kb1 > kb0;                                      // a trailing slice may be empty
 
