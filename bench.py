@@ -387,7 +387,8 @@ def main() -> None:
                     help="weak (default): --batch sequences on every GPU; strong: --batch sequences in total, split over the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--micro", default=None, help="run one single-kernel microbenchmark instead of the model "
-                    "(gemm, ccgqa_block, pre_attention, attention, rms_norm, rope, swiglu_ffn, swiglu_act, model_hidden, decode)")
+                    "(gemm, gemm_skinny, ccgqa_block, pre_attention, attention, rms_norm, rope, swiglu_ffn, swiglu_act, "
+                    "model_hidden, decode, sample_rows)")
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=5632)
     ap.add_argument("--k", type=int, default=1024)
