@@ -47,6 +47,11 @@ def test_host_side_argument_validation_without_a_gpu():
     assert L.hb200_gemm_bf16(None, None, None, 1, 1, 1, 8, 8, 8, 0, None, 1.0, None, None, 0, None, None) == -1
     assert L.hb200_model_workspace_bytes(None, 1, 1) == 0
     assert L.hb200_profile_reset(None) == -1
+    assert L.hb200_sample_rows(None, 1, 8, 8, 0.8, 50, 0.9, None, None, None) == -1
+    assert L.hb200_cross_entropy_rows(None, None, 1, 8, 8, -100, None, None) == -1
+    assert L.hb200_argmax_rows(None, 1, 8, 8, None, None) == -1
+    assert L.hb200_gemm_skinny_bf16(None, None, None, 1, 8, 8, 8, 8, 8, 0, None, 1.0, None, None, None, None) == -1
+    assert L.hb200_decode_workspace_bytes(None, 1) == 0
 
 
 def test_registry_matches_reference_semantics():
@@ -139,6 +144,11 @@ def test_product_path_refuses_cpu_tensors():
     from hydra_b200.model import HydraB200Model
     with pytest.raises(RuntimeError, match="CUDA"):
         HydraB200Model({}, n_heads=8, n_kv_heads=2, device="cpu")
+    from hydra_b200.sampling import cross_entropy_rows, sample_rows
+    with pytest.raises(RuntimeError, match="CUDA"):
+        sample_rows(torch.zeros(2, 8, dtype=torch.bfloat16), 0.8, 5, 0.9)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        cross_entropy_rows(torch.zeros(2, 8, dtype=torch.bfloat16), torch.zeros(2, dtype=torch.int64))
     st = K.get_kernel_status()
     for key in ("triton_available", "use_triton_kernels", "fused_rope", "fused_qk_norm", "fused_swiglu",
                 "fused_rms_norm", "liger_ce_available", "use_liger_ce"):
