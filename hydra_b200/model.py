@@ -147,6 +147,16 @@ def _untied_output(sd: Dict[str, Tensor], dev) -> Optional[Tensor]:
     return _bf16(o, dev)
 
 
+def _pad_after_eos(seq: Tensor, prompt_len: int, eos_token_id: Optional[int]) -> Tensor:
+    """Overwrite what follows the first generated ``eos_token_id`` of each row with that token (no-op for None)."""
+    if eos_token_id is None or seq.shape[1] <= prompt_len:
+        return seq
+    gen = seq[:, prompt_len:]
+    after = (gen == eos_token_id).to(torch.int32).cumsum(dim=1) > 0          # from the first end-of-text token on
+    gen[after] = eos_token_id
+    return seq
+
+
 def load_checkpoint(path: str, **model_kwargs) -> "HydraB200Model":
     """Build a HydraB200Model from a checkpoint file written by the reference's trainer (``torch.save`` payload with the
     weights under ``"model"``).  Head counts and routing settings are not stored in the weights: pass ``n_heads``,
@@ -339,12 +349,15 @@ class HydraB200Model:
 
     def generate(self, prompt_ids: Tensor, max_new_tokens: int, mode: str = "reforward", use_graph: bool = True,
                  temperature: Optional[float] = None, top_k: int = 50, top_p: float = 0.9,
-                 generator: Optional[torch.Generator] = None) -> Tensor:
+                 generator: Optional[torch.Generator] = None, eos_token_id: Optional[int] = None) -> Tensor:
         """Generation.  ``mode="reforward"`` (default) is the reference's way; ``mode="cached"`` runs
         :meth:`generate_cached` (latent-space KV cache; an addition the reference does not have).
         ``temperature=None`` (default) chooses greedily; a number turns on the reference's sampler
         (diagnostics/eval_checkpoint.py:133-155: temperature, ``top_k``, ``top_p``; its defaults are 0.8 / 50 / 0.9)
         with uniform numbers drawn from ``generator`` (:func:`hydra_b200.sampling.sample_rows`).
+        ``eos_token_id``: the reference's helper stops its single sequence at the first end-of-text token
+        (eval_checkpoint.py:158-160); a batch advances in lockstep here, so every sequence runs the full length and
+        whatever follows a sequence's first end-of-text token is overwritten with that token.
 
         Re-forward: the whole sequence is run through the model again for every new
         token (diagnostics/eval_checkpoint.py:127-160 re-forwards ``generated`` each step; the reference has no KV
@@ -353,8 +366,9 @@ class HydraB200Model:
         (temperature -> 0): next token = argmax of the last position's logits.
         prompt_ids int64 [B, P] on this device -> int64 [B, P + max_new_tokens]."""
         if mode == "cached":
-            return self.generate_cached(prompt_ids, max_new_tokens, use_graph=use_graph, temperature=temperature,
-                                        top_k=top_k, top_p=top_p, generator=generator)
+            seq = self.generate_cached(prompt_ids, max_new_tokens, use_graph=use_graph, temperature=temperature,
+                                       top_k=top_k, top_p=top_p, generator=generator)
+            return _pad_after_eos(seq, prompt_ids.shape[1], eos_token_id)
         if mode != "reforward":
             raise ValueError(f"unknown generation mode {mode!r} (use 'reforward' or 'cached')")
         if not prompt_ids.is_cuda or prompt_ids.device != self.device:
@@ -386,7 +400,7 @@ class HydraB200Model:
                     sample_rows(last_logits, temperature, top_k, top_p, generator=generator, vocab=self.vocab_size,
                                 out=nxt)
             seq[:, cur] = nxt
-        return seq
+        return _pad_after_eos(seq, P, eos_token_id)
 
     # -- cached decode -----------------------------------------------------------------------------------------------
     def new_decode_session(self, batch: int, capacity: int) -> "DecodeSession":

@@ -201,3 +201,15 @@ def test_install_rebinds_reference_names_and_uninstall_restores(monkeypatch):
     assert mods["hydra.layers.common"].fused_swiglu is orig
     assert mods["hydra.model.framework.blocks"].build_hybrid_attention_module is orig
     assert mods["hydra.layers.common"].FUSED_KERNELS_AVAILABLE is False
+
+
+def test_end_of_text_padding_of_generated_sequences():
+    """generate(eos_token_id=...): the reference's helper stops its sequence at the first end-of-text token
+    (eval_checkpoint.py:158-160); in a batch, what follows a row's first one is overwritten with it.  The prompt is
+    never touched, even if it holds the token."""
+    from hydra_b200.model import _pad_after_eos
+    s = torch.tensor([[9, 2, 3, 9, 4, 5], [1, 2, 7, 7, 9, 3], [1, 2, 3, 4, 5, 6]])
+    out = _pad_after_eos(s.clone(), 2, 9)
+    assert out.tolist() == [[9, 2, 3, 9, 9, 9], [1, 2, 7, 7, 9, 9], [1, 2, 3, 4, 5, 6]]
+    assert torch.equal(_pad_after_eos(s.clone(), 2, None), s)
+    assert torch.equal(_pad_after_eos(s.clone(), 6, 9), s)
