@@ -161,6 +161,13 @@ def test_sampled_generation_in_both_modes():
         assert torch.equal(a, b) and not torch.equal(a, c), mode
         assert torch.equal(a[:, :16], prompt) and int(a.max()) < cfg.vocab_size
         assert not torch.equal(a, m.generate(prompt.cuda(), n_new, mode=mode).cpu())      # not the greedy sequence
+    # end-of-text handling: what follows a row's first end-of-text token is overwritten with it, in both modes
+    greedy = m.generate(prompt.cuda(), n_new, mode="cached").cpu()
+    eos = int(greedy[0, 16 + 3])
+    for mode in ("reforward", "cached"):
+        padded = m.generate(prompt.cuda(), n_new, mode=mode, eos_token_id=eos).cpu()
+        first = int((padded[0, 16:] == eos).nonzero()[0])
+        assert first <= 3 and bool((padded[0, 16 + first:] == eos).all()) and torch.equal(padded[:, :16], prompt)
     gen = torch.Generator(device="cuda").manual_seed(9)
     seq, lg = m.generate_cached(prompt.cuda(), n_new, return_logits=True, temperature=1.0, top_k=40, top_p=0.95,
                                 generator=gen)
