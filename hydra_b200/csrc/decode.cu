@@ -39,7 +39,7 @@ namespace hb200 {
 int launch_argmax_rows(const void* x, int64_t rows, int cols, int64_t ld, int64_t* out, cudaStream_t st, bool chained);
 
 struct DecodeWs {
-  __nv_bfloat16 *x0, *x1, *a, *qkv, *aq, *ak, *c2q, *qnew, *o, *cur, *ug, *act, *hid, *logits;
+  __nv_bfloat16 *sout, *x0, *x1, *a, *qkv, *aq, *ak, *c2q, *qnew, *o, *cur, *ug, *act, *hid, *logits;
   float *qm, *km, *score, *rlogit;
   int32_t *depth, *rows, *counts, *hints;
   size_t bytes;
@@ -57,6 +57,7 @@ static DecodeWs carve_decode(const hb200_model* m, int B, void* base) {
     return p;
   };
   DecodeWs w{};
+  w.sout = (__nv_bfloat16*)take(m->static_routing ? B * D * 2 : 0);   // static routing: weighted sum of the recursion states
   w.x0 = (__nv_bfloat16*)take(B * D * 2);
   w.x1 = (__nv_bfloat16*)take(B * D * 2);
   w.a = (__nv_bfloat16*)take(B * D * 2);
@@ -520,7 +521,9 @@ __global__ void __launch_bounds__(ROUTE_THREADS) decode_route_kernel(
     const float* __restrict__ mor_b, float* __restrict__ score_cache, int32_t* __restrict__ depth, int min_active,
     int32_t* __restrict__ rows, int32_t* __restrict__ count, int32_t* __restrict__ next_count,
     __nv_bfloat16* __restrict__ ug, const int32_t* __restrict__ pos_ptr, int B, int D, int capacity, float cap_ratio,
-    float eps, int n_rec, int min_d) {
+    float eps, int n_rec, int min_d, float* __restrict__ stat_q, float* __restrict__ stat_logit) {
+  // stat_q != nullptr: static routing - every row is taken, the MoD probability sigmoid(clamp(score)) and (recursion 0)
+  // the raw depth-router logit are left for decode_static_update_kernel
   __shared__ float red[ROUTE_THREADS / 32][4];
   __shared__ int bcast[2];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -620,9 +623,12 @@ __global__ void __launch_bounds__(ROUTE_THREADS) decode_route_kernel(
     for (int w8 = 0; w8 < ROUTE_THREADS / 32; ++w8) total += __float_as_int(red[w8][3]);
     sel = total < k;
   }
-  const bool take = room && sel && dep >= min_active;
+  const bool is_static = stat_q != nullptr;
+  const bool take = room && (is_static || (sel && dep >= min_active));
   if (tid == 0) {
     if (HAS_ROUTER) depth[b] = dep;
+    if (HAS_ROUTER && is_static) stat_logit[b] = lm + bias_mor;
+    if (is_static) stat_q[b] = HAS_MOD ? 1.f / (1.f + expf(-fminf(fmaxf(s, -10.f), 10.f))) : 1.f;
     if (HAS_MOD && room) sc[pos] = s;
     int j = -1;
     if (take) {
@@ -638,6 +644,47 @@ __global__ void __launch_bounds__(ROUTE_THREADS) decode_route_kernel(
 #pragma unroll
   for (int q = 0; q < 8; ++q) o[q] = v[q] * ri * g2[q];
   store_bf16x8(ug + (size_t)j * D + i, o);
+}
+
+// ---- static routing, one compact row per CTA (slot j holds sequence rows[j]):
+//   cur[b] += q * mlp[j] + (1 - q) * u[j];   out[b] (+)= w_r * cur[b]   (static_update_kernel of the prefill, same formulas)
+__global__ void __launch_bounds__(256) decode_static_update_kernel(
+    __nv_bfloat16* __restrict__ cur, const __nv_bfloat16* __restrict__ mlp, const __nv_bfloat16* __restrict__ u,
+    const int32_t* __restrict__ rows, const int32_t* __restrict__ count, const float* __restrict__ stat_q,
+    const float* __restrict__ stat_logit, __nv_bfloat16* __restrict__ out, int D, int r, int R, int has_out) {
+  chain_release();
+  chain_wait();
+  const int j = blockIdx.x;
+  if (j >= __ldcg(count)) return;
+  const int b = __ldcg(rows + j);
+  const int i = threadIdx.x * 8;
+  if (i >= D) return;
+  const float q = __ldcg(stat_q + b);
+  float wr = 0.f;
+  if (has_out) {
+    const float d = (float)(R - 1) / (1.f + expf(-3.f * tanhf(0.5f * __ldcg(stat_logit + b))));
+    float sum = 0.f;
+    for (int jj = 0; jj < R; ++jj) {
+      const float e = expf(-(d - (float)jj) * (d - (float)jj));
+      sum += e;
+      if (jj == r) wr = e;
+    }
+    wr /= sum + 1e-8f;
+  }
+  float c[8], m[8], un[8], o[8];
+  load_bf16x8_cg(cur + (size_t)b * D + i, c);
+  load_bf16x8_cg(mlp + (size_t)j * D + i, m);
+  load_bf16x8_cg(u + (size_t)j * D + i, un);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) o[k] = 0.f;
+  if (has_out && r > 0) load_bf16x8_cg(out + (size_t)b * D + i, o);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    c[k] += q * m[k] + (1.f - q) * un[k];
+    o[k] += wr * c[k];
+  }
+  store_bf16x8(cur + (size_t)b * D + i, c);
+  if (has_out) store_bf16x8(out + (size_t)b * D + i, o);
 }
 
 // ---- block exit for one row per CTA: y = RMSNorm(src; w1) (or src if w1 == nullptr), z = RMSNorm(y; w2) --------
@@ -773,6 +820,7 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
   const int lat = H * hd, kvd = KV * hd, C = lat + kvd, nq = lat + 2 * kvd;
   const unsigned row_grid = (unsigned)ceil_div(B, 8);
   const size_t cache_block = (size_t)B * KV * cap * hd;
+  const bool stat = m->static_routing != 0;   // dense compute, soft routing weights (cur is updated by a separate link)
   const float scale = 1.0f / sqrtf((float)hd);
 
   // Every launch of the step is a link of one programmatic-dependent-launch chain: a kernel's scheduling and
@@ -841,8 +889,9 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
 #define HB_DROUTE(MOD_, ROUTER_)                                                                                     \
   HB_PROPAGATE(launch_chained(decode_route_kernel<MOD_, ROUTER_>, dim3(B), dim3(ROUTE_THREADS), 0, st, chain, 1,         \
                               (const __nv_bfloat16*)w.cur, rec, bw.norm2_w, bw.mod_wn, bw.mod_b, bw.mor_w, bw.mor_b,     \
-                              cache, w.depth, r, w.rows, count, (r + 1 < R) ? count + 1 : (int32_t*)nullptr, w.ug,       \
-                              (const int32_t*)ds->pos, B, D, cap, m->mod_capacity, m->norm_eps, R, m->min_depth))
+                              cache, w.depth, stat ? 0 : r, w.rows, count, (r + 1 < R) ? count + 1 : (int32_t*)nullptr, w.ug,       \
+                              (const int32_t*)ds->pos, B, D, cap, m->mod_capacity, m->norm_eps, R, m->min_depth,          \
+                              stat ? w.score : (float*)nullptr, stat ? w.rlogit : (float*)nullptr))
       { PS(HB200_K_SELECT, r, D, 0);
       if (has_mod && need_router) HB_DROUTE(true, true);
       else if (has_mod) HB_DROUTE(true, false);
@@ -854,13 +903,24 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
       HB_PROPAGATE(dgemm(m, w, w.ug, bw.w_gate_up, w.act, B, 2 * F, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count, err, st,
                          chain, hint)); }
       { PS(HB200_K_GEMM_DOWN, r, D, F);
-      HB_PROPAGATE(dgemm(m, w, w.act, bw.w_down, w.cur, B, D, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count, err, st,
-                         chain, (r > 0) ? w.hints + ((size_t)bi * R + r) * 2 + 1 : nullptr)); }
+      if (!stat) {
+        HB_PROPAGATE(dgemm(m, w, w.act, bw.w_down, w.cur, B, D, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count, err, st,
+                           chain, (r > 0) ? w.hints + ((size_t)bi * R + r) * 2 + 1 : nullptr));
+      } else {
+        // static routing: the MLP result of every row (compact order) goes to w.a, free between the qkv projection and
+        // the exit norm; one more link of the chain mixes it into cur and accumulates the weighted state
+        HB_PROPAGATE(dgemm(m, w, w.act, bw.w_down, w.a, B, D, F, D, EPI_STORE, nullptr, 1.0f, nullptr, count, err, st, chain));
+        HB_PROPAGATE(launch_chained(decode_static_update_kernel, dim3(B), dim3(256), 0, st, chain, 1, w.cur,
+                                    (const __nv_bfloat16*)w.a, (const __nv_bfloat16*)w.ug, (const int32_t*)w.rows,
+                                    (const int32_t*)count, (const float*)w.score, (const float*)w.rlogit, w.sout, D, r, R,
+                                    m->adaptive ? 1 : 0));
+      } }
     }
     const float* next_w = last ? m->norm_w : m->blocks[bi + 1].norm1_w;
     { PS(HB200_K_RMS_NORM, R, D, 0);
-    HB_PROPAGATE(launch_chained(decode_dual_norm_kernel, dim3(B), dim3(256), 0, st, chain, 1, (const __nv_bfloat16*)w.cur,
-                                bw.final_norm_w, xout, next_w, last ? w.hid : w.a, D, m->norm_eps)); }
+    HB_PROPAGATE(launch_chained(decode_dual_norm_kernel, dim3(B), dim3(256), 0, st, chain, 1,
+                                (const __nv_bfloat16*)((stat && m->adaptive) ? w.sout : w.cur), bw.final_norm_w, xout, next_w,
+                                last ? w.hid : w.a, D, m->norm_eps)); }
     std::swap(xin, xout);
   }
 #undef HB_ROW_LAUNCH

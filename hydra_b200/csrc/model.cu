@@ -256,7 +256,6 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
   const bool stat = m->static_routing != 0;
   if (stat) {
     HB_REQUIRE(!force, HB200_ERR_INVALID, "static routing makes no routing decisions to replay");
-    HB_REQUIRE(ds == nullptr, HB200_ERR_UNSUPPORTED, "static routing: cached decode is not built (use the re-forward mode)");
   }
   if ((!m->adaptive || stat) && !force) {                  // static routing: every token runs every recursion
     ProfScope ps(m->profile, st, HB200_K_OTHER, bi, 0, T, 0, 0);

@@ -405,8 +405,6 @@ class HydraB200Model:
     # -- cached decode -----------------------------------------------------------------------------------------------
     def new_decode_session(self, batch: int, capacity: int) -> "DecodeSession":
         """Device state for ``batch`` sequences of up to ``capacity`` positions (prompt + generated)."""
-        if getattr(self, "static_routing_mode", False):
-            raise NotImplementedError("cached decode is not built for static_routing_mode (use mode='reforward')")
         return DecodeSession(self, batch, capacity)
 
     def generate_cached(self, prompt_ids: Tensor, max_new_tokens: int, use_graph: bool = True,

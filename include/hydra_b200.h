@@ -233,7 +233,8 @@ typedef struct hb200_model {
   int32_t static_routing;         /* 1: the model was built with static_routing_mode (model.py:202, honoured in eval
                                      too): every token runs every recursion; MoD mixes mlp(u) with u by the router
                                      probability (blocks.py:190-241), MoR weights each recursion's state by soft depth
-                                     weights (mixture_of_recursions.py:482-558).  Prefill / forward only. */
+                                     weights (mixture_of_recursions.py:482-558).  Honoured by the forward, the cached prefill
+                                     and the decode step. */
 } hb200_model;
 
 /* Optional routing taps / forced routing for one forward (device pointers or NULL). */

@@ -629,6 +629,26 @@ def cached_decode_step(tokens: Tensor, p: Dict[str, Tensor], cfg: HydraConfig, c
             depth = torch.full((B,), R - 1, dtype=torch.int64)
         rec = p[pre + "mor_executor.recursion_bias"].reshape(R, D) + p[pre + "mor_executor.recursion_embed.weight"]
         cur = h
+        if cfg.static_routing:
+            # static routing is causal throughout (no top-k over the sequence): the cached step is the forward of the
+            # newest position, exactly (static_block_forward)
+            if cfg.adaptive:
+                d = torch.sigmoid(torch.tanh(logit / 2.0) * 3.0) * (R - 1)
+                wts = torch.exp(-((d.unsqueeze(0) - torch.arange(R, dtype=h.dtype).view(-1, 1)) ** 2))
+                wts = wts / (wts.sum(dim=0, keepdim=True) + 1e-8)
+            out = torch.zeros_like(h)
+            for r in range(R):
+                u = ada_rms_norm(cur + rec[r], p[pre + "norm2.weight"], cfg.norm_eps)
+                delta = swiglu_mlp(u, p[pre + "mlp.gate_up.weight"], p[pre + "mlp.down.weight"])
+                if cfg.block_has_mod(i):
+                    mp = pre + "mod_mlp_wrapper.mod_router.router."
+                    qq = torch.sigmoid((u @ p[mp + "weight"].reshape(-1) + p[mp + "bias"]).clamp(-10.0, 10.0))[:, None]
+                    delta = delta * qq + u * (1 - qq)
+                cur = cur + delta
+                if cfg.adaptive:
+                    out = out + wts[r][:, None] * cur
+            x = rms_norm(out if cfg.adaptive else cur, p[pre + "final_norm.weight"], cfg.norm_eps)
+            continue
         for r in range(R):
             u = ada_rms_norm(cur + rec[r], p[pre + "norm2.weight"], cfg.norm_eps)
             use = depth >= r

@@ -154,6 +154,22 @@ def test_batches_beyond_one_row_tile(B):
     check_against_oracle(build(w, cfg), w, cfg, prompt, 4, f"B={B}")
 
 
+def test_static_routing_mode_decodes_exactly():
+    """static_routing_mode has no top-k over the sequence, so the cached step computes what the re-forward computes for
+    the newest position at ANY MoD capacity: against the oracle's cached decode (teacher-forced), against the GPU's own
+    re-forward of the generated sequence, adaptive and fixed-depth."""
+    fx, cfg, w = G.model_fixture("model_static.npz")
+    assert cfg.static_routing and cfg.mod_capacity < 1.0
+    for adaptive in (True, False):
+        cfg.adaptive = adaptive
+        m = build(w, cfg, static_routing_mode=True)
+        prompt = torch.from_numpy(fx["ids"])[:, :21].clamp(0, cfg.vocab_size - 1)
+        seq, lg = check_against_oracle(m, w, cfg, prompt, 8, f"static routing, adaptive={adaptive}")
+        full = m(seq[:, :-1].cuda()).float().cpu()[:, 20:]          # logits each generated token was chosen from
+        assert rel_l2(lg, full) < 1e-2
+        assert torch.equal(m.generate(prompt.cuda(), 8, mode="cached").cpu(), seq)
+
+
 def test_session_errors():
     fx, cfg, w = G.model_fixture("model_hd16.npz")
     m = build(w, cfg)

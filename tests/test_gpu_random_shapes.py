@@ -2,7 +2,7 @@
 compression factor 2 / 4 / 8, 2-4 blocks of 1-4 recursions, sequence lengths 1 ... 1100 (ragged tiles, sequences
 shorter than the conv halo), batch 1-9, MoD capacity 0.3-1.0, fixed depth, min_depth 1, static routing, untied output
 projection.  Each case: prefill logits against the oracle with the GPU's routing replayed (rel. L2 <= 1.2e-2) and, where
-the mode has one and the shape is within the decode step's limits, cached decode against the oracle's cached decode fed
+the shape is within the decode step's limits, cached decode against the oracle's cached decode fed
 with the GPU's tokens (rel. L2 <= 4e-2: routing is not replayed there, so one depth or MoD decision that flips on bf16
 noise moves a whole row; observed worst 2.3e-2, typical 3e-3).
 Most shapes have no tiled pre-attention kernel of their own and run on the CUDA-core kernel."""
@@ -70,7 +70,7 @@ def test_random_shapes_against_the_oracle(seed):
         e2 = 0.0
         kvd, lat = c["KV"] * c["hd"], c["H"] * c["hd"]
         decodable = kvd <= 256 and lat + kvd <= 1536 and c["H"] // c["KV"] <= 8      # the decode step's stated limits
-        if S >= 2 and not c["static"] and decodable:
+        if S >= 2 and decodable:
             P = max(1, S - 4)
             n_new = min(4, cfg.max_seq_len - P)
             prompt = ids[:, :P]

@@ -62,3 +62,20 @@ def test_cached_decode_with_an_untied_output_projection():
         assert float((full - logits_c[:, step]).abs().max()) < 2e-4
         seq_r = torch.cat([seq_r, full.argmax(-1, keepdim=True)], dim=1)
     assert torch.equal(seq_c, seq_r)
+
+
+def test_cached_decode_in_static_routing_mode_equals_the_reforward():
+    """static_routing_mode has no top-k over the sequence: every operation is causal, so the cached step must reproduce
+    the re-forward of the longer sequence for any MoD capacity (adaptive and fixed-depth blocks)."""
+    fx, cfg, w = G.model_fixture("model_static.npz")
+    assert cfg.static_routing and cfg.mod_capacity < 1.0
+    for adaptive in (True, False):
+        cfg.adaptive = adaptive
+        prompt = torch.from_numpy(fx["ids"])[:, :13].clamp(0, cfg.vocab_size - 1)
+        seq_c, logits_c = O.cached_generate(prompt, w, cfg, 5, return_logits=True)
+        seq_r = prompt.clone()
+        for step in range(5):
+            full = O.model_forward(seq_r, w, cfg)[:, -1]
+            assert float((full - logits_c[:, step]).abs().max()) < 2e-4
+            seq_r = torch.cat([seq_r, full.argmax(-1, keepdim=True)], dim=1)
+        assert torch.equal(seq_c, seq_r)
