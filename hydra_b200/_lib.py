@@ -30,7 +30,7 @@ class Model(C.Structure):
         "min_depth", "adaptive", "max_seq_len", "gemm_impl")] + [
         (n, c_f32) for n in ("mod_capacity", "norm_eps", "residual_scale", "output_scale")] + [
         ("tok_emb", c_vp), ("norm_w", c_vp), ("rope_cos", c_vp), ("rope_sin", c_vp),
-        ("blocks", C.POINTER(BlockWeights)), ("profile", c_vp), ("lm_head", c_vp), ("static_routing", C.c_int32)]
+        ("blocks", C.POINTER(BlockWeights)), ("profile", c_vp), ("lm_head", c_vp), ("static_routing", C.c_int32), ("mor_rampup", c_f32)]
 
 
 class LaunchRecord(C.Structure):

@@ -111,7 +111,7 @@ class PackedModel:
                  ffn_hidden: int, min_depth: int, adaptive: bool, max_seq_len: int, mod_capacity: float,
                  norm_eps: float, residual_scale: float, output_scale: float, blocks: List[PackedBlock],
                  tok_emb: Optional[Tensor], norm_w: Optional[Tensor], device, gemm_impl: int = 0,
-                 lm_head: Optional[Tensor] = None, static_routing: bool = False):
+                 lm_head: Optional[Tensor] = None, static_routing: bool = False, mor_rampup: float = 0.0):
         self.blocks = blocks
         self.block_array = (_lib.BlockWeights * len(blocks))(*[b.struct for b in blocks])
         self.cos, self.sin = rope_tables(max_seq_len, head_dim, device)
@@ -126,7 +126,8 @@ class PackedModel:
             norm_w=norm_w.data_ptr() if norm_w is not None else None,
             rope_cos=self.cos.data_ptr(), rope_sin=self.sin.data_ptr(),
             blocks=C.cast(self.block_array, C.POINTER(_lib.BlockWeights)),
-            lm_head=lm_head.data_ptr() if lm_head is not None else None, static_routing=int(bool(static_routing)))
+            lm_head=lm_head.data_ptr() if lm_head is not None else None, static_routing=int(bool(static_routing)),
+            mor_rampup=float(mor_rampup))
         self._ws: Dict[tuple, Tensor] = {}
         self.device = device
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)

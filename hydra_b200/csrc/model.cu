@@ -59,13 +59,16 @@ __global__ void repack_conv_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfl
 
 // ---- workspace ----------------------------------------------------------------------------------------------
 struct Workspace {
-  __nv_bfloat16 *x0, *x1, *a, *qkv, *q, *k, *v, *o, *cur, *ug, *act;
+  __nv_bfloat16 *x0, *x1, *a, *qkv, *q, *k, *v, *o, *cur, *ug, *act, *blend;
   float *scores, *logits;
-  int32_t *depth, *rows, *sel_idx, *counts;
+  int32_t *depth, *rows, *sel_idx, *counts, *counts2;
   size_t bytes;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// MoR curriculum in the middle of its ramp: the block output is a blend of the adaptive and the fixed-depth path
+static bool mor_blend_active(const hb200_model* m) { return m->adaptive && m->mor_rampup > 0.f && m->mor_rampup < 1.f; }
 
 static Workspace carve(const hb200_model* m, int B, int S, void* base) {
   const size_t T = (size_t)B * S, D = m->dim, lat = (size_t)m->n_heads * m->head_dim,
@@ -94,6 +97,9 @@ static Workspace carve(const hb200_model* m, int B, int S, void* base) {
   w.rows = (int32_t*)take(T * 4);
   w.sel_idx = (int32_t*)take(T * 4);
   w.counts = (int32_t*)take((size_t)m->n_blocks * m->n_rec * 4);
+  const bool blend = mor_blend_active(m);                   // second block output + second set of row counters
+  w.blend = (__nv_bfloat16*)take(blend ? T * D * 2 : 0);
+  w.counts2 = (int32_t*)take(blend ? (size_t)m->n_blocks * m->n_rec * 4 : 0);
   w.bytes = off;
   return w;
 }
@@ -336,6 +342,53 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
   return 0;
 }
 
+// y = s * y + (1 - s) * other, 8 columns per thread
+__global__ void __launch_bounds__(256) blend_rows_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ other,
+                                                         int64_t n8, float s) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float a[8], b[8];
+  load_bf16x8(y + i * 8, a);
+  load_bf16x8(other + i * 8, b);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] = s * a[j] + (1.f - s) * b[j];
+  store_bf16x8(y + i * 8, a);
+}
+
+// HydraMoRBlock.forward (blocks.py:645-657): with the MoR ramp-up scale strictly between 0 and 1 the block is run twice
+// from the same input - fixed depth, then adaptive (whose routing the taps record) - and the two outputs are blended;
+// the next consumer's input norm is then taken from the blend.
+static int block_forward_or_blend(const hb200_model* m, int bi, const __nv_bfloat16* x, const __nv_bfloat16* a_in,
+                                  __nv_bfloat16* y, const float* next_w, __nv_bfloat16* a_next, int B, int S,
+                                  const Workspace& w, const hb200_taps* taps, int32_t* counts, int32_t* err, cudaStream_t st,
+                                  const hb200_decode_state* ds) {
+  if (!mor_blend_active(m)) return block_forward(m, bi, x, a_in, y, next_w, a_next, B, S, w, taps, counts, err, st, ds);
+  HB_REQUIRE(ds == nullptr, HB200_ERR_UNSUPPORTED, "MoR ramp-up blend: cached decode is not built (forward / prefill only)");
+  HB_REQUIRE(!(taps && taps->force_routing), HB200_ERR_UNSUPPORTED, "MoR ramp-up blend: forced routing is not built");
+  const int64_t T = (int64_t)B * S;
+  const int D = m->dim, R = m->n_rec;
+  hb200_model fixed = *m, adaptive = *m;
+  fixed.adaptive = 0;
+  fixed.mor_rampup = adaptive.mor_rampup = 0.f;
+  HB_CUDA(cudaMemsetAsync(w.counts2 + (size_t)bi * R, 0, (size_t)R * 4, st));
+  // both passes take their own input norm (a_in = nullptr): the static-routing path uses w.a as scratch
+  HB_PROPAGATE(block_forward(&fixed, bi, x, nullptr, w.blend, nullptr, nullptr, B, S, w, nullptr, w.counts2, err, st, nullptr));
+  HB_PROPAGATE(block_forward(&adaptive, bi, x, nullptr, y, nullptr, nullptr, B, S, w, taps, counts, err, st, nullptr));
+  {
+    ProfScope ps(m->profile, st, HB200_K_OTHER, bi, R, (int)T, D, 0);
+    blend_rows_kernel<<<(unsigned)ceil_div64(T * (D / 8), 256), 256, 0, st>>>(y, w.blend, T * (D / 8), m->mor_rampup);
+    HB_LAUNCH_CHECK();
+  }
+  if (next_w != nullptr && a_next != nullptr) {
+    ProfScope ps(m->profile, st, HB200_K_RMS_NORM, bi, R, (int)T, D, 0);
+    HB_PROPAGATE(hb200_rms_norm(y, next_w, a_next, T, D, m->norm_eps, HB200_BF16, HB200_F32, st));
+  }
+  if (taps && taps->block_out)
+    HB_CUDA(cudaMemcpyAsync((__nv_bfloat16*)taps->block_out + (size_t)bi * T * D, y, (size_t)T * D * 2,
+                            cudaMemcpyDeviceToDevice, st));
+  return 0;
+}
+
 }  // namespace hb200
 
 using namespace hb200;
@@ -489,8 +542,8 @@ extern "C" int hb200_block_forward(const hb200_model* m, int block_index, const 
   cudaStream_t st = (cudaStream_t)stream;
   int32_t* counts = (taps && taps->mlp_rows) ? taps->mlp_rows : w.counts;
   HB_CUDA(cudaMemsetAsync(counts + (size_t)block_index * m->n_rec, 0, (size_t)m->n_rec * 4, st));
-  return block_forward(m, block_index, (const __nv_bfloat16*)x, nullptr, (__nv_bfloat16*)y, nullptr, nullptr, B, S, w,
-                       taps, counts, err_flag, st);
+  return block_forward_or_blend(m, block_index, (const __nv_bfloat16*)x, nullptr, (__nv_bfloat16*)y, nullptr, nullptr, B, S,
+                                w, taps, counts, err_flag, st, nullptr);
 }
 
 static int run_model(const hb200_model* m, const int64_t* ids, int B, int S, const Workspace& w, void* logits,
@@ -516,7 +569,8 @@ static int run_model(const hb200_model* m, const int64_t* ids, int B, int S, con
     const bool last = (bi == m->n_blocks - 1);
     const float* next_w = last ? m->norm_w : m->blocks[bi + 1].norm1_w;
     // w.a is read by this block's qkv GEMM long before its exit norm overwrites it with the next block's input
-    HB_PROPAGATE(block_forward(m, bi, xin, w.a, xout, next_w, last ? hid : w.a, B, S, w, taps, counts, err_flag, st, ds));
+    HB_PROPAGATE(block_forward_or_blend(m, bi, xin, w.a, xout, next_w, last ? hid : w.a, B, S, w, taps, counts, err_flag, st,
+                                        ds));
     std::swap(xin, xout);
   }
   if (logits != nullptr)

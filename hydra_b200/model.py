@@ -175,7 +175,7 @@ class HydraB200Model:
     def __init__(self, state_dict: Dict[str, Tensor], *, n_heads: int, n_kv_heads: int, compression_factor: int = 4,
                  max_seq_len: int = 2048, mod_capacity: float = 0.5, mor_min_depth: int = 0, adaptive: bool = True,
                  device: str | torch.device = "cuda", norm_eps: float = 1e-6, gemm_impl: int = 0,
-                 static_routing_mode: bool = False):
+                 static_routing_mode: bool = False, mor_rampup_scale: float = 1.0):
         dev = torch.device(device)
         if dev.type != "cuda":
             raise RuntimeError("HydraB200Model needs a CUDA device (there is no CPU fallback)")
@@ -193,6 +193,11 @@ class HydraB200Model:
         self.max_seq_len, self.mod_capacity, self.mor_min_depth, self.adaptive = max_seq_len, mod_capacity, mor_min_depth, adaptive
         # static_routing_mode (model.py:202; the reference honours it in eval too): dense compute, soft routing weights
         self.static_routing_mode = bool(static_routing_mode)
+        # MoR curriculum scale (HydraMoRBlock.get_mor_rampup_scale, blocks.py:645-657): 1 = adaptive routing, <= 0 = the
+        # fixed-depth path, in between every block returns scale * adaptive + (1 - scale) * fixed (forward / prefill only)
+        self.mor_rampup_scale = float(mor_rampup_scale)
+        if adaptive and self.mor_rampup_scale <= 0.0:
+            adaptive = self.adaptive = False
         self.device = dev
         with kernels._on(dev):
             blocks = [PackedBlock(sd, f"layers.{i}.", dev) for i in range(nb)]
@@ -203,7 +208,8 @@ class HydraB200Model:
                 norm_eps=norm_eps, residual_scale=0.5,
                 output_scale=float(os.environ.get("HYDRA_CCGQA_OUTPUT_SCALE", "1.0")), blocks=blocks,
                 tok_emb=_bf16(sd["tok_emb.weight"], dev), norm_w=_f32(sd["norm.weight"], dev), device=dev,
-                gemm_impl=gemm_impl, lm_head=_untied_output(sd, dev), static_routing=self.static_routing_mode)
+                gemm_impl=gemm_impl, lm_head=_untied_output(sd, dev), static_routing=self.static_routing_mode,
+                mor_rampup=self.mor_rampup_scale if 0.0 < self.mor_rampup_scale < 1.0 else 0.0)
         self.ld_logits = (V + 7) // 8 * 8
         self._logits: Optional[Tensor] = None
         self.last_taps: Optional[Taps] = None
@@ -222,7 +228,9 @@ class HydraB200Model:
         kw = dict(n_heads=model.n_heads, n_kv_heads=model.n_kv_heads, compression_factor=model.compression_factor,
                   max_seq_len=model.max_seq_len, mod_capacity=model.mod_capacity,
                   mor_min_depth=getattr(model, "mor_min_depth", 0), adaptive=model.adaptive,
-                  static_routing_mode=bool(getattr(model, "static_routing_mode", False)))
+                  static_routing_mode=bool(getattr(model, "static_routing_mode", False)),
+                  mor_rampup_scale=float(model.layers[0].get_mor_rampup_scale())
+                  if hasattr(model.layers[0], "get_mor_rampup_scale") else 1.0)
         kw.update(overrides)
         return cls(model.state_dict(), **kw)
 
@@ -405,6 +413,9 @@ class HydraB200Model:
     # -- cached decode -----------------------------------------------------------------------------------------------
     def new_decode_session(self, batch: int, capacity: int) -> "DecodeSession":
         """Device state for ``batch`` sequences of up to ``capacity`` positions (prompt + generated)."""
+        if self.adaptive and 0.0 < getattr(self, "mor_rampup_scale", 1.0) < 1.0:
+            raise NotImplementedError("cached decode is not built for a MoR ramp-up scale between 0 and 1 "
+                                      "(use mode='reforward')")
         return DecodeSession(self, batch, capacity)
 
     def generate_cached(self, prompt_ids: Tensor, max_new_tokens: int, use_graph: bool = True,

@@ -235,6 +235,10 @@ typedef struct hb200_model {
                                      probability (blocks.py:190-241), MoR weights each recursion's state by soft depth
                                      weights (mixture_of_recursions.py:482-558).  Honoured by the forward, the cached prefill
                                      and the decode step. */
+  float mor_rampup;               /* MoR curriculum scale (blocks.py:645-657, 731-745).  Strictly between 0 and 1 (with
+                                     adaptive = 1): every block returns scale * adaptive + (1 - scale) * fixed-depth, both
+                                     computed in full - forward / prefill only.  Any other value (0 included): no blend,
+                                     `adaptive` alone decides. */
 } hb200_model;
 
 /* Optional routing taps / forced routing for one forward (device pointers or NULL). */

@@ -57,6 +57,8 @@ class HydraConfig:
     rope_theta: float = 10000.0
     hidden_dim: Optional[int] = None  # override of the MLP width (op-level tests)
     static_routing: bool = False     # static_routing_mode (model.py:202): dense compute with soft routing weights
+    mor_rampup_scale: float = 1.0    # MoR curriculum (blocks.py:731-757): strictly between 0 and 1 the block returns
+                                     # scale * adaptive + (1 - scale) * fixed-depth; <= 0 is the fixed-depth path
 
     @property
     def latent_dim(self) -> int:
@@ -346,6 +348,19 @@ def mor_block_forward(x: Tensor, p: Dict[str, Tensor], i: int, cfg: HydraConfig,
     ``forced`` replays another run's depths / MoD index lists instead of computing
     them, so numerical error can be separated from routing flips.
     """
+    if cfg.adaptive and cfg.mor_rampup_scale < 1.0:
+        # HydraMoRBlock.forward (blocks.py:645-657): both paths are whole block forwards (attention included)
+        import dataclasses
+        s_ = float(cfg.mor_rampup_scale)
+        fixed_cfg = dataclasses.replace(cfg, adaptive=False, mor_rampup_scale=1.0)
+        fixed = mor_block_forward(x, p, i, fixed_cfg, None, forced if s_ <= 0.0 else None)
+        if s_ <= 0.0:
+            return fixed
+        adaptive = mor_block_forward(x, p, i, dataclasses.replace(cfg, mor_rampup_scale=1.0), taps, forced)
+        y = s_ * adaptive + (1.0 - s_) * fixed
+        if taps is not None:
+            taps.block_out[-1] = y.clone()
+        return y
     if cfg.static_routing:
         if forced is not None:
             raise ValueError("static routing makes no routing decisions to replay")

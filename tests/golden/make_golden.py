@@ -135,7 +135,8 @@ def gen_attention(name: str, dim: int, H: int, KV: int, B: int, S: int, seed: in
 
 # ----------------------------------------------------------------------------
 def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: int, mlp_ratio: float,
-              B: int, S: int, cap: float, seed: int, tie: bool = True, static: bool = False) -> None:
+              B: int, S: int, cap: float, seed: int, tie: bool = True, static: bool = False,
+              rampup: float = 1.0) -> None:
     from hydra.model.framework import HydraModel
 
     torch.manual_seed(seed)
@@ -155,7 +156,11 @@ def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: i
         for p in m.parameters():
             bf16_round_(p)
     m.eval()
+    if rampup < 1.0:             # MoR curriculum in the middle of its ramp: scale = steps since enable / ramp steps
+        m.set_mor_curriculum(enable_step=10 ** 6 - int(round(rampup * 1000)) + 1, rampup_steps=1000)
     m.set_global_step(10 ** 6)   # MoD hard routing is off in eval until the step passes its warm-up
+    if rampup < 1.0:
+        assert abs(m.layers[0].get_mor_rampup_scale() - rampup) < 1e-9
     ids = torch.randint(0, vocab, (B, S), generator=torch.Generator().manual_seed(seed + 2))
     ids[0, 0] = vocab + 5        # out-of-range ids are clamped by the reference
     ids[0, 1] = -3
@@ -182,6 +187,7 @@ def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: i
         cap=np.array([cap], dtype=np.float64),
         ffn_hidden=np.array([m.layers[0].mlp.down.weight.shape[1]], dtype=np.int64),
         ids=ids.numpy(), logits=f32(logits), static=np.array([int(static)], dtype=np.int64),
+        rampup=np.array([rampup], dtype=np.float64),
     )
     for i, d in enumerate(depths):
         arrs[f"depths:{i}"] = d.numpy().astype(np.int32)
@@ -336,6 +342,10 @@ if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "sampler":  # only the sampler's filtered distributions
         gen_sampler()
         sys.exit(0)
+    if len(sys.argv) > 1 and sys.argv[1] == "rampup":   # only the model in the middle of its MoR ramp-up
+        gen_model("model_rampup.npz", vocab=200, dim=256, NB=3, R=3, H=4, KV=2, mlp_ratio=1.0,
+                  B=2, S=64, cap=0.75, seed=27, rampup=0.4)
+        sys.exit(0)
     if len(sys.argv) > 1 and sys.argv[1] == "static":   # only the static-routing model
         gen_model("model_static.npz", vocab=200, dim=256, NB=3, R=3, H=4, KV=2, mlp_ratio=1.0,
                   B=2, S=64, cap=0.75, seed=23, static=True)
@@ -366,3 +376,6 @@ if __name__ == "__main__":
     # static_routing_mode=True: dense compute, soft routing weights (also honoured in eval)
     gen_model("model_static.npz", vocab=200, dim=256, NB=3, R=3, H=4, KV=2, mlp_ratio=1.0,
               B=2, S=64, cap=0.75, seed=23, static=True)
+    # MoR curriculum mid-ramp: every block returns 0.4 * adaptive + 0.6 * fixed-depth
+    gen_model("model_rampup.npz", vocab=200, dim=256, NB=3, R=3, H=4, KV=2, mlp_ratio=1.0,
+              B=2, S=64, cap=0.75, seed=27, rampup=0.4)

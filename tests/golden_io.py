@@ -47,5 +47,6 @@ def model_fixture(name: str):
     cfg = HydraConfig(vocab_size=vocab, dim=dim, n_mor_blocks=NB, recursions_per_block=R, n_heads=H,
                       n_kv_heads=KV, max_seq_len=S, mod_capacity=float(fx["cap"][0]),
                       hidden_dim=int(fx["ffn_hidden"][0]),
-                      static_routing=bool(int(fx["static"][0])) if "static" in fx else False)
+                      static_routing=bool(int(fx["static"][0])) if "static" in fx else False,
+                      mor_rampup_scale=float(fx["rampup"][0]) if "rampup" in fx else 1.0)
     return fx, cfg, weights(fx)

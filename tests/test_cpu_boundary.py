@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layouts_match_header_sizes():
     from hydra_b200 import _lib
     assert ctypes.sizeof(_lib.BlockWeights) == 16 * 8 + 8      # 16 pointers + one float, padded
-    assert ctypes.sizeof(_lib.Model) == 12 * 4 + 4 * 4 + 7 * 8 + 8   # last int32 padded to the pointer alignment
+    assert ctypes.sizeof(_lib.Model) == 12 * 4 + 4 * 4 + 7 * 8 + 8   # trailing int32 + float fill one pointer slot
     assert ctypes.sizeof(_lib.Taps) == 6 * 8 + 8
     assert ctypes.sizeof(_lib.LaunchRecord) == 24
     assert ctypes.sizeof(_lib.DecodeState) == 2 * 4 + 8 * 8    # batch, capacity, eight device pointers

@@ -460,3 +460,37 @@ def test_model_level_mask_is_ignored_as_in_the_reference():
     mask = torch.ones_like(ids)
     mask[:, -7:] = 0
     assert torch.equal(m(ids, mask).clone(), m(ids))
+
+
+def test_mor_rampup_blend():
+    """MoR curriculum in the middle of its ramp (blocks.py:645-657): every block returns 0.4 * adaptive + 0.6 * fixed.
+    Logits against the reference's own run (twice its bf16 error), block outputs against the oracle, the end points of
+    the ramp against the two plain paths bit for bit; cached decode and forced replay are refused."""
+    from hydra_b200._lib import Hb200Error
+    fx, cfg, w = G.model_fixture("model_rampup.npz")
+    ids = torch.from_numpy(fx["ids"])
+    B, S = ids.shape
+    m = build(w, cfg, mor_rampup_scale=cfg.mor_rampup_scale)
+    lg = m(ids.cuda(), taps=True, block_out=True).float().cpu()
+    m.check_device_errors()
+    ref = torch.from_numpy(fx["logits"])
+    err, own = rel_l2(lg, ref), float(fx["ref_bf16_rel_l2"][0])
+    print(f"ramp-up blend vs reference fp32 logits: rel_l2 {err:.3e}; reference's own bf16 path: {own:.3e}")
+    assert err <= 2.0 * own + 1e-3
+    ot = O.RoutingTaps()
+    assert max_abs(O.model_forward(ids, w, cfg, taps=ot), ref) < 5e-5
+    tp = m.last_taps
+    bo = tp.block_out.float().cpu().view(cfg.n_mor_blocks, B, S, -1)
+    for i in range(cfg.n_mor_blocks):
+        assert rel_l2(bo[i], ot.block_out[i]) <= 1.5e-2, f"block {i}"
+    d = tp.depths.cpu().long().view(cfg.n_mor_blocks, B, S)
+    assert float((d[0] == ot.depths[0]).float().mean()) > 0.99        # the adaptive pass's routing is what the taps hold
+    ids_c = ids.clamp(0, cfg.vocab_size - 1).cuda()
+    assert torch.equal(build(w, cfg, mor_rampup_scale=0.0)(ids_c), build(w, cfg, adaptive=False)(ids_c))
+    assert torch.equal(build(w, cfg, mor_rampup_scale=1.0)(ids_c), build(w, cfg)(ids_c))
+    assert rel_l2(build(w, cfg)(ids_c).float().cpu(), lg) > 3e-3       # the blend is neither end point
+    with pytest.raises(NotImplementedError):
+        m.generate(ids_c[:, :10], 2, mode="cached")
+    assert m.generate(ids_c[:, :10], 2).shape == (B, 12)
+    with pytest.raises(Hb200Error):
+        m(ids.cuda(), forced=tp)

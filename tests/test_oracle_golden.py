@@ -205,3 +205,23 @@ def test_eval_loss_is_cross_entropy_of_the_forward():
     assert float(O.eval_loss(ids, w, cfg)) == pytest.approx(float(want) / ids[:, 1:].numel(), rel=1e-6)
     # an untrained model scores near the uniform loss
     assert abs(float(O.eval_loss(ids, w, cfg)) - float(torch.log(torch.tensor(float(cfg.vocab_size))))) < 1.5
+
+
+def test_mor_rampup_blend_matches_reference():
+    """MoR curriculum in the middle of its ramp (blocks.py:645-657, 731-745): every block returns
+    0.4 * adaptive + 0.6 * fixed-depth.  Logits, block outputs and the adaptive pass's depths against the reference."""
+    fx, cfg, w = G.model_fixture("model_rampup.npz")
+    assert cfg.mor_rampup_scale == pytest.approx(0.4)
+    ids = torch.from_numpy(fx["ids"])
+    taps = O.RoutingTaps()
+    close(O.model_forward(ids, w, cfg, taps=taps), fx["logits"], 5e-6)
+    for i in range(cfg.n_mor_blocks):
+        close(taps.block_out[i], fx[f"block_out:{i}"], 5e-6)
+        assert np.array_equal(taps.depths[i].numpy().astype(np.int32), fx[f"depths:{i}"])
+    # the end points of the ramp are the two plain paths
+    import dataclasses
+    full = O.model_forward(ids, w, dataclasses.replace(cfg, mor_rampup_scale=1.0))
+    fixed = O.model_forward(ids, w, dataclasses.replace(cfg, adaptive=False, mor_rampup_scale=1.0))
+    close(O.model_forward(ids, w, dataclasses.replace(cfg, mor_rampup_scale=0.0)), fixed.numpy(), 1e-6)
+    close(fixed, fx["logits_fixed"], 5e-6)
+    assert float((full - torch.from_numpy(fx["logits"])).abs().max()) > 1e-3
