@@ -1,4 +1,4 @@
-// Causal grouped-query attention in the CCGQA latent space (head_dim 16 / 32 / 64).
+// Causal grouped-query attention in the CCGQA latent space (head_dim 16 / 32 / 64; 8 on a CUDA-core kernel).
 //
 // One CTA = 64 query rows of one (batch, q-head): 4 warps x 16 rows.  K/V tiles of 64 keys are staged in
 // shared memory; S = QK^T and O += PV run on the tensor cores (mma.sync m16n8k16, bf16 in / fp32 acc),
@@ -177,6 +177,67 @@ __global__ void __launch_bounds__(128) attention_causal_gqa_kernel(const __nv_bf
   }
 }
 
+// Heads narrower than a tensor-core k-step (head_dim 8: the reference's small test models, dim 128 with four heads):
+// one thread per query row, online softmax in registers, K / V rows read as 16-byte pieces (every thread of a warp asks
+// for the same key, so each piece is one broadcast).  Built for coverage, not speed.
+template <int HD>
+__global__ void __launch_bounds__(128) attention_small_head_kernel(const __nv_bfloat16* __restrict__ q,
+                                                                   const __nv_bfloat16* __restrict__ k,
+                                                                   const __nv_bfloat16* __restrict__ v,
+                                                                   __nv_bfloat16* __restrict__ o, int S, int H, int KV,
+                                                                   float scale_log2) {
+  const int i = blockIdx.x * 128 + threadIdx.x;       // query position
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (H / KV);
+  const __nv_bfloat16* kp = k + ((size_t)b * KV + kvh) * S * HD;
+  const __nv_bfloat16* vp = v + ((size_t)b * KV + kvh) * S * HD;
+  float qv[HD], acc[HD];
+#pragma unroll
+  for (int d = 0; d < HD; ++d) { qv[d] = 0.f; acc[d] = 0.f; }
+  if (i < S) {
+#pragma unroll
+    for (int c = 0; c < HD / 8; ++c) {
+      float t[8];
+      load_bf16x8(q + (((size_t)b * H + h) * S + i) * HD + c * 8, t);
+#pragma unroll
+      for (int d = 0; d < 8; ++d) qv[c * 8 + d] = t[d] * scale_log2;
+    }
+  }
+  float mx = -INFINITY, l = 0.f;
+  const int last = min(S - 1, blockIdx.x * 128 + 127);  // keys any row of this CTA may need
+  for (int j = 0; j <= last; ++j) {
+    float kr[HD], vr[HD];
+#pragma unroll
+    for (int c = 0; c < HD / 8; ++c) {
+      float tk[8], tv[8];
+      load_bf16x8(kp + (size_t)j * HD + c * 8, tk);
+      load_bf16x8(vp + (size_t)j * HD + c * 8, tv);
+#pragma unroll
+      for (int d = 0; d < 8; ++d) { kr[c * 8 + d] = tk[d]; vr[c * 8 + d] = tv[d]; }
+    }
+    if (j > i || i >= S) continue;
+    float sc = 0.f;
+#pragma unroll
+    for (int d = 0; d < HD; ++d) sc += qv[d] * kr[d];
+    const float nm = fmaxf(mx, sc);
+    const float corr = exp2f(mx - nm), pj = exp2f(sc - nm);   // exp2f(-inf) = 0 on the first key
+    l = l * corr + pj;
+#pragma unroll
+    for (int d = 0; d < HD; ++d) acc[d] = acc[d] * corr + pj * vr[d];
+    mx = nm;
+  }
+  if (i >= S) return;
+  const float inv = 1.0f / l;
+  __nv_bfloat16* dst = o + ((size_t)b * S + i) * ((size_t)H * HD) + (size_t)h * HD;
+#pragma unroll
+  for (int c = 0; c < HD / 8; ++c) {
+    float t[8];
+#pragma unroll
+    for (int d = 0; d < 8; ++d) t[d] = acc[c * 8 + d] * inv;
+    store_bf16x8(dst + c * 8, t);
+  }
+}
+
 int launch_attention_tcgen05(const void* q, const void* k, const void* v, void* o, int B, int S, int H, int KV, int hd,
                              float scale, float logit_bound, int32_t* err_flag, cudaStream_t st);
 
@@ -206,8 +267,11 @@ extern "C" int hb200_attention_causal_gqa(const void* q, const void* k, const vo
     attention_causal_gqa_kernel<32><<<grid, 128, 0, st>>>(qp, kp, vp, (__nv_bfloat16*)o, S, H, KV, scale_log2);
   else if (hd == 64)
     attention_causal_gqa_kernel<64><<<grid, 128, 0, st>>>(qp, kp, vp, (__nv_bfloat16*)o, S, H, KV, scale_log2);
+  else if (hd == 8)
+    attention_small_head_kernel<8><<<dim3((S + 127) / 128, H, B), 128, 0, st>>>(qp, kp, vp, (__nv_bfloat16*)o, S, H, KV,
+                                                                              scale_log2);
   else {
-    set_error("attention: head_dim %d not built (16, 32, 64)", hd);
+    set_error("attention: head_dim %d not built (8, 16, 32, 64)", hd);
     return HB200_ERR_UNSUPPORTED;
   }
   HB_LAUNCH_CHECK();

@@ -504,9 +504,10 @@ extern "C" int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, con
   if (hd == 16 && lat == 384 && kvd == 64) return launch_pre<16, 12, 4, 32, 32>(p, st);
   if (hd == 16 && lat == 320 && kvd == 80) return launch_pre<16, 10, 5, 64, 32>(p, st);
   // everything else with a head_dim the attention kernels are built for
+  if (hd == 8) return launch_pre_generic<8>(p, st);
   if (hd == 16) return launch_pre_generic<16>(p, st);
   if (hd == 32) return launch_pre_generic<32>(p, st);
   if (hd == 64) return launch_pre_generic<64>(p, st);
-  set_error("ccgqa_pre_attention: head_dim %d not built (16, 32, 64)", hd);
+  set_error("ccgqa_pre_attention: head_dim %d not built (8, 16, 32, 64)", hd);
   return HB200_ERR_UNSUPPORTED;
 }

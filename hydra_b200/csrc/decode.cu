@@ -803,8 +803,8 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
   HB_REQUIRE(m->dim % 8 == 0 && m->dim <= 256 * ROW_NCH && m->ffn_hidden % 8 == 0, HB200_ERR_UNSUPPORTED,
              "decode_step: dim %d must be a multiple of 8 and at most %d, ffn hidden a multiple of 8", m->dim,
              256 * ROW_NCH);
-  HB_REQUIRE(m->head_dim == 16 || m->head_dim == 32 || m->head_dim == 64, HB200_ERR_UNSUPPORTED,
-             "decode_step: head_dim %d (16, 32 or 64 are built)", m->head_dim);
+  HB_REQUIRE(m->head_dim == 8 || m->head_dim == 16 || m->head_dim == 32 || m->head_dim == 64, HB200_ERR_UNSUPPORTED,
+             "decode_step: head_dim %d (8, 16, 32 or 64 are built)", m->head_dim);
   HB_REQUIRE(m->n_kv_heads >= 1 && m->n_heads % m->n_kv_heads == 0 && m->n_heads / m->n_kv_heads <= DATT_GMAX,
              HB200_ERR_UNSUPPORTED, "decode_step: at most %d query heads per kv head", DATT_GMAX);
   HB_REQUIRE((size_t)8 * (m->n_heads + m->n_kv_heads) * m->head_dim * sizeof(float) <= 48 * 1024, HB200_ERR_UNSUPPORTED,
@@ -859,7 +859,8 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
                               (__nv_bfloat16*)ds->halo + (size_t)bi * B * 4 * C,                                               \
                               (__nv_bfloat16*)ds->vshift + (size_t)bi * B * (kvd / 2), vc, w.aq, w.ak, w.qm, w.km,             \
                               w.counts + (size_t)bi * R, (const int32_t*)ds->pos, B, H, KV, cap))
-    if (hd == 16) HB_CONV_PREP(16);
+    if (hd == 8) HB_CONV_PREP(8);
+    else if (hd == 16) HB_CONV_PREP(16);
     else if (hd == 32) HB_CONV_PREP(32);
     else HB_CONV_PREP(64);
 #undef HB_CONV_PREP
@@ -873,6 +874,7 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
                                 bw.key_temperature, w.qnew, kc, (const int32_t*)ds->pos, H, KV, hd, cap)); }
     { PS(HB200_K_ATTENTION, 0, lat, cap);
     switch (hd) {
+      case 8: HB_PROPAGATE(launch_decode_attention<8>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st, chain)); break;
       case 16: HB_PROPAGATE(launch_decode_attention<16>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st, chain)); break;
       case 32: HB_PROPAGATE(launch_decode_attention<32>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st, chain)); break;
       default: HB_PROPAGATE(launch_decode_attention<64>(w.qnew, kc, vc, w.o, ds->pos, B, H, KV, cap, scale, st, chain)); break;

@@ -91,6 +91,76 @@ def random_state_dict(*, vocab_size: int = 50257, dim: int, n_mor_blocks: int, r
     return sd
 
 
+def random_base_state_dict(*, vocab_size: int = 50257, dim: int, n_layers: int, n_heads: int, n_kv_heads: int,
+                           compression_factor: int = 4, mlp_ratio: float = 2.67, seed: int = 0,
+                           device="cuda") -> Dict[str, Tensor]:
+    """Seeded random-init weights of a HydraBaseModel (model.py:82-138: Linear / Embedding / Conv1d N(0, 0.02), o_proj and
+    down scaled by 1/sqrt(2*n_layers), norm gains 1, key_temperature sqrt(head_dim)); the draw order is this function's."""
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    lat = dim // compression_factor
+    hd = lat // n_heads
+    kvd = n_kv_heads * hd
+    F = ((int(dim * mlp_ratio) + 255) // 256) * 256
+    res = 1.0 / math.sqrt(2 * n_layers)
+
+    def nrm(*shape, std=0.02):
+        return torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * std
+
+    sd: Dict[str, Tensor] = {"tok_emb.weight": nrm(vocab_size, dim), "norm.weight": torch.ones(dim, device=dev)}
+    for i in range(n_layers):
+        pre = f"layers.{i}."
+        sd[pre + "attention.qkv_proj.weight"] = nrm(lat + 2 * kvd, dim)
+        sd[pre + "attention.o_proj.weight"] = nrm(dim, lat) * res
+        sd[pre + "attention.q_conv.conv1.weight"] = nrm(lat, hd, 3)
+        sd[pre + "attention.q_conv.conv2.weight"] = nrm(lat, lat, 3)
+        sd[pre + "attention.k_conv.conv1.weight"] = nrm(kvd, hd, 3)
+        sd[pre + "attention.k_conv.conv2.weight"] = nrm(kvd, kvd, 3)
+        sd[pre + "attention.key_temperature"] = torch.full((1,), float(hd ** 0.5), device=dev)
+        sd[pre + "norm1.weight"] = torch.ones(dim, device=dev)
+        sd[pre + "norm2.weight"] = torch.ones(dim, device=dev)
+        sd[pre + "mlp.gate_up.weight"] = nrm(2 * F, dim)
+        sd[pre + "mlp.down.weight"] = nrm(dim, F) * res
+    return sd
+
+
+def create_hydra_model(vocab_size: int = 50257, dim: int = 2048, n_mor_blocks: int = 8, recursions_per_block: int = 4,
+                       n_heads: int = 32, n_kv_heads: int = 4, compression_factor: int = 4, mlp_ratio: float = 2.67,
+                       max_seq_len: int = 8192, mod_capacity: float = 0.5, adaptive: bool = True, seed: int = 0,
+                       device="cuda", **ignored) -> "HydraB200Model":
+    """``hydra.model.framework.factory.create_hydra_model`` (factory.py:11-50, same arguments and defaults; the
+    training-only ones - aux_loss_weight, warm-ups, depth scaling - are accepted and ignored): a seeded random-init
+    model of that architecture on this backend."""
+    sd = random_state_dict(vocab_size=vocab_size, dim=dim, n_mor_blocks=n_mor_blocks,
+                           recursions_per_block=recursions_per_block, n_heads=n_heads, n_kv_heads=n_kv_heads,
+                           compression_factor=compression_factor, mlp_ratio=mlp_ratio, mod_capacity=mod_capacity,
+                           seed=seed, device=device)
+    return HydraB200Model(sd, n_heads=n_heads, n_kv_heads=n_kv_heads, compression_factor=compression_factor,
+                          max_seq_len=max_seq_len, mod_capacity=mod_capacity, adaptive=adaptive, device=device)
+
+
+def create_base_model(spec, seed: int = 0, device="cuda") -> "HydraB200BaseModel":
+    """``create_base_model(spec)`` (factory.py:53-66): the routing-free baseline from an object with the reference's
+    spec attributes (vocab_size, dim, n_layers, n_heads, n_kv_heads, compression_factor, mlp_ratio, max_seq_len), same
+    defaults; seeded random init."""
+    kw = dict(vocab_size=getattr(spec, "vocab_size", 50257), dim=getattr(spec, "dim", 1344),
+              n_layers=getattr(spec, "n_layers", 24), n_heads=getattr(spec, "n_heads", 21),
+              n_kv_heads=getattr(spec, "n_kv_heads", 3), compression_factor=getattr(spec, "compression_factor", 4),
+              mlp_ratio=getattr(spec, "mlp_ratio", 2.67))
+    sd = random_base_state_dict(seed=seed, device=device, **kw)
+    if not getattr(spec, "tie_weights", True):
+        g = torch.Generator(device=torch.device(device)).manual_seed(seed + 1)
+        sd["output.weight"] = torch.randn(kw["vocab_size"], kw["dim"], generator=g, device=device) * 0.02
+    return HydraB200BaseModel(sd, n_heads=kw["n_heads"], n_kv_heads=kw["n_kv_heads"],
+                              compression_factor=kw["compression_factor"],
+                              max_seq_len=getattr(spec, "max_seq_len", 8192), device=device)
+
+
+# the reference's backward-compatible names (factory.py:69-71)
+create_ccgqa_model = create_base_model
+create_ccgqa_mod_mor_model = create_hydra_model
+
+
 def normalize_state_dict(obj) -> Dict[str, Tensor]:
     """Checkpoint payload -> flat state_dict with the current key names.
 
@@ -189,6 +259,7 @@ class HydraB200Model:
         lat = D // compression_factor
         hd = lat // n_heads
         self.vocab_size, self.dim, self.n_mor_blocks, self.recursions_per_block = V, D, nb, R
+        self.effective_layers = nb * R
         self.n_heads, self.n_kv_heads, self.head_dim, self.ffn_hidden = n_heads, n_kv_heads, hd, F
         self.max_seq_len, self.mod_capacity, self.mor_min_depth, self.adaptive = max_seq_len, mod_capacity, mor_min_depth, adaptive
         # static_routing_mode (model.py:202; the reference honours it in eval too): dense compute, soft routing weights

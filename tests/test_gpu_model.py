@@ -411,7 +411,8 @@ def test_static_routing_mode():
     (1792, 28, 4, "500M / 1B presets, group of 7"), (1536, 24, 4, "750M preset, group of 6"),
     (1280, 20, 5, "trainer default, 5 KV heads"), (1344, 21, 3, "base-model default: latent 336, CUDA-core kernel"),
     (768, 6, 3, "heads of 32, 3 KV heads: CUDA-core kernel"), (512, 2, 1, "heads of 64, one KV head: CUDA-core kernel"),
-    (192, 3, 3, "H == KV with three heads: CUDA-core kernel")])
+    (192, 3, 3, "H == KV with three heads: CUDA-core kernel"),
+    (128, 4, 2, "heads of 8 (the reference's small test models, dim 128): CUDA-core attention and pre-attention")])
 def test_head_shapes_of_the_reference_presets(dim, H, KV, note):
     """Every (dim, heads, kv heads) of the reference's size presets (hydra/training/config.py:460-580) and a few shapes
     no tiled pre-attention kernel is instantiated for (they take the CUDA-core kernel): prefill against the oracle with
@@ -494,3 +495,45 @@ def test_mor_rampup_blend():
     assert m.generate(ids_c[:, :10], 2).shape == (B, 12)
     with pytest.raises(Hb200Error):
         m(ids.cuda(), forced=tp)
+
+
+def test_factories_mirror_the_reference():
+    """create_hydra_model / create_base_model and their older names (hydra/model/framework/factory.py), exercised the
+    way the reference's own tests exercise them (tests/test_ccgqa_model.py: factory attributes, forward shape,
+    inference without NaNs, RoPE cache resize)."""
+    from hydra_b200.model import (create_base_model, create_ccgqa_mod_mor_model, create_ccgqa_model, create_hydra_model)
+
+    class MockSpec:
+        vocab_size = 1000
+        dim = 128
+        n_layers = 4
+        n_heads = 4
+        n_kv_heads = 2
+        compression_factor = 2
+        mlp_ratio = 2.67
+        max_seq_len = 512
+        tie_weights = True
+
+    base = create_ccgqa_model(MockSpec())
+    assert create_ccgqa_model is create_base_model and base.dim == 128 and base.n_layers == 4
+    x = torch.randint(0, 1000, (2, 64), device="cuda")
+    out = base(x)
+    assert out.shape == (2, 64, 1000) and torch.isfinite(out.float()).all()
+    MockSpec.tie_weights = False
+    untied = create_base_model(MockSpec())
+    assert untied.packed.lm_head is not None and untied(x).shape == (2, 64, 1000)
+
+    model = create_ccgqa_mod_mor_model(vocab_size=1000, dim=128, n_mor_blocks=4, recursions_per_block=2, n_heads=4,
+                                       n_kv_heads=2, max_seq_len=512, mor_warmup=1000, dim_ref=768)
+    assert create_ccgqa_mod_mor_model is create_hydra_model
+    assert model.dim == 128 and model.n_mor_blocks == 4 and model.effective_layers == 8
+    out = model(torch.randint(0, 1000, (2, 32), device="cuda"))
+    assert out.shape == (2, 32, 1000) and not torch.isnan(out.float()).any()
+    model.resize_rope_cache(1024)
+    assert model.max_seq_len == 1024
+    assert model(torch.randint(0, 1000, (2, 128), device="cuda")).shape == (2, 128, 1000)
+    # same seed, same model
+    again = create_hydra_model(vocab_size=1000, dim=128, n_mor_blocks=4, recursions_per_block=2, n_heads=4, n_kv_heads=2,
+                               max_seq_len=512)
+    assert torch.equal(again(x[:, :32]), create_hydra_model(vocab_size=1000, dim=128, n_mor_blocks=4, recursions_per_block=2,
+                                                           n_heads=4, n_kv_heads=2, max_seq_len=512)(x[:, :32]))
