@@ -317,8 +317,8 @@ class HydraB200Model:
                     mlp_rows=torch.zeros((NB, R), dtype=torch.int32, device=d),
                     block_out=torch.zeros((NB, T, self.dim), dtype=torch.bfloat16, device=d) if block_out else None)
 
-    def forward(self, ids: Tensor, mask: Optional[Tensor] = None, *, taps: bool = False, forced: Optional[Taps] = None,
-                block_out: bool = False, logits: bool = True, hidden: bool = False):
+    def forward(self, ids: Tensor, mask: Optional[Tensor] = None, return_losses: bool = False, *, taps: bool = False,
+                forced: Optional[Taps] = None, block_out: bool = False, logits: bool = True, hidden: bool = False):
         """ids int64 [B, S] on this model's device -> logits bf16 [B, S, vocab] (a view of a buffer whose rows are
         padded to a multiple of 8 columns; the buffer is reused by the next call with the same shape).
 
@@ -328,6 +328,9 @@ class HydraB200Model:
         taps=True records routing decisions in ``self.last_taps``; ``forced`` replays the decisions of an earlier
         run (its ``depths`` and ``mod_idx``).  hidden=True returns the post-norm hidden state instead/as well.
         """
+        if return_losses:
+            raise NotImplementedError("return_losses=True is the training path (auxiliary routing losses); this is the "
+                                      "inference forward, HydraModel.forward(x, return_losses=False)")
         if not ids.is_cuda or ids.device != self.device:
             raise RuntimeError(f"ids must be on {self.device} (there is no CPU fallback)")
         if ids.dim() != 2:

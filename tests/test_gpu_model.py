@@ -527,8 +527,10 @@ def test_factories_mirror_the_reference():
                                        n_kv_heads=2, max_seq_len=512, mor_warmup=1000, dim_ref=768)
     assert create_ccgqa_mod_mor_model is create_hydra_model
     assert model.dim == 128 and model.n_mor_blocks == 4 and model.effective_layers == 8
-    out = model(torch.randint(0, 1000, (2, 32), device="cuda"))
+    out = model(torch.randint(0, 1000, (2, 32), device="cuda"), return_losses=False)
     assert out.shape == (2, 32, 1000) and not torch.isnan(out.float()).any()
+    with pytest.raises(NotImplementedError):
+        model(torch.randint(0, 1000, (2, 32), device="cuda"), return_losses=True)
     model.resize_rope_cache(1024)
     assert model.max_seq_len == 1024
     assert model(torch.randint(0, 1000, (2, 128), device="cuda")).shape == (2, 128, 1000)
