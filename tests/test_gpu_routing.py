@@ -101,3 +101,18 @@ def test_mor_depths_match_oracle(L):
             cont = min_d + torch.sigmoid(sq) * (n_rec - 1 - min_d)
             assert ((cont - cont.floor() - 0.5).abs() < 1e-5).all()
         assert int(diff.sum()) <= 2
+
+
+def test_public_routing_wrappers():
+    """hydra_b200.routing.mod_select / mor_depths: the same entry points behind a tensor-in, tensor-out interface."""
+    from hydra_b200.routing import mod_k, mod_select, mor_depths
+    g = torch.Generator().manual_seed(3)
+    scores = torch.randn(4, 333, generator=g) * 2
+    for cap in (0.75, 0.3, 1.0, 1e-6):
+        assert mod_k(333, cap) == O.mod_k(333, cap)
+        assert torch.equal(mod_select(scores.cuda(), cap).cpu(), O.mod_select(scores, cap))
+    logits = torch.randn(3, 200, generator=g) * 2
+    for R, md in ((4, 0), (4, 1), (2, 0), (1, 0)):
+        assert torch.equal(mor_depths(logits.cuda(), R, md).cpu(), O.mor_depths(logits, R, md)[0])
+    with pytest.raises(RuntimeError):
+        mod_select(scores, 0.5)
