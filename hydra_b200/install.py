@@ -20,6 +20,10 @@ _KERNEL_MODULES = ("hydra.kernels", "hydra.kernels.fused_ops", "hydra.layers.com
 _FACTORY_MODULES = ("hydra.attention", "hydra.attention.factory", "hydra.model.framework.blocks")
 _REGISTRY = ("resolve_hybrid_attention_backend", "available_hybrid_attention_backends",
              "is_hybrid_attention_backend_available")
+# the attention class itself is bound by name where it is constructed directly: HydraBlock / the MoD block wrapper
+# (hydra/model/framework/blocks.py:20,52,383) and the backend's standard constructor (backends/ccgqa/backend.py:5-17)
+_CLASS_MODULES = ("hydra.model.framework.blocks", "hydra.attention.backends.ccgqa.backend")
+_BUILDER_MODULES = ("hydra.attention.backends.ccgqa", "hydra.attention.backends.ccgqa.backend")
 
 _saved: List[Tuple[Any, str, Any]] = []
 
@@ -51,6 +55,15 @@ def install(kernels: bool = True, attention: bool = True) -> Dict[str, List[str]
         for fn in _REGISTRY:
             _set(mod, fn, getattr(_attention, fn))
             done.setdefault("hydra.attention", []).append(fn)
+        for mname, name, value in [(m_, "CCGQAAttention", _attention.CCGQAAttention) for m_ in _CLASS_MODULES] + \
+                                  [(m_, "build_ccqa_attention", _attention.build_ccqa_attention) for m_ in _BUILDER_MODULES]:
+            try:
+                mod = importlib.import_module(mname)
+            except ImportError:
+                continue
+            if hasattr(mod, name):
+                _set(mod, name, value)
+                done.setdefault(mname, []).append(name)
     return done
 
 

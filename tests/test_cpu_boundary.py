@@ -187,9 +187,11 @@ def test_install_rebinds_reference_names_and_uninstall_restores(monkeypatch):
     mk("hydra.attention", build_hybrid_attention_module=orig, resolve_hybrid_attention_backend=orig,
        available_hybrid_attention_backends=orig, is_hybrid_attention_backend_available=orig)
     mk("hydra.attention.factory", build_hybrid_attention_module=orig)
-    mk("hydra.attention.backends"); mk("hydra.attention.backends.ccgqa")
+    mk("hydra.attention.backends"); mk("hydra.attention.backends.ccgqa", build_ccqa_attention=orig)
+    mk("hydra.attention.backends.ccgqa.backend", build_ccqa_attention=orig, CCGQAAttention=orig)
     mk("hydra.attention.backends.ccgqa.attention", fused_rope=orig, FUSED_KERNELS_AVAILABLE=False)
-    mk("hydra.model"); mk("hydra.model.framework"); mk("hydra.model.framework.blocks", build_hybrid_attention_module=orig)
+    mk("hydra.model"); mk("hydra.model.framework")
+    mk("hydra.model.framework.blocks", build_hybrid_attention_module=orig, CCGQAAttention=orig)
     from hydra_b200 import install as I, kernels as K, attention as A
     done = I.install()
     assert mods["hydra.layers.common"].fused_swiglu is K.fused_swiglu
@@ -197,7 +199,11 @@ def test_install_rebinds_reference_names_and_uninstall_restores(monkeypatch):
     assert mods["hydra.attention.backends.ccgqa.attention"].fused_rope is K.fused_rope
     assert mods["hydra.model.framework.blocks"].build_hybrid_attention_module is A.build_hybrid_attention_module
     assert "hydra.kernels" in done and "hydra.attention.factory" in done
+    assert mods["hydra.model.framework.blocks"].CCGQAAttention is A.CCGQAAttention       # HydraBlock builds it by name
+    assert mods["hydra.attention.backends.ccgqa"].build_ccqa_attention is A.build_ccqa_attention
+    assert mods["hydra.attention.backends.ccgqa.backend"].CCGQAAttention is A.CCGQAAttention
     I.uninstall()
+    assert mods["hydra.model.framework.blocks"].CCGQAAttention is orig
     assert mods["hydra.layers.common"].fused_swiglu is orig
     assert mods["hydra.model.framework.blocks"].build_hybrid_attention_module is orig
     assert mods["hydra.layers.common"].FUSED_KERNELS_AVAILABLE is False
