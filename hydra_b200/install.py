@@ -81,6 +81,8 @@ def uninstall() -> None:
 
 
 def accelerate(model, **overrides):
-    """Reference ``HydraModel`` instance -> ``HydraB200Model`` sharing its weights' values."""
-    from .model import HydraB200Model
-    return HydraB200Model.from_reference(model, **overrides)
+    """Reference ``HydraModel`` / ``HydraBaseModel`` instance -> ``HydraB200Model`` / ``HydraB200BaseModel`` holding a
+    copy of its weights (the routed model is recognised by its MoR executor)."""
+    from .model import HydraB200BaseModel, HydraB200Model
+    routed = hasattr(model.layers[0], "mor_executor")
+    return (HydraB200Model if routed else HydraB200BaseModel).from_reference(model, **overrides)
