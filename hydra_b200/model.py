@@ -616,7 +616,7 @@ class HydraB200BaseModel(HydraB200Model):
         """Build from a reference ``HydraBaseModel`` instance."""
         attn = model.layers[0].attention
         kw = dict(n_heads=attn.n_heads, n_kv_heads=attn.n_kv_heads, compression_factor=attn.compression_factor,
-                  max_seq_len=attn.cos_cached.shape[0])
+                  max_seq_len=int(attn.cos_cached.shape[-2]))     # [1, 1, S, hd/2] in the reference, [S, hd/2] here
         kw.update(overrides)
         return cls(model.state_dict(), **kw)
 
