@@ -293,15 +293,25 @@ class HydraB200Model:
         """The reference enables MoD hard routing in eval only after its warm-up step
         (hydra/model/framework/blocks.py:136-140); here it is always enabled, so this is a no-op."""
 
+    @staticmethod
+    def reference_kwargs(model) -> dict:
+        """Constructor arguments read off a reference ``HydraModel`` instance: shape attributes, routing settings, and
+        the curriculum state its blocks are in (static routing, MoR ramp-up scale)."""
+        # MoD hard routing is on only once the wrapper's warm-up has passed (blocks.py:140,162-186: `_mod_enabled`, set
+        # by set_global_step); before that every token goes through the MLP, which is capacity 1.0 here
+        wrappers = [l.mod_mlp_wrapper for l in model.layers if getattr(l, "mod_mlp_wrapper", None) is not None]
+        mod_on = bool(wrappers) and all(getattr(w_, "_mod_enabled", False) for w_ in wrappers)
+        return dict(n_heads=model.n_heads, n_kv_heads=model.n_kv_heads, compression_factor=model.compression_factor,
+                    max_seq_len=model.max_seq_len, mod_capacity=model.mod_capacity if mod_on else 1.0,
+                    mor_min_depth=getattr(model, "mor_min_depth", 0), adaptive=model.adaptive,
+                    static_routing_mode=bool(getattr(model, "static_routing_mode", False)),
+                    mor_rampup_scale=float(model.layers[0].get_mor_rampup_scale())
+                    if hasattr(model.layers[0], "get_mor_rampup_scale") else 1.0)
+
     @classmethod
     def from_reference(cls, model, **overrides) -> "HydraB200Model":
         """Build from a reference ``HydraModel`` instance (reads its shape attributes and state_dict)."""
-        kw = dict(n_heads=model.n_heads, n_kv_heads=model.n_kv_heads, compression_factor=model.compression_factor,
-                  max_seq_len=model.max_seq_len, mod_capacity=model.mod_capacity,
-                  mor_min_depth=getattr(model, "mor_min_depth", 0), adaptive=model.adaptive,
-                  static_routing_mode=bool(getattr(model, "static_routing_mode", False)),
-                  mor_rampup_scale=float(model.layers[0].get_mor_rampup_scale())
-                  if hasattr(model.layers[0], "get_mor_rampup_scale") else 1.0)
+        kw = cls.reference_kwargs(model)
         kw.update(overrides)
         return cls(model.state_dict(), **kw)
 
@@ -611,12 +621,17 @@ class HydraB200BaseModel(HydraB200Model):
         self._logits = None
         self.last_taps = None
 
+    @staticmethod
+    def reference_kwargs(model) -> dict:
+        """Constructor arguments read off a reference ``HydraBaseModel`` instance (it keeps them on its attention modules)."""
+        attn = model.layers[0].attention
+        return dict(n_heads=attn.n_heads, n_kv_heads=attn.n_kv_heads, compression_factor=attn.compression_factor,
+                    max_seq_len=int(attn.cos_cached.shape[-2]))   # [1, 1, S, hd/2] in the reference, [S, hd/2] here
+
     @classmethod
     def from_reference(cls, model, **overrides) -> "HydraB200BaseModel":
         """Build from a reference ``HydraBaseModel`` instance."""
-        attn = model.layers[0].attention
-        kw = dict(n_heads=attn.n_heads, n_kv_heads=attn.n_kv_heads, compression_factor=attn.compression_factor,
-                  max_seq_len=int(attn.cos_cached.shape[-2]))     # [1, 1, S, hd/2] in the reference, [S, hd/2] here
+        kw = cls.reference_kwargs(model)
         kw.update(overrides)
         return cls(model.state_dict(), **kw)
 

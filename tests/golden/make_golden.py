@@ -136,7 +136,7 @@ def gen_attention(name: str, dim: int, H: int, KV: int, B: int, S: int, seed: in
 # ----------------------------------------------------------------------------
 def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: int, mlp_ratio: float,
               B: int, S: int, cap: float, seed: int, tie: bool = True, static: bool = False,
-              rampup: float = 1.0) -> None:
+              rampup: float = 1.0, fresh: bool = False) -> None:
     from hydra.model.framework import HydraModel
 
     torch.manual_seed(seed)
@@ -158,7 +158,8 @@ def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: i
     m.eval()
     if rampup < 1.0:             # MoR curriculum in the middle of its ramp: scale = steps since enable / ramp steps
         m.set_mor_curriculum(enable_step=10 ** 6 - int(round(rampup * 1000)) + 1, rampup_steps=1000)
-    m.set_global_step(10 ** 6)   # MoD hard routing is off in eval until the step passes its warm-up
+    if not fresh:                # fresh: the model as constructed - MoD still in its warm-up, every token through the MLP
+        m.set_global_step(10 ** 6)   # MoD hard routing is off in eval until the step passes its warm-up
     if rampup < 1.0:
         assert abs(m.layers[0].get_mor_rampup_scale() - rampup) < 1e-9
     ids = torch.randint(0, vocab, (B, S), generator=torch.Generator().manual_seed(seed + 2))
@@ -189,6 +190,10 @@ def gen_model(name: str, *, vocab: int, dim: int, NB: int, R: int, H: int, KV: i
         ids=ids.numpy(), logits=f32(logits), static=np.array([int(static)], dtype=np.int64),
         rampup=np.array([rampup], dtype=np.float64),
     )
+    # what HydraB200Model.from_reference would read off this instance (checked on the GPU against the logits above)
+    import json
+    from hydra_b200.model import HydraB200Model
+    arrs["reference_kwargs"] = np.frombuffer(json.dumps(HydraB200Model.reference_kwargs(m)).encode(), dtype=np.uint8)
     for i, d in enumerate(depths):
         arrs[f"depths:{i}"] = d.numpy().astype(np.int32)
         arrs[f"router_logits:{i}"] = f32(rlogits[i])
@@ -342,6 +347,10 @@ if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "sampler":  # only the sampler's filtered distributions
         gen_sampler()
         sys.exit(0)
+    if len(sys.argv) > 1 and sys.argv[1] == "fresh":    # only the freshly constructed model (MoD warm-up not passed)
+        gen_model("model_fresh.npz", vocab=200, dim=256, NB=3, R=2, H=4, KV=2, mlp_ratio=1.0,
+                  B=2, S=48, cap=0.5, seed=29, fresh=True)
+        sys.exit(0)
     if len(sys.argv) > 1 and sys.argv[1] == "rampup":   # only the model in the middle of its MoR ramp-up
         gen_model("model_rampup.npz", vocab=200, dim=256, NB=3, R=3, H=4, KV=2, mlp_ratio=1.0,
                   B=2, S=64, cap=0.75, seed=27, rampup=0.4)
@@ -379,3 +388,6 @@ if __name__ == "__main__":
     # MoR curriculum mid-ramp: every block returns 0.4 * adaptive + 0.6 * fixed-depth
     gen_model("model_rampup.npz", vocab=200, dim=256, NB=3, R=3, H=4, KV=2, mlp_ratio=1.0,
               B=2, S=64, cap=0.75, seed=27, rampup=0.4)
+    # a model as constructed (no set_global_step): MoD is still in its warm-up, so every token goes through the MLP
+    gen_model("model_fresh.npz", vocab=200, dim=256, NB=3, R=2, H=4, KV=2, mlp_ratio=1.0,
+              B=2, S=48, cap=0.5, seed=29, fresh=True)

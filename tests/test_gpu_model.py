@@ -539,3 +539,19 @@ def test_factories_mirror_the_reference():
                                max_seq_len=512)
     assert torch.equal(again(x[:, :32]), create_hydra_model(vocab_size=1000, dim=128, n_mor_blocks=4, recursions_per_block=2,
                                                            n_heads=4, n_kv_heads=2, max_seq_len=512)(x[:, :32]))
+
+
+@pytest.mark.parametrize("name", ["model_fresh.npz", "model_rampup.npz", "model_static.npz", "model_untied.npz"])
+def test_arguments_read_off_a_reference_instance_reproduce_it(name):
+    """from_reference = state_dict + HydraB200Model.reference_kwargs(model).  The fixtures store what reference_kwargs
+    read off the live reference instance (MoD warm-up state, static routing, MoR ramp-up scale, shapes); a model built
+    from exactly those arguments must reproduce that instance's logits."""
+    import json
+    fx, cfg, w = G.model_fixture(name)
+    kw = json.loads(bytes(fx["reference_kwargs"]).decode())
+    from hydra_b200.model import HydraB200Model
+    m = HydraB200Model(w, **kw)
+    lg = m(torch.from_numpy(fx["ids"]).cuda()).float().cpu()
+    err, own = rel_l2(lg, torch.from_numpy(fx["logits"])), float(fx["ref_bf16_rel_l2"][0])
+    print(f"{name}: {kw} -> rel_l2 {err:.3e} (reference's own bf16 path {own:.3e})")
+    assert err <= 2.0 * own + 1e-3

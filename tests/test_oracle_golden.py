@@ -225,3 +225,21 @@ def test_mor_rampup_blend_matches_reference():
     close(O.model_forward(ids, w, dataclasses.replace(cfg, mor_rampup_scale=0.0)), fixed.numpy(), 1e-6)
     close(fixed, fx["logits_fixed"], 5e-6)
     assert float((full - torch.from_numpy(fx["logits"])).abs().max()) > 1e-3
+
+
+def reference_kwargs(fx):
+    import json
+    return json.loads(bytes(fx["reference_kwargs"]).decode())
+
+
+def test_freshly_constructed_model_runs_every_token_through_the_mlp():
+    """A HydraModel right after construction (no set_global_step): MoD is still in its warm-up (blocks.py:140,162-186),
+    i.e. capacity 1.0 whatever capacity it was built with - which is what from_reference reads off such an instance."""
+    fx, cfg, w = G.model_fixture("model_fresh.npz")
+    kw = reference_kwargs(fx)
+    assert cfg.mod_capacity == 0.5 and kw["mod_capacity"] == 1.0 and kw["mor_rampup_scale"] == 1.0
+    ids = torch.from_numpy(fx["ids"])
+    cfg.mod_capacity = kw["mod_capacity"]
+    close(O.model_forward(ids, w, cfg), fx["logits"], 5e-6)
+    cfg.mod_capacity = 0.5
+    assert float((O.model_forward(ids, w, cfg) - torch.from_numpy(fx["logits"])).abs().max()) > 1e-3
