@@ -280,6 +280,9 @@ def gen_base_model(name: str, *, vocab: int, dim: int, n_layers: int, H: int, KV
     err = lb - logits
     arrs["ref_bf16_maxabs"] = np.array([float(err.abs().max())])
     arrs["ref_bf16_rel_l2"] = np.array([float(err.norm() / logits.norm())])
+    import json
+    from hydra_b200.model import HydraB200BaseModel
+    arrs["reference_kwargs"] = np.frombuffer(json.dumps(HydraB200BaseModel.reference_kwargs(m)).encode(), dtype=np.uint8)
     save(name, **arrs)
 
 

@@ -555,3 +555,16 @@ def test_arguments_read_off_a_reference_instance_reproduce_it(name):
     err, own = rel_l2(lg, torch.from_numpy(fx["logits"])), float(fx["ref_bf16_rel_l2"][0])
     print(f"{name}: {kw} -> rel_l2 {err:.3e} (reference's own bf16 path {own:.3e})")
     assert err <= 2.0 * own + 1e-3
+
+
+def test_base_model_arguments_read_off_a_reference_instance():
+    """HydraB200BaseModel.reference_kwargs on the live HydraBaseModel (stored in the fixture): head counts, compression
+    and the RoPE table length - the reference keeps its table as [1, 1, S, hd/2]."""
+    import json
+    from hydra_b200.model import HydraB200BaseModel
+    fx, cfg, w = G.model_fixture("base_model_hd16.npz")
+    kw = json.loads(bytes(fx["reference_kwargs"]).decode())
+    assert kw == dict(n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, compression_factor=4, max_seq_len=cfg.max_seq_len)
+    m = HydraB200BaseModel(w, **kw)
+    lg = m(torch.from_numpy(fx["ids"]).cuda()).float().cpu()
+    assert rel_l2(lg, torch.from_numpy(fx["logits"])) <= 2.0 * float(fx["ref_bf16_rel_l2"][0]) + 1e-3
