@@ -34,6 +34,14 @@ __global__ void fill_i32_kernel(int32_t* p, int64_t n, int32_t val) {
   if (i < n) p[i] = val;
 }
 
+// Row list of every token in order (static routing: the dense MLP result is read back by token index, so the list has
+// to be the identity; the compacting kernel orders its 4096-token chunks by atomic reservation)
+__global__ void all_rows_kernel(int32_t* __restrict__ rows, int64_t n, int32_t* __restrict__ count) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) rows[i] = (int32_t)i;
+  if (i == 0) *count = (int32_t)n;
+}
+
 // gate_up [2F,K] -> rows interleaved in groups of 8 (8 gate rows, 8 up rows, ...)
 __global__ void interleave_gate_up_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ o, int F,
                                           int K) {
@@ -295,6 +303,9 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
       int32_t* slot = (taps && taps->mod_idx) ? taps->mod_idx + ((size_t)bi * R + r) * B * k : w.sel_idx;
       HB_PROPAGATE(launch_mod_select(scores, B, S, k, force ? nullptr : slot, depth, r, w.rows, count,
                                      force ? slot : nullptr, st));
+    } else if (stat) {
+      all_rows_kernel<<<(unsigned)ceil_div(T, 256), 256, 0, st>>>(w.rows, T, count);
+      HB_LAUNCH_CHECK();
     } else {
       HB_PROPAGATE(launch_compact_active(depth, T, r, w.rows, count, st));
     }

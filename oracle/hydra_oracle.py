@@ -353,7 +353,8 @@ def mor_block_forward(x: Tensor, p: Dict[str, Tensor], i: int, cfg: HydraConfig,
         import dataclasses
         s_ = float(cfg.mor_rampup_scale)
         fixed_cfg = dataclasses.replace(cfg, adaptive=False, mor_rampup_scale=1.0)
-        fixed = mor_block_forward(x, p, i, fixed_cfg, None, forced if s_ <= 0.0 else None)
+        # before the ramp starts the fixed path is the whole block: its MoD routing is what taps record / forced replays
+        fixed = mor_block_forward(x, p, i, fixed_cfg, taps if s_ <= 0.0 else None, forced if s_ <= 0.0 else None)
         if s_ <= 0.0:
             return fixed
         adaptive = mor_block_forward(x, p, i, dataclasses.replace(cfg, mor_rampup_scale=1.0), taps, forced)
@@ -610,6 +611,11 @@ def cached_decode_step(tokens: Tensor, p: Dict[str, Tensor], cfg: HydraConfig, c
     t = cache.pos
     lat, kvd, H, KV, hd = cfg.latent_dim, cfg.kv_dim, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
     R, D = cfg.recursions_per_block, cfg.dim
+    if cfg.adaptive and cfg.mor_rampup_scale < 1.0:
+        if cfg.mor_rampup_scale > 0.0:
+            raise ValueError("cached decode inside the MoR ramp-up blend is not defined (two block outputs per step)")
+        import dataclasses
+        cfg = dataclasses.replace(cfg, adaptive=False, mor_rampup_scale=1.0)   # before the ramp: the fixed-depth path
     x = embed(tokens.view(B, 1), p, cfg)[:, 0]                               # [B, D]
     for i in range(cfg.n_mor_blocks):
         pre = f"layers.{i}."

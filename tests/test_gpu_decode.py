@@ -71,6 +71,20 @@ def test_short_prompt_fixed_depth_and_single_sequence():
         check_against_oracle(build(w, cfg), w, cfg, prompt, 7, f"P={P} adaptive={adaptive} B={rows}")
 
 
+def test_before_the_mor_ramp_decode_runs_the_fixed_depth_path():
+    """MoR curriculum scale 0 (what a reference model reports before MoR is enabled): prefill and cached decode are the
+    fixed-depth path, bit for bit the model built without the depth router, and match the oracle in that state."""
+    import dataclasses
+    fx, cfg, w = G.model_fixture("model_hd16.npz")
+    prompt = torch.from_numpy(fx["ids"])[:, :21].clamp(0, cfg.vocab_size - 1)
+    before = dataclasses.replace(cfg, mor_rampup_scale=0.0)
+    m = build(w, cfg, mor_rampup_scale=0.0)
+    seq, lg = check_against_oracle(m, w, before, prompt, 8, "ramp-up scale 0")
+    cfg.adaptive = False
+    seq_f, lg_f = build(w, cfg).generate_cached(prompt.cuda(), 8, return_logits=True)
+    assert torch.equal(seq, seq_f.cpu()) and torch.equal(lg, lg_f.float().cpu())
+
+
 def test_graph_replay_equals_direct_launches():
     fx, cfg, w = G.model_fixture("model_hd16.npz")
     prompt = torch.from_numpy(fx["ids"])[:, :25].clamp(0, cfg.vocab_size - 1).cuda()

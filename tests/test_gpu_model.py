@@ -406,6 +406,26 @@ def test_static_routing_mode():
         m(ids.cuda(), forced=tp)
 
 
+@pytest.mark.parametrize("ramp", [1.0, 0.7])
+def test_static_routing_with_more_than_4096_tokens(ramp):
+    """Static routing reads the dense MLP result back by token index, so its row list must be the identity at any
+    token count (the compacting kernel used for hard routing orders its 4096-token chunks by reservation).  5 x 1100
+    tokens, also inside the MoR ramp-up blend; every block's output against the oracle."""
+    cfg = O.HydraConfig(vocab_size=97, dim=256, n_mor_blocks=3, recursions_per_block=3, n_heads=4, n_kv_heads=2,
+                        max_seq_len=1100, mod_capacity=0.3, hidden_dim=384, static_routing=True, mor_rampup_scale=ramp)
+    w = O.init_params(cfg, seed=75, perturb=True)
+    ids = torch.randint(0, cfg.vocab_size, (5, 1100), generator=torch.Generator().manual_seed(75))
+    m = build(w, cfg, static_routing_mode=True, mor_rampup_scale=ramp)
+    lg = m(ids.cuda(), taps=True, block_out=True).float().cpu()
+    m.check_device_errors()
+    ot = O.RoutingTaps()
+    ref = O.model_forward(ids, w, cfg, taps=ot)
+    bo = m.last_taps.block_out.float().cpu().view(cfg.n_mor_blocks, 5, 1100, -1)
+    for i in range(cfg.n_mor_blocks):
+        assert rel_l2(bo[i], ot.block_out[i]) <= 1e-2, f"block {i}"
+    assert rel_l2(lg, ref) <= 1e-2
+
+
 @pytest.mark.parametrize("dim,H,KV,note", [
     (384, 6, 2, "6q/2kv x16 (tiled kernel)"), (1152, 18, 3, "300M preset, group of 6"),
     (1792, 28, 4, "500M / 1B presets, group of 7"), (1536, 24, 4, "750M preset, group of 6"),

@@ -79,3 +79,23 @@ def test_cached_decode_in_static_routing_mode_equals_the_reforward():
             assert float((full - logits_c[:, step]).abs().max()) < 2e-4
             seq_r = torch.cat([seq_r, full.argmax(-1, keepdim=True)], dim=1)
         assert torch.equal(seq_c, seq_r)
+
+
+def test_cached_decode_before_the_mor_ramp_is_the_fixed_depth_path():
+    """MoR curriculum scale 0 (HydraMoRBlock.forward, blocks.py:645-649): the block is the fixed-depth path, in the
+    cached prefill and step too - same logits as a model built without the depth router; inside the ramp the cached step
+    is undefined and refuses."""
+    import dataclasses
+    import pytest
+    fx, cfg, w = G.model_fixture("model_hd16.npz")
+    before = dataclasses.replace(cfg, mor_rampup_scale=0.0)
+    fixed = dataclasses.replace(cfg, adaptive=False)
+    prompt = torch.from_numpy(fx["ids"])[:, :9].clamp(0, cfg.vocab_size - 1)
+    seq_a, lg_a = O.cached_generate(prompt, w, before, 5, return_logits=True)
+    seq_b, lg_b = O.cached_generate(prompt, w, fixed, 5, return_logits=True)
+    assert torch.equal(seq_a, seq_b) and torch.equal(lg_a, lg_b)
+    _, lg_c = O.cached_generate(prompt, w, cfg, 5, return_logits=True)
+    assert float((lg_c - lg_a).abs().max()) > 1e-3                 # the depth router does change the result
+    _, cache = O.cached_prefill(prompt, w, dataclasses.replace(cfg, mor_rampup_scale=0.5))
+    with pytest.raises(ValueError):
+        O.cached_decode_step(prompt[:, -1], w, dataclasses.replace(cfg, mor_rampup_scale=0.5), cache)
