@@ -28,7 +28,8 @@ constexpr int SMP_WORDS = SMP_KEYS / 2;                       // two 16-bit coun
 constexpr int SMP_BM_WORDS = SMP_KEYS / 32;                   // one presence bit per value
 constexpr size_t SMP_SMEM = (size_t)(SMP_WORDS + SMP_BM_WORDS + 64 + 2 + SMP_THREADS) * 4;
 
-// Values are ordered through a 16-bit key whose unsigned order is the order of the bf16 values (-0 directly below +0).
+// Values are ordered through a 16-bit key whose unsigned order is the order of the bf16 values; -0 is read as +0
+// (canon_zero), so the two compare equal as they do in floating point and tie by token id.
 // Keys above 0xff80 and below 0x007f are NaNs.
 __device__ __forceinline__ uint32_t raw_to_key(uint32_t r) { return (r & 0x8000u) ? (~r & 0xffffu) : (r | 0x8000u); }
 __device__ __forceinline__ uint32_t key_to_raw(uint32_t k) { return (k & 0x8000u) ? (k & 0x7fffu) : (~k & 0xffffu); }
@@ -50,13 +51,18 @@ __device__ __forceinline__ uint32_t count_of(const uint32_t* cnt, uint32_t key) 
   return (cnt[count_word(raw)] >> ((raw & 1u) << 4)) & 0xffffu;
 }
 
+// -0 (0x8000) -> +0 in both halves of a word
+__device__ __forceinline__ uint32_t canon_zero(uint32_t w) { return w & ~(__vcmpeq2(w, 0x80008000u) & 0x80008000u); }
+__device__ __forceinline__ uint4 canon_zero(uint4 q) {
+  return make_uint4(canon_zero(q.x), canon_zero(q.y), canon_zero(q.z), canon_zero(q.w));
+}
 // the 8 elements [i, i + 8) of a row as four words of two bf16 each (i a multiple of 8); elements past the end read 0
 __device__ __forceinline__ uint4 load_raw8(const unsigned short* bits, int i, int cols, bool vec) {
-  if (vec && i + 8 <= cols) return __ldcg(reinterpret_cast<const uint4*>(bits + i));
+  if (vec && i + 8 <= cols) return canon_zero(__ldcg(reinterpret_cast<const uint4*>(bits + i)));
   uint32_t h[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) h[j] = (i + j < cols) ? (uint32_t)__ldcg(bits + i + j) : 0u;
-  return make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+  return canon_zero(make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16)));
 }
 // how many of the elements [i, i + 8) hold exactly the bits `raw` (pat2 = raw in both halves of a word)
 __device__ __forceinline__ uint32_t count_equal8(const uint4& q, int i, int cols, uint32_t raw, uint32_t pat2) {
@@ -158,7 +164,8 @@ sample_rows_kernel(const __nv_bfloat16* __restrict__ x, int cols, int64_t ld, fl
     uint4 q[4];
     if (vec && i0 + 3 * SMP_THREADS * 8 + 8 <= cols) {       // all four inside the row: nothing between the loads
 #pragma unroll
-      for (int b = 0; b < 4; ++b) q[b] = __ldcg(reinterpret_cast<const uint4*>(bits + i0 + b * SMP_THREADS * 8));
+      for (int b = 0; b < 4; ++b)
+        q[b] = canon_zero(__ldcg(reinterpret_cast<const uint4*>(bits + i0 + b * SMP_THREADS * 8)));
     } else {
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
@@ -364,7 +371,7 @@ sample_rows_kernel(const __nv_bfloat16* __restrict__ x, int cols, int64_t ld, fl
     if (vec && w0 + seg <= w1) {                             // a full segment inside the row: nothing between the loads
 #pragma unroll
       for (int b = 0; b < 8; ++b)
-        q[b] = (b * 256 < seg) ? __ldcg(reinterpret_cast<const uint4*>(bits + w0 + b * 256 + lane * 8))
+        q[b] = (b * 256 < seg) ? canon_zero(__ldcg(reinterpret_cast<const uint4*>(bits + w0 + b * 256 + lane * 8)))
                                : make_uint4(0u, 0u, 0u, 0u);
     } else {
 #pragma unroll

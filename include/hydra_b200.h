@@ -188,8 +188,9 @@ int hb200_cross_entropy_rows(const void* logits, const int64_t* targets, int64_t
  * probabilities being the softmax of what top-k left; then one draw from the renormalised rest.  The reference draws
  * with torch.multinomial; here out[r] is the inverse CDF, in descending-logit order with equal logits by ascending
  * index, at uniforms[r] in [0,1) (device fp32 [rows]) - a function of (row, uniform), reproducible on any stream.
- * temperature <= 0 or top_k == 1 gives the argmax (uniforms may then be NULL).  cols <= 65535.  Arithmetic: fp32
- * exponentials of the bf16 logits, masses accumulated exactly in 64-bit fixed point. */
+ * temperature <= 0 or top_k == 1 gives the argmax (uniforms may then be NULL).  cols <= 65535.  NaN logits take no
+ * part; -0 and +0 are one value.  Arithmetic: fp32 exponentials of the bf16 logits, masses accumulated exactly in
+ * 64-bit fixed point. */
 int hb200_sample_rows(const void* logits, int64_t rows, int cols, int64_t ld, float temperature, int top_k,
                       float top_p, const float* uniforms, int64_t* out, void* stream);
 

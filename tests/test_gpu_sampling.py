@@ -101,6 +101,14 @@ def test_greedy_limits_ties_and_unaligned_rows():
     uu = (torch.arange(64, dtype=torch.float32) + 0.5) / 64
     got = sample_rows(flat.cuda(), 1.0, 0, 1.0, uniforms=uu.cuda()).cpu()
     assert torch.equal(got, (uu.double() * 1000).long())
+    # signed zeros are one value (they compare equal): ties among them go by token id, and -0 ties with a +0 k-th value
+    z = (torch.randn(64, 257, generator=g) * 2).round() / 2
+    z[:, ::5] = -0.0
+    z[:, 1::7] = 0.0
+    uz = torch.rand(64, generator=g)
+    for (t, k, p) in ((1.0, 0, 1.0), (5.0, 100, 0.999), (0.8, 20, 0.9)):
+        got = sample_rows(z.to(torch.bfloat16).cuda(), t, k, p, uniforms=uz.cuda()).cpu()
+        assert torch.equal(got, O.sample_next_token(z, t, k, p, uz)), f"signed zeros, T={t} k={k} p={p}"
     # a row view that starts at an odd element (no 16-byte alignment) and one row only
     wide = (torch.randn(5, 777, generator=g) * 2).to(torch.bfloat16).cuda()
     view = wide[:, 3:]
