@@ -588,3 +588,36 @@ def test_base_model_arguments_read_off_a_reference_instance():
     m = HydraB200BaseModel(w, **kw)
     lg = m(torch.from_numpy(fx["ids"]).cuda()).float().cpu()
     assert rel_l2(lg, torch.from_numpy(fx["logits"])) <= 2.0 * float(fx["ref_bf16_rel_l2"][0]) + 1e-3
+
+
+def test_side_stream_gives_the_same_results():
+    """Everything is enqueued on the caller's current stream: forward, graph-replayed cached decode, sampled generation
+    and the evaluation loss under ``torch.cuda.stream(side)`` - with the side stream kept busy so that a launch landing
+    on another stream would be ordered wrongly - are bit for bit the default-stream results."""
+    cfg = O.HydraConfig(vocab_size=1000, dim=512, n_mor_blocks=3, recursions_per_block=2, n_heads=8, n_kv_heads=2,
+                        max_seq_len=256, mod_capacity=0.75)
+    w = O.init_params(cfg, seed=0, perturb=True)
+    ids = torch.randint(0, 1000, (3, 200), generator=torch.Generator().manual_seed(0)).cuda()
+    m = build(w, cfg)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+
+    def everything():
+        lg = m(ids).clone()
+        seq, dl = m.generate_cached(ids[:, :40], 6, use_graph=True, return_logits=True)
+        gen.manual_seed(5)
+        smp = m.generate(ids[:, :40], 5, mode="cached", temperature=0.8, top_k=50, top_p=0.9, generator=gen)
+        return lg, seq.clone(), dl.clone(), smp.clone(), m.eval_loss(ids).clone()
+
+    want = everything()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    big = torch.randn(4096, 4096, device="cuda")
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            for _ in range(10):
+                big @ big
+            got = everything()
+            side.synchronize()
+            for a, b in zip(got, want):
+                assert torch.equal(a, b)
+    m.check_device_errors()
