@@ -1,7 +1,7 @@
 """Seeded random model shapes against the oracle: head_dim 8 / 16 / 32 / 64, 1-5 KV heads, 1-8 query heads per KV head,
 compression factor 2 / 4 / 8, 2-4 blocks of 1-4 recursions, sequence lengths 1 ... 1100 (ragged tiles, sequences
 shorter than the conv halo), batch 1-9, MoD capacity 0.3-1.0, fixed depth, min_depth 1, static routing, untied output
-projection.  Each case: prefill logits against the oracle with the GPU's routing replayed (rel. L2 <= 1.2e-2) and, where
+projection, MoR curriculum scale 0 / inside the ramp / 1.  Each case: prefill logits against the oracle with the GPU's routing replayed (rel. L2 <= 1.2e-2) and, where
 the shape is within the decode step's limits, cached decode against the oracle's cached decode fed
 with the GPU's tokens (rel. L2 <= 4e-2: routing is not replayed there, so one depth or MoD decision that flips on bf16
 noise moves a whole row; observed worst 2.3e-2, typical 3e-3).
@@ -31,7 +31,7 @@ def draw_case(rng: random.Random):
                 S=rng.choice([1, 2, 3, 5, 31, 64, 100, 129, 200, 257, 600, 1100]), B=rng.choice([1, 2, 3, 5, 9]),
                 cap=rng.choice([0.3, 0.5, 0.75, 1.0]), vocab=rng.choice([97, 256, 1000]), F=rng.choice([128, 256, 384]),
                 adaptive=rng.random() < 0.8, mind=rng.choice([0, 0, 1]) if R > 1 else 0,
-                static=rng.random() < 0.15, untied=rng.random() < 0.2)
+                static=rng.random() < 0.15, untied=rng.random() < 0.2, ramp=rng.choice([1.0, 1.0, 1.0, 0.3, 0.7, 0.0]))
 
 
 @pytest.mark.parametrize("seed", [1, 7, 11])
@@ -44,7 +44,7 @@ def test_random_shapes_against_the_oracle(seed):
         cfg = O.HydraConfig(vocab_size=c["vocab"], dim=c["dim"], n_mor_blocks=c["NB"], recursions_per_block=c["R"],
                             n_heads=c["H"], n_kv_heads=c["KV"], compression_factor=c["cf"], max_seq_len=c["S"] + 8,
                             mod_capacity=c["cap"], hidden_dim=c["F"], mor_min_depth=c["mind"], adaptive=c["adaptive"],
-                            static_routing=c["static"])
+                            static_routing=c["static"], mor_rampup_scale=c["ramp"])
         w = O.init_params(cfg, seed=1000 * seed + case, perturb=True)
         if c["untied"]:
             g = torch.Generator().manual_seed(case + 7)
@@ -53,11 +53,12 @@ def test_random_shapes_against_the_oracle(seed):
         ids = torch.randint(0, c["vocab"], (B, S), generator=torch.Generator().manual_seed(case))
         m = HydraB200Model(w, n_heads=c["H"], n_kv_heads=c["KV"], compression_factor=c["cf"], max_seq_len=cfg.max_seq_len,
                            mod_capacity=c["cap"], mor_min_depth=c["mind"], adaptive=c["adaptive"],
-                           static_routing_mode=c["static"])
+                           static_routing_mode=c["static"], mor_rampup_scale=c["ramp"])
         lg = m(ids.cuda(), taps=True).float().cpu()
         m.check_device_errors()
         forced = None
-        if not c["static"]:
+        blend = c["adaptive"] and 0.0 < c["ramp"] < 1.0     # two block outputs per step: no replay, no cached decode
+        if not c["static"] and not blend:
             tp = m.last_taps
             forced = O.RoutingTaps()
             d = tp.depths.cpu().long().view(NB, B, S)
@@ -70,7 +71,7 @@ def test_random_shapes_against_the_oracle(seed):
         e2 = 0.0
         kvd, lat = c["KV"] * c["hd"], c["H"] * c["hd"]
         decodable = kvd <= 256 and lat + kvd <= 1536 and c["H"] // c["KV"] <= 8      # the decode step's stated limits
-        if S >= 2 and decodable:
+        if S >= 2 and decodable and not blend:
             P = max(1, S - 4)
             n_new = min(4, cfg.max_seq_len - P)
             prompt = ids[:, :P]
