@@ -230,14 +230,42 @@ def causal_gqa_attention(q: Tensor, k: Tensor, v: Tensor) -> Tensor:
     return pr @ vv
 
 
-def ccgqa_forward(x: Tensor, p: Dict[str, Tensor], pre: str, cfg: HydraConfig) -> Tensor:
-    """CCGQAAttention.forward, causal, no padding mask (attention.py:201-331)."""
+def masked_gqa_attention(q: Tensor, k: Tensor, v: Tensor, mask: Tensor, semantics: str = "reference") -> Tensor:
+    """Attention with a padding mask [B,S] (1 = valid token, 0 = padding); query i may use key j where
+      "reference": j > i or key j is padding - what CCGQAAttention.forward(x, mask) computes: it builds a boolean mask that
+                   is True for future and padded keys (attention.py:269-283) and F.scaled_dot_product_attention reads True
+                   as "takes part";
+      "intended":  j <= i and key j is valid - what the comments there describe.
+    A query with no usable key gives zeros (SDPA's result for a fully masked row)."""
+    B, H, S, hd = q.shape
+    G = H // k.shape[1]
+    kk = k.repeat_interleave(G, dim=1)
+    vv = v.repeat_interleave(G, dim=1)
+    s = (q @ kk.transpose(-1, -2)) * (1.0 / math.sqrt(hd))
+    future = torch.ones(S, S, dtype=torch.bool).triu(1)[None, None]
+    pad = (mask == 0).view(B, 1, 1, S)
+    if semantics == "reference":
+        allowed = future | pad
+    elif semantics == "intended":
+        allowed = ~future & ~pad
+    else:
+        raise ValueError(f"unknown mask semantics {semantics!r}")
+    s = s.masked_fill(~allowed, float("-inf"))
+    pr = torch.softmax(s, dim=-1)
+    pr = torch.where(allowed.any(dim=-1, keepdim=True), pr, torch.zeros_like(pr))
+    return pr @ vv
+
+
+def ccgqa_forward(x: Tensor, p: Dict[str, Tensor], pre: str, cfg: HydraConfig, mask: Optional[Tensor] = None,
+                  mask_semantics: str = "reference") -> Tensor:
+    """CCGQAAttention.forward (attention.py:201-331): causal, or with a padding mask (see masked_gqa_attention; the
+    projections, convolutions and the value shift run over padded positions unchanged)."""
     B, S, _ = x.shape
     cos, sin = rope_tables(S, cfg.head_dim, cfg.rope_theta)
     cos, sin = cos.to(x.dtype), sin.to(x.dtype)
     qkv = x @ p[pre + "qkv_proj.weight"].transpose(0, 1)
     q, k, v = ccgqa_pre_attention(qkv, p, pre, cfg, cos, sin)
-    o = causal_gqa_attention(q, k, v)
+    o = causal_gqa_attention(q, k, v) if mask is None else masked_gqa_attention(q, k, v, mask, mask_semantics)
     o = o.transpose(1, 2).reshape(B, S, cfg.latent_dim)
     return (o @ p[pre + "o_proj.weight"].transpose(0, 1)) * cfg.output_scale
 

@@ -85,6 +85,40 @@ def gen_fused_ops() -> None:
 
 
 # ----------------------------------------------------------------------------
+def gen_attention_masked(name: str, dim: int, H: int, KV: int, S: int, seed: int) -> None:
+    """CCGQAAttention.forward(x, mask) as the reference computes it (attention.py:269-283): one sequence per mask
+    pattern - all valid, right-padded, left-padded, holes, all padded.  `y` is the reference's output as it is; the
+    boolean mask it hands to SDPA is True for future and padded keys, which SDPA reads as "take part"."""
+    from hydra.attention import build_hybrid_attention_module
+
+    torch.manual_seed(seed)
+    m = build_hybrid_attention_module("ccgqa", dim=dim, n_heads=H, n_kv_heads=KV, max_seq_len=S,
+                                      compression_factor=4, attention_kwargs={})
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() >= 2:
+                torch.nn.init.xavier_uniform_(p)
+        for p in m.parameters():
+            bf16_round_(p)
+    m.eval()
+    g = torch.Generator().manual_seed(seed + 100)
+    mask = torch.ones(5, S, dtype=torch.int64)
+    mask[1, S - 7:] = 0                                   # right padding
+    mask[2, :5] = 0                                       # left padding
+    mask[3] = (torch.rand(S, generator=g) > 0.3).long()   # holes
+    mask[4] = 0                                           # nothing valid
+    x = torch.randn(5, S, dim, generator=g).to(torch.bfloat16).to(torch.float32)
+    with torch.no_grad():
+        y = m(x, mask)
+        y_plain = m(x)
+    arrs = dict(meta=np.array([dim, H, KV, 5, S], dtype=np.int64), x=to_bits(x), mask=mask.numpy(), y=f32(y),
+                y_plain=f32(y_plain))
+    for kname, t in m.state_dict().items():
+        arrs["w:" + kname] = to_bits(t) if t.dim() >= 2 else f32(t)
+    save(name, **arrs)
+
+
+# ----------------------------------------------------------------------------
 def gen_attention(name: str, dim: int, H: int, KV: int, B: int, S: int, seed: int,
                   temperature: float | None = None) -> None:
     from hydra.attention import build_hybrid_attention_module
@@ -354,6 +388,9 @@ if __name__ == "__main__":
         gen_model("model_fresh.npz", vocab=200, dim=256, NB=3, R=2, H=4, KV=2, mlp_ratio=1.0,
                   B=2, S=48, cap=0.5, seed=29, fresh=True)
         sys.exit(0)
+    if len(sys.argv) > 1 and sys.argv[1] == "mask":     # only the attention module called with a padding mask
+        gen_attention_masked("ccgqa_mask.npz", 256, 4, 2, 40, seed=31)
+        sys.exit(0)
     if len(sys.argv) > 1 and sys.argv[1] == "rampup":   # only the model in the middle of its MoR ramp-up
         gen_model("model_rampup.npz", vocab=200, dim=256, NB=3, R=3, H=4, KV=2, mlp_ratio=1.0,
                   B=2, S=64, cap=0.75, seed=27, rampup=0.4)
@@ -375,6 +412,7 @@ if __name__ == "__main__":
     gen_attention("ccgqa_kv3.npz", 768, 12, 3, 1, 40, seed=4)
     # n_groups == 1 branch of the QK-mean coupling (H == KV)
     gen_attention("ccgqa_mha.npz", 256, 4, 4, 1, 33, seed=6)
+    gen_attention_masked("ccgqa_mask.npz", 256, 4, 2, 40, seed=31)
     # whole model, 4 blocks so that blocks 1 and 2 carry MoD
     gen_model("model_hd16.npz", vocab=384, dim=256, NB=4, R=3, H=4, KV=2, mlp_ratio=1.0,
               B=2, S=128, cap=0.75, seed=0)
