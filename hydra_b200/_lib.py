@@ -15,6 +15,7 @@ from . import build as _build
 c_i32, c_i64, c_f32, c_vp, c_sz = C.c_int, C.c_int64, C.c_float, C.c_void_p, C.c_size_t
 
 HB200_F32, HB200_BF16, HB200_F16 = 0, 1, 2
+MASK_AS_REFERENCE, MASK_INTENDED = 0, 1        # hb200_attention_masked_gqa / hb200_ccgqa_forward_masked mask modes
 EPI_STORE, EPI_RESID, EPI_SWIGLU, EPI_SCATTER_ADD = 0, 1, 2, 3
 
 
@@ -84,6 +85,10 @@ SIGNATURES = {
     "hb200_model_prefill_cached": (c_i32, [C.POINTER(Model), c_vp, c_i32, c_i32, c_vp, c_sz, C.POINTER(DecodeState),
                                            c_vp, c_i64, c_vp, c_vp]),
     "hb200_model_decode_step": (c_i32, [C.POINTER(Model), C.POINTER(DecodeState), c_vp, c_sz, c_vp, c_i64, c_vp, c_vp]),
+    "hb200_ccgqa_forward_masked": (c_i32, [C.POINTER(Model), c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_sz, c_vp,
+                                           c_vp]),
+    "hb200_attention_masked_gqa": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_f32,
+                                           c_vp]),
     "hb200_ccgqa_forward_static_max_bytes": (c_sz, []),
     "hb200_ccgqa_forward_static": (c_i32, [C.POINTER(Model), c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp]),
     "hb200_profile_create": (c_vp, [c_i32]),

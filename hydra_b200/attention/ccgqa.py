@@ -68,6 +68,10 @@ class CCGQAAttention(nn.Module):
         self._init_rope(max_seq_len)
         self.scale = self.head_dim ** -0.5
         self.max_seq_len = max_seq_len
+        # forward(x, mask): "reference" = what the reference module computes when it is handed a padding mask - its boolean
+        # mask is True for future and padded keys (attention.py:269-283) and SDPA lets True keys take part, so a query
+        # uses the keys after it and the padded ones; "intended" = causal over the valid keys, as its comments describe
+        self.mask_semantics = os.environ.get("HYDRA_B200_MASK_SEMANTICS", "reference").strip().lower()
         self._packed: Optional[PackedModel] = None
         self._packed_key = None
 
@@ -126,8 +130,6 @@ class CCGQAAttention(nn.Module):
                                       error_msgs)
 
     def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if mask is not None:
-            raise NotImplementedError("hydra_b200 CCGQAAttention: the padding-mask path is not built (causal only)")
         if not x.is_cuda:
             raise RuntimeError("hydra_b200 CCGQAAttention runs on CUDA tensors only (there is no CPU fallback)")
         B, S, D = x.shape
@@ -139,6 +141,19 @@ class CCGQAAttention(nn.Module):
         if B * S == 0:
             return y.to(x.dtype)
         ws = pm.workspace(B, S)
+        if mask is not None:
+            # mask [B, S], 1 = valid token, 0 = padding (attention.py:269-283); see ``mask_semantics``
+            if tuple(mask.shape) != (B, S):
+                raise ValueError(f"mask must be [batch, seq_len] = {(B, S)}, got {tuple(mask.shape)}")
+            modes = {"reference": _lib.MASK_AS_REFERENCE, "intended": _lib.MASK_INTENDED}
+            if self.mask_semantics not in modes:
+                raise ValueError(f"mask_semantics must be 'reference' or 'intended', got {self.mask_semantics!r}")
+            valid = (mask.to(x.device) != 0).to(torch.uint8).contiguous()
+            with kernels._on(x.device):
+                _lib.check(_lib.lib().hb200_ccgqa_forward_masked(
+                    C.byref(pm.struct), 0, xb.data_ptr(), y.data_ptr(), valid.data_ptr(), modes[self.mask_semantics], B, S,
+                    ws.data_ptr(), ws.numel(), pm.err_flag.data_ptr(), kernels._stream(x.device)), "ccgqa_forward_masked")
+            return y if x.dtype == torch.bfloat16 else y.to(x.dtype)
         with kernels._on(x.device):
             _lib.check(_lib.lib().hb200_ccgqa_forward(C.byref(pm.struct), 0, xb.data_ptr(), y.data_ptr(), B, S,
                                                       ws.data_ptr(), ws.numel(), pm.err_flag.data_ptr(),

@@ -238,6 +238,77 @@ __global__ void __launch_bounds__(128) attention_small_head_kernel(const __nv_bf
   }
 }
 
+// Attention with a padding mask (key_valid[b, j] != 0 <=> token j of sequence b is not padding), one thread per query row,
+// online softmax in registers, K and V rows read in 16-byte pieces (all threads of a warp ask for the same key: one
+// broadcast each).  Which keys query i may use:
+//   mode HB200_MASK_AS_REFERENCE: j > i or key j is padding - what the reference module computes when it is handed a
+//     mask: it marks future and padded keys True in a boolean mask (attention.py:269-283), which SDPA reads as "takes part";
+//   mode HB200_MASK_INTENDED:     j <= i and key j is valid - what its comments describe.
+// A query with no usable key gives zeros.  The reference's models never reach this path (their blocks drop the mask);
+// it is built for the module contract, not for speed.
+template <int HD>
+__global__ void __launch_bounds__(128) attention_masked_kernel(const __nv_bfloat16* __restrict__ q,
+                                                               const __nv_bfloat16* __restrict__ k,
+                                                               const __nv_bfloat16* __restrict__ v,
+                                                               const uint8_t* __restrict__ key_valid,
+                                                               __nv_bfloat16* __restrict__ o, int S, int H, int KV,
+                                                               float scale_log2, int mode) {
+  const int i = blockIdx.x * 128 + threadIdx.x;       // query position
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (H / KV);
+  const __nv_bfloat16* kp = k + ((size_t)b * KV + kvh) * S * HD;
+  const __nv_bfloat16* vp = v + ((size_t)b * KV + kvh) * S * HD;
+  const uint8_t* valid = key_valid + (size_t)b * S;
+  float qv[HD], acc[HD];
+#pragma unroll
+  for (int d = 0; d < HD; ++d) { qv[d] = 0.f; acc[d] = 0.f; }
+  if (i < S) {
+#pragma unroll
+    for (int c = 0; c < HD / 8; ++c) {
+      float t[8];
+      load_bf16x8(q + (((size_t)b * H + h) * S + i) * HD + c * 8, t);
+#pragma unroll
+      for (int d = 0; d < 8; ++d) qv[c * 8 + d] = t[d] * scale_log2;
+    }
+  }
+  float mx = -INFINITY, l = 0.f;
+  for (int j = 0; j < S; ++j) {
+    const bool ok = valid[j] != 0;                                           // uniform over the CTA
+    const bool use = i < S && (mode == HB200_MASK_AS_REFERENCE ? (j > i || !ok) : (j <= i && ok));
+    if (!__syncthreads_or(use)) continue;                                    // no row of this CTA wants key j
+    float sc = 0.f;
+#pragma unroll
+    for (int c = 0; c < HD / 8; ++c) {
+      float tk[8];
+      load_bf16x8(kp + (size_t)j * HD + c * 8, tk);
+#pragma unroll
+      for (int d = 0; d < 8; ++d) sc += qv[c * 8 + d] * tk[d];
+    }
+    if (!use) continue;
+    const float nm = fmaxf(mx, sc);
+    const float corr = exp2f(mx - nm), pj = exp2f(sc - nm);                  // exp2f(-inf) = 0 on the first key
+    l = l * corr + pj;
+#pragma unroll
+    for (int c = 0; c < HD / 8; ++c) {
+      float tv[8];
+      load_bf16x8(vp + (size_t)j * HD + c * 8, tv);
+#pragma unroll
+      for (int d = 0; d < 8; ++d) acc[c * 8 + d] = acc[c * 8 + d] * corr + pj * tv[d];
+    }
+    mx = nm;
+  }
+  if (i >= S) return;
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  __nv_bfloat16* dst = o + ((size_t)b * S + i) * ((size_t)H * HD) + (size_t)h * HD;
+#pragma unroll
+  for (int c = 0; c < HD / 8; ++c) {
+    float t[8];
+#pragma unroll
+    for (int d = 0; d < 8; ++d) t[d] = acc[c * 8 + d] * inv;
+    store_bf16x8(dst + c * 8, t);
+  }
+}
+
 int launch_attention_tcgen05(const void* q, const void* k, const void* v, void* o, int B, int S, int H, int KV, int hd,
                              float scale, float logit_bound, int32_t* err_flag, cudaStream_t st);
 
@@ -274,6 +345,35 @@ extern "C" int hb200_attention_causal_gqa(const void* q, const void* k, const vo
     set_error("attention: head_dim %d not built (8, 16, 32, 64)", hd);
     return HB200_ERR_UNSUPPORTED;
   }
+  HB_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int hb200_attention_masked_gqa(const void* q, const void* k, const void* v, void* o, const uint8_t* key_valid,
+                                          int mode, int B, int S, int H, int KV, int hd, float scale, void* stream) {
+  HB_REQUIRE(q && k && v && o && key_valid, HB200_ERR_INVALID, "masked attention: null pointer");
+  HB_REQUIRE(B >= 0 && S >= 0 && H >= 1 && KV >= 1 && H % KV == 0, HB200_ERR_INVALID, "masked attention: bad shape");
+  HB_REQUIRE(mode == HB200_MASK_AS_REFERENCE || mode == HB200_MASK_INTENDED, HB200_ERR_INVALID,
+             "masked attention: unknown mask mode %d", mode);
+  HB_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o), HB200_ERR_INVALID,
+             "masked attention: pointers must be 16-byte aligned");
+  HB_REQUIRE(B <= 65535 && H <= 65535, HB200_ERR_UNSUPPORTED, "masked attention: batch/head count beyond grid limits");
+  if ((int64_t)B * S == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  const dim3 grid((S + 127) / 128, H, B);
+  const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k, *vp = (const __nv_bfloat16*)v;
+#define HB_MASKED(HD_)                                                                                          \
+  attention_masked_kernel<HD_><<<grid, 128, 0, st>>>(qp, kp, vp, key_valid, (__nv_bfloat16*)o, S, H, KV, scale_log2, mode)
+  if (hd == 8) HB_MASKED(8);
+  else if (hd == 16) HB_MASKED(16);
+  else if (hd == 32) HB_MASKED(32);
+  else if (hd == 64) HB_MASKED(64);
+  else {
+    set_error("masked attention: head_dim %d not built (8, 16, 32, 64)", hd);
+    return HB200_ERR_UNSUPPORTED;
+  }
+#undef HB_MASKED
   HB_LAUNCH_CHECK();
   return 0;
 }

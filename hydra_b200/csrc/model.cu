@@ -144,7 +144,8 @@ static int gemm(const hb200_model* m, int kind, int bi, int r, const void* A, co
 
 // attention sub-block: y_out = epilogue(o Wo^T); resid == nullptr -> plain store scaled by alpha
 static int attention_part(const hb200_model* m, int bi, const hb200_block_weights& bw, const Workspace& w, const void* a_in,
-                          const void* resid, float alpha, void* out, int B, int S, int32_t* err, cudaStream_t st) {
+                          const void* resid, float alpha, void* out, int B, int S, int32_t* err, cudaStream_t st,
+                          const uint8_t* key_valid = nullptr, int mask_mode = 0) {
   const int T = B * S, D = m->dim, H = m->n_heads, KV = m->n_kv_heads, hd = m->head_dim;
   const int lat = H * hd, kvd = KV * hd, nq = lat + 2 * kvd;
   HB_PROPAGATE(gemm(m, HB200_K_GEMM_QKV, bi, 0, a_in, bw.w_qkv, w.qkv, T, nq, D, D, D, nq, EPI_STORE, nullptr, 1.0f,
@@ -156,8 +157,12 @@ static int attention_part(const hb200_model* m, int bi, const hb200_block_weight
   }
   {
     ProfScope ps(m->profile, st, HB200_K_ATTENTION, bi, 0, T, lat, S);
-    HB_PROPAGATE(hb200_attention_causal_gqa(w.q, w.k, w.v, w.o, B, S, H, KV, hd, 1.0f / sqrtf((float)hd),
-                                            bw.attn_logit_bound, err, st));
+    if (key_valid != nullptr)
+      HB_PROPAGATE(hb200_attention_masked_gqa(w.q, w.k, w.v, w.o, key_valid, mask_mode, B, S, H, KV, hd,
+                                              1.0f / sqrtf((float)hd), st));
+    else
+      HB_PROPAGATE(hb200_attention_causal_gqa(w.q, w.k, w.v, w.o, B, S, H, KV, hd, 1.0f / sqrtf((float)hd),
+                                              bw.attn_logit_bound, err, st));
   }
   HB_PROPAGATE(gemm(m, HB200_K_GEMM_O, bi, 0, w.o, bw.w_o, out, T, D, lat, lat, lat, D, resid ? EPI_RESID : EPI_STORE, resid, alpha, nullptr,
                     nullptr, err, st));
@@ -475,6 +480,18 @@ extern "C" int hb200_ccgqa_forward(const hb200_model* m, int block_index, const 
   HB_REQUIRE(workspace_bytes >= w.bytes, HB200_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.bytes);
   return attention_part(m, block_index, m->blocks[block_index], w, x, nullptr, m->output_scale, y, B, S, err_flag,
                         (cudaStream_t)stream);
+}
+
+extern "C" int hb200_ccgqa_forward_masked(const hb200_model* m, int block_index, const void* x, void* y,
+                                          const uint8_t* key_valid, int mask_mode, int B, int S, void* workspace,
+                                          size_t workspace_bytes, int32_t* err_flag, void* stream) {
+  HB_PROPAGATE(check_model(m, B, S));
+  HB_REQUIRE(x && y && workspace && key_valid, HB200_ERR_INVALID, "ccgqa_forward_masked: null pointer");
+  HB_REQUIRE(block_index >= 0 && block_index < m->n_blocks, HB200_ERR_INVALID, "ccgqa_forward_masked: bad block index");
+  Workspace w = carve(m, B, S, workspace);
+  HB_REQUIRE(workspace_bytes >= w.bytes, HB200_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.bytes);
+  return attention_part(m, block_index, m->blocks[block_index], w, x, nullptr, m->output_scale, y, B, S, err_flag,
+                        (cudaStream_t)stream, key_valid, mask_mode);
 }
 
 // ---- attention forward on library-owned scratch (no allocation anywhere on the call path) -------------------

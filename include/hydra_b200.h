@@ -145,6 +145,18 @@ int hb200_attention_causal_gqa(const void* q, const void* k, const void* v, void
                                int H, int KV, int hd, float scale, float logit_bound, int32_t* err_flag,
                                void* stream);
 
+/* Attention with a padding mask: CCGQAAttention.forward(x, mask), mask [B,S] with 1 = valid token, 0 = padding
+ * (attention.py:269-283).  key_valid: device uint8 [B*S], non-zero = valid.  Query i uses key j where
+ *   HB200_MASK_AS_REFERENCE: j > i or key j is padding.  This is what the reference computes: its boolean mask is True
+ *     for future and padded keys, and F.scaled_dot_product_attention reads True as "takes part";
+ *   HB200_MASK_INTENDED:     j <= i and key j is valid - what the comments at that place describe.
+ * A query with no usable key gives zeros (SDPA's result for a fully masked row).  Same layouts as
+ * hb200_attention_causal_gqa.  One CUDA-core kernel (a thread per query): the reference's models never reach this
+ * path - both block types drop the mask - so it is built for the module contract, not for speed. */
+enum { HB200_MASK_AS_REFERENCE = 0, HB200_MASK_INTENDED = 1 };
+int hb200_attention_masked_gqa(const void* q, const void* k, const void* v, void* o, const uint8_t* key_valid,
+                               int mode, int B, int S, int H, int KV, int hd, float scale, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Routing  (hydra/routing/mixture_of_depths.py:159-216, mixture_of_recursions.py:251-291,
  *           hydra/model/framework/blocks.py:243-269)
@@ -274,6 +286,11 @@ int hb200_block_forward(const hb200_model* m, int block_index, const void* x, vo
  * (y = o_proj(attn) * output_scale; no residual). Uses blocks[block_index] weights. */
 int hb200_ccgqa_forward(const hb200_model* m, int block_index, const void* x, void* y, int B, int S,
                         void* workspace, size_t workspace_bytes, int32_t* err_flag, void* stream);
+/* The same with a padding mask (key_valid, mask_mode: see hb200_attention_masked_gqa).  Projections, convolutions and
+ * the value shift run over padded positions unchanged, as in the reference; only the attention core reads the mask. */
+int hb200_ccgqa_forward_masked(const hb200_model* m, int block_index, const void* x, void* y, const uint8_t* key_valid,
+                               int mask_mode, int B, int S, void* workspace, size_t workspace_bytes, int32_t* err_flag,
+                               void* stream);
 
 /* ---------------------------------------------------------------------------
  * Cached (incremental) decode.  The reference has no KV cache and no decode path: its generation helper

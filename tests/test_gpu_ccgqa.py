@@ -183,8 +183,6 @@ def test_module_through_factory_matches_reference_output(name):
     q = torch.randn(1, cfg.n_heads, 8, cfg.head_dim, device="cuda")
     c, s = O.rope_tables(8, cfg.head_dim)
     assert max_abs(m._apply_rope(q, 8), O.rope(q.cpu(), c, s)) < 1e-5
-    with pytest.raises(NotImplementedError):
-        m(x.cuda(), mask=torch.ones(x.shape[:2], device="cuda"))
 
 
 def test_config2_block_batch_independence_and_determinism():
@@ -212,3 +210,66 @@ def test_config2_block_batch_independence_and_determinism():
     assert torch.equal(prefix[5], y[5, :1000])
     assert torch.isfinite(y.float()).all()
     m._packed.check_device_errors()
+
+
+def masked_module(cfg, w):
+    from hydra_b200.attention import build_hybrid_attention_module
+    m = build_hybrid_attention_module("ccgqa", dim=cfg.dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads,
+                                      max_seq_len=cfg.max_seq_len, compression_factor=4, attention_kwargs={})
+    m.load_state_dict({k[len("attn."):]: v for k, v in w.items()}, strict=True)
+    return m.cuda()
+
+
+def test_module_with_a_padding_mask_matches_the_reference_output():
+    """forward(x, mask) against the reference module's own output for five mask patterns (all valid, right padding,
+    left padding, holes, nothing valid).  The default semantics are the reference's computation, inversion included (a
+    query uses the keys after it and the padded ones; the last query of an all-valid sequence uses none and gives
+    zeros); ``mask_semantics = "intended"`` is causal attention over the valid keys, against the oracle."""
+    fx, cfg, w = G.attention_fixture("ccgqa_mask.npz")
+    x, mask = G.tensor(fx["x"]), torch.from_numpy(fx["mask"])
+    m = masked_module(cfg, w)
+    assert m.mask_semantics == "reference"
+    ref = torch.from_numpy(fx["y"])
+    for mk in (mask.cuda(), mask.bool().cuda(), mask.float()):        # integer, boolean, float masks; host or device
+        y = m(x.to(torch.bfloat16).cuda(), mask=mk)
+        m._packed.check_device_errors()
+        r, a = rel_l2(y, ref), max_abs(y, ref)
+        assert r < 1e-2 and a < 0.03 * float(ref.abs().max()), f"rel_l2 {r:.3e} max_abs {a:.3e}"
+    assert float(y[0, -1].float().abs().max()) == 0.0                 # no usable key: zeros, as in the reference
+    assert rel_l2(m(x.to(torch.bfloat16).cuda()), torch.from_numpy(fx["y_plain"])) < 1e-2   # unmasked path untouched
+    m.mask_semantics = "intended"
+    yi = m(x.to(torch.bfloat16).cuda(), mask=mask.cuda())
+    want = O.ccgqa_forward(x, w, "attn.", cfg, mask=mask, mask_semantics="intended")
+    assert rel_l2(yi, want) < 1e-2
+    assert rel_l2(yi[0], torch.from_numpy(fx["y_plain"])[0]) < 1e-2   # an all-ones mask changes nothing
+    assert float(yi[4].float().abs().max()) == 0.0                    # nothing valid: zeros
+    assert float(yi[2, :5].float().abs().max()) == 0.0                # left padding: no valid key yet
+    m.mask_semantics = "something else"
+    with pytest.raises(ValueError):
+        m(x.cuda(), mask=mask.cuda())
+    m.mask_semantics = "reference"
+    with pytest.raises(ValueError):
+        m(x.cuda(), mask=mask[:, :-1].cuda())
+
+
+@pytest.mark.parametrize("mode", ["reference", "intended"])
+@pytest.mark.parametrize("hd,H,KV,S", [(8, 4, 2, 50), (16, 8, 2, 257), (32, 6, 3, 130), (64, 2, 2, 300), (32, 2, 1, 1)])
+def test_masked_attention_core(L, hd, H, KV, S, mode):
+    """hb200_attention_masked_gqa against the oracle for every head size, random masks, ragged lengths."""
+    g = torch.Generator().manual_seed(11)
+    B = 3
+    q = bf16_round(torch.nn.functional.normalize(torch.randn(B, H, S, hd, generator=g), dim=-1))
+    k = bf16_round(torch.nn.functional.normalize(torch.randn(B, KV, S, hd, generator=g), dim=-1) * math.sqrt(hd))
+    v = bf16_round(torch.randn(B, KV, S, hd, generator=g))
+    mask = (torch.rand(B, S, generator=g) > 0.25).long()
+    mask[0] = 1
+    ref = O.masked_gqa_attention(q, k, v, mask, mode).transpose(1, 2).reshape(B, S, H * hd)
+    o = torch.full((B, S, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    qc, kc, vc = (t.to(torch.bfloat16).cuda().contiguous() for t in (q, k, v))
+    valid = mask.to(torch.uint8).cuda()
+    L.check(L.lib().hb200_attention_masked_gqa(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), valid.data_ptr(),
+                                               L.MASK_AS_REFERENCE if mode == "reference" else L.MASK_INTENDED, B, S, H,
+                                               KV, hd, 1.0 / math.sqrt(hd), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.isfinite(o.float()).all()
+    assert rel_l2(o, ref) < 5e-3

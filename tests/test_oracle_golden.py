@@ -50,6 +50,27 @@ def test_ccgqa_attention(name):
     close(O.ccgqa_forward(x, w, "attn.", cfg), fx["y"])
 
 
+def test_ccgqa_attention_with_a_padding_mask():
+    """CCGQAAttention.forward(x, mask) as the reference computes it (five mask patterns, run on the reference module):
+    the "reference" semantics reproduce it - a query uses the keys after it and the padded ones, a query without any
+    gives zeros -; the "intended" semantics are causal attention over the valid keys: an all-ones mask then changes
+    nothing, and a sequence without a valid token gives zeros."""
+    fx, cfg, w = G.attention_fixture("ccgqa_mask.npz")
+    x, mask = G.tensor(fx["x"]), torch.from_numpy(fx["mask"])
+    assert mask[0].all() and not mask[4].any()
+    close(O.ccgqa_forward(x, w, "attn.", cfg, mask=mask), fx["y"])
+    close(O.ccgqa_forward(x, w, "attn.", cfg), fx["y_plain"])
+    assert float(torch.from_numpy(fx["y"])[0, -1].abs().max()) == 0.0
+    yi = O.ccgqa_forward(x, w, "attn.", cfg, mask=mask, mask_semantics="intended")
+    close(yi[0], fx["y_plain"][0])
+    assert float(yi[4].abs().max()) == 0.0 and float(yi[2, :5].abs().max()) == 0.0
+    # right padding: the valid prefix does not see the padding at all
+    n = int(mask[1].sum())
+    close(yi[1, :n], O.ccgqa_forward(x[1:2, :n], w, "attn.", cfg)[0].numpy())
+    with pytest.raises(ValueError):
+        O.ccgqa_forward(x, w, "attn.", cfg, mask=mask, mask_semantics="other")
+
+
 @pytest.mark.parametrize("name", ["model_hd16.npz", "model_hd32.npz", "model_untied.npz"])
 def test_model_forward_and_routing(name):
     fx, cfg, w = G.model_fixture(name)
