@@ -7,8 +7,9 @@ Same constructor arguments, attributes, parameter names (``qkv_proj.weight``, ``
 extension: qkv GEMM (tcgen05), fused pre-attention kernel, causal GQA attention, output GEMM (tcgen05).
 
 Arithmetic: bf16 storage, fp32 accumulation; an fp32/fp16 input is converted to bf16 and the result converted
-back.  CUDA only.  Inference only (no autograd through the kernels).  Not built: the padding-mask path
-(``mask is not None``) and non-default ``use_*`` switches - both raise NotImplementedError.
+back.  CUDA only.  Inference only (no autograd through the kernels).  ``forward(x, mask)`` with a padding mask
+([B, S], 1 = valid) runs a CUDA-core attention kernel and by default computes what the reference computes there (see
+``mask_semantics``).  Not built: non-default ``use_*`` switches, which raise NotImplementedError.
 """
 from __future__ import annotations
 
