@@ -15,6 +15,7 @@ from . import build as _build
 c_i32, c_i64, c_f32, c_vp, c_sz = C.c_int, C.c_int64, C.c_float, C.c_void_p, C.c_size_t
 
 HB200_F32, HB200_BF16, HB200_F16 = 0, 1, 2
+ATTN_NO_ROPE, ATTN_NO_QK_NORM, ATTN_NO_CONVS, ATTN_NO_QK_MEAN, ATTN_NO_VALUE_SHIFT = 1, 2, 4, 8, 16   # hb200_model.attn_disable
 MASK_AS_REFERENCE, MASK_INTENDED = 0, 1        # hb200_attention_masked_gqa / hb200_ccgqa_forward_masked mask modes
 EPI_STORE, EPI_RESID, EPI_SWIGLU, EPI_SCATTER_ADD = 0, 1, 2, 3
 
@@ -31,7 +32,8 @@ class Model(C.Structure):
         "min_depth", "adaptive", "max_seq_len", "gemm_impl")] + [
         (n, c_f32) for n in ("mod_capacity", "norm_eps", "residual_scale", "output_scale")] + [
         ("tok_emb", c_vp), ("norm_w", c_vp), ("rope_cos", c_vp), ("rope_sin", c_vp),
-        ("blocks", C.POINTER(BlockWeights)), ("profile", c_vp), ("lm_head", c_vp), ("static_routing", C.c_int32), ("mor_rampup", c_f32)]
+        ("blocks", C.POINTER(BlockWeights)), ("profile", c_vp), ("lm_head", c_vp), ("static_routing", C.c_int32), ("mor_rampup", c_f32),
+        ("attn_disable", C.c_int32)]
 
 
 class LaunchRecord(C.Structure):
@@ -67,6 +69,7 @@ SIGNATURES = {
     "hb200_interleave_gate_up": (c_i32, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "hb200_repack_conv_weight": (c_i32, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "hb200_ccgqa_pre_attention": (c_i32, [c_vp] * 10 + [c_i32] * 5 + [c_vp, c_vp]),
+    "hb200_ccgqa_pre_attention_ablated": (c_i32, [c_vp] * 10 + [c_i32] * 6 + [c_vp, c_vp]),
     "hb200_attention_causal_gqa": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_f32, c_f32,
                                            c_vp, c_vp]),
     "hb200_mod_topk_select": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp]),

@@ -59,17 +59,23 @@ def interleave_gate_up(w: Tensor, device) -> Tensor:
 class PackedBlock:
     """Device tensors of one HydraMoRBlock (kept alive here) and the matching C struct."""
 
-    def __init__(self, sd: Dict[str, Tensor], pre: str, device, *, attention_only: bool = False, plain: bool = False):
+    def __init__(self, sd: Dict[str, Tensor], pre: str, device, *, attention_only: bool = False, plain: bool = False,
+                 head_dim: Optional[int] = None):
         """plain: a HydraBlock (blocks.py:33-70) - attention and one MLP pass, no routers, no recursion offsets, no exit
         norm; expressed as a one-recursion block with a zero offset."""
         a = pre if attention_only else pre + "attention."
         t: Dict[str, Optional[Tensor]] = {}
         t["w_qkv"] = _bf16(sd[a + "qkv_proj.weight"], device)
         t["w_o"] = _bf16(sd[a + "o_proj.weight"], device)
-        t["w1_qk"] = torch.cat([repack_conv(sd[a + "q_conv.conv1.weight"], device),
-                                repack_conv(sd[a + "k_conv.conv1.weight"], device)], dim=0).contiguous()
-        t["w2_q"] = repack_conv(sd[a + "q_conv.conv2.weight"], device)
-        t["w2_k"] = repack_conv(sd[a + "k_conv.conv2.weight"], device)
+        if a + "q_conv.conv1.weight" in sd:
+            t["w1_qk"] = torch.cat([repack_conv(sd[a + "q_conv.conv1.weight"], device),
+                                    repack_conv(sd[a + "k_conv.conv1.weight"], device)], dim=0).contiguous()
+            t["w2_q"] = repack_conv(sd[a + "q_conv.conv2.weight"], device)
+            t["w2_k"] = repack_conv(sd[a + "k_conv.conv2.weight"], device)
+        else:                                   # a module built with use_convs=False has no conv parameters
+            if head_dim is None:
+                raise KeyError(f"{a}q_conv.conv1.weight is missing (a module without convolutions must state its head_dim)")
+            t["w1_qk"] = t["w2_q"] = t["w2_k"] = None
         t["key_temperature"] = _f32(sd[a + "key_temperature"], device).reshape(1)
         for k in ("norm1_w", "norm2_w", "final_norm_w", "w_gate_up", "w_down", "mor_w", "mor_b", "rec",
                   "mod_wn", "mod_b"):
@@ -97,7 +103,7 @@ class PackedBlock:
         self.tensors = t
         # q is a unit vector and |k| = |key_temperature| after the fused pre-attention kernel (RoPE is a rotation), so
         # |q.k| / sqrt(hd) <= |temperature| / sqrt(hd); 2% slack covers the bf16 rounding of q and k
-        hd = sd[a + "q_conv.conv1.weight"].shape[1]
+        hd = head_dim if head_dim is not None else sd[a + "q_conv.conv1.weight"].shape[1]
         temp = abs(float(sd[a + "key_temperature"].detach().float().reshape(-1)[0].item()))
         self.attn_logit_bound = max(temp, 1e-3) / math.sqrt(hd) * 1.02
         self.struct = _lib.BlockWeights(**{k: (v.data_ptr() if v is not None else None) for k, v in t.items()},
@@ -111,7 +117,8 @@ class PackedModel:
                  ffn_hidden: int, min_depth: int, adaptive: bool, max_seq_len: int, mod_capacity: float,
                  norm_eps: float, residual_scale: float, output_scale: float, blocks: List[PackedBlock],
                  tok_emb: Optional[Tensor], norm_w: Optional[Tensor], device, gemm_impl: int = 0,
-                 lm_head: Optional[Tensor] = None, static_routing: bool = False, mor_rampup: float = 0.0):
+                 lm_head: Optional[Tensor] = None, static_routing: bool = False, mor_rampup: float = 0.0,
+                 attn_disable: int = 0):
         self.blocks = blocks
         self.block_array = (_lib.BlockWeights * len(blocks))(*[b.struct for b in blocks])
         self.cos, self.sin = rope_tables(max_seq_len, head_dim, device)
@@ -127,7 +134,7 @@ class PackedModel:
             rope_cos=self.cos.data_ptr(), rope_sin=self.sin.data_ptr(),
             blocks=C.cast(self.block_array, C.POINTER(_lib.BlockWeights)),
             lm_head=lm_head.data_ptr() if lm_head is not None else None, static_routing=int(bool(static_routing)),
-            mor_rampup=float(mor_rampup))
+            mor_rampup=float(mor_rampup), attn_disable=int(attn_disable))
         self._ws: Dict[tuple, Tensor] = {}
         self.device = device
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)

@@ -9,7 +9,8 @@ extension: qkv GEMM (tcgen05), fused pre-attention kernel, causal GQA attention,
 Arithmetic: bf16 storage, fp32 accumulation; an fp32/fp16 input is converted to bf16 and the result converted
 back.  CUDA only.  Inference only (no autograd through the kernels).  ``forward(x, mask)`` with a padding mask
 ([B, S], 1 = valid) runs a CUDA-core attention kernel and by default computes what the reference computes there (see
-``mask_semantics``).  Not built: non-default ``use_*`` switches, which raise NotImplementedError.
+``mask_semantics``).  The ``use_*`` ablation switches are honoured (a stage that is off selects a CUDA-core kernel);
+``conv_kernel_size`` other than 3 raises NotImplementedError.
 """
 from __future__ import annotations
 
@@ -56,15 +57,18 @@ class CCGQAAttention(nn.Module):
         self.kv_dim = n_kv_heads * self.head_dim
         assert self.latent_dim % n_heads == 0, f"latent_dim {self.latent_dim} must be divisible by n_heads {n_heads}"
         assert self.head_dim % 2 == 0, f"head_dim {self.head_dim} must be even for RoPE (splits into pairs)"
-        if not (use_rope and use_qk_norm and use_convs and use_qk_mean and use_value_shift) or conv_kernel_size != 3:
-            raise NotImplementedError(
-                "hydra_b200 CCGQAAttention implements the default CCGQA configuration only "
-                "(rope, qk-norm, convs with kernel size 3, qk-mean and value shift all enabled)")
+        if conv_kernel_size != 3 and use_convs:
+            raise NotImplementedError("hydra_b200 CCGQAAttention implements convolutions of kernel size 3 only")
+        # the reference's ablation switches: a stage that is off selects the CUDA-core pre-attention kernel
+        self._attn_disable = ((0 if use_rope else _lib.ATTN_NO_ROPE) | (0 if use_qk_norm else _lib.ATTN_NO_QK_NORM) |
+                              (0 if use_convs else _lib.ATTN_NO_CONVS) | (0 if use_qk_mean else _lib.ATTN_NO_QK_MEAN) |
+                              (0 if use_value_shift else _lib.ATTN_NO_VALUE_SHIFT))
         self.qkv_proj = nn.Linear(dim, self.latent_dim + 2 * self.kv_dim, bias=False)
         self.o_proj = nn.Linear(self.latent_dim, dim, bias=False)
         self.output_scale = float(os.environ.get("HYDRA_CCGQA_OUTPUT_SCALE", "1.0"))
-        self.q_conv = ConvSequence(self.latent_dim, n_heads, 1, conv_kernel_size)
-        self.k_conv = ConvSequence(self.kv_dim, n_kv_heads, 1, conv_kernel_size)
+        if use_convs:                            # as in the reference, a module without convolutions has no conv parameters
+            self.q_conv = ConvSequence(self.latent_dim, n_heads, 1, conv_kernel_size)
+            self.k_conv = ConvSequence(self.kv_dim, n_kv_heads, 1, conv_kernel_size)
         self.key_temperature = nn.Parameter(torch.full((1,), float(self.head_dim ** 0.5)))
         self._init_rope(max_seq_len)
         self.scale = self.head_dim ** -0.5
@@ -97,12 +101,13 @@ class CCGQAAttention(nn.Module):
         key = (device, self.cos_cached.shape[2]) + tuple((p.data_ptr(), p._version) for p in self.parameters())
         if self._packed is None or self._packed_key != key:
             sd = {k: v for k, v in self.state_dict().items()}
-            blk = PackedBlock(sd, "", device, attention_only=True)
+            blk = PackedBlock(sd, "", device, attention_only=True, head_dim=self.head_dim)
             self._packed = PackedModel(
                 vocab=8, dim=self.dim, n_rec=1, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
                 head_dim=self.head_dim, ffn_hidden=8, min_depth=0, adaptive=False,
                 max_seq_len=self.cos_cached.shape[2], mod_capacity=1.0, norm_eps=1e-6, residual_scale=1.0,
-                output_scale=self.output_scale, blocks=[blk], tok_emb=None, norm_w=None, device=device)
+                output_scale=self.output_scale, blocks=[blk], tok_emb=None, norm_w=None, device=device,
+                attn_disable=self._attn_disable)
             self._packed_key = key
         return self._packed
 

@@ -34,6 +34,7 @@ struct PreParams {
   __nv_bfloat16* k;
   __nv_bfloat16* v;
   int B, S, H, KV;
+  int disable;               // HB200_ATTN_NO_* bits (generic kernel only; the tiled kernels run the full sequence)
 };
 
 // out[m][n] (fp32 regs) = sum_{j<3} sum_{c<Cin} Y1[m + 14 + j][col_off + c] * W[n][j*Cin + c]
@@ -343,9 +344,12 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
     xs[idx] = (tok >= 0 && tok < S) ? __bfloat162float(qkv_b[(size_t)tok * QKV_LD + c]) : 0.f;
   }
   __syncthreads();
+  const bool convs = !(p.disable & HB200_ATTN_NO_CONVS), couple_on = !(p.disable & HB200_ATTN_NO_QK_MEAN);
+  const bool norm_on = !(p.disable & HB200_ATTN_NO_QK_NORM), rope_on = !(p.disable & HB200_ATTN_NO_ROPE);
+  const bool shift_on = !(p.disable & HB200_ATTN_NO_VALUE_SHIFT);
 
   // grouped conv: y1[t][c] = sum_j sum_i w1[c][j*HD + i] * x[t-2+j][head(c)*HD + i]
-  for (int c = tid; c < C; c += 256) {
+  for (int c = tid; convs && c < C; c += 256) {
     float acc[TT + 2];
 #pragma unroll
     for (int r = 0; r < TT + 2; ++r) acc[r] = 0.f;
@@ -364,7 +368,7 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
   __syncthreads();
 
   // dense conv: y2[t][c] = sum_j sum_ci w2[c][j*Cin + ci] * y1[t-2+j][off + ci]
-  for (int c = tid; c < C; c += 256) {
+  for (int c = tid; convs && c < C; c += 256) {
     float acc[TT];
 #pragma unroll
     for (int r = 0; r < TT; ++r) acc[r] = 0.f;
@@ -380,8 +384,10 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
 #pragma unroll
     for (int r = 0; r < TT; ++r) y2[r * C + c] = acc[r];
   }
+  if (!convs)                               // no convolutions: q and k go on as projected
+    for (int idx = tid; idx < TT * C; idx += 256) y2[idx] = xs[4 * C + idx];
   // QK-mean vectors from the un-convolved q0 / k0 of each token
-  if (H != KV) {
+  if (H != KV && couple_on) {
     for (int idx = tid; idx < TT * 2 * HD; idx += 256) {
       const int r = idx / (2 * HD), which = (idx / HD) & 1, d = idx % HD;
       const float* row = xs + (r + 4) * C;
@@ -394,7 +400,7 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
   __syncthreads();
 
   // finish: coupling, L2 norm, temperature, RoPE; one thread per (token, head)
-  const float temp = *p.temp;
+  const float temp = norm_on ? *p.temp : 1.0f;
   for (int idx = tid; idx < TT * (H + KV); idx += 256) {
     const int r = idx / (H + KV), hh = idx - r * (H + KV), tok = t0 + r;
     if (tok >= S) continue;
@@ -406,28 +412,30 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
     float ss = 0.f;
 #pragma unroll
     for (int d = 0; d < HD; ++d) {
-      float couple;
-      if (H == KV) couple = 0.5f * (x0[h * HD + d] + x0[LAT + h * HD + d]);   // m = 0.5 (q0 + k0), channel by channel
+      float couple = 0.f;
+      if (!couple_on) {}
+      else if (H == KV) couple = 0.5f * (x0[h * HD + d] + x0[LAT + h * HD + d]);   // m = 0.5 (q0 + k0), channel by channel
       else couple = is_q ? mean[(r * 2 + 1) * HD + d] : mean[(r * 2 + 0) * HD + d];
       v[d] = y2[r * C + c0 + d] + couple;
       ss += v[d] * v[d];
     }
-    const float inv = (is_q ? 1.0f : temp) / fmaxf(sqrtf(ss), 1e-12f);
+    const float inv = norm_on ? (is_q ? 1.0f : temp) / fmaxf(sqrtf(ss), 1e-12f) : 1.0f;
     __nv_bfloat16* dst = is_q ? p.q + (((size_t)b * H + h) * S + tok) * HD : p.k + (((size_t)b * KV + h) * S + tok) * HD;
     const float* cs = p.cos_t + (size_t)tok * (HD / 2);
     const float* sn = p.sin_t + (size_t)tok * (HD / 2);
 #pragma unroll
     for (int i = 0; i < HD / 2; ++i) {
       const float a0 = v[2 * i] * inv, a1 = v[2 * i + 1] * inv;
-      dst[2 * i] = __float2bfloat16(a0 * cs[i] - a1 * sn[i]);
-      dst[2 * i + 1] = __float2bfloat16(a0 * sn[i] + a1 * cs[i]);
+      const float c_ = rope_on ? cs[i] : 1.0f, s_ = rope_on ? sn[i] : 0.0f;
+      dst[2 * i] = __float2bfloat16(a0 * c_ - a1 * s_);
+      dst[2 * i + 1] = __float2bfloat16(a0 * s_ + a1 * c_);
     }
   }
   // value shift: first half of the channels from this token, second half from the previous one
   for (int idx = tid; idx < TT * KVD; idx += 256) {
     const int r = idx / KVD, c = idx - r * KVD, tok = t0 + r;
     if (tok >= S) continue;
-    const int src = (c < KVD / 2) ? tok : tok - 1;
+    const int src = (c < KVD / 2 || !shift_on) ? tok : tok - 1;
     p.v[(((size_t)b * KV + c / HD) * S + tok) * HD + (c % HD)] =
         src >= 0 ? qkv_b[(size_t)src * QKV_LD + LAT + KVD + c] : __float2bfloat16(0.f);
   }
@@ -460,30 +468,35 @@ int launch_ccgqa_pre_tc(const void* qkv, const void* w1_qk, const void* w2_q, co
 
 using namespace hb200;
 
-extern "C" int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k,
-                                         const float* cos_t, const float* sin_t, const float* key_temperature, void* q,
-                                         void* k, void* v, int B, int S, int H, int KV, int hd, int32_t* err_flag,
-                                         void* stream) {
-  HB_REQUIRE(qkv && w1_qk && w2_q && w2_k && cos_t && sin_t && key_temperature && q && k && v, HB200_ERR_INVALID,
-             "ccgqa_pre_attention: null pointer");
+static int pre_attention(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k, const float* cos_t,
+                         const float* sin_t, const float* key_temperature, void* q, void* k, void* v, int B, int S, int H,
+                         int KV, int hd, int disable, int32_t* err_flag, void* stream) {
+  HB_REQUIRE(qkv && q && k && v, HB200_ERR_INVALID, "ccgqa_pre_attention: null pointer");
+  HB_REQUIRE((disable & ~HB200_ATTN_NO_ALL) == 0, HB200_ERR_INVALID, "ccgqa_pre_attention: unknown switch bits %d", disable);
+  HB_REQUIRE((disable & HB200_ATTN_NO_CONVS) || (w1_qk && w2_q && w2_k), HB200_ERR_INVALID,
+             "ccgqa_pre_attention: null conv weights");
+  HB_REQUIRE((disable & HB200_ATTN_NO_ROPE) || (cos_t && sin_t), HB200_ERR_INVALID, "ccgqa_pre_attention: null RoPE tables");
+  HB_REQUIRE((disable & HB200_ATTN_NO_QK_NORM) || key_temperature, HB200_ERR_INVALID,
+             "ccgqa_pre_attention: null key temperature");
   HB_REQUIRE(B >= 0 && S >= 0 && H >= 1 && KV >= 1 && H % KV == 0, HB200_ERR_INVALID,
              "ccgqa_pre_attention: bad shape B=%d S=%d H=%d KV=%d", B, S, H, KV);
   HB_REQUIRE(aligned16(qkv) && aligned16(w2_q) && aligned16(w2_k) && aligned16(q) && aligned16(k) && aligned16(v),
              HB200_ERR_INVALID, "ccgqa_pre_attention: pointers must be 16-byte aligned");
+  HB_REQUIRE(hd % 2 == 0, HB200_ERR_INVALID, "ccgqa_pre_attention: head_dim must be even");
   if ((int64_t)B * S == 0) return 0;
   const int lat = H * hd, kvd = KV * hd;
   PreParams p{(const __nv_bfloat16*)qkv, (const __nv_bfloat16*)w1_qk, (const __nv_bfloat16*)w2_q,
               (const __nv_bfloat16*)w2_k, cos_t, sin_t, key_temperature, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
-              (__nv_bfloat16*)v, B, S, H, KV};
+              (__nv_bfloat16*)v, B, S, H, KV, disable};
   cudaStream_t st = (cudaStream_t)stream;
-  {
+  if (disable == 0) {
     // tcgen05 kernel for the 250M-class shapes; HB200_ERR_UNSUPPORTED means "not this shape", anything else is final
     const int rc = launch_ccgqa_pre_tc(qkv, w1_qk, w2_q, w2_k, cos_t, sin_t, key_temperature, q, k, v, B, S, H, KV, hd,
                                        err_flag, st);
     if (rc != HB200_ERR_UNSUPPORTED) return rc;
   }
 #define HB_PRE_CASE(HD_, NTQ_, NTK_) \
-  if (hd == HD_ && lat == NTQ_ * 32 && kvd == NTK_ * 16) return launch_pre<HD_, NTQ_, NTK_>(p, st);
+  if (disable == 0 && hd == HD_ && lat == NTQ_ * 32 && kvd == NTK_ * 16) return launch_pre<HD_, NTQ_, NTK_>(p, st);
   HB_PRE_CASE(32, 8, 4)    // dim 1024: 8q/2kv heads of 32
   HB_PRE_CASE(16, 8, 4)    // dim 1024: 16q/4kv heads of 16
   HB_PRE_CASE(16, 4, 2)    // dim 512: 8q/2kv heads of 16
@@ -497,12 +510,12 @@ extern "C" int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, con
   HB_PRE_CASE(16, 9, 3)    // dim 1152: 18q/3kv heads of 16 (the reference's 300M preset)
 #undef HB_PRE_CASE
   // latent 512 (dim 2048, 32q/4kv heads of 16: the 1.5B shape): 32-token tiles and 32-wide weight chunks to fit
-  if (hd == 16 && lat == 512 && kvd == 64) return launch_pre<16, 16, 4, 32, 32>(p, st);
+  if (disable == 0 && hd == 16 && lat == 512 && kvd == 64) return launch_pre<16, 16, 4, 32, 32>(p, st);
   // the reference's other presets, same tile shape: dim 1792 (28q/4kv: 500M, 1B), dim 1536 (24q/4kv: 750M) and the
   // trainer's default dim 1280 (20q/5kv)
-  if (hd == 16 && lat == 448 && kvd == 64) return launch_pre<16, 14, 4, 32, 32>(p, st);
-  if (hd == 16 && lat == 384 && kvd == 64) return launch_pre<16, 12, 4, 32, 32>(p, st);
-  if (hd == 16 && lat == 320 && kvd == 80) return launch_pre<16, 10, 5, 64, 32>(p, st);
+  if (disable == 0 && hd == 16 && lat == 448 && kvd == 64) return launch_pre<16, 14, 4, 32, 32>(p, st);
+  if (disable == 0 && hd == 16 && lat == 384 && kvd == 64) return launch_pre<16, 12, 4, 32, 32>(p, st);
+  if (disable == 0 && hd == 16 && lat == 320 && kvd == 80) return launch_pre<16, 10, 5, 64, 32>(p, st);
   // everything else with a head_dim the attention kernels are built for
   if (hd == 8) return launch_pre_generic<8>(p, st);
   if (hd == 16) return launch_pre_generic<16>(p, st);
@@ -510,4 +523,19 @@ extern "C" int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, con
   if (hd == 64) return launch_pre_generic<64>(p, st);
   set_error("ccgqa_pre_attention: head_dim %d not built (8, 16, 32, 64)", hd);
   return HB200_ERR_UNSUPPORTED;
+}
+
+extern "C" int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k,
+                                         const float* cos_t, const float* sin_t, const float* key_temperature, void* q,
+                                         void* k, void* v, int B, int S, int H, int KV, int hd, int32_t* err_flag,
+                                         void* stream) {
+  return pre_attention(qkv, w1_qk, w2_q, w2_k, cos_t, sin_t, key_temperature, q, k, v, B, S, H, KV, hd, 0, err_flag, stream);
+}
+
+extern "C" int hb200_ccgqa_pre_attention_ablated(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k,
+                                                 const float* cos_t, const float* sin_t, const float* key_temperature,
+                                                 void* q, void* k, void* v, int B, int S, int H, int KV, int hd,
+                                                 int disable, int32_t* err_flag, void* stream) {
+  return pre_attention(qkv, w1_qk, w2_q, w2_k, cos_t, sin_t, key_temperature, q, k, v, B, S, H, KV, hd, disable, err_flag,
+                       stream);
 }

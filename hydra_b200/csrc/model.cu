@@ -152,8 +152,9 @@ static int attention_part(const hb200_model* m, int bi, const hb200_block_weight
                     nullptr, nullptr, err, st));
   {
     ProfScope ps(m->profile, st, HB200_K_PRE_ATTENTION, bi, 0, T, nq, 0);
-    HB_PROPAGATE(hb200_ccgqa_pre_attention(w.qkv, bw.w1_qk, bw.w2_q, bw.w2_k, m->rope_cos, m->rope_sin,
-                                           bw.key_temperature, w.q, w.k, w.v, B, S, H, KV, hd, err, st));
+    HB_PROPAGATE(hb200_ccgqa_pre_attention_ablated(w.qkv, bw.w1_qk, bw.w2_q, bw.w2_k, m->rope_cos, m->rope_sin,
+                                                   bw.key_temperature, w.q, w.k, w.v, B, S, H, KV, hd, m->attn_disable,
+                                                   err, st));
   }
   {
     ProfScope ps(m->profile, st, HB200_K_ATTENTION, bi, 0, T, lat, S);
@@ -161,8 +162,10 @@ static int attention_part(const hb200_model* m, int bi, const hb200_block_weight
       HB_PROPAGATE(hb200_attention_masked_gqa(w.q, w.k, w.v, w.o, key_valid, mask_mode, B, S, H, KV, hd,
                                               1.0f / sqrtf((float)hd), st));
     else
+      // without the QK norm nothing bounds the logits: the online-softmax kernel
       HB_PROPAGATE(hb200_attention_causal_gqa(w.q, w.k, w.v, w.o, B, S, H, KV, hd, 1.0f / sqrtf((float)hd),
-                                              bw.attn_logit_bound, err, st));
+                                              (m->attn_disable & HB200_ATTN_NO_QK_NORM) ? 0.f : bw.attn_logit_bound,
+                                              err, st));
   }
   HB_PROPAGATE(gemm(m, HB200_K_GEMM_O, bi, 0, w.o, bw.w_o, out, T, D, lat, lat, lat, D, resid ? EPI_RESID : EPI_STORE, resid, alpha, nullptr,
                     nullptr, err, st));
@@ -649,6 +652,9 @@ extern "C" int hb200_model_prefill_cached(const hb200_model* m, const int64_t* i
   HB_REQUIRE(state->batch == B && state->capacity >= S && state->capacity <= m->max_seq_len, HB200_ERR_INVALID,
              "prefill_cached: state is for batch %d / capacity %d (need batch %d, %d <= capacity <= %d)", state->batch,
              state->capacity, B, S, m->max_seq_len);
+  HB_REQUIRE(m->attn_disable == 0, HB200_ERR_UNSUPPORTED,
+             "prefill_cached: attention stages switched off (attn_disable = %d) are not built for the cached decode",
+             m->attn_disable);
   HB_REQUIRE(ld_logits >= m->vocab && ld_logits % 8 == 0, HB200_ERR_INVALID, "prefill_cached: bad ld_logits");
   HB_REQUIRE(m->dim % 8 == 0, HB200_ERR_UNSUPPORTED, "prefill_cached: dim must be a multiple of 8");
   Workspace w = carve(m, B, S, workspace);

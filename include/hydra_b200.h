@@ -133,6 +133,21 @@ int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, const void* w2
                               void* q, void* k, void* v, int B, int S, int H, int KV, int hd,
                               int32_t* err_flag, void* stream);
 
+/* The same with some of the reference module's stages switched off (CCGQAAttention(use_rope=, use_qk_norm=, use_convs=,
+ * use_qk_mean=, use_value_shift=), attention.py:74-160, 211-266): `disable` is a mask of the bits below; 0 is
+ * hb200_ccgqa_pre_attention.  Without convolutions q and k go on as projected (conv weights may be NULL); without the
+ * QK norm neither the L2 normalisation nor the key temperature is applied (key_temperature may be NULL); without RoPE
+ * the tables may be NULL; without the value shift v is the last kv_dim columns of qkv.  Any switched-off stage selects
+ * the CUDA-core kernel (the reference's models never switch one off: these are its ablation switches). */
+enum {
+  HB200_ATTN_NO_ROPE = 1, HB200_ATTN_NO_QK_NORM = 2, HB200_ATTN_NO_CONVS = 4, HB200_ATTN_NO_QK_MEAN = 8,
+  HB200_ATTN_NO_VALUE_SHIFT = 16, HB200_ATTN_NO_ALL = 31
+};
+int hb200_ccgqa_pre_attention_ablated(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k,
+                                      const float* cos_t, const float* sin_t, const float* key_temperature,
+                                      void* q, void* k, void* v, int B, int S, int H, int KV, int hd, int disable,
+                                      int32_t* err_flag, void* stream);
+
 /* Causal grouped-query attention in the latent space (attention.py:288-327):
  * o[b,t,h,:] = softmax_causal(q[b,h] k[b,h/(H/KV)]^T * scale) v[b,h/(H/KV)].
  * q [B,H,S,hd], k/v [B,KV,S,hd] bf16; o token-major [B,S,H*hd] bf16.
@@ -252,6 +267,10 @@ typedef struct hb200_model {
                                      adaptive = 1): every block returns scale * adaptive + (1 - scale) * fixed-depth, both
                                      computed in full - forward / prefill only.  Any other value (0 included): no blend,
                                      `adaptive` alone decides. */
+  int32_t attn_disable;           /* HB200_ATTN_NO_* bits: stages of the attention module that are switched off (the
+                                     reference's ablation switches).  0 for every model the reference builds; non-zero is
+                                     honoured by hb200_ccgqa_forward[_masked] / hb200_block_forward / hb200_model_forward
+                                     and refused by the cached decode. */
 } hb200_model;
 
 /* Optional routing taps / forced routing for one forward (device pointers or NULL). */

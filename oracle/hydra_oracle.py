@@ -176,12 +176,17 @@ def conv_sequence(x: Tensor, w1: Tensor, w2: Tensor, groups1: int) -> Tensor:
     return causal_conv_k3(causal_conv_k3(x, w1, groups1), w2, 1)
 
 
+ATTENTION_STAGES = ("rope", "qk_norm", "convs", "qk_mean", "value_shift")
+
+
 def ccgqa_pre_attention(qkv: Tensor, p: Dict[str, Tensor], pre: str, cfg: HydraConfig,
-                        cos: Tensor, sin: Tensor) -> Tuple[Tensor, Tensor, Tensor]:
+                        cos: Tensor, sin: Tensor, off=()) -> Tuple[Tensor, Tensor, Tensor]:
     """Everything between qkv_proj and SDPA (attention.py:208-266).
 
     qkv [B,S,lat+2*kvd] -> q [B,H,S,hd], k [B,KV,S,hd], v [B,KV,S,hd].
+    ``off``: names from ATTENTION_STAGES that are switched off (the module's ``use_*`` arguments, attention.py:74-160).
     """
+    assert set(off) <= set(ATTENTION_STAGES), off
     B, S, _ = qkv.shape
     lat, kvd, H, KV, hd = cfg.latent_dim, cfg.kv_dim, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
     q0 = qkv[..., :lat]
@@ -191,11 +196,18 @@ def ccgqa_pre_attention(qkv: Tensor, p: Dict[str, Tensor], pre: str, cfg: HydraC
     v = qkv.new_zeros(B, S, kvd)
     v[..., :half] = qkv[..., lat + kvd:lat + kvd + half]
     v[:, 1:, half:] = qkv[:, :-1, lat + kvd + half:]
+    if "value_shift" in off:
+        v = qkv[..., lat + kvd:].clone()
     # conv sequences (attention.py:228-231)
-    q1 = conv_sequence(q0, p[pre + "q_conv.conv1.weight"], p[pre + "q_conv.conv2.weight"], H)
-    k1 = conv_sequence(k0, p[pre + "k_conv.conv1.weight"], p[pre + "k_conv.conv2.weight"], KV)
+    if "convs" in off:
+        q1, k1 = q0, k0
+    else:
+        q1 = conv_sequence(q0, p[pre + "q_conv.conv1.weight"], p[pre + "q_conv.conv2.weight"], H)
+        k1 = conv_sequence(k0, p[pre + "k_conv.conv1.weight"], p[pre + "k_conv.conv2.weight"], KV)
     # QK-mean coupling (attention.py:233-246)
-    if H // KV == 1:
+    if "qk_mean" in off:
+        q2, k2 = q1, k1
+    elif H // KV == 1:
         m = 0.5 * (q0 + k0)
         q2, k2 = q1 + m, k1 + m
     else:
@@ -207,11 +219,13 @@ def ccgqa_pre_attention(qkv: Tensor, p: Dict[str, Tensor], pre: str, cfg: HydraC
     k = k2.reshape(B, S, KV, hd).transpose(1, 2)
     v = v.reshape(B, S, KV, hd).transpose(1, 2)
     # L2 norm, key temperature (attention.py:260-262)
-    q = l2_normalize(q)
-    k = l2_normalize(k) * p[pre + "key_temperature"].to(k.dtype)
+    if "qk_norm" not in off:
+        q = l2_normalize(q)
+        k = l2_normalize(k) * p[pre + "key_temperature"].to(k.dtype)
     # RoPE after the norm (attention.py:264-266)
-    q = rope(q, cos, sin)
-    k = rope(k, cos, sin)
+    if "rope" not in off:
+        q = rope(q, cos, sin)
+        k = rope(k, cos, sin)
     return q.contiguous(), k.contiguous(), v.contiguous()
 
 
@@ -257,14 +271,14 @@ def masked_gqa_attention(q: Tensor, k: Tensor, v: Tensor, mask: Tensor, semantic
 
 
 def ccgqa_forward(x: Tensor, p: Dict[str, Tensor], pre: str, cfg: HydraConfig, mask: Optional[Tensor] = None,
-                  mask_semantics: str = "reference") -> Tensor:
+                  mask_semantics: str = "reference", off=()) -> Tensor:
     """CCGQAAttention.forward (attention.py:201-331): causal, or with a padding mask (see masked_gqa_attention; the
     projections, convolutions and the value shift run over padded positions unchanged)."""
     B, S, _ = x.shape
     cos, sin = rope_tables(S, cfg.head_dim, cfg.rope_theta)
     cos, sin = cos.to(x.dtype), sin.to(x.dtype)
     qkv = x @ p[pre + "qkv_proj.weight"].transpose(0, 1)
-    q, k, v = ccgqa_pre_attention(qkv, p, pre, cfg, cos, sin)
+    q, k, v = ccgqa_pre_attention(qkv, p, pre, cfg, cos, sin, off)
     o = causal_gqa_attention(q, k, v) if mask is None else masked_gqa_attention(q, k, v, mask, mask_semantics)
     o = o.transpose(1, 2).reshape(B, S, cfg.latent_dim)
     return (o @ p[pre + "o_proj.weight"].transpose(0, 1)) * cfg.output_scale

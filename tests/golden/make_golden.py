@@ -85,6 +85,39 @@ def gen_fused_ops() -> None:
 
 
 # ----------------------------------------------------------------------------
+def gen_attention_ablated(name: str, dim: int, H: int, KV: int, B: int, S: int, seed: int) -> None:
+    """The reference module built with each of its ablation switches off in turn, and with all of them off
+    (attention.py:74-160): one variant per entry, each with its own weights (`v{i}:w:` keys), the same input."""
+    from hydra.attention import build_hybrid_attention_module
+
+    stages = ["rope", "qk_norm", "convs", "qk_mean", "value_shift"]
+    variants = [[s_] for s_ in stages] + [["convs", "qk_mean"], stages]
+    g = torch.Generator().manual_seed(seed + 100)
+    x = torch.randn(B, S, dim, generator=g).to(torch.bfloat16).to(torch.float32)
+    arrs = dict(meta=np.array([dim, H, KV, B, S], dtype=np.int64), x=to_bits(x),
+                variants=np.array([",".join(v) for v in variants]))
+    for i, off in enumerate(variants):
+        torch.manual_seed(seed + i)
+        kw = {f"use_{s_}" if s_ != "convs" else "use_convs": (s_ not in off) for s_ in stages}
+        m = build_hybrid_attention_module("ccgqa", dim=dim, n_heads=H, n_kv_heads=KV, max_seq_len=S,
+                                          compression_factor=4, attention_kwargs=kw)
+        with torch.no_grad():
+            for p in m.parameters():
+                if p.dim() >= 2:
+                    torch.nn.init.xavier_uniform_(p)
+            for p in m.parameters():
+                bf16_round_(p)
+        m.eval()
+        for s_ in stages:
+            assert getattr(m, f"use_{s_}") == (s_ not in off)
+        with torch.no_grad():
+            arrs[f"v{i}:y"] = f32(m(x))
+        for kname, t in m.state_dict().items():
+            arrs[f"v{i}:w:" + kname] = to_bits(t) if t.dim() >= 2 else f32(t)
+    save(name, **arrs)
+
+
+# ----------------------------------------------------------------------------
 def gen_attention_masked(name: str, dim: int, H: int, KV: int, S: int, seed: int) -> None:
     """CCGQAAttention.forward(x, mask) as the reference computes it (attention.py:269-283): one sequence per mask
     pattern - all valid, right-padded, left-padded, holes, all padded.  `y` is the reference's output as it is; the
@@ -387,6 +420,9 @@ if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "fresh":    # only the freshly constructed model (MoD warm-up not passed)
         gen_model("model_fresh.npz", vocab=200, dim=256, NB=3, R=2, H=4, KV=2, mlp_ratio=1.0,
                   B=2, S=48, cap=0.5, seed=29, fresh=True)
+        sys.exit(0)
+    if len(sys.argv) > 1 and sys.argv[1] == "ablate":   # only the attention module with its ablation switches off
+        gen_attention_ablated("ccgqa_ablated.npz", 256, 4, 2, 2, 24, seed=37)
         sys.exit(0)
     if len(sys.argv) > 1 and sys.argv[1] == "mask":     # only the attention module called with a padding mask
         gen_attention_masked("ccgqa_mask.npz", 256, 4, 2, 40, seed=31)

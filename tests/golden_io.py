@@ -40,6 +40,17 @@ def attention_fixture(name: str):
     return fx, cfg, weights(fx, "attn.")
 
 
+def ablated_attention_fixture(name: str):
+    """(fx, cfg, [(stages that are off, weights with the 'attn.' prefix, reference output y), ...])."""
+    fx, cfg, _ = attention_fixture(name)
+    out = []
+    for i, names in enumerate(fx["variants"].tolist()):
+        pre = f"v{i}:w:"
+        w = {"attn." + k[len(pre):]: tensor(v).to(torch.float32) for k, v in fx.items() if k.startswith(pre)}
+        out.append((tuple(names.split(",")), w, torch.from_numpy(fx[f"v{i}:y"])))
+    return fx, cfg, out
+
+
 def model_fixture(name: str):
     from oracle.hydra_oracle import HydraConfig
     fx = load(name)

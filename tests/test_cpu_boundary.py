@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layouts_match_header_sizes():
     from hydra_b200 import _lib
     assert ctypes.sizeof(_lib.BlockWeights) == 16 * 8 + 8      # 16 pointers + one float, padded
-    assert ctypes.sizeof(_lib.Model) == 12 * 4 + 4 * 4 + 7 * 8 + 8   # trailing int32 + float fill one pointer slot
+    assert ctypes.sizeof(_lib.Model) == 12 * 4 + 4 * 4 + 7 * 8 + 16  # trailing int32, float, int32 + padding: two slots
     assert ctypes.sizeof(_lib.Taps) == 6 * 8 + 8
     assert ctypes.sizeof(_lib.LaunchRecord) == 24
     assert ctypes.sizeof(_lib.DecodeState) == 2 * 4 + 8 * 8    # batch, capacity, eight device pointers
@@ -90,9 +90,14 @@ def test_factory_builds_module_with_reference_parameter_layout(monkeypatch):
     m2 = build_hybrid_attention_module("ccqa", dim=512, n_heads=8, n_kv_heads=2, max_seq_len=64, compression_factor=4,
                                        attention_kwargs={})
     assert m2.use_fused_kernel is False
+    # the ablation switches: a module without convolutions has no conv parameters, as in the reference
+    m3 = build_hybrid_attention_module("ccqa", dim=512, n_heads=8, n_kv_heads=2, max_seq_len=64, compression_factor=4,
+                                       attention_kwargs={"use_convs": False, "use_rope": False})
+    assert not hasattr(m3, "q_conv") and m3.use_convs is False and m3.use_rope is False and m3.use_qk_norm is True
+    assert set(m3.state_dict()) == {"qkv_proj.weight", "o_proj.weight", "key_temperature"}
     with pytest.raises(NotImplementedError):
         build_hybrid_attention_module("ccqa", dim=512, n_heads=8, n_kv_heads=2, max_seq_len=64, compression_factor=4,
-                                      attention_kwargs={"use_convs": False})
+                                      attention_kwargs={"conv_kernel_size": 5})
 
 
 def test_legacy_checkpoint_layouts_are_remapped():

@@ -273,3 +273,41 @@ def test_masked_attention_core(L, hd, H, KV, S, mode):
     torch.cuda.synchronize()
     assert torch.isfinite(o.float()).all()
     assert rel_l2(o, ref) < 5e-3
+
+
+def test_module_with_stages_switched_off_matches_the_reference_output():
+    """The factory's use_* arguments (the reference's ablation switches): each stage off in turn, two off, all off - the
+    module against the reference module built the same way, a padding mask on top of one of them, and the cached
+    decode's refusal at model level is a C-side check (attn_disable)."""
+    from hydra_b200.attention import build_hybrid_attention_module
+    fx, cfg, variants = G.ablated_attention_fixture("ccgqa_ablated.npz")
+    x = G.tensor(fx["x"])
+    stages = ["rope", "qk_norm", "convs", "qk_mean", "value_shift"]
+    for off, w, ref in variants:
+        kw = {f"use_{s}": (s not in off) for s in stages}
+        m = build_hybrid_attention_module("ccgqa", dim=cfg.dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads,
+                                          max_seq_len=cfg.max_seq_len, compression_factor=4, attention_kwargs=kw)
+        m.load_state_dict({k[len("attn."):]: v for k, v in w.items()}, strict=True)
+        m = m.cuda()
+        assert hasattr(m, "q_conv") == ("convs" not in off)
+        y = m(x.to(torch.bfloat16).cuda())
+        m._packed.check_device_errors()
+        r, a = rel_l2(y, ref), max_abs(y, ref)
+        print(f"off {off}: rel_l2 {r:.3e} max_abs {a:.3e} (ref range {float(ref.abs().max()):.3g})")
+        assert r < 1e-2 and a < 0.03 * float(ref.abs().max()), f"off {off}"
+    # a padding mask and switched-off stages together, against the oracle
+    off, w, _ = variants[-2]
+    mask = torch.ones(x.shape[:2], dtype=torch.int64)
+    mask[0, -5:] = 0
+    kw = {f"use_{s}": (s not in off) for s in stages}
+    m = build_hybrid_attention_module("ccgqa", dim=cfg.dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads,
+                                      max_seq_len=cfg.max_seq_len, compression_factor=4, attention_kwargs=kw)
+    m.load_state_dict({k[len("attn."):]: v for k, v in w.items()}, strict=True)
+    m = m.cuda()
+    m.mask_semantics = "intended"
+    want = O.ccgqa_forward(x, w, "attn.", cfg, mask=mask, mask_semantics="intended", off=off)
+    assert rel_l2(m(x.to(torch.bfloat16).cuda(), mask=mask.cuda()), want) < 1e-2
+    with pytest.raises(NotImplementedError):
+        build_hybrid_attention_module("ccgqa", dim=cfg.dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads,
+                                      max_seq_len=cfg.max_seq_len, compression_factor=4,
+                                      attention_kwargs={"conv_kernel_size": 5})

@@ -50,6 +50,19 @@ def test_ccgqa_attention(name):
     close(O.ccgqa_forward(x, w, "attn.", cfg), fx["y"])
 
 
+def test_ccgqa_attention_with_stages_switched_off():
+    """The module's ablation switches (use_rope / use_qk_norm / use_convs / use_qk_mean / use_value_shift), each off in
+    turn, two off, all off: the oracle against the reference module built that way."""
+    fx, cfg, variants = G.ablated_attention_fixture("ccgqa_ablated.npz")
+    x = G.tensor(fx["x"])
+    assert len(variants) == 7
+    for off, w, y in variants:
+        assert ("attn.q_conv.conv1.weight" in w) == ("convs" not in off)      # no conv parameters without convolutions
+        close(O.ccgqa_forward(x, w, "attn.", cfg, off=off), y.numpy())
+    full = O.ccgqa_forward(x, variants[0][1], "attn.", cfg)
+    assert float((full - variants[0][2]).abs().max()) > 1e-3                  # the switch does change the result
+
+
 def test_ccgqa_attention_with_a_padding_mask():
     """CCGQAAttention.forward(x, mask) as the reference computes it (five mask patterns, run on the reference module):
     the "reference" semantics reproduce it - a query uses the keys after it and the padded ones, a query without any
