@@ -245,7 +245,8 @@ class HydraB200Model:
     def __init__(self, state_dict: Dict[str, Tensor], *, n_heads: int, n_kv_heads: int, compression_factor: int = 4,
                  max_seq_len: int = 2048, mod_capacity: float = 0.5, mor_min_depth: int = 0, adaptive: bool = True,
                  device: str | torch.device = "cuda", norm_eps: float = 1e-6, gemm_impl: int = 0,
-                 static_routing_mode: bool = False, mor_rampup_scale: float = 1.0):
+                 static_routing_mode: bool = False, mor_rampup_scale: float = 1.0, use_rope: bool = True,
+                 use_qk_norm: bool = True, use_convs: bool = True, use_qk_mean: bool = True, use_value_shift: bool = True):
         dev = torch.device(device)
         if dev.type != "cuda":
             raise RuntimeError("HydraB200Model needs a CUDA device (there is no CPU fallback)")
@@ -270,8 +271,13 @@ class HydraB200Model:
         if adaptive and self.mor_rampup_scale <= 0.0:
             adaptive = self.adaptive = False
         self.device = dev
+        # the attention modules' ablation switches: HydraMoRBlock hands use_* kwargs to the attention factory
+        # (blocks.py:482-490); HydraModel itself forwards none, so these only matter for a model assembled from such blocks
+        self.attn_disable = ((0 if use_rope else _lib.ATTN_NO_ROPE) | (0 if use_qk_norm else _lib.ATTN_NO_QK_NORM) |
+                             (0 if use_convs else _lib.ATTN_NO_CONVS) | (0 if use_qk_mean else _lib.ATTN_NO_QK_MEAN) |
+                             (0 if use_value_shift else _lib.ATTN_NO_VALUE_SHIFT))
         with kernels._on(dev):
-            blocks = [PackedBlock(sd, f"layers.{i}.", dev) for i in range(nb)]
+            blocks = [PackedBlock(sd, f"layers.{i}.", dev, head_dim=hd) for i in range(nb)]
             self.has_mod = [b.tensors["mod_wn"] is not None for b in blocks]
             self.packed = PackedModel(
                 vocab=V, dim=D, n_rec=R, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=hd, ffn_hidden=F,
@@ -280,7 +286,8 @@ class HydraB200Model:
                 output_scale=float(os.environ.get("HYDRA_CCGQA_OUTPUT_SCALE", "1.0")), blocks=blocks,
                 tok_emb=_bf16(sd["tok_emb.weight"], dev), norm_w=_f32(sd["norm.weight"], dev), device=dev,
                 gemm_impl=gemm_impl, lm_head=_untied_output(sd, dev), static_routing=self.static_routing_mode,
-                mor_rampup=self.mor_rampup_scale if 0.0 < self.mor_rampup_scale < 1.0 else 0.0)
+                mor_rampup=self.mor_rampup_scale if 0.0 < self.mor_rampup_scale < 1.0 else 0.0,
+                attn_disable=self.attn_disable)
         self.ld_logits = (V + 7) // 8 * 8
         self._logits: Optional[Tensor] = None
         self.last_taps: Optional[Taps] = None
@@ -301,7 +308,11 @@ class HydraB200Model:
         # by set_global_step); before that every token goes through the MLP, which is capacity 1.0 here
         wrappers = [l.mod_mlp_wrapper for l in model.layers if getattr(l, "mod_mlp_wrapper", None) is not None]
         mod_on = bool(wrappers) and all(getattr(w_, "_mod_enabled", False) for w_ in wrappers)
-        return dict(n_heads=model.n_heads, n_kv_heads=model.n_kv_heads, compression_factor=model.compression_factor,
+        attn = model.layers[0].attention
+        switches = {name: bool(getattr(attn, name, True))
+                    for name in ("use_rope", "use_qk_norm", "use_convs", "use_qk_mean", "use_value_shift")}
+        return dict(**{k: v for k, v in switches.items() if not v},       # only the ones that are off
+                    n_heads=model.n_heads, n_kv_heads=model.n_kv_heads, compression_factor=model.compression_factor,
                     max_seq_len=model.max_seq_len, mod_capacity=model.mod_capacity if mod_on else 1.0,
                     mor_min_depth=getattr(model, "mor_min_depth", 0), adaptive=model.adaptive,
                     static_routing_mode=bool(getattr(model, "static_routing_mode", False)),
@@ -499,6 +510,9 @@ class HydraB200Model:
         """Device state for ``batch`` sequences of up to ``capacity`` positions (prompt + generated)."""
         if self.adaptive and 0.0 < getattr(self, "mor_rampup_scale", 1.0) < 1.0:
             raise NotImplementedError("cached decode is not built for a MoR ramp-up scale between 0 and 1 "
+                                      "(use mode='reforward')")
+        if getattr(self, "attn_disable", 0):
+            raise NotImplementedError("cached decode is not built for attention modules with a stage switched off "
                                       "(use mode='reforward')")
         return DecodeSession(self, batch, capacity)
 

@@ -56,6 +56,9 @@ class HydraConfig:
     norm_eps: float = 1e-6
     rope_theta: float = 10000.0
     hidden_dim: Optional[int] = None  # override of the MLP width (op-level tests)
+    attn_off: tuple = ()             # attention stages switched off in every block (ATTENTION_STAGES): what blocks built as
+                                     # HydraMoRBlock(..., use_convs=False, ...) compute (blocks.py:482-490 hands the use_*
+                                     # kwargs to the attention factory; HydraModel itself forwards none of them)
     static_routing: bool = False     # static_routing_mode (model.py:202): dense compute with soft routing weights
     mor_rampup_scale: float = 1.0    # MoR curriculum (blocks.py:731-757): strictly between 0 and 1 the block returns
                                      # scale * adaptive + (1 - scale) * fixed-depth; <= 0 is the fixed-depth path
@@ -346,7 +349,7 @@ def static_block_forward(x: Tensor, p: Dict[str, Tensor], i: int, cfg: HydraConf
     R = cfg.recursions_per_block
     B, L, D = x.shape
     a = ada_rms_norm(x, p[pre + "norm1.weight"], cfg.norm_eps)
-    h = x + cfg.residual_scale * ccgqa_forward(a, p, pre + "attention.", cfg)
+    h = x + cfg.residual_scale * ccgqa_forward(a, p, pre + "attention.", cfg, off=cfg.attn_off)
     if cfg.adaptive:
         logits = h @ p[pre + "mor_router.router.weight"].reshape(-1) + p[pre + "mor_router.router.bias"]
         d = torch.sigmoid(torch.tanh(logits / 2.0) * 3.0) * (R - 1)
@@ -412,7 +415,7 @@ def mor_block_forward(x: Tensor, p: Dict[str, Tensor], i: int, cfg: HydraConfig,
     R = cfg.recursions_per_block
     B, L, D = x.shape
     a = ada_rms_norm(x, p[pre + "norm1.weight"], cfg.norm_eps)
-    att = ccgqa_forward(a, p, pre + "attention.", cfg)
+    att = ccgqa_forward(a, p, pre + "attention.", cfg, off=cfg.attn_off)
     h = x + cfg.residual_scale * att
     if cfg.adaptive:
         logits = h @ p[pre + "mor_router.router.weight"].reshape(-1) + p[pre + "mor_router.router.bias"]
@@ -489,7 +492,7 @@ def base_block_forward(x: Tensor, p: Dict[str, Tensor], i: int, cfg: HydraConfig
     """HydraBlock.forward (blocks.py:68-70): h = x + attn(norm1 x); h + mlp(norm2 h).  No routing, no residual
     scale, no exit norm."""
     pre = f"layers.{i}."
-    h = x + ccgqa_forward(rms_norm(x, p[pre + "norm1.weight"], cfg.norm_eps), p, pre + "attention.", cfg)
+    h = x + ccgqa_forward(rms_norm(x, p[pre + "norm1.weight"], cfg.norm_eps), p, pre + "attention.", cfg, off=cfg.attn_off)
     return h + swiglu_mlp(rms_norm(h, p[pre + "norm2.weight"], cfg.norm_eps), p[pre + "mlp.gate_up.weight"],
                           p[pre + "mlp.down.weight"])
 

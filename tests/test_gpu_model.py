@@ -621,3 +621,25 @@ def test_side_stream_gives_the_same_results():
             for a, b in zip(got, want):
                 assert torch.equal(a, b)
     m.check_device_errors()
+
+
+def test_attention_switches_at_model_level():
+    """HydraMoRBlock hands use_* kwargs to the attention factory (blocks.py:482-490; HydraModel itself forwards none of
+    them): a model assembled from blocks with stages switched off runs the same executor (hb200_model.attn_disable) -
+    prefill against the oracle with the routing replayed, generation by re-forward; the cached decode refuses."""
+    off = ("convs", "value_shift")
+    cfg = O.HydraConfig(vocab_size=97, dim=256, n_mor_blocks=3, recursions_per_block=2, n_heads=4, n_kv_heads=2,
+                        max_seq_len=80, mod_capacity=0.5, attn_off=off)
+    w = O.init_params(cfg, seed=4, perturb=True)
+    w = {k: v for k, v in w.items() if "_conv." not in k}                  # such a model has no conv parameters
+    ids = torch.randint(0, 97, (3, 70), generator=torch.Generator().manual_seed(4))
+    m = build(w, cfg, use_convs=False, use_value_shift=False)
+    lg = m(ids.cuda(), taps=True).float().cpu()
+    m.check_device_errors()
+    ref = O.model_forward(ids, w, cfg, forced=taps_to_oracle(m, m.last_taps, *ids.shape))
+    assert rel_l2(lg, ref) <= 1e-2
+    full = build(O.init_params(cfg, seed=4, perturb=True), cfg)(ids.cuda()).float().cpu()
+    assert rel_l2(full, lg) > 2e-2                                          # the switches change the result
+    assert m.generate(ids[:, :20].cuda(), 3).shape == (3, 23)
+    with pytest.raises(NotImplementedError):
+        m.generate(ids[:, :20].cuda(), 3, mode="cached")
