@@ -153,20 +153,22 @@ def swiglu(gate: Tensor, up: Tensor) -> Tensor:
 # CCGQA attention  (hydra/attention/backends/ccgqa/attention.py:201-331)
 # ----------------------------------------------------------------------------
 def causal_conv_k3(x: Tensor, w: Tensor, groups: int) -> Tensor:
-    """One causal Conv1d (cross-correlation, kernel 3, left zero padding of 2, no bias).
+    """One causal Conv1d (cross-correlation, left zero padding of K - 1, no bias); K = 3 in every model of the reference,
+    other sizes through the module's ``conv_kernel_size``.
 
-    x [B,S,C]; w [C, C/groups, 3]   (kernels/fused_conv.py:22-37,48-57).
-    y[t, c] = sum_j sum_{c' in group(c)} w[c, c', j] * x[t-2+j, c'],  x[<0] := 0.
+    x [B,S,C]; w [C, C/groups, K]   (kernels/fused_conv.py:22-37,48-57).
+    y[t, c] = sum_j sum_{c' in group(c)} w[c, c', j] * x[t-(K-1)+j, c'],  x[<0] := 0.
     """
     B, S, C = x.shape
+    K = w.shape[-1]
     cg = C // groups
-    xp = torch.cat([x.new_zeros(B, 2, C), x], dim=1)           # [B, S+2, C]
+    xp = torch.cat([x.new_zeros(B, K - 1, C), x], dim=1)       # [B, S+K-1, C]
     y = x.new_zeros(B, S, C)
     for g in range(groups):
-        xs = xp[:, :, g * cg:(g + 1) * cg]                     # [B, S+2, cg]
-        wg = w[g * cg:(g + 1) * cg]                            # [cg_out, cg_in, 3]
+        xs = xp[:, :, g * cg:(g + 1) * cg]                     # [B, S+K-1, cg]
+        wg = w[g * cg:(g + 1) * cg]                            # [cg_out, cg_in, K]
         acc = 0
-        for j in range(3):
+        for j in range(K):
             acc = acc + xs[:, j:j + S, :] @ wg[:, :, j].transpose(0, 1)
         y[:, :, g * cg:(g + 1) * cg] = acc
     return y

@@ -86,19 +86,23 @@ def gen_fused_ops() -> None:
 
 # ----------------------------------------------------------------------------
 def gen_attention_ablated(name: str, dim: int, H: int, KV: int, B: int, S: int, seed: int) -> None:
-    """The reference module built with each of its ablation switches off in turn, and with all of them off
-    (attention.py:74-160): one variant per entry, each with its own weights (`v{i}:w:` keys), the same input."""
+    """The reference module built with each of its ablation switches off in turn, two off, all of them off, and with conv
+    kernel sizes 2 and 5 (attention.py:74-160): one variant per entry, each with its own weights (`v{i}:w:` keys), the
+    same input."""
     from hydra.attention import build_hybrid_attention_module
 
     stages = ["rope", "qk_norm", "convs", "qk_mean", "value_shift"]
-    variants = [[s_] for s_ in stages] + [["convs", "qk_mean"], stages]
+    variants = [[s_] for s_ in stages] + [["convs", "qk_mean"], stages, ["ksize=2"], ["ksize=5"]]
     g = torch.Generator().manual_seed(seed + 100)
     x = torch.randn(B, S, dim, generator=g).to(torch.bfloat16).to(torch.float32)
     arrs = dict(meta=np.array([dim, H, KV, B, S], dtype=np.int64), x=to_bits(x),
                 variants=np.array([",".join(v) for v in variants]))
     for i, off in enumerate(variants):
         torch.manual_seed(seed + i)
-        kw = {f"use_{s_}" if s_ != "convs" else "use_convs": (s_ not in off) for s_ in stages}
+        kw = {f"use_{s_}": (s_ not in off) for s_ in stages}
+        for tag in off:
+            if tag.startswith("ksize="):                  # a variant with another conv kernel size, every stage on
+                kw["conv_kernel_size"] = int(tag[6:])
         m = build_hybrid_attention_module("ccgqa", dim=dim, n_heads=H, n_kv_heads=KV, max_seq_len=S,
                                           compression_factor=4, attention_kwargs=kw)
         with torch.no_grad():

@@ -41,13 +41,14 @@ def attention_fixture(name: str):
 
 
 def ablated_attention_fixture(name: str):
-    """(fx, cfg, [(stages that are off, weights with the 'attn.' prefix, reference output y), ...])."""
+    """(fx, cfg, [(stages that are off, weights with the 'attn.' prefix, reference output y), ...]); the variants with
+    another conv kernel size have every stage on and show it in the shape of their conv weights."""
     fx, cfg, _ = attention_fixture(name)
     out = []
     for i, names in enumerate(fx["variants"].tolist()):
         pre = f"v{i}:w:"
         w = {"attn." + k[len(pre):]: tensor(v).to(torch.float32) for k, v in fx.items() if k.startswith(pre)}
-        out.append((tuple(names.split(",")), w, torch.from_numpy(fx[f"v{i}:y"])))
+        out.append((tuple(n for n in names.split(",") if not n.startswith("ksize=")), w, torch.from_numpy(fx[f"v{i}:y"])))
     return fx, cfg, out
 
 

@@ -52,10 +52,10 @@ def test_ccgqa_attention(name):
 
 def test_ccgqa_attention_with_stages_switched_off():
     """The module's ablation switches (use_rope / use_qk_norm / use_convs / use_qk_mean / use_value_shift), each off in
-    turn, two off, all off: the oracle against the reference module built that way."""
+    turn, two off, all off, and conv kernel sizes 2 and 5: the oracle against the reference module built that way."""
     fx, cfg, variants = G.ablated_attention_fixture("ccgqa_ablated.npz")
     x = G.tensor(fx["x"])
-    assert len(variants) == 7
+    assert len(variants) == 9 and [v[1]["attn.q_conv.conv1.weight"].shape[-1] for v in variants[-2:]] == [2, 5]
     for off, w, y in variants:
         assert ("attn.q_conv.conv1.weight" in w) == ("convs" not in off)      # no conv parameters without convolutions
         close(O.ccgqa_forward(x, w, "attn.", cfg, off=off), y.numpy())
