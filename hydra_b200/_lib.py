@@ -33,7 +33,7 @@ class Model(C.Structure):
         (n, c_f32) for n in ("mod_capacity", "norm_eps", "residual_scale", "output_scale")] + [
         ("tok_emb", c_vp), ("norm_w", c_vp), ("rope_cos", c_vp), ("rope_sin", c_vp),
         ("blocks", C.POINTER(BlockWeights)), ("profile", c_vp), ("lm_head", c_vp), ("static_routing", C.c_int32), ("mor_rampup", c_f32),
-        ("attn_disable", C.c_int32)]
+        ("attn_disable", C.c_int32), ("conv_ksize", C.c_int32)]
 
 
 class LaunchRecord(C.Structure):
@@ -69,7 +69,8 @@ SIGNATURES = {
     "hb200_interleave_gate_up": (c_i32, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "hb200_repack_conv_weight": (c_i32, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "hb200_ccgqa_pre_attention": (c_i32, [c_vp] * 10 + [c_i32] * 5 + [c_vp, c_vp]),
-    "hb200_ccgqa_pre_attention_ablated": (c_i32, [c_vp] * 10 + [c_i32] * 6 + [c_vp, c_vp]),
+    "hb200_ccgqa_pre_attention_ablated": (c_i32, [c_vp] * 10 + [c_i32] * 7 + [c_vp, c_vp]),
+    "hb200_repack_conv_weight_k": (c_i32, [c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "hb200_attention_causal_gqa": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_f32, c_f32,
                                            c_vp, c_vp]),
     "hb200_mod_topk_select": (c_i32, [c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp]),

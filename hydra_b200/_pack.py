@@ -35,13 +35,13 @@ def _stream(device) -> int:
 
 
 def repack_conv(w: Tensor, device) -> Tensor:
-    """Conv1d weight [C_out, C_in/groups, 3] -> bf16 [C_out, 3*C_in/groups], (co, j*cin+ci) = w[co, ci, j]."""
+    """Conv1d weight [C_out, C_in/groups, K] -> bf16 [C_out, K*C_in/groups], (co, j*cin+ci) = w[co, ci, j]."""
     src = _bf16(w, device)
     co, ci, ks = src.shape
-    if ks != 3:
-        raise NotImplementedError(f"conv kernel size {ks}: the fused kernel is built for kernel size 3")
-    out = torch.empty((co, 3 * ci), dtype=torch.bfloat16, device=device)
-    _lib.check(_lib.lib().hb200_repack_conv_weight(src.data_ptr(), out.data_ptr(), co, ci, _stream(device)),
+    if not 1 <= ks <= 8:
+        raise NotImplementedError(f"conv kernel size {ks}: the pre-attention kernels are built for kernel sizes 1 to 8")
+    out = torch.empty((co, ks * ci), dtype=torch.bfloat16, device=device)
+    _lib.check(_lib.lib().hb200_repack_conv_weight_k(src.data_ptr(), out.data_ptr(), co, ci, ks, _stream(device)),
                "repack_conv_weight")
     return out
 
@@ -72,10 +72,12 @@ class PackedBlock:
                                     repack_conv(sd[a + "k_conv.conv1.weight"], device)], dim=0).contiguous()
             t["w2_q"] = repack_conv(sd[a + "q_conv.conv2.weight"], device)
             t["w2_k"] = repack_conv(sd[a + "k_conv.conv2.weight"], device)
+            self.conv_ksize = int(sd[a + "q_conv.conv1.weight"].shape[-1])
         else:                                   # a module built with use_convs=False has no conv parameters
             if head_dim is None:
                 raise KeyError(f"{a}q_conv.conv1.weight is missing (a module without convolutions must state its head_dim)")
             t["w1_qk"] = t["w2_q"] = t["w2_k"] = None
+            self.conv_ksize = 3
         t["key_temperature"] = _f32(sd[a + "key_temperature"], device).reshape(1)
         for k in ("norm1_w", "norm2_w", "final_norm_w", "w_gate_up", "w_down", "mor_w", "mor_b", "rec",
                   "mod_wn", "mod_b"):
@@ -134,7 +136,10 @@ class PackedModel:
             rope_cos=self.cos.data_ptr(), rope_sin=self.sin.data_ptr(),
             blocks=C.cast(self.block_array, C.POINTER(_lib.BlockWeights)),
             lm_head=lm_head.data_ptr() if lm_head is not None else None, static_routing=int(bool(static_routing)),
-            mor_rampup=float(mor_rampup), attn_disable=int(attn_disable))
+            mor_rampup=float(mor_rampup), attn_disable=int(attn_disable),
+            conv_ksize=blocks[0].conv_ksize if blocks else 3)
+        if any(b.conv_ksize != blocks[0].conv_ksize for b in blocks):
+            raise ValueError("blocks with different conv kernel sizes")
         self._ws: Dict[tuple, Tensor] = {}
         self.device = device
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)

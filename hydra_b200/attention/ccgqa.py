@@ -10,7 +10,7 @@ Arithmetic: bf16 storage, fp32 accumulation; an fp32/fp16 input is converted to 
 back.  CUDA only.  Inference only (no autograd through the kernels).  ``forward(x, mask)`` with a padding mask
 ([B, S], 1 = valid) runs a CUDA-core attention kernel and by default computes what the reference computes there (see
 ``mask_semantics``).  The ``use_*`` ablation switches are honoured (a stage that is off selects a CUDA-core kernel);
-``conv_kernel_size`` other than 3 raises NotImplementedError.
+so does a ``conv_kernel_size`` other than 3; sizes above 8 raise NotImplementedError.
 """
 from __future__ import annotations
 
@@ -57,8 +57,8 @@ class CCGQAAttention(nn.Module):
         self.kv_dim = n_kv_heads * self.head_dim
         assert self.latent_dim % n_heads == 0, f"latent_dim {self.latent_dim} must be divisible by n_heads {n_heads}"
         assert self.head_dim % 2 == 0, f"head_dim {self.head_dim} must be even for RoPE (splits into pairs)"
-        if conv_kernel_size != 3 and use_convs:
-            raise NotImplementedError("hydra_b200 CCGQAAttention implements convolutions of kernel size 3 only")
+        if use_convs and not 1 <= conv_kernel_size <= 8:
+            raise NotImplementedError("hydra_b200 CCGQAAttention implements conv kernel sizes 1 to 8")
         # the reference's ablation switches: a stage that is off selects the CUDA-core pre-attention kernel
         self._attn_disable = ((0 if use_rope else _lib.ATTN_NO_ROPE) | (0 if use_qk_norm else _lib.ATTN_NO_QK_NORM) |
                               (0 if use_convs else _lib.ATTN_NO_CONVS) | (0 if use_qk_mean else _lib.ATTN_NO_QK_MEAN) |

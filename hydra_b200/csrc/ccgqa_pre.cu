@@ -35,6 +35,7 @@ struct PreParams {
   __nv_bfloat16* v;
   int B, S, H, KV;
   int disable;               // HB200_ATTN_NO_* bits (generic kernel only; the tiled kernels run the full sequence)
+  int ksize;                 // conv kernel size (generic kernel only; the tiled kernels are built for 3)
 };
 
 // out[m][n] (fp32 regs) = sum_{j<3} sum_{c<Cin} Y1[m + 14 + j][col_off + c] * W[n][j*Cin + c]
@@ -324,14 +325,16 @@ static int launch_pre(const PreParams& p, cudaStream_t st) {
 // kernels round their operand), everything after it stays in fp32 until the final store.  One CTA = TT tokens of one
 // sequence; thread = output channel in both convs (its weight row is read once and used for all TT tokens, the
 // activations come from shared memory as broadcasts).  Built for coverage, not speed.
+constexpr int PRE_GENERIC_MAX_K = 8;       // largest conv kernel size of the generic kernel (register rows per thread)
 template <int HD, int TT>
 __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams p) {
   extern __shared__ __align__(16) float gsm[];
   const int H = p.H, KV = p.KV, S = p.S;
   const int LAT = H * HD, KVD = KV * HD, C = LAT + KVD, QKV_LD = LAT + 2 * KVD;
-  float* xs = gsm;                        // [TT + 4][C]  q|k columns of tokens t0-4 .. t0+TT-1 (0 before the sequence)
-  float* y1 = xs + (TT + 4) * C;          // [TT + 2][C]  grouped-conv output of tokens t0-2 .. (0 before the sequence)
-  float* y2 = y1 + (TT + 2) * C;          // [TT][C]      dense-conv output of tokens t0 ..
+  const int K = p.ksize, PAD = K - 1;     // causal convs of kernel size K look PAD tokens back (K = 3: the model's)
+  float* xs = gsm;                        // [TT + 2 PAD][C]  q|k columns of tokens t0-2 PAD .. t0+TT-1 (0 before the sequence)
+  float* y1 = xs + (TT + 2 * PAD) * C;    // [TT + PAD][C]    grouped-conv output of tokens t0-PAD .. (0 before the sequence)
+  float* y2 = y1 + (TT + PAD) * C;        // [TT][C]          dense-conv output of tokens t0 ..
   float* mean = y2 + TT * C;              // [TT][2][HD]  0.5 * mean over heads of q0 / of k0 (H != KV only)
   const int tid = threadIdx.x;
   const int tiles_per_seq = (S + TT - 1) / TT;
@@ -339,8 +342,8 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
   const int t0 = (blockIdx.x % tiles_per_seq) * TT;
   const __nv_bfloat16* qkv_b = p.qkv + (size_t)b * S * QKV_LD;
 
-  for (int idx = tid; idx < (TT + 4) * C; idx += 256) {
-    const int r = idx / C, c = idx - r * C, tok = t0 - 4 + r;
+  for (int idx = tid; idx < (TT + 2 * PAD) * C; idx += 256) {
+    const int r = idx / C, c = idx - r * C, tok = t0 - 2 * PAD + r;
     xs[idx] = (tok >= 0 && tok < S) ? __bfloat162float(qkv_b[(size_t)tok * QKV_LD + c]) : 0.f;
   }
   __syncthreads();
@@ -350,20 +353,22 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
 
   // grouped conv: y1[t][c] = sum_j sum_i w1[c][j*HD + i] * x[t-2+j][head(c)*HD + i]
   for (int c = tid; convs && c < C; c += 256) {
-    float acc[TT + 2];
+    float acc[TT + PRE_GENERIC_MAX_K - 1];
 #pragma unroll
-    for (int r = 0; r < TT + 2; ++r) acc[r] = 0.f;
-    const __nv_bfloat16* w = p.w1 + (size_t)c * 3 * HD;
+    for (int r = 0; r < TT + PRE_GENERIC_MAX_K - 1; ++r) acc[r] = 0.f;
+    const __nv_bfloat16* w = p.w1 + (size_t)c * K * HD;
     const int c0 = (c / HD) * HD;
-    for (int j = 0; j < 3; ++j)
+    for (int j = 0; j < K; ++j)
       for (int i = 0; i < HD; ++i) {
         const float wv = __bfloat162float(w[j * HD + i]);
 #pragma unroll
-        for (int r = 0; r < TT + 2; ++r) acc[r] += wv * xs[(r + j) * C + c0 + i];
+        for (int r = 0; r < TT + PRE_GENERIC_MAX_K - 1; ++r)
+          if (r < TT + PAD) acc[r] += wv * xs[(r + j) * C + c0 + i];
       }
 #pragma unroll
-    for (int r = 0; r < TT + 2; ++r)
-      y1[r * C + c] = (t0 - 2 + r >= 0) ? __bfloat162float(__float2bfloat16(acc[r])) : 0.f;   // conv2 pads with zeros
+    for (int r = 0; r < TT + PRE_GENERIC_MAX_K - 1; ++r)
+      if (r < TT + PAD)
+        y1[r * C + c] = (t0 - PAD + r >= 0) ? __bfloat162float(__float2bfloat16(acc[r])) : 0.f;   // conv2 pads with zeros
   }
   __syncthreads();
 
@@ -374,8 +379,8 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
     for (int r = 0; r < TT; ++r) acc[r] = 0.f;
     const bool is_q = c < LAT;
     const int cin = is_q ? LAT : KVD, off = is_q ? 0 : LAT;
-    const __nv_bfloat16* w = is_q ? p.w2q + (size_t)c * 3 * LAT : p.w2k + (size_t)(c - LAT) * 3 * KVD;
-    for (int j = 0; j < 3; ++j)
+    const __nv_bfloat16* w = is_q ? p.w2q + (size_t)c * K * LAT : p.w2k + (size_t)(c - LAT) * K * KVD;
+    for (int j = 0; j < K; ++j)
       for (int ci = 0; ci < cin; ++ci) {
         const float wv = __bfloat162float(w[j * cin + ci]);
 #pragma unroll
@@ -385,12 +390,12 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
     for (int r = 0; r < TT; ++r) y2[r * C + c] = acc[r];
   }
   if (!convs)                               // no convolutions: q and k go on as projected
-    for (int idx = tid; idx < TT * C; idx += 256) y2[idx] = xs[4 * C + idx];
+    for (int idx = tid; idx < TT * C; idx += 256) y2[idx] = xs[2 * PAD * C + idx];
   // QK-mean vectors from the un-convolved q0 / k0 of each token
   if (H != KV && couple_on) {
     for (int idx = tid; idx < TT * 2 * HD; idx += 256) {
       const int r = idx / (2 * HD), which = (idx / HD) & 1, d = idx % HD;
-      const float* row = xs + (r + 4) * C;
+      const float* row = xs + (r + 2 * PAD) * C;
       float sum = 0.f;
       if (which == 0) { for (int h = 0; h < H; ++h) sum += row[h * HD + d]; sum *= 0.5f / (float)H; }
       else            { for (int h = 0; h < KV; ++h) sum += row[LAT + h * HD + d]; sum *= 0.5f / (float)KV; }
@@ -407,7 +412,7 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
     const bool is_q = hh < H;
     const int h = is_q ? hh : hh - H;
     const int c0 = is_q ? h * HD : LAT + h * HD;
-    const float* x0 = xs + (r + 4) * C;
+    const float* x0 = xs + (r + 2 * PAD) * C;
     float v[HD];
     float ss = 0.f;
 #pragma unroll
@@ -444,7 +449,8 @@ __global__ void __launch_bounds__(256) ccgqa_pre_generic_kernel(const PreParams 
 template <int HD>
 static int launch_pre_generic(const PreParams& p, cudaStream_t st) {
   const size_t C = (size_t)(p.H + p.KV) * HD;
-  auto bytes = [&](int tt) { return ((size_t)(3 * tt + 6) * C + (size_t)tt * 2 * HD) * sizeof(float); };
+  const int pad = p.ksize - 1;
+  auto bytes = [&](int tt) { return ((size_t)(3 * tt + 3 * pad) * C + (size_t)tt * 2 * HD) * sizeof(float); };
   if (bytes(16) <= 200 * 1024) {
     auto kern = ccgqa_pre_generic_kernel<HD, 16>;
     HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, bytes(16)));
@@ -470,8 +476,10 @@ using namespace hb200;
 
 static int pre_attention(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k, const float* cos_t,
                          const float* sin_t, const float* key_temperature, void* q, void* k, void* v, int B, int S, int H,
-                         int KV, int hd, int disable, int32_t* err_flag, void* stream) {
+                         int KV, int hd, int disable, int conv_ksize, int32_t* err_flag, void* stream) {
   HB_REQUIRE(qkv && q && k && v, HB200_ERR_INVALID, "ccgqa_pre_attention: null pointer");
+  HB_REQUIRE(conv_ksize >= 1 && conv_ksize <= PRE_GENERIC_MAX_K, HB200_ERR_UNSUPPORTED,
+             "ccgqa_pre_attention: conv kernel size %d not built (1 .. %d)", conv_ksize, PRE_GENERIC_MAX_K);
   HB_REQUIRE((disable & ~HB200_ATTN_NO_ALL) == 0, HB200_ERR_INVALID, "ccgqa_pre_attention: unknown switch bits %d", disable);
   HB_REQUIRE((disable & HB200_ATTN_NO_CONVS) || (w1_qk && w2_q && w2_k), HB200_ERR_INVALID,
              "ccgqa_pre_attention: null conv weights");
@@ -487,8 +495,9 @@ static int pre_attention(const void* qkv, const void* w1_qk, const void* w2_q, c
   const int lat = H * hd, kvd = KV * hd;
   PreParams p{(const __nv_bfloat16*)qkv, (const __nv_bfloat16*)w1_qk, (const __nv_bfloat16*)w2_q,
               (const __nv_bfloat16*)w2_k, cos_t, sin_t, key_temperature, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
-              (__nv_bfloat16*)v, B, S, H, KV, disable};
+              (__nv_bfloat16*)v, B, S, H, KV, disable, conv_ksize};
   cudaStream_t st = (cudaStream_t)stream;
+  if (conv_ksize != 3) disable |= 1 << 30;     // any other kernel size: CUDA-core kernel (bit 30 only steers the dispatch below)
   if (disable == 0) {
     // tcgen05 kernel for the 250M-class shapes; HB200_ERR_UNSUPPORTED means "not this shape", anything else is final
     const int rc = launch_ccgqa_pre_tc(qkv, w1_qk, w2_q, w2_k, cos_t, sin_t, key_temperature, q, k, v, B, S, H, KV, hd,
@@ -529,13 +538,14 @@ extern "C" int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, con
                                          const float* cos_t, const float* sin_t, const float* key_temperature, void* q,
                                          void* k, void* v, int B, int S, int H, int KV, int hd, int32_t* err_flag,
                                          void* stream) {
-  return pre_attention(qkv, w1_qk, w2_q, w2_k, cos_t, sin_t, key_temperature, q, k, v, B, S, H, KV, hd, 0, err_flag, stream);
+  return pre_attention(qkv, w1_qk, w2_q, w2_k, cos_t, sin_t, key_temperature, q, k, v, B, S, H, KV, hd, 0, 3, err_flag,
+                       stream);
 }
 
 extern "C" int hb200_ccgqa_pre_attention_ablated(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k,
                                                  const float* cos_t, const float* sin_t, const float* key_temperature,
                                                  void* q, void* k, void* v, int B, int S, int H, int KV, int hd,
-                                                 int disable, int32_t* err_flag, void* stream) {
-  return pre_attention(qkv, w1_qk, w2_q, w2_k, cos_t, sin_t, key_temperature, q, k, v, B, S, H, KV, hd, disable, err_flag,
-                       stream);
+                                                 int disable, int conv_ksize, int32_t* err_flag, void* stream) {
+  return pre_attention(qkv, w1_qk, w2_q, w2_k, cos_t, sin_t, key_temperature, q, k, v, B, S, H, KV, hd, disable,
+                       conv_ksize, err_flag, stream);
 }

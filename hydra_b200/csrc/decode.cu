@@ -793,9 +793,9 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
                                        size_t workspace_bytes, void* last_logits, int64_t ld_logits, int32_t* err,
                                        void* stream) {
   HB_REQUIRE(m && m->blocks && ds && workspace, HB200_ERR_INVALID, "decode_step: null pointer");
-  HB_REQUIRE(m->attn_disable == 0, HB200_ERR_UNSUPPORTED,
-             "decode_step: attention stages switched off (attn_disable = %d) are not built for the cached decode",
-             m->attn_disable);
+  HB_REQUIRE(m->attn_disable == 0 && (m->conv_ksize == 0 || m->conv_ksize == 3), HB200_ERR_UNSUPPORTED,
+             "decode_step: attention stages switched off (attn_disable = %d) or conv kernel size %d are not built for the "
+             "cached decode", m->attn_disable, m->conv_ksize);
   HB_REQUIRE(!(m->adaptive && m->mor_rampup > 0.f && m->mor_rampup < 1.f), HB200_ERR_UNSUPPORTED,
              "decode_step: the MoR ramp-up blend is built for the forward / prefill only");
   HB_REQUIRE(ds->kcache && ds->vcache && ds->halo && ds->vshift && ds->scores && ds->pos && ds->tokens,

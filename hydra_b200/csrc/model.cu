@@ -55,14 +55,14 @@ __global__ void interleave_gate_up_kernel(const __nv_bfloat16* __restrict__ w, _
       *reinterpret_cast<const uint4*>(w + (size_t)srow * K + piece * 8);
 }
 
-// Conv1d weight [Cout, Cin, 3] -> [Cout, 3*Cin] with (co, j*Cin + ci) = w[co, ci, j]
+// Conv1d weight [Cout, Cin, K] -> [Cout, K*Cin] with (co, j*Cin + ci) = w[co, ci, j]
 __global__ void repack_conv_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ o, int cout,
-                                   int cin) {
+                                   int cin, int ks) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)cout * cin * 3) return;
-  const int co = (int)(idx / (3 * cin)), rem = (int)(idx % (3 * cin));
+  if (idx >= (int64_t)cout * cin * ks) return;
+  const int co = (int)(idx / (ks * cin)), rem = (int)(idx % (ks * cin));
   const int j = rem / cin, ci = rem % cin;
-  o[idx] = w[((size_t)co * cin + ci) * 3 + j];
+  o[idx] = w[((size_t)co * cin + ci) * ks + j];
 }
 
 // ---- workspace ----------------------------------------------------------------------------------------------
@@ -154,7 +154,7 @@ static int attention_part(const hb200_model* m, int bi, const hb200_block_weight
     ProfScope ps(m->profile, st, HB200_K_PRE_ATTENTION, bi, 0, T, nq, 0);
     HB_PROPAGATE(hb200_ccgqa_pre_attention_ablated(w.qkv, bw.w1_qk, bw.w2_q, bw.w2_k, m->rope_cos, m->rope_sin,
                                                    bw.key_temperature, w.q, w.k, w.v, B, S, H, KV, hd, m->attn_disable,
-                                                   err, st));
+                                                   m->conv_ksize ? m->conv_ksize : 3, err, st));
   }
   {
     ProfScope ps(m->profile, st, HB200_K_ATTENTION, bi, 0, T, lat, S);
@@ -460,13 +460,18 @@ extern "C" int hb200_interleave_gate_up(const void* w_gate_up, void* w_out, int 
   return 0;
 }
 
-extern "C" int hb200_repack_conv_weight(const void* w, void* w_out, int c_out, int c_in, void* stream) {
-  HB_REQUIRE(w && w_out && w != w_out && c_out > 0 && c_in > 0, HB200_ERR_INVALID, "repack_conv_weight: bad arguments");
-  const int64_t n = (int64_t)c_out * c_in * 3;
+extern "C" int hb200_repack_conv_weight_k(const void* w, void* w_out, int c_out, int c_in, int ksize, void* stream) {
+  HB_REQUIRE(w && w_out && w != w_out && c_out > 0 && c_in > 0 && ksize >= 1, HB200_ERR_INVALID,
+             "repack_conv_weight: bad arguments");
+  const int64_t n = (int64_t)c_out * c_in * ksize;
   repack_conv_kernel<<<(unsigned)ceil_div64(n, 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)w, (__nv_bfloat16*)w_out, c_out, c_in);
+      (const __nv_bfloat16*)w, (__nv_bfloat16*)w_out, c_out, c_in, ksize);
   HB_LAUNCH_CHECK();
   return 0;
+}
+
+extern "C" int hb200_repack_conv_weight(const void* w, void* w_out, int c_out, int c_in, void* stream) {
+  return hb200_repack_conv_weight_k(w, w_out, c_out, c_in, 3, stream);
 }
 
 extern "C" size_t hb200_model_workspace_bytes(const hb200_model* m, int B, int S) {
@@ -652,9 +657,9 @@ extern "C" int hb200_model_prefill_cached(const hb200_model* m, const int64_t* i
   HB_REQUIRE(state->batch == B && state->capacity >= S && state->capacity <= m->max_seq_len, HB200_ERR_INVALID,
              "prefill_cached: state is for batch %d / capacity %d (need batch %d, %d <= capacity <= %d)", state->batch,
              state->capacity, B, S, m->max_seq_len);
-  HB_REQUIRE(m->attn_disable == 0, HB200_ERR_UNSUPPORTED,
-             "prefill_cached: attention stages switched off (attn_disable = %d) are not built for the cached decode",
-             m->attn_disable);
+  HB_REQUIRE(m->attn_disable == 0 && (m->conv_ksize == 0 || m->conv_ksize == 3), HB200_ERR_UNSUPPORTED,
+             "prefill_cached: attention stages switched off (attn_disable = %d) or conv kernel size %d are not built for "
+             "the cached decode", m->attn_disable, m->conv_ksize);
   HB_REQUIRE(ld_logits >= m->vocab && ld_logits % 8 == 0, HB200_ERR_INVALID, "prefill_cached: bad ld_logits");
   HB_REQUIRE(m->dim % 8 == 0, HB200_ERR_UNSUPPORTED, "prefill_cached: dim must be a multiple of 8");
   Workspace w = carve(m, B, S, workspace);

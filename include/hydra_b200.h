@@ -117,6 +117,8 @@ int hb200_interleave_gate_up(const void* w_gate_up, void* w_out, int F, int K, v
 /* Repack Conv1d weights [C, C/groups, 3] (kernels/fused_conv.py:22-37) to [C, 3*(C/groups)]
  * with element (c_out, j*cin + c_in) = w[c_out, c_in, j], bf16 -> bf16. */
 int hb200_repack_conv_weight(const void* w, void* w_out, int c_out, int c_in, void* stream);
+/* The same for kernel size ksize: [C, C/groups, ksize] -> [C, ksize*(C/groups)]. */
+int hb200_repack_conv_weight_k(const void* w, void* w_out, int c_out, int c_in, int ksize, void* stream);
 
 /* Everything between qkv_proj and SDPA in one kernel (attention.py:208-266,
  * kernels/fused_conv.py:39-62): value shift, grouped k=3 causal conv, dense k=3 causal conv,
@@ -137,8 +139,11 @@ int hb200_ccgqa_pre_attention(const void* qkv, const void* w1_qk, const void* w2
  * use_qk_mean=, use_value_shift=), attention.py:74-160, 211-266): `disable` is a mask of the bits below; 0 is
  * hb200_ccgqa_pre_attention.  Without convolutions q and k go on as projected (conv weights may be NULL); without the
  * QK norm neither the L2 normalisation nor the key temperature is applied (key_temperature may be NULL); without RoPE
- * the tables may be NULL; without the value shift v is the last kv_dim columns of qkv.  Any switched-off stage selects
- * the CUDA-core kernel (the reference's models never switch one off: these are its ablation switches). */
+ * the tables may be NULL; without the value shift v is the last kv_dim columns of qkv.  conv_ksize is the module's
+ * conv_kernel_size (1 .. 8; weights repacked with hb200_repack_conv_weight_k: w1_qk [lat+kvd, ksize*hd], w2_q
+ * [lat, ksize*lat], w2_k [kvd, ksize*kvd]; each conv pads ksize-1 zeros on the left).  Any switched-off stage, and any
+ * kernel size other than 3, selects the CUDA-core kernel (the reference's models never do either: these are its
+ * ablation switches). */
 enum {
   HB200_ATTN_NO_ROPE = 1, HB200_ATTN_NO_QK_NORM = 2, HB200_ATTN_NO_CONVS = 4, HB200_ATTN_NO_QK_MEAN = 8,
   HB200_ATTN_NO_VALUE_SHIFT = 16, HB200_ATTN_NO_ALL = 31
@@ -146,7 +151,7 @@ enum {
 int hb200_ccgqa_pre_attention_ablated(const void* qkv, const void* w1_qk, const void* w2_q, const void* w2_k,
                                       const float* cos_t, const float* sin_t, const float* key_temperature,
                                       void* q, void* k, void* v, int B, int S, int H, int KV, int hd, int disable,
-                                      int32_t* err_flag, void* stream);
+                                      int conv_ksize, int32_t* err_flag, void* stream);
 
 /* Causal grouped-query attention in the latent space (attention.py:288-327):
  * o[b,t,h,:] = softmax_causal(q[b,h] k[b,h/(H/KV)]^T * scale) v[b,h/(H/KV)].
@@ -271,6 +276,9 @@ typedef struct hb200_model {
                                      reference's ablation switches).  0 for every model the reference builds; non-zero is
                                      honoured by hb200_ccgqa_forward[_masked] / hb200_block_forward / hb200_model_forward
                                      and refused by the cached decode. */
+  int32_t conv_ksize;             /* conv kernel size of the attention modules (conv_kernel_size, attention.py:86); 0 means 3,
+                                     the value of every model the reference builds.  Other sizes (1 .. 8) run the CUDA-core
+                                     pre-attention kernel and are refused by the cached decode. */
 } hb200_model;
 
 /* Optional routing taps / forced routing for one forward (device pointers or NULL). */

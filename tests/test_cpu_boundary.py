@@ -97,7 +97,10 @@ def test_factory_builds_module_with_reference_parameter_layout(monkeypatch):
     assert set(m3.state_dict()) == {"qkv_proj.weight", "o_proj.weight", "key_temperature"}
     with pytest.raises(NotImplementedError):
         build_hybrid_attention_module("ccqa", dim=512, n_heads=8, n_kv_heads=2, max_seq_len=64, compression_factor=4,
-                                      attention_kwargs={"conv_kernel_size": 5})
+                                      attention_kwargs={"conv_kernel_size": 9})
+    m4 = build_hybrid_attention_module("ccqa", dim=512, n_heads=8, n_kv_heads=2, max_seq_len=64, compression_factor=4,
+                                       attention_kwargs={"conv_kernel_size": 5})
+    assert tuple(m4.q_conv.conv1.weight.shape) == (128, 16, 5) and tuple(m4.k_conv.conv2.weight.shape) == (32, 32, 5)
 
 
 def test_legacy_checkpoint_layouts_are_remapped():

@@ -276,15 +276,17 @@ def test_masked_attention_core(L, hd, H, KV, S, mode):
 
 
 def test_module_with_stages_switched_off_matches_the_reference_output():
-    """The factory's use_* arguments (the reference's ablation switches): each stage off in turn, two off, all off - the
-    module against the reference module built the same way, a padding mask on top of one of them, and the cached
-    decode's refusal at model level is a C-side check (attn_disable)."""
+    """The factory's use_* arguments (the reference's ablation switches) and conv_kernel_size: each stage off in turn, two
+    off, all off, kernel sizes 2 and 5 - the module against the reference module built the same way, and a padding mask
+    on top of one of them."""
     from hydra_b200.attention import build_hybrid_attention_module
     fx, cfg, variants = G.ablated_attention_fixture("ccgqa_ablated.npz")
     x = G.tensor(fx["x"])
     stages = ["rope", "qk_norm", "convs", "qk_mean", "value_shift"]
     for off, w, ref in variants:
         kw = {f"use_{s}": (s not in off) for s in stages}
+        if "convs" not in off:
+            kw["conv_kernel_size"] = w["attn.q_conv.conv1.weight"].shape[-1]
         m = build_hybrid_attention_module("ccgqa", dim=cfg.dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads,
                                           max_seq_len=cfg.max_seq_len, compression_factor=4, attention_kwargs=kw)
         m.load_state_dict({k[len("attn."):]: v for k, v in w.items()}, strict=True)
@@ -293,10 +295,11 @@ def test_module_with_stages_switched_off_matches_the_reference_output():
         y = m(x.to(torch.bfloat16).cuda())
         m._packed.check_device_errors()
         r, a = rel_l2(y, ref), max_abs(y, ref)
-        print(f"off {off}: rel_l2 {r:.3e} max_abs {a:.3e} (ref range {float(ref.abs().max()):.3g})")
+        print(f"off {off} conv kernel size {kw.get('conv_kernel_size')}: rel_l2 {r:.3e} max_abs {a:.3e} (ref range {float(ref.abs().max()):.3g})")
         assert r < 1e-2 and a < 0.03 * float(ref.abs().max()), f"off {off}"
     # a padding mask and switched-off stages together, against the oracle
-    off, w, _ = variants[-2]
+    off, w, _ = variants[5]
+    assert off == ("convs", "qk_mean")
     mask = torch.ones(x.shape[:2], dtype=torch.int64)
     mask[0, -5:] = 0
     kw = {f"use_{s}": (s not in off) for s in stages}
@@ -310,4 +313,4 @@ def test_module_with_stages_switched_off_matches_the_reference_output():
     with pytest.raises(NotImplementedError):
         build_hybrid_attention_module("ccgqa", dim=cfg.dim, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads,
                                       max_seq_len=cfg.max_seq_len, compression_factor=4,
-                                      attention_kwargs={"conv_kernel_size": 5})
+                                      attention_kwargs={"conv_kernel_size": 9})
