@@ -511,9 +511,9 @@ class HydraB200Model:
         if self.adaptive and 0.0 < getattr(self, "mor_rampup_scale", 1.0) < 1.0:
             raise NotImplementedError("cached decode is not built for a MoR ramp-up scale between 0 and 1 "
                                       "(use mode='reforward')")
-        if getattr(self, "attn_disable", 0):
-            raise NotImplementedError("cached decode is not built for attention modules with a stage switched off "
-                                      "(use mode='reforward')")
+        if getattr(self, "attn_disable", 0) or self.packed.blocks[0].conv_ksize != 3:
+            raise NotImplementedError("cached decode is not built for attention modules with a stage switched off or a "
+                                      "conv kernel size other than 3 (use mode='reforward')")
         return DecodeSession(self, batch, capacity)
 
     def generate_cached(self, prompt_ids: Tensor, max_new_tokens: int, use_graph: bool = True,
