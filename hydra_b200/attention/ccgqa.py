@@ -136,6 +136,11 @@ class CCGQAAttention(nn.Module):
                                       error_msgs)
 
     def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if torch.is_grad_enabled() and x.requires_grad:
+            # the kernels are forward-only and the result carries no grad_fn: a training step through this module would
+            # silently get zero gradient for everything upstream of it
+            raise RuntimeError("hydra_b200 CCGQAAttention is inference only (no autograd through its kernels): wrap the "
+                               "call in torch.no_grad(), or uninstall() before training")
         if not x.is_cuda:
             raise RuntimeError("hydra_b200 CCGQAAttention runs on CUDA tensors only (there is no CPU fallback)")
         B, S, D = x.shape

@@ -207,6 +207,45 @@ def normalize_state_dict(obj) -> Dict[str, Tensor]:
     return out
 
 
+_BLOCK_KEYS = (
+    "attention.qkv_proj.weight", "attention.o_proj.weight", "attention.q_conv.conv1.weight",
+    "attention.q_conv.conv2.weight", "attention.k_conv.conv1.weight", "attention.k_conv.conv2.weight",
+    "attention.key_temperature", "norm1.weight", "norm2.weight", "final_norm.weight", "mlp.gate_up.weight",
+    "mlp.down.weight", "mor_router.router.weight", "mor_router.router.bias", "mor_executor.recursion_bias",
+    "mor_executor.recursion_embed.weight", "mod_mlp_wrapper.mod_router.router.weight",
+    "mod_mlp_wrapper.mod_router.router.bias")
+# RoPE tables / masks that older checkpoints saved; recomputed here
+_IGNORED_SUFFIXES = ("cos_cached", "sin_cached", "causal_mask")
+
+
+def check_state_dict_is_consumed(sd: Dict[str, Tensor]) -> None:
+    """Refuse weights this executor would silently drop.  A reference model built with ``moe_enabled`` runs its
+    ``moe_layers`` after the scheduled blocks (model.py:431-503); the MoE feed-forward is not part of this backend, so a
+    state_dict that carries ``moe_layers.*`` would give plausible but wrong logits.  Any other key that no kernel reads is
+    reported the same way."""
+    moe = sorted(k for k in sd if k.startswith("moe_layers.") or ".moe_layers." in k)
+    if moe:
+        raise NotImplementedError(
+            f"the state_dict carries {len(moe)} mixture-of-experts tensors ({moe[0]} ...): HydraModel(moe_enabled=True) "
+            "runs those layers inside its forward and this backend does not implement them")
+    unknown = []
+    for k in sd:
+        if k in ("tok_emb.weight", "norm.weight", "output.weight"):
+            continue
+        # bookkeeping buffers of the reference (step counters, routing statistics, the loss tracker's running means):
+        # every one of them is registered under a name with a leading underscore, no parameter is
+        if k.endswith(_IGNORED_SUFFIXES) or k.rsplit(".", 1)[-1].startswith("_"):
+            continue
+        if k.startswith("layers."):
+            rest = k.split(".", 2)[2] if k.count(".") >= 2 else ""
+            if rest in _BLOCK_KEYS:
+                continue
+        unknown.append(k)
+    if unknown:
+        raise KeyError(f"state_dict keys that this backend does not consume (refusing to drop them silently): "
+                       f"{sorted(unknown)[:8]}{' ...' if len(unknown) > 8 else ''}")
+
+
 def _untied_output(sd: Dict[str, Tensor], dev) -> Optional[Tensor]:
     """bf16 copy of an untied output projection left in a normalised state_dict, or None when the projection is tied."""
     o = sd.get("output.weight")
@@ -253,6 +292,7 @@ class HydraB200Model:
         if dev.index is None:
             dev = torch.device("cuda", torch.cuda.current_device())
         sd = normalize_state_dict(state_dict)
+        check_state_dict_is_consumed(sd)
         V, D = sd["tok_emb.weight"].shape
         nb = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("layers."))
         R = sd["layers.0.mor_executor.recursion_embed.weight"].shape[0]
@@ -304,6 +344,10 @@ class HydraB200Model:
     def reference_kwargs(model) -> dict:
         """Constructor arguments read off a reference ``HydraModel`` instance: shape attributes, routing settings, and
         the curriculum state its blocks are in (static routing, MoR ramp-up scale)."""
+        if getattr(model, "moe_enabled", False) and len(getattr(model, "moe_layers", ())) > 0:
+            raise NotImplementedError("this HydraModel was built with moe_enabled=True: its forward runs "
+                                      f"{len(model.moe_layers)} mixture-of-experts layers (model.py:431-503) that this "
+                                      "backend does not implement")
         # MoD hard routing is on only once the wrapper's warm-up has passed (blocks.py:140,162-186: `_mod_enabled`, set
         # by set_global_step); before that every token goes through the MLP, which is capacity 1.0 here
         wrappers = [l.mod_mlp_wrapper for l in model.layers if getattr(l, "mod_mlp_wrapper", None) is not None]
@@ -339,9 +383,12 @@ class HydraB200Model:
                     block_out=torch.zeros((NB, T, self.dim), dtype=torch.bfloat16, device=d) if block_out else None)
 
     def forward(self, ids: Tensor, mask: Optional[Tensor] = None, return_losses: bool = False, *, taps: bool = False,
-                forced: Optional[Taps] = None, block_out: bool = False, logits: bool = True, hidden: bool = False):
+                forced: Optional[Taps] = None, block_out: bool = False, logits: bool = True, hidden: bool = False,
+                reuse_buffer: bool = False):
         """ids int64 [B, S] on this model's device -> logits bf16 [B, S, vocab] (a view of a buffer whose rows are
-        padded to a multiple of 8 columns; the buffer is reused by the next call with the same shape).
+        padded to a multiple of 8 columns).  Every call returns a tensor of its own, as the reference does;
+        ``reuse_buffer=True`` writes into one buffer kept by the model instead (the next such call of the same shape
+        overwrites it) - for benchmark and generation loops that want no allocation per step.
 
         ``mask`` is accepted and ignored, exactly as the reference does: ``HydraModel.forward(x, mask)`` hands it to
         its blocks, and both block types drop it before the attention call (blocks.py:645-657, model.py:143-159).
@@ -362,11 +409,13 @@ class HydraB200Model:
         ws = pm.workspace(B, S)
         T = B * S
         out = None
-        if logits:
+        if logits and reuse_buffer:
             if self._logits is None or self._logits.shape[0] != T:
                 self._logits = None
                 self._logits = torch.empty((T, self.ld_logits), dtype=torch.bfloat16, device=self.device)
             out = self._logits
+        elif logits:
+            out = torch.empty((T, self.ld_logits), dtype=torch.bfloat16, device=self.device)
         hid = torch.empty((T, self.dim), dtype=torch.bfloat16, device=self.device) if hidden else None
         tp = None
         tstruct = None
@@ -415,8 +464,9 @@ class HydraB200Model:
         if tuple(targets.shape) != tuple(ids.shape):
             raise ValueError("targets must have the shape of ids")
         B, S = ids.shape
-        self.forward(ids)
-        nll = cross_entropy_rows(self._logits, targets.to(self.device).reshape(-1), vocab=self.vocab_size,
+        lg = self.forward(ids)
+        padded = lg.as_strided((B * S, self.ld_logits), (self.ld_logits, 1))      # the rows with their padding columns
+        nll = cross_entropy_rows(padded, targets.to(self.device).reshape(-1), vocab=self.vocab_size,
                                  ignore_index=ignore_index)
         if reduction == "none":
             return nll.view(B, S)
@@ -442,7 +492,7 @@ class HydraB200Model:
         forward (all logits are computed and stay resident in HBM), and returns the last position's logits
         [B, vocab] in host memory - what a decoder needs next."""
         ids = ids_host.to(self.device, non_blocking=True)
-        lg = self.forward(ids)
+        lg = self.forward(ids, reuse_buffer=True)
         last = lg[:, -1, :]
         if out_host is None:
             out_host = torch.empty(last.shape, dtype=last.dtype, pin_memory=True)
@@ -612,6 +662,7 @@ class HydraB200BaseModel(HydraB200Model):
         if dev.index is None:
             dev = torch.device("cuda", torch.cuda.current_device())
         sd = normalize_state_dict(state_dict)
+        check_state_dict_is_consumed(sd)
         V, D = sd["tok_emb.weight"].shape
         nb = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("layers."))
         F = sd["layers.0.mlp.down.weight"].shape[1]

@@ -227,3 +227,58 @@ def test_end_of_text_padding_of_generated_sequences():
     assert out.tolist() == [[9, 2, 3, 9, 9, 9], [1, 2, 7, 7, 9, 9], [1, 2, 3, 4, 5, 6]]
     assert torch.equal(_pad_after_eos(s.clone(), 2, None), s)
     assert torch.equal(_pad_after_eos(s.clone(), 6, 9), s)
+
+
+def _tiny_state_dict():
+    from oracle import hydra_oracle as O
+    cfg = O.HydraConfig(vocab_size=32, dim=64, n_mor_blocks=3, recursions_per_block=2, n_heads=2, n_kv_heads=1,
+                        max_seq_len=16, mod_capacity=0.5)
+    return O.init_params(cfg, seed=0)
+
+
+def test_weights_that_no_kernel_reads_are_refused():
+    """A reference model built with moe_enabled runs its moe_layers inside the forward (model.py:431-503); this backend has
+    no such layers, so a state_dict that carries them - or any other tensor it would drop - is refused, not half-loaded."""
+    from hydra_b200.model import check_state_dict_is_consumed, normalize_state_dict
+    sd = normalize_state_dict(_tiny_state_dict())
+    check_state_dict_is_consumed(sd)                                            # a plain model passes
+    ok = dict(sd)
+    ok["layers.1.mod_mlp_wrapper.mod_router._aux_loss"] = torch.zeros(())       # bookkeeping buffers are not weights
+    ok["loss_baseline._ema"] = torch.zeros(())
+    ok["layers.0.attention.cos_cached"] = torch.zeros(1, 1, 16, 16)
+    check_state_dict_is_consumed(ok)
+    moe = dict(sd)
+    moe["moe_layers.0.moe.experts.0.gate_up.weight"] = torch.zeros(8, 64)
+    with pytest.raises(NotImplementedError, match="mixture-of-experts"):
+        check_state_dict_is_consumed(moe)
+    stray = dict(sd)
+    stray["layers.0.adapter.weight"] = torch.zeros(4, 4)
+    with pytest.raises(KeyError, match="adapter"):
+        check_state_dict_is_consumed(stray)
+
+
+def test_reference_instance_with_moe_layers_is_refused():
+    from hydra_b200.model import HydraB200Model
+
+    class FakeRef:
+        moe_enabled = True
+        moe_layers = [object(), object()]
+        layers = []
+
+    with pytest.raises(NotImplementedError, match="moe_enabled"):
+        HydraB200Model.reference_kwargs(FakeRef())
+    with pytest.raises(NotImplementedError, match="moe_enabled"):
+        HydraB200Model.from_reference(FakeRef())
+
+
+def test_attention_module_refuses_a_training_call():
+    """The module's kernels are forward-only; an input that carries a gradient would silently get none back."""
+    from hydra_b200.attention import build_hybrid_attention_module
+    m = build_hybrid_attention_module("ccqa", dim=512, n_heads=8, n_kv_heads=2, max_seq_len=16, compression_factor=4,
+                                      attention_kwargs={})
+    x = torch.zeros(1, 4, 512, requires_grad=True)
+    with pytest.raises(RuntimeError, match="inference only"):
+        m(x)
+    with torch.no_grad():                       # under no_grad the refusal that applies is the CPU one
+        with pytest.raises(RuntimeError, match="CUDA"):
+            m(x)
