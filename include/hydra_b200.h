@@ -372,11 +372,18 @@ int hb200_model_decode_step(const hb200_model* m, const hb200_decode_state* stat
  * (bf16 [B*S, dim] each, 16-byte aligned).
  *
  * Limits and rules:
- *   - B*S tokens must fit: B*S*2*(2*latent + 3*kv_dim) bytes (rounded up per buffer to 256) <= 8 MiB, i.e. 4096
- *     tokens at dim 1024 with 8q/2kv heads; larger requests return HB200_ERR_WORKSPACE and launch nothing
- *     (hb200_ccgqa_forward_static_max_bytes() reports the capacity);
- *   - the first call on each device resolves the array's device address (cudaGetSymbolAddress, with that device
- *     current); make that first call outside any stream capture;
+ *   - B*S tokens must fit: qkv (latent + 2*kv_dim) + q (latent) + k (kv_dim) + v (kv_dim) + o (latent) columns of
+ *     bf16 per token, i.e. B*S*2*(3*latent + 4*kv_dim) bytes (each of the five buffers rounded up to 256) <= 8 MiB:
+ *     4096 tokens at dim 1024 with 8q/2kv heads (latent 256, kv_dim 64: 2048 B per token); larger requests return
+ *     HB200_ERR_WORKSPACE and launch nothing (hb200_ccgqa_forward_static_max_bytes() reports the capacity);
+ *   - the first call on each device is the set-up call: it resolves the array's device address
+ *     (cudaGetSymbolAddress, with that device current), and with CUDA's default lazy module loading that is also the
+ *     moment the driver loads the part of the library that holds the array, so THAT call can take the 8 MiB (plus the
+ *     kernels' code) from the device and can fail with HB200_ERR_CUDA if the device has nothing left.  Only the calls
+ *     after it are allocation-free.  Make the set-up call once at start-up, while memory can still be had, and
+ *     outside any stream capture;
+ *   - the resolved address is remembered per device for the life of the process; cudaDeviceReset invalidates it, so
+ *     a process that resets a device must not use this entry point on that device afterwards;
  *   - all calls on one device share the one array and it keeps the previous call's contents.  Every byte a call
  *     reads it has written first, so nothing needs clearing, but two calls that overlap on the GPU (different
  *     streams) race on it: serialise them. */

@@ -28,14 +28,20 @@ def _module(dim, H, KV, S):
     return m.cuda()
 
 
-def _run_static(L, pm, x, B, S):
+def _run_static(L, pm, x, B, S, check_device_free=False):
     y = torch.full_like(x, float("nan"))
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before = torch.cuda.mem_get_info()[0]
     st = L.lib().hb200_ccgqa_forward_static(C.byref(pm.struct), 0, x.data_ptr(), y.data_ptr(), B, S,
                                            pm.err_flag.data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert torch.cuda.memory_allocated() == before, "the call must not allocate through torch either"
     L.check(st, "ccgqa_forward_static")
     torch.cuda.synchronize()
+    if check_device_free:
+        # what the driver itself reports as free: neither cudaMalloc nor a lazily loaded module may have taken any
+        # (the first call on a device is the set-up call and is allowed to; this is asked of the calls after it)
+        assert torch.cuda.mem_get_info()[0] == free_before, "a call after the set-up call took device memory"
     return y
 
 
@@ -49,7 +55,7 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(dim, H, KV, B,
     ref1, ref2 = m(x1).clone(), m(x2).clone()          # hb200_ccgqa_forward with a torch-allocated workspace
     pm = m._packed
     y1 = _run_static(L, pm, x1, B, S)                  # first call on this device also resolves the array address
-    y2 = _run_static(L, pm, x2, B, S)                  # second call: the array still holds the first call's data
+    y2 = _run_static(L, pm, x2, B, S, check_device_free=True)   # second call: the array still holds the first call's data
     pm.check_device_errors()
     assert torch.isfinite(y1.float()).all() and torch.isfinite(y2.float()).all()
     assert torch.equal(y1, ref1), "first call differs from the workspace-based entry point"
