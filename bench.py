@@ -4,7 +4,8 @@
     python bench.py --gpus 1 --steps K --warmup W
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
-    python bench.py --impl reference ...      # the CPU arm: the oracle port of the reference's eager forward
+    python bench.py --impl reference ...      # the CPU arm: the reference's own HydraModel.forward on the host cores
+                                              # (from oracle/_ref; the CPU restatement when that is absent)
 
 Workload (the HYDRA-250M prefill benchmark configuration): dim 1024, 10 MoR blocks x 4 recursions, CCGQA 4x compression with 8 query /
 2 KV heads (head_dim 32), SwiGLU hidden 2816, MoD top-k at 75% capacity in the interior blocks, vocab 50257, tied
@@ -19,6 +20,13 @@ One step = one full forward (embedding -> 10 blocks -> final norm -> all 65536 x
   roofline  the dominant kernel (tcgen05 gate_up GEMM with the SwiGLU epilogue): FLOPs actually routed to it
             divided by its summed launch time, both measured in the timed steps with CUDA events recorded by
             the executor around every launch
+  parity    outside the timed region: sequence 0 of the batch that was timed against the CPU oracle with the GPU's
+            routing replayed (sequences are independent bit for bit, so one speaks for the batch)
+  ccgqa_block  outside the timed region: the CCGQA-block microbenchmark (8 x 2048 x 1024) and its fused pre-attention
+            kernel against their rooflines - the second half of the headline metric
+  library_baseline  outside the timed region: the library calls the reference makes on a GPU (cuBLAS F.linear, SDPA,
+            cuDNN Conv1d, its bf16 eager model) timed on this GPU beside this package's kernels at the same shapes
+  strong    N > 1 only: the same model on a global batch of 32 sequences split over the ranks
 """
 from __future__ import annotations
 
@@ -163,6 +171,47 @@ def cpu_forward_tokens_per_s(n_seq: int, steps: int, warmup: int, state_dict=Non
     return n_seq * SEQ / dt, dt, threads
 
 
+REF_ARGS = dict(vocab_size=ARCH["vocab_size"], dim=ARCH["dim"], n_mor_blocks=ARCH["n_mor_blocks"],
+                recursions_per_block=ARCH["recursions_per_block"], n_heads=ARCH["n_heads"], n_kv_heads=ARCH["n_kv_heads"],
+                compression_factor=ARCH["compression_factor"], max_seq_len=SEQ, mod_capacity=ARCH["mod_capacity"])
+
+
+def reference_available() -> bool:
+    from oracle import build_ref
+    return build_ref.add_ref_to_path()
+
+
+def reference_forward_tokens_per_s(n_seq: int, steps: int, warmup: int) -> tuple[float, float, int]:
+    """The reference's own eager fp32 HydraModel.forward (hydra/model/framework/model.py:408-506; the unmodified package
+    under oracle/_ref) on the host, all host threads; seeded random-init weights of the benchmarked architecture
+    (its own initialiser).  Returns (tok/s, s/step, threads)."""
+    from oracle import build_ref
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(threads)
+    model = build_ref.reference_model(seed=SEED, **REF_ARGS)
+    ids = torch.randint(0, ARCH["vocab_size"], (n_seq, SEQ), generator=torch.Generator().manual_seed(SEED))
+    for _ in range(warmup):
+        build_ref.reference_forward(model, ids)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        build_ref.reference_forward(model, ids)
+    dt = (time.perf_counter() - t0) / max(1, steps)
+    return n_seq * SEQ / dt, dt, threads
+
+
+def cpu_arm(n_seq: int, steps: int, warmup: int, state_dict=None) -> dict:
+    """cpu_baseline record: the reference itself when oracle/_ref is there, else the CPU restatement (labelled)."""
+    if reference_available():
+        tps, dt, threads = reference_forward_tokens_per_s(n_seq, steps, warmup)
+        kind, what = "reference", "the reference's own HydraModel.forward, eager fp32 (unmodified package, oracle/_ref)"
+    else:
+        tps, dt, threads = cpu_forward_tokens_per_s(n_seq, steps, warmup, state_dict)
+        kind, what = "port", "CPU restatement of the reference's eager fp32 forward (oracle/_ref has not been built)"
+    return {"value": tps, "unit": "tok/s", "cores": threads, "kind": kind, "s_per_step": dt,
+            "sample": f"{n_seq} sequence x {SEQ} tokens of the same workload per step, {steps} timed step(s) after "
+                      f"{warmup} warm-up; {what}"}
+
+
 def cpu_generation_baseline(blocks: int, prompt: int) -> dict:
     """What the reference does to generate one token (its helper re-runs the whole forward on the sequence so far,
     diagnostics/eval_checkpoint.py:127-160), timed with the oracle port on the host cores at the 1.5B shape:
@@ -191,18 +240,18 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    n_seq = 1
-    tps, dt, threads = cpu_forward_tokens_per_s(n_seq, args.steps, min(args.warmup, 1))
+    n_seq = 1                                   # a bounded sample: one sequence of the workload per step
+    warm = min(args.warmup, 1)
+    base = cpu_arm(n_seq, args.steps, warm)
+    tps, dt = base["value"], base["s_per_step"]
     cfg = workload_config(args.batch, args.gpus)
+    cfg["timed_batch"] = n_seq                  # what one step of THIS arm processes (the workload's batch is above)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": getattr(args, "scaling_mode", "weak"),
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
-        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
-                         "sample": f"{n_seq} sequence x {SEQ} tokens of the same workload per step "
-                                   "(CPU port of the reference's eager fp32 forward; the Python reference itself "
-                                   "cannot travel to the GPU box)"},
+        "cpu_baseline": base,
         "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -226,6 +275,71 @@ def routed_flops(records, mlp_rows, T: int) -> dict:
             f = 0.0
         fl[kd] = fl.get(kd, 0.0) + f
     return fl
+
+
+def parity_record(model, ids_dev, timed_logits_seq0, sd) -> dict:
+    """Sequence 0 of the batch that was timed, against the CPU oracle with the GPU's own routing replayed; also the
+    agreement of the free-running oracle's depth decisions.  Run after the timed region."""
+    from oracle import hydra_oracle as O
+    solo = model(ids_dev[:1], taps=True)
+    tp = model.last_taps
+    same = bool(torch.equal(solo[0], timed_logits_seq0))      # sequence alone == the same sequence inside the batch
+    w = {k: v.to(torch.bfloat16).float().cpu() for k, v in sd.items()}
+    cfg = O.config_from_state_dict(w, n_heads=ARCH["n_heads"], n_kv_heads=ARCH["n_kv_heads"],
+                                   mod_capacity=ARCH["mod_capacity"], max_seq_len=SEQ)
+    NB, R = cfg.n_mor_blocks, cfg.recursions_per_block
+    rt = O.RoutingTaps()
+    d = tp.depths.cpu().long().view(NB, 1, SEQ)
+    idx = tp.mod_idx.cpu().long()
+    for i in range(NB):
+        rt.depths.append(d[i])
+        for r in range(R):
+            rt.mod_indices[(i, r)] = idx[i, r]
+    ids_cpu = ids_dev[:1].cpu()
+    free = O.RoutingTaps()
+    with torch.no_grad():
+        ref_free = O.model_forward(ids_cpu, w, cfg, taps=free)
+        ref = O.model_forward(ids_cpu, w, cfg, forced=rt)
+    lg = solo.float().cpu()
+    agree = [float((d[i] == free.depths[i]).float().mean()) for i in range(NB)]
+    return {"checked": "sequence 0 of the timed batch vs the CPU oracle, GPU routing replayed",
+            "batch_equals_solo_bitwise": same,
+            "rel_l2": float((lg - ref).norm() / ref.norm()), "max_abs": float((lg - ref).abs().max()),
+            "logit_range": float(ref.abs().max()),
+            "free_run_rel_l2": float((lg - ref_free).norm() / ref_free.norm()),
+            "depth_agree_min": min(agree), "depth_agree_mean": sum(agree) / len(agree),
+            "finite": bool(torch.isfinite(lg).all())}
+
+
+def ccgqa_block_record(peaks: dict, iters: int = 20) -> dict:
+    """The CCGQA-block microbenchmark (B=8, S=2048, dim 1024, 8q/2kv heads of 32, temperature 1.0, Xavier weights from
+    seed 1) and its fused pre-attention kernel, timed alone with rotating buffers larger than L2."""
+    import microbench
+    ns = microbench.argparse_like(batch=8, iters=iters, impl=0)
+    blk = microbench.ccgqa_block(ns)
+    pre = microbench.pre_attention(ns)
+    att = microbench.attention(ns)
+    burst, sust, hbm = float(peaks["bf16_tflops"]), float(peaks["bf16_tflops_sustained"]), float(peaks["hbm_gbs"])
+    return {"shape": [8, 2048, 1024], "us": blk["ms"] * 1e3, "gflop": blk["algorithmic_flops"] / 1e9,
+            "tflops": blk["achieved"], "frac_of_burst": blk["achieved"] / burst, "frac_of_sustained": blk["achieved"] / sust,
+            "parts_us": {k: v * 1e3 for k, v in blk["parts_ms"].items()},
+            "pre_attention": {"us": pre["ms"] * 1e3, "algorithmic_mb": pre["algorithmic_bytes"] / 1e6,
+                              "gbs": pre["achieved"], "frac_of_hbm": pre["achieved"] / hbm,
+                              "conv_tflops": pre["conv_tflops"], "conv_frac_of_burst": pre["conv_tflops"] / burst},
+            "attention": {"us": att["ms"] * 1e3, "tflops": att["achieved"], "frac_of_burst": att["achieved"] / burst,
+                          "exp_floor_us": 8 * 8 * 2048 * (2048 / 2 + 64) / (148 * 16 * 1.965e9) * 1e6,
+                          "note": "exp floor = one ex2 per score at 16 per clock per SM, 148 SMs, 1965 MHz"}}
+
+
+def decode_record(peaks: dict, steps: int = 48) -> dict:
+    """Cached greedy decode at the 1.5B shape (dim 2048, 22 blocks x 4 recursions, 32q/4kv heads of 16, SwiGLU 5632),
+    batch 64, prompt 1024: ms per step and the weight + cache stream against the HBM peak."""
+    import microbench
+    ns = microbench.argparse_like(batch=64, blocks=22, prompt=1024, new_tokens=steps + 3, iters=1, impl=0)
+    r = microbench.decode(ns)
+    return {"shape": "1.5B: dim 2048, 22x4, 32q/4kv x16, F 5632; batch 64, prompt 1024", "ms_per_step": r["ms"],
+            "tok_per_s": r["decode_tok_per_s"], "gbs": r["achieved"], "frac_of_hbm": r["achieved"] / float(peaks["hbm_gbs"]),
+            "timed_steps": r["timed_steps"], "note": r["note"]}
 
 
 def run_ours(args) -> None:
@@ -254,7 +368,6 @@ def run_ours(args) -> None:
                              generator=torch.Generator().manual_seed(SEED + 1 + rank)).pin_memory()
     ids = ids_host.to(dev)
     T = B * SEQ
-    model.enable_profile(2048)
 
     def sync_all():
         torch.cuda.synchronize(dev)
@@ -262,43 +375,46 @@ def run_ours(args) -> None:
             dist.barrier()
             torch.cuda.synchronize(dev)
 
-    # routing statistics of this workload (deterministic): rows per (block, recursion)
-    model(ids, taps=True)
+    def timed(fn, steps):
+        """K calls bracketed by barrier + synchronize, CUDA events on the launching stream; max over ranks below."""
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        return e0.elapsed_time(e1)
+
+    # routing statistics of this workload (deterministic): rows per (block, recursion); and how many launches one
+    # forward makes, which sizes the launch recorder for the K timed steps
+    model.enable_profile(4096)
+    model(ids, taps=True, reuse_buffer=True)
     torch.cuda.synchronize(dev)
     mlp_rows = model.last_taps.mlp_rows.cpu().tolist()
-    model.read_profile()
+    launches_per_forward = len(model.read_profile())
+    model.disable_profile()
+    model.enable_profile(launches_per_forward * K + 64)
     for _ in range(W):
-        model(ids)
+        model(ids, reuse_buffer=True)
     sync_all()
     model.read_profile()
 
     # ---- timed region: K forwards, ids resident in HBM
     sampler = ClockSampler(local) if rank == 0 else None
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    per_step_records = []
-    ev0.record()
-    for _ in range(K):
-        model(ids)
-    ev1.record()
-    sync_all()
-    ms_total = ev0.elapsed_time(ev1)
-    records = model.read_profile()
-    launches_per_step = len(records) // max(1, K)
+    ms_total = timed(lambda: model(ids, reuse_buffer=True), K)
+    records = model.read_profile()              # raises if the recorder overflowed
+    if len(records) != launches_per_forward * K:
+        raise SystemExit(f"launch recorder: {len(records)} records for {K} steps of {launches_per_forward} launches")
     model.check_device_errors()
+    model.disable_profile()
+    timed_seq0 = model._logits[:SEQ, :ARCH["vocab_size"]].clone()      # sequence 0 of the last timed step
 
     # ---- e2e: pinned host ids -> device, forward, last-position logits -> host, every step
     out_host = torch.empty((B, ARCH["vocab_size"]), dtype=torch.bfloat16).pin_memory()
-    model.disable_profile()
     for _ in range(2):
         model.prefill(ids_host, out_host)
-    sync_all()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(K):
-        model.prefill(ids_host, out_host)
-    e1.record()
-    sync_all()
-    ms_e2e = e0.elapsed_time(e1)
+    ms_e2e = timed(lambda: model.prefill(ids_host, out_host), K)
     clocks = sampler.stop() if sampler is not None else None
 
     t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
@@ -309,9 +425,23 @@ def run_ours(args) -> None:
     value = tokens_all / (ms_total * 1e-3)
     e2e = tokens_all / (ms_e2e * 1e-3)
 
+    # ---- N > 1: the strong-scaling form of the same workload (a global batch of 32 sequences split over the ranks)
+    strong = None
+    if dist is not None and args.scaling_mode == "weak" and 32 % world == 0:
+        Bs = 32 // world
+        ids_s = ids[:Bs].contiguous() if Bs <= B else torch.randint(0, ARCH["vocab_size"], (Bs, SEQ), device=dev)
+        for _ in range(3):
+            model(ids_s, reuse_buffer=True)
+        ms_s = timed(lambda: model(ids_s, reuse_buffer=True), K)
+        ts = torch.tensor([ms_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+        ms_s = float(ts[0])
+        strong = {"global_batch": 32, "batch_per_gpu": Bs, "ms_per_step": ms_s / K, "value": 32 * SEQ * K / (ms_s * 1e-3),
+                  "unit": "tok/s", "scaling": "strong"}
+
     # outside the timed region: gather the last-position logits of every rank (NCCL over NVLink)
     if dist is not None:
-        last = model(ids)[:, -1, :].contiguous()
+        last = model(ids, reuse_buffer=True)[:, -1, :].contiguous()
         gathered = torch.empty((world * B, ARCH["vocab_size"]), dtype=last.dtype, device=dev)
         dist.all_gather_into_tensor(gathered, last)
         torch.cuda.synchronize(dev)
@@ -326,7 +456,7 @@ def run_ours(args) -> None:
             d["ms"] += r["ms"]
         tot = sum(d["ms"] for d in by_kind.values()) or 1.0
         fl = routed_flops(records, mlp_rows, T)
-        breakdown = {k: {"launches_per_step": d["launches"] // K, "ms_per_step": d["ms"] / K, "share": d["ms"] / tot,
+        breakdown = {k: {"launches_per_step": d["launches"] / K, "ms_per_step": d["ms"] / K, "share": d["ms"] / tot,
                          "tflops": (fl.get(k, 0.0) / (d["ms"] * 1e-3) / 1e12) if fl.get(k) else None}
                      for k, d in sorted(by_kind.items(), key=lambda kv: -kv[1]["ms"])}
         dom = "gemm_gate_up"
@@ -341,8 +471,12 @@ def run_ours(args) -> None:
         dom_nk = next((r["n"] * r["k"] for r in records if r["kind"] == dom), 0)
         avg_rows = fl.get(dom, 0.0) / (2.0 * dom_nk) / n_dom if dom_nk else 0.0
         traffic = cap_weight + (cap_read - cap_weight + cap_write) / cap_rows * avg_rows
-        all_gemm_fl = sum(v for k, v in fl.items())
-        routed_per_token = all_gemm_fl / (T * K)
+        all_fl = sum(v for k, v in fl.items())
+        # the pre-attention convolutions are tensor work too (6 * (lat*hd + lat^2 + kvd*hd + kvd^2) FLOP per token and block)
+        lat, hd = ARCH["dim"] // ARCH["compression_factor"], ARCH["dim"] // ARCH["compression_factor"] // ARCH["n_heads"]
+        kvd = ARCH["n_kv_heads"] * hd
+        all_fl += 6.0 * (lat * hd + lat * lat + kvd * hd + kvd * kvd) * T * ARCH["n_mor_blocks"] * K
+        routed_per_token = all_fl / (T * K)
         line = {
             "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": getattr(args, "scaling_mode", "weak"),
@@ -351,29 +485,49 @@ def run_ours(args) -> None:
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": world * B * SEQ * 8,
                     "d2h_bytes_per_step": world * B * ARCH["vocab_size"] * 2, "ms_per_step": ms_e2e / K,
                     "api": "HydraB200Model.prefill(pinned int64 ids [B,S]) -> last-position logits [B,V] bf16 on the host"},
-            "gpu_launches": launches_per_step * K,
+            "gpu_launches": launches_per_forward * K,
+            "launches_per_step": launches_per_forward,
             "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<256> (gate_up + SwiGLU epilogue)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
                          "peak_source": f"bf16_tflops_sustained, {peak_src}", "traffic": traffic,
                          "traffic_unit": "B/launch (DRAM read + write, scaled by rows from the ncu capture at M=8192)",
                          "avg_rows_per_launch": avg_rows,
-                         "launches_per_step": by_kind.get(dom, {"launches": 0})["launches"] // K},
+                         "launches_per_step": by_kind.get(dom, {"launches": 0})["launches"] / K},
             "model_tflops": {"routed_flops_per_token": routed_per_token,
                              "dense_flops_per_token": 823.4e6,
-                             "achieved_routed": routed_per_token * T * K / (ms_total * 1e-3) / 1e12 / 1.0,
+                             "achieved_routed": routed_per_token * T * K / (ms_total * 1e-3) / 1e12,
                              "frac_of_sustained_peak_routed": routed_per_token * T * K / (ms_total * 1e-3) / 1e12 / peak},
-            "breakdown": breakdown, "mlp_rows": mlp_rows, "clocks": clocks,
+            "breakdown": breakdown, "breakdown_ms_sum": tot / K, "mlp_rows": mlp_rows, "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu_baseline:
-            cpu_sd = {k: v.to(torch.bfloat16).float().cpu() for k, v in sd.items()}
-            tps, dt, threads = cpu_forward_tokens_per_s(1, 1, 0, cpu_sd)
-            line["cpu_baseline"] = {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
-                                    "sample": f"1 sequence x {SEQ} tokens of the same workload and weights, one timed "
-                                              f"forward ({dt:.1f} s), CPU port of the reference's eager fp32 forward"}
+        if strong is not None:
+            line["strong"] = strong
+        if world == 1:
+            if not args.no_parity:
+                line["parity"] = parity_record(model, ids, timed_seq0, sd)
+            del timed_seq0
+            model._logits = None
+            torch.cuda.empty_cache()
+            if not args.no_cpu_baseline:
+                cpu_sd = {k: v.to(torch.bfloat16).float().cpu() for k, v in sd.items()}
+                line["cpu_baseline"] = cpu_arm(1, 2, 1, cpu_sd)
+            if not args.no_extras:
+                line["ccgqa_block"] = ccgqa_block_record(peaks)
+                line["library_baseline"] = microbench_library_baseline(avg_rows)
+                del model, sd
+                torch.cuda.empty_cache()
+                line["decode"] = decode_record(peaks)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def microbench_library_baseline(avg_rows: float) -> dict:
+    import microbench
+    try:
+        return microbench.library_baseline(avg_rows, ROOT, REF_ARGS if reference_available() else None)
+    except Exception as e:   # the comparator must never take the headline line down with it
+        return {"unavailable": f"{type(e).__name__}: {e}"[:300]}
 
 
 def main() -> None:
@@ -386,6 +540,9 @@ def main() -> None:
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="weak (default): --batch sequences on every GPU; strong: --batch sequences in total, split over the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the post-timing comparison with the CPU oracle")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the records measured after the headline: ccgqa_block, library_baseline, decode")
     ap.add_argument("--micro", default=None, help="run one single-kernel microbenchmark instead of the model "
                     "(gemm, gemm_skinny, ccgqa_block, pre_attention, attention, rms_norm, rope, swiglu_ffn, swiglu_act, "
                     "model_hidden, decode, sample_rows)")
@@ -400,7 +557,7 @@ def main() -> None:
     ap.add_argument("--gemm-impl", dest="impl_gemm", type=int, default=0)
     args = ap.parse_args()
     if args.micro is not None:
-        from hydra_b200 import microbench
+        import microbench
         if args.micro == "decode":
             args.batch = 64 if args.batch == 32 else args.batch
         elif args.micro not in ("gemm", "gemm_skinny", "model_hidden"):

@@ -712,6 +712,7 @@ extern "C" void hb200_profile_destroy(void* profile) {
 extern "C" int hb200_profile_reset(void* profile) {
   HB_REQUIRE(profile != nullptr, HB200_ERR_INVALID, "profile_reset: null handle");
   static_cast<Profile*>(profile)->count = 0;
+  static_cast<Profile*>(profile)->dropped = 0;
   return 0;
 }
 
@@ -723,5 +724,5 @@ extern "C" int hb200_profile_read(void* profile, hb200_launch_record* records, f
     records[i] = p->rec[i];
     HB_CUDA(cudaEventElapsedTime(&ms[i], p->ev[2 * i], p->ev[2 * i + 1]));
   }
-  return p->count;
+  return p->count + p->dropped;
 }

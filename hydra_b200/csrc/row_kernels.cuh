@@ -18,6 +18,7 @@ struct Profile {
   std::vector<hb200_launch_record> rec;
   int count = 0;
   int capacity = 0;
+  int dropped = 0;                      // launches that found the recorder full (reported by hb200_profile_read)
 };
 
 struct ProfScope {
@@ -30,6 +31,8 @@ struct ProfScope {
       slot = p->count++;
       p->rec[slot] = hb200_launch_record{kind, block, rec, m, n, k};
       cudaEventRecord(p->ev[2 * slot], st);
+    } else if (p != nullptr) {
+      ++p->dropped;
     }
   }
   ~ProfScope() {

@@ -632,6 +632,9 @@ class HydraB200Model:
         n = _lib.lib().hb200_profile_read(self._profile, recs, ms, cap)
         if n < 0:
             _lib.check(n, "profile_read")
+        if n > cap:
+            raise _lib.Hb200Error(f"the launch recorder holds {cap} records but {n} launches were made since the last "
+                                  "read: the breakdown would be truncated (enable_profile with a larger capacity)")
         out = [dict(kind=_lib.KERNEL_KINDS[recs[i].kind], block=recs[i].block, rec=recs[i].rec, m=recs[i].m,
                     n=recs[i].n, k=recs[i].k, ms=float(ms[i])) for i in range(min(n, cap))]
         if reset:

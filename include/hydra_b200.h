@@ -411,7 +411,9 @@ void hb200_profile_destroy(void* profile);
 /* Forget the recorded launches (call between measured steps, after reading). */
 int hb200_profile_reset(void* profile);
 /* After the stream has been synchronised: copies up to `max_records` records and their durations in
- * milliseconds; returns the number of launches recorded since the last reset (negative on error). */
+ * milliseconds; returns the number of launches the executor made since the last reset (negative on error).  A
+ * return value above the recorder's capacity means that many launches found it full and were not recorded: size
+ * the recorder for the launches between two reads. */
 int hb200_profile_read(void* profile, hb200_launch_record* records, float* ms, int max_records);
 
 #ifdef __cplusplus

@@ -16,8 +16,8 @@ from typing import Callable, Dict
 
 import torch
 
-from . import _lib, kernels
-from ._pack import PackedBlock, PackedModel, interleave_gate_up, repack_conv, rope_tables
+from hydra_b200 import _lib, kernels
+from hydra_b200._pack import PackedBlock, PackedModel, interleave_gate_up, repack_conv, rope_tables
 
 L2_BYTES = 126 * 1024 * 1024
 
@@ -119,7 +119,7 @@ def gemm_skinny(args) -> dict:
 
 
 def _attention_module(dim=1024, H=8, KV=2, S=2048, temperature=1.0):
-    from .attention import build_hybrid_attention_module
+    from hydra_b200.attention import build_hybrid_attention_module
     torch.manual_seed(1)
     m = build_hybrid_attention_module("ccgqa", dim=dim, n_heads=H, n_kv_heads=KV, max_seq_len=S, compression_factor=4,
                                       attention_kwargs={})
@@ -292,7 +292,7 @@ def swiglu_act(args) -> dict:
 def model_hidden(args) -> dict:
     """The 250M model without the output projection (forward_hidden), batch x 2048: a few GB on the device, every
     block kernel at its full-size shape - the command used to capture the row / routing kernels under ncu."""
-    from .model import HydraB200Model, random_state_dict
+    from hydra_b200.model import HydraB200Model, random_state_dict
     arch = dict(vocab_size=50257, dim=1024, n_mor_blocks=10, recursions_per_block=4, n_heads=8, n_kv_heads=2,
                 compression_factor=4, mlp_ratio=2.67, mod_capacity=0.75)
     sd = random_state_dict(seed=0, device="cuda", **arch)
@@ -310,7 +310,7 @@ def decode(args) -> dict:
     F 5632, MoD 0.75): `batch` sequences per GPU, prompt of 1024 uniform-random tokens, 256 new tokens.  Reports the
     decode phase (steps replayed from one CUDA graph) against the weight-streaming bound: every step reads each
     weight once (the activations of `batch` rows are negligible) plus the cached keys / values of every position."""
-    from .model import HydraB200Model, random_state_dict
+    from hydra_b200.model import HydraB200Model, random_state_dict
     arch = dict(vocab_size=50257, dim=2048, n_mor_blocks=args.blocks, recursions_per_block=4, n_heads=32, n_kv_heads=4,
                 compression_factor=4, mlp_ratio=2.67, mod_capacity=0.75)
     sd = random_state_dict(seed=0, device="cuda", **arch)
@@ -354,7 +354,7 @@ def decode(args) -> dict:
 def sample_rows(args) -> dict:
     """Next-token sampling (temperature 0.8, top-k 50, top-p 0.9: the reference sampler's defaults) and the greedy
     argmax on --batch logit rows of 50257 bf16 columns: one read of the rows is the algorithmic traffic."""
-    from .sampling import sample_rows as sample
+    from hydra_b200.sampling import sample_rows as sample
     B, V, ld = int(args.batch), 50257, 50264
     ns = _sets(B * ld * 2)
     xs = [_rand_bf16(B, ld, scale=2.5, seed=i) for i in range(ns)]
@@ -373,6 +373,140 @@ def sample_rows(args) -> dict:
     return {"kernel": "sample_rows_kernel", "shape": [B, V], "ms": ms, "bound": "hbm",
             "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "algorithmic_bytes": nbytes,
             "ms_nucleus_only": ms_nuc, "ms_argmax_rows": ms_arg}
+
+
+# ------------------------------------------------------------------------------------------------------------
+def _time_us(fn: Callable[[int], None], iters: int = 10, warmup: int = 3) -> float:
+    return _time(fn, iters, warmup) * 1e3
+
+
+def library_baseline(gemm_rows: int, root: str, ref_model_args: dict | None = None, iters: int = 10) -> dict:
+    """The library calls the reference makes on a CUDA device, timed on this GPU beside this package's kernels at the
+    same shapes (CUDA events, same process): ``F.linear`` (cuBLAS) for the five contractions of the 250M model
+    (hydra/layers/common.py:221-230, attention.py:122-124), ``F.scaled_dot_product_attention(is_causal=True,
+    enable_gqa=True)`` at the CCGQA-block microbenchmark shape (attention.py:288-299), the four ``Conv1d`` calls with
+    their transposes and pads as the reference issues them (kernels/fused_conv.py:39-62; compared with the whole fused
+    pre-attention kernel, which also does the QK-mean, L2 norm, RoPE and value shift), and - when the reference
+    package is present under oracle/_ref - the reference's own bf16 eager model at the prefill workload.
+    ``gemm_rows``: rows of the gate_up / down contractions (the average number of rows routed to them per launch)."""
+    import torch.nn.functional as F
+    T, D, Fh, V = 65536, 1024, 2816, 50257
+    lib = _lib.lib()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out: dict = {"method": f"CUDA events, {iters} launches after 3 warm-up launches, one process, operands larger than L2"}
+
+    def ours_gemm(A, W, Cm, M, N, K, epi, ldc):
+        return lambda i: _lib.check(lib.hb200_gemm_bf16(A.data_ptr(), W.data_ptr(), Cm.data_ptr(), M, N, K, K, K, ldc, epi,
+                                                        None, 1.0, None, None, 0, err.data_ptr(), _stream()))
+
+    gemms = {}
+    Mr = max(128, (int(gemm_rows) + 127) // 128 * 128)
+    for name, (M, N, K) in {"qkv": (T, 384, D), "o_proj": (T, D, 256), "gate_up": (Mr, 2 * Fh, D), "down": (Mr, D, Fh),
+                            "lm_head": (T, V, D)}.items():
+        A = _rand_bf16(M, K, seed=3)
+        W = _rand_bf16(N, K, scale=0.03, seed=4)
+        ldc = (N + 7) // 8 * 8
+        Cm = torch.empty(M, ldc, dtype=torch.bfloat16, device="cuda")
+        flops = 2.0 * M * N * K
+        t_lib = _time_us(lambda i: F.linear(A, W), iters)
+        if name == "gate_up":
+            # ours fuses the SwiGLU activation into the epilogue; the library side is the bare contraction plus the
+            # reference's separate activation pass over the [M, 2F] result (common.py:224-230)
+            Wi = interleave_gate_up(W, torch.device("cuda", torch.cuda.current_device()))
+            act = torch.empty(M, Fh, dtype=torch.bfloat16, device="cuda")
+            t_ours = _time_us(ours_gemm(A, Wi, act, M, N, K, 2, Fh), iters)
+
+            def lib_mlp(i):
+                gu = F.linear(A, W)
+                g, u = gu.chunk(2, dim=-1)
+                return F.silu(g) * u
+            t_lib_act = _time_us(lib_mlp, iters)
+            gemms[name] = {"shape": [M, N, K], "torch_us": t_lib, "torch_with_activation_us": t_lib_act, "ours_us": t_ours,
+                           "torch_tflops": flops / t_lib / 1e6, "ours_tflops": flops / t_ours / 1e6,
+                           "note": "ours includes the SwiGLU epilogue"}
+        else:
+            t_ours = _time_us(ours_gemm(A, W, Cm, M, N, K, 0, ldc), iters)
+            gemms[name] = {"shape": [M, N, K], "torch_us": t_lib, "ours_us": t_ours,
+                           "torch_tflops": flops / t_lib / 1e6, "ours_tflops": flops / t_ours / 1e6}
+        del A, W, Cm
+    assert int(err.item()) == 0
+    out["gemm"] = gemms
+
+    # attention core, config 2
+    B, S, H, KV, hd = 8, 2048, 8, 2, 32
+    q = torch.nn.functional.normalize(_rand_bf16(B, H, S, hd).float(), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(_rand_bf16(B, KV, S, hd, seed=1).float(), dim=-1).to(torch.bfloat16)
+    v = _rand_bf16(B, KV, S, hd, seed=2)
+    o = torch.empty(B, S, H * hd, dtype=torch.bfloat16, device="cuda")
+    t_sdpa = _time_us(lambda i: F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True), iters)
+    t_att = _time_us(lambda i: _lib.check(lib.hb200_attention_causal_gqa(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), B, S, H, KV, hd, 1.0 / math.sqrt(hd),
+        1.02 / math.sqrt(hd), err.data_ptr(), _stream())), iters)
+    out["attention"] = {"shape": [B, H, S, hd], "torch_sdpa_us": t_sdpa, "ours_us": t_att}
+
+    # the reference's conv path at config 2: [B,S,C] -> transpose -> pad -> grouped conv -> pad -> dense conv -> transpose
+    lat, kvd = H * hd, KV * hd
+    xq, xk = _rand_bf16(B, S, lat, seed=5), _rand_bf16(B, S, kvd, seed=6)
+    wq1, wq2 = _rand_bf16(lat, hd, 3, scale=0.05, seed=7), _rand_bf16(lat, lat, 3, scale=0.05, seed=8)
+    wk1, wk2 = _rand_bf16(kvd, hd, 3, scale=0.05, seed=9), _rand_bf16(kvd, kvd, 3, scale=0.05, seed=10)
+
+    def conv_seq(x, w1, w2, groups):
+        y = x.transpose(1, 2).contiguous()
+        y = F.conv1d(F.pad(y, (2, 0)), w1, groups=groups)
+        y = F.conv1d(F.pad(y, (2, 0)), w2)
+        return y.transpose(1, 2).contiguous()
+
+    def convs(i):
+        conv_seq(xq, wq1, wq2, H)
+        conv_seq(xk, wk1, wk2, KV)
+    t_conv = _time_us(convs, iters)
+    ns = argparse_like(batch=B, iters=iters)
+    out["convs"] = {"shape": [B, S, lat + kvd], "torch_conv1d_x4_us": t_conv,
+                    "ours_whole_pre_attention_us": pre_attention(ns)["ms"] * 1e3,
+                    "note": "ours is the whole fused pre-attention kernel (value shift, both conv pairs, QK-mean, L2 norm, "
+                            "temperature, RoPE); the library side is the two conv pairs only"}
+
+    if ref_model_args is not None:
+        out["reference_eager_bf16"] = reference_eager_on_gpu(ref_model_args, root)
+    return out
+
+
+class argparse_like:
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def reference_eager_on_gpu(ref_model_args: dict, root: str) -> dict:
+    """The reference's own HydraModel (unmodified package under oracle/_ref), bf16, eager, on this GPU at the prefill
+    workload (diagnostics/benchmark_hydra_models.py:133-143 times it this way): tokens/s of its forward."""
+    import sys
+    sys.path.insert(0, root) if root not in sys.path else None
+    from oracle import build_ref
+    if not build_ref.add_ref_to_path():
+        return {"unavailable": "oracle/_ref has not been built"}
+    try:
+        model = build_ref.reference_model(**ref_model_args).cuda().bfloat16()
+    except Exception as e:   # pragma: no cover - depends on the box
+        return {"unavailable": f"building the reference model failed: {type(e).__name__}: {e}"[:300]}
+    S = ref_model_args["max_seq_len"]
+    res = {}
+    for B in (32, 8):
+        try:
+            ids = torch.randint(0, ref_model_args["vocab_size"], (B, S), device="cuda")
+            with torch.no_grad():
+                ms = _time(lambda i: build_ref.reference_forward(model, ids), 3, warmup=2)
+            res = {"batch": B, "seq_len": S, "ms": ms, "tok_per_s": B * S / (ms * 1e-3),
+                   "kernels": build_ref.reference_kernel_status()}
+            break
+        except torch.cuda.OutOfMemoryError:
+            torch.cuda.empty_cache()
+            res = {"unavailable": f"out of memory at batch {B}"}
+        except Exception as e:   # pragma: no cover
+            res = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+            break
+    del model
+    torch.cuda.empty_cache()
+    return res
 
 
 CASES: Dict[str, Callable] = {

@@ -63,6 +63,44 @@ def build_ref(reference_root: str, force: bool = False) -> str:
     return REF_DIR
 
 
+def reference_model(*, vocab_size: int, dim: int, n_mor_blocks: int, recursions_per_block: int, n_heads: int,
+                    n_kv_heads: int, max_seq_len: int, mod_capacity: float, compression_factor: int = 4, seed: int = 0,
+                    **extra):
+    """The reference's HydraModel, seeded, in eval mode with MoD hard routing switched on (its warm-up passed), the
+    way the reference's own inference benchmarks build it.  Needs add_ref_to_path() first."""
+    import torch
+    from hydra.model.framework.model import HydraModel
+    torch.manual_seed(seed)
+    m = HydraModel(vocab_size=vocab_size, dim=dim, n_mor_blocks=n_mor_blocks, recursions_per_block=recursions_per_block,
+                   n_heads=n_heads, n_kv_heads=n_kv_heads, compression_factor=compression_factor,
+                   max_seq_len=max_seq_len, mod_capacity=mod_capacity, **extra)
+    m.eval()
+    m.set_global_step(10 ** 6)
+    return m
+
+
+def reference_forward(model, ids):
+    """model(ids) under no_grad.  On a CUDA device the reference routes RoPE / SwiGLU / RMSNorm through its Triton
+    kernels; if those cannot be compiled on the box, they are switched off with the reference's own switch
+    (hydra.kernels.set_use_triton_kernels) and the call is repeated on its PyTorch path."""
+    import torch
+    with torch.no_grad():
+        try:
+            return model(ids)
+        except Exception:
+            if not ids.is_cuda:
+                raise
+            from hydra.kernels import fused_ops
+            fused_ops.set_use_triton_kernels(False)
+            return model(ids)
+
+
+def reference_kernel_status() -> dict:
+    from hydra.kernels import fused_ops
+    st = fused_ops.get_kernel_status()
+    return {k: st.get(k) for k in ("triton_available", "use_triton_kernels", "fused_rope", "fused_swiglu", "fused_rms_norm")}
+
+
 if __name__ == "__main__":
     root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("HYDRA_REFERENCE_ROOT", "")
     if not root:

@@ -5,8 +5,8 @@ Three kinds of check:
     sits within bf16 noise of its threshold (reported, bounded);
   * numerics with routing held equal: the oracle replays the GPU's own routing decisions (forced), so the
     remaining difference is arithmetic only - rel-L2 <= 1e-2, max-abs <= 4% of the logit range;
-  * free run against the reference's fp32 logits: our error must not exceed 2x the reference's OWN bf16 error on
-    the same inputs (stored in the fixture).
+  * free run against the reference's fp32 logits: our error must not exceed the reference's OWN bf16 error on
+    the same inputs (stored in the fixture) by more than 10 %.
 """
 import numpy as np
 import pytest
@@ -40,7 +40,7 @@ def taps_to_oracle(m, tp, B, S):
     return rt
 
 
-def compare_with_oracle(m, w, cfg, ids, golden_logits=None, ref_err=None, label=""):
+def compare_with_oracle(m, w, cfg, ids, golden_logits=None, ref_err=None, label="", min_depth_agree=0.97):
     B, S = ids.shape
     lg = m(ids.cuda(), taps=True, block_out=True).float().cpu()
     m.check_device_errors()
@@ -56,7 +56,7 @@ def compare_with_oracle(m, w, cfg, ids, golden_logits=None, ref_err=None, label=
     d_agree = [float((d_gpu[i] == ot.depths[i]).float().mean()) for i in range(NB)]
     print(f"{label} depth agreement per block: {d_agree}")
     assert torch.equal(d_gpu[0], ot.depths[0]) or d_agree[0] > 0.995
-    assert min(d_agree) > 0.97
+    assert min(d_agree) > min_depth_agree
     # ---- (2) forced replay: numerics only
     rt = taps_to_oracle(m, tp, B, S)
     ft = O.RoutingTaps()
@@ -89,7 +89,7 @@ def compare_with_oracle(m, w, cfg, ids, golden_logits=None, ref_err=None, label=
     fr, fa = rel_l2(lg, ref), max_abs(lg, ref)
     print(f"{label} free-run vs fp32 reference: rel_l2 {fr:.3e} max_abs {fa:.3e}; reference's own bf16 path: {ref_err}")
     if ref_err is not None:
-        assert fr <= 2.0 * ref_err[1] + 1e-3, "error vs the fp32 reference exceeds twice the reference's own bf16 error"
+        assert fr <= 1.1 * ref_err[1] + 2e-4, "error vs the fp32 reference exceeds the reference's own bf16 error (+10 %)"
     return lg, tp
 
 
@@ -207,6 +207,25 @@ def test_long_sequence_beyond_one_select_pass():
     assert torch.equal(idx, O.mod_select(sc[1, 0], 0.75))
 
 
+def test_headline_configuration_against_the_oracle():
+    """The benchmarked model itself - dim 1024, 10 blocks x 4 recursions, 8q/2kv heads of 32, SwiGLU 2816, MoD 0.75,
+    vocabulary 50257, sequences of 2048 tokens, the seeded random-init weights the benchmark uses - on two sequences,
+    against the CPU oracle: routing agreement of the free runs, logits and every block output with the GPU's routing
+    replayed (rel-L2 <= 1e-2, max-abs <= 4 % of the logit range).  Sequences are independent bit for bit
+    (test_batch_independence_determinism_and_sharding_250m), so two of them speak for a batch of 32."""
+    from hydra_b200.model import random_state_dict
+    arch = dict(vocab_size=50257, dim=1024, n_mor_blocks=10, recursions_per_block=4, n_heads=8, n_kv_heads=2,
+                compression_factor=4, mlp_ratio=2.67, mod_capacity=0.75)
+    sd = random_state_dict(seed=0, device="cuda", **arch)
+    w = {k: v.to(torch.bfloat16).float().cpu() for k, v in sd.items()}       # the values the kernels see
+    cfg = O.config_from_state_dict(w, n_heads=8, n_kv_heads=2, mod_capacity=0.75, max_seq_len=2048)
+    m = build(w, cfg)
+    ids = torch.randint(0, 50257, (2, 2048), generator=torch.Generator().manual_seed(1))
+    lg, tp = compare_with_oracle(m, w, cfg, ids, label="250M x 2 x 2048", min_depth_agree=0.95)
+    rows = tp.mlp_rows.cpu()
+    assert int(rows[0, 0]) == 2 * 2048 and int(rows[1, 0]) <= 2 * O.mod_k(2048, 0.75)
+
+
 def test_batch_independence_determinism_and_sharding_250m():
     """The 250M prefill architecture (dim 1024, 10x4, 8q/2kv, F 2816, MoD 0.75, S 2048) at batch 4: properties that
     hold at any size - two runs agree bit for bit, a sequence run alone equals the same sequence inside the batch
@@ -304,7 +323,7 @@ def test_base_model_without_routing():
     ref = torch.from_numpy(fx["logits"])
     err = rel_l2(lg, ref)
     print(f"base model vs reference fp32 logits: rel_l2 {err:.3e}; reference's own bf16 path: {float(fx['ref_bf16_rel_l2'][0]):.3e}")
-    assert err <= 2.0 * float(fx["ref_bf16_rel_l2"][0]) + 1e-3
+    assert err <= 1.1 * float(fx["ref_bf16_rel_l2"][0]) + 2e-4
     bo = m.last_taps.block_out.float().cpu().view(cfg.n_mor_blocks, *ids.shape, -1)
     for i in range(cfg.n_mor_blocks):
         assert rel_l2(bo[i], torch.from_numpy(fx[f"block_out:{i}"])) <= 1e-2, f"block {i}"
@@ -644,3 +663,52 @@ def test_attention_switches_at_model_level():
     assert m.generate(ids[:, :20].cuda(), 3).shape == (3, 23)
     with pytest.raises(NotImplementedError):
         m.generate(ids[:, :20].cuda(), 3, mode="cached")
+
+
+def test_checkpoint_file_written_the_trainers_way(tmp_path):
+    """load_checkpoint() on a file laid out as the reference's trainer writes it and its evaluation helper reads it
+    (diagnostics/eval_checkpoint.py:88-99): weights under "model", every key prefixed with "_orig_mod." (torch.compile),
+    the tied output projection saved a second time, MoD bookkeeping buffers and the alias keys of the wrapped MLP
+    present, plus trainer state next to the weights.  The loaded model must reproduce the fixture's logits."""
+    from hydra_b200.model import load_checkpoint
+    fx, cfg, w = G.model_fixture("model_hd16.npz")
+    payload = {"model": {}, "step": 1234, "optimizer": {"state": {}}, "config": {"model_size": "debug"}}
+    for k, v in w.items():
+        payload["model"]["_orig_mod." + k] = v.clone()
+        if ".mlp." in k and cfg.block_has_mod(int(k.split(".")[1])):
+            payload["model"]["_orig_mod." + k.replace(".mlp.", ".mod_mlp_wrapper.mlp.")] = v.clone()
+    payload["model"]["_orig_mod.output.weight"] = w["tok_emb.weight"].clone()
+    for i in range(cfg.n_mor_blocks):
+        if cfg.block_has_mod(i):
+            payload["model"][f"_orig_mod.layers.{i}.mod_mlp_wrapper.mod_router._aux_loss"] = torch.zeros(())
+    path = tmp_path / "hydra_debug_step_1234.pt"
+    torch.save(payload, path)
+    m = load_checkpoint(str(path), n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, max_seq_len=cfg.max_seq_len,
+                        mod_capacity=cfg.mod_capacity)
+    ids = torch.from_numpy(fx["ids"])
+    lg = m(ids.cuda()).float().cpu()
+    m.check_device_errors()
+    direct = build(w, cfg)(ids.cuda()).float().cpu()
+    assert torch.equal(lg, direct), "the checkpoint route must give the same model as the state_dict route"
+    own = float(fx["ref_bf16_rel_l2"][0])
+    assert rel_l2(lg, torch.from_numpy(fx["logits"])) <= 1.1 * own + 2e-4
+    # a checkpoint of a model with mixture-of-experts layers is refused, not half-loaded
+    payload["model"]["_orig_mod.moe_layers.0.moe.router.gate.weight"] = torch.zeros(4, cfg.dim)
+    torch.save(payload, path)
+    with pytest.raises(NotImplementedError):
+        load_checkpoint(str(path), n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads)
+
+
+def test_trainer_built_250m_shape():
+    """The 250M model as the reference's trainer builds it (hydra/training/config.py:515-524, trainer.py:519): dim 1024,
+    16 query / 4 KV heads of 16, mlp_ratio 3.6 -> SwiGLU width 3840, mor_min_depth 1, MoD 0.75 - three blocks of it, on
+    sequences long enough for several attention tiles, against the oracle with the GPU's routing replayed."""
+    cfg = O.HydraConfig(vocab_size=2000, dim=1024, n_mor_blocks=3, recursions_per_block=4, n_heads=16, n_kv_heads=4,
+                        max_seq_len=640, mod_capacity=0.75, mlp_ratio=3.6, mor_min_depth=1)
+    assert cfg.ffn_hidden == 3840
+    w = O.init_params(cfg, seed=21, perturb=True)
+    ids = torch.randint(0, cfg.vocab_size, (2, 600), generator=torch.Generator().manual_seed(21))
+    m = build(w, cfg)
+    assert m.ffn_hidden == 3840 and m.head_dim == 16
+    lg, tp = compare_with_oracle(m, w, cfg, ids, label="trainer-built 250M shape")
+    assert int(tp.depths.min()) >= 1

@@ -67,6 +67,36 @@ def test_ties_nan_inf_and_signed_zero(L):
     assert (got[:, 1:] > got[:, :-1]).all(), "ascending and unique"
 
 
+def test_tie_order_beside_torch_topk_on_the_same_device(L, capsys):
+    """What CUDA torch.topk does with tie-heavy scores (the reference's bf16 path produces bf16-quantised scores,
+    mixture_of_depths.py:187): its choice among equal scores is not specified, so this reports how often it picks the
+    same positions as the lowest-index-first rule used here, and asserts only what any valid top-k must satisfy -
+    the same multiset of selected VALUES."""
+    g = torch.Generator().manual_seed(9)
+    q = (torch.randn(32, 2048, generator=g) * 3).to(torch.bfloat16).float()
+    k = 1536
+    got = select(L, q, k).long()
+    tv, ti = torch.topk(q.cuda(), k, dim=-1)
+    ti = ti.sort(dim=-1)[0].cpu()
+    assert torch.equal(torch.gather(q, 1, got).sort(dim=1, descending=True)[0], tv.cpu())
+    rows_equal = int((got == ti).all(dim=1).sum())
+    pos_equal = float((got == ti).float().mean())
+    kth = tv[:, -1].cpu()
+    tied_at_cut = [(int((q[b] == kth[b]).sum()), int(((q[b] == kth[b]) & (torch.zeros(2048, dtype=torch.bool).scatter_(0, ti[b], True))).sum()))
+                   for b in range(32)]
+    # among the scores equal to the k-th value, does torch keep the lowest positions too?
+    lowest_first = 0
+    for b in range(32):
+        eq = torch.nonzero(q[b] == kth[b]).flatten()
+        kept = torch.isin(eq, ti[b])
+        n_kept = int(kept.sum())
+        lowest_first += int(bool(kept[:n_kept].all()))
+    with capsys.disabled():
+        print(f"\n[tie report] rows with identical index lists: {rows_equal}/32; positions equal: {pos_equal:.4f}; "
+              f"rows where torch.topk (CUDA) also keeps the lowest positions among the tied cut value: {lowest_first}/32; "
+              f"(tied at cut, kept) first rows: {tied_at_cut[:4]}")
+
+
 def test_active_intersection_and_row_list(L):
     g = torch.Generator().manual_seed(4)
     B, Ln, k = 6, 512, 384
