@@ -536,7 +536,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--batch", type=int, default=32, help="sequences per GPU")
+    ap.add_argument("--batch", type=int, default=None, help="sequences per GPU (default 32; the microbenchmarks default "
+                    "to their own configuration: 8 sequences, 64 for decode)")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="weak (default): --batch sequences on every GPU; strong: --batch sequences in total, split over the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -558,10 +559,8 @@ def main() -> None:
     args = ap.parse_args()
     if args.micro is not None:
         import microbench
-        if args.micro == "decode":
-            args.batch = 64 if args.batch == 32 else args.batch
-        elif args.micro not in ("gemm", "gemm_skinny", "model_hidden"):
-            args.batch = 8 if args.batch == 32 else args.batch
+        if args.batch is None:
+            args.batch = 64 if args.micro == "decode" else (32 if args.micro in ("gemm", "gemm_skinny", "model_hidden") else 8)
         args.impl = args.impl_gemm
         names = [n for n in microbench.CASES if n not in ("model_hidden", "decode", "gemm_skinny")] if args.micro == "all" else [args.micro]
         world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -592,6 +591,8 @@ def main() -> None:
             dist.destroy_process_group()
         return
     args.scaling_mode = args.scaling
+    if args.batch is None:
+        args.batch = 32
     if args.scaling == "strong":
         world = int(os.environ.get("WORLD_SIZE", "1"))
         if args.batch % world != 0:

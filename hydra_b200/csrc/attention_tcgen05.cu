@@ -1,13 +1,19 @@
 // Causal grouped-query attention on the 5th-generation tensor cores (tcgen05 + TMEM, operands fed by TMA).
 //
 // One CTA = 128 query rows of one (batch, q-head).  Per tile of 128 keys:
-//   warp 0     TMA producer: Q once, then K and V tiles ([128 keys, hd], swizzle = row width) through a 2-stage ring;
+//   warp 0     TMA producer: Q once, then K and V tiles ([128 keys, hd], swizzle = row width) through a 5- or 6-stage ring
+//              (a tile takes ~2500 clocks to arrive from L2; with fewer stages that latency sets the pace);
 //   warp 1     one thread issues  S = Q K^T   (tcgen05.mma M128 x N128 x K=hd, fp32 S in TMEM columns 0..127)
-//              and, once the probabilities are in shared memory,  O += P V  (M128 x N=hd x K128, V as the MN-major
-//              B operand exactly as TMA delivered it, O accumulating in TMEM columns 128..128+hd across ALL tiles);
+//              and, once the probabilities are back in TMEM,  O += P V  (M128 x N=hd x K128: P is the A operand READ
+//              FROM TENSOR MEMORY, V the MN-major B operand exactly as TMA delivered it; O accumulates in TMEM across
+//              ALL tiles);
 //   warps 2-9  softmax: two warps per TMEM lane quadrant, each owning 64 of the tile's 128 keys; thread = query row;
 //              tcgen05.ld 32 columns of S at a time, p = 2^(s*scale*log2e - bound), causal mask on the diagonal tile,
-//              P as bf16 into a 128B-swizzled K-major A-operand tile in shared memory (double buffered).
+//              P as packed bf16 pairs straight back into 64 TMEM columns (tcgen05.st).
+//   Why P lives in tensor memory: a K = 16 slice of a 128-row operand tile in shared memory is 128 separate 32-byte
+//   pieces, one shared-memory wavefront each, so every M128 x N=hd MMA with P in shared memory occupied the tensor
+//   pipe for ~128 clocks however small N was - the kernel was bound by that operand fetch, not by the exponentials.
+//   Read from tensor memory the same MMA costs a few tens of clocks, and P never touches shared memory at all.
 //   The softmax denominator is produced by the tensor core as well: a third, 16-column accumulator receives
 //   P x ones (the same bf16 P that multiplies V), so the softmax threads issue one FFMA, one ex2 and half a
 //   byte-permute per score, and numerator and denominator see identical probabilities (which is also why P may
@@ -19,8 +25,11 @@
 // stays <= 0.  That makes the kernel a single pass over S limited by the exp (MUFU) rate - the attention core at
 // head_dim <= 32 costs one exp per 128 tensor FLOPs - and lets O stay in TMEM untouched until the end.
 //
-// Two CTAs fit per SM (104 KB of shared memory and 256 TMEM columns each at hd 32), so one CTA's softmax overlaps
-// the other's MMAs.  Every mbarrier wait is bounded; on expiry the CTA flags the error, frees TMEM and returns.
+// CTAs are ordered heaviest first over the whole grid (the last query tile of every (batch, head) before any
+// second-to-last one), so the hardware scheduler fills the tail with the short ones.  K / V / Q are addressed through
+// [heads][S][hd] tensor maps: rows past the end of a sequence read as zero instead of the next head's rows.
+// Two CTAs fit per SM (256 TMEM columns each at hd <= 32), so one CTA's softmax overlaps the other's MMAs.
+// Every mbarrier wait is bounded; on expiry the CTA flags the error, frees TMEM and returns.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -42,16 +51,17 @@ template <int HD> struct AttCfg {
   static constexpr int SBO = 8 * ROW_BYTES;                              // stride between 8-row groups
   static constexpr int Q_BYTES = AQ * ROW_BYTES;
   static constexpr int KV_BYTES = AK * ROW_BYTES;
-  static constexpr int P_BYTES = AQ * AK * 2;                            // two 64-key halves of 16 KB
-  static constexpr int STAGES = 2;
+  static constexpr int STAGES = HD == 64 ? 5 : 6;                        // K/V tiles in flight: a load takes ~2500 clocks to land
+  static_assert(STAGES <= 8, "barrier slots are laid out for at most eight stages");
   static constexpr int OFF_K = Q_BYTES;
   static constexpr int OFF_V = OFF_K + STAGES * KV_BYTES;
-  static constexpr int OFF_P = OFF_V + STAGES * KV_BYTES;
-  static constexpr int OFF_ONES = OFF_P + 2 * P_BYTES;                   // [128 keys][16] bf16, all 1.0
+  static constexpr int OFF_ONES = OFF_V + STAGES * KV_BYTES;             // [128 keys][16] bf16, all 1.0
   static constexpr int ONES_BYTES = AK * 32;
   static constexpr int OFF_BAR = OFF_ONES + ONES_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  static constexpr uint32_t TMEM_COLS = 256;                             // S: 0..127, O: 128..128+HD, row sums: 192..207
+  // S: 0..127, O: 128..128+HD, row sums: 128+HD..+16, P (bf16 pairs, 64 cells): the last 64 columns
+  static constexpr uint32_t TMEM_COLS = HD <= 32 ? 256 : 512;
+  static constexpr uint32_t COL_O = 128, COL_L = 128 + HD, COL_P = TMEM_COLS - 64;
 };
 
 struct AttParams {
@@ -63,7 +73,7 @@ struct AttParams {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(ATT_THREADS) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q,
+__global__ void __launch_bounds__(ATT_THREADS, (HD <= 32 ? 2 : 1)) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_q,
                                                                 const __grid_constant__ CUtensorMap tma_k,
                                                                 const __grid_constant__ CUtensorMap tma_v,
                                                                 const AttParams p) {
@@ -74,34 +84,31 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_tcgen05_kernel(const __
   const uint32_t bars = base + Cfg::OFF_BAR;
   // barrier slots (8 bytes each)
   const uint32_t q_full = bars, s_full = bars + 8, s_free = bars + 16, o_full = bars + 24;
-  auto kv_full = [&](int s) { return bars + 32u + 8u * s; };
-  auto kv_empty = [&](int s) { return bars + 48u + 8u * s; };
-  auto p_full = [&](int b) { return bars + 64u + 8u * b; };
-  auto p_free = [&](int b) { return bars + 80u + 8u * b; };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + Cfg::OFF_BAR + 96);
+  const uint32_t p_full = bars + 32u, p_free = bars + 40u;
+  auto kv_full = [&](int s) { return bars + 48u + 8u * s; };
+  auto kv_empty = [&](int s) { return bars + 112u + 8u * s; };      // up to eight stages each
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + Cfg::OFF_BAR + 176);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.S, H = p.H, KV = p.KV;
   const int n_qt = (S + AQ - 1) / AQ;
-  const int qt = n_qt - 1 - (int)blockIdx.x;   // late query tiles (most keys) first
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int qt = n_qt - 1 - (int)blockIdx.y;   // late query tiles (most keys) first, over the whole grid
+  const int h = (int)blockIdx.x % H, b = (int)blockIdx.x / H;
   const int kvh = h / (H / KV);
   const int q0 = qt * AQ;
   const int n_kt = qt + 1;                     // causal: key tiles 0..qt
-  const int q_row0 = (b * H + h) * S + q0;     // row of the [B*H*S, hd] view
-  const int kv_row0 = (b * KV + kvh) * S;      // row of the [B*KV*S, hd] view
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     mbar_init(s_full, 1);
     mbar_init(s_free, SOFTMAX_WARPS);
     mbar_init(o_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    mbar_init(p_full, SOFTMAX_WARPS);
+    mbar_init(p_free, 1);
+    for (int i = 0; i < Cfg::STAGES; ++i) {
       mbar_init(kv_full(i), 1);
       mbar_init(kv_empty(i), 1);
-      mbar_init(p_full(i), SOFTMAX_WARPS);
-      mbar_init(p_free(i), 1);
     }
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -115,69 +122,76 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_tcgen05_kernel(const __
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128u, tmem_l = tmem_base + 192u;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + Cfg::COL_O, tmem_l = tmem_base + Cfg::COL_L,
+                 tmem_p = tmem_base + Cfg::COL_P;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
-      tma_load_2d(base, &tma_q, 0, q_row0, q_full);
+      tma_load_3d(base, &tma_q, 0, q0, b * H + h, q_full);
+      int s = 0;
+      uint32_t ph = 0;
       for (int j = 0; j < n_kt; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(kv_empty(s), (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag)) break;
+        if (!mbar_wait(kv_empty(s), ph ^ 1u, abort_flag)) break;
         mbar_arrive_expect_tx(kv_full(s), 2 * Cfg::KV_BYTES);
-        tma_load_2d(base + Cfg::OFF_K + s * Cfg::KV_BYTES, &tma_k, 0, kv_row0 + j * AK, kv_full(s));
-        tma_load_2d(base + Cfg::OFF_V + s * Cfg::KV_BYTES, &tma_v, 0, kv_row0 + j * AK, kv_full(s));
+        tma_load_3d(base + Cfg::OFF_K + s * Cfg::KV_BYTES, &tma_k, 0, j * AK, b * KV + kvh, kv_full(s));
+        tma_load_3d(base + Cfg::OFF_V + s * Cfg::KV_BYTES, &tma_v, 0, j * AK, b * KV + kvh, kv_full(s));
+        if (++s == Cfg::STAGES) { s = 0; ph ^= 1u; }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    // The whole warp runs this loop with warp-uniform values; one elected lane issues each MMA / commit (see the
+    // *_elect wrappers: a fraction of the issue cost of a single-lane loop, and these MMAs are small).
+    {
       constexpr uint32_t idesc_s = make_idesc(AQ, AK);          // Q, K both K-major
-      constexpr uint32_t idesc_pv = make_idesc_b_mn(AQ, HD);    // P K-major, V MN-major
+      constexpr uint32_t idesc_pv = make_idesc_b_mn(AQ, HD);    // P from tensor memory, V MN-major
       constexpr uint32_t idesc_l = make_idesc_b_mn(AQ, 16);     // P x ones -> row sums
       bool ok = mbar_wait(q_full, 0u, abort_flag);
       const uint64_t dq = make_smem_desc_ex(base, Cfg::SBO, Cfg::LAYOUT, 16);
-      auto issue_s = [&](int j) {   // S = Q K_j^T into the (single) S accumulator
-        const uint64_t dk = make_smem_desc_ex(base + Cfg::OFF_K + (j & 1) * Cfg::KV_BYTES, Cfg::SBO, Cfg::LAYOUT, 16);
+      const uint64_t dk0 = make_smem_desc_ex(base + Cfg::OFF_K, Cfg::SBO, Cfg::LAYOUT, 16);
+      const uint64_t dv0 = make_smem_desc_ex(base + Cfg::OFF_V, Cfg::SBO, Cfg::LAYOUT, Cfg::KV_BYTES);
+      const uint64_t d10 = make_smem_desc_ex(base + Cfg::OFF_ONES, 256, 6u, Cfg::ONES_BYTES);
+      auto issue_s = [&](int stage) {   // S = Q K^T into the (single) S accumulator
+        const uint64_t dk = dk0 + (uint64_t)((stage * Cfg::KV_BYTES) >> 4);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) umma_bf16(tmem_s, dq + 2u * k, dk + 2u * k, idesc_s, k ? 1u : 0u);
-        umma_commit(s_full);
+        for (int k = 0; k < HD / 16; ++k) umma_bf16_elect(tmem_s, dq + 2u * k, dk + 2u * k, idesc_s, k ? 1u : 0u);
+        umma_commit_elect(s_full);
       };
       if (ok && (ok = mbar_wait(kv_full(0), 0u, abort_flag))) {
         tcgen05_fence_after();
         issue_s(0);
       }
+      int s = 0, sn = 1 % Cfg::STAGES;        // stage of tile j, stage of tile j + 1
+      uint32_t phn = (Cfg::STAGES == 1) ? 1u : 0u;   // parity of kv_full(sn) for tile j + 1
       for (int j = 0; ok && j < n_kt; ++j) {
-        const int s = j & 1, pb = j & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1);
         if (j + 1 < n_kt) {
           // QK^T of the NEXT tile goes out as soon as the softmax warps have pulled S of this tile into registers,
           // so it runs in the shadow of their exponentials
-          if (!mbar_wait(kv_full((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1), abort_flag)) break;
+          if (!mbar_wait(kv_full(sn), phn, abort_flag)) break;
           if (!mbar_wait(s_free, (uint32_t)(j & 1), abort_flag)) break;
           tcgen05_fence_after();
-          issue_s(j + 1);
+          issue_s(sn);
         }
-        if (!mbar_wait(p_full(pb), ph, abort_flag)) break;
+        if (!mbar_wait(p_full, (uint32_t)(j & 1), abort_flag)) break;
         tcgen05_fence_after();
-        const uint32_t pbase = base + Cfg::OFF_P + pb * Cfg::P_BYTES;
-        const uint32_t vbase = base + Cfg::OFF_V + s * Cfg::KV_BYTES;
+        const uint64_t dvs = dv0 + (uint64_t)((s * Cfg::KV_BYTES) >> 4);
+        const uint32_t first = j ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < AK / 16; ++kk) {
-          // A: P, K-major, 128B swizzle, two 64-key halves 16 KB apart, 32 bytes per 16 keys inside a half
-          const uint64_t dp = make_smem_desc(pbase + (kk >> 2) * (AQ * 128) + (kk & 3) * 32);
-          // B: V as stored [key][dim] = MN-major; 16 keys = two 8-key groups SBO apart
-          const uint64_t dv = make_smem_desc_ex(vbase + kk * 16 * Cfg::ROW_BYTES, Cfg::SBO, Cfg::LAYOUT, Cfg::KV_BYTES);
-          umma_bf16(tmem_o, dp, dv, idesc_pv, (j | kk) ? 1u : 0u);
-          const uint64_t d1 = make_smem_desc_ex(base + Cfg::OFF_ONES + kk * 16 * 32, 256, 6u, Cfg::ONES_BYTES);
-          umma_bf16(tmem_l, dp, d1, idesc_l, (j | kk) ? 1u : 0u);
+          // A: P in tensor memory, 16 keys = 8 cells; B: V as stored [key][dim] = MN-major, 16 keys = two 8-key groups
+          umma_bf16_ts_elect(tmem_o, tmem_p + (uint32_t)(kk * 8), dvs + (uint64_t)((kk * 16 * Cfg::ROW_BYTES) >> 4), idesc_pv,
+                             kk ? 1u : first);
+          umma_bf16_ts_elect(tmem_l, tmem_p + (uint32_t)(kk * 8), d10 + (uint64_t)((kk * 16 * 32) >> 4), idesc_l, kk ? 1u : first);
         }
-        umma_commit(kv_empty(s));    // K/V stage reusable once these MMAs have read it
-        umma_commit(p_free(pb));     // P buffer reusable
+        umma_commit_elect(kv_empty(s));    // K/V stage reusable once these MMAs have read it
+        umma_commit_elect(p_free);         // P cells reusable
+        s = sn;
+        if (++sn == Cfg::STAGES) { sn = 0; phn ^= 1u; }
       }
-      umma_commit(o_full);
+      umma_commit_elect(o_full);
     }
     __syncwarp();
   } else {
@@ -189,14 +203,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_tcgen05_kernel(const __
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     bool ok = true;
     for (int j = 0; j < n_kt; ++j) {
-      const int pb = j & 1;
       if (!mbar_wait(s_full, (uint32_t)(j & 1), abort_flag)) ok = false;
-      if (ok && !mbar_wait(p_free(pb), (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
       const bool diag = (j == n_kt - 1);
-      const uint32_t prow = base + Cfg::OFF_P + pb * Cfg::P_BYTES + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
       // both 32-column loads of this thread's 64 keys go out before one wait; S is then free for the next QK^T
       uint32_t sraw[2][32];
       tmem_ld_32x32_nowait(tmem_s + lane_off + (uint32_t)(half * 64), sraw[0]);
@@ -205,35 +216,39 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_tcgen05_kernel(const __
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
+      uint32_t packed[32];           // 64 probabilities as bf16 pairs: cell i = keys 2i (low half), 2i+1 (high half)
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
         const int key0 = j * AK + c * 32;
-        uint32_t packed[16];
+        if (diag && c > quad) {      // every key of these 32 lies after every row of this warp: no exponentials needed
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(sraw[cc][i]), p.scale_log2, -p.bound_log2));
-          float p1 = ex2_approx(fmaf(__uint_as_float(sraw[cc][i + 1]), p.scale_log2, -p.bound_log2));
-          if (diag) {
-            if (key0 + i > qrow) p0 = 0.f;
-            if (key0 + i + 1 > qrow) p1 = 0.f;
+          for (int i = 0; i < 16; ++i) packed[cc * 16 + i] = 0u;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = ex2_approx(fmaf(__uint_as_float(sraw[cc][i]), p.scale_log2, -p.bound_log2));
+            float p1 = ex2_approx(fmaf(__uint_as_float(sraw[cc][i + 1]), p.scale_log2, -p.bound_log2));
+            if (diag) {
+              if (key0 + i > qrow) p0 = 0.f;
+              if (key0 + i + 1 > qrow) p1 = 0.f;
+            }
+            // bf16 by truncation: one byte-permute on the integer pipe instead of a conversion on the (saturated)
+            // special-function pipe.  The truncation bias cancels: the denominator is summed from the same bf16 values.
+            packed[cc * 16 + (i >> 1)] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
           }
-          // bf16 by truncation: one byte-permute on the integer pipe instead of a conversion on the (saturated)
-          // special-function pipe.  The truncation bias cancels: the denominator is summed from the same bf16 values.
-          packed[i >> 1] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
-        }
-        // 32 keys = 64 bytes = four 16-byte pieces of this row inside half (c >> 1)
-        const uint32_t half_base = prow + (uint32_t)(c >> 1) * (AQ * 128);
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int piece = (c & 1) * 4 + q4;
-          st_shared_v4(half_base + (uint32_t)((piece ^ (r & 7)) << 4),
-                       make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]));
         }
       }
-      fence_proxy_async_smem();
+      // the P cells may be overwritten once the PV MMAs of the previous tile have read them
+      if (!mbar_wait(p_free, (uint32_t)((j & 1) ^ 1), abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      tmem_st_32x32(tmem_p + lane_off + (uint32_t)(half * 32), packed);
+      tmem_wait_st();
+      tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full(pb));
+      if (lane == 0) mbar_arrive(p_full);
     }
     // ---- finish: O / l -> bf16, token-major ----
     if (ok && !mbar_wait(o_full, 0u, abort_flag)) ok = false;
@@ -300,17 +315,18 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-// [rows, hd] bf16 matrix, boxes of 128 rows x hd columns, swizzle width = row width
-static int make_rows_map(CUtensorMap* map, const void* ptr, uint64_t rows, int hd) {
+// [heads, S, hd] bf16 tensor, boxes of 128 rows x hd columns of one head, swizzle width = row width; rows past S read
+// as zero
+static int make_rows_map(CUtensorMap* map, const void* ptr, uint64_t heads, uint64_t S, int hd) {
   auto fn = encode_fn();
   HB_REQUIRE(fn != nullptr, HB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t gdim[2] = {(cuuint64_t)hd, rows};
-  cuuint64_t gstride[1] = {(cuuint64_t)hd * 2};
-  cuuint32_t box[2] = {(cuuint32_t)hd, 128};
-  cuuint32_t estr[2] = {1, 1};
+  cuuint64_t gdim[3] = {(cuuint64_t)hd, S, heads};
+  cuuint64_t gstride[2] = {(cuuint64_t)hd * 2, (cuuint64_t)S * hd * 2};
+  cuuint32_t box[3] = {(cuuint32_t)hd, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapSwizzle sw = hd == 64 ? CU_TENSOR_MAP_SWIZZLE_128B
                                          : (hd == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   HB_REQUIRE(r == CUDA_SUCCESS, HB200_ERR_CUDA, "cuTensorMapEncodeTiled (attention) failed with CUresult %d", (int)r);
@@ -321,12 +337,12 @@ template <int HD>
 static int launch_att(const void* q, const void* k, const void* v, const AttParams& p, int B, cudaStream_t st) {
   using Cfg = AttCfg<HD>;
   CUtensorMap tq, tk, tv;
-  HB_PROPAGATE(make_rows_map(&tq, q, (uint64_t)B * p.H * p.S, HD));
-  HB_PROPAGATE(make_rows_map(&tk, k, (uint64_t)B * p.KV * p.S, HD));
-  HB_PROPAGATE(make_rows_map(&tv, v, (uint64_t)B * p.KV * p.S, HD));
+  HB_PROPAGATE(make_rows_map(&tq, q, (uint64_t)B * p.H, (uint64_t)p.S, HD));
+  HB_PROPAGATE(make_rows_map(&tk, k, (uint64_t)B * p.KV, (uint64_t)p.S, HD));
+  HB_PROPAGATE(make_rows_map(&tv, v, (uint64_t)B * p.KV, (uint64_t)p.S, HD));
   auto kern = attention_tcgen05_kernel<HD>;
   HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(Cfg::SMEM_BYTES)));
-  dim3 grid((p.S + AQ - 1) / AQ, p.H, B);
+  dim3 grid(B * p.H, (p.S + AQ - 1) / AQ, 1);
   kern<<<grid, ATT_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
   HB_LAUNCH_CHECK();
   return 0;

@@ -2,62 +2,93 @@
 //
 //   qkv [B,S,lat+2kvd] (read once)  ->  q [B,H,S,hd], k [B,KV,S,hd], v [B,KV,S,hd]  (written once)
 //
-// One CTA = 128 tokens of one sequence (+ a 4-token causal halo).
-//   phase 1 (all 8 warps)
-//     - the q|k columns of tokens t0-4 .. t0+141 go to shared memory (zero outside the sequence);
-//     - conv1 (grouped k=3 causal conv, 1/9 of the FLOPs) per head on mma.sync; its bf16 result y1 is written to
-//       shared memory in the tensor core's un-swizzled K-major "core matrix" layout with the 8-row groups packed
-//       back to back: [16-byte channel chunk][row][8 channels].  In that layout a shift by j rows is a shift of
-//       the operand's start address by 16*j bytes, so the three taps of the dense conv are three A-operand
-//       descriptors over the same tile - no im2col copy.
-//   phase 2 (warp-specialised)
-//     - warp 0: TMA producer streaming the repacked conv2 weight [C_out, 3*C_in] (128B-swizzled 64-wide K blocks)
-//       through a 4-stage ring that re-uses the shared memory of the phase-1 input tile;
-//     - warp 1: one thread issues tcgen05.mma M128 x N256 x K16 (q) and M128 x N64 x K16 (k): conv2 is a
-//       [128, 768] x [768, 256] contraction per tile with fp32 accumulators in TMEM;
-//     - warps 2-3: value shift (first half of the v channels from this token, second half from the previous one),
-//       a pure copy global -> global that overlaps the contraction;
-//     - warps 4-7: epilogue, thread = token.  While the MMAs run each thread computes the QK-mean vectors of its
-//       token from its qkv row (L2-resident) and fetches its RoPE row; then per head: tcgen05.ld of the head's
-//       32 accumulator columns, + 0.5*mean, L2 norm (in-thread, no shuffles), key temperature, RoPE, 64-byte store.
+// Persistent: one CTA per SM walks over tiles of 126 tokens (one sequence each) and keeps four things in flight at
+// once - the input of the NEXT tile on its way from HBM, the two convolutions of the CURRENT tile on the tensor
+// cores, the conv weights streaming from L2, and the epilogue of the PREVIOUS accumulators.
 //
-// Every mbarrier wait is bounded; on expiry the CTA flags the error, frees its TMEM and returns.
+// Both convolutions are tcgen05.mma contractions over the same operand layout.  A tile's q|k columns sit in shared
+// memory as 40 "planes" of 8 channels: plane[c8][row][8 channels], rows 16 bytes apart.  That is the tensor core's
+// un-swizzled K-major core-matrix layout with the 8-row groups packed back to back, in which a shift by j rows is a
+// shift of the operand's start address by 16*j bytes - so the three taps of a causal k=3 convolution are three
+// A-operand descriptors over one tile, no im2col copy:
+//   conv1 (grouped, per head):  y1[128 rows, hd]   = sum_j  x [rows j..j+127, head's channels] W1_j^T      K = 3*hd
+//   conv2 (dense):              out[128 rows, C]   = sum_j  y1[rows j..j+127, all channels]    W2_j^T      K = 3*C
+// y1 row r is token t0-2+r, x row r is token t0-4+r, output row m is token t0+m.  x and y1 hold 128 rows each, and
+// the taps of rows near the end read up to two rows past the plane (the first rows of the next plane: finite data),
+// so y1 rows 0..125 and output rows 0..123 are exact: 124 tokens per tile, the rest is thrown away.  (At 2048 tokens
+// per sequence that is 17 tiles, the same count as 126 would give.)
+// Rows before the sequence start are zero in x, hence zero in y1 (no bias): the reference's causal padding of both
+// convolutions.  The x planes are written by TMA: one [8 channels x 128 rows] box per plane from a [B][S][C] tensor
+// map, whose out-of-range rows (before the sequence, after it) arrive as zeros.
+//
+// Roles (15 warps):
+//   warp 0      weight producer: TMA streams, in consumption order, the conv1 weight of 64 channels at a time, the query
+//               conv2 weight in [256 out-channels x 32 K] blocks (64B-swizzled) and the key conv2 weight in [64 x 64]
+//               blocks (128B-swizzled) through a ring of four 16 KB stages;
+//   warp 1      MMA issuer: the whole warp runs the loop with warp-uniform operands and one elected lane issues (a
+//               single-lane loop costs ~46 clocks per MMA to issue, this form 24-34, and the conv1 / key MMAs hold less
+//               math than that): conv1 in five rounds of 64 channels into a double-buffered 64-column accumulator, then
+//               conv2 of the queries (M128 x N256) and of the keys (N64);
+//   warps 2-5   (a) drain each conv1 round: TMEM -> bf16 -> y1 planes; (b) copy the tile's value columns with the
+//               one-token shift; (c) epilogue of the key accumulator (thread = token): + 0.5 * mean query (summed from
+//               the x planes while they are in shared memory), L2 norm, temperature, RoPE;
+//   warps 6-13  epilogue of the query accumulator, thread = token, two warps per TMEM lane quadrant, four heads each:
+//               + 0.5 * mean key (from the x planes), L2 norm, RoPE, 64-byte stores - while the key conv and the next
+//               tile's conv1 run;
+//   warp 14     x loader: as soon as conv1 and the mean readers are done with the x planes, one lane issues the 40 TMA
+//               loads of the next tile's planes (a 16-byte-row box is slow to issue, ~230 clocks each, which is why
+//               this is nobody else's job); they land while conv2 of the current tile runs.
+// The conv2 K blocks of a tile are visited in an order rotated by the tile's position in its sequence: CTAs that run
+// side by side then stream different weight blocks instead of all hitting the same L2 lines at once, and the order
+// (hence the fp32 summation order) stays a function of the token position alone, so a sequence gives the same bits
+// whatever batch it is part of.
+//
+// TMEM (512 columns): queries at 0, keys at 256, conv1 rounds at 320 / 384.
+// Every mbarrier wait is bounded; on expiry the CTA raises its abort flag, every role leaves its loop, the error is
+// reported through err_flag, TMEM is released and the kernel returns.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
 #include <mutex>
 
 #include "common.cuh"
-#include "mma.cuh"
 #include "tcgen05.cuh"
+#include "tma_host.cuh"
 
 namespace hb200 {
 
 namespace pretc {
-constexpr int TT = 128;                  // output tokens per tile
+constexpr int TT = 124;                  // output tokens per tile
+constexpr int MR = 128;                  // rows of every MMA
 constexpr int LAT = 256, KVD = 64, C = LAT + KVD;
-constexpr int YROWS = 144;               // y1 rows computed (t0-2 .. t0+141): nine m16 tiles, 130 are needed
-constexpr int XROWS = YROWS + 2;         // x rows held (t0-4 .. t0+141)
-constexpr int LDX = C + 8;               // padded x row (bf16 elements): conflict-free fragment loads
-constexpr int CHUNKS = C / 8;            // 16-byte channel chunks of y1
-constexpr int CHUNK_BYTES = YROWS * 16;  // one chunk: all rows, 16 bytes each
-constexpr int STAGE_BYTES = 256 * 64 * 2;   // one conv2 weight block: 256 rows x 64 K (k-conv blocks use 8 KB of it)
+constexpr int PLANES = C / 8;            // 40 planes of 8 channels
+constexpr int XROWS = MR;                // x rows held: tokens t0-4 .. t0+123 (one TMA box of 128 rows per plane)
+constexpr int XP_PLANE = XROWS * 16;
+constexpr int XP_BYTES = PLANES * XP_PLANE;
+constexpr int Y1_PLANE = MR * 16;
+constexpr int Y1_BYTES = PLANES * Y1_PLANE;
+constexpr int STAGE_BYTES = 16384;
 constexpr int STAGES = 4;
-constexpr int RING_BYTES = STAGES * STAGE_BYTES;          // 128 KB; its first 96 KB hold x during phase 1
-constexpr int Y1_BYTES = CHUNKS * CHUNK_BYTES;            // 90 KB
-constexpr int OFF_Y1 = RING_BYTES;
-constexpr int OFF_BAR = OFF_Y1 + Y1_BYTES;
+constexpr int OFF_RING = 0;
+constexpr int OFF_XP = STAGES * STAGE_BYTES;
+constexpr int OFF_Y1 = OFF_XP + XP_BYTES;
+constexpr int OFF_TAIL = OFF_Y1 + Y1_BYTES;   // 64 zero bytes: the last plane's two overhanging rows
+constexpr int OFF_BAR = OFF_TAIL + 64;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-static_assert(XROWS * LDX * 2 <= 3 * STAGE_BYTES, "x tile must fit in the first three ring stages");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
-constexpr int QBLOCKS = 3 * LAT / 64;    // 12 K blocks of the q conv2
-constexpr int KBLOCKS = 3 * KVD / 64;    // 3 K blocks of the k conv2
-constexpr uint32_t TMEM_COLS = 512;      // q accumulator 0..255, k accumulator 256..319
+constexpr int ROUND_CH = 64;             // channels per conv1 round
+constexpr int ROUNDS = C / ROUND_CH;     // 5
+constexpr int QBLOCKS = 3 * LAT / 32;    // 24 K blocks of 32 of the q conv2 (a [256 x 32] weight block fills one stage)
+constexpr int KBLOCKS = 3 * KVD / 64;    // 3 K blocks of 64 of the k conv2
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_Q = 0, COL_K = 256, COL_C1 = 320;
+constexpr int WARPS = 15, THREADS = WARPS * 32;
+constexpr int DL_WARP0 = 2, DL_WARPS = 4, DL_THREADS = DL_WARPS * 32;
+constexpr int E_WARP0 = 6, X_WARP = 14;
 }  // namespace pretc
 
 struct PreTcParams {
   const __nv_bfloat16* qkv;
-  const __nv_bfloat16* w1;   // [lat+kvd][3*hd]
   const float* cos_t;
   const float* sin_t;
   const float* temp;
@@ -65,6 +96,7 @@ struct PreTcParams {
   __nv_bfloat16* k;
   __nv_bfloat16* v;
   int B, S, H, KV;
+  int n_tiles, tiles_per_seq;
   int32_t* err_flag;
 };
 
@@ -95,309 +127,389 @@ __device__ __forceinline__ void finish_head(const float* acc, const float* coupl
   }
 }
 
+// 0.5 * mean over `heads` head vectors of HD channels, read from the x planes in shared memory: `plane0_row` is the
+// address of this token's 16 bytes in the first plane of the channel range, planes are `plane_stride` bytes apart
 template <int HD>
-__global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_constant__ CUtensorMap tma_w2q,
-                                                              const __grid_constant__ CUtensorMap tma_w2k,
-                                                              const PreTcParams p) {
+__device__ __forceinline__ void head_mean_planes(uint32_t plane0_row, uint32_t plane_stride, int heads, float (&m)[HD]) {
+#pragma unroll
+  for (int d = 0; d < HD; ++d) m[d] = 0.f;
+  const int pieces = heads * HD / 8;
+#pragma unroll 1
+  for (int i0 = 0; i0 < pieces; i0 += 8) {
+    uint4 raw[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) raw[u] = ld_shared_v4(plane0_row + (uint32_t)(i0 + u) * plane_stride);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint32_t w4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+      const int d0 = (u * 8) % HD;       // i0 is a multiple of 8 pieces = 64 channels, a multiple of HD
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        m[d0 + 2 * jj] += __uint_as_float(w4[jj] << 16);
+        m[d0 + 2 * jj + 1] += __uint_as_float(w4[jj] & 0xffff0000u);
+      }
+    }
+  }
+  const float s = 0.5f / (float)heads;
+#pragma unroll
+  for (int d = 0; d < HD; ++d) m[d] *= s;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const __grid_constant__ CUtensorMap tma_x,
+                                                                         const __grid_constant__ CUtensorMap tma_w1,
+                                                                         const __grid_constant__ CUtensorMap tma_w2q,
+                                                                         const __grid_constant__ CUtensorMap tma_w2k,
+                                                                         const PreTcParams p) {
   using namespace pretc;
   static_assert(HD == 16 || HD == 32, "head_dim 16 or 32");
+  constexpr int QKV_LD = LAT + 2 * KVD;
+  constexpr int W1_BYTES = ROUND_CH * 3 * HD * 2;   // conv1 weight of one round: 64 rows x 3*hd
+  constexpr int KCHUNKS1 = 3 * HD / 8;              // 16-byte K chunks of a conv1 weight row
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (s_addr(smem_dyn) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_dyn + (base - s_addr(smem_dyn));
-  __nv_bfloat16* X = reinterpret_cast<__nv_bfloat16*>(base_ptr);                 // [XROWS][LDX], phase 1 only
-  __nv_bfloat16* Y1 = reinterpret_cast<__nv_bfloat16*>(base_ptr + OFF_Y1);        // [CHUNKS][YROWS][8]
-  const uint32_t y1_addr = base + OFF_Y1;
+  const uint32_t xp_addr = base + OFF_XP, y1_addr = base + OFF_Y1;
   const uint32_t bars = base + OFF_BAR;
-  auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 32u + 8u * s; };
-  const uint32_t acc_full = bars + 64u;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + OFF_BAR + 72);
+  auto w_full = [&](int s) { return bars + 8u * s; };
+  auto w_empty = [&](int s) { return bars + 32u + 8u * s; };
+  const uint32_t xp_full = bars + 64u, y1_full = bars + 72u;
+  auto c1_full = [&](int b) { return bars + 80u + 8u * b; };
+  auto c1_free = [&](int b) { return bars + 96u + 8u * b; };
+  const uint32_t q_full = bars + 112u, q_free = bars + 128u;
+  const uint32_t k_full = bars + 144u, k_free = bars + 152u, xp_free = bars + 160u;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + OFF_BAR + 176);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int H = p.H, KV = p.KV, S = p.S;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int g = lane >> 2, t4 = lane & 3;
-  const int tiles_per_seq = (S + TT - 1) / TT;
-  const int b = blockIdx.x / tiles_per_seq;
-  const int t0 = (blockIdx.x % tiles_per_seq) * TT;
-  constexpr int QKV_LD = LAT + 2 * KVD;
-  const __nv_bfloat16* qkv_b = p.qkv + (size_t)b * S * QKV_LD;
+  const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // tiles blockIdx.x + it*gridDim.x
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+      mbar_init(w_full(s), 1);
+      mbar_init(w_empty(s), 1);
     }
-    mbar_init(acc_full, 1);
+    mbar_init(xp_full, 1);
+    mbar_init(xp_free, 1 + DL_WARPS + 8);          // conv1 complete (MMA commit) + the 12 warps that read their means from x
+    mbar_init(y1_full, DL_WARPS);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(c1_full(b), 1);
+      mbar_init(c1_free(b), DL_WARPS);
+    }
+    mbar_init(q_full, 1);
+    mbar_init(q_free, 8);
+    mbar_init(k_full, 1);
+    mbar_init(k_free, DL_WARPS);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    // the first weight block starts its trip now: ring slot i lives in physical stage (i + 3) % 4, and the last
-    // physical stage is the one the input tile does not occupy during phase 1
-    mbar_arrive_expect_tx(full_bar(0), LAT * 64 * 2);
-    tma_load_2d(base + (STAGES - 1) * STAGE_BYTES, &tma_w2q, 0, 0, full_bar(0));
   }
+  if (tid < 4) reinterpret_cast<uint4*>(base_ptr + OFF_TAIL)[tid] = make_uint4(0u, 0u, 0u, 0u);
   if (warp == 1) tmem_alloc(s_addr(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
-
-  // ---------------- phase 1a: q|k columns of the tile -> shared memory ----------------
-  // every 16-byte piece is its own asynchronous copy (23 per thread, all in flight at once: one memory latency for the
-  // whole tile instead of one per batch of register-staged loads); rows outside the sequence are zero
-  {
-    constexpr int PIECES = XROWS * (C / 8);
-    const uint32_t x_s = s_addr(X);
-    for (int idx = tid; idx < PIECES; idx += 256) {
-      const int r = idx / (C / 8), piece = idx % (C / 8);
-      const int tok = t0 - 4 + r;
-      const uint32_t dst = x_s + (uint32_t)(r * LDX + piece * 8) * 2u;
-      if (tok >= 0 && tok < S) cp_async16(dst, qkv_b + (size_t)tok * QKV_LD + piece * 8);
-      else st_shared_v4(dst, make_uint4(0u, 0u, 0u, 0u));
-    }
-    cp_async16_commit();
-    cp_async16_wait_all();
-  }
+  fence_proxy_async_smem();
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // ---------------- phase 1b: conv1 (grouped) on mma.sync: y1 row r <-> token t0-2+r ----------------
-  // Work units are (head, m16 tile), head-major; each warp takes a contiguous range, so it changes head at most
-  // twice and keeps the head's whole weight block (3*hd x hd) in registers as B fragments: the inner loop touches
-  // shared memory only (the 61 KB weight would not survive in the little L1 left beside 224 KB of shared memory).
-  {
-    constexpr int NT1 = HD / 8, KS1 = 3 * HD / 16, MT = YROWS / 16;
-    const int units = MT * (H + KV);
-    const int u_begin = (units * warp) / 8, u_end = (units * (warp + 1)) / 8;
-    uint32_t bfrag[KS1][NT1][2];
-    int cur_head = -1;
-    for (int u = u_begin; u < u_end; ++u) {
-      const int hg = u / MT, mt = u % MT;
-      const int cb = hg * HD;
-      if (hg != cur_head) {
-        cur_head = hg;
-#pragma unroll
-        for (int ks = 0; ks < KS1; ++ks)
-#pragma unroll
-          for (int nt = 0; nt < NT1; ++nt) {
-            const __nv_bfloat16* wr = p.w1 + (size_t)(cb + nt * 8 + g) * (3 * HD) + ks * 16 + 2 * t4;
-            bfrag[ks][nt][0] = __ldg(reinterpret_cast<const unsigned int*>(wr));
-            bfrag[ks][nt][1] = __ldg(reinterpret_cast<const unsigned int*>(wr + 8));
-          }
-      }
-      float acc[NT1][4];
-#pragma unroll
-      for (int i = 0; i < NT1; ++i)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) acc[i][c] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < KS1; ++ks) {
-        const int kk0 = ks * 16;
-        const int j = kk0 / HD, c0 = kk0 % HD;
-        const __nv_bfloat16* r0 = X + (mt * 16 + g + j) * LDX + cb + c0 + 2 * t4;
-        const __nv_bfloat16* r1 = r0 + 8 * LDX;
-        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(r0);
-        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(r1);
-        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(r0 + 8);
-        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(r1 + 8);
-#pragma unroll
-        for (int nt = 0; nt < NT1; ++nt) mma_bf16_16816(acc[nt], a0, a1, a2, a3, bfrag[ks][nt][0], bfrag[ks][nt][1]);
-      }
-      // C fragment (row, cols 2t..2t+1 of n-tile nt) -> chunk (cb/8 + nt), row, element 2t
-#pragma unroll
-      for (int nt = 0; nt < NT1; ++nt) {
-        __nv_bfloat16* y = Y1 + (size_t)(cb / 8 + nt) * (YROWS * 8) + (mt * 16 + g) * 8 + 2 * t4;
-        *reinterpret_cast<uint32_t*>(y) = pack_bf16x2(acc[nt][0], acc[nt][1]);
-        *reinterpret_cast<uint32_t*>(y + 8 * 8) = pack_bf16x2(acc[nt][2], acc[nt][3]);
-      }
-    }
-  }
-  // y1 was written through the generic proxy and is read by the tensor core; x is about to be overwritten by TMA
-  fence_proxy_async_smem();
-  __syncthreads();
-
-  // ---------------- phase 2: warp-specialised ----------------
-  // epilogue geometry: thread = token r of the tile, for warp w and warp w + 4 alike (TMEM lane quarter w % 4)
-  const int quad = warp & 3;
-  const int r = quad * 32 + lane;
-  const int tok = t0 + r;
-  const bool valid = tok < S;
-  const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-  float qm[HD], km[HD], cs[HD / 2], sn[HD / 2];
   if (warp == 0) {
+    // ------------------------------ weight producer ------------------------------
     if (lane == 0) {
-      int stage = 1;                                   // block 0 was issued at kernel start
+      int stage = 0;
       uint32_t phase = 0;
-      for (int kb = 1; kb < QBLOCKS + KBLOCKS; ++kb) {
-        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
-        const uint32_t dst = base + ((stage + STAGES - 1) % STAGES) * STAGE_BYTES;
-        if (kb < QBLOCKS) {
-          mbar_arrive_expect_tx(full_bar(stage), LAT * 64 * 2);
-          tma_load_2d(dst, &tma_w2q, kb * 64, 0, full_bar(stage));
-        } else {
-          mbar_arrive_expect_tx(full_bar(stage), KVD * 64 * 2);
-          tma_load_2d(dst, &tma_w2k, (kb - QBLOCKS) * 64, 0, full_bar(stage));
+      bool ok = true;
+      auto next_stage = [&]() -> uint32_t {      // waits for the next ring slot, returns its address (0 on abort)
+        if (!mbar_wait(w_empty(stage), phase ^ 1u, abort_flag)) { ok = false; return 0u; }
+        return base + OFF_RING + stage * STAGE_BYTES;
+      };
+      auto advance = [&]() { if (++stage == STAGES) { stage = 0; phase ^= 1u; } };
+      for (int it = 0; ok && it < my_tiles; ++it) {
+        for (int rd = 0; ok && rd < ROUNDS; ++rd) {                 // conv1 weight of 64 output channels
+          const uint32_t dst = next_stage();
+          if (!ok) break;
+          mbar_arrive_expect_tx(w_full(stage), W1_BYTES);
+#pragma unroll 1
+          for (int kc = 0; kc < KCHUNKS1; ++kc) tma_load_2d(dst + kc * (ROUND_CH * 16), &tma_w1, kc * 8, rd * ROUND_CH, w_full(stage));
+          advance();
         }
-        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        const int pos = ((int)blockIdx.x + it * (int)gridDim.x) % p.tiles_per_seq;
+        for (int i = 0; ok && i < QBLOCKS; ++i) {                   // conv2 weight of the queries: all 256 output channels x 32 K
+          const uint32_t dst = next_stage();
+          if (!ok) break;
+          const int kb = (i + pos * 7) % QBLOCKS;
+          mbar_arrive_expect_tx(w_full(stage), LAT * 32 * 2);
+          tma_load_2d(dst, &tma_w2q, kb * 32, 0, w_full(stage));
+          advance();
+        }
+        for (int kb = 0; ok && kb < KBLOCKS; ++kb) {                // conv2 weight of the keys
+          const uint32_t dst = next_stage();
+          if (!ok) break;
+          mbar_arrive_expect_tx(w_full(stage), KVD * 64 * 2);
+          tma_load_2d(dst, &tma_w2k, kb * 64, 0, w_full(stage));
+          advance();
+        }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_q = make_idesc(128, LAT);
-      constexpr uint32_t idesc_k = make_idesc(128, KVD);
+    // ------------------------------ MMA issuer (whole warp, one elected lane issues) ------------------------------
+    {
+      constexpr uint32_t idesc_c1 = make_idesc(MR, HD);
+      constexpr uint32_t idesc_q = make_idesc(MR, LAT);
+      constexpr uint32_t idesc_k = make_idesc(MR, KVD);
+      // descriptor templates; per MMA only the start-address field (16-byte units, low bits) moves
+      const uint64_t dx0 = make_smem_desc_ex(xp_addr, 128, 0u, XP_PLANE);           // x planes: 8-row groups 128 B apart
+      const uint64_t dy0 = make_smem_desc_ex(y1_addr, 128, 0u, Y1_PLANE);           // y1 planes
+      const uint64_t dw1 = make_smem_desc_ex(base + OFF_RING, 128, 0u, ROUND_CH * 16);   // conv1 weight [K chunk][64 rows][16 B]
+      const uint64_t dwq = make_smem_desc_ex(base + OFF_RING, 512, 4u, 16);         // [256 rows][64 B], 64B swizzle
+      const uint64_t dwk = make_smem_desc(base + OFF_RING);                         // [64 rows][128 B], 128B swizzle
       int stage = 0;
-      uint32_t phase = 0;
+      uint32_t phase = 0, c1_use[2] = {0u, 0u};
       bool ok = true;
-      for (int kb = 0; ok && kb < QBLOCKS + KBLOCKS; ++kb) {
-        if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+      auto wait_stage = [&]() -> uint32_t {      // returns the stage's offset in 16-byte units
+        if (!mbar_wait(w_full(stage), phase, abort_flag)) { ok = false; return 0u; }
         tcgen05_fence_after();
-        const bool is_q = kb < QBLOCKS;
-        const int kq = is_q ? kb : kb - QBLOCKS;
-        const int cin = is_q ? LAT : KVD;
-        const int j = (kq * 64) / cin;                         // conv tap of this K block
-        const int ch0 = (kq * 64) % cin + (is_q ? 0 : LAT);    // first y1 channel of this K block
-        const uint32_t sb = base + ((stage + STAGES - 1) % STAGES) * STAGE_BYTES;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          // A: y1 rows j..j+127, 16 channels = two 16-byte chunks CHUNK_BYTES apart; 8-row groups are 128 B apart
-          const uint32_t a_addr = y1_addr + (uint32_t)((ch0 + ks * 16) / 8) * CHUNK_BYTES + (uint32_t)j * 16u;
-          const uint64_t da = make_smem_desc_ex(a_addr, 128, 0u, CHUNK_BYTES);
-          const uint64_t db = make_smem_desc(sb + ks * 32);
-          if (is_q)
-            umma_bf16(tmem_base, da, db, idesc_q, (kq | ks) ? 1u : 0u);
-          else
-            umma_bf16(tmem_base + 256u, da, db, idesc_k, (kq | ks) ? 1u : 0u);
-        }
-        umma_commit(empty_bar(stage));
+        return (uint32_t)(stage * STAGE_BYTES) >> 4;
+      };
+      auto release_stage = [&]() {
+        umma_commit_elect(w_empty(stage));
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      };
+      for (int it = 0; ok && it < my_tiles; ++it) {
+        const uint32_t tpar = (uint32_t)(it & 1);
+        if (!mbar_wait(xp_full, tpar, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        // ---- conv1: five rounds of 64 channels, each head its own M128 x N=hd x K=3*hd contraction ----
+        for (int rd = 0; ok && rd < ROUNDS; ++rd) {
+          const int cb = rd & 1;
+          const uint32_t so = wait_stage();
+          if (!ok) break;
+          if (!mbar_wait(c1_free(cb), (c1_use[cb] & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint64_t dx_rd = dx0 + (uint64_t)((uint32_t)(rd * (ROUND_CH / 8) * XP_PLANE) >> 4);
+          const uint64_t dw_rd = dw1 + (uint64_t)so;
+          const uint32_t d_rd = tmem_base + COL_C1 + (uint32_t)(cb * ROUND_CH);
+#pragma unroll
+          for (int hh = 0; hh < ROUND_CH / HD; ++hh) {
+#pragma unroll
+            for (int ks = 0; ks < 3 * HD / 16; ++ks) {
+              const int j = (ks * 16) / HD, ci0 = (ks * 16) % HD;
+              // A: x rows j..j+127 of the 16 input channels hh*HD+ci0.. of this round (two planes)
+              const uint32_t a_off = (uint32_t)(((hh * HD + ci0) / 8) * XP_PLANE + j * 16) >> 4;
+              // B: this head's rows of the round's weight block, K chunks 2ks and 2ks+1
+              const uint32_t b_off = (uint32_t)((2 * ks) * (ROUND_CH * 16) + (hh * HD) * 16) >> 4;
+              umma_bf16_elect(d_rd + (uint32_t)(hh * HD), dx_rd + a_off, dw_rd + b_off, idesc_c1, ks ? 1u : 0u);
+            }
+          }
+          release_stage();
+          umma_commit_elect(c1_full(cb));
+          ++c1_use[cb];
+        }
+        if (!ok) break;
+        umma_commit_elect(xp_free);              // every conv1 MMA of this tile has read its x planes
+        // ---- conv2 ----
+        const int pos = ((int)blockIdx.x + it * (int)gridDim.x) % p.tiles_per_seq;   // tile position in its sequence
+        if (!mbar_wait(y1_full, tpar, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(q_free, tpar ^ 1u, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        for (int i = 0; ok && i < QBLOCKS; ++i) {
+          const uint32_t so = wait_stage();
+          if (!ok) break;
+          const int kb = (i + pos * 7) % QBLOCKS;          // rotated start, same order as the producer's
+          const int j = (kb * 32) / LAT, ch0 = (kb * 32) % LAT;
+          const uint64_t da = dy0 + (uint64_t)((uint32_t)((ch0 / 8) * Y1_PLANE + j * 16) >> 4);
+          const uint64_t db = dwq + (uint64_t)so;
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks)
+            umma_bf16_elect(tmem_base + COL_Q, da + (uint64_t)((uint32_t)(ks * 2 * Y1_PLANE) >> 4), db + (uint64_t)(ks * 2), idesc_q,
+                            (i | ks) ? 1u : 0u);
+          release_stage();
+        }
+        if (!ok) break;
+        umma_commit_elect(q_full);
+        if (!mbar_wait(k_free, tpar ^ 1u, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        for (int kb = 0; ok && kb < KBLOCKS; ++kb) {
+          const uint32_t so = wait_stage();
+          if (!ok) break;
+          const int j = (kb * 64) / KVD, ch0 = LAT + (kb * 64) % KVD;
+          const uint64_t da = dy0 + (uint64_t)((uint32_t)((ch0 / 8) * Y1_PLANE + j * 16) >> 4);
+          const uint64_t db = dwk + (uint64_t)so;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_bf16_elect(tmem_base + COL_K, da + (uint64_t)((uint32_t)(ks * 2 * Y1_PLANE) >> 4), db + (uint64_t)(ks * 2), idesc_k,
+                            (kb | ks) ? 1u : 0u);
+          release_stage();
+        }
+        if (ok) umma_commit_elect(k_full);
       }
-      if (ok) umma_commit(acc_full);
     }
     __syncwarp();
-  } else if (warp < 4) {
-    // ---- value shift: warps 2,3 copy 128 tokens x 128 bytes as 16-byte pieces, 16 loads in flight per thread ----
-    const int vt = tid - 64;                       // 0..63
-    constexpr int VP = KVD / 8;                    // pieces per token
+  } else if (warp < E_WARP0) {
+    // ------------------ conv1 drain + value shift + key epilogue (warps 2..5) ------------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;                        // y1 row this thread drains / token row of the key epilogue
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const int dt = tid - DL_WARP0 * 32;                    // 0..127
+    const float temp = *p.temp;
+    uint32_t c1_use[2] = {0u, 0u};
+    bool ok = true;
+    constexpr int VP = KVD / 8;                            // 16-byte pieces of a token's value columns
+    constexpr int VPT = (TT * VP + DL_THREADS - 1) / DL_THREADS;   // pieces per thread (8)
+    for (int it = 0; ok && it < my_tiles; ++it) {
+      const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+      const int b = tile / p.tiles_per_seq, t0 = (tile % p.tiles_per_seq) * TT;
+      const int tok = t0 + r;
+      const bool valid = r < TT && tok < S;
+      const __nv_bfloat16* qkv_b = p.qkv + (size_t)b * S * QKV_LD;
+      float mean[HD], cs[HD / 2], sn[HD / 2];
+#pragma unroll
+      for (int i = 0; i < HD / 2; i += 4) {
+        const float4 c4 = valid ? *reinterpret_cast<const float4*>(p.cos_t + (size_t)tok * (HD / 2) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 s4 = valid ? *reinterpret_cast<const float4*>(p.sin_t + (size_t)tok * (HD / 2) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        cs[i] = c4.x; cs[i + 1] = c4.y; cs[i + 2] = c4.z; cs[i + 3] = c4.w;
+        sn[i] = s4.x; sn[i + 1] = s4.y; sn[i + 2] = s4.z; sn[i + 3] = s4.w;
+      }
+      // mean query of this token from the x planes (x row of output row r is r + 4; rows past 127 belong to no token)
+      if (!mbar_wait(xp_full, (uint32_t)(it & 1), abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      head_mean_planes<HD>(xp_addr + (uint32_t)((r + 4) & (XROWS - 1)) * 16u, XP_PLANE, H, mean);   // keys are coupled with the mean query
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xp_free);
+      for (int rd = 0; rd < ROUNDS; ++rd) {
+        const int cb = rd & 1;
+        if (!mbar_wait(c1_full(cb), c1_use[cb] & 1u, abort_flag)) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        ++c1_use[cb];
+        tcgen05_fence_after();
+        uint32_t raw[2][32];
+        tmem_ld_32x32_nowait(tmem_base + lane_off + COL_C1 + (uint32_t)(cb * ROUND_CH), raw[0]);
+        tmem_ld_32x32_nowait(tmem_base + lane_off + COL_C1 + (uint32_t)(cb * ROUND_CH + 32), raw[1]);
+        tmem_wait_ld();
+        tcgen05_fence_before();
+        // 64 channels of this row -> eight 16-byte pieces, one per plane
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc) {
+          const uint32_t* s8 = &raw[pc >> 2][(pc & 3) * 8];
+          uint4 o;
+          o.x = pack_bf16x2_rn(__uint_as_float(s8[0]), __uint_as_float(s8[1]));
+          o.y = pack_bf16x2_rn(__uint_as_float(s8[2]), __uint_as_float(s8[3]));
+          o.z = pack_bf16x2_rn(__uint_as_float(s8[4]), __uint_as_float(s8[5]));
+          o.w = pack_bf16x2_rn(__uint_as_float(s8[6]), __uint_as_float(s8[7]));
+          st_shared_v4(y1_addr + (uint32_t)(rd * 8 + pc) * Y1_PLANE + (uint32_t)r * 16u, o);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(c1_free(cb));
+          if (rd == ROUNDS - 1) mbar_arrive(y1_full);
+        }
+      }
+      if (!ok) break;
+      // value shift of this tile (first half of the v channels from this token, second half from the previous one):
+      // a plain copy that runs while conv2 keeps the tensor cores busy
+      {
+        uint4 val[VPT];
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+          const int idx = u * DL_THREADS + dt;
+          const int vt = t0 + idx / VP, c = (idx % VP) * 8;
+          const int src_tok = (c < KVD / 2) ? vt : vt - 1;
+          val[u] = make_uint4(0, 0, 0, 0);
+          if (idx < TT * VP && vt < S && src_tok >= 0)
+            val[u] = *reinterpret_cast<const uint4*>(qkv_b + (size_t)src_tok * QKV_LD + LAT + KVD + c);
+        }
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+          const int idx = u * DL_THREADS + dt;
+          const int vt = t0 + idx / VP, c = (idx % VP) * 8;
+          if (idx < TT * VP && vt < S)
+            *reinterpret_cast<uint4*>(p.v + (((size_t)b * KV + c / HD) * S + vt) * HD + (c % HD)) = val[u];
+        }
+      }
+      if (!mbar_wait(k_full, (uint32_t)(it & 1), abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
 #pragma unroll 1
-    for (int i0 = 0; i0 < TT * VP; i0 += 64 * 16) {
-      uint4 val[16];
+      for (int c = 0; c < KVD / 32; ++c) {
+        float v[32];
+        tmem_ld_32x32(tmem_base + lane_off + COL_K + (uint32_t)(c * 32), v);   // warp-collective
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        const int idx = i0 + u * 64 + vt;
-        const int tok = t0 + idx / VP, c = (idx % VP) * 8;
-        const int src_tok = (c < KVD / 2) ? tok : tok - 1;
-        val[u] = make_uint4(0, 0, 0, 0);
-        if (tok < S && src_tok >= 0)
-          val[u] = *reinterpret_cast<const uint4*>(qkv_b + (size_t)src_tok * QKV_LD + LAT + KVD + c);
+        for (int hh = 0; hh < 32 / HD; ++hh) {
+          const int h = (c * 32) / HD + hh;
+          finish_head<HD>(v + hh * HD, mean, temp, cs, sn, p.k + (((size_t)b * KV + h) * S + tok) * HD, valid);
+        }
       }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(k_free);
+    }
+  } else if (warp < X_WARP) {
+    // ------------------------------ query epilogue warps (6..13): thread = token ------------------------------
+    const int quad = warp & 3;
+    const int half = (warp - E_WARP0) >> 2;                // which four 32-column chunks of the query accumulator
+    const int r = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < my_tiles; ++it) {
+      const uint32_t tpar = (uint32_t)(it & 1);
+      const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+      const int b = tile / p.tiles_per_seq, t0 = (tile % p.tiles_per_seq) * TT;
+      const int tok = t0 + r;
+      const bool valid = r < TT && tok < S;
+      float mean[HD], cs[HD / 2], sn[HD / 2];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        const int idx = i0 + u * 64 + vt;
-        const int tok = t0 + idx / VP, c = (idx % VP) * 8;
-        if (tok < S)
-          *reinterpret_cast<uint4*>(p.v + (((size_t)b * KV + c / HD) * S + tok) * HD + (c % HD)) = val[u];
+      for (int i = 0; i < HD / 2; i += 4) {
+        const float4 c4 = valid ? *reinterpret_cast<const float4*>(p.cos_t + (size_t)tok * (HD / 2) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 s4 = valid ? *reinterpret_cast<const float4*>(p.sin_t + (size_t)tok * (HD / 2) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        cs[i] = c4.x; cs[i + 1] = c4.y; cs[i + 2] = c4.z; cs[i + 3] = c4.w;
+        sn[i] = s4.x; sn[i + 1] = s4.y; sn[i + 2] = s4.z; sn[i + 3] = s4.w;
       }
+      if (!mbar_wait(xp_full, tpar, abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      // queries are coupled with the mean key: the key channels are planes 32..39
+      head_mean_planes<HD>(xp_addr + (uint32_t)(LAT / 8) * XP_PLANE + (uint32_t)((r + 4) & (XROWS - 1)) * 16u, XP_PLANE, KV, mean);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xp_free);
+      if (!mbar_wait(q_full, tpar, abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld_32x32(tmem_base + lane_off + COL_Q + (uint32_t)(half * 128 + c * 32), v);   // warp-collective
+#pragma unroll
+        for (int hh = 0; hh < 32 / HD; ++hh) {
+          const int h = (half * 128 + c * 32) / HD + hh;
+          finish_head<HD>(v + hh * HD, mean, 1.0f, cs, sn, p.q + (((size_t)b * H + h) * S + tok) * HD, valid);
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_free);
     }
   } else {
-    // ---- warps 4..7 prepare the per-token vectors of the epilogue while the contraction runs ----
-    // QK-mean vectors of this token (0.5 * mean over heads), straight from its qkv row
-#pragma unroll
-    for (int d = 0; d < HD; ++d) qm[d] = km[d] = 0.f;
-    if (valid) {
-      const __nv_bfloat16* row = qkv_b + (size_t)tok * QKV_LD;
-      // 32 + 8 sixteen-byte pieces; piece i covers channels 8i..8i+7 = dims (8i mod HD).. of head 8i / HD
-#pragma unroll
-      for (int i0 = 0; i0 < LAT / 8; i0 += 8) {
-        uint4 raw[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const uint4*>(row + (i0 + u) * 8);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const uint32_t w4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-          const int d0 = ((i0 + u) * 8) % HD;
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            qm[d0 + 2 * jj] += __uint_as_float(w4[jj] << 16);
-            qm[d0 + 2 * jj + 1] += __uint_as_float(w4[jj] & 0xffff0000u);
-          }
-        }
-      }
-      {
-        uint4 raw[KVD / 8];
-#pragma unroll
-        for (int u = 0; u < KVD / 8; ++u) raw[u] = *reinterpret_cast<const uint4*>(row + LAT + u * 8);
-#pragma unroll
-        for (int u = 0; u < KVD / 8; ++u) {
-          const uint32_t w4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-          const int d0 = (u * 8) % HD;
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            km[d0 + 2 * jj] += __uint_as_float(w4[jj] << 16);
-            km[d0 + 2 * jj + 1] += __uint_as_float(w4[jj] & 0xffff0000u);
-          }
-        }
-      }
-    }
-    const float sq = 0.5f / (float)H, sk = 0.5f / (float)KV;
-#pragma unroll
-    for (int d = 0; d < HD; ++d) { qm[d] *= sq; km[d] *= sk; }
-#pragma unroll
-    for (int i = 0; i < HD / 2; ++i) {
-      cs[i] = valid ? p.cos_t[(size_t)tok * (HD / 2) + i] : 1.f;
-      sn[i] = valid ? p.sin_t[(size_t)tok * (HD / 2) + i] : 0.f;
-    }
-  }
-
-  // ---------------- epilogue: all 8 warps, thread = token, the ten 32-column chunks split 5 + 5 ----------------
-  // Warps 0-3 are done with their roles by now (the producer long before).  Warps 4-7 hand their token's vectors to
-  // warps 0-3 through the weight ring, which is idle once the accumulators are complete.
-  {
-    const float temp = *p.temp;
-    bool ok = mbar_wait(acc_full, 0u, abort_flag);
-    ok = __all_sync(0xffffffffu, ok);
-    tcgen05_fence_after();
-    float* hand = reinterpret_cast<float*>(base_ptr);        // [2*HD + HD][128] floats: field-major, token-minor
-    if (warp >= 4) {
-#pragma unroll
-      for (int d = 0; d < HD; ++d) { hand[d * TT + r] = qm[d]; hand[(HD + d) * TT + r] = km[d]; }
-#pragma unroll
-      for (int i = 0; i < HD / 2; ++i) { hand[(2 * HD + i) * TT + r] = cs[i]; hand[(2 * HD + HD / 2 + i) * TT + r] = sn[i]; }
-    }
-    __syncthreads();
-    if (warp < 4) {
-#pragma unroll
-      for (int d = 0; d < HD; ++d) { qm[d] = hand[d * TT + r]; km[d] = hand[(HD + d) * TT + r]; }
-#pragma unroll
-      for (int i = 0; i < HD / 2; ++i) { cs[i] = hand[(2 * HD + i) * TT + r]; sn[i] = hand[(2 * HD + HD / 2 + i) * TT + r]; }
-    }
-    if (ok) {
-      constexpr int QCH = LAT / 32, KCH = KVD / 32, HALF = (QCH + KCH) / 2;
-      const int c_begin = warp >= 4 ? 0 : HALF, c_end = warp >= 4 ? HALF : QCH + KCH;
+    // ------------------------------ x loader (warp 14) ------------------------------
+    if (lane == 0) {
+      for (int it = 0; it < my_tiles; ++it) {
+        // the planes may be overwritten once conv1 of the previous tile and its mean readers are done with them
+        if (it > 0 && !mbar_wait(xp_free, (uint32_t)((it - 1) & 1), abort_flag)) break;
+        const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+        const int b = tile / p.tiles_per_seq, t0 = (tile % p.tiles_per_seq) * TT;
+        mbar_arrive_expect_tx(xp_full, XP_BYTES);
 #pragma unroll 1
-      for (int c = c_begin; c < c_end; ++c) {
-        float v[32];
-        if (c < QCH) {
-          // queries: LAT accumulator columns = H heads of HD
-          tmem_ld_32x32(tmem_base + lane_off + (uint32_t)(c * 32), v);   // warp-collective
-#pragma unroll
-          for (int hh = 0; hh < 32 / HD; ++hh) {
-            const int h = c * (32 / HD) + hh;
-            finish_head<HD>(v + hh * HD, km, 1.0f, cs, sn, p.q + (((size_t)b * H + h) * S + tok) * HD, valid);
-          }
-        } else {
-          // keys: KVD columns at 256..
-          const int ck = c - QCH;
-          tmem_ld_32x32(tmem_base + lane_off + (uint32_t)(256 + ck * 32), v);
-#pragma unroll
-          for (int hh = 0; hh < 32 / HD; ++hh) {
-            const int h = ck * (32 / HD) + hh;
-            finish_head<HD>(v + hh * HD, qm, temp, cs, sn, p.k + (((size_t)b * KV + h) * S + tok) * HD, valid);
-          }
-        }
+        for (int pl = 0; pl < PLANES; ++pl) tma_load_3d(xp_addr + (uint32_t)pl * XP_PLANE, &tma_x, pl * 8, t0 - 4, b, xp_full);
       }
     }
+    __syncwarp();
   }
 
-  // ---------------- teardown ----------------
+  // ------------------------------ teardown ------------------------------
   tcgen05_fence_before();
   __syncthreads();
   if (*abort_flag != 0u) {
@@ -411,31 +523,19 @@ __global__ void __launch_bounds__(256, 1) ccgqa_pre_tc_kernel(const __grid_const
 }
 
 // ---- host side ---------------------------------------------------------------------------------------------------
-static PFN_cuTensorMapEncodeTiled_v12000 pre_encode_fn() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
-  });
-  return fn;
-}
-
-// repacked conv2 weight [rows, 3*cin] bf16, blocks of `rows` x 64 K, 128-byte swizzle
-static int make_w2_map(CUtensorMap* map, const void* ptr, int rows, int cin) {
-  auto fn = pre_encode_fn();
+// 2-D bf16 map over a row-major [rows, cols] weight, box [box_rows, box_cols]
+static int make_weight_map(CUtensorMap* map, const void* ptr, int rows, int cols, int box_rows, int box_cols,
+                           CUtensorMapSwizzle swizzle) {
+  auto fn = get_encode_fn();
   HB_REQUIRE(fn != nullptr, HB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t gdim[2] = {(cuuint64_t)3 * cin, (cuuint64_t)rows};
-  cuuint64_t gstride[1] = {(cuuint64_t)3 * cin * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)rows};
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  HB_REQUIRE(r == CUDA_SUCCESS, HB200_ERR_CUDA, "cuTensorMapEncodeTiled (conv2 weight) failed with CUresult %d", (int)r);
+  HB_REQUIRE(r == CUDA_SUCCESS, HB200_ERR_CUDA, "cuTensorMapEncodeTiled (conv weight) failed with CUresult %d", (int)r);
   return 0;
 }
 
@@ -445,20 +545,38 @@ int launch_ccgqa_pre_tc(const void* qkv, const void* w1_qk, const void* w2_q, co
                         int KV, int hd, int32_t* err_flag, cudaStream_t st) {
   using namespace pretc;
   if (H * hd != LAT || KV * hd != KVD || H == KV || (hd != 16 && hd != 32)) return HB200_ERR_UNSUPPORTED;
-  CUtensorMap tq, tk;
-  HB_PROPAGATE(make_w2_map(&tq, w2_q, LAT, LAT));
-  HB_PROPAGATE(make_w2_map(&tk, w2_k, KVD, KVD));
-  PreTcParams p{(const __nv_bfloat16*)qkv, (const __nv_bfloat16*)w1_qk, cos_t, sin_t, key_temperature,
-                (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, B, S, H, KV, err_flag};
-  const int tiles = B * ((S + TT - 1) / TT);
+  CUtensorMap tx, t1, tq, tk;
+  {
+    // qkv as [B][S][lat+2kvd]: boxes of 8 channels x 128 rows of one sequence, un-swizzled -> one x plane each
+    auto fn = get_encode_fn();
+    HB_REQUIRE(fn != nullptr, HB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t gdim[3] = {(cuuint64_t)(LAT + 2 * KVD), (cuuint64_t)S, (cuuint64_t)B};
+    cuuint64_t gstride[2] = {(cuuint64_t)(LAT + 2 * KVD) * 2, (cuuint64_t)S * (LAT + 2 * KVD) * 2};
+    cuuint32_t box[3] = {8, (cuuint32_t)XROWS, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(qkv), gdim, gstride, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    HB_REQUIRE(r == CUDA_SUCCESS, HB200_ERR_CUDA, "cuTensorMapEncodeTiled (qkv planes) failed with CUresult %d", (int)r);
+  }
+  // conv1 weight [C, 3*hd]: boxes of 64 rows x 8 K elements (16 bytes), laid down un-swizzled as [row][16 B]
+  HB_PROPAGATE(make_weight_map(&t1, w1_qk, C, 3 * hd, ROUND_CH, 8, CU_TENSOR_MAP_SWIZZLE_NONE));
+  // conv2 weights [C_out, 3*C_in]: queries in blocks of 256 rows x 32 K (64-byte swizzle), keys 64 rows x 64 K (128-byte)
+  HB_PROPAGATE(make_weight_map(&tq, w2_q, LAT, 3 * LAT, LAT, 32, CU_TENSOR_MAP_SWIZZLE_64B));
+  HB_PROPAGATE(make_weight_map(&tk, w2_k, KVD, 3 * KVD, KVD, 64, CU_TENSOR_MAP_SWIZZLE_128B));
+  const int tiles_per_seq = (S + TT - 1) / TT;
+  const int n_tiles = B * tiles_per_seq;
+  PreTcParams p{(const __nv_bfloat16*)qkv, cos_t, sin_t, key_temperature, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
+                (__nv_bfloat16*)v, B, S, H, KV, n_tiles, tiles_per_seq, err_flag};
+  const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
   if (hd == 32) {
     auto kern = ccgqa_pre_tc_kernel<32>;
     HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(SMEM_BYTES)));
-    kern<<<tiles, 256, SMEM_BYTES, st>>>(tq, tk, p);
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tx, t1, tq, tk, p);
   } else {
     auto kern = ccgqa_pre_tc_kernel<16>;
     HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(SMEM_BYTES)));
-    kern<<<tiles, 256, SMEM_BYTES, st>>>(tq, tk, p);
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tx, t1, tq, tk, p);
   }
   HB_LAUNCH_CHECK();
   return 0;
