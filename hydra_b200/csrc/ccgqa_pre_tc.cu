@@ -22,19 +22,20 @@
 // map, whose out-of-range rows (before the sequence, after it) arrive as zeros.
 //
 // Roles (15 warps):
-//   warp 0      weight producer: TMA streams, in consumption order, the conv1 weight of 64 channels at a time, the query
-//               conv2 weight in [256 out-channels x 32 K] blocks (64B-swizzled) and the key conv2 weight in [64 x 64]
-//               blocks (128B-swizzled) through a ring of four 16 KB stages;
+//   warp 0      weight producer: TMA streams, in consumption order, the conv1 weight of 64 channels at a time (two swizzled
+//               boxes), the query conv2 weight in [128 out-channels x 64 K] blocks and the key conv2 weight in [64 x 64]
+//               blocks (128B-swizzled, 128-byte rows) through a ring of four 16 KB stages.  The TMA unit works through
+//               a box one row at a time, about 1.6 clocks per row whatever its width, so every weight box has the
+//               widest rows its layout allows: with 16- or 64-byte rows the unit itself set the pace of the kernel;
 //   warp 1      MMA issuer: the whole warp runs the loop with warp-uniform operands and one elected lane issues (a
 //               single-lane loop costs ~46 clocks per MMA to issue, this form 24-34, and the conv1 / key MMAs hold less
 //               math than that): conv1 in five rounds of 64 channels into a double-buffered 64-column accumulator, then
-//               conv2 of the queries (M128 x N256) and of the keys (N64);
-//   warps 2-5   (a) drain each conv1 round: TMEM -> bf16 -> y1 planes; (b) copy the tile's value columns with the
-//               one-token shift; (c) epilogue of the key accumulator (thread = token): + 0.5 * mean query (summed from
-//               the x planes while they are in shared memory), L2 norm, temperature, RoPE;
-//   warps 6-13  epilogue of the query accumulator, thread = token, two warps per TMEM lane quadrant, four heads each:
-//               + 0.5 * mean key (from the x planes), L2 norm, RoPE, 64-byte stores - while the key conv and the next
-//               tile's conv1 run;
+//               conv2 of the queries (two M128 x N128 halves per K block, one weight stage each) and of the keys (N64);
+//   warps 2-5   drain each conv1 round (TMEM -> bf16 -> y1 planes), nothing else on their critical path; between tiles
+//               they copy the value columns with the one-token shift;
+//   warps 6-13  epilogue, thread = token, two warps per TMEM lane quadrant: + 0.5 * mean key / mean query (summed from
+//               the x planes while they are in shared memory), L2 norm, key temperature, RoPE, 64-byte stores - five
+//               32-column chunks per warp (queries 0-2 and the keys, or queries 3-7) while the next tile's conv1 runs;
 //   warp 14     x loader: as soon as conv1 and the mean readers are done with the x planes, one lane issues the 40 TMA
 //               loads of the next tile's planes (a 16-byte-row box is slow to issue, ~230 clocks each, which is why
 //               this is nobody else's job); they land while conv2 of the current tile runs.
@@ -78,7 +79,7 @@ constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 constexpr int ROUND_CH = 64;             // channels per conv1 round
 constexpr int ROUNDS = C / ROUND_CH;     // 5
-constexpr int QBLOCKS = 3 * LAT / 32;    // 24 K blocks of 32 of the q conv2 (a [256 x 32] weight block fills one stage)
+constexpr int QBLOCKS = 2 * (3 * LAT / 64);   // q conv2: 12 K blocks of 64, each as two [128 out-channels x 64 K] stages
 constexpr int KBLOCKS = 3 * KVD / 64;    // 3 K blocks of 64 of the k conv2
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_Q = 0, COL_K = 256, COL_C1 = 320;
@@ -111,7 +112,8 @@ __device__ __forceinline__ void finish_head(const float* acc, const float* coupl
     v[d] = acc[d] + couple[d];
     ss += v[d] * v[d];
   }
-  const float inv = mult / fmaxf(sqrtf(ss), 1e-12f);
+  // mult / max(|v|, 1e-12): rsqrt of the clamped sum of squares (2 ulp, far inside the bf16 rounding of the result)
+  const float inv = mult * rsqrtf(fmaxf(ss, 1e-24f));
   if (!valid) return;
 #pragma unroll
   for (int d8 = 0; d8 < HD / 8; ++d8) {
@@ -157,15 +159,19 @@ __device__ __forceinline__ void head_mean_planes(uint32_t plane0_row, uint32_t p
 
 template <int HD>
 __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const __grid_constant__ CUtensorMap tma_x,
-                                                                         const __grid_constant__ CUtensorMap tma_w1,
+                                                                         const __grid_constant__ CUtensorMap tma_w1a,
+                                                                         const __grid_constant__ CUtensorMap tma_w1b,
                                                                          const __grid_constant__ CUtensorMap tma_w2q,
                                                                          const __grid_constant__ CUtensorMap tma_w2k,
                                                                          const PreTcParams p) {
   using namespace pretc;
   static_assert(HD == 16 || HD == 32, "head_dim 16 or 32");
   constexpr int QKV_LD = LAT + 2 * KVD;
-  constexpr int W1_BYTES = ROUND_CH * 3 * HD * 2;   // conv1 weight of one round: 64 rows x 3*hd
-  constexpr int KCHUNKS1 = 3 * HD / 8;              // 16-byte K chunks of a conv1 weight row
+  // conv1 weight of one round: 64 rows x 3*hd, as two K-major swizzled boxes - taps 0 and 1 (2*hd columns) and tap 2
+  // (hd columns); the swizzle width of each is its row width
+  constexpr int W1A_ROW = 4 * HD, W1B_ROW = 2 * HD;                 // bytes per row: 128 / 64 (hd 32), 64 / 32 (hd 16)
+  constexpr int W1A_BYTES = ROUND_CH * W1A_ROW, W1_BYTES = ROUND_CH * (W1A_ROW + W1B_ROW);
+  constexpr uint32_t W1A_LAYOUT = W1A_ROW == 128 ? 2u : 4u, W1B_LAYOUT = W1B_ROW == 64 ? 4u : 6u;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (s_addr(smem_dyn) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_dyn + (base - s_addr(smem_dyn));
@@ -191,7 +197,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
       mbar_init(w_empty(s), 1);
     }
     mbar_init(xp_full, 1);
-    mbar_init(xp_free, 1 + DL_WARPS + 8);          // conv1 complete (MMA commit) + the 12 warps that read their means from x
+    mbar_init(xp_free, 1 + 8);                     // conv1 complete (MMA commit) + the 8 warps that read their means from x
     mbar_init(y1_full, DL_WARPS);
     for (int b = 0; b < 2; ++b) {
       mbar_init(c1_full(b), 1);
@@ -200,7 +206,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
     mbar_init(q_full, 1);
     mbar_init(q_free, 8);
     mbar_init(k_full, 1);
-    mbar_init(k_free, DL_WARPS);
+    mbar_init(k_free, 4);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -228,17 +234,17 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
           const uint32_t dst = next_stage();
           if (!ok) break;
           mbar_arrive_expect_tx(w_full(stage), W1_BYTES);
-#pragma unroll 1
-          for (int kc = 0; kc < KCHUNKS1; ++kc) tma_load_2d(dst + kc * (ROUND_CH * 16), &tma_w1, kc * 8, rd * ROUND_CH, w_full(stage));
+          tma_load_2d(dst, &tma_w1a, 0, rd * ROUND_CH, w_full(stage));
+          tma_load_2d(dst + W1A_BYTES, &tma_w1b, 2 * HD, rd * ROUND_CH, w_full(stage));
           advance();
         }
         const int pos = ((int)blockIdx.x + it * (int)gridDim.x) % p.tiles_per_seq;
-        for (int i = 0; ok && i < QBLOCKS; ++i) {                   // conv2 weight of the queries: all 256 output channels x 32 K
+        for (int i = 0; ok && i < QBLOCKS; ++i) {                   // conv2 weight of the queries: 128 output channels x 64 K per stage
           const uint32_t dst = next_stage();
           if (!ok) break;
-          const int kb = (i + pos * 7) % QBLOCKS;
-          mbar_arrive_expect_tx(w_full(stage), LAT * 32 * 2);
-          tma_load_2d(dst, &tma_w2q, kb * 32, 0, w_full(stage));
+          const int kb = ((i >> 1) + pos * 5) % (QBLOCKS / 2);
+          mbar_arrive_expect_tx(w_full(stage), 128 * 64 * 2);
+          tma_load_2d(dst, &tma_w2q, kb * 64, (i & 1) * 128, w_full(stage));
           advance();
         }
         for (int kb = 0; ok && kb < KBLOCKS; ++kb) {                // conv2 weight of the keys
@@ -255,13 +261,13 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
     // ------------------------------ MMA issuer (whole warp, one elected lane issues) ------------------------------
     {
       constexpr uint32_t idesc_c1 = make_idesc(MR, HD);
-      constexpr uint32_t idesc_q = make_idesc(MR, LAT);
+      constexpr uint32_t idesc_q = make_idesc(MR, 128);
       constexpr uint32_t idesc_k = make_idesc(MR, KVD);
       // descriptor templates; per MMA only the start-address field (16-byte units, low bits) moves
       const uint64_t dx0 = make_smem_desc_ex(xp_addr, 128, 0u, XP_PLANE);           // x planes: 8-row groups 128 B apart
       const uint64_t dy0 = make_smem_desc_ex(y1_addr, 128, 0u, Y1_PLANE);           // y1 planes
-      const uint64_t dw1 = make_smem_desc_ex(base + OFF_RING, 128, 0u, ROUND_CH * 16);   // conv1 weight [K chunk][64 rows][16 B]
-      const uint64_t dwq = make_smem_desc_ex(base + OFF_RING, 512, 4u, 16);         // [256 rows][64 B], 64B swizzle
+      const uint64_t dw1a = make_smem_desc_ex(base + OFF_RING, 8 * W1A_ROW, W1A_LAYOUT, 16);             // conv1 weight, taps 0-1
+      const uint64_t dw1b = make_smem_desc_ex(base + OFF_RING + W1A_BYTES, 8 * W1B_ROW, W1B_LAYOUT, 16); // conv1 weight, tap 2
       const uint64_t dwk = make_smem_desc(base + OFF_RING);                         // [64 rows][128 B], 128B swizzle
       int stage = 0;
       uint32_t phase = 0, c1_use[2] = {0u, 0u};
@@ -287,7 +293,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
           if (!mbar_wait(c1_free(cb), (c1_use[cb] & 1u) ^ 1u, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
           const uint64_t dx_rd = dx0 + (uint64_t)((uint32_t)(rd * (ROUND_CH / 8) * XP_PLANE) >> 4);
-          const uint64_t dw_rd = dw1 + (uint64_t)so;
+          const uint64_t dwa_rd = dw1a + (uint64_t)so, dwb_rd = dw1b + (uint64_t)so;
           const uint32_t d_rd = tmem_base + COL_C1 + (uint32_t)(cb * ROUND_CH);
 #pragma unroll
           for (int hh = 0; hh < ROUND_CH / HD; ++hh) {
@@ -296,9 +302,11 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
               const int j = (ks * 16) / HD, ci0 = (ks * 16) % HD;
               // A: x rows j..j+127 of the 16 input channels hh*HD+ci0.. of this round (two planes)
               const uint32_t a_off = (uint32_t)(((hh * HD + ci0) / 8) * XP_PLANE + j * 16) >> 4;
-              // B: this head's rows of the round's weight block, K chunks 2ks and 2ks+1
-              const uint32_t b_off = (uint32_t)((2 * ks) * (ROUND_CH * 16) + (hh * HD) * 16) >> 4;
-              umma_bf16_elect(d_rd + (uint32_t)(hh * HD), dx_rd + a_off, dw_rd + b_off, idesc_c1, ks ? 1u : 0u);
+              // B: this head's rows of the round's weight block; K = 16 ks .. sits in the first box (taps 0, 1) or the second
+              const uint64_t db = (ks * 16 < 2 * HD)
+                                      ? dwa_rd + (uint64_t)((uint32_t)(hh * HD * W1A_ROW + ks * 32) >> 4)
+                                      : dwb_rd + (uint64_t)((uint32_t)(hh * HD * W1B_ROW + (ks * 16 - 2 * HD) * 2) >> 4);
+              umma_bf16_elect(d_rd + (uint32_t)(hh * HD), dx_rd + a_off, db, idesc_c1, ks ? 1u : 0u);
             }
           }
           release_stage();
@@ -315,14 +323,14 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
         for (int i = 0; ok && i < QBLOCKS; ++i) {
           const uint32_t so = wait_stage();
           if (!ok) break;
-          const int kb = (i + pos * 7) % QBLOCKS;          // rotated start, same order as the producer's
-          const int j = (kb * 32) / LAT, ch0 = (kb * 32) % LAT;
+          const int kb = ((i >> 1) + pos * 5) % (QBLOCKS / 2);   // rotated start, same order as the producer's
+          const int j = (kb * 64) / LAT, ch0 = (kb * 64) % LAT;
           const uint64_t da = dy0 + (uint64_t)((uint32_t)((ch0 / 8) * Y1_PLANE + j * 16) >> 4);
-          const uint64_t db = dwq + (uint64_t)so;
+          const uint64_t db = dwk + (uint64_t)so;              // same [rows][128 B] 128B-swizzled form as the key weight
 #pragma unroll
-          for (int ks = 0; ks < 2; ++ks)
-            umma_bf16_elect(tmem_base + COL_Q, da + (uint64_t)((uint32_t)(ks * 2 * Y1_PLANE) >> 4), db + (uint64_t)(ks * 2), idesc_q,
-                            (i | ks) ? 1u : 0u);
+          for (int ks = 0; ks < 4; ++ks)
+            umma_bf16_elect(tmem_base + COL_Q + (uint32_t)((i & 1) * 128), da + (uint64_t)((uint32_t)(ks * 2 * Y1_PLANE) >> 4),
+                            db + (uint64_t)(ks * 2), idesc_q, ((i >> 1) | ks) ? 1u : 0u);
           release_stage();
         }
         if (!ok) break;
@@ -346,12 +354,11 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
     }
     __syncwarp();
   } else if (warp < E_WARP0) {
-    // ------------------ conv1 drain + value shift + key epilogue (warps 2..5) ------------------
+    // ------------------ conv1 drain + value shift (warps 2..5) ------------------
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;                        // y1 row this thread drains / token row of the key epilogue
+    const int r = quad * 32 + lane;                        // y1 row this thread drains
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const int dt = tid - DL_WARP0 * 32;                    // 0..127
-    const float temp = *p.temp;
     uint32_t c1_use[2] = {0u, 0u};
     bool ok = true;
     constexpr int VP = KVD / 8;                            // 16-byte pieces of a token's value columns
@@ -359,24 +366,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
     for (int it = 0; ok && it < my_tiles; ++it) {
       const int tile = (int)blockIdx.x + it * (int)gridDim.x;
       const int b = tile / p.tiles_per_seq, t0 = (tile % p.tiles_per_seq) * TT;
-      const int tok = t0 + r;
-      const bool valid = r < TT && tok < S;
       const __nv_bfloat16* qkv_b = p.qkv + (size_t)b * S * QKV_LD;
-      float mean[HD], cs[HD / 2], sn[HD / 2];
-#pragma unroll
-      for (int i = 0; i < HD / 2; i += 4) {
-        const float4 c4 = valid ? *reinterpret_cast<const float4*>(p.cos_t + (size_t)tok * (HD / 2) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
-        const float4 s4 = valid ? *reinterpret_cast<const float4*>(p.sin_t + (size_t)tok * (HD / 2) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-        cs[i] = c4.x; cs[i + 1] = c4.y; cs[i + 2] = c4.z; cs[i + 3] = c4.w;
-        sn[i] = s4.x; sn[i + 1] = s4.y; sn[i + 2] = s4.z; sn[i + 3] = s4.w;
-      }
-      // mean query of this token from the x planes (x row of output row r is r + 4; rows past 127 belong to no token)
-      if (!mbar_wait(xp_full, (uint32_t)(it & 1), abort_flag)) ok = false;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      head_mean_planes<HD>(xp_addr + (uint32_t)((r + 4) & (XROWS - 1)) * 16u, XP_PLANE, H, mean);   // keys are coupled with the mean query
-      __syncwarp();
-      if (lane == 0) mbar_arrive(xp_free);
       for (int rd = 0; rd < ROUNDS; ++rd) {
         const int cb = rd & 1;
         if (!mbar_wait(c1_full(cb), c1_use[cb] & 1u, abort_flag)) ok = false;
@@ -429,30 +419,16 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
             *reinterpret_cast<uint4*>(p.v + (((size_t)b * KV + c / HD) * S + vt) * HD + (c % HD)) = val[u];
         }
       }
-      if (!mbar_wait(k_full, (uint32_t)(it & 1), abort_flag)) ok = false;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tcgen05_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < KVD / 32; ++c) {
-        float v[32];
-        tmem_ld_32x32(tmem_base + lane_off + COL_K + (uint32_t)(c * 32), v);   // warp-collective
-#pragma unroll
-        for (int hh = 0; hh < 32 / HD; ++hh) {
-          const int h = (c * 32) / HD + hh;
-          finish_head<HD>(v + hh * HD, mean, temp, cs, sn, p.k + (((size_t)b * KV + h) * S + tok) * HD, valid);
-        }
-      }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(k_free);
     }
   } else if (warp < X_WARP) {
-    // ------------------------------ query epilogue warps (6..13): thread = token ------------------------------
+    // ------------------------------ epilogue warps (6..13): thread = token ------------------------------
+    // Ten 32-column chunks per tile and lane quadrant - eight of the query accumulator, two of the key accumulator,
+    // which is complete last.  Warps 6-9 take query chunks 0-2 and then the keys, warps 10-13 query chunks 3-7.
     const int quad = warp & 3;
-    const int half = (warp - E_WARP0) >> 2;                // which four 32-column chunks of the query accumulator
+    const int half = (warp - E_WARP0) >> 2;
     const int r = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const float temp = *p.temp;
     bool ok = true;
     for (int it = 0; it < my_tiles; ++it) {
       const uint32_t tpar = (uint32_t)(it & 1);
@@ -460,7 +436,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
       const int b = tile / p.tiles_per_seq, t0 = (tile % p.tiles_per_seq) * TT;
       const int tok = t0 + r;
       const bool valid = r < TT && tok < S;
-      float mean[HD], cs[HD / 2], sn[HD / 2];
+      float km[HD], qm[HD], cs[HD / 2], sn[HD / 2];
 #pragma unroll
       for (int i = 0; i < HD / 2; i += 4) {
         const float4 c4 = valid ? *reinterpret_cast<const float4*>(p.cos_t + (size_t)tok * (HD / 2) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
@@ -471,27 +447,49 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
       if (!mbar_wait(xp_full, tpar, abort_flag)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      // queries are coupled with the mean key: the key channels are planes 32..39
-      head_mean_planes<HD>(xp_addr + (uint32_t)(LAT / 8) * XP_PLANE + (uint32_t)((r + 4) & (XROWS - 1)) * 16u, XP_PLANE, KV, mean);
+      // the means come from the x planes while they are in shared memory (x row of output row r is r + 4; rows past
+      // 127 belong to no token): queries are coupled with the mean key (planes 32..39), keys with the mean query
+      const uint32_t xrow = xp_addr + (uint32_t)((r + 4) & (XROWS - 1)) * 16u;
+      head_mean_planes<HD>(xrow + (uint32_t)(LAT / 8) * XP_PLANE, XP_PLANE, KV, km);
+      if (half == 0) head_mean_planes<HD>(xrow, XP_PLANE, H, qm);
       __syncwarp();
       if (lane == 0) mbar_arrive(xp_free);
       if (!mbar_wait(q_full, tpar, abort_flag)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
+      const int c_begin = half == 0 ? 0 : 3, c_end = half == 0 ? 3 : 8;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = c_begin; c < c_end; ++c) {
         float v[32];
-        tmem_ld_32x32(tmem_base + lane_off + COL_Q + (uint32_t)(half * 128 + c * 32), v);   // warp-collective
+        tmem_ld_32x32(tmem_base + lane_off + COL_Q + (uint32_t)(c * 32), v);   // warp-collective
 #pragma unroll
         for (int hh = 0; hh < 32 / HD; ++hh) {
-          const int h = (half * 128 + c * 32) / HD + hh;
-          finish_head<HD>(v + hh * HD, mean, 1.0f, cs, sn, p.q + (((size_t)b * H + h) * S + tok) * HD, valid);
+          const int h = (c * 32) / HD + hh;
+          finish_head<HD>(v + hh * HD, km, 1.0f, cs, sn, p.q + (((size_t)b * H + h) * S + tok) * HD, valid);
         }
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(q_free);
+      if (half != 0) continue;
+      if (!mbar_wait(k_full, tpar, abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < KVD / 32; ++c) {
+        float v[32];
+        tmem_ld_32x32(tmem_base + lane_off + COL_K + (uint32_t)(c * 32), v);   // warp-collective
+#pragma unroll
+        for (int hh = 0; hh < 32 / HD; ++hh) {
+          const int h = (c * 32) / HD + hh;
+          finish_head<HD>(v + hh * HD, qm, temp, cs, sn, p.k + (((size_t)b * KV + h) * S + tok) * HD, valid);
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(k_free);
     }
   } else {
     // ------------------------------ x loader (warp 14) ------------------------------
@@ -545,7 +543,7 @@ int launch_ccgqa_pre_tc(const void* qkv, const void* w1_qk, const void* w2_q, co
                         int KV, int hd, int32_t* err_flag, cudaStream_t st) {
   using namespace pretc;
   if (H * hd != LAT || KV * hd != KVD || H == KV || (hd != 16 && hd != 32)) return HB200_ERR_UNSUPPORTED;
-  CUtensorMap tx, t1, tq, tk;
+  CUtensorMap tx, t1a, t1b, tq, tk;
   {
     // qkv as [B][S][lat+2kvd]: boxes of 8 channels x 128 rows of one sequence, un-swizzled -> one x plane each
     auto fn = get_encode_fn();
@@ -559,10 +557,11 @@ int launch_ccgqa_pre_tc(const void* qkv, const void* w1_qk, const void* w2_q, co
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     HB_REQUIRE(r == CUDA_SUCCESS, HB200_ERR_CUDA, "cuTensorMapEncodeTiled (qkv planes) failed with CUresult %d", (int)r);
   }
-  // conv1 weight [C, 3*hd]: boxes of 64 rows x 8 K elements (16 bytes), laid down un-swizzled as [row][16 B]
-  HB_PROPAGATE(make_weight_map(&t1, w1_qk, C, 3 * hd, ROUND_CH, 8, CU_TENSOR_MAP_SWIZZLE_NONE));
-  // conv2 weights [C_out, 3*C_in]: queries in blocks of 256 rows x 32 K (64-byte swizzle), keys 64 rows x 64 K (128-byte)
-  HB_PROPAGATE(make_weight_map(&tq, w2_q, LAT, 3 * LAT, LAT, 32, CU_TENSOR_MAP_SWIZZLE_64B));
+  // conv1 weight [C, 3*hd]: per round of 64 rows one box of the first two taps and one of the third, swizzle = row width
+  HB_PROPAGATE(make_weight_map(&t1a, w1_qk, C, 3 * hd, ROUND_CH, 2 * hd, hd == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B));
+  HB_PROPAGATE(make_weight_map(&t1b, w1_qk, C, 3 * hd, ROUND_CH, hd, hd == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B));
+  // conv2 weights [C_out, 3*C_in]: blocks of 128 (queries) / 64 (keys) rows x 64 K, 128-byte swizzle
+  HB_PROPAGATE(make_weight_map(&tq, w2_q, LAT, 3 * LAT, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B));
   HB_PROPAGATE(make_weight_map(&tk, w2_k, KVD, 3 * KVD, KVD, 64, CU_TENSOR_MAP_SWIZZLE_128B));
   const int tiles_per_seq = (S + TT - 1) / TT;
   const int n_tiles = B * tiles_per_seq;
@@ -572,11 +571,11 @@ int launch_ccgqa_pre_tc(const void* qkv, const void* w1_qk, const void* w2_q, co
   if (hd == 32) {
     auto kern = ccgqa_pre_tc_kernel<32>;
     HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(SMEM_BYTES)));
-    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tx, t1, tq, tk, p);
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tx, t1a, t1b, tq, tk, p);
   } else {
     auto kern = ccgqa_pre_tc_kernel<16>;
     HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(SMEM_BYTES)));
-    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tx, t1, tq, tk, p);
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tx, t1a, t1b, tq, tk, p);
   }
   HB_LAUNCH_CHECK();
   return 0;
