@@ -42,7 +42,8 @@ namespace hb200 {
 
 constexpr int AQ = 128;   // query rows per CTA
 constexpr int AK = 128;   // keys per tile
-constexpr int SOFTMAX_WARPS = 8;
+constexpr int CPW = 2;             // 32-key chunks of a tile per softmax warp
+constexpr int SOFTMAX_WARPS = 4 * (4 / CPW);
 constexpr int ATT_THREADS = (2 + SOFTMAX_WARPS) * 32;
 
 template <int HD> struct AttCfg {
@@ -133,7 +134,7 @@ __global__ void __launch_bounds__(ATT_THREADS, (HD <= 32 ? 2 : 1)) attention_tcg
       int s = 0;
       uint32_t ph = 0;
       for (int j = 0; j < n_kt; ++j) {
-        if (!mbar_wait(kv_empty(s), ph ^ 1u, abort_flag)) break;
+        if (!mbar_wait(kv_empty(s), ph ^ 1u, abort_flag, 256u)) break;   // five tiles ahead: no hurry
         mbar_arrive_expect_tx(kv_full(s), 2 * Cfg::KV_BYTES);
         tma_load_3d(base + Cfg::OFF_K + s * Cfg::KV_BYTES, &tma_k, 0, j * AK, b * KV + kvh, kv_full(s));
         tma_load_3d(base + Cfg::OFF_V + s * Cfg::KV_BYTES, &tma_v, 0, j * AK, b * KV + kvh, kv_full(s));
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(ATT_THREADS, (HD <= 32 ? 2 : 1)) attention_tcg
       constexpr uint32_t idesc_s = make_idesc(AQ, AK);          // Q, K both K-major
       constexpr uint32_t idesc_pv = make_idesc_b_mn(AQ, HD);    // P from tensor memory, V MN-major
       constexpr uint32_t idesc_l = make_idesc_b_mn(AQ, 16);     // P x ones -> row sums
-      bool ok = mbar_wait(q_full, 0u, abort_flag);
+      bool ok = mbar_wait(q_full, 0u, abort_flag, 64u);
       const uint64_t dq = make_smem_desc_ex(base, Cfg::SBO, Cfg::LAYOUT, 16);
       const uint64_t dk0 = make_smem_desc_ex(base + Cfg::OFF_K, Cfg::SBO, Cfg::LAYOUT, 16);
       const uint64_t dv0 = make_smem_desc_ex(base + Cfg::OFF_V, Cfg::SBO, Cfg::LAYOUT, Cfg::KV_BYTES);
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(ATT_THREADS, (HD <= 32 ? 2 : 1)) attention_tcg
         for (int k = 0; k < HD / 16; ++k) umma_bf16_elect(tmem_s, dq + 2u * k, dk + 2u * k, idesc_s, k ? 1u : 0u);
         umma_commit_elect(s_full);
       };
-      if (ok && (ok = mbar_wait(kv_full(0), 0u, abort_flag))) {
+      if (ok && (ok = mbar_wait(kv_full(0), 0u, abort_flag, 64u))) {
         tcgen05_fence_after();
         issue_s(0);
       }
@@ -170,12 +171,12 @@ __global__ void __launch_bounds__(ATT_THREADS, (HD <= 32 ? 2 : 1)) attention_tcg
         if (j + 1 < n_kt) {
           // QK^T of the NEXT tile goes out as soon as the softmax warps have pulled S of this tile into registers,
           // so it runs in the shadow of their exponentials
-          if (!mbar_wait(kv_full(sn), phn, abort_flag)) break;
-          if (!mbar_wait(s_free, (uint32_t)(j & 1), abort_flag)) break;
+          if (!mbar_wait(kv_full(sn), phn, abort_flag, 64u)) break;
+          if (!mbar_wait(s_free, (uint32_t)(j & 1), abort_flag, 32u)) break;
           tcgen05_fence_after();
           issue_s(sn);
         }
-        if (!mbar_wait(p_full, (uint32_t)(j & 1), abort_flag)) break;
+        if (!mbar_wait(p_full, (uint32_t)(j & 1), abort_flag, 32u)) break;
         tcgen05_fence_after();
         const uint64_t dvs = dv0 + (uint64_t)((s * Cfg::KV_BYTES) >> 4);
         const uint32_t first = j ? 1u : 0u;
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(ATT_THREADS, (HD <= 32 ? 2 : 1)) attention_tcg
   } else {
     // ------------------------------ softmax warps (2..9): thread = query row, half of the keys ------------------
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;          // keys [64*half, 64*half + 64) of every tile
+    const int part = (warp - 2) >> 2;          // keys [32*CPW*part, +32*CPW) of every tile
     const int r = quad * 32 + lane;            // row inside the tile
     const int qrow = q0 + r;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
@@ -209,32 +210,40 @@ __global__ void __launch_bounds__(ATT_THREADS, (HD <= 32 ? 2 : 1)) attention_tcg
       tcgen05_fence_after();
       const bool diag = (j == n_kt - 1);
       // both 32-column loads of this thread's 64 keys go out before one wait; S is then free for the next QK^T
-      uint32_t sraw[2][32];
-      tmem_ld_32x32_nowait(tmem_s + lane_off + (uint32_t)(half * 64), sraw[0]);
-      tmem_ld_32x32_nowait(tmem_s + lane_off + (uint32_t)(half * 64 + 32), sraw[1]);
+      uint32_t sraw[CPW][32];
+#pragma unroll
+      for (int cc = 0; cc < CPW; ++cc) tmem_ld_32x32_nowait(tmem_s + lane_off + (uint32_t)((part * CPW + cc) * 32), sraw[cc]);
       tmem_wait_ld();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
-      uint32_t packed[32];           // 64 probabilities as bf16 pairs: cell i = keys 2i (low half), 2i+1 (high half)
+      uint32_t packed[CPW * 16];     // probabilities as bf16 pairs: cell i = keys 2i (low half), 2i+1 (high half)
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;
+      for (int cc = 0; cc < CPW; ++cc) {
+        const int c = part * CPW + cc;
         const int key0 = j * AK + c * 32;
-        if (diag && c > quad) {      // every key of these 32 lies after every row of this warp: no exponentials needed
+        // Three separately compiled bodies, chosen by a warp-uniform branch: the common tile carries no mask code at all
+        // (as one loop with the mask predicated in, every tile paid two compares and two selects per pair of scores,
+        // more than the exponentials themselves cost to issue).
+        if (!diag) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sraw[cc][i]), p.scale_log2, -p.bound_log2));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sraw[cc][i + 1]), p.scale_log2, -p.bound_log2));
+            // bf16 by truncation: one byte-permute on the integer pipe instead of a conversion on the special-function
+            // pipe.  The truncation bias cancels: the denominator is summed from the same bf16 values.
+            packed[cc * 16 + (i >> 1)] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
+          }
+        } else if (c > quad) {       // every key of these 32 lies after every row of this warp: no exponentials needed
 #pragma unroll
           for (int i = 0; i < 16; ++i) packed[cc * 16 + i] = 0u;
-        } else {
+        } else {                     // the diagonal tile: causal mask
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             float p0 = ex2_approx(fmaf(__uint_as_float(sraw[cc][i]), p.scale_log2, -p.bound_log2));
             float p1 = ex2_approx(fmaf(__uint_as_float(sraw[cc][i + 1]), p.scale_log2, -p.bound_log2));
-            if (diag) {
-              if (key0 + i > qrow) p0 = 0.f;
-              if (key0 + i + 1 > qrow) p1 = 0.f;
-            }
-            // bf16 by truncation: one byte-permute on the integer pipe instead of a conversion on the (saturated)
-            // special-function pipe.  The truncation bias cancels: the denominator is summed from the same bf16 values.
+            if (key0 + i > qrow) p0 = 0.f;
+            if (key0 + i + 1 > qrow) p1 = 0.f;
             packed[cc * 16 + (i >> 1)] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
           }
         }
@@ -244,7 +253,8 @@ __global__ void __launch_bounds__(ATT_THREADS, (HD <= 32 ? 2 : 1)) attention_tcg
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
-      tmem_st_32x32(tmem_p + lane_off + (uint32_t)(half * 32), packed);
+      if constexpr (CPW == 2) tmem_st_32x32(tmem_p + lane_off + (uint32_t)(part * 32), reinterpret_cast<const uint32_t(&)[32]>(packed));
+      else tmem_st_32x16(tmem_p + lane_off + (uint32_t)(part * 16), packed);
       tmem_wait_st();
       tcgen05_fence_before();
       __syncwarp();
@@ -253,7 +263,7 @@ __global__ void __launch_bounds__(ATT_THREADS, (HD <= 32 ? 2 : 1)) attention_tcg
     // ---- finish: O / l -> bf16, token-major ----
     if (ok && !mbar_wait(o_full, 0u, abort_flag)) ok = false;
     ok = __all_sync(0xffffffffu, ok);
-    if (ok && half == 0) {
+    if (ok && part == 0) {
       tcgen05_fence_after();
       float lsum[16];
       tmem_ld_32x16(tmem_l + lane_off, lsum);     // every column of the ones-MMA holds the row sum

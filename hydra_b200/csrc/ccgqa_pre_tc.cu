@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
       uint32_t phase = 0;
       bool ok = true;
       auto next_stage = [&]() -> uint32_t {      // waits for the next ring slot, returns its address (0 on abort)
-        if (!mbar_wait(w_empty(stage), phase ^ 1u, abort_flag)) { ok = false; return 0u; }
+        if (!mbar_wait(w_empty(stage), phase ^ 1u, abort_flag, 64u)) { ok = false; return 0u; }
         return base + OFF_RING + stage * STAGE_BYTES;
       };
       auto advance = [&]() { if (++stage == STAGES) { stage = 0; phase ^= 1u; } };
@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
       };
       for (int it = 0; ok && it < my_tiles; ++it) {
         const uint32_t tpar = (uint32_t)(it & 1);
-        if (!mbar_wait(xp_full, tpar, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(xp_full, tpar, abort_flag, 32u)) { ok = false; break; }
         tcgen05_fence_after();
         // ---- conv1: five rounds of 64 channels, each head its own M128 x N=hd x K=3*hd contraction ----
         for (int rd = 0; ok && rd < ROUNDS; ++rd) {
@@ -317,8 +317,8 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
         umma_commit_elect(xp_free);              // every conv1 MMA of this tile has read its x planes
         // ---- conv2 ----
         const int pos = ((int)blockIdx.x + it * (int)gridDim.x) % p.tiles_per_seq;   // tile position in its sequence
-        if (!mbar_wait(y1_full, tpar, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(q_free, tpar ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(y1_full, tpar, abort_flag, 32u)) { ok = false; break; }
+        if (!mbar_wait(q_free, tpar ^ 1u, abort_flag, 32u)) { ok = false; break; }
         tcgen05_fence_after();
         for (int i = 0; ok && i < QBLOCKS; ++i) {
           const uint32_t so = wait_stage();
@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
         }
         if (!ok) break;
         umma_commit_elect(q_full);
-        if (!mbar_wait(k_free, tpar ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(k_free, tpar ^ 1u, abort_flag, 32u)) { ok = false; break; }
         tcgen05_fence_after();
         for (int kb = 0; ok && kb < KBLOCKS; ++kb) {
           const uint32_t so = wait_stage();
@@ -444,7 +444,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
         cs[i] = c4.x; cs[i + 1] = c4.y; cs[i + 2] = c4.z; cs[i + 3] = c4.w;
         sn[i] = s4.x; sn[i + 1] = s4.y; sn[i + 2] = s4.z; sn[i + 3] = s4.w;
       }
-      if (!mbar_wait(xp_full, tpar, abort_flag)) ok = false;
+      if (!mbar_wait(xp_full, tpar, abort_flag, 64u)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       // the means come from the x planes while they are in shared memory (x row of output row r is r + 4; rows past
@@ -454,7 +454,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
       if (half == 0) head_mean_planes<HD>(xrow, XP_PLANE, H, qm);
       __syncwarp();
       if (lane == 0) mbar_arrive(xp_free);
-      if (!mbar_wait(q_full, tpar, abort_flag)) ok = false;
+      if (!mbar_wait(q_full, tpar, abort_flag, 64u)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
@@ -473,7 +473,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
       __syncwarp();
       if (lane == 0) mbar_arrive(q_free);
       if (half != 0) continue;
-      if (!mbar_wait(k_full, tpar, abort_flag)) ok = false;
+      if (!mbar_wait(k_full, tpar, abort_flag, 64u)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
@@ -496,7 +496,7 @@ __global__ void __launch_bounds__(pretc::THREADS, 1) ccgqa_pre_tc_kernel(const _
     if (lane == 0) {
       for (int it = 0; it < my_tiles; ++it) {
         // the planes may be overwritten once conv1 of the previous tile and its mean readers are done with them
-        if (it > 0 && !mbar_wait(xp_free, (uint32_t)((it - 1) & 1), abort_flag)) break;
+        if (it > 0 && !mbar_wait(xp_free, (uint32_t)((it - 1) & 1), abort_flag, 256u)) break;
         const int tile = (int)blockIdx.x + it * (int)gridDim.x;
         const int b = tile / p.tiles_per_seq, t0 = (tile % p.tiles_per_seq) * TT;
         mbar_arrive_expect_tx(xp_full, XP_BYTES);

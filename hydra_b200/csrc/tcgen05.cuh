@@ -43,11 +43,17 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 // Bounded wait. Returns false if the wait was abandoned (own time-out or another role's abort).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+// backoff_ns > 0: the warp sleeps that long between polls instead of spinning.  A spinning warp issues an instruction
+// every other clock and takes those issue slots from the warps of its scheduler that do the arithmetic (in the attention
+// kernel two thirds of all issued instructions were polls of the producer and MMA warps); use it wherever the waiter
+// has a few hundred clocks of slack, i.e. everywhere but the innermost dependency of a pipeline.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t backoff_ns = 0u) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns != 0u) __nanosleep(backoff_ns);
     if ((it & 63u) == 0u) {
       if (*abort_flag != 0u) return false;
       if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
@@ -246,6 +252,14 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
         "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
