@@ -23,7 +23,8 @@ EPI_STORE, EPI_RESID, EPI_SWIGLU, EPI_SCATTER_ADD = 0, 1, 2, 3
 class BlockWeights(C.Structure):
     _fields_ = [(n, c_vp) for n in (
         "norm1_w", "norm2_w", "final_norm_w", "w_qkv", "w_o", "w1_qk", "w2_q", "w2_k", "key_temperature",
-        "w_gate_up", "w_down", "mor_w", "mor_b", "rec", "mod_wn", "mod_b")] + [("attn_logit_bound", c_f32)]
+        "w_gate_up", "w_down", "mor_w", "mor_b", "rec", "mod_wn", "mod_b")] + [("attn_logit_bound", c_f32),
+                                                                               ("w_gate_up_n", c_vp), ("gate_up_bias", c_vp)]
 
 
 class Model(C.Structure):

@@ -60,7 +60,7 @@ class PackedBlock:
     """Device tensors of one HydraMoRBlock (kept alive here) and the matching C struct."""
 
     def __init__(self, sd: Dict[str, Tensor], pre: str, device, *, attention_only: bool = False, plain: bool = False,
-                 head_dim: Optional[int] = None):
+                 head_dim: Optional[int] = None, fold_norm: bool = False):
         """plain: a HydraBlock (blocks.py:33-70) - attention and one MLP pass, no routers, no recursion offsets, no exit
         norm; expressed as a one-recursion block with a zero offset."""
         a = pre if attention_only else pre + "attention."
@@ -102,6 +102,20 @@ class PackedBlock:
                 # Linear(norm(x)) = rsqrt(..) * sum x_d * (gain_d * w_d): fold the norm gain into the router weight
                 t["mod_wn"] = (_f32(sd[mk + "weight"], device).reshape(-1) * t["norm2_w"]).contiguous()
                 t["mod_b"] = _f32(sd[mk + "bias"], device).reshape(1)
+        # optional: the pre-MLP norm folded into the first MLP contraction: norm(x + rec; g) W^T = inv_rms * (x W'^T +
+        # rec W'^T) with W' = W diag(g) (rounded to bf16 once, here) and the per-recursion bias rec W'^T in fp32.  With
+        # these the executor contracts the routed rows of the hidden state directly instead of a normalised copy.
+        t["w_gate_up_n"] = t["gate_up_bias"] = None
+        if fold_norm and not attention_only and t["rec"] is not None:
+            wf = _f32(sd[pre + "mlp.gate_up.weight"], device) * t["norm2_w"][None, :]
+            wn = wf.to(torch.bfloat16)
+            F2 = wn.shape[0]
+            orow = torch.arange(F2, device=device)
+            grp, r16 = orow // 16, orow % 16
+            srow = torch.where(r16 < 8, grp * 8 + r16, F2 // 2 + grp * 8 + (r16 - 8))     # interleaved row -> source row
+            t["w_gate_up_n"] = interleave_gate_up(wn, device)
+            t["gate_up_bias"] = (t["rec"] @ wn.float().T)[:, srow].contiguous()            # [R, 2F], interleaved order
+            del wf, wn
         self.tensors = t
         # q is a unit vector and |k| = |key_temperature| after the fused pre-attention kernel (RoPE is a rotation), so
         # |q.k| / sqrt(hd) <= |temperature| / sqrt(hd); 2% slack covers the bf16 rounding of q and k

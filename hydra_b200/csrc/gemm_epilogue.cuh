@@ -18,6 +18,12 @@ struct GemmParams {
   const int32_t* rows;    // SCATTER_ADD target rows
   const int32_t* m_dev;   // optional live row count on the device
   int32_t* err_flag;
+  // tcgen05 kernel only: rows of A gathered through `a_rows` (A row of tile row m = a_rows[m]; A then needs no compact
+  // copy), and the SwiGLU epilogue applied to  row_scale[a_rows[m]] * (acc + col_bias[col])  instead of acc - the
+  // pre-MLP norm folded into the contraction: norm(x + rec) W^T = inv_rms * (x W'^T + rec W'^T) with W' = W diag(gain).
+  const int32_t* a_rows = nullptr;
+  const float* row_scale = nullptr;
+  const float* col_bias = nullptr;
   int32_t* m_hint = nullptr;   // skinny kernel only: the live row count this launch site saw the last time (written by
                                // the kernel, read before the wait on the predecessor): 0 -> no speculative weight prefetch
 };

@@ -14,6 +14,15 @@
 // row count may come from device memory (MoD/MoR compaction), in which case the tile loop bounds are computed
 // in-kernel and no host synchronisation is needed.
 //
+// GATHER variant (the MLP's first contraction behind MoD / MoR routing): A is not a compact matrix but the rows
+// a_rows[0..M) of a larger one.  Four extra warps then fill the A half of every stage themselves - tile row = 8 lanes,
+// 16 bytes each per 64-column block, cp.async into the same 128B-swizzled layout TMA would have written - and the
+// SwiGLU epilogue applies the per-row norm scale and per-column bias, so the normalised rows never exist in memory.
+// A gather thread never waits for its copies: cp.async.mbarrier.arrive.noinc makes the stage's barrier count them in
+// when they land, next to the TMA transaction count of the W half, so all stages stay in flight as with TMA.  The
+// copies are generic-proxy writes; the MMA thread orders them before its tensor-core (async-proxy) reads with a
+// fence.proxy.async after it has acquired the barrier.
+//
 // Every mbarrier wait is bounded (wall-clock limit via %globaltimer): on expiry the CTA raises an abort flag that
 // all roles poll, reports through err_flag, lets copies in flight land, frees its TMEM and returns.
 #include <cuda.h>
@@ -32,6 +41,9 @@ constexpr int GBK = 64;             // K per stage = one 128-byte swizzle span o
 constexpr int GROUP_M_DEFAULT = 16; // m-tiles per rasterisation group (keeps an A panel L2-resident)
 constexpr int EPI_WARPS = 8;        // two per TMEM lane quadrant
 constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;
+constexpr int GATHER_WARPS = 4;     // GATHER variant: 128 threads, 8 lanes per tile row and 64-column block
+constexpr int GEMM_THREADS_GATHER = GEMM_THREADS + GATHER_WARPS * 32;
+
 
 // NSTAGES = 0 selects the default ring depth for the tile width; a shallow ring (2 stages, 128-wide tiles) leaves
 // room for two CTAs per SM, which is what the short-K, epilogue-bound contractions want (o_proj: K = 256).
@@ -63,8 +75,8 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   mt = first_m + in % gm;
 }
 
-template <int BN, int NSTAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_SM)) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
+template <int BN, int NSTAGES, bool GATHER = false>
+__global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_SM)) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                               const __grid_constant__ CUtensorMap tma_b,
                                                               const __grid_constant__ CUtensorMap tma_c,
                                                               const GemmParams p, const int group_m) {
@@ -92,7 +104,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), GATHER ? 1 + GATHER_WARPS * 32 : 1);   // TMA transaction (+ every gather thread)
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < Cfg::ACCS; ++a) {
@@ -120,8 +132,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
-          mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
-          tma_load_2d(sa, &tma_a, kb * GBK, mt * GBM, full_bar(stage));
+          mbar_arrive_expect_tx(full_bar(stage), GATHER ? Cfg::B_BYTES : Cfg::STAGE_BYTES);
+          if constexpr (!GATHER) tma_load_2d(sa, &tma_a, kb * GBK, mt * GBM, full_bar(stage));
 #pragma unroll
           for (int bb = 0; bb < BN / Cfg::B_BOX_ROWS; ++bb)
             tma_load_2d(sa + Cfg::A_BYTES + bb * Cfg::B_BOX_ROWS * GBK * 2, &tma_b, kb * GBK,
@@ -145,6 +157,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
         const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          if constexpr (GATHER) fence_proxy_async_smem();   // the A half was written by cp.async (generic proxy)
           tcgen05_fence_after();
           const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
           const uint64_t da = make_smem_desc(sa);
@@ -168,6 +181,42 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
       }
     }
     __syncwarp();
+  } else if (GATHER && warp >= 2 + EPI_WARPS) {
+    // ------------------------------ A gather warps (10..13) ------------------------------
+    // warp w covers tile rows 32w..32w+31; per 64-column block an instruction copies 4 rows x 128 bytes (8 lanes per
+    // row), eight instructions per block.  Rows past the live count are zero-filled (source size 0).
+    const int gw = warp - (2 + EPI_WARPS);
+    const int sub = lane >> 3, piece = lane & 7;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      int mt, nt;
+      tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
+      const int m_lane = mt * GBM + gw * 32 + lane;
+      const int my_row = m_lane < M ? __ldg(p.a_rows + m_lane) : -1;       // A row of tile row 32*gw + lane
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 96u)) { ok = false; break; }   // sleeps, does not spin
+        const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = i * 4 + sub;                                      // row inside this warp's 32
+          const int src_row = __shfl_sync(0xffffffffu, my_row, rr);
+          const int tr = gw * 32 + rr;                                     // tile row
+          const uint32_t dst = sa + (uint32_t)((tr >> 3) * 1024 + (tr & 7) * 128 + ((piece ^ (tr & 7)) << 4));
+          const int col = kb * GBK + piece * 8;
+          const bool in = src_row >= 0 && col < p.K;
+          const void* src = in ? (const void*)(p.A + (size_t)src_row * p.lda + col) : (const void*)p.A;
+          const int nbytes = in ? 16 : 0;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(nbytes) : "memory");
+        }
+        // arrives on the stage's barrier once this thread's copies above have landed (no increment of the pending
+        // count: the barrier was initialised expecting one such arrival per gather thread)
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(stage)) : "memory");
+        if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+    cp_async16_wait_all();      // nothing of this thread's is still in flight when the CTA tears down
   } else {
     // ------------------------------ epilogue warps (2..9) ------------------------------
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
@@ -185,6 +234,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
       int mt, nt;
       tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
       const int m = mt * GBM + quad * 32 + lane;
+      float row_scale = 1.0f;                    // norm scale of this thread's row (GATHER SwiGLU form)
+      if (p.row_scale != nullptr && m < M) row_scale = __ldg(p.row_scale + __ldg(p.a_rows + m));
       // Read-modify-write epilogues (residual, scatter-add).  The accumulator comes out of TMEM with thread = row, but
       // rows are 2 KB or more apart in memory, so row-per-thread 16-byte accesses would touch 32 partial sectors per
       // request.  Instead the warp's staging box (32 rows x 64 columns, 128B-swizzled) is the meeting point: the old
@@ -228,6 +279,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
           for (int c = 0; c < acc_per_box / 32; ++c) {
             float v[32];
             tmem_ld_32x32(t_row + (uint32_t)(acc0 + c * 32), v);       // warp-collective
+            if (swiglu && p.row_scale != nullptr) {
+              // pre-MLP norm folded in: inv_rms[row] * (acc + bias[col]) is what the activation sees
+              const int col0 = nt * BN + acc0 + c * 32;
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4) {
+                const float4 b4 = (col0 + q4 * 4 < p.N) ? __ldg(reinterpret_cast<const float4*>(p.col_bias + col0 + q4 * 4))
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[q4 * 4 + 0] = row_scale * (v[q4 * 4 + 0] + b4.x);
+                v[q4 * 4 + 1] = row_scale * (v[q4 * 4 + 1] + b4.y);
+                v[q4 * 4 + 2] = row_scale * (v[q4 * 4 + 2] + b4.z);
+                v[q4 * 4 + 3] = row_scale * (v[q4 * 4 + 3] + b4.w);
+              }
+            }
             if (swiglu) {
 #pragma unroll
               for (int h16 = 0; h16 < 2; ++h16) {
@@ -338,11 +402,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_
 }
 
 // ---- host side -----------------------------------------------------------------------------------------------
-template <int BN, int NSTAGES = 0>
+template <int BN, int NSTAGES = 0, bool GATHER = false>
 static int launch_bn(const GemmParams& p, cudaStream_t st) {
   using Cfg = GemmCfg<BN, NSTAGES>;
   CUtensorMap ta, tb, tc;
-  HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, GBM));
+  // (the gathered form never issues a TMA load of A; the map only has to be a valid one)
+  HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)(GATHER ? GBM : p.M), (uint64_t)p.K, (uint64_t)p.lda, GBM));
   HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, Cfg::B_BOX_ROWS));
   if (p.epilogue == EPI_STORE || p.epilogue == EPI_SWIGLU) {
     // output map for the staged TMA-store epilogue: boxes of 32 rows x 64 columns, clipped at [M, n_out]
@@ -351,7 +416,7 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
   } else {
     tc = ta;   // unused by the direct epilogues
   }
-  auto kern = gemm_tcgen05_kernel<BN, NSTAGES>;
+  auto kern = gemm_tcgen05_kernel<BN, NSTAGES, GATHER>;
   HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(Cfg::SMEM_BYTES)));
   const int64_t tiles = (int64_t)ceil_div(p.M, GBM) * ceil_div(p.N, BN);
   const int grid = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * Cfg::CTAS_PER_SM);
@@ -360,12 +425,18 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
   // the group's A panel (group_m x 128 rows x K) must itself stay L2-resident (<= 16 MB).
   int group_m = GROUP_M_DEFAULT;
   if ((size_t)p.N * p.K * 2 > (size_t)48 << 20) group_m = (int)std::max<size_t>(16, std::min<size_t>(64, ((size_t)16 << 20) / ((size_t)GBM * p.K * 2)));
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, tc, p, group_m);
+  kern<<<grid, GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, tc, p, group_m);
   HB_LAUNCH_CHECK();
   return 0;
 }
 
 int launch_gemm_tcgen05(const GemmParams& p, cudaStream_t st) {
+  if (p.a_rows != nullptr) {
+    // gathered A: the MLP's gate_up contraction with the norm folded in
+    HB_REQUIRE(p.epilogue == EPI_SWIGLU && p.row_scale != nullptr && p.col_bias != nullptr && p.K % 8 == 0, HB200_ERR_INVALID,
+               "gemm: gathered A is built for the SwiGLU epilogue with row scale and column bias");
+    return launch_bn<256, 0, true>(p, st);
+  }
   // wide tiles unless N is a small multiple of 128 (qkv projection: 384); the SwiGLU epilogue pairs columns inside
   // 128-column halves of a 256-wide tile and always takes the wide kernel
   // a 384-column projection (qkv of the 8q/2kv and 16q/4kv shapes at latent 256) as one tile per row block: the A

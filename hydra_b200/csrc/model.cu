@@ -13,8 +13,11 @@
 //     s    = MoD router(AdaRMSNorm(cur + rec_r))          mor_score kernel (all tokens, streaming, nothing written
 //                                                         but the scores)
 //     rows = topk(s) AND depth >= r   (or depth >= r)     mod_select / compact_active kernel -> device row list
-//     ug   = AdaRMSNorm(cur[rows] + rec_r)                norm_gather kernel (compact)
-//     act  = silu(ug Wg^T) * (ug Wu^T)                    tcgen05 GEMM, SwiGLU epilogue, device row count
+//     act  = silu(u Wg^T) * (u Wu^T), u = AdaRMSNorm(cur[rows] + rec_r):  tcgen05 GEMM over the routed rows of cur
+//                                                         themselves (gathered by the kernel), norm folded in as
+//                                                         inv_rms[row] * (cur W'^T + rec_r W'^T) in the SwiGLU epilogue;
+//                                                         inv_rms comes from the score pass (or a rows-only pass)
+//        (without the folded weights, static routing, cross-check GEMM: ug = norm_gather(...) then the plain GEMM)
 //     cur[rows] += act Wd^T                               tcgen05 GEMM, scatter-add epilogue
 //   y = RMSNorm(cur)        (the executor's output accumulator equals the final `cur`: a token stops
 //                            changing after its exit recursion, and it exits exactly once)
@@ -68,7 +71,7 @@ __global__ void repack_conv_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfl
 // ---- workspace ----------------------------------------------------------------------------------------------
 struct Workspace {
   __nv_bfloat16 *x0, *x1, *a, *qkv, *q, *k, *v, *o, *cur, *ug, *act, *blend;
-  float *scores, *logits;
+  float *scores, *logits, *inv_rms;
   int32_t *depth, *rows, *sel_idx, *counts, *counts2;
   size_t bytes;
 };
@@ -101,6 +104,7 @@ static Workspace carve(const hb200_model* m, int B, int S, void* base) {
   w.act = (__nv_bfloat16*)take(T * F * 2);
   w.scores = (float*)take(T * 4);
   w.logits = (float*)take(T * 4);
+  w.inv_rms = (float*)take(T * 4);
   w.depth = (int32_t*)take(T * 4);
   w.rows = (int32_t*)take(T * 4);
   w.sel_idx = (int32_t*)take(T * 4);
@@ -259,6 +263,9 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
   const bool has_mod = bw.mod_wn != nullptr;
   const int k = mod_k(S, m->mod_capacity);
   const unsigned row_grid = (unsigned)ceil_div(T, 8);
+  // pre-MLP norm folded into the first MLP contraction (needs the folded weights; not for static routing, whose mixing
+  // step reads the normalised rows, nor for the cross-check GEMM)
+  const bool fold = bw.w_gate_up_n != nullptr && bw.gate_up_bias != nullptr && m->static_routing == 0 && m->gemm_impl == 0;
 
   // attention half
   if (a_in == nullptr) {
@@ -291,16 +298,23 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
     float* scores = (taps && taps->mod_scores) ? taps->mod_scores + ((size_t)bi * R + r) * T : w.scores;
     if (need_router || has_mod) {
       ProfScope ps(m->profile, st, HB200_K_MOR_SCORE, bi, r, T, D, 0);
-#define HB_SCORE(MOD_, ROUTER_)                                                                                   \
-  HB_DISPATCH_NCH(D, mor_score_kernel<NCH, MOD_, ROUTER_><<<(unsigned)ceil_div(T, 8 * SCORE_ROWS), 256, 0, st>>>( \
-                         w.cur, rec, bw.mod_wn, bw.mod_b, bw.mor_w, bw.mor_b, scores, logits,                     \
-                         (force || stat) ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth))
-      if (has_mod && need_router) HB_SCORE(true, true);
-      else if (has_mod) HB_SCORE(true, false);
-      else HB_SCORE(false, true);
+#define HB_SCORE(MOD_, ROUTER_, SS_)                                                                                   \
+  HB_DISPATCH_NCH(D, mor_score_kernel<NCH, MOD_, ROUTER_, SS_><<<(unsigned)ceil_div(T, 8 * SCORE_ROWS), 256, 0, st>>>( \
+                         w.cur, rec, bw.mod_wn, bw.mod_b, bw.mor_w, bw.mor_b, scores, logits,                          \
+                         (force || stat) ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth, w.inv_rms))
+      if (fold) {                                   // the pass over every row also leaves its norm scale
+        if (has_mod && need_router) HB_SCORE(true, true, true);
+        else if (has_mod) HB_SCORE(true, false, true);
+        else HB_SCORE(false, true, true);
+      } else {
+        if (has_mod && need_router) HB_SCORE(true, true, false);
+        else if (has_mod) HB_SCORE(true, false, false);
+        else HB_SCORE(false, true, false);
+      }
 #undef HB_SCORE
       HB_LAUNCH_CHECK();
     }
+    const bool have_scale = fold && (need_router || has_mod);
     if (ds != nullptr && has_mod)   // decode cache: the score of every prompt position, row stride = capacity
       HB_CUDA(cudaMemcpy2DAsync(ds->scores + (((size_t)bi * R + r) * B) * ds->capacity, (size_t)ds->capacity * 4, scores,
                                 (size_t)S * 4, (size_t)S * 4, B, cudaMemcpyDeviceToDevice, st));
@@ -318,14 +332,30 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
       HB_PROPAGATE(launch_compact_active(depth, T, r, w.rows, count, st));
     }
     }
-    {
-      ProfScope ps(m->profile, st, HB200_K_NORM_GATHER, bi, r, T, D, 0);
-      HB_DISPATCH_NCH(D, norm_gather_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, w.rows, count, w.ug, D,
-                                                                           m->norm_eps));
-      HB_LAUNCH_CHECK();
+    if (fold) {
+      if (!have_scale) {                          // no score pass touched the rows: norm scale of the routed rows only
+        ProfScope ps(m->profile, st, HB200_K_NORM_GATHER, bi, r, T, D, 0);
+        HB_DISPATCH_NCH(D, rows_inv_rms_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, rec, w.rows, count, w.inv_rms, D,
+                                                                              m->norm_eps));
+        HB_LAUNCH_CHECK();
+      }
+      ProfScope ps(m->profile, st, HB200_K_GEMM_GATE_UP, bi, r, T, 2 * F, D);
+      GemmParams gp{w.cur, (const __nv_bfloat16*)bw.w_gate_up_n, w.act, T, 2 * F, D, D, D, F, EPI_SWIGLU, nullptr, 1.0f,
+                    nullptr, count, err};
+      gp.a_rows = w.rows;
+      gp.row_scale = w.inv_rms;
+      gp.col_bias = bw.gate_up_bias + (size_t)r * 2 * F;
+      HB_PROPAGATE(launch_gemm_tcgen05(gp, st));
+    } else {
+      {
+        ProfScope ps(m->profile, st, HB200_K_NORM_GATHER, bi, r, T, D, 0);
+        HB_DISPATCH_NCH(D, norm_gather_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, w.rows, count, w.ug, D,
+                                                                             m->norm_eps));
+        HB_LAUNCH_CHECK();
+      }
+      HB_PROPAGATE(gemm(m, HB200_K_GEMM_GATE_UP, bi, r, w.ug, bw.w_gate_up, w.act, T, 2 * F, D, D, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count,
+                        err, st));
     }
-    HB_PROPAGATE(gemm(m, HB200_K_GEMM_GATE_UP, bi, r, w.ug, bw.w_gate_up, w.act, T, 2 * F, D, D, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count,
-                      err, st));
     if (!stat) {
       HB_PROPAGATE(gemm(m, HB200_K_GEMM_DOWN, bi, r, w.act, bw.w_down, w.cur, T, D, F, F, F, D, EPI_SCATTER_ADD, nullptr, 1.0f, w.rows, count,
                         err, st));

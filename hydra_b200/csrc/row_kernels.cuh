@@ -99,15 +99,17 @@ __device__ __forceinline__ void scale_row(const float* __restrict__ w, float r, 
 //   MoD score   s = rsqrt(mean((x+rec)^2) + eps) * sum_d (x_d + rec_d) * wn_d + b,  wn = norm2 gain * MoD weight
 //               (the fp32 value of Linear(AdaRMSNorm(x + rec)) without rounding the normalised row to bf16)
 //   MoR depth   from l = sum_d x_d * mor_w_d + b on the raw row (recursion 0 only)
+//   norm scale  inv_rms = rsqrt(mean((x+rec)^2) + eps) of every row (HAS_SS): what the MLP's first contraction applies
+//               in its epilogue when the pre-MLP norm is folded into it
 constexpr int SCORE_ROWS = 4;
-template <int NCH, bool HAS_MOD, bool HAS_ROUTER>
+template <int NCH, bool HAS_MOD, bool HAS_ROUTER, bool HAS_SS = false>
 __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __restrict__ cur,
                                                         const float* __restrict__ rec, const float* __restrict__ mod_wn,
                                                         const float* __restrict__ mod_b,
                                                         const float* __restrict__ mor_w, const float* __restrict__ mor_b,
                                                         float* __restrict__ scores, float* __restrict__ logits,
                                                         int32_t* __restrict__ depth, int64_t T, int D, float eps,
-                                                        int n_rec, int min_d) {
+                                                        int n_rec, int min_d, float* __restrict__ inv_rms = nullptr) {
   const int lane = threadIdx.x & 31;
   const int64_t row0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * SCORE_ROWS;
   if (row0 >= T) return;
@@ -133,8 +135,10 @@ __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __r
     if (i < D) {
       if (HAS_MOD) {
         const float4 a0 = *reinterpret_cast<const float4*>(mod_wn + i), a1 = *reinterpret_cast<const float4*>(mod_wn + i + 4);
-        const float4 b0 = *reinterpret_cast<const float4*>(rec + i), b1 = *reinterpret_cast<const float4*>(rec + i + 4);
         wn[0] = a0.x; wn[1] = a0.y; wn[2] = a0.z; wn[3] = a0.w; wn[4] = a1.x; wn[5] = a1.y; wn[6] = a1.z; wn[7] = a1.w;
+      }
+      if (HAS_MOD || HAS_SS) {
+        const float4 b0 = *reinterpret_cast<const float4*>(rec + i), b1 = *reinterpret_cast<const float4*>(rec + i + 4);
         rc[0] = b0.x; rc[1] = b0.y; rc[2] = b0.z; rc[3] = b0.w; rc[4] = b1.x; rc[5] = b1.y; rc[6] = b1.z; rc[7] = b1.w;
       }
       if (HAS_ROUTER) {
@@ -148,10 +152,10 @@ __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __r
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float x = (j & 1) ? __uint_as_float(w4[j >> 1] & 0xffff0000u) : __uint_as_float(w4[j >> 1] << 16);
-        if (HAS_MOD) {
+        if (HAS_MOD || HAS_SS) {
           const float xr = x + rc[j];
           ss[r] += xr * xr;
-          dm[r] += xr * wn[j];
+          if (HAS_MOD) dm[r] += xr * wn[j];
         }
         if (HAS_ROUTER) lm[r] += x * wr[j];
       }
@@ -160,13 +164,12 @@ __global__ void __launch_bounds__(256) mor_score_kernel(const __nv_bfloat16* __r
 #pragma unroll
   for (int r = 0; r < SCORE_ROWS; ++r) {
     float s2 = 0.f, d2 = 0.f, l2 = 0.f;
-    if (HAS_MOD) {
-      s2 = warp_sum(ss[r]);
-      d2 = warp_sum(dm[r]);
-    }
+    if (HAS_MOD || HAS_SS) s2 = warp_sum(ss[r]);
+    if (HAS_MOD) d2 = warp_sum(dm[r]);
     if (HAS_ROUTER) l2 = warp_sum(lm[r]);
     if (lane == 0 && row0 + r < T) {
       if (HAS_MOD) scores[row0 + r] = rsqrtf(s2 / (float)D + eps) * d2 + mod_b[0];
+      if (HAS_SS) inv_rms[row0 + r] = rsqrtf(s2 / (float)D + eps);
       if (HAS_ROUTER) {
         const float l = l2 + mor_b[0];
         if (logits != nullptr) logits[row0 + r] = l;
@@ -195,6 +198,23 @@ __global__ void __launch_bounds__(256) norm_gather_kernel(const __nv_bfloat16* _
     const int i = (c * 32 + lane) * 8;
     if (i < D) store_bf16x8(ug + j * D + i, v[c]);
   }
+}
+
+// inv_rms[rows[j]] = rsqrt(mean((cur[rows[j]] + rec)^2) + eps) for j < *count: the norm scale of the rows routed to
+// the MLP in a block without a score pass (one warp per listed row, nothing but 4 bytes written).
+template <int NCH>
+__global__ void __launch_bounds__(256) rows_inv_rms_kernel(const __nv_bfloat16* __restrict__ cur,
+                                                           const float* __restrict__ rec,
+                                                           const int32_t* __restrict__ rows,
+                                                           const int32_t* __restrict__ count,
+                                                           float* __restrict__ inv_rms, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t j = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (j >= *count) return;
+  const int64_t src = rows[j];
+  float v[NCH][8];
+  const float ss = load_row_add<NCH>(cur + src * D, rec, D, lane, v);
+  if (lane == 0) inv_rms[src] = rsqrtf(ss / (float)D + eps);
 }
 
 // y = RMSNorm(src; w1) rounded to bf16 (the block output), z = RMSNorm(y; w2) (the next block's pre-attention norm,

@@ -285,7 +285,11 @@ class HydraB200Model:
                  max_seq_len: int = 2048, mod_capacity: float = 0.5, mor_min_depth: int = 0, adaptive: bool = True,
                  device: str | torch.device = "cuda", norm_eps: float = 1e-6, gemm_impl: int = 0,
                  static_routing_mode: bool = False, mor_rampup_scale: float = 1.0, use_rope: bool = True,
-                 use_qk_norm: bool = True, use_convs: bool = True, use_qk_mean: bool = True, use_value_shift: bool = True):
+                 use_qk_norm: bool = True, use_convs: bool = True, use_qk_mean: bool = True, use_value_shift: bool = True,
+                 fold_norm: bool = False):
+        """fold_norm: fold the pre-MLP norm into the first MLP contraction (``hb200_block_weights.w_gate_up_n``): the
+        routed rows of the hidden state are gathered by the GEMM itself and no normalised copy is written.  Off by
+        default: with the gather done by cp.async the contraction loses more than the copy costs (measured)."""
         dev = torch.device(device)
         if dev.type != "cuda":
             raise RuntimeError("HydraB200Model needs a CUDA device (there is no CPU fallback)")
@@ -317,7 +321,7 @@ class HydraB200Model:
                              (0 if use_convs else _lib.ATTN_NO_CONVS) | (0 if use_qk_mean else _lib.ATTN_NO_QK_MEAN) |
                              (0 if use_value_shift else _lib.ATTN_NO_VALUE_SHIFT))
         with kernels._on(dev):
-            blocks = [PackedBlock(sd, f"layers.{i}.", dev, head_dim=hd) for i in range(nb)]
+            blocks = [PackedBlock(sd, f"layers.{i}.", dev, head_dim=hd, fold_norm=fold_norm) for i in range(nb)]
             self.has_mod = [b.tensors["mod_wn"] is not None for b in blocks]
             self.packed = PackedModel(
                 vocab=V, dim=D, n_rec=R, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=hd, ffn_hidden=F,

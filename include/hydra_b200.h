@@ -249,6 +249,12 @@ typedef struct hb200_block_weights {
   const float* mod_wn;           /* fp32 [D] MoD router weight times the norm2 gain (elementwise), or NULL */
   const float* mod_b;            /* fp32 [1] MoD router bias, or NULL    */
   float attn_logit_bound;        /* HOST value: |key_temperature| / sqrt(head_dim) * 1.02, or 0 if unknown */
+  /* Optional pair that folds the pre-MLP norm into the first MLP contraction (both or neither):
+   *   AdaRMSNorm(x + rec_r; g) W^T  =  inv_rms(x + rec_r) * ( x W'^T + rec_r W'^T ),   W' = W diag(g).
+   * With them the executor contracts the routed rows of the hidden state directly (no normalised copy is written
+   * or re-read) and applies the row scale and the per-recursion column bias in the SwiGLU epilogue. */
+  const void* w_gate_up_n;       /* bf16 [2F, D]: gate_up.weight * norm2 gain (per input column), interleaved as w_gate_up; or NULL */
+  const float* gate_up_bias;     /* fp32 [R, 2F]: rec[r] . w_gate_up_n rows (fp32 sums over the bf16 values), same interleaving; or NULL */
 } hb200_block_weights;
 
 typedef struct hb200_model {

@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_struct_layouts_match_header_sizes():
     from hydra_b200 import _lib
-    assert ctypes.sizeof(_lib.BlockWeights) == 16 * 8 + 8      # 16 pointers + one float, padded
+    assert ctypes.sizeof(_lib.BlockWeights) == 16 * 8 + 8 + 2 * 8      # 16 pointers, one float (padded), 2 pointers
     assert ctypes.sizeof(_lib.Model) == 12 * 4 + 4 * 4 + 7 * 8 + 16  # trailing int32, float, int32 + padding: two slots
     assert ctypes.sizeof(_lib.Taps) == 6 * 8 + 8
     assert ctypes.sizeof(_lib.LaunchRecord) == 24

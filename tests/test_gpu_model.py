@@ -712,3 +712,19 @@ def test_trainer_built_250m_shape():
     assert m.ffn_hidden == 3840 and m.head_dim == 16
     lg, tp = compare_with_oracle(m, w, cfg, ids, label="trainer-built 250M shape")
     assert int(tp.depths.min()) >= 1
+
+
+def test_pre_mlp_norm_folded_into_the_contraction():
+    """fold_norm=True: the MLP's first contraction gathers the routed rows of the hidden state itself and applies the
+    norm as a row scale and a column bias in its epilogue (no normalised copy).  Same routing decisions as the default
+    path (the scores come from the same pass), logits and block outputs against the oracle with the routing replayed."""
+    fx, cfg, w = G.model_fixture("model_hd32.npz")
+    ids = torch.from_numpy(fx["ids"])
+    plain = build(w, cfg)
+    folded = build(w, cfg, fold_norm=True)
+    a = plain(ids.cuda(), taps=True).float().cpu()
+    ta = plain.last_taps
+    lg, tb = compare_with_oracle(folded, w, cfg, ids, label="folded norm")
+    # block 0 sees identical inputs on both paths: its decisions must be identical
+    assert torch.equal(ta.depths[0], tb.depths[0])
+    assert rel_l2(lg, a) < 1e-2
