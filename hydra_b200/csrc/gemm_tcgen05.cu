@@ -101,6 +101,25 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
   const int n_tiles = (p.N + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles;
   const int k_blocks = (p.K + GBK - 1) / GBK;
+  // Work items = tiles, except in the last, partial wave: when the tiles left over after the full waves would occupy at
+  // most half of the CTAs, each of them is split into its two 128-column halves, so that the tail of the launch costs
+  // half a tile time instead of a whole one (the scatter-add contraction of the MLP has 5.4 waves of tiles at the
+  // benchmark's row counts).  Not for the SwiGLU epilogue, whose output boxes pair columns across the whole tile.
+  const int full_items = (total_tiles / (int)gridDim.x) * (int)gridDim.x;
+  const int rem_tiles = total_tiles - full_items;
+  const bool split_tail = BN == 256 && !GATHER && p.epilogue != EPI_SWIGLU && rem_tiles > 0 && 2 * rem_tiles <= (int)gridDim.x;
+  const int total_items = split_tail ? full_items + 2 * rem_tiles : total_tiles;
+  auto item_tile = [&](int w, int& tile, int& col_off, int& ncols) {
+    if (split_tail && w >= full_items) {
+      tile = full_items + ((w - full_items) >> 1);
+      col_off = ((w - full_items) & 1) * 128;
+      ncols = 128;
+    } else {
+      tile = w;
+      col_off = 0;
+      ncols = BN;
+    }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
@@ -126,8 +145,9 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        int mt, nt;
+      for (int w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
+        int tile, col_off, ncols, mt, nt;
+        item_tile(w, tile, col_off, ncols);
         tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -151,7 +171,10 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
       int stage = 0, as = 0;
       uint32_t phase = 0, aphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
+        int tile, col_off, ncols;
+        item_tile(w, tile, col_off, ncols);
+        const uint32_t idesc_w = (ncols == BN) ? idesc : make_idesc(GBM, 128);   // a half tile: N = 128
         if (!mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
@@ -161,11 +184,11 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
           tcgen05_fence_after();
           const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
           const uint64_t da = make_smem_desc(sa);
-          const uint64_t db = make_smem_desc(sa + Cfg::A_BYTES);
+          const uint64_t db = make_smem_desc(sa + Cfg::A_BYTES + (uint32_t)col_off * (GBK * 2));   // W rows col_off..
 #pragma unroll
           for (int k = 0; k < GBK / 16; ++k) {
             // advance 16 elements (32 bytes) along K inside the swizzle span: +2 in 16-byte units
-            umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) ? 1u : 0u);
+            umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc_w, (kb | k) ? 1u : 0u);
             if constexpr (BN > 256) {
               // B rows 256.. start 256 rows x 128 bytes further on; their accumulator columns follow the first 256
               const uint64_t db_tail = make_smem_desc(sa + Cfg::A_BYTES + 256 * GBK * 2);
@@ -190,7 +213,7 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+    for (int tile = blockIdx.x; ok && tile < total_items; tile += gridDim.x) {   // (no split tail in this variant)
       int mt, nt;
       tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
       const int m_lane = mt * GBM + gw * 32 + lane;
@@ -221,7 +244,7 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
     // ------------------------------ epilogue warps (2..9) ------------------------------
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;          // which half of the tile's columns this warp drains
-    constexpr int CHUNKS = BN / 32 / (EPI_WARPS / 4);
+    constexpr int CHUNKS_FULL = BN / 32 / (EPI_WARPS / 4);
     const bool swiglu = (p.epilogue == EPI_SWIGLU);
     const bool tma_store = (p.epilogue == EPI_STORE) || swiglu;
     const bool rmw = !tma_store && (p.N % 8 == 0);   // residual / scatter-add with whole 16-byte pieces
@@ -230,9 +253,12 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
     int as = 0;
     uint32_t aphase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      int mt, nt;
+    for (int w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
+      int tile, col_off, ncols, mt, nt;
+      item_tile(w, tile, col_off, ncols);
       tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
+      const int CHUNKS = (ncols == BN) ? CHUNKS_FULL : 128 / 32 / (EPI_WARPS / 4);   // 32-column chunks this warp drains
+      const int col_base = nt * BN + col_off;                                        // first output column of the item
       const int m = mt * GBM + quad * 32 + lane;
       float row_scale = 1.0f;                    // norm scale of this thread's row (GATHER SwiGLU form)
       if (p.row_scale != nullptr && m < M) row_scale = __ldg(p.row_scale + __ldg(p.a_rows + m));
@@ -242,8 +268,8 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
       // values are fetched with eight lanes per row (whole 128-byte lines, cp.async, issued BEFORE the accumulator
       // wait so the latency hides behind the mainloop), each thread then updates its own row inside the box, and the
       // box leaves again with eight lanes per row.
-      constexpr int RMW_BOXES = CHUNKS * 32 / 64;
-      const int rmw_col0 = nt * BN + half * CHUNKS * 32;
+      const int RMW_BOXES = CHUNKS * 32 / 64;
+      const int rmw_col0 = col_base + half * CHUNKS * 32;
       long long grow = -1;                       // global row this lane's tile row reads / writes, -1 = none
       const __nv_bfloat16* rmw_src = (p.epilogue == EPI_RESID) ? p.resid : p.C;
       auto rmw_fetch = [&](int bx) {
@@ -281,7 +307,7 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
             tmem_ld_32x32(t_row + (uint32_t)(acc0 + c * 32), v);       // warp-collective
             if (swiglu && p.row_scale != nullptr) {
               // pre-MLP norm folded in: inv_rms[row] * (acc + bias[col]) is what the activation sees
-              const int col0 = nt * BN + acc0 + c * 32;
+              const int col0 = col_base + acc0 + c * 32;
 #pragma unroll
               for (int q4 = 0; q4 < 8; ++q4) {
                 const float4 b4 = (col0 + q4 * 4 < p.N) ? __ldg(reinterpret_cast<const float4*>(p.col_bias + col0 + q4 * 4))
@@ -319,7 +345,7 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            const int out_col = swiglu ? (nt * BN + acc0) / 2 : nt * BN + acc0;
+            const int out_col = swiglu ? (col_base + acc0) / 2 : col_base + acc0;
             if (out_col < n_out) {
               tma_store_2d(&tma_c, out_col, mt * GBM + quad * 32, my_box);
               bulk_commit();
@@ -374,7 +400,7 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
         for (int c = half * CHUNKS; c < (half + 1) * CHUNKS; ++c) {
           float v[32];
           tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);   // warp-collective
-          const int col = nt * BN + c * 32;
+          const int col = col_base + c * 32;
           if (m < M && col < p.N) epilogue_row_chunk<32>(p, m, col, v);
         }
       }
