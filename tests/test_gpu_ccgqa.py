@@ -129,6 +129,36 @@ def test_attention_core(L, hd, H, KV, S, bounded):
     assert rel_l2(o, ref) < 5e-3
 
 
+def test_attention_core_keeps_a_non_finite_value_inside_its_own_sequence(L):
+    """S = 100 is not a multiple of the 128-row tile, so the diagonal key tile of every (sequence, kv head) reaches past
+    the sequence.  Those rows are zero-filled by the tensor map ([heads][S][hd], box 1 x 128 x hd), never the next
+    head's rows: with one sequence's V all NaN, every other sequence stays finite and equal to what it computes alone
+    (the reference's batched == solo property, tests/test_paper_compliance.py:640-716)."""
+    g = torch.Generator().manual_seed(3)
+    B, H, KV, S, hd = 3, 8, 2, 100, 32
+    q = bf16_round(torch.nn.functional.normalize(torch.randn(B, H, S, hd, generator=g), dim=-1))
+    k = bf16_round(torch.nn.functional.normalize(torch.randn(B, KV, S, hd, generator=g), dim=-1) * math.sqrt(hd))
+    v = bf16_round(torch.randn(B, KV, S, hd, generator=g))
+
+    def run(vv):
+        o = torch.zeros((B, S, H * hd), dtype=torch.bfloat16, device="cuda")
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        qc, kc, vc = (t.to(torch.bfloat16).cuda().contiguous() for t in (q, k, vv))
+        L.check(L.lib().hb200_attention_causal_gqa(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), B, S, H, KV,
+                                                   hd, 1.0 / math.sqrt(hd), 1.02, err.data_ptr(),
+                                                   torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0
+        return o
+
+    clean = run(v)
+    bad = v.clone()
+    bad[1] = float("nan")
+    got = run(bad)
+    assert torch.isnan(got[1].float()).all()
+    assert torch.equal(got[0], clean[0]) and torch.equal(got[2], clean[2])
+
+
 def test_attention_core_long_sequence_two_kernels_agree(L):
     """S = 8192 (the reference's default max_seq_len; 64 key tiles per query tile) is beyond what the CPU oracle finishes
     in seconds: the tcgen05 kernel (bounded softmax) and the independent mma.sync kernel (online softmax) must agree, the

@@ -300,6 +300,21 @@ def test_prefill_api_from_host_memory():
     assert torch.equal(last.float(), full[:, -1])
 
 
+def test_consecutive_forwards_return_independent_tensors():
+    """As with the reference (hydra/model/framework/model.py:408-506 returns a new tensor per call), a result must not
+    change when the model is called again; only ``reuse_buffer=True`` hands out the model's own logits buffer."""
+    fx, cfg, w = G.model_fixture("model_hd16.npz")
+    m = build(w, cfg)
+    ids = torch.from_numpy(fx["ids"]).cuda()
+    a = m(ids)
+    keep = a.clone()
+    b = m(torch.flip(ids, dims=[1]))
+    assert a.data_ptr() != b.data_ptr() and torch.equal(a, keep) and not torch.equal(a, b)
+    c = m(ids, reuse_buffer=True)
+    d = m(torch.flip(ids, dims=[1]), reuse_buffer=True)
+    assert c.data_ptr() == d.data_ptr() and torch.equal(d, b)
+
+
 def test_errors():
     fx, cfg, w = G.model_fixture("model_hd16.npz")
     m = build(w, cfg)
