@@ -362,7 +362,7 @@ def run_ours(args) -> None:
 
     sd = random_state_dict(seed=SEED, device=dev, **ARCH)
     model = HydraB200Model(sd, n_heads=ARCH["n_heads"], n_kv_heads=ARCH["n_kv_heads"], max_seq_len=SEQ,
-                           mod_capacity=ARCH["mod_capacity"], device=dev)
+                           mod_capacity=ARCH["mod_capacity"], device=dev, fold_norm=args.fold_norm)
     # every rank draws its own sequences (seed offset by rank): a sharded global batch of world*B sequences
     ids_host = torch.randint(0, ARCH["vocab_size"], (B, SEQ),
                              generator=torch.Generator().manual_seed(SEED + 1 + rank)).pin_memory()
@@ -540,6 +540,8 @@ def main() -> None:
                     "to their own configuration: 8 sequences, 64 for decode)")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="weak (default): --batch sequences on every GPU; strong: --batch sequences in total, split over the GPUs")
+    ap.add_argument("--fold-norm", dest="fold_norm", action="store_true",
+                    help="pre-MLP norm folded into the first MLP contraction (rows gathered by the GEMM itself)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the post-timing comparison with the CPU oracle")
     ap.add_argument("--no-extras", action="store_true",
