@@ -29,6 +29,8 @@
 
 #include "gemm_epilogue.cuh"
 #include "row_kernels.cuh"
+#include "row_stream.cuh"
+#include "tma_host.cuh"
 
 namespace hb200 {
 
@@ -266,6 +268,11 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
   // pre-MLP norm folded into the first MLP contraction (needs the folded weights; not for static routing, whose mixing
   // step reads the normalised rows, nor for the cross-check GEMM)
   const bool fold = bw.w_gate_up_n != nullptr && bw.gate_up_bias != nullptr && m->static_routing == 0 && m->gemm_impl == 0;
+  // row kernels in their streaming form (rows staged through shared memory by bulk copies) unless switched off
+  static const bool stream_on = [] {
+    const char* e = getenv("HB200_ROW_STREAM");
+    return e == nullptr || e[0] != '0';
+  }();
 
   // attention half
   if (a_in == nullptr) {
@@ -299,9 +306,22 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
     if (need_router || has_mod) {
       ProfScope ps(m->profile, st, HB200_K_MOR_SCORE, bi, r, T, D, 0);
 #define HB_SCORE(MOD_, ROUTER_, SS_)                                                                                   \
-  HB_DISPATCH_NCH(D, mor_score_kernel<NCH, MOD_, ROUTER_, SS_><<<(unsigned)ceil_div(T, 8 * SCORE_ROWS), 256, 0, st>>>( \
-                         w.cur, rec, bw.mod_wn, bw.mod_b, bw.mor_w, bw.mor_b, scores, logits,                          \
-                         (force || stat) ? nullptr : depth, T, D, m->norm_eps, R, m->min_depth, w.inv_rms))
+  HB_DISPATCH_NCH(D, {                                                                                                 \
+    if (stream_on) {                                                                                                   \
+      using SCfg = StreamCfg<NCH, 3>;                                                                                  \
+      auto kern = mor_score_stream_kernel<NCH, MOD_, ROUTER_, SS_>;                                                    \
+      HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)SCfg::SMEM_BYTES));                                  \
+      const int64_t n_tiles = ceil_div64(T, SCfg::TILE_ROWS);                                                          \
+      const unsigned sgrid = (unsigned)std::min<int64_t>(n_tiles, sm_count());                                         \
+      kern<<<sgrid, STREAM_THREADS, SCfg::SMEM_BYTES, st>>>(                                                           \
+          w.cur, rec, bw.mod_wn, bw.mod_b, bw.mor_w, bw.mor_b, scores, logits, (force || stat) ? nullptr : depth, T, D, \
+          m->norm_eps, R, m->min_depth, w.inv_rms, err);                                                               \
+    } else {                                                                                                           \
+      mor_score_kernel<NCH, MOD_, ROUTER_, SS_><<<(unsigned)ceil_div(T, 8 * SCORE_ROWS), 256, 0, st>>>(                \
+          w.cur, rec, bw.mod_wn, bw.mod_b, bw.mor_w, bw.mor_b, scores, logits, (force || stat) ? nullptr : depth, T, D, \
+          m->norm_eps, R, m->min_depth, w.inv_rms);                                                                    \
+    }                                                                                                                  \
+  })
       if (fold) {                                   // the pass over every row also leaves its norm scale
         if (has_mod && need_router) HB_SCORE(true, true, true);
         else if (has_mod) HB_SCORE(true, false, true);
@@ -349,8 +369,17 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
     } else {
       {
         ProfScope ps(m->profile, st, HB200_K_NORM_GATHER, bi, r, T, D, 0);
-        HB_DISPATCH_NCH(D, norm_gather_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, w.rows, count, w.ug, D,
-                                                                             m->norm_eps));
+        HB_DISPATCH_NCH(D, {
+          if (stream_on) {
+            using SCfg = StreamCfg<NCH, 2>;
+            auto kern = norm_gather_stream_kernel<NCH>;
+            HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)SCfg::SMEM_BYTES));
+            const unsigned sgrid = (unsigned)std::min<int64_t>(ceil_div64(T, SCfg::TILE_ROWS), sm_count());
+            kern<<<sgrid, STREAM_THREADS, SCfg::SMEM_BYTES, st>>>(w.cur, rec, bw.norm2_w, w.rows, count, w.ug, D, m->norm_eps, err);
+          } else {
+            norm_gather_kernel<NCH><<<row_grid, 256, 0, st>>>(w.cur, rec, bw.norm2_w, w.rows, count, w.ug, D, m->norm_eps);
+          }
+        });
         HB_LAUNCH_CHECK();
       }
       HB_PROPAGATE(gemm(m, HB200_K_GEMM_GATE_UP, bi, r, w.ug, bw.w_gate_up, w.act, T, 2 * F, D, D, D, F, EPI_SWIGLU, nullptr, 1.0f, nullptr, count,
@@ -381,8 +410,19 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
   {
     ProfScope ps(m->profile, st, HB200_K_RMS_NORM, bi, R, T, D, 0);
     const __nv_bfloat16* exit_src = (stat && m->adaptive) ? y : w.cur;      // static + depth router: the weighted sum
-    HB_DISPATCH_NCH(D, dual_norm_kernel<NCH><<<row_grid, 256, 0, st>>>(exit_src, bw.final_norm_w, y, next_w,
-                                                                         next_w ? a_next : nullptr, T, D, m->norm_eps));
+    HB_DISPATCH_NCH(D, {
+      if (stream_on) {
+        using SCfg = StreamCfg<NCH, 2>;
+        auto kern = dual_norm_stream_kernel<NCH>;
+        HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)SCfg::SMEM_BYTES));
+        const unsigned sgrid = (unsigned)std::min<int64_t>(ceil_div64(T, SCfg::TILE_ROWS), sm_count());
+        kern<<<sgrid, STREAM_THREADS, SCfg::SMEM_BYTES, st>>>(exit_src, bw.final_norm_w, y, next_w, next_w ? a_next : nullptr,
+                                                             (int64_t)T, D, m->norm_eps, err);
+      } else {
+        dual_norm_kernel<NCH><<<row_grid, 256, 0, st>>>(exit_src, bw.final_norm_w, y, next_w, next_w ? a_next : nullptr, T, D,
+                                                        m->norm_eps);
+      }
+    });
     HB_LAUNCH_CHECK();
   }
   if (taps && taps->block_out)
