@@ -816,8 +816,9 @@ extern "C" int hb200_model_decode_step(const hb200_model* m, const hb200_decode_
              m->n_kv_heads * m->head_dim);
   HB_REQUIRE(decode_attention_smem(m->head_dim, m->n_heads / m->n_kv_heads, ds->capacity) <= 200 * 1024,
              HB200_ERR_UNSUPPORTED, "decode_step: capacity %d needs more shared memory than one CTA has", ds->capacity);
-  const size_t ld = ((size_t)m->vocab + 7) / 8 * 8;
-  HB_REQUIRE(last_logits == nullptr || (size_t)ld_logits == ld, HB200_ERR_INVALID, "decode_step: ld_logits must be %zu", ld);
+  HB_REQUIRE(last_logits == nullptr || (ld_logits >= m->vocab && ld_logits % 8 == 0), HB200_ERR_INVALID,
+             "decode_step: ld_logits must be >= vocab and a multiple of 8");
+  const size_t ld = last_logits ? (size_t)ld_logits : ((size_t)m->vocab + 7) / 8 * 8;
   DecodeWs w = carve_decode(m, B, workspace);
   HB_REQUIRE(workspace_bytes >= w.bytes, HB200_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.bytes);
   cudaStream_t st = (cudaStream_t)stream;

@@ -302,7 +302,8 @@ typedef struct hb200_taps {
 size_t hb200_model_workspace_bytes(const hb200_model* m, int B, int S);
 
 /* HydraModel.forward in eval (model.py:408-506): ids int64 [B,S] -> logits bf16 [B*S, ld_logits]
- * (ld_logits >= vocab, multiple of 8).  `hidden_out` (bf16 [B*S, D], optional) receives the
+ * (ld_logits >= vocab, multiple of 8; a multiple of 64 - rows on 128-byte boundaries - lets the output projection
+ * store whole memory sectors and is what the Python layer uses).  `hidden_out` (bf16 [B*S, D], optional) receives the
  * post-norm hidden state (forward_hidden).  If logits is NULL the output projection is skipped.
  * err_flag: device int32, set non-zero if a bounded in-kernel wait ran out. */
 int hb200_model_forward(const hb200_model* m, const int64_t* ids, int B, int S, void* workspace,
