@@ -237,15 +237,18 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1)
                               int32_t* err_flag) {
   using Cfg = StreamCfg<NCH, 2>;
   extern __shared__ unsigned char stream_smem[];
-  const StreamCtx cx = stream_setup<Cfg>(stream_smem);
   const int64_t n = *count;
-  if (n > 0)
+  // a CTA without a tile (few routed rows: the late recursions) leaves before it sets anything up
+  if ((int64_t)blockIdx.x * Cfg::TILE_ROWS >= n) return;
+  const StreamCtx cx = stream_setup<Cfg>(stream_smem);
+  {
     for (int i = threadIdx.x; i < Cfg::DPAD; i += STREAM_THREADS) {
       const bool in = i < D;
       const int slot = stream_vec_slot(i);
       cx.vec[slot] = in ? rec[i] : 0.f;
       cx.vec[Cfg::DPAD + slot] = in ? w2[i] : 0.f;
     }
+  }
   __syncthreads();
   if ((threadIdx.x >> 5) == STREAM_CONSUMERS) {
     stream_produce<Cfg>(cx, cur, rows, n, D);

@@ -743,3 +743,31 @@ def test_pre_mlp_norm_folded_into_the_contraction():
     # block 0 sees identical inputs on both paths: its decisions must be identical
     assert torch.equal(ta.depths[0], tb.depths[0])
     assert rel_l2(lg, a) < 1e-2
+
+
+def test_streaming_row_kernels_give_the_bits_of_the_register_resident_ones(tmp_path):
+    """The router-score, gather + pre-MLP norm and exit-norm kernels exist in two forms: rows staged through shared
+    memory by bulk copies (the default) and register-resident rows (HB200_ROW_STREAM=0).  Both do the same arithmetic in
+    the same order, so the logits of a model with MoD, MoR and an odd sequence length agree bit for bit.  The switch is
+    read once per process, so the second form runs in a child process."""
+    import os
+    import subprocess
+    import sys
+    fx, cfg, w = G.model_fixture("model_hd32.npz")
+    ids = torch.from_numpy(fx["ids"])
+    here = build(w, cfg)(ids.cuda()).cpu()
+    out = tmp_path / "logits_register_rows.pt"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, torch\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "from tests import golden_io as G\n"
+        "from tests.test_gpu_model import build\n"
+        "fx, cfg, w = G.model_fixture('model_hd32.npz')\n"
+        "ids = torch.from_numpy(fx['ids'])\n"
+        f"torch.save(build(w, cfg)(ids.cuda()).cpu(), {str(out)!r})\n")
+    env = dict(os.environ, HB200_ROW_STREAM="0", HB200_NO_REBUILD="1")
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    there = torch.load(out)
+    assert torch.equal(here, there)
