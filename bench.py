@@ -501,9 +501,9 @@ def run_ours(args) -> None:
         }
         if strong is not None:
             line["strong"] = strong
+        if not args.no_parity:      # rank 0's first sequence, at every N (the other ranks wait at the final barrier)
+            line["parity"] = parity_record(model, ids, timed_seq0, sd)
         if world == 1:
-            if not args.no_parity:
-                line["parity"] = parity_record(model, ids, timed_seq0, sd)
             del timed_seq0
             model._logits = None
             torch.cuda.empty_cache()
