@@ -337,6 +337,11 @@ class HydraB200Model:
         self.ld_logits = (V + 63) // 64 * 64
         self._logits: Optional[Tensor] = None
         self.last_taps: Optional[Taps] = None
+        # forward(reuse_buffer=True) replays a CUDA graph of the launch sequence from the second call of a shape on (the
+        # executor never synchronises with the host: row counts stay on the device); HB200_PREFILL_GRAPH=0 switches it off
+        self.use_graph = os.environ.get("HB200_PREFILL_GRAPH", "1").strip() != "0"
+        self._graphs: Dict[tuple, tuple] = {}
+        self._graph_seen: Dict[tuple, int] = {}
 
     # -- reference-compatible conveniences ----------------------------------------------------------------------
     def eval(self):
@@ -439,12 +444,40 @@ class HydraB200Model:
                                 mlp_rows=tp.mlp_rows.data_ptr(),
                                 block_out=tp.block_out.data_ptr() if tp.block_out is not None else None,
                                 force_routing=1 if forced is not None else 0)
-        with kernels._on(self.device):
-            _lib.check(_lib.lib().hb200_model_forward(
-                C.byref(pm.struct), ids.data_ptr(), B, S, ws.data_ptr(), ws.numel(),
-                out.data_ptr() if out is not None else None, self.ld_logits,
-                hid.data_ptr() if hid is not None else None, C.byref(tstruct) if tstruct is not None else None,
-                pm.err_flag.data_ptr(), kernels._stream(self.device)), "model_forward")
+        def launch(ids_):
+            with kernels._on(self.device):
+                _lib.check(_lib.lib().hb200_model_forward(
+                    C.byref(pm.struct), ids_.data_ptr(), B, S, ws.data_ptr(), ws.numel(),
+                    out.data_ptr() if out is not None else None, self.ld_logits,
+                    hid.data_ptr() if hid is not None else None, C.byref(tstruct) if tstruct is not None else None,
+                    pm.err_flag.data_ptr(), kernels._stream(self.device)), "model_forward")
+
+        graphable = (self.use_graph and logits and reuse_buffer and not hidden and tp is None and
+                     getattr(self, "_profile", None) is None and not torch.cuda.is_current_stream_capturing())
+        if graphable:
+            # the launch sequence of a shape is fixed (no host decision depends on device data), so it is captured
+            # once - after one ordinary call has set the kernels' attributes and sized the buffers - and replayed
+            key = (B, S)
+            entry = self._graphs.get(key)
+            if entry is not None and entry[2:] != (ws.data_ptr(), out.data_ptr()):
+                entry = None                                   # a buffer was re-allocated: the captured pointers are stale
+                self._graphs.pop(key, None)
+            if entry is None and self._graph_seen.get(key, 0) >= 1:
+                static_ids = ids.clone()
+                graph = torch.cuda.CUDAGraph()
+                torch.cuda.current_stream(self.device).synchronize()
+                with torch.cuda.graph(graph):
+                    launch(static_ids)
+                entry = (graph, static_ids, ws.data_ptr(), out.data_ptr())
+                self._graphs[key] = entry
+            if entry is not None:
+                entry[1].copy_(ids)
+                entry[0].replay()
+            else:
+                self._graph_seen[key] = self._graph_seen.get(key, 0) + 1
+                launch(ids)
+        else:
+            launch(ids)
         self.last_taps = tp
         lg = out[:, :self.vocab_size].view(B, S, self.vocab_size) if out is not None else None
         if hidden and logits:
@@ -694,6 +727,9 @@ class HydraB200BaseModel(HydraB200Model):
         self.ld_logits = (V + 63) // 64 * 64
         self._logits = None
         self.last_taps = None
+        self.use_graph = os.environ.get("HB200_PREFILL_GRAPH", "1").strip() != "0"
+        self._graphs = {}
+        self._graph_seen = {}
 
     @staticmethod
     def reference_kwargs(model) -> dict:

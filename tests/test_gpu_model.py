@@ -771,3 +771,25 @@ def test_streaming_row_kernels_give_the_bits_of_the_register_resident_ones(tmp_p
     assert r.returncode == 0, r.stderr[-2000:]
     there = torch.load(out)
     assert torch.equal(here, there)
+
+
+def test_graph_replay_of_the_forward_equals_direct_launches():
+    """forward(reuse_buffer=True) captures the launch sequence of a shape at its second call and replays it from then
+    on (the executor takes no decision on the host that depends on device data).  Replays must give the bits of direct
+    launches for new token ids too, and a different shape in between must not disturb them."""
+    fx, cfg, w = G.model_fixture("model_hd32.npz")
+    m = build(w, cfg)
+    ids = torch.from_numpy(fx["ids"]).cuda()
+    variants = [ids, torch.flip(ids, dims=[1]), torch.roll(ids, 3, dims=1), ids]
+    direct = [m(v).clone() for v in variants]                       # fresh tensors: never graphed
+    for i, v in enumerate(variants):
+        got = m(v, reuse_buffer=True)
+        assert torch.equal(got, direct[i]), f"call {i}"
+        if i == 1:
+            assert (ids.shape[0], ids.shape[1]) in m._graphs        # captured at the second call of the shape
+            other = m(ids[:1, :17].contiguous(), reuse_buffer=True).clone()   # another shape re-sizes the logits buffer
+            assert torch.equal(other, m(ids[:1, :17].contiguous()))
+    m.check_device_errors()
+    # prefill() from pinned host memory goes the same way
+    last = m.prefill(variants[2].cpu().pin_memory())
+    assert torch.equal(last.float(), direct[2][:, -1].float().cpu())
