@@ -28,6 +28,8 @@
 #include <vector>
 
 #include "gemm_epilogue.cuh"
+#include <nvtx3/nvToolsExt.h>
+
 #include "row_kernels.cuh"
 #include "row_stream.cuh"
 #include "tma_host.cuh"
@@ -69,6 +71,20 @@ __global__ void repack_conv_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfl
   const int j = rem / cin, ci = rem % cin;
   o[idx] = w[((size_t)co * cin + ci) * ks + j];
 }
+
+// Named host-side ranges around the stages of a forward (block, attention half, each MLP recursion, output projection)
+// for timeline tools that read NVTX; without such a tool attached the calls return at once.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  NvtxRange(const char* fmt, int a) {
+    char buf[48];
+    snprintf(buf, sizeof(buf), fmt, a);
+    nvtxRangePushA(buf);
+  }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 // ---- workspace ----------------------------------------------------------------------------------------------
 struct Workspace {
@@ -274,13 +290,17 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
     return e == nullptr || e[0] != '0';
   }();
 
+  NvtxRange block_range("hb200 block %d", bi);
   // attention half
   if (a_in == nullptr) {
     ProfScope ps(m->profile, st, HB200_K_RMS_NORM, bi, 0, T, D, 0);
     HB_PROPAGATE(hb200_rms_norm(x, bw.norm1_w, w.a, T, D, m->norm_eps, HB200_BF16, HB200_F32, st));
     a_in = w.a;
   }
-  HB_PROPAGATE(attention_part(m, bi, bw, w, a_in, x, m->residual_scale * m->output_scale, w.cur, B, S, err, st));
+  {
+    NvtxRange r("hb200 attention");
+    HB_PROPAGATE(attention_part(m, bi, bw, w, a_in, x, m->residual_scale * m->output_scale, w.cur, B, S, err, st));
+  }
 
   if (ds != nullptr) HB_PROPAGATE(capture_attention_state(m, bi, w, B, S, ds, st));
 
@@ -300,6 +320,7 @@ static int block_forward(const hb200_model* m, int bi, const __nv_bfloat16* x, c
   }
 
   for (int r = 0; r < R; ++r) {
+    NvtxRange rec_range("hb200 mlp recursion %d", r);
     const float* rec = bw.rec + (size_t)r * D;
     const bool need_router = (r == 0) && m->adaptive;
     float* scores = (taps && taps->mod_scores) ? taps->mod_scores + ((size_t)bi * R + r) * T : w.scores;
@@ -679,9 +700,11 @@ static int run_model(const hb200_model* m, const int64_t* ids, int B, int S, con
                                         ds));
     std::swap(xin, xout);
   }
-  if (logits != nullptr)
+  if (logits != nullptr) {
+    NvtxRange r("hb200 output projection");
     HB_PROPAGATE(gemm(m, HB200_K_GEMM_LM_HEAD, m->n_blocks, 0, hid, output_weight(m), logits, T, m->vocab, D, D, D, ld_logits,
                       EPI_STORE, nullptr, 1.0f, nullptr, nullptr, err_flag, st));
+  }
   return 0;
 }
 
