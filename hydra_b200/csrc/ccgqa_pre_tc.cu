@@ -2,7 +2,7 @@
 //
 //   qkv [B,S,lat+2kvd] (read once)  ->  q [B,H,S,hd], k [B,KV,S,hd], v [B,KV,S,hd]  (written once)
 //
-// Persistent: one CTA per SM walks over tiles of 126 tokens (one sequence each) and keeps four things in flight at
+// Persistent: one CTA per SM walks over tiles of 124 tokens (one sequence each) and keeps four things in flight at
 // once - the input of the NEXT tile on its way from HBM, the two convolutions of the CURRENT tile on the tensor
 // cores, the conv weights streaming from L2, and the epilogue of the PREVIOUS accumulators.
 //
