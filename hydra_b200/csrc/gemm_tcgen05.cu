@@ -10,6 +10,15 @@
 //               asynchronous, clipped at the matrix edge by the tensor map); the residual and scatter-add epilogues
 //               read-modify-write their rows directly with 16-byte accesses.
 //
+// CTA pairs (PAIR; the 256-column tiles of the MLP and vocabulary projections): two CTAs of one cluster share a
+// 256 x 256 tile.  Each stages its own 128 rows of A and HALF of the tile's W rows per K block; CTA 0 issues one
+// tcgen05.mma.cta_group::2 (M = 256) per K step, which reads both CTAs' shared memory and writes each CTA's 128 rows into
+// that CTA's own tensor memory; both CTAs' loads are counted on CTA 0's stage barrier, tcgen05.commit signals the stage
+// and accumulator barriers of both, and the epilogue warps of both report to CTA 0.  A stage is 32 KB instead of 48 KB
+// per SM - a third less shared-memory and L2 traffic per FLOP and six stages instead of four - which measured 5-11 %
+// faster on the down and vocabulary projections (and lets the SMs hold a higher clock under the power cap); the
+// epilogues are per CTA and unchanged.
+//
 // TMEM holds two BN-column accumulators so the epilogue of tile i overlaps the mainloop of tile i+1.  The live
 // row count may come from device memory (MoD/MoR compaction), in which case the tile loop bounds are computed
 // in-kernel and no host synchronisation is needed.
@@ -64,6 +73,25 @@ template <int BN, int NSTAGES = 0> struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + BAR_BYTES + 1024;   // + alignment slack
 };
 
+// CTA pair (cta_group::2): a 256-row x BN tile per pair of CTAs of one cluster.  Each CTA stages its own 128 rows of A
+// and HALF of the tile's W rows per K block (32 KB per stage instead of 48 KB: the tensor cores of both SMs read the W
+// halves from each other's shared memory), which leaves room for six stages.
+template <int BN> struct GemmCfgPair {
+  static constexpr int A_BYTES = GBM * GBK * 2;
+  static constexpr int B_BYTES = (BN / 2) * GBK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int CTAS_PER_SM = 1;
+  static constexpr int ACCS = 2;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int B_BOX_ROWS = BN / 2;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int STORE_BOX_BYTES = 32 * 128;
+  static constexpr int STORE_BYTES = EPI_WARPS * STORE_BOX_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + BAR_BYTES + 1024;
+  static_assert(BN == 256, "the pair kernel is built for 256-column tiles");
+};
+
 // tile index -> (m_tile, n_tile): groups of group_m m-tiles, n outer / m inner inside a group
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int& mt, int& nt) {
   const int per_group = group_m * n_tiles;
@@ -75,12 +103,13 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   mt = first_m + in % gm;
 }
 
-template <int BN, int NSTAGES, bool GATHER = false>
-__global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (GemmCfg<BN, NSTAGES>::CTAS_PER_SM)) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
+template <int BN, int NSTAGES, bool GATHER = false, bool PAIR = false>
+__global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (PAIR ? 1 : GemmCfg<BN, NSTAGES>::CTAS_PER_SM)) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                               const __grid_constant__ CUtensorMap tma_b,
                                                               const __grid_constant__ CUtensorMap tma_c,
                                                               const GemmParams p, const int group_m) {
-  using Cfg = GemmCfg<BN, NSTAGES>;
+  using Cfg = std::conditional_t<PAIR, GemmCfgPair<PAIR ? BN : 256>, GemmCfg<BN, NSTAGES>>;
+  static_assert(!(PAIR && GATHER), "the gathered form is single-CTA");
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (s_addr(smem_dyn) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_dyn + (base - s_addr(smem_dyn));
@@ -97,7 +126,11 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int M = p.m_dev ? min(*p.m_dev, p.M) : p.M;
-  const int m_tiles = (M + GBM - 1) / GBM;
+  // PAIR: the work item is a 256-row tile of the pair; CTA `rank` of the pair owns its rows rank*128 .. rank*128+127
+  const uint32_t rank = PAIR ? cluster_cta_rank() : 0u;
+  const int cta_first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // first work item of this CTA (pair)
+  const int cta_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int m_tiles = PAIR ? (M + 2 * GBM - 1) / (2 * GBM) : (M + GBM - 1) / GBM;
   const int n_tiles = (p.N + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles;
   const int k_blocks = (p.K + GBK - 1) / GBK;
@@ -107,7 +140,7 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
   // benchmark's row counts).  Not for the SwiGLU epilogue, whose output boxes pair columns across the whole tile.
   const int full_items = (total_tiles / (int)gridDim.x) * (int)gridDim.x;
   const int rem_tiles = total_tiles - full_items;
-  const bool split_tail = BN == 256 && !GATHER && p.epilogue != EPI_SWIGLU && rem_tiles > 0 && 2 * rem_tiles <= (int)gridDim.x;
+  const bool split_tail = BN == 256 && !GATHER && !PAIR && p.epilogue != EPI_SWIGLU && rem_tiles > 0 && 2 * rem_tiles <= (int)gridDim.x;
   const int total_items = split_tail ? full_items + 2 * rem_tiles : total_tiles;
   auto item_tile = [&](int w, int& tile, int& col_off, int& ncols) {
     if (split_tail && w >= full_items) {
@@ -123,19 +156,24 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
-      mbar_init(full_bar(s), GATHER ? 1 + GATHER_WARPS * 32 : 1);   // TMA transaction (+ every gather thread)
+      // TMA transaction (+ every gather thread); PAIR: both CTAs' producers arrive on CTA 0's barrier
+      mbar_init(full_bar(s), GATHER ? 1 + GATHER_WARPS * 32 : (PAIR ? 2 : 1));
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < Cfg::ACCS; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), EPI_WARPS);
+      mbar_init(tempty_bar(a), PAIR ? 2 * EPI_WARPS : EPI_WARPS);      // PAIR: the epilogue warps of both CTAs, on CTA 0's
     }
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(s_addr(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+  if (warp == 1) {
+    if constexpr (PAIR) tmem_alloc_pair(s_addr(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+    else tmem_alloc(s_addr(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+  }
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_barrier_all();     // the peer's barriers are initialised before anything signals them
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -145,19 +183,27 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
+      for (int w = cta_first; ok && w < total_items; w += cta_step) {
         int tile, col_off, ncols, mt, nt;
         item_tile(w, tile, col_off, ncols);
         tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
-          mbar_arrive_expect_tx(full_bar(stage), GATHER ? Cfg::B_BYTES : Cfg::STAGE_BYTES);
-          if constexpr (!GATHER) tma_load_2d(sa, &tma_a, kb * GBK, mt * GBM, full_bar(stage));
+          if constexpr (PAIR) {
+            // this CTA's 128 rows of A and its half of the W rows, counted on the barrier of the pair's CTA 0
+            const uint32_t full0 = cluster_map_shared(full_bar(stage), 0u);
+            mbar_arrive_expect_tx_cluster(full0, Cfg::STAGE_BYTES);
+            tma_load_2d_pair(sa, &tma_a, kb * GBK, (2 * mt + (int)rank) * GBM, full0);
+            tma_load_2d_pair(sa + Cfg::A_BYTES, &tma_b, kb * GBK, nt * BN + (int)rank * Cfg::B_BOX_ROWS, full0);
+          } else {
+            mbar_arrive_expect_tx(full_bar(stage), GATHER ? Cfg::B_BYTES : Cfg::STAGE_BYTES);
+            if constexpr (!GATHER) tma_load_2d(sa, &tma_a, kb * GBK, mt * GBM, full_bar(stage));
 #pragma unroll
-          for (int bb = 0; bb < BN / Cfg::B_BOX_ROWS; ++bb)
-            tma_load_2d(sa + Cfg::A_BYTES + bb * Cfg::B_BOX_ROWS * GBK * 2, &tma_b, kb * GBK,
-                        nt * BN + bb * Cfg::B_BOX_ROWS, full_bar(stage));
+            for (int bb = 0; bb < BN / Cfg::B_BOX_ROWS; ++bb)
+              tma_load_2d(sa + Cfg::A_BYTES + bb * Cfg::B_BOX_ROWS * GBK * 2, &tma_b, kb * GBK,
+                          nt * BN + bb * Cfg::B_BOX_ROWS, full_bar(stage));
+          }
           if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -165,13 +211,13 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(GBM, BN > 256 ? 256 : BN);
+    if (lane == 0 && rank == 0u) {                     // PAIR: CTA 0 issues for both
+      constexpr uint32_t idesc = make_idesc(PAIR ? 2 * GBM : GBM, BN > 256 ? 256 : BN);
       constexpr uint32_t idesc_tail = make_idesc(GBM, BN > 256 ? BN - 256 : 16);   // columns beyond one MMA's 256
       int stage = 0, as = 0;
       uint32_t phase = 0, aphase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
+      for (int w = cta_first; ok && w < total_items; w += cta_step) {
         int tile, col_off, ncols;
         item_tile(w, tile, col_off, ncols);
         const uint32_t idesc_w = (ncols == BN) ? idesc : make_idesc(GBM, 128);   // a half tile: N = 128
@@ -188,18 +234,30 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
 #pragma unroll
           for (int k = 0; k < GBK / 16; ++k) {
             // advance 16 elements (32 bytes) along K inside the swizzle span: +2 in 16-byte units
-            umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc_w, (kb | k) ? 1u : 0u);
+            if constexpr (PAIR) umma_bf16_pair(d_tmem, da + 2u * k, db + 2u * k, idesc_w, (kb | k) ? 1u : 0u);
+            else umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc_w, (kb | k) ? 1u : 0u);
             if constexpr (BN > 256) {
               // B rows 256.. start 256 rows x 128 bytes further on; their accumulator columns follow the first 256
               const uint64_t db_tail = make_smem_desc(sa + Cfg::A_BYTES + 256 * GBK * 2);
               umma_bf16(d_tmem + 256u, da + 2u * k, db_tail + 2u * k, idesc_tail, (kb | k) ? 1u : 0u);
             }
           }
-          umma_commit(empty_bar(stage));   // stage reusable once these MMAs have read it
+          // stage reusable once these MMAs have read it (PAIR: in both CTAs)
+          if constexpr (PAIR) {
+            umma_commit_pair(empty_bar(stage));
+            umma_commit_pair(cluster_map_shared(empty_bar(stage), 1u));
+          } else {
+            umma_commit(empty_bar(stage));
+          }
           if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(tfull_bar(as));        // accumulator complete
+        if constexpr (PAIR) {              // accumulator complete, in both CTAs' tensor memory
+          umma_commit_pair(tfull_bar(as));
+          umma_commit_pair(cluster_map_shared(tfull_bar(as), 1u));
+        } else {
+          umma_commit(tfull_bar(as));
+        }
         if (++as == Cfg::ACCS) { as = 0; aphase ^= 1u; }
       }
     }
@@ -253,10 +311,11 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
     int as = 0;
     uint32_t aphase = 0;
     bool ok = true;
-    for (int w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
+    for (int w = cta_first; ok && w < total_items; w += cta_step) {
       int tile, col_off, ncols, mt, nt;
       item_tile(w, tile, col_off, ncols);
       tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
+      if constexpr (PAIR) mt = 2 * mt + (int)rank;     // this CTA's 128 rows of the pair's tile
       const int CHUNKS = (ncols == BN) ? CHUNKS_FULL : 128 / 32 / (EPI_WARPS / 4);   // 32-column chunks this warp drains
       const int col_base = nt * BN + col_off;                                        // first output column of the item
       const int m = mt * GBM + quad * 32 + lane;
@@ -406,7 +465,10 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(as));
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(cluster_map_shared(tempty_bar(as), 0u));
+        else mbar_arrive(tempty_bar(as));
+      }
       if (++as == Cfg::ACCS) { as = 0; aphase ^= 1u; }
     }
     if (lane == 0) bulk_wait0();   // this thread's bulk stores have completed before the CTA may exit
@@ -424,7 +486,14 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
     __syncthreads();
   }
   tcgen05_fence_after();
-  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  if constexpr (PAIR) {
+    // nobody leaves while the peer's tensor core may still read this CTA's shared memory or signal its barriers; every
+    // thread of both CTAs reaches this barrier whatever happened above
+    cluster_barrier_all();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+  } else {
+    if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
 }
 
 // ---- host side -----------------------------------------------------------------------------------------------
@@ -456,7 +525,35 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
   return 0;
 }
 
+// CTA-pair form of the 256-column kernel: clusters of two CTAs, one 256 x 256 tile per pair.
+static int launch_pair(const GemmParams& p, cudaStream_t st) {
+  constexpr int BN = 256;
+  using Cfg = GemmCfgPair<BN>;
+  CUtensorMap ta, tb, tc;
+  HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, GBM));
+  HB_PROPAGATE(make_tmap(&tb, p.W, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.ldw, Cfg::B_BOX_ROWS));
+  if (p.epilogue == EPI_STORE || p.epilogue == EPI_SWIGLU) {
+    const uint64_t n_out = p.epilogue == EPI_SWIGLU ? (uint64_t)p.N / 2 : (uint64_t)p.N;
+    HB_PROPAGATE(make_tmap(&tc, p.C, (uint64_t)p.M, n_out, (uint64_t)p.ldc, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE));
+  } else {
+    tc = ta;
+  }
+  auto kern = gemm_tcgen05_kernel<BN, 0, false, true>;
+  HB_PROPAGATE(ensure_dynamic_smem((const void*)kern, (size_t)(Cfg::SMEM_BYTES)));
+  const int64_t tiles = (int64_t)ceil_div(p.M, 2 * GBM) * ceil_div(p.N, BN);
+  const int pairs = (int)std::min<int64_t>(tiles, (int64_t)(sm_count() / 2));
+  int group_m = GROUP_M_DEFAULT / 2;       // in 256-row tiles
+  if ((size_t)p.N * p.K * 2 > (size_t)48 << 20)
+    group_m = (int)std::max<size_t>(8, std::min<size_t>(32, ((size_t)16 << 20) / ((size_t)2 * GBM * p.K * 2)));
+  return launch_chained(kern, dim3(2 * pairs), dim3(GEMM_THREADS), (size_t)Cfg::SMEM_BYTES, st, false, 2, ta, tb, tc, p, group_m);
+}
+
 int launch_gemm_tcgen05(const GemmParams& p, cudaStream_t st) {
+  // 256-column tiles run as CTA pairs (below) unless HB200_GEMM_PAIR=0 asks for the single-CTA kernel
+  static const bool pair_on = [] {
+    const char* e = getenv("HB200_GEMM_PAIR");
+    return e == nullptr || e[0] != '0';
+  }();
   if (p.a_rows != nullptr) {
     // gathered A: the MLP's gate_up contraction with the norm folded in
     HB_REQUIRE(p.epilogue == EPI_SWIGLU && p.row_scale != nullptr && p.col_bias != nullptr && p.K % 8 == 0, HB200_ERR_INVALID,
@@ -473,6 +570,7 @@ int launch_gemm_tcgen05(const GemmParams& p, cudaStream_t st) {
   // per SM (2 x 256 TMEM columns, 2 x 97 KB of shared memory) and let their epilogues overlap
   if ((p.epilogue == EPI_RESID || p.epilogue == EPI_SCATTER_ADD) && p.K <= 512 && p.N % 128 == 0)
     return launch_bn<128, 2>(p, st);
+  if (pair_on && p.M >= 2 * GBM) return launch_pair(p, st);
   return launch_bn<256>(p, st);
 }
 
