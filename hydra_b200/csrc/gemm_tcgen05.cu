@@ -76,20 +76,23 @@ template <int BN, int NSTAGES = 0> struct GemmCfg {
 // CTA pair (cta_group::2): a 256-row x BN tile per pair of CTAs of one cluster.  Each CTA stages its own 128 rows of A
 // and HALF of the tile's W rows per K block (32 KB per stage instead of 48 KB: the tensor cores of both SMs read the W
 // halves from each other's shared memory), which leaves room for six stages.
+// 384-column tiles (the qkv projection) as a pair: one MMA of N = 256 and one of N = 128 per K step, as in the single-CTA
+// form; a CTA's half of the W rows is then rows [128 rank, +128) of the tile for the first and [256 + 64 rank, +64) for
+// the second, fetched as three boxes of 64 rows.
 template <int BN> struct GemmCfgPair {
   static constexpr int A_BYTES = GBM * GBK * 2;
   static constexpr int B_BYTES = (BN / 2) * GBK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = 6;
+  static constexpr int STAGES = BN == 384 ? 4 : 6;
   static constexpr int CTAS_PER_SM = 1;
-  static constexpr int ACCS = 2;
-  static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int B_BOX_ROWS = BN / 2;
+  static constexpr int ACCS = BN == 384 ? 1 : 2;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int B_BOX_ROWS = BN == 384 ? 64 : BN / 2;
   static constexpr int BAR_BYTES = 256;
   static constexpr int STORE_BOX_BYTES = 32 * 128;
   static constexpr int STORE_BYTES = EPI_WARPS * STORE_BOX_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + BAR_BYTES + 1024;
-  static_assert(BN == 256, "the pair kernel is built for 256-column tiles");
+  static_assert(BN == 256 || BN == 384, "the pair kernel is built for 256- and 384-column tiles");
 };
 
 // tile index -> (m_tile, n_tile): groups of group_m m-tiles, n outer / m inner inside a group
@@ -108,7 +111,7 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
                                                               const __grid_constant__ CUtensorMap tma_b,
                                                               const __grid_constant__ CUtensorMap tma_c,
                                                               const GemmParams p, const int group_m) {
-  using Cfg = std::conditional_t<PAIR, GemmCfgPair<PAIR ? BN : 256>, GemmCfg<BN, NSTAGES>>;
+  using Cfg = std::conditional_t<PAIR, GemmCfgPair<(PAIR && BN == 384) ? 384 : 256>, GemmCfg<BN, NSTAGES>>;
   static_assert(!(PAIR && GATHER), "the gathered form is single-CTA");
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (s_addr(smem_dyn) + 1023u) & ~1023u;
@@ -195,7 +198,14 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
             const uint32_t full0 = cluster_map_shared(full_bar(stage), 0u);
             mbar_arrive_expect_tx_cluster(full0, Cfg::STAGE_BYTES);
             tma_load_2d_pair(sa, &tma_a, kb * GBK, (2 * mt + (int)rank) * GBM, full0);
-            tma_load_2d_pair(sa + Cfg::A_BYTES, &tma_b, kb * GBK, nt * BN + (int)rank * Cfg::B_BOX_ROWS, full0);
+            if constexpr (BN == 384) {
+              const uint32_t sb = sa + Cfg::A_BYTES;
+              tma_load_2d_pair(sb, &tma_b, kb * GBK, nt * BN + (int)rank * 128, full0);
+              tma_load_2d_pair(sb + 64 * GBK * 2, &tma_b, kb * GBK, nt * BN + (int)rank * 128 + 64, full0);
+              tma_load_2d_pair(sb + 128 * GBK * 2, &tma_b, kb * GBK, nt * BN + 256 + (int)rank * 64, full0);
+            } else {
+              tma_load_2d_pair(sa + Cfg::A_BYTES, &tma_b, kb * GBK, nt * BN + (int)rank * Cfg::B_BOX_ROWS, full0);
+            }
           } else {
             mbar_arrive_expect_tx(full_bar(stage), GATHER ? Cfg::B_BYTES : Cfg::STAGE_BYTES);
             if constexpr (!GATHER) tma_load_2d(sa, &tma_a, kb * GBK, mt * GBM, full_bar(stage));
@@ -213,7 +223,7 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0 && rank == 0u) {                     // PAIR: CTA 0 issues for both
       constexpr uint32_t idesc = make_idesc(PAIR ? 2 * GBM : GBM, BN > 256 ? 256 : BN);
-      constexpr uint32_t idesc_tail = make_idesc(GBM, BN > 256 ? BN - 256 : 16);   // columns beyond one MMA's 256
+      constexpr uint32_t idesc_tail = make_idesc(PAIR ? 2 * GBM : GBM, BN > 256 ? BN - 256 : 16);   // columns beyond one MMA's 256
       int stage = 0, as = 0;
       uint32_t phase = 0, aphase = 0;
       bool ok = true;
@@ -238,8 +248,10 @@ __global__ void __launch_bounds__(GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS, (
             else umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc_w, (kb | k) ? 1u : 0u);
             if constexpr (BN > 256) {
               // B rows 256.. start 256 rows x 128 bytes further on; their accumulator columns follow the first 256
-              const uint64_t db_tail = make_smem_desc(sa + Cfg::A_BYTES + 256 * GBK * 2);
-              umma_bf16(d_tmem + 256u, da + 2u * k, db_tail + 2u * k, idesc_tail, (kb | k) ? 1u : 0u);
+              // (PAIR: this CTA's share of those rows follows its 128 rows of the first MMA)
+              const uint64_t db_tail = make_smem_desc(sa + Cfg::A_BYTES + (PAIR ? 128 : 256) * GBK * 2);
+              if constexpr (PAIR) umma_bf16_pair(d_tmem + 256u, da + 2u * k, db_tail + 2u * k, idesc_tail, (kb | k) ? 1u : 0u);
+              else umma_bf16(d_tmem + 256u, da + 2u * k, db_tail + 2u * k, idesc_tail, (kb | k) ? 1u : 0u);
             }
           }
           // stage reusable once these MMAs have read it (PAIR: in both CTAs)
@@ -526,8 +538,8 @@ static int launch_bn(const GemmParams& p, cudaStream_t st) {
 }
 
 // CTA-pair form of the 256-column kernel: clusters of two CTAs, one 256 x 256 tile per pair.
+template <int BN>
 static int launch_pair(const GemmParams& p, cudaStream_t st) {
-  constexpr int BN = 256;
   using Cfg = GemmCfgPair<BN>;
   CUtensorMap ta, tb, tc;
   HB_PROPAGATE(make_tmap(&ta, p.A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.lda, GBM));
@@ -564,13 +576,13 @@ int launch_gemm_tcgen05(const GemmParams& p, cudaStream_t st) {
   // 128-column halves of a 256-wide tile and always takes the wide kernel
   // a 384-column projection (qkv of the 8q/2kv and 16q/4kv shapes at latent 256) as one tile per row block: the A
   // panel is fetched once instead of once per 128-column tile
-  if (p.epilogue == EPI_STORE && p.N == 384) return launch_bn<384>(p, st);
+  if (p.epilogue == EPI_STORE && p.N == 384) return (pair_on && p.M >= 2 * GBM) ? launch_pair<384>(p, st) : launch_bn<384>(p, st);
   if (p.epilogue != EPI_SWIGLU && p.N % 256 != 0 && p.N % 128 == 0 && p.N <= 1024) return launch_bn<128>(p, st);
   // short K with a read-modify-write epilogue (o_proj + residual): the epilogue dominates, so run two narrower CTAs
   // per SM (2 x 256 TMEM columns, 2 x 97 KB of shared memory) and let their epilogues overlap
   if ((p.epilogue == EPI_RESID || p.epilogue == EPI_SCATTER_ADD) && p.K <= 512 && p.N % 128 == 0)
     return launch_bn<128, 2>(p, st);
-  if (pair_on && p.M >= 2 * GBM) return launch_pair(p, st);
+  if (pair_on && p.M >= 2 * GBM) return launch_pair<256>(p, st);
   return launch_bn<256>(p, st);
 }
 
