@@ -469,6 +469,8 @@ class HydraB200Model:
                 with torch.cuda.graph(graph):
                     launch(static_ids)
                 entry = (graph, static_ids, ws.data_ptr(), out.data_ptr())
+                while len(self._graphs) >= 8:                   # a handful of shapes at most: drop the oldest capture
+                    self._graphs.pop(next(iter(self._graphs)))
                 self._graphs[key] = entry
             if entry is not None:
                 entry[1].copy_(ids)
