@@ -234,3 +234,46 @@ def test_skinny_argument_errors(L):
     A, W = rnd(513, 64), rnd(128, 64)
     with pytest.raises(L.Hb200Error):
         skinny(L, A, W)                                # more than four 128-row tiles
+
+
+def _pair_cases(L):
+    """Outputs of the shapes that run as CTA pairs (256- and 384-column tiles, >= 256 rows), every epilogue, odd row and
+    column counts, a device-side row count: a dict of CPU tensors."""
+    out = {}
+    for (M, N, K) in [(513, 1024, 2816), (2048, 5632, 1024), (1000, 384, 1024), (300, 1000, 192), (777, 50257, 256)]:
+        A, W = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=0.05)
+        out[f"store {M}x{N}x{K}"] = gemm(L, A, W).cpu()
+    A, W = rnd(1300, 1024, seed=3), rnd(2 * 2816, 1024, seed=4, scale=0.05)
+    out["swiglu"] = gemm(L, A, W, epi=L.EPI_SWIGLU).cpu()
+    A, W = rnd(900, 2816, seed=5), rnd(1024, 2816, seed=6, scale=0.05)
+    cur = rnd(4000, 1024, seed=7)
+    rows = torch.randperm(4000, generator=torch.Generator().manual_seed(8))[:900].to(torch.int32).cuda()
+    m_dev = torch.tensor([700], dtype=torch.int32, device="cuda")
+    out["scatter"] = gemm(L, A, W, epi=L.EPI_SCATTER_ADD, rows=rows, m_dev=m_dev, C_out=cur.clone()).cpu()
+    out["resid"] = gemm(L, rnd(640, 256, seed=9), rnd(768, 256, seed=10, scale=0.05), epi=L.EPI_RESID,
+                        resid=rnd(640, 768, seed=11), alpha=0.5).cpu()
+    return out
+
+
+def test_cta_pair_form_gives_the_bits_of_the_single_cta_form(L, tmp_path):
+    """256- and 384-column tiles run as CTA pairs (tcgen05.mma.cta_group::2) unless HB200_GEMM_PAIR=0.  Both forms add the
+    same products in the same order, so their outputs agree bit for bit.  The switch is read once per process, so the
+    single-CTA form runs in a child process."""
+    import os
+    import subprocess
+    import sys
+    here = _pair_cases(L)
+    out = tmp_path / "single_cta.pt"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import sys, torch\n"
+            f"sys.path.insert(0, {root!r})\n"
+            "from hydra_b200 import _lib\n"
+            "from tests.test_gpu_gemm import _pair_cases\n"
+            f"torch.save(_pair_cases(_lib), {str(out)!r})\n")
+    env = dict(os.environ, HB200_GEMM_PAIR="0", HB200_NO_REBUILD="1")
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    there = torch.load(out)
+    assert set(here) == set(there)
+    for k in here:
+        assert torch.equal(here[k], there[k]), k
